@@ -1,0 +1,175 @@
+/*
+ * common.h -- shared declarations of the host runtime behind accb200.h.
+ *
+ * The runtime is the C++ counterpart of accelerate-cuda's Haskell host code:
+ * State/Context (Data/Array/Accelerate/CUDA/State.hs, Context.hs), the memory
+ * table (Array/Remote.hs, Array/Prim.hs), the kernel table (Compile.hs,
+ * Persistent.hs), launch analysis (Analysis/Launch.hs) and the per-skeleton
+ * drivers of Execute.hs.
+ */
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <future>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../../include/accb200.h"
+#include "../cubits/accb_params.h"
+#include "memtable.h"
+
+namespace accb_rt {
+
+/* ---- driver API, resolved at run time so that the library loads (and its
+ * symbol table can be inspected) on a machine without libcuda ---- */
+struct Driver {
+    bool ok = false;
+    std::string why;
+    CUresult (*ModuleLoadData)(CUmodule *, const void *) = nullptr;
+    CUresult (*ModuleUnload)(CUmodule) = nullptr;
+    CUresult (*ModuleGetFunction)(CUfunction *, CUmodule, const char *) = nullptr;
+    CUresult (*ModuleGetGlobal)(CUdeviceptr *, size_t *, CUmodule, const char *) = nullptr;
+    CUresult (*FuncGetAttribute)(int *, CUfunction_attribute, CUfunction) = nullptr;
+    CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+    CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int *, CUfunction, int, size_t) = nullptr;
+    CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
+                             CUstream, void **, void **) = nullptr;
+    CUresult (*CtxPushCurrent)(CUcontext) = nullptr;
+    CUresult (*CtxPopCurrent)(CUcontext *) = nullptr;
+    CUresult (*GetErrorString)(CUresult, const char **) = nullptr;
+    CUresult (*MemcpyDtoH)(void *, CUdeviceptr, size_t) = nullptr;
+};
+const Driver &driver();
+
+/* ---- kernel table ---- */
+struct SkeletonDesc {
+    const char *name;     /* C-ABI name */
+    const char *header;   /* file under skeletons/ */
+    const char *macro;    /* instantiation macro */
+    int id;
+};
+enum SkeletonId { SK_MAP = 1, SK_FOLD_ALL, SK_FOLD_DIM, SK_FOLD_SEG, SK_SCAN, SK_PERMUTE, SK_PERMUTE_SMEM,
+                  SK_STENCIL, SK_STENCIL2 };
+const SkeletonDesc *find_skeleton(const char *name);
+
+struct CompileResult {
+    int status = ACCB_OK;
+    std::string log;
+    std::string cubin; /* bytes */
+    int source = 0;    /* 1 memory, 2 disk, 3 compiled */
+};
+
+struct KernelMeta {
+    int v[8] = {0};
+};
+
+struct LoadedModule {
+    CUmodule mod = nullptr;
+    KernelMeta meta;
+    std::unordered_map<std::string, CUfunction> fn;
+};
+
+}  // namespace accb_rt
+
+struct accb_kernel {
+    std::string key;  /* hex hash */
+    int skeleton = 0;
+    std::shared_future<accb_rt::CompileResult> result;
+    std::mutex mu;
+    std::map<accb_context *, accb_rt::LoadedModule> loaded; /* one module per context */
+    std::atomic<int> refs{1};
+};
+
+struct accb_event {
+    cudaEvent_t ev = nullptr;
+};
+
+namespace accb_rt {
+
+struct StreamScratch {
+    void *status = nullptr;       /* scan tile status */
+    size_t status_bytes = 0;
+    int status_layout = 0;        /* bytes per tile record of the last scan */
+    void *partial = nullptr;      /* fold partials */
+    size_t partial_bytes = 0;
+    unsigned *words = nullptr;    /* [0] fold ticket, [1] scan ticket, [2] error word */
+    unsigned scan_ticket = 0;     /* host mirror of words[1] */
+    unsigned epoch = 0;
+};
+
+struct CudaAllocator : DeviceAllocator {
+    void *alloc(size_t bytes) override;
+    void release(void *p) override;
+    bool copy_to_host(void *host, const void *dev, size_t bytes) override;
+};
+
+}  // namespace accb_rt
+
+struct accb_context {
+    int device = 0;
+    CUcontext foreign = nullptr; /* non-null: a context the caller owns */
+    int sm_count = 0, cc_major = 0, cc_minor = 0;
+    size_t total_mem = 0;
+    std::recursive_mutex mu;
+    std::string last_error;
+    accb_rt::CudaAllocator allocator;
+    accb_rt::MemTable mem{&allocator};
+    std::vector<cudaStream_t> stream_pool;     /* idle streams (reservoir) */
+    std::vector<cudaEvent_t> event_pool;       /* idle events */
+    std::map<cudaStream_t, accb_rt::StreamScratch> scratch;
+    void *l2_flush = nullptr;
+    size_t l2_flush_bytes = 0;
+    unsigned long long launches = 0;
+    size_t mem_hits = 0, disk_hits = 0, compiles = 0;
+    bool trace_exec = false, trace_gc = false, trace_cc = false;
+};
+
+namespace accb_rt {
+
+/* makes the context's device (or foreign CUcontext) current for a scope */
+struct CtxGuard {
+    accb_context *c;
+    bool pushed = false;
+    explicit CtxGuard(accb_context *ctx);
+    ~CtxGuard();
+};
+
+int fail(accb_context *ctx, int code, const char *fmt, ...);
+int check_cuda(accb_context *ctx, cudaError_t e, const char *what);
+int check_cu(accb_context *ctx, CUresult e, const char *what);
+void set_global_error(const std::string &s);
+
+StreamScratch *scratch_for(accb_context *ctx, cudaStream_t s);
+
+/* kernel cache */
+std::string cache_key(const SkeletonDesc *sk, const char *src, const char *name, const char *flags);
+std::string make_source(const SkeletonDesc *sk, const char *src, const char *name);
+CompileResult compile_or_load(const std::string &key, const std::string &source, const char *flags,
+                              const char *cache_dir_override);
+std::string default_cache_dir();
+std::string preseed_cache_dir();
+std::string include_dir();
+bool trace_enabled(const char *family);
+
+/* launching */
+int get_function(accb_context *ctx, accb_kernel *k, const char *entry, CUfunction *fn, KernelMeta *meta);
+int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blocks_per_sm);
+int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, size_t smem,
+           cudaStream_t stream, const accb_kparams &p);
+
+/* host fault injection: ACCB_FAIL=<site>[:N] makes the N-th call at <site>
+ * fail (sites: malloc, nvcc, cache_io) */
+bool inject_failure(const char *site);
+
+}  // namespace accb_rt

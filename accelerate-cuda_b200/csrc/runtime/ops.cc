@@ -1,0 +1,494 @@
+/*
+ * ops.cc -- launch analysis and the per-skeleton host drivers.
+ *
+ * Replaces Data/Array/Accelerate/CUDA/Analysis/Launch.hs:42-172 (block size,
+ * grid size, shared memory) and the drivers executeOp, foldCore/foldRec,
+ * foldSegOp, scanOp/scan1Op/scan'Op/scanCore, permuteOp, stencilOp and
+ * stencil2Op of Data/Array/Accelerate/CUDA/Execute.hs:264-450 with the
+ * marshalling and launch code of Execute.hs:823-982.
+ *
+ * Launch policy.  The reference picks the block size from an occupancy
+ * search and caps the grid at SMs x resident blocks (Launch.hs:42-55) with one
+ * element per thread per trip.  Here the block size is fixed by each skeleton
+ * (it fixes the tile shape), the grid is SMs x resident blocks for the
+ * persistent kernels (map, folds, permute) and one block per tile for the
+ * ticketed scan and the stencil, and the resident-block count comes from the
+ * driver's occupancy calculator for the compiled kernel.
+ */
+#include <algorithm>
+#include <cstdlib>
+
+#include "common.h"
+
+namespace accb_rt {
+
+int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blocks_per_sm) {
+    int n = 0;
+    int st = check_cu(ctx, driver().OccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, block, smem),
+                      "cuOccupancyMaxActiveBlocksPerMultiprocessor");
+    if (st != ACCB_OK) return st;
+    *blocks_per_sm = std::max(1, n);
+    return ACCB_OK;
+}
+
+int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, size_t smem, cudaStream_t stream,
+           const accb_kparams &p) {
+    void *args[] = {const_cast<accb_kparams *>(&p)};
+    if (ctx->trace_exec)
+        fprintf(stderr, "[accb exec] %s<<<%d,%d,%zu>>> n=%lld\n", name, grid, block, smem, p.n);
+    int st = check_cu(ctx, driver().LaunchKernel(fn, (unsigned)grid, 1, 1, (unsigned)block, 1, 1, (unsigned)smem,
+                                                 (CUstream)stream, args, nullptr),
+                      name);
+    if (st == ACCB_OK) ctx->launches++;
+    return st;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+/* environment arrays -> slots, shapes, alignment flag */
+static int fill_env(accb_context *ctx, accb_kparams &p, const accb_array *env, int nenv) {
+    if (nenv < 0 || nenv > ACCB_MAX_ARR) return fail(ctx, ACCB_EINVAL, "too many environment arrays (%d)", nenv);
+    if (nenv > 0 && !env) return fail(ctx, ACCB_EINVAL, "null environment");
+    int slot = 0;
+    bool vec = true;
+    for (int a = 0; a < nenv; ++a) {
+        if (env[a].rank < 0 || env[a].rank > ACCB_MAX_RANK || env[a].ncomp < 0 || env[a].ncomp > ACCB_ARRAY_MAX_COMP)
+            return fail(ctx, ACCB_EINVAL, "environment array %d: bad rank or component count", a);
+        p.in_first[a] = slot;
+        for (int d = 0; d < env[a].rank; ++d) p.in_shape[a][d] = env[a].shape[d];
+        for (int c = 0; c < env[a].ncomp; ++c) {
+            if (slot >= ACCB_MAX_IN) return fail(ctx, ACCB_EINVAL, "more than %d input components", ACCB_MAX_IN);
+            p.in[slot++] = env[a].ptr[c];
+            vec = vec && aligned16(env[a].ptr[c]);
+        }
+    }
+    if (vec) p.flags |= ACCB_F_VEC;
+    return ACCB_OK;
+}
+
+static int fill_out(accb_context *ctx, accb_kparams &p, const accb_array *out, int first_slot = 0) {
+    if (!out) return fail(ctx, ACCB_EINVAL, "null output array");
+    if (out->ncomp < 1 || first_slot + out->ncomp > ACCB_MAX_OUT)
+        return fail(ctx, ACCB_EINVAL, "bad output component count %d", out->ncomp);
+    for (int c = 0; c < out->ncomp; ++c) {
+        if (!out->ptr[c]) return fail(ctx, ACCB_EINVAL, "null output pointer");
+        p.out[first_slot + c] = out->ptr[c];
+        if (first_slot == 0 && !aligned16(out->ptr[c])) p.flags &= ~ACCB_F_VEC;
+    }
+    if (first_slot == 0)
+        for (int d = 0; d < out->rank && d < ACCB_MAX_RANK; ++d) p.out_shape[d] = out->shape[d];
+    return ACCB_OK;
+}
+
+static long long array_size(const accb_array *a) {
+    long long n = 1;
+    for (int d = 0; d < a->rank; ++d) n *= a->shape[d];
+    return n;
+}
+
+static int fill_scalars(accb_context *ctx, accb_kparams &p, const void *s, size_t bytes) {
+    if (bytes > ACCB_SCALAR_BYTES) return fail(ctx, ACCB_EINVAL, "scalar block of %zu bytes exceeds %d", bytes, ACCB_SCALAR_BYTES);
+    if (bytes && !s) return fail(ctx, ACCB_EINVAL, "null scalar block");
+    if (bytes) memcpy(p.scalars, s, bytes);
+    return ACCB_OK;
+}
+
+static int grow(accb_context *ctx, void **buf, size_t *have, size_t want, cudaStream_t stream, bool zero) {
+    if (*have >= want) return ACCB_OK;
+    /* the old buffer may still be read by work enqueued earlier on this stream */
+    int st = check_cuda(ctx, cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    if (st != ACCB_OK) return st;
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr;
+    *have = 0;
+    const size_t bytes = std::max(want, (size_t)1 << 20);
+    void *p = ctx->mem.alloc_raw(bytes);
+    if (!p) return fail(ctx, ACCB_ENOMEM, "device out of memory allocating %zu bytes of scratch", bytes);
+    *buf = p;
+    *have = bytes;
+    if (zero) return check_cuda(ctx, cudaMemsetAsync(p, 0, bytes, stream), "cudaMemsetAsync");
+    return ACCB_OK;
+}
+
+struct Prep {
+    CUfunction fn = nullptr;
+    KernelMeta meta;
+    int block = 0;
+    int per_sm = 1;
+};
+
+static int prepare(accb_context *ctx, accb_kernel *k, const char *entry, size_t smem, Prep *pr) {
+    if (!k) return fail(ctx, ACCB_EINVAL, "null kernel");
+    int st = get_function(ctx, k, entry, &pr->fn, &pr->meta);
+    if (st != ACCB_OK) return st;
+    pr->block = pr->meta.v[1];
+    if (pr->block <= 0) return fail(ctx, ACCB_EINVAL, "kernel %s carries no launch metadata", k->key.c_str());
+    return occupancy(ctx, pr->fn, pr->block, smem, &pr->per_sm);
+}
+
+static int check_skeleton(accb_context *ctx, accb_kernel *k, std::initializer_list<int> ids, const char *what) {
+    if (!k) return fail(ctx, ACCB_EINVAL, "null kernel");
+    for (int id : ids)
+        if (k->skeleton == id) return ACCB_OK;
+    return fail(ctx, ACCB_EINVAL, "kernel %s was not built for the %s skeleton", k->key.c_str(), what);
+}
+
+static long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
+
+}  // namespace accb_rt
+
+using namespace accb_rt;
+
+#define LOCK(ctx)                                                   \
+    if (!(ctx)) return fail(nullptr, ACCB_EINVAL, "null context"); \
+    std::lock_guard<std::recursive_mutex> lock_((ctx)->mu);         \
+    CtxGuard guard_(ctx)
+#define TRY(expr)                     \
+    do {                              \
+        int st_ = (expr);             \
+        if (st_ != ACCB_OK) return st_; \
+    } while (0)
+
+extern "C" {
+
+int accb_launch_count(accb_context *ctx, unsigned long long *launches) {
+    LOCK(ctx);
+    if (launches) *launches = ctx->launches;
+    return ACCB_OK;
+}
+
+int accb_launch_config(accb_context *ctx, accb_kernel *k, const char *entry, long long n, int *block, int *grid,
+                       int *dynamic_smem) {
+    LOCK(ctx);
+    Prep pr;
+    TRY(prepare(ctx, k, entry, 0, &pr));
+    const long long per_block = (long long)pr.block * std::max(1, pr.meta.v[4]) * 4;
+    const long long units = std::max(1LL, ceil_div(n, per_block));
+    if (block) *block = pr.block;
+    if (grid) *grid = (int)std::min<long long>(units, (long long)ctx->sm_count * pr.per_sm);
+    if (dynamic_smem) *dynamic_smem = 0;
+    return ACCB_OK;
+}
+
+/* ------------------------------------------------------------------ map */
+int accb_map(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+             const void *scalars, size_t scalar_bytes, const accb_array *out) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_MAP}, "map"));
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    TRY(fill_env(ctx, p, env, nenv));
+    TRY(fill_out(ctx, p, out));
+    TRY(fill_scalars(ctx, p, scalars, scalar_bytes));
+    p.n = array_size(out);
+    if (p.n == 0) return ACCB_OK;
+    Prep pr;
+    TRY(prepare(ctx, k, "map", 0, &pr));
+    const long long units = ceil_div(p.n, (long long)pr.block * pr.meta.v[4] * 4);
+    const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * pr.per_sm);
+    return launch(ctx, pr.fn, "map", grid, pr.block, 0, (cudaStream_t)stream, p);
+}
+
+/* ---------------------------------------------------------------- folds */
+static int set_seed(accb_context *ctx, accb_kparams &p, const void *seed, size_t seed_bytes) {
+    if (!seed) return ACCB_OK;
+    TRY(fill_scalars(ctx, p, seed, seed_bytes));
+    p.flags |= ACCB_F_HAS_SEED;
+    return ACCB_OK;
+}
+
+int accb_fold_all(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                  long long n, const void *seed, size_t seed_bytes, const accb_array *out) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_FOLD_ALL}, "fold_all"));
+    if (n < 0) return fail(ctx, ACCB_EINVAL, "negative size");
+    if (n == 0 && !seed) return fail(ctx, ACCB_EBOUNDS, "fold1: empty array");
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    TRY(fill_env(ctx, p, env, nenv));
+    TRY(fill_out(ctx, p, out));
+    TRY(set_seed(ctx, p, seed, seed_bytes));
+    p.n = n;
+    Prep pr;
+    TRY(prepare(ctx, k, "foldAll", 0, &pr));
+    const long long quantum = (long long)pr.block * pr.meta.v[4] * 4;
+    const int grid = (int)std::min<long long>(std::max(1LL, ceil_div(n, quantum)), (long long)ctx->sm_count * pr.per_sm);
+    cudaStream_t s = (cudaStream_t)stream;
+    StreamScratch *sc = scratch_for(ctx, s);
+    if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+    TRY(grow(ctx, &sc->partial, &sc->partial_bytes, (size_t)grid * std::max(8, pr.meta.v[2]), s, false));
+    p.aux[0] = sc->partial;
+    p.aux[1] = sc->words + 0;
+    return launch(ctx, pr.fn, "foldAll", grid, pr.block, 0, s, p);
+}
+
+int accb_fold_dim(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                  long long rows, long long cols, const void *seed, size_t seed_bytes, const accb_array *out) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_FOLD_DIM}, "fold_dim"));
+    if (rows < 0 || cols < 0) return fail(ctx, ACCB_EINVAL, "negative extent");
+    if (cols == 0 && !seed) return fail(ctx, ACCB_EBOUNDS, "fold1: empty array");
+    if (rows == 0) return ACCB_OK;
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    TRY(fill_env(ctx, p, env, nenv));
+    TRY(fill_out(ctx, p, out));
+    TRY(set_seed(ctx, p, seed, seed_bytes));
+    p.n = rows * cols;
+    p.ip[0] = rows;
+    p.ip[1] = cols;
+    /* threads per row: a whole block for long rows, a warp, or 4 lanes */
+    const char *entry = cols >= 2048 ? "fold" : (cols >= 32 ? "fold_warp" : "fold_sub");
+    Prep pr;
+    TRY(prepare(ctx, k, entry, 0, &pr));
+    const int group = cols >= 2048 ? pr.block : (cols >= 32 ? 32 : 4);
+    const long long units = ceil_div(rows, pr.block / group);
+    const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * pr.per_sm);
+    return launch(ctx, pr.fn, entry, grid, pr.block, 0, (cudaStream_t)stream, p);
+}
+
+int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                  long long rows, long long cols, const int *offsets, long long nseg, const void *seed,
+                  size_t seed_bytes, const accb_array *out) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_FOLD_SEG}, "fold_seg"));
+    if (rows < 0 || cols < 0 || nseg < 0) return fail(ctx, ACCB_EINVAL, "negative extent");
+    if (!offsets) return fail(ctx, ACCB_EINVAL, "null segment offsets");
+    if (rows * nseg == 0) return ACCB_OK;
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    TRY(fill_env(ctx, p, env, nenv));
+    TRY(fill_out(ctx, p, out));
+    TRY(set_seed(ctx, p, seed, seed_bytes));
+    p.n = rows * cols;
+    p.ip[0] = rows;
+    p.ip[1] = cols;
+    p.ip[2] = nseg;
+    p.aux[0] = const_cast<int *>(offsets);
+    Prep pr;
+    TRY(prepare(ctx, k, "foldSeg", 0, &pr));
+    /* one warp per segment (Launch.hs:118) */
+    const long long units = ceil_div(rows * nseg, pr.block / 32);
+    const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * pr.per_sm);
+    return launch(ctx, pr.fn, "foldSeg", grid, pr.block, 0, (cudaStream_t)stream, p);
+}
+
+/* ----------------------------------------------------------------- scan */
+int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv, long long n,
+              int direction, int kind, const void *seed, size_t seed_bytes, const accb_array *out,
+              const accb_array *total) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_SCAN}, "scan"));
+    if (n < 0) return fail(ctx, ACCB_EINVAL, "negative size");
+    const bool right = direction == ACCB_SCAN_RIGHT;
+    const bool seed_on_device = (kind & ACCB_SEED_ON_DEVICE) != 0;
+    kind &= ~ACCB_SEED_ON_DEVICE;
+    if (kind != ACCB_SCAN_INCLUSIVE && !seed) return fail(ctx, ACCB_EINVAL, "scanl/scanr/scan' need a seed");
+    if (kind == ACCB_SCAN_INCLUSIVE && seed) return fail(ctx, ACCB_EINVAL, "scanl1/scanr1 take no seed");
+    if (kind == ACCB_SCAN_PRIME && !total) return fail(ctx, ACCB_EINVAL, "scan' needs a total array");
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    TRY(fill_env(ctx, p, env, nenv));
+    TRY(fill_out(ctx, p, out));
+    if (seed_on_device) {
+        /* the seed is produced by earlier work on this stream: pass its address */
+        TRY(fill_scalars(ctx, p, &seed, sizeof(void *)));
+        p.flags |= ACCB_F_HAS_SEED | ACCB_F_SEED_PTR;
+    } else {
+        TRY(set_seed(ctx, p, seed, seed_bytes));
+    }
+    p.n = n;
+    p.ip[3] = -1;
+    p.ip[4] = -1;
+    const char *entry;
+    if (kind == ACCB_SCAN_INCLUSIVE) {
+        entry = right ? "scanr1" : "scanl1";
+    } else if (kind == ACCB_SCAN_PRIME) {
+        entry = right ? "scanr" : "scanl";
+        TRY(fill_out(ctx, p, total, out->ncomp));
+        p.ip[3] = 0;
+    } else if (!right) { /* scanl: exclusive body aligned with the input, total at out[n] */
+        entry = "scanl";
+        TRY(fill_out(ctx, p, out, out->ncomp));
+        p.ip[3] = n;
+    } else { /* scanr: seeded inclusive body, the seed itself at out[n] */
+        entry = "scanr1";
+        TRY(fill_out(ctx, p, out, out->ncomp));
+        p.ip[4] = n;
+    }
+    Prep pr;
+    TRY(prepare(ctx, k, entry, 0, &pr));
+    const int rec = pr.meta.v[2];
+    const long long tile = pr.meta.v[3];
+    if (rec <= 0 || tile <= 0) return fail(ctx, ACCB_EINVAL, "kernel %s carries no scan metadata", k->key.c_str());
+    const long long ntiles = ceil_div(n, tile);
+    if (ntiles > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one scan launch");
+    cudaStream_t s = (cudaStream_t)stream;
+    StreamScratch *sc = scratch_for(ctx, s);
+    if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+    const size_t need = (size_t)std::max(1LL, ntiles) * rec;
+    const bool regrow = sc->status_bytes < need;
+    TRY(grow(ctx, &sc->status, &sc->status_bytes, need, s, true));
+    if (!regrow && (sc->status_layout != rec || sc->epoch >= (1u << 30) - 2)) {
+        /* another record layout or an exhausted epoch counter: old words could alias new flags */
+        TRY(check_cuda(ctx, cudaMemsetAsync(sc->status, 0, sc->status_bytes, s), "cudaMemsetAsync"));
+        if (sc->epoch >= (1u << 30) - 2) sc->epoch = 0;
+    }
+    sc->status_layout = rec;
+    sc->epoch++;
+    p.ip[0] = ntiles;
+    p.ip[1] = sc->scan_ticket;
+    p.ip[2] = sc->epoch;
+    p.aux[0] = sc->status;
+    p.aux[1] = sc->words + 1;
+    p.aux[2] = sc->words + 2;
+    const int grid = (int)std::max(1LL, ntiles);
+    if (n > 0) sc->scan_ticket += (unsigned)grid; /* every block of the launch takes exactly one ticket */
+    return launch(ctx, pr.fn, entry, grid, pr.block, 0, s, p);
+}
+
+/* -------------------------------------------------------------- permute */
+int accb_permute_defaults(accb_context *ctx, accb_stream stream, const accb_array *defaults, const accb_array *out,
+                          const int *comp_bytes) {
+    LOCK(ctx);
+    if (!defaults || !out || !comp_bytes || defaults->ncomp != out->ncomp)
+        return fail(ctx, ACCB_EINVAL, "defaults / result mismatch");
+    const long long n = array_size(out);
+    if (array_size(defaults) != n) return fail(ctx, ACCB_EINVAL, "defaults and result differ in size");
+    /* device-to-device copy on the same stream, ahead of the kernel (Execute.hs:405-407) */
+    for (int c = 0; c < out->ncomp; ++c)
+        TRY(check_cuda(ctx,
+                       cudaMemcpyAsync(out->ptr[c], defaults->ptr[c], (size_t)n * comp_bytes[c],
+                                       cudaMemcpyDeviceToDevice, (cudaStream_t)stream),
+                       "copying permute defaults"));
+    return ACCB_OK;
+}
+
+int accb_permute(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                 long long n_src, const void *scalars, size_t scalar_bytes, const accb_array *out) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_PERMUTE, SK_PERMUTE_SMEM}, "permute"));
+    if (n_src < 0) return fail(ctx, ACCB_EINVAL, "negative size");
+    if (!out || out->rank < 1) return fail(ctx, ACCB_EINVAL, "permute into a rank-0 array is not supported"); /* IndexSpace.hs:230 */
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    TRY(fill_env(ctx, p, env, nenv));
+    const unsigned vec = p.flags & ACCB_F_VEC; /* only the inputs are read as vectors */
+    TRY(fill_out(ctx, p, out));
+    p.flags |= vec;
+    TRY(fill_scalars(ctx, p, scalars, scalar_bytes));
+    p.n = n_src;
+    const long long nout = array_size(out);
+    p.ip[0] = nout;
+    if (n_src == 0 || nout == 0) return ACCB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    StreamScratch *sc = scratch_for(ctx, s);
+    if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+    p.aux[1] = sc->words + 2;
+
+    Prep pr;
+    TRY(prepare(ctx, k, "permute", 0, &pr));
+    const int elem = pr.meta.v[2];
+    const bool needs_lock = pr.meta.v[5] != 0;
+    /* privatise in shared memory when R skewed copies of the destination fit */
+    if (k->skeleton == SK_PERMUTE_SMEM && (nout + 1) * elem <= 96 * 1024) {
+        int R = 4;
+        if (const char *e = getenv("ACCB_PERMUTE_REPLICAS")) R = std::max(1, atoi(e));
+        while (R > 1 && (R & (R - 1))) R &= R - 1; /* power of two */
+        while (R > 1 && (long long)R * (nout + 1) * elem > 200 * 1024) R >>= 1;
+        const size_t smem = (size_t)R * (nout + 1) * elem;
+        Prep ps;
+        TRY(prepare(ctx, k, "permute_smem", smem, &ps));
+        p.ip[1] = R;
+        const long long units = ceil_div(n_src, (long long)ps.block * ps.meta.v[4] * 4);
+        const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * ps.per_sm);
+        return launch(ctx, ps.fn, "permute_smem", grid, ps.block, smem, s, p);
+    }
+    if (needs_lock) {
+        /* one lock word per destination element, cleared for every launch (Execute.hs:402-405) */
+        TRY(grow(ctx, &sc->partial, &sc->partial_bytes, (size_t)nout * sizeof(int), s, false));
+        TRY(check_cuda(ctx, cudaMemsetAsync(sc->partial, 0, (size_t)nout * sizeof(int), s), "cudaMemsetAsync"));
+        p.aux[0] = sc->partial;
+    }
+    const long long units = ceil_div(n_src, (long long)pr.block * pr.meta.v[4] * 4);
+    const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * pr.per_sm);
+    return launch(ctx, pr.fn, "permute", grid, pr.block, 0, s, p);
+}
+
+/* -------------------------------------------------------------- stencil */
+static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, cudaStream_t s,
+                          const accb_array *const *src, int nsrc, int boundary, const void *constant,
+                          size_t constant_bytes, const accb_array *out) {
+    if (!out || out->rank < 1 || out->rank > 2) return fail(ctx, ACCB_EINVAL, "stencils support rank 1 and 2");
+    if (boundary < ACCB_CLAMP || boundary > ACCB_CONSTANT) return fail(ctx, ACCB_EINVAL, "unknown boundary %d", boundary);
+    if (boundary == ACCB_CONSTANT && !constant) return fail(ctx, ACCB_EINVAL, "Constant boundary needs a value");
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    p.flags |= ACCB_F_VEC;
+    for (int a = 0; a < nsrc; ++a) {
+        if (!src[a] || src[a]->rank != out->rank || src[a]->ncomp != 1 || !src[a]->ptr[0])
+            return fail(ctx, ACCB_EINVAL, "stencil source %d: rank / component mismatch", a);
+        p.in[a] = src[a]->ptr[0];
+        if (!aligned16(src[a]->ptr[0])) p.flags &= ~ACCB_F_VEC;
+        p.ip[5 + 2 * a] = out->rank == 2 ? src[a]->shape[1] : 1;
+        p.ip[6 + 2 * a] = src[a]->shape[0];
+    }
+    TRY(fill_out(ctx, p, out));
+    if (constant) TRY(fill_scalars(ctx, p, constant, constant_bytes));
+    const int W = out->shape[0], H = out->rank == 2 ? out->shape[1] : 1;
+    p.n = (long long)W * H;
+    if (p.n == 0) return ACCB_OK;
+    for (int a = 0; a < nsrc; ++a)
+        if (p.ip[5 + 2 * a] < H || p.ip[6 + 2 * a] < W)
+            return fail(ctx, ACCB_EINVAL, "stencil result larger than source %d", a);
+    Prep pr;
+    TRY(prepare(ctx, k, entry, 0, &pr));
+    int txw = 32;
+    while (txw < pr.block && txw * 4 < W) txw *= 2;
+    int rb = 32;
+    if (const char *e = getenv("ACCB_STENCIL_ROWS")) rb = std::max(1, atoi(e));
+    const int ty = pr.block / txw;
+    p.ip[0] = H;
+    p.ip[1] = W;
+    p.ip[2] = rb;
+    p.ip[3] = txw;
+    p.ip[4] = boundary;
+    const long long tasks = ceil_div(W, (long long)txw * 4) * ceil_div(H, (long long)rb * ty);
+    const int grid = (int)std::min<long long>(tasks, 1 << 20);
+    return launch(ctx, pr.fn, entry, grid, pr.block, 0, s, p);
+}
+
+int accb_stencil(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *src, int boundary,
+                 const void *constant, size_t constant_bytes, const accb_array *out) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_STENCIL}, "stencil"));
+    const accb_array *srcs[1] = {src};
+    return stencil_launch(ctx, k, "stencil", (cudaStream_t)stream, srcs, 1, boundary, constant, constant_bytes, out);
+}
+
+int accb_stencil2(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *src1,
+                  const accb_array *src2, int boundary, const void *constant, size_t constant_bytes,
+                  const accb_array *out) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_STENCIL2}, "stencil2"));
+    const accb_array *srcs[2] = {src1, src2};
+    return stencil_launch(ctx, k, "stencil2", (cudaStream_t)stream, srcs, 2, boundary, constant, constant_bytes, out);
+}
+
+int accb_stencil_iterate(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *a,
+                         const accb_array *b, int iters, int boundary, const void *constant, size_t constant_bytes,
+                         int *result_in_b) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_STENCIL}, "stencil"));
+    if (!a || !b || iters < 0) return fail(ctx, ACCB_EINVAL, "bad argument");
+    const accb_array *cur = a, *nxt = b;
+    for (int i = 0; i < iters; ++i) {
+        const accb_array *srcs[1] = {cur};
+        TRY(stencil_launch(ctx, k, "stencil", (cudaStream_t)stream, srcs, 1, boundary, constant, constant_bytes, nxt));
+        std::swap(cur, nxt);
+    }
+    if (result_in_b) *result_in_b = (cur == b);
+    return ACCB_OK;
+}
+
+} /* extern "C" */

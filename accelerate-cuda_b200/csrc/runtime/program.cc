@@ -1,0 +1,487 @@
+/*
+ * program.cc -- whole programs: the AccFFI.h surface (accelerateCreate,
+ * runProgram, freeOutput, freeProgram, accelerateDestroy) and the op list
+ * that stands in for a compiled Accelerate function.
+ *
+ * Replaces Data/Array/Accelerate/CUDA/Foreign/Export.hs:100-283 and the
+ * execute phase executeAfun1 / executeOpenAcc of
+ * Data/Array/Accelerate/CUDA/Execute.hs:143-219 for straight-line programs
+ * (a let-bound chain of collective operations).  In the reference an
+ * AccProgram is a StablePtr to a Haskell closure `run1With ctx f`
+ * (Export.hs:255-265); here it is a list of nodes, each naming a compiled
+ * kernel, the values it reads and how the shape of its result follows from
+ * them (Execute.hs:264-450).
+ *
+ * Intermediate arrays are kept in a per-program pool and reused from run to
+ * run when large enough, instead of one cuMemAlloc per intermediate per run
+ * (Array/Sugar.hs:40-44 via Execute.hs:264-268).
+ */
+#include <algorithm>
+#include <cstdlib>
+
+#include "common.h"
+
+using namespace accb_rt;
+
+namespace {
+
+enum NodeKind { N_MAP, N_FOLD, N_SCAN, N_PERMUTE, N_STENCIL };
+
+struct Node {
+    NodeKind kind;
+    accb_kernel *k = nullptr;
+    std::vector<int> env;
+    int shape_like = 0;
+    int all = 0;          /* fold: reduce everything */
+    int direction = 0, scan_kind = 0;
+    int defaults_id = -1; /* permute */
+    int boundary = 0, iters = 1;
+    bool has_seed = false;
+    std::vector<unsigned char> scalars; /* map scalars / fold+scan seed / stencil constant */
+    int out_id = -1;      /* first value id produced */
+    accb_value_type out_type;
+};
+
+struct PoolBuf {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+
+}  // namespace
+
+struct accb_program {
+    accb_context *ctx = nullptr;
+    int ninputs = 0;
+    std::vector<accb_value_type> types; /* per value id */
+    std::vector<Node> nodes;
+    std::vector<int> outputs;
+    std::vector<std::vector<PoolBuf>> pool; /* per value id, per component (stencil uses 2x) */
+    std::vector<std::vector<PoolBuf>> in_pool;
+    cudaStream_t host_stream = nullptr;
+    int status = ACCB_OK;
+};
+
+namespace {
+
+long long size_of(const accb_array &a) {
+    long long n = 1;
+    for (int d = 0; d < a.rank; ++d) n *= a.shape[d];
+    return n;
+}
+
+int pool_get(accb_program *p, PoolBuf &b, size_t bytes, void **out) {
+    bytes = std::max<size_t>(bytes, 16);
+    if (b.bytes < bytes) {
+        if (b.ptr) {
+            cudaDeviceSynchronize(); /* earlier runs may still read it */
+            cudaFree(b.ptr);
+            b.ptr = nullptr;
+            b.bytes = 0;
+        }
+        void *q = p->ctx->mem.alloc_raw(bytes);
+        if (!q) return fail(p->ctx, ACCB_ENOMEM, "device out of memory allocating %zu bytes for an intermediate", bytes);
+        b.ptr = q;
+        b.bytes = MemTable::round_up(bytes);
+    }
+    *out = b.ptr;
+    return ACCB_OK;
+}
+
+/* allocate the components of value `id` with shape already set in `a` */
+int alloc_value(accb_program *p, int id, accb_array &a, bool fresh, int pool_slot = 0) {
+    const accb_value_type &t = p->types[id];
+    a.ncomp = t.ncomp;
+    const long long n = std::max(1LL, size_of(a)); /* at least one element (Prim.hs:167,186) */
+    for (int c = 0; c < t.ncomp; ++c) {
+        const size_t bytes = (size_t)n * t.comp_bytes[c];
+        if (fresh) {
+            a.ptr[c] = p->ctx->mem.alloc_raw(bytes);
+            if (!a.ptr[c]) return fail(p->ctx, ACCB_ENOMEM, "device out of memory allocating %zu bytes for a result", bytes);
+        } else {
+            auto &slots = p->pool[id];
+            const size_t idx = (size_t)pool_slot * ACCB_ARRAY_MAX_COMP + c;
+            if (slots.size() <= idx) slots.resize(idx + 1);
+            int st = pool_get(p, slots[idx], bytes, &a.ptr[c]);
+            if (st != ACCB_OK) return st;
+        }
+    }
+    return ACCB_OK;
+}
+
+#define TRY(expr)                       \
+    do {                                \
+        int st_ = (expr);               \
+        if (st_ != ACCB_OK) return st_; \
+    } while (0)
+
+int run_internal(accb_program *p, cudaStream_t s, const accb_array *inputs, accb_array *outputs, bool fresh_outputs) {
+    accb_context *ctx = p->ctx;
+    std::vector<accb_array> val(p->types.size());
+    for (int i = 0; i < p->ninputs; ++i) val[i] = inputs[i];
+    auto is_output = [&](int id) { return std::find(p->outputs.begin(), p->outputs.end(), id) != p->outputs.end(); };
+
+    for (Node &nd : p->nodes) {
+        std::vector<accb_array> env;
+        for (int e : nd.env) env.push_back(val[e]);
+        const accb_array &like = val[nd.shape_like];
+        accb_array out;
+        memset(&out, 0, sizeof out);
+        const bool fresh = fresh_outputs && is_output(nd.out_id);
+        const void *sc = nd.scalars.empty() ? nullptr : nd.scalars.data();
+        switch (nd.kind) {
+            case N_MAP: {
+                out.rank = like.rank;
+                memcpy(out.shape, like.shape, sizeof out.shape);
+                TRY(alloc_value(p, nd.out_id, out, fresh));
+                TRY(accb_map(ctx, nd.k, s, env.data(), (int)env.size(), sc, nd.scalars.size(), &out));
+                break;
+            }
+            case N_FOLD: {
+                const void *seed = nd.has_seed ? sc : nullptr;
+                if (nd.all || like.rank <= 1) {
+                    out.rank = 0;
+                    TRY(alloc_value(p, nd.out_id, out, fresh));
+                    TRY(accb_fold_all(ctx, nd.k, s, env.data(), (int)env.size(), size_of(like), seed, nd.scalars.size(), &out));
+                } else {
+                    /* result drops the innermost extent; zero outer extents become 1 (Execute.hs:287-289) */
+                    out.rank = like.rank - 1;
+                    long long rows = 1;
+                    for (int d = 1; d < like.rank; ++d) {
+                        out.shape[d - 1] = nd.has_seed ? std::max(1, like.shape[d]) : like.shape[d];
+                        rows *= out.shape[d - 1];
+                    }
+                    TRY(alloc_value(p, nd.out_id, out, fresh));
+                    TRY(accb_fold_dim(ctx, nd.k, s, env.data(), (int)env.size(), rows, like.shape[0], seed,
+                                      nd.scalars.size(), &out));
+                }
+                break;
+            }
+            case N_SCAN: {
+                if (like.rank != 1) return fail(ctx, ACCB_EINVAL, "scans are defined on vectors only"); /* PrefixSum.hs:39-46 */
+                const long long n = like.shape[0];
+                out.rank = 1;
+                out.shape[0] = (int)(nd.scan_kind == ACCB_SCAN_EXCLUSIVE ? n + 1 : n);
+                TRY(alloc_value(p, nd.out_id, out, fresh));
+                accb_array total;
+                memset(&total, 0, sizeof total);
+                if (nd.scan_kind == ACCB_SCAN_PRIME)
+                    TRY(alloc_value(p, nd.out_id + 1, total, fresh_outputs && is_output(nd.out_id + 1)));
+                TRY(accb_scan(ctx, nd.k, s, env.data(), (int)env.size(), n, nd.direction, nd.scan_kind,
+                              nd.has_seed ? sc : nullptr, nd.scalars.size(), &out,
+                              nd.scan_kind == ACCB_SCAN_PRIME ? &total : nullptr));
+                if (nd.scan_kind == ACCB_SCAN_PRIME) val[nd.out_id + 1] = total;
+                break;
+            }
+            case N_PERMUTE: {
+                const accb_array &dfl = val[nd.defaults_id];
+                out.rank = dfl.rank;
+                memcpy(out.shape, dfl.shape, sizeof out.shape);
+                TRY(alloc_value(p, nd.out_id, out, fresh));
+                TRY(accb_permute_defaults(ctx, s, &dfl, &out, p->types[nd.out_id].comp_bytes));
+                TRY(accb_permute(ctx, nd.k, s, env.data(), (int)env.size(), size_of(like), nullptr, 0, &out));
+                break;
+            }
+            case N_STENCIL: {
+                out.rank = like.rank;
+                memcpy(out.shape, like.shape, sizeof out.shape);
+                if (nd.iters <= 1) {
+                    TRY(alloc_value(p, nd.out_id, out, fresh));
+                    TRY(accb_stencil(ctx, nd.k, s, &like, nd.boundary, sc, nd.scalars.size(), &out));
+                } else {
+                    /* ping-pong: the final grid must land in `out` */
+                    accb_array tmp = out;
+                    TRY(alloc_value(p, nd.out_id, out, fresh, 0));
+                    TRY(alloc_value(p, nd.out_id, tmp, false, 1));
+                    accb_array *dst = (nd.iters % 2) ? &out : &tmp;
+                    accb_array *other = (nd.iters % 2) ? &tmp : &out;
+                    TRY(accb_stencil(ctx, nd.k, s, &like, nd.boundary, sc, nd.scalars.size(), dst));
+                    int in_b = 0;
+                    TRY(accb_stencil_iterate(ctx, nd.k, s, dst, other, nd.iters - 1, nd.boundary, sc, nd.scalars.size(), &in_b));
+                }
+                break;
+            }
+        }
+        val[nd.out_id] = out;
+    }
+    for (size_t j = 0; j < p->outputs.size(); ++j) outputs[j] = val[p->outputs[j]];
+    return ACCB_OK;
+}
+
+int add_node(accb_program *p, Node &nd, const accb_value_type *out_type, int nvalues) {
+    if (!out_type || out_type->ncomp < 1 || out_type->ncomp > ACCB_ARRAY_MAX_COMP)
+        return -fail(p->ctx, ACCB_EINVAL, "bad result type");
+    for (int e : nd.env)
+        if (e < 0 || e >= (int)p->types.size()) return -fail(p->ctx, ACCB_EINVAL, "unknown value id %d", e);
+    if (nd.shape_like < 0 || nd.shape_like >= (int)p->types.size()) return -fail(p->ctx, ACCB_EINVAL, "unknown value id");
+    nd.out_id = (int)p->types.size();
+    nd.out_type = *out_type;
+    p->types.push_back(*out_type);
+    if (nvalues == 2) { /* scan': the total is a scalar of the same element type */
+        accb_value_type t = *out_type;
+        t.rank = 0;
+        p->types.push_back(t);
+    }
+    p->pool.resize(p->types.size());
+    p->nodes.push_back(nd);
+    return nd.out_id;
+}
+
+struct Handle {
+    accb_context *ctx = nullptr;
+    int status = ACCB_OK;
+};
+
+struct OutputOwner {
+    accb_context *ctx;
+    std::vector<void *> ptrs;
+};
+
+}  // namespace
+
+#define PLOCK(p)                                                      \
+    if (!(p)) return fail(nullptr, ACCB_EINVAL, "null program");      \
+    std::lock_guard<std::recursive_mutex> lock_((p)->ctx->mu);        \
+    CtxGuard guard_((p)->ctx)
+
+extern "C" {
+
+int accb_program_create(accb_context *ctx, int ninputs, const accb_value_type *input_types, accb_program **prog) {
+    if (!ctx || !prog || ninputs < 0 || (ninputs > 0 && !input_types)) return fail(ctx, ACCB_EINVAL, "bad argument");
+    accb_program *p = new accb_program;
+    p->ctx = ctx;
+    p->ninputs = ninputs;
+    p->types.assign(input_types, input_types + ninputs);
+    p->pool.resize(ninputs);
+    p->in_pool.resize(ninputs);
+    *prog = p;
+    return ACCB_OK;
+}
+
+/* the add functions return the new value id (>= 0) or minus a status code */
+int accb_program_map(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like,
+                     const accb_value_type *out_type, const void *scalars, size_t scalar_bytes) {
+    if (!p || !k) return -ACCB_EINVAL;
+    Node nd;
+    nd.kind = N_MAP;
+    nd.k = k;
+    nd.env.assign(env_ids, env_ids + nenv);
+    nd.shape_like = shape_like;
+    if (scalars) nd.scalars.assign((const unsigned char *)scalars, (const unsigned char *)scalars + scalar_bytes);
+    return add_node(p, nd, out_type, 1);
+}
+
+int accb_program_fold(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like, int all,
+                      const void *seed, size_t seed_bytes, const accb_value_type *out_type) {
+    if (!p || !k) return -ACCB_EINVAL;
+    Node nd;
+    nd.kind = N_FOLD;
+    nd.k = k;
+    nd.env.assign(env_ids, env_ids + nenv);
+    nd.shape_like = shape_like;
+    nd.all = all;
+    nd.has_seed = seed != nullptr;
+    if (seed) nd.scalars.assign((const unsigned char *)seed, (const unsigned char *)seed + seed_bytes);
+    return add_node(p, nd, out_type, 1);
+}
+
+int accb_program_scan(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like, int direction,
+                      int kind, const void *seed, size_t seed_bytes, const accb_value_type *out_type) {
+    if (!p || !k) return -ACCB_EINVAL;
+    Node nd;
+    nd.kind = N_SCAN;
+    nd.k = k;
+    nd.env.assign(env_ids, env_ids + nenv);
+    nd.shape_like = shape_like;
+    nd.direction = direction;
+    nd.scan_kind = kind;
+    nd.has_seed = seed != nullptr;
+    if (seed) nd.scalars.assign((const unsigned char *)seed, (const unsigned char *)seed + seed_bytes);
+    return add_node(p, nd, out_type, kind == ACCB_SCAN_PRIME ? 2 : 1);
+}
+
+int accb_program_permute(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like,
+                         int defaults_id, const accb_value_type *out_type) {
+    if (!p || !k) return -ACCB_EINVAL;
+    if (defaults_id < 0 || defaults_id >= (int)p->types.size()) return -fail(p->ctx, ACCB_EINVAL, "unknown defaults id");
+    Node nd;
+    nd.kind = N_PERMUTE;
+    nd.k = k;
+    nd.env.assign(env_ids, env_ids + nenv);
+    nd.shape_like = shape_like;
+    nd.defaults_id = defaults_id;
+    return add_node(p, nd, out_type, 1);
+}
+
+int accb_program_stencil(accb_program *p, accb_kernel *k, int src_id, int boundary, const void *constant,
+                         size_t constant_bytes, int iters, const accb_value_type *out_type) {
+    if (!p || !k) return -ACCB_EINVAL;
+    Node nd;
+    nd.kind = N_STENCIL;
+    nd.k = k;
+    nd.env.push_back(src_id);
+    nd.shape_like = src_id;
+    nd.boundary = boundary;
+    nd.iters = std::max(1, iters);
+    if (constant) nd.scalars.assign((const unsigned char *)constant, (const unsigned char *)constant + constant_bytes);
+    return add_node(p, nd, out_type, 1);
+}
+
+int accb_program_outputs(accb_program *p, const int *ids, int nout) {
+    if (!p || !ids || nout < 1) return fail(p ? p->ctx : nullptr, ACCB_EINVAL, "bad argument");
+    for (int i = 0; i < nout; ++i)
+        if (ids[i] < 0 || ids[i] >= (int)p->types.size()) return fail(p->ctx, ACCB_EINVAL, "unknown value id %d", ids[i]);
+    p->outputs.assign(ids, ids + nout);
+    return ACCB_OK;
+}
+
+int accb_program_run(accb_program *p, accb_stream stream, const accb_array *inputs, accb_array *outputs) {
+    PLOCK(p);
+    if ((p->ninputs && !inputs) || !outputs || p->outputs.empty()) return fail(p->ctx, ACCB_EINVAL, "bad argument");
+    return run_internal(p, (cudaStream_t)stream, inputs, outputs, false);
+}
+
+int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array *host_out) {
+    PLOCK(p);
+    if ((p->ninputs && !host_in) || !host_out || p->outputs.empty()) return fail(p->ctx, ACCB_EINVAL, "bad argument");
+    accb_context *ctx = p->ctx;
+    if (!p->host_stream) TRY(check_cuda(ctx, cudaStreamCreateWithFlags(&p->host_stream, cudaStreamNonBlocking), "cudaStreamCreate"));
+    cudaStream_t s = p->host_stream;
+    /* upload (useArrayAsync, Execute.hs:151-154) */
+    std::vector<accb_array> dev_in(p->ninputs);
+    for (int i = 0; i < p->ninputs; ++i) {
+        dev_in[i] = host_in[i];
+        const long long n = std::max(1LL, size_of(host_in[i]));
+        auto &slots = p->in_pool[i];
+        if ((int)slots.size() < p->types[i].ncomp) slots.resize(p->types[i].ncomp);
+        for (int c = 0; c < p->types[i].ncomp; ++c) {
+            const size_t bytes = (size_t)n * p->types[i].comp_bytes[c];
+            TRY(pool_get(p, slots[c], bytes, &dev_in[i].ptr[c]));
+            TRY(check_cuda(ctx, cudaMemcpyAsync(dev_in[i].ptr[c], host_in[i].ptr[c], (size_t)size_of(host_in[i]) * p->types[i].comp_bytes[c],
+                                                cudaMemcpyHostToDevice, s), "upload"));
+        }
+    }
+    std::vector<accb_array> dev_out(p->outputs.size());
+    TRY(run_internal(p, s, dev_in.data(), dev_out.data(), false));
+    /* collect: every result goes back to the host (CUDA.hs:382-389) */
+    for (size_t j = 0; j < p->outputs.size(); ++j) {
+        const accb_value_type &t = p->types[p->outputs[j]];
+        void *host_ptr[ACCB_ARRAY_MAX_COMP];
+        for (int c = 0; c < t.ncomp; ++c) host_ptr[c] = host_out[j].ptr[c];
+        host_out[j].rank = dev_out[j].rank;
+        memcpy(host_out[j].shape, dev_out[j].shape, sizeof dev_out[j].shape);
+        host_out[j].ncomp = t.ncomp;
+        for (int c = 0; c < t.ncomp; ++c) {
+            if (!host_ptr[c]) return fail(ctx, ACCB_EINVAL, "null host buffer for result %zu", j);
+            TRY(check_cuda(ctx, cudaMemcpyAsync(host_ptr[c], dev_out[j].ptr[c], (size_t)size_of(dev_out[j]) * t.comp_bytes[c],
+                                                cudaMemcpyDeviceToHost, s), "download"));
+        }
+    }
+    TRY(check_cuda(ctx, cudaStreamSynchronize(s), "cudaStreamSynchronize"));
+    return ACCB_OK;
+}
+
+int accb_program_destroy(accb_program *p) {
+    if (!p) return ACCB_OK;
+    {
+        std::lock_guard<std::recursive_mutex> lock_(p->ctx->mu);
+        CtxGuard g(p->ctx);
+        cudaDeviceSynchronize();
+        for (auto &v : p->pool)
+            for (auto &b : v)
+                if (b.ptr) cudaFree(b.ptr);
+        for (auto &v : p->in_pool)
+            for (auto &b : v)
+                if (b.ptr) cudaFree(b.ptr);
+        if (p->host_stream) cudaStreamDestroy(p->host_stream);
+    }
+    delete p;
+    return ACCB_OK;
+}
+
+/* ----------------------------------------------------- AccFFI.h surface */
+AccHandle accelerateCreate(int32_t device, void *cu_context) {
+    accb_context *ctx = nullptr;
+    if (accb_context_create(device, cu_context, &ctx) != ACCB_OK) return nullptr;
+    Handle *h = new Handle;
+    h->ctx = ctx;
+    return h;
+}
+
+void accelerateDestroy(AccHandle hndl) {
+    Handle *h = static_cast<Handle *>(hndl);
+    if (!h) return;
+    accb_context_destroy(h->ctx);
+    delete h;
+}
+
+int accelerateStatus(AccHandle hndl) {
+    Handle *h = static_cast<Handle *>(hndl);
+    return h ? h->status : ACCB_EINVAL;
+}
+
+accb_context *accelerateContext(AccHandle hndl) {
+    Handle *h = static_cast<Handle *>(hndl);
+    return h ? h->ctx : nullptr;
+}
+
+/* in: ninputs consecutive InputArray structs (device pointers, borrowed);
+ * out: one OutputArray per program output, filled with malloc'ed shape and
+ * pointer buffers that freeOutput releases (Export.hs:155-166,203-226). */
+void runProgram(AccHandle hndl, AccProgram prog, InputArray *in, OutputArray *out) {
+    Handle *h = static_cast<Handle *>(hndl);
+    accb_program *p = static_cast<accb_program *>(prog);
+    if (!h || !p || !out) {
+        if (h) h->status = ACCB_EINVAL;
+        return;
+    }
+    std::lock_guard<std::recursive_mutex> lock_(p->ctx->mu);
+    CtxGuard g(p->ctx);
+    std::vector<accb_array> inputs(p->ninputs);
+    for (int i = 0; i < p->ninputs; ++i) {
+        accb_array &a = inputs[i];
+        memset(&a, 0, sizeof a);
+        a.rank = p->types[i].rank;
+        a.ncomp = p->types[i].ncomp;
+        for (int d = 0; d < a.rank; ++d) a.shape[d] = in[i].shape[d];
+        for (int c = 0; c < a.ncomp; ++c) a.ptr[c] = in[i].adata[c];
+    }
+    std::vector<accb_array> outputs(p->outputs.size());
+    h->status = run_internal(p, nullptr, inputs.data(), outputs.data(), true);
+    if (h->status == ACCB_OK) h->status = check_cuda(p->ctx, cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
+    for (size_t j = 0; j < outputs.size(); ++j) {
+        out[j].shape = nullptr;
+        out[j].adata = nullptr;
+        out[j].stable_ptr = nullptr;
+        if (h->status != ACCB_OK) continue;
+        const accb_array &a = outputs[j];
+        out[j].shape = (int *)malloc(sizeof(int) * std::max(1, a.rank));
+        out[j].adata = (void **)malloc(sizeof(void *) * a.ncomp);
+        OutputOwner *own = new OutputOwner;
+        own->ctx = p->ctx;
+        for (int d = 0; d < a.rank; ++d) out[j].shape[d] = a.shape[d];
+        for (int c = 0; c < a.ncomp; ++c) {
+            out[j].adata[c] = a.ptr[c];
+            own->ptrs.push_back(a.ptr[c]);
+        }
+        out[j].stable_ptr = own;
+    }
+}
+
+void freeOutput(OutputArray *out) {
+    if (!out) return;
+    free(out->shape);
+    free(out->adata);
+    if (OutputOwner *own = static_cast<OutputOwner *>(out->stable_ptr)) {
+        std::lock_guard<std::recursive_mutex> lock_(own->ctx->mu);
+        CtxGuard g(own->ctx);
+        for (void *q : own->ptrs) cudaFree(q);
+        delete own;
+    }
+    out->shape = nullptr;
+    out->adata = nullptr;
+    out->stable_ptr = nullptr;
+}
+
+void freeProgram(AccProgram p) { accb_program_destroy(static_cast<accb_program *>(p)); }
+
+} /* extern "C" */

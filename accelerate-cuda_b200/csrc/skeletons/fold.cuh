@@ -1,0 +1,335 @@
+/*
+ * fold.cuh -- reductions: foldAll / fold1All, fold / fold1 over the innermost
+ * dimension, foldSeg / fold1Seg.
+ *
+ * Replaces mkFoldAll' (two kernels relaunched until one value is left,
+ * Data/Array/Accelerate/CUDA/CodeGen/Reduction.hs:87-215 with the host
+ * recursion foldCore/foldRec, Execute.hs:291-318), mkFoldDim (one block per
+ * row, Reduction.hs:221-367) and mkFoldSeg' (one warp per segment,
+ * Reduction.hs:421-574).  Semantics kept from there:
+ *   - the seed is combined on the right, f(acc, seed) (Reduction.hs:203-215,
+ *     364-367, 567-574); an empty input yields the seed (:204-214, :351-362);
+ *   - like the reference's strided accumulation (:160-165) the combiner is
+ *     assumed associative AND commutative.
+ *
+ * Functor contract (derive from accb::Fold<T[, Acc]> for the defaults):
+ *   using In  = accb::types<...>;          element-wise inputs of the producer
+ *   typedef T  elem;  typedef Acc acc;     value type / accumulator type
+ *   static T   get(env, i, in-values...);  the fused producer
+ *   static Acc lift(T);  static T lower(Acc);
+ *   static Acc combine(Acc, Acc);
+ *   using Out = accb::types<...>;  static void put(T, out-references...);
+ * `Acc` wider than `T` (double for a recognised (+) on Float) keeps a float32
+ * sum within one rounding of the exact result.
+ *
+ * foldAll is ONE launch: persistent blocks accumulate with 128-bit streaming
+ * loads, write one partial each, and the block that finishes last (ticket
+ * counter) combines the partials in block order and applies the seed.  The
+ * partials and the ticket live in runtime-owned scratch (aux[0], aux[1]);
+ * the last block resets the ticket, so no memset is needed between launches.
+ */
+#pragma once
+#include "../cubits/accb_vec.cuh"
+#include "../cubits/accb_warp.cuh"
+
+namespace accb {
+
+template <class T, class A = T>
+struct Fold {
+    typedef T elem;
+    typedef A acc;
+    typedef types<T> Out;
+    static __device__ __forceinline__ A lift(T x) { return static_cast<A>(x); }
+    static __device__ __forceinline__ T lower(A a) { return static_cast<T>(a); }
+    static __device__ __forceinline__ void put(T r, T &o) { o = r; }
+};
+
+/* (have, value) pairs: a reduction without an identity element */
+template <class A>
+struct Opt {
+    A v;
+    int have;
+};
+template <class Fn>
+struct OptCombine {
+    typedef typename Fn::acc A;
+    __device__ __forceinline__ Opt<A> operator()(Opt<A> a, Opt<A> b) const {
+        Opt<A> r;
+        r.have = a.have | b.have;
+        r.v = (a.have && b.have) ? Fn::combine(a.v, b.v) : (a.have ? a.v : b.v);
+        return r;
+    }
+};
+
+template <class Fn, int N, int... I>
+__device__ __forceinline__ void fold_get(const Env &env, long long i0, regs<N, typename Fn::In> &a,
+                                         typename Fn::elem (&x)[N], std::integer_sequence<int, I...>) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) x[k] = Fn::get(env, i0 + k, comp<I>(a)[k]...);
+}
+
+template <class Fn, int... O>
+__device__ __forceinline__ void fold_put(const accb_kparams &p, long long j, typename Fn::elem r,
+                                         std::integer_sequence<int, O...>) {
+    regs<1, typename Fn::Out> b;
+    Fn::put(r, comp<O>(b)[0]...);
+    store_one(p.out, j, b);
+}
+
+template <class Fn>
+__device__ __forceinline__ typename Fn::elem fold_seed(const accb_kparams &p) {
+    typedef typename Fn::elem T;
+    if (p.flags & ACCB_F_SEED_PTR) {
+        /* the scalar block holds a device pointer to the seed (a carry produced
+         * by earlier device work, e.g. the totals of lower-ranked shards) */
+        const T *q = Env(p).scalar<const T *>(0);
+        return *q;
+    }
+    return Env(p).scalar<T>(0);
+}
+
+/* Accumulate elements [lo, lo+len) of the producer into `acc`, all threads of
+ * a group of G threads (rank `g`) cooperating; vec_ok says lo and the slots
+ * are vector aligned. */
+template <class Fn, int U>
+__device__ __forceinline__ void fold_range(const accb_kparams &p, const Env &env, long long lo, long long len,
+                                           int g, int G, bool vec_ok, Opt<typename Fn::acc> &acc) {
+    typedef typename Fn::In In;
+    typedef typename Fn::elem T;
+    typedef typename Fn::acc A;
+    const auto iseq = std::make_integer_sequence<int, In::size>();
+    const long long nvec = vec_ok ? len / V : 0;
+    const long long v_lo = lo / V; /* lo is a multiple of V when vec_ok */
+    const long long TRIP = (long long)G * U;
+    const long long ntrip = nvec / TRIP;
+    for (long long t = 0; t < ntrip; ++t) {
+        const long long v0 = v_lo + t * TRIP + g;
+        regs<V, In> a[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) load_all(p.in, v0 + (long long)u * G, a[u]);
+        A part;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            T x[V];
+            fold_get<Fn>(env, (v0 + (long long)u * G) * V, a[u], x, iseq);
+            A s = Fn::combine(Fn::combine(Fn::lift(x[0]), Fn::lift(x[1])),
+                              Fn::combine(Fn::lift(x[2]), Fn::lift(x[3])));
+            part = (u == 0) ? s : Fn::combine(part, s);
+        }
+        acc.v = acc.have ? Fn::combine(acc.v, part) : part;
+        acc.have = 1;
+    }
+    for (long long v = v_lo + ntrip * TRIP + g; v < v_lo + nvec; v += G) {
+        regs<V, In> a;
+        T x[V];
+        load_all(p.in, v, a);
+        fold_get<Fn>(env, v * V, a, x, iseq);
+        A s = Fn::combine(Fn::combine(Fn::lift(x[0]), Fn::lift(x[1])),
+                          Fn::combine(Fn::lift(x[2]), Fn::lift(x[3])));
+        acc.v = acc.have ? Fn::combine(acc.v, s) : s;
+        acc.have = 1;
+    }
+    for (long long i = lo + nvec * V + g; i < lo + len; i += G) {
+        regs<1, In> a;
+        T x[1];
+        load_one(p.in, i, a);
+        fold_get<Fn>(env, i, a, x, iseq);
+        A s = Fn::lift(x[0]);
+        acc.v = acc.have ? Fn::combine(acc.v, s) : s;
+        acc.have = 1;
+    }
+}
+
+/* ------------------------------------------------------------------ foldAll */
+template <class Fn, int CTA, int U>
+__device__ __forceinline__ void fold_all_body(const accb_kparams &p) {
+    typedef typename Fn::acc A;
+    typedef Opt<A> O;
+    __shared__ O s_red[CTA / 32];
+    __shared__ int s_last;
+    const Env env(p);
+    const OptCombine<Fn> oc;
+    const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
+    const long long n = p.n;
+    const bool vec_ok = (p.flags & ACCB_F_VEC) != 0;
+
+    /* contiguous slab per block, boundaries on multiples of CTA*U*V */
+    const long long quantum = (long long)CTA * U * V;
+    const long long nq = (n + quantum - 1) / quantum;
+    const long long q_per = (nq + gridDim.x - 1) / gridDim.x;
+    long long lo = (long long)blockIdx.x * q_per * quantum;
+    long long hi = lo + q_per * quantum;
+    if (lo > n) lo = n;
+    if (hi > n) hi = n;
+
+    O acc;
+    acc.have = 0;
+    fold_range<Fn, U>(p, env, lo, hi - lo, threadIdx.x, CTA, vec_ok, acc);
+    acc = block_reduce<CTA>(acc, oc, s_red);
+
+    O *partial = static_cast<O *>(p.aux[0]);
+    unsigned int *ticket = static_cast<unsigned int *>(p.aux[1]);
+    if (threadIdx.x == 0) {
+        partial[blockIdx.x] = acc;
+        __threadfence();
+        const unsigned int t = atomicAdd(ticket, 1u);
+        s_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+
+    /* last block: combine the partials in block order */
+    __threadfence();
+    O tot;
+    tot.have = 0;
+    for (unsigned int b = threadIdx.x; b < gridDim.x; b += CTA) {
+        O x = ld_cg(partial + b);
+        tot = oc(tot, x);
+    }
+    tot = block_reduce<CTA>(tot, oc, s_red);
+    if (threadIdx.x == 0) {
+        *ticket = 0u;
+        if (p.flags & ACCB_F_HAS_SEED) {
+            const A z = Fn::lift(fold_seed<Fn>(p));
+            tot.v = tot.have ? Fn::combine(tot.v, z) : z;
+            tot.have = 1;
+        }
+        if (tot.have) fold_put<Fn>(p, 0, Fn::lower(tot.v), oseq);
+    }
+}
+
+/* ------------------------------------------------------ fold over inner dim */
+/* ip[0] = rows (outer size), ip[1] = cols (innermost extent).
+ * GROUP = threads cooperating on one row: CTA (block per row) or 32/16/8/... */
+template <class Fn, int CTA, int GROUP, int U>
+__device__ __forceinline__ void fold_dim_body(const accb_kparams &p) {
+    typedef typename Fn::acc A;
+    typedef Opt<A> O;
+    __shared__ O s_red[CTA / 32];
+    const Env env(p);
+    const OptCombine<Fn> oc;
+    const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
+    const long long rows = p.ip[0], cols = p.ip[1];
+    const bool vec_ok = (p.flags & ACCB_F_VEC) != 0 && (cols % V) == 0;
+    const bool seeded = (p.flags & ACCB_F_HAS_SEED) != 0;
+
+    if constexpr (GROUP == CTA) {
+        for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+            O acc;
+            acc.have = 0;
+            fold_range<Fn, U>(p, env, r * cols, cols, threadIdx.x, CTA, vec_ok, acc);
+            acc = block_reduce<CTA>(acc, oc, s_red);
+            if (threadIdx.x == 0) {
+                if (seeded) {
+                    const A z = Fn::lift(fold_seed<Fn>(p));
+                    acc.v = acc.have ? Fn::combine(acc.v, z) : z;
+                    acc.have = 1;
+                }
+                if (acc.have) fold_put<Fn>(p, r, Fn::lower(acc.v), oseq);
+            }
+        }
+    } else {
+        constexpr int PER = CTA / GROUP; /* rows per block per trip */
+        const int g = threadIdx.x % GROUP;
+        for (long long r = (long long)blockIdx.x * PER + threadIdx.x / GROUP; r < rows;
+             r += (long long)gridDim.x * PER) {
+            O acc;
+            acc.have = 0;
+            fold_range<Fn, U>(p, env, r * cols, cols, g, GROUP, vec_ok, acc);
+            /* reduce inside the aligned group of GROUP lanes; a group's lanes
+             * share r, so they leave the loop together */
+            const unsigned gmask =
+                GROUP == 32 ? FULL : (((1u << GROUP) - 1u) << ((threadIdx.x & 31) / GROUP * GROUP));
+#pragma unroll
+            for (int m = GROUP / 2; m > 0; m >>= 1) {
+                O o;
+                o.have = __shfl_xor_sync(gmask, acc.have, m);
+                constexpr int W = (sizeof(A) + 3) / 4;
+                unsigned w[W] = {};
+                memcpy(w, &acc.v, sizeof(A));
+#pragma unroll
+                for (int k = 0; k < W; ++k) w[k] = __shfl_xor_sync(gmask, w[k], m);
+                memcpy(&o.v, w, sizeof(A));
+                acc = oc(acc, o);
+            }
+            if (g == 0) {
+                if (seeded) {
+                    const A z = Fn::lift(fold_seed<Fn>(p));
+                    acc.v = acc.have ? Fn::combine(acc.v, z) : z;
+                    acc.have = 1;
+                }
+                if (acc.have) fold_put<Fn>(p, r, Fn::lower(acc.v), oseq);
+            }
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ foldSeg */
+/* One warp per (row, segment).  aux[0] = Int32 offsets, length nseg+1: the
+ * exclusive scan of the segment lengths (Execute.hs:320-324).
+ * ip[0] = rows, ip[1] = cols (innermost extent of the source), ip[2] = nseg. */
+template <class Fn, int CTA>
+__device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
+    typedef typename Fn::acc A;
+    typedef Opt<A> O;
+    const Env env(p);
+    const OptCombine<Fn> oc;
+    const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
+    const long long rows = p.ip[0], cols = p.ip[1], nseg = p.ip[2];
+    const int *offs = static_cast<const int *>(p.aux[0]);
+    const bool seeded = (p.flags & ACCB_F_HAS_SEED) != 0;
+    const long long total = rows * nseg;
+    constexpr int WPB = CTA / 32;
+    for (long long w = (long long)blockIdx.x * WPB + warp_id(); w < total; w += (long long)gridDim.x * WPB) {
+        const long long r = w / nseg, s = w - r * nseg;
+        const long long lo = offs[s], hi = offs[s + 1];
+        O acc;
+        acc.have = 0;
+        fold_range<Fn, 1>(p, env, r * cols + lo, hi - lo, lane_id(), 32, false, acc);
+        acc = warp_reduce_xor(acc, oc);
+        if (lane_id() == 0) {
+            if (seeded) {
+                const A z = Fn::lift(fold_seed<Fn>(p));
+                acc.v = acc.have ? Fn::combine(acc.v, z) : z;
+                acc.have = 1;
+            }
+            if (acc.have) fold_put<Fn>(p, w, Fn::lower(acc.v), oseq);
+        }
+    }
+}
+
+}  // namespace accb
+
+#define ACCB_FOLD_CTA 256
+#define ACCB_FOLD_U 4
+
+/* Entry points named after the reference's kernels (Reduction.hs:111,229,430);
+ * the seeded and seedless forms share a kernel (flag ACCB_F_HAS_SEED). */
+#define ACCB_INSTANTIATE_FOLD_ALL(Fn)                                                   \
+    ACCB_META(2, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, ACCB_FOLD_U, 0)           \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
+        foldAll(const __grid_constant__ accb_kparams p) {                               \
+        accb::fold_all_body<Fn, ACCB_FOLD_CTA, ACCB_FOLD_U>(p);                         \
+    }
+
+#define ACCB_INSTANTIATE_FOLD_DIM(Fn)                                                   \
+    ACCB_META(3, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, ACCB_FOLD_U, 0)           \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
+        fold(const __grid_constant__ accb_kparams p) {                                  \
+        accb::fold_dim_body<Fn, ACCB_FOLD_CTA, ACCB_FOLD_CTA, ACCB_FOLD_U>(p);          \
+    }                                                                                   \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
+        fold_warp(const __grid_constant__ accb_kparams p) {                             \
+        accb::fold_dim_body<Fn, ACCB_FOLD_CTA, 32, 2>(p);                               \
+    }                                                                                   \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
+        fold_sub(const __grid_constant__ accb_kparams p) {                              \
+        accb::fold_dim_body<Fn, ACCB_FOLD_CTA, 4, 1>(p);                                \
+    }
+
+#define ACCB_INSTANTIATE_FOLD_SEG(Fn)                                                   \
+    ACCB_META(4, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, 1, 0)                     \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
+        foldSeg(const __grid_constant__ accb_kparams p) {                               \
+        accb::fold_seg_body<Fn, ACCB_FOLD_CTA>(p);                                      \
+    }

@@ -1,0 +1,478 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 skeleton library on BASELINE.json's metric:
+effective HBM GB/s per skeleton.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload scan] [--impl reference]
+
+A step is one pass of one skeleton over its synthetic input.  The default
+workload is the prefix sum ``scanl (+) 0`` over 2^28 Int32 per GPU; the other
+configurations are measured after the timed region and reported under
+``skeletons`` (N = 1 only).  With N > 1 (under torchrun) every rank scans its
+own 2^28-element slab of one N*2^28-element vector and the slabs are joined by
+a carry: weak scaling.
+
+One JSON line on stdout (rank 0):
+  value      algorithmic bytes of all ranks / device time of the K timed steps
+             (CUDA events on the launching stream, max over ranks), GB/s;
+  roofline   the same for the dominant kernel against the measured HBM copy
+             bandwidth of MEASURED_PEAKS.json;
+  e2e        the metric through run1 on pinned HOST arrays: upload, launch,
+             download inside the timed region;
+  cpu_baseline  the CPU oracle (a port: the reference's own interpreter
+             cannot be built here) on a bounded sample, one core.
+``--impl reference`` times that oracle with all host threads instead.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "effective HBM GB/s per skeleton at 2^28 elems"
+SPEC_PEAK_GBS = 8000.0
+FALLBACK_PEAK_GBS = 6650.0
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_PEAK_GBS, "fallback"
+
+
+# ----------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, device: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            self.nv = nv
+            self.h = nv.nvmlDeviceGetHandleByIndex(device)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self.nv:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr:
+            self._thr.join()
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# -------------------------------------------------------------- workloads
+class Workload:
+    name = ""
+    dtype = ""
+
+    def __init__(self, accb, ctx, torch, rank, world):
+        self.accb, self.ctx, self.t, self.rank, self.world = accb, ctx, torch, rank, world
+        self.P = importlib.import_module("accelerate-cuda_b200.programs")
+        self.W = importlib.import_module("accelerate-cuda_b200.workloads")
+
+
+class ScanWorkload(Workload):
+    """scanl (+) 0 over Int32, values uniform in [0,16); 2^28 elements per GPU."""
+    name, dtype = "scanl (+) 0, Int32, 2^28 per GPU", "int32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.n = n or W.N28
+        self.x = t.empty(self.n, dtype=t.int32, device="cuda")
+        self.ctx.gen_uniform_i32(self.x, self.n, self.rank * self.n, W.SEED, W.S_SCAN, 16)
+        # rank r writes its slab of the global result; the last rank also owns out[n_total]
+        self.out = t.empty(self.n + 1, dtype=t.int32, device="cuda")
+        self.k = self.ctx.kernel(self.P.SCAN_ADD_I32).wait()
+        self.bytes = W.bytes_scan(self.n)
+        if self.world > 1:
+            import torch.distributed as dist
+            self.dist = dist
+            self.ksum = self.ctx.kernel(self.P.SUM_I32).wait()
+            self.total = t.zeros(1, dtype=t.int32, device="cuda")
+            self.gathered = t.zeros(self.world, dtype=t.int32, device="cuda")
+            self.carry = t.zeros(1, dtype=t.int32, device="cuda")
+            self.bytes = W.bytes_scan(self.n)  # algorithmic bytes stay 8 B/element; the reduce pass is overhead
+        self.ctx.sync()
+
+    def step(self):
+        if self.world == 1:
+            self.ctx.scan(self.k, [self.x], self.n, self.out, seed=np.int32(0))
+            return 1
+        # carry pass: slab totals -> all-gather -> exclusive sum of the lower ranks -> seeded local scan
+        self.ctx.fold_all(self.ksum, [self.x], self.n, self.total, seed=np.int32(0))
+        self.dist.all_gather_into_tensor(self.gathered, self.total)
+        self.carry.copy_(self.gathered[: self.rank].sum(dtype=self.t.int32).reshape(1)) if self.rank else self.carry.zero_()
+        self.ctx.scan(self.k, [self.x], self.n, self.out, seed=self.carry)
+        return 2
+
+    def verify(self):
+        """out[i+1] - out[i] == x[i] everywhere and out[0] == carry: a size-independent property."""
+        t = self.t
+        d = self.out[1:] - self.out[:-1]
+        ok = bool(t.equal(d, self.x))
+        if self.world == 1:
+            ok = ok and int(self.out[0]) == 0 and int(self.out[-1]) == int(self.x.sum(dtype=t.int64) & 0xffffffff)
+        return ok
+
+    def program(self):
+        """The same operation as a run1 function on host arrays."""
+        accb, P = self.accb, self.P
+        return accb.run1With(self.ctx, lambda v: accb.scan(P.SCAN_ADD_I32, [v], np.int32, seed=np.int32(0)),
+                             accb.ArrayType(1, np.int32))
+
+
+class DotWorkload(Workload):
+    name, dtype = "foldAll (+) 0 (zipWith (*) xs ys), Float32, 2^28", "f32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.n = n or W.N28
+        self.x = t.empty(self.n, dtype=t.float32, device="cuda")
+        self.y = t.empty(self.n, dtype=t.float32, device="cuda")
+        self.ctx.gen_uniform_f32(self.x, self.n, 0, W.SEED, W.S_XS, -1.0, 1.0)
+        self.ctx.gen_uniform_f32(self.y, self.n, 0, W.SEED, W.S_YS, -1.0, 1.0)
+        self.out = t.zeros(1, dtype=t.float32, device="cuda")
+        self.k = self.ctx.kernel(self.P.DOT).wait()
+        self.bytes = W.bytes_dot(self.n)
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.fold_all(self.k, [self.x, self.y], self.n, self.out, seed=np.float32(0))
+        return 1
+
+    def verify(self):
+        ref = float((self.x.double() * self.y.double()).sum())
+        return abs(float(self.out[0]) - ref) <= 1e-5 * abs(ref)
+
+
+class HistWorkload(Workload):
+    name, dtype = "permute (+) histogram, 2^28 Int32 keys, 4096 bins", "int32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.n = n or W.N28
+        self.keys = t.empty(self.n, dtype=t.int32, device="cuda")
+        cdf = t.from_numpy(W.zipf_cdf()).cuda()
+        self.ctx.gen_zipf_mix_i32(self.keys, self.n, 0, W.SEED, cdf, W.HIST_BINS)
+        self.defaults = t.zeros(W.HIST_BINS, dtype=t.int32, device="cuda")
+        self.out = t.zeros(W.HIST_BINS, dtype=t.int32, device="cuda")
+        self.k = self.ctx.kernel(self.P.HIST).wait()
+        self.bytes = W.bytes_hist(self.n)
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.permute(self.k, [self.keys], self.n, self.out, defaults=self.defaults)
+        return 1
+
+    def verify(self):
+        t = self.t
+        ref = t.bincount(self.keys.long(), minlength=self.W.HIST_BINS).int()
+        return bool(t.equal(ref, self.out)) and int(self.out.sum()) == self.n
+
+
+class StencilWorkload(Workload):
+    name, dtype = "10 x stencil 3x3 blur Clamp, Float32 8192x8192", "f32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.h = self.w = n or 8192
+        self.iters = 10
+        self.a = t.empty((self.h, self.w), dtype=t.float32, device="cuda")
+        self.b = t.empty_like(self.a)
+        self.src = t.empty_like(self.a)
+        self.ctx.gen_uniform_f32(self.src, self.h * self.w, 0, W.SEED, W.S_GRID, 0.0, 1.0)
+        self.k = self.ctx.kernel(self.P.BLUR).wait()
+        self.bytes = W.bytes_stencil(self.h, self.w, self.iters)
+        self.ctx.sync()
+
+    def step(self):
+        # first application reads the pristine source, so every step does identical work
+        self.ctx.stencil(self.k, self.src, self.a, boundary="clamp")
+        self.res = self.ctx.stencil_iterate(self.k, self.a, self.b, self.iters - 1, boundary="clamp")
+        return self.iters
+
+    def verify(self):
+        # blur with Clamp keeps values inside [min, max] of the source and (interior) preserves the mean
+        r = self.res
+        return bool(r.min() >= self.src.min()) and bool(r.max() <= self.src.max()) and abs(float(r.mean()) - float(self.src.mean())) < 1e-3
+
+
+class BlackScholesWorkload(Workload):
+    name, dtype = "map Black-Scholes, 2^26 options, Float32", "f32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.n = n or W.N26
+        mk = lambda: t.empty(self.n, dtype=t.float32, device="cuda")
+        self.s, self.k_, self.y, self.call, self.put = mk(), mk(), mk(), mk(), mk()
+        self.ctx.gen_uniform_f32(self.s, self.n, 0, W.SEED, W.S_SPOT, 5.0, 30.0)
+        self.ctx.gen_uniform_f32(self.k_, self.n, 0, W.SEED, W.S_STRIKE, 1.0, 100.0)
+        self.ctx.gen_uniform_f32(self.y, self.n, 0, W.SEED, W.S_YEARS, 0.25, 10.0)
+        self.k = self.ctx.kernel(self.P.BLACKSCHOLES).wait()
+        self.bytes = W.bytes_blackscholes(self.n)
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.map(self.k, [(self.s, self.k_, self.y)], (self.call, self.put))
+        return 1
+
+    def verify(self):
+        # put-call parity: call - put = S - K exp(-rT)
+        t = self.t
+        lhs = (self.call - self.put).double()
+        rhs = self.s.double() - self.k_.double() * t.exp(-0.02 * self.y.double())
+        return bool(((lhs - rhs).abs() <= 1e-5 * rhs.abs() + 1e-4).all())
+
+
+class RowSumWorkload(Workload):
+    name, dtype = "fold (+) 0 over rows, Float32 16384x16384", "f32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.rows = self.cols = n or 16384
+        self.m = t.empty((self.rows, self.cols), dtype=t.float32, device="cuda")
+        self.ctx.gen_uniform_f32(self.m, self.rows * self.cols, 0, W.SEED, W.S_MATRIX, -1.0, 1.0)
+        self.out = t.zeros(self.rows, dtype=t.float32, device="cuda")
+        self.k = self.ctx.kernel(self.P.ROWSUM).wait()
+        self.bytes = W.bytes_rowsum(self.rows, self.cols)
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.fold_dim(self.k, [self.m], self.rows, self.cols, self.out, seed=np.float32(0))
+        return 1
+
+    def verify(self):
+        ref = self.m.double().sum(dim=1)
+        return bool(((self.out.double() - ref).abs() <= 1e-5 * ref.abs() + 1e-6).all())
+
+
+WORKLOADS = {"scan": ScanWorkload, "dot": DotWorkload, "hist": HistWorkload, "stencil": StencilWorkload,
+             "blackscholes": BlackScholesWorkload, "rowsum": RowSumWorkload}
+
+
+def time_steps(torch, wl, steps, warmup):
+    """K steps between two CUDA events on the launching (current) stream; returns (ms total, launches)."""
+    for _ in range(warmup):
+        wl.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+    e0.record()
+    for _ in range(steps):
+        launches += wl.step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1), launches
+
+
+# --------------------------------------------------------- CPU reference arm
+def cpu_scan_sample(threads: int, n: int, repeats: int):
+    oracle = importlib.import_module("oracle")
+    W = importlib.import_module("accelerate-cuda_b200.workloads")
+    x = W.uniform_i32(W.SEED, W.S_SCAN, n, 16)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        out = oracle.scanl_i32(x, 0, nthreads=threads)
+        best = min(best, time.perf_counter() - t0)
+    assert int(out[-1]) == int(x.astype(np.int64).sum() & 0xffffffff)
+    return W.bytes_scan(n) / best / 1e9, best
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oracle = importlib.import_module("oracle")
+    threads = oracle.max_threads()
+    n = 1 << 26
+    W = importlib.import_module("accelerate-cuda_b200.workloads")
+    x = W.uniform_i32(W.SEED, W.S_SCAN, n, 16)
+    for _ in range(args.warmup):
+        oracle.scanl_i32(x, 0, nthreads=threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.scanl_i32(x, 0, nthreads=threads)
+    dt = time.perf_counter() - t0
+    gbs = W.bytes_scan(n) * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+        "config": {"workload": ScanWorkload.name, "sample": "2^26-element slice per step"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "scanl (+) 0 over a 2^26-element Int32 slice per step, blocked two-pass OpenMP scan"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's own CPU path (Accelerate's interpreter) cannot be built here (no GHC); this is the C oracle port",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# -------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="scan", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--size", type=int, default=None, help="override the problem size (profiling small cases)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-skeleton table, e2e and CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    accb = importlib.import_module("accelerate-cuda_b200")
+    ctx = accb.Context(local)
+    peak, peak_kind = measured_peak()
+
+    wl = WORKLOADS[args.workload](accb, ctx, torch, rank, world)
+    wl.setup(args.size)
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clocks:
+        ms, launches = time_steps(torch, wl, args.steps, args.warmup)
+    if dist:
+        tm = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ms = float(tm[0])
+        dist.barrier()
+    ok = wl.verify()
+    if dist:
+        okt = torch.tensor([int(ok)], device="cuda")
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        ok = bool(okt[0])
+    ms_step = ms / args.steps
+    total_bytes = wl.bytes * world
+    value = total_bytes / (ms_step * 1e-3) / 1e9
+    per_gpu = wl.bytes / (ms_step * 1e-3) / 1e9
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+        "data": "synthetic",
+        "config": {"workload": wl.name, "l2": "inputs larger than L2 (1 GiB read per step)", "parity_check": ok,
+                   "elements_per_gpu": getattr(wl, "n", None), "seed": hex(wl.W.SEED)},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+        "pct_of_spec_peak_8TBs": 100.0 * per_gpu / SPEC_PEAK_GBS,
+    }
+    # dominant kernel = the skeleton's kernel; one launch per step moves the algorithmic bytes of a step
+    line["roofline"] = {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                        "traffic": None, "peak_kind": peak_kind,
+                        "kernel": "scanl" if args.workload == "scan" else args.workload}
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        # ---- e2e: run1 on pinned host arrays (upload + launch + download inside the timed region)
+        try:
+            prog = wl.program()
+            n = wl.n
+            hin = torch.empty(n, dtype=torch.int32).pin_memory()
+            hin.copy_(wl.x.cpu())
+            hout = torch.empty(n + 1, dtype=torch.int32).pin_memory()
+            xin, xout = hin.numpy(), hout.numpy()
+            for _ in range(2):
+                prog(xin, out=[[xout]])
+            reps = max(3, min(args.steps, 5))
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                prog(xin, out=[[xout]])
+            dt = (time.perf_counter() - t0) / reps
+            assert int(xout[-1]) == int(wl.out[-1])
+            line["e2e"] = {"value": wl.bytes / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n,
+                           "d2h_bytes_per_step": 4 * (n + 1), "ms_per_step": dt * 1e3, "steps": reps}
+            prog.destroy()
+            del hin, hout
+        except AttributeError:
+            line["e2e"] = None
+        # ---- CPU baseline on a bounded sample, one core
+        gbs, secs = cpu_scan_sample(1, 1 << 26, 3)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port",
+                                "sample": "sequential scanl (+) 0 over a 2^26-element Int32 slice, best of 3"}
+        # ---- the other skeletons, each on its configuration
+        del wl
+        torch.cuda.empty_cache()
+        table = {args.workload: {"GB/s": per_gpu, "frac_of_measured": per_gpu / peak, "ms": ms_step, "parity_check": ok}}
+        for name, cls in WORKLOADS.items():
+            if name == args.workload:
+                continue
+            w2 = cls(accb, ctx, torch, 0, 1)
+            w2.setup(None)
+            ms2, _ = time_steps(torch, w2, 10, 3)
+            g = w2.bytes / (ms2 / 10 * 1e-3) / 1e9
+            table[name] = {"GB/s": g, "frac_of_measured": g / peak, "ms": ms2 / 10, "parity_check": bool(w2.verify()),
+                           "workload": w2.name}
+            del w2
+            torch.cuda.empty_cache()
+        line["skeletons"] = table
+    elif rank == 0:
+        line["e2e"] = None
+    ctx.sync()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,288 @@
+/*
+ * accb200.h -- C ABI of the B200 execution backend for Accelerate's collective
+ * operations (libaccb200.so).
+ *
+ * This header is the successor of accelerate-cuda's include/AccFFI.h:7-30 and
+ * of the Haskell-internal interfaces behind it.  Each group below names the
+ * reference interface it replaces (paths are relative to the accelerate-cuda
+ * source tree).  Conventions:
+ *   - every function returns an int status (ACCB_OK == 0); no exception and no
+ *     process exit crosses this boundary (the reference's functions are void
+ *     and a CUDA error terminates the process, Data/Array/Accelerate/CUDA/State.hs:84-92);
+ *     accb_last_error() gives the message of the last failure on a context;
+ *   - plain pointers and sizes only; device pointers are ordinary CUDA device
+ *     pointers of the context's device; streams are cudaStream_t / CUstream
+ *     passed as void*;
+ *   - arrays of tuples are structure-of-arrays, one device pointer per
+ *     flattened scalar component (CUDA/CodeGen/Base.hs:69-79);
+ *   - shapes list the INNERMOST extent first, like the shape buffers of
+ *     AccFFI.h (CUDA/Foreign/Export.hs:210-214,274-275);
+ *   - all functions are thread-safe; calls on one context are serialised by an
+ *     internal mutex except for the asynchronous device work they enqueue.
+ */
+#ifndef ACCB200_H
+#define ACCB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ACCB_API __attribute__((visibility("default")))
+
+/* ---------------------------------------------------------------- status */
+enum {
+    ACCB_OK = 0,
+    ACCB_EINVAL = 1,    /* bad argument */
+    ACCB_ECUDA = 2,     /* a CUDA runtime / driver call failed */
+    ACCB_ENOMEM = 3,    /* device memory exhausted even after eviction */
+    ACCB_ECOMPILE = 4,  /* nvcc failed; the log is in accb_last_error() */
+    ACCB_EIO = 5,       /* kernel cache I/O */
+    ACCB_EBOUNDS = 6,   /* e.g. fold1 of an empty array (CUDA/Execute.hs:283-285) */
+    ACCB_ETIMEOUT = 7,  /* a bounded device-side wait gave up */
+    ACCB_ENOTFOUND = 8, /* unknown key / entry point */
+    ACCB_ENODRIVER = 9  /* libcuda.so.1 is not available */
+};
+
+typedef struct accb_context accb_context;
+typedef struct accb_kernel accb_kernel;
+typedef struct accb_event accb_event;
+typedef void *accb_stream;
+
+#define ACCB_ARRAY_MAX_RANK 4
+#define ACCB_ARRAY_MAX_COMP 8
+
+/* One array as the launch functions see it: replaces the Marshalable
+ * instance for arrays (shape ints followed by one pointer per component,
+ * CUDA/Execute.hs:823-873). */
+typedef struct accb_array {
+    int rank;                          /* 0 for a scalar */
+    int shape[ACCB_ARRAY_MAX_RANK];    /* innermost extent first */
+    int ncomp;                         /* flattened tuple components */
+    void *ptr[ACCB_ARRAY_MAX_COMP];    /* device pointers, leftmost field first */
+} accb_array;
+
+/* ------------------------------------------------- runtime and contexts
+ * replaces accelerateCreate / accelerateDestroy (include/AccFFI.h:21-30,
+ * CUDA/Foreign/Export.hs:146-153), Context.create / destroy
+ * (CUDA/Context.hs:55-93) and the global state of CUDA/State.hs:61-132.   */
+ACCB_API int accb_init(void);
+ACCB_API int accb_device_count(int *count);
+ACCB_API const char *accb_version(void);
+/* cu_context: NULL to use the device's primary context (shared with the CUDA
+ * runtime and with PyTorch), or a CUcontext the caller owns. */
+ACCB_API int accb_context_create(int device, void *cu_context, accb_context **ctx);
+ACCB_API int accb_context_destroy(accb_context *ctx);
+/* Waits for all work enqueued through this context and reports device-side
+ * bounded-wait failures (ACCB_ETIMEOUT). */
+ACCB_API int accb_context_sync(accb_context *ctx);
+ACCB_API const char *accb_last_error(accb_context *ctx); /* ctx may be NULL */
+ACCB_API int accb_device_info(accb_context *ctx, int *sm_count, size_t *total_mem, int *cc_major,
+                              int *cc_minor);
+
+/* ----------------------------------------------------- streams and events
+ * replaces the stream reservoir and event table, CUDA/Execute/Stream.hs:52-140
+ * and CUDA/Execute/Event.hs:38-140.                                        */
+ACCB_API int accb_stream_acquire(accb_context *ctx, accb_stream *stream);
+ACCB_API int accb_stream_release(accb_context *ctx, accb_stream stream);
+ACCB_API int accb_stream_sync(accb_context *ctx, accb_stream stream);
+ACCB_API int accb_event_record(accb_context *ctx, accb_stream stream, accb_event **event);
+ACCB_API int accb_stream_wait_event(accb_context *ctx, accb_stream stream, accb_event *event);
+ACCB_API int accb_event_sync(accb_context *ctx, accb_event *event);
+ACCB_API int accb_event_query(accb_context *ctx, accb_event *event, int *done);
+ACCB_API int accb_event_release(accb_context *ctx, accb_event *event);
+
+/* ------------------------------------------------- device memory table
+ * replaces CUDA/Array/Remote.hs:91-202 (malloc, withRemote, free,
+ * insertUnmanaged, reclaim) and the typed transfer functions of
+ * CUDA/Array/Prim.hs:159-472.  `key` identifies a host array (the reference
+ * uses the host array's stable name).  Allocation sizes are rounded up to
+ * 1024 bytes (Remote.hs:60-80).  When the device is full, least recently
+ * used unpinned entries with a host copy are written back and evicted.    */
+ACCB_API int accb_malloc(accb_context *ctx, uint64_t key, size_t bytes, void **dptr);
+/* upload-if-absent of a host array (useArrayAsync, Prim.hs:226-234) */
+ACCB_API int accb_use(accb_context *ctx, uint64_t key, const void *host, size_t bytes, accb_stream stream,
+                      void **dptr);
+/* register memory the caller owns; never freed by the table (Remote.hs:168-184) */
+ACCB_API int accb_insert_unmanaged(accb_context *ctx, uint64_t key, void *dptr, size_t bytes);
+/* pin / unpin an entry while device work uses it (withRemote, Remote.hs:113-134) */
+ACCB_API int accb_with_ptr(accb_context *ctx, uint64_t key, void **dptr, size_t *bytes);
+ACCB_API int accb_release(accb_context *ctx, uint64_t key);
+ACCB_API int accb_peek(accb_context *ctx, uint64_t key, size_t offset, void *host, size_t bytes,
+                       accb_stream stream); /* device -> host (peekArrayAsync) */
+ACCB_API int accb_poke(accb_context *ctx, uint64_t key, size_t offset, const void *host, size_t bytes,
+                       accb_stream stream); /* host -> device (pokeArrayAsync) */
+ACCB_API int accb_copy(accb_context *ctx, uint64_t src_key, uint64_t dst_key, size_t bytes,
+                       accb_stream stream); /* device -> device (copyArrayAsync) */
+ACCB_API int accb_copy_peer(accb_context *src_ctx, uint64_t src_key, accb_context *dst_ctx, uint64_t dst_key,
+                            size_t bytes, accb_stream stream); /* copyArrayPeerAsync, Prim.hs:306-335 */
+/* read one element synchronously (indexArray, Prim.hs:189-211) */
+ACCB_API int accb_index(accb_context *ctx, uint64_t key, size_t index, size_t elt_bytes, void *out);
+ACCB_API int accb_free(accb_context *ctx, uint64_t key);    /* unsafeFree, CUDA.hs:421-431 */
+ACCB_API int accb_reclaim(accb_context *ctx);               /* performGC, CUDA.hs:433-441 */
+ACCB_API int accb_memory_stats(accb_context *ctx, size_t *entries, size_t *bytes_resident, size_t *evictions);
+
+/* ---------------------------------------------------- kernel cache (JIT)
+ * replaces build / compile / link of CUDA/Compile.hs:439-660 and the
+ * two-level KernelTable of CUDA/Persistent.hs:77-378.
+ * `skeleton` is one of "map", "fold_all", "fold_dim", "fold_seg", "scan",
+ * "permute", "permute_smem", "stencil", "stencil2"; `functor_src` is C++
+ * source defining a struct (what the scalar code generator CUDA/CodeGen.hs
+ * prints for the user's functions); `functor_name` is that struct's name;
+ * `nvcc_flags` may add -D options or NULL.  The result is looked up by
+ * hash(arch, skeleton library, source, flags) in memory, then on disk, and
+ * only then compiled with nvcc -arch=sm_100a -cubin in a worker thread; the
+ * call returns at once and the first launch waits for the compiler
+ * (the reference's lazy link, Compile.hs:444-459).                          */
+ACCB_API int accb_kernel_get(accb_context *ctx, const char *skeleton, const char *functor_src,
+                             const char *functor_name, const char *nvcc_flags, accb_kernel **kernel);
+ACCB_API int accb_kernel_wait(accb_context *ctx, accb_kernel *kernel); /* block until linked */
+/* registers, static shared memory, block size and resident blocks per SM of
+ * an entry point (determineOccupancy, CUDA/Analysis/Launch.hs:62-74) */
+ACCB_API int accb_kernel_info(accb_context *ctx, accb_kernel *kernel, const char *entry, int *regs,
+                              int *static_smem, int *block, int *blocks_per_sm);
+ACCB_API int accb_kernel_release(accb_context *ctx, accb_kernel *kernel);
+/* Compile into a cache directory without a GPU (build-time pre-seeding). */
+ACCB_API int accb_kernel_precompile(const char *skeleton, const char *functor_src, const char *functor_name,
+                                    const char *nvcc_flags, const char *cache_dir, char *log, size_t log_bytes);
+/* the cache key (32 hex digits) the library derives for a kernel: the name of
+ * its cubin in the cache directories (Compile.hs:565, Persistent.hs:218-228) */
+ACCB_API int accb_kernel_key(const char *skeleton, const char *functor_src, const char *functor_name,
+                             const char *nvcc_flags, char *key, size_t key_bytes);
+ACCB_API int accb_cache_flush(accb_context *ctx); /* -fflush-cache, Persistent.hs:305-344 */
+ACCB_API int accb_cache_stats(accb_context *ctx, size_t *mem_hits, size_t *disk_hits, size_t *compiles);
+/* grid the runtime would use for `n` elements (launchConfig, Launch.hs:42-55) */
+ACCB_API int accb_launch_config(accb_context *ctx, accb_kernel *kernel, const char *entry, long long n,
+                                int *block, int *grid, int *dynamic_smem);
+ACCB_API int accb_launch_count(accb_context *ctx, unsigned long long *launches);
+
+/* ------------------------------------------- skeleton launches (Execute)
+ * replace executeOp, foldCore/foldRec, foldSegOp, scanOp/scan1Op/scan'Op,
+ * permuteOp, stencilOp and stencil2Op of CUDA/Execute.hs:264-450 together
+ * with configure/execute/launch (:930-982).  `env` are the free array
+ * variables of the functor in Gamma order (CUDA/AST.hs:72-112); `scalars` is
+ * a packed block of user scalars the functor reads with env.scalar<T>(off).
+ * All launches are asynchronous on `stream`.                               */
+ACCB_API int accb_map(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                      const void *scalars, size_t scalar_bytes, const accb_array *out);
+
+/* seed == NULL selects fold1 / fold1All (no seed) */
+ACCB_API int accb_fold_all(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
+                           int nenv, long long n, const void *seed, size_t seed_bytes, const accb_array *out);
+ACCB_API int accb_fold_dim(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
+                           int nenv, long long rows, long long cols, const void *seed, size_t seed_bytes,
+                           const accb_array *out);
+/* offsets: Int32 device array of nseg+1 exclusive-scanned segment lengths */
+ACCB_API int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
+                           int nenv, long long rows, long long cols, const int *offsets, long long nseg,
+                           const void *seed, size_t seed_bytes, const accb_array *out);
+
+enum { ACCB_SCAN_LEFT = 0, ACCB_SCAN_RIGHT = 1 };
+enum {
+    ACCB_SCAN_EXCLUSIVE = 0, /* scanl / scanr : out has n+1 elements            */
+    ACCB_SCAN_INCLUSIVE = 1, /* scanl1 / scanr1: out has n elements, no seed    */
+    ACCB_SCAN_PRIME = 2      /* scanl' / scanr': out has n elements + `total`   */
+};
+/* OR into `kind`: `seed` is a DEVICE pointer to the seed value, written by
+ * earlier work on the same stream (the carry of a sharded scan). */
+#define ACCB_SEED_ON_DEVICE 0x100
+ACCB_API int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                       long long n, int direction, int kind, const void *seed, size_t seed_bytes,
+                       const accb_array *out, const accb_array *total);
+
+/* out must already hold the default values (the reference copies them first,
+ * Execute.hs:405-407); use accb_permute_defaults to do that copy. */
+ACCB_API int accb_permute_defaults(accb_context *ctx, accb_stream stream, const accb_array *defaults,
+                                   const accb_array *out, const int *comp_bytes);
+ACCB_API int accb_permute(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
+                          int nenv, long long n_src, const void *scalars, size_t scalar_bytes,
+                          const accb_array *out);
+
+enum { ACCB_CLAMP = 0, ACCB_MIRROR = 1, ACCB_WRAP = 2, ACCB_CONSTANT = 3 };
+ACCB_API int accb_stencil(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *src,
+                          int boundary, const void *constant, size_t constant_bytes, const accb_array *out);
+ACCB_API int accb_stencil2(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *src1,
+                           const accb_array *src2, int boundary, const void *constant, size_t constant_bytes,
+                           const accb_array *out);
+/* `iters` applications ping-ponging between a and b; *result tells which of
+ * the two holds the final grid.  Replaces a chain of Stencil nodes, each of
+ * which allocates a fresh array in the reference (Execute.hs:413-425). */
+ACCB_API int accb_stencil_iterate(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *a,
+                                  const accb_array *b, int iters, int boundary, const void *constant,
+                                  size_t constant_bytes, int *result_in_b);
+
+/* -------------------------------------- whole programs (AccFFI.h surface)
+ * Same struct layouts and entry points as include/AccFFI.h:10-30.  An
+ * AccProgram is an op list built with accb_program_* instead of a Haskell
+ * closure exported by Template Haskell (CUDA/Foreign/Export.hs:231-265).   */
+typedef void *AccHandle;
+typedef void *AccProgram;
+typedef struct {
+    int *shape;
+    void **adata;
+} InputArray;
+typedef struct {
+    int *shape;
+    void **adata;
+    void *stable_ptr;
+} OutputArray;
+
+ACCB_API AccHandle accelerateCreate(int32_t device, void *cu_context);
+ACCB_API void accelerateDestroy(AccHandle hndl);
+ACCB_API void runProgram(AccHandle hndl, AccProgram p, InputArray *in, OutputArray *out);
+ACCB_API void freeOutput(OutputArray *out);
+ACCB_API void freeProgram(AccProgram p);
+/* status of the last runProgram on this handle (the reference has none) */
+ACCB_API int accelerateStatus(AccHandle hndl);
+ACCB_API accb_context *accelerateContext(AccHandle hndl);
+
+/* Program construction.  Values are numbered: 0..ninputs-1 are the program
+ * inputs, each added node returns the id of its result (scan' returns the
+ * body id; the total is id+1).  Shapes of results follow Execute.hs:264-450. */
+typedef struct accb_program accb_program;
+typedef struct accb_value_type {
+    int rank;
+    int ncomp;
+    int comp_bytes[ACCB_ARRAY_MAX_COMP];
+} accb_value_type;
+ACCB_API int accb_program_create(accb_context *ctx, int ninputs, const accb_value_type *input_types,
+                                 accb_program **prog);
+ACCB_API int accb_program_map(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like,
+                              const accb_value_type *out_type, const void *scalars, size_t scalar_bytes);
+ACCB_API int accb_program_fold(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like,
+                               int all, const void *seed, size_t seed_bytes, const accb_value_type *out_type);
+ACCB_API int accb_program_scan(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like,
+                               int direction, int kind, const void *seed, size_t seed_bytes,
+                               const accb_value_type *out_type);
+ACCB_API int accb_program_permute(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like,
+                                  int defaults_id, const accb_value_type *out_type);
+ACCB_API int accb_program_stencil(accb_program *p, accb_kernel *k, int src_id, int boundary,
+                                  const void *constant, size_t constant_bytes, int iters,
+                                  const accb_value_type *out_type);
+ACCB_API int accb_program_outputs(accb_program *p, const int *ids, int nout);
+/* run with DEVICE arrays (what runProgram does) */
+ACCB_API int accb_program_run(accb_program *p, accb_stream stream, const accb_array *inputs,
+                              accb_array *outputs);
+/* run1 with HOST arrays: upload, execute, download (CUDA.hs:307-330,382-389).
+ * host_in[i] / host_out[j] point to one host buffer per component. */
+ACCB_API int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array *host_out);
+ACCB_API int accb_program_destroy(accb_program *p);
+
+/* -------------------------------------------- synthetic benchmark inputs
+ * Index-addressable generators (any shard can produce its own slice).      */
+ACCB_API int accb_gen_uniform_f32(accb_context *ctx, accb_stream stream, float *dst, long long n,
+                                  long long first_index, uint64_t seed, uint64_t stream_id, float lo, float hi);
+ACCB_API int accb_gen_uniform_i32(accb_context *ctx, accb_stream stream, int32_t *dst, long long n,
+                                  long long first_index, uint64_t seed, uint64_t stream_id, int32_t m);
+/* 50 % Zipf (inverse CDF table of `nbins` doubles on the device) / 50 % uniform */
+ACCB_API int accb_gen_zipf_mix_i32(accb_context *ctx, accb_stream stream, int32_t *dst, long long n,
+                                   long long first_index, uint64_t seed, const double *cdf, int nbins);
+/* writes `bytes` of a private buffer larger than L2 to evict cached lines */
+ACCB_API int accb_flush_l2(accb_context *ctx, accb_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ACCB200_H */

@@ -1,0 +1,498 @@
+"""Parity of every skeleton against the CPU oracle, through the C ABI.
+
+Integer results are compared bit-exactly; float32 results against the float64
+oracle with |got - ref| <= RTOL*|ref| + ATOL where RTOL = 1e-5 and the
+absolute floor is stated per test.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-5
+
+# ragged sizes around the vector width (4), the warp (32), the map/fold trip
+# (2048 / 4096) and the scan tile (8192)
+SIZES = [1, 3, 4, 5, 31, 32, 33, 127, 1000, 2047, 2048, 2049, 4095, 4097, 8191, 8192, 8193, 16385, 100003,
+         (1 << 20) + 7]
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def close(got, ref, atol):
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    err = np.abs(got - ref)
+    tol = RTOL * np.abs(ref) + atol
+    assert np.all(err <= tol), f"max excess {np.max(err - tol)} at {np.argmax(err - tol)}"
+
+
+# ------------------------------------------------------------------- map
+@pytest.mark.parametrize("n", [0] + SIZES)
+def test_map_saxpy(ctx, P, torch_cuda, rng, n):
+    t = torch_cuda
+    x, y = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    out = t.empty(n, dtype=t.float32, device="cuda")
+    ctx.map(P.SAXPY, [dev(t, x), dev(t, y)], out, scalars=np.float32(2.5))
+    ctx.sync()
+    ref = np.float32(2.5) * x + y  # one rounding per op, fma contraction aside
+    close(out.cpu().numpy(), ref.astype(np.float64), 1e-6)
+
+
+def test_map_unaligned_falls_back_to_scalar_path(ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    n = 10001
+    x, y = rng.standard_normal(n + 1).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    xd = dev(t, x)[1:]  # 4-byte aligned only
+    out = t.empty(n, dtype=t.float32, device="cuda")
+    ctx.map(P.SAXPY, [xd, dev(t, y)], out, scalars=np.float32(-1.0))
+    ctx.sync()
+    close(out.cpu().numpy(), (-x[1:].astype(np.float64) + y), 1e-6)
+
+
+@pytest.mark.parametrize("n", [1, 1000, 65537])
+def test_generate_from_index(ctx, P, torch_cuda, n):
+    t = torch_cuda
+    out = t.empty(n, dtype=t.int32, device="cuda")
+    ctx.map(P.IOTA_SQ, [], out)
+    ctx.sync()
+    i = np.arange(n, dtype=np.int64)
+    assert np.array_equal(out.cpu().numpy(), (i * i + 1).astype(np.int32))
+
+
+@pytest.mark.parametrize("n", [5, 4096, 70001])
+def test_backpermute_gather(ctx, P, torch_cuda, oracle, rng, n):
+    t = torch_cuda
+    src = rng.integers(-1000, 1000, 3000).astype(np.int32)
+    idx = rng.integers(0, src.size, n).astype(np.int32)
+    out = t.empty(n, dtype=t.int32, device="cuda")
+    ctx.map(P.GATHER, [dev(t, idx), dev(t, src)], out)
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), oracle.backpermute_i32(src, idx))
+
+
+def test_transpose_by_index_arithmetic(ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    a = rng.standard_normal((37, 53)).astype(np.float32)
+    out = t.empty((53, 37), dtype=t.float32, device="cuda")
+    ctx.map(P.TRANSPOSE, [dev(t, a)], out)
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), a.T)
+
+
+@pytest.mark.parametrize("n", [7, 4096, 12345])
+def test_map_mixed_widths(ctx, P, torch_cuda, rng, n):
+    t = torch_cuda
+    a = rng.integers(-128, 128, n).astype(np.int8)
+    b = rng.integers(-30000, 30000, n).astype(np.int16)
+    c = rng.standard_normal(n) * 1000
+    o = t.empty(n, dtype=t.int64, device="cuda")
+    f = t.empty(n, dtype=t.uint8, device="cuda")
+    ctx.map(P.WIDEN, [(dev(t, a), dev(t, b), dev(t, c))], (o, f))
+    ctx.sync()
+    assert np.array_equal(o.cpu().numpy(), a.astype(np.int64) * b + c.astype(np.int64))
+    assert np.array_equal(f.cpu().numpy(), (a > 0).astype(np.uint8))
+
+
+def test_blackscholes(ctx, P, torch_cuda, oracle, workloads):
+    t = torch_cuda
+    n = 1 << 20
+    W = workloads
+    s = W.uniform_f32(W.SEED, W.S_SPOT, n, 5, 30)
+    k = W.uniform_f32(W.SEED, W.S_STRIKE, n, 1, 100)
+    y = W.uniform_f32(W.SEED, W.S_YEARS, n, 0.25, 10)
+    call = t.empty(n, dtype=t.float32, device="cuda")
+    put = t.empty(n, dtype=t.float32, device="cuda")
+    ctx.map(P.BLACKSCHOLES, [(dev(t, s), dev(t, k), dev(t, y))], (call, put))
+    ctx.sync()
+    rc, rp = oracle.blackscholes(s, k, y)
+    # absolute floor: prices reach 100 and float32 rounding of d1 alone moves them by ~1e-5
+    close(call.cpu().numpy(), rc, 2e-5)
+    close(put.cpu().numpy(), rp, 2e-5)
+
+
+# ------------------------------------------------------------------ folds
+@pytest.mark.parametrize("n", SIZES)
+def test_fold_all_dot(ctx, P, torch_cuda, oracle, rng, n):
+    t = torch_cuda
+    x = rng.uniform(-1, 1, n).astype(np.float32)
+    y = rng.uniform(-1, 1, n).astype(np.float32)
+    out = t.zeros(1, dtype=t.float32, device="cuda")
+    ctx.fold_all(P.DOT, [dev(t, x), dev(t, y)], n, out, seed=np.float32(0))
+    ctx.sync()
+    # double accumulation: the result is the correctly rounded float32 of the exact sum
+    close(out.cpu().numpy()[0], oracle.dot_f32(x, y), 0.0 if n > 64 else 1e-7)
+
+
+def test_fold_all_float32_accumulator_is_within_tolerance_of_sum_of_magnitudes(ctx, P, torch_cuda, oracle, rng):
+    t = torch_cuda
+    n = 1 << 22
+    x = rng.uniform(-1, 1, n).astype(np.float32)
+    y = rng.uniform(-1, 1, n).astype(np.float32)
+    out = t.zeros(1, dtype=t.float32, device="cuda")
+    ctx.fold_all(P.DOT_F32ACC, [dev(t, x), dev(t, y)], n, out, seed=np.float32(0))
+    ctx.sync()
+    ref = oracle.dot_f32(x, y)
+    assert abs(out.cpu().numpy()[0] - ref) <= 1e-5 * float(np.sum(np.abs(x.astype(np.float64) * y)))
+
+
+@pytest.mark.parametrize("n", [0, 1, 33, 5000, 300001])
+def test_fold_all_int_with_seed(ctx, P, torch_cuda, rng, n):
+    t = torch_cuda
+    x = rng.integers(-2**31, 2**31 - 1, n).astype(np.int32)
+    out = t.zeros(1, dtype=t.int32, device="cuda")
+    ctx.fold_all(P.SUM_I32, [dev(t, x)], n, out, seed=np.int32(17))
+    ctx.sync()
+    ref = np.int32((int(x.astype(np.int64).sum()) + 17) & 0xffffffff if True else 0)
+    assert out.cpu().numpy()[0] == np.array((int(x.astype(np.int64).sum()) + 17) & 0xffffffff, np.uint32).astype(np.int32)
+
+
+def test_fold1_all_max_and_empty_is_a_bounds_error(ctx, P, accb, torch_cuda, rng):
+    t = torch_cuda
+    x = rng.integers(-10**6, 10**6, 77777).astype(np.int32)
+    out = t.zeros(1, dtype=t.int32, device="cuda")
+    ctx.fold_all(P.MAX_I32, [dev(t, x)], x.size, out)  # no seed: fold1All
+    ctx.sync()
+    assert out.cpu().numpy()[0] == x.max()
+    with pytest.raises(accb.AccbError) as e:
+        ctx.fold_all(P.MAX_I32, [dev(t, x)], 0, out)
+    assert e.value.status == accb.EBOUNDS
+
+
+def test_fold_all_tuple_argmax(ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    x = rng.standard_normal(123457).astype(np.float32)
+    v = t.zeros(1, dtype=t.float32, device="cuda")
+    i = t.zeros(1, dtype=t.int32, device="cuda")
+    ctx.fold_all(P.ARGMAX, [dev(t, x)], x.size, (v, i))
+    ctx.sync()
+    assert i.cpu().numpy()[0] == int(np.argmax(x)) and v.cpu().numpy()[0] == x.max()
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (7, 3), (5, 31), (100, 32), (33, 100), (64, 1000), (9, 2048),
+                                       (17, 4099), (3, 16384), (300, 516)])
+def test_fold_rows(ctx, P, torch_cuda, oracle, rng, rows, cols):
+    t = torch_cuda
+    m = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    out = t.zeros(rows, dtype=t.float32, device="cuda")
+    ctx.fold_dim(P.ROWSUM, [dev(t, m)], rows, cols, out, seed=np.float32(0))
+    ctx.sync()
+    close(out.cpu().numpy(), oracle.fold_rows_f32(m), 1e-7)
+    mi = rng.integers(-2**31, 2**31 - 1, (rows, cols)).astype(np.int32)
+    oi = t.zeros(rows, dtype=t.int32, device="cuda")
+    ctx.fold_dim(P.ROWSUM_I32, [dev(t, mi)], rows, cols, oi, seed=np.int32(-5))
+    ctx.sync()
+    assert np.array_equal(oi.cpu().numpy(), oracle.fold_rows_i32(mi, -5))
+
+
+def test_fold_rows_empty_inner_dimension_yields_seed(ctx, P, accb, torch_cuda):
+    t = torch_cuda
+    out = t.zeros(6, dtype=t.int32, device="cuda")
+    empty = t.zeros(1, dtype=t.int32, device="cuda")
+    ctx.fold_dim(P.ROWSUM_I32, [empty], 6, 0, out, seed=np.int32(42))
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), np.full(6, 42, np.int32))
+    with pytest.raises(accb.AccbError) as e:
+        ctx.fold_dim(P.ROWMIN_I32, [empty], 6, 0, out)  # fold1 of empty rows
+    assert e.value.status == accb.EBOUNDS
+
+
+def test_fold1_rows_min(ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    m = rng.integers(-10**6, 10**6, (50, 777)).astype(np.int32)
+    out = t.zeros(50, dtype=t.int32, device="cuda")
+    ctx.fold_dim(P.ROWMIN_I32, [dev(t, m)], 50, 777, out)
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), m.min(axis=1))
+
+
+def test_fold_seg(ctx, P, torch_cuda, oracle, rng):
+    t = torch_cuda
+    lens = rng.integers(0, 200, 500)
+    lens[::7] = 0  # empty segments yield the seed
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    x = rng.integers(-1000, 1000, int(offs[-1])).astype(np.int32)
+    out = t.zeros(lens.size, dtype=t.int32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_I32, [dev(t, x)], 1, x.size, dev(t, offs), lens.size, out, seed=np.int32(3))
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), oracle.fold_seg_i32(x, offs, 3))
+    xf = rng.uniform(-1, 1, x.size).astype(np.float32)
+    of = t.zeros(lens.size, dtype=t.float32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_F32, [dev(t, xf)], 1, x.size, dev(t, offs), lens.size, of, seed=np.float32(0))
+    ctx.sync()
+    close(of.cpu().numpy(), oracle.fold_seg_f32(xf, offs), 1e-7)
+
+
+def test_fold_seg_rank2(ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    lens = np.array([3, 0, 10, 40, 1])
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    m = rng.integers(-50, 50, (4, int(offs[-1]))).astype(np.int32)
+    out = t.zeros((4, lens.size), dtype=t.int32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_I32, [dev(t, m)], 4, m.shape[1], dev(t, offs), lens.size, out, seed=np.int32(0))
+    ctx.sync()
+    ref = np.stack([[m[r, offs[s]:offs[s + 1]].sum() for s in range(lens.size)] for r in range(4)]).astype(np.int32)
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
+# ------------------------------------------------------------------ scans
+def test_scan_known_answers_from_the_reference_docs(ctx, P, accb, torch_cuda):
+    """CodeGen/PrefixSum.hs:149-153, 162-166, 176-180."""
+    t = torch_cuda
+    ones = t.ones(10, dtype=t.int32, device="cuda")
+    out = t.zeros(11, dtype=t.int32, device="cuda")
+    ctx.scan(P.SCAN_ADD_I32, [ones], 10, out, seed=np.int32(10))
+    ctx.sync()
+    assert out.cpu().tolist() == [10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20]
+    out1 = t.zeros(10, dtype=t.int32, device="cuda")
+    ctx.scan(P.SCAN_ADD_I32, [ones], 10, out1, kind=accb.SCAN_INCLUSIVE)
+    ctx.sync()
+    assert out1.cpu().tolist() == [1, 2, 3, 4, 5, 6, 7, 8, 9, 10]
+    body = t.zeros(10, dtype=t.int32, device="cuda")
+    tot = t.zeros(1, dtype=t.int32, device="cuda")
+    ctx.scan(P.SCAN_ADD_I32, [ones], 10, body, kind=accb.SCAN_PRIME, seed=np.int32(10), total=tot)
+    ctx.sync()
+    assert body.cpu().tolist() == [10, 11, 12, 13, 14, 15, 16, 17, 18, 19] and tot.cpu().tolist() == [20]
+
+
+@pytest.mark.parametrize("n", [0] + SIZES)
+def test_scan_all_six_variants_int32(ctx, P, accb, torch_cuda, oracle, rng, n):
+    t = torch_cuda
+    x = rng.integers(-2**31, 2**31 - 1, n).astype(np.int32)  # wraps: addition is modulo 2^32
+    xd = dev(t, x) if n else t.zeros(1, dtype=t.int32, device="cuda")
+    z = np.int32(-7)
+    out = t.zeros(n + 1, dtype=t.int32, device="cuda")
+    ctx.scan(P.SCAN_ADD_I32, [xd], n, out, seed=z)
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), oracle.scanl_i32(x, z))
+    ctx.scan(P.SCAN_ADD_I32, [xd], n, out, direction=accb.SCAN_RIGHT, seed=z)
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), oracle.scanr_i32(x, z))
+    body = t.zeros(max(n, 1), dtype=t.int32, device="cuda")
+    tot = t.zeros(1, dtype=t.int32, device="cuda")
+    for direction, ref in ((accb.SCAN_LEFT, oracle.scanl_prime_i32), (accb.SCAN_RIGHT, oracle.scanr_prime_i32)):
+        ctx.scan(P.SCAN_ADD_I32, [xd], n, body, direction=direction, kind=accb.SCAN_PRIME, seed=z, total=tot)
+        ctx.sync()
+        rb, rt = ref(x, z)
+        assert np.array_equal(body.cpu().numpy()[:n], rb) and tot.cpu().numpy()[0] == rt
+    if n:
+        for direction, ref in ((accb.SCAN_LEFT, oracle.scanl1_i32), (accb.SCAN_RIGHT, oracle.scanr1_i32)):
+            ctx.scan(P.SCAN_ADD_I32, [xd], n, body, direction=direction, kind=accb.SCAN_INCLUSIVE)
+            ctx.sync()
+            assert np.array_equal(body.cpu().numpy()[:n], ref(x))
+
+
+@pytest.mark.parametrize("n", [1, 100, 8193, 250007])
+def test_scan_non_commutative_pairs_keeps_order(ctx, P, accb, torch_cuda, oracle, rng, n):
+    """Affine-map composition: associative, not commutative, two SoA components."""
+    t = torch_cuda
+    a = rng.integers(0, 2**32, n, dtype=np.uint64).astype(np.uint32) | np.uint32(1)
+    b = rng.integers(0, 2**32, n, dtype=np.uint64).astype(np.uint32)
+    M = 1 << 32
+    f = lambda p, q: ((q[0] * p[0]) % M, (q[0] * p[1] + q[1]) % M)  # p then q
+    items = list(zip(a.tolist(), b.tolist()))
+    ad, bd = dev(t, a.view(np.int32)), dev(t, b.view(np.int32))
+    oa = t.zeros(n + 1, dtype=t.int32, device="cuda")
+    ob = t.zeros(n + 1, dtype=t.int32, device="cuda")
+    seed = (np.uint32(3), np.uint32(5))
+    for direction, dname in ((accb.SCAN_LEFT, "l"), (accb.SCAN_RIGHT, "r")):
+        ctx.scan(P.SCAN_AFFINE, [(ad, bd)], n, (oa, ob), direction=direction, seed=seed)
+        ctx.sync()
+        ref = oracle.scan_generic(items, f, (3, 5), direction=dname, kind="excl") if n <= 8193 else None
+        if ref is not None:
+            got = list(zip(oa.cpu().numpy().view(np.uint32).tolist(), ob.cpu().numpy().view(np.uint32).tolist()))
+            assert got == ref
+    if n > 8193:  # large case: check the recurrence out[i+1] = f(out[i], x[i]) everywhere (left scan)
+        ctx.scan(P.SCAN_AFFINE, [(ad, bd)], n, (oa, ob), seed=seed)
+        ctx.sync()
+        ga = oa.cpu().numpy().view(np.uint32).astype(np.uint64)
+        gb = ob.cpu().numpy().view(np.uint32).astype(np.uint64)
+        A, B = a.astype(np.uint64), b.astype(np.uint64)
+        assert ga[0] == 3 and gb[0] == 5
+        assert np.array_equal(ga[1:], (A * ga[:-1]) % M) and np.array_equal(gb[1:], (A * gb[:-1] + B) % M)
+
+
+@pytest.mark.parametrize("n", [5, 8192, 100001])
+def test_scan_int64_and_float(ctx, P, accb, torch_cuda, oracle, rng, n):
+    t = torch_cuda
+    x = rng.integers(-2**40, 2**40, n).astype(np.int64)
+    out = t.zeros(n + 1, dtype=t.int64, device="cuda")
+    ctx.scan(P.SCAN_ADD_I64, [dev(t, x)], n, out, seed=np.int64(1))
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), np.concatenate([[1], 1 + np.cumsum(x)]))
+    xf = rng.uniform(0, 1, n).astype(np.float32)
+    of = t.zeros(n + 1, dtype=t.float32, device="cuda")
+    ctx.scan(P.SCAN_ADD_F32, [dev(t, xf)], n, of, seed=np.float32(0))
+    ctx.sync()
+    # float32 running sums of positive terms: error grows with the prefix, bound it by eps*log2(n)*prefix
+    ref = oracle.scanl_f32(xf)
+    assert np.all(np.abs(of.cpu().numpy() - ref) <= 1e-5 * np.abs(ref) + 1e-6)
+    xm = rng.integers(-10**9, 10**9, n).astype(np.int32)
+    om = t.zeros(n, dtype=t.int32, device="cuda")
+    ctx.scan(P.SCAN_MAX_I32, [dev(t, xm)], n, om, kind=accb.SCAN_INCLUSIVE)
+    ctx.sync()
+    assert np.array_equal(om.cpu().numpy(), np.maximum.accumulate(xm))
+
+
+def test_scan_back_to_back_launches_share_scratch(ctx, P, accb, torch_cuda, oracle, rng):
+    """Status words are never cleared between launches: epochs must keep them apart."""
+    t = torch_cuda
+    for n in (100000, 30, 250000, 8192, 77):
+        x = rng.integers(0, 16, n).astype(np.int32)
+        out = t.zeros(n + 1, dtype=t.int32, device="cuda")
+        ctx.scan(P.SCAN_ADD_I32, [dev(t, x)], n, out, seed=np.int32(0))
+        a = rng.integers(0, 100, n).astype(np.int64)
+        o64 = t.zeros(n + 1, dtype=t.int64, device="cuda")
+        ctx.scan(P.SCAN_ADD_I64, [dev(t, a)], n, o64, seed=np.int64(0))  # other record layout, same scratch
+        ctx.sync()
+        assert np.array_equal(out.cpu().numpy(), oracle.scanl_i32(x, 0))
+        assert np.array_equal(o64.cpu().numpy()[1:], np.cumsum(a))
+
+
+# ---------------------------------------------------------------- permute
+@pytest.mark.parametrize("n", [0, 1, 33, 4097, 1 << 20])
+def test_histogram(ctx, P, torch_cuda, oracle, workloads, n):
+    t = torch_cuda
+    W = workloads
+    cdf = W.zipf_cdf()
+    keys = W.zipf_mix_keys(W.SEED, n, cdf) if n else np.zeros(0, np.int32)
+    kd = dev(t, keys) if n else t.zeros(1, dtype=t.int32, device="cuda")
+    defaults = t.arange(W.HIST_BINS, dtype=t.int32, device="cuda")  # non-zero defaults must survive
+    ref = oracle.permute_add_i32(keys, W.HIST_BINS, defaults=np.arange(W.HIST_BINS, dtype=np.int32))
+    for spec in (P.HIST, P.HIST_GLOBAL):
+        out = t.zeros(W.HIST_BINS, dtype=t.int32, device="cuda")
+        ctx.permute(spec, [kd], n, out, defaults=defaults)
+        ctx.sync()
+        assert np.array_equal(out.cpu().numpy(), ref)
+
+
+def test_permute_ignores_out_of_range_and_negative_destinations(ctx, P, torch_cuda, oracle, rng):
+    t = torch_cuda
+    keys = rng.integers(-5, 40, 10000).astype(np.int32)  # bins are [0, 32)
+    w = rng.integers(-9, 9, keys.size).astype(np.int32)
+    out = t.zeros(32, dtype=t.int32, device="cuda")
+    ctx.permute(P.HIST_WEIGHTED, [(dev(t, keys), dev(t, w))], keys.size, out, defaults=t.zeros(32, dtype=t.int32, device="cuda"))
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), oracle.permute_add_i32(keys, 32, weights=w))
+
+
+def test_permute_cas_float_max(ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    keys = rng.integers(0, 50, 100000).astype(np.int32)
+    v = rng.standard_normal(keys.size).astype(np.float32)
+    dfl = np.full(50, -1e30, np.float32)
+    out = t.zeros(50, dtype=t.float32, device="cuda")
+    ctx.permute(P.SCATTER_MAX_F32, [(dev(t, keys), dev(t, v))], keys.size, out, defaults=dev(t, dfl))
+    ctx.sync()
+    ref = dfl.copy()
+    np.maximum.at(ref, keys, v)
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
+def test_permute_plain_scatter_is_a_permutation(ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    n = 50000
+    perm = rng.permutation(n).astype(np.int32)
+    v = rng.integers(-10**6, 10**6, n).astype(np.int32)
+    out = t.zeros(n, dtype=t.int32, device="cuda")
+    ctx.permute(P.SCATTER, [(dev(t, perm), dev(t, v))], n, out, defaults=t.zeros(n, dtype=t.int32, device="cuda"))
+    ctx.sync()
+    ref = np.zeros(n, np.int32)
+    ref[perm] = v
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
+def test_permute_tuple_value_under_lock(ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    keys = rng.integers(0, 97, 20000).astype(np.int32)
+    v = rng.integers(-100, 100, keys.size).astype(np.int32)
+    s = t.zeros(97, dtype=t.int32, device="cuda")
+    c = t.zeros(97, dtype=t.int32, device="cuda")
+    z = t.zeros(97, dtype=t.int32, device="cuda")
+    ctx.permute(P.SCATTER_PAIR, [(dev(t, keys), dev(t, v))], keys.size, (s, c), defaults=(z, z))
+    ctx.sync()
+    rs, rc = np.zeros(97, np.int64), np.zeros(97, np.int64)
+    np.add.at(rs, keys, v)
+    np.add.at(rc, keys, 1)
+    assert np.array_equal(s.cpu().numpy(), rs.astype(np.int32)) and np.array_equal(c.cpu().numpy(), rc.astype(np.int32))
+
+
+# ---------------------------------------------------------------- stencil
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
+@pytest.mark.parametrize("shape", [(3, 3), (5, 7), (32, 128), (33, 130), (70, 1031), (257, 64)])
+def test_stencil_blur_all_boundaries(ctx, P, torch_cuda, oracle, workloads, rng, boundary, shape):
+    t = torch_cuda
+    a = rng.uniform(0, 1, shape).astype(np.float32)
+    out = t.zeros(shape, dtype=t.float32, device="cuda")
+    ctx.stencil(P.BLUR, dev(t, a), out, boundary=boundary, constant=np.float32(0.5))
+    ctx.sync()
+    close(out.cpu().numpy(), oracle.stencil2d(a, workloads.BLUR_WEIGHTS, boundary, 0.5), 1e-6)
+
+
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
+def test_stencil_radius2_and_laplace(ctx, P, torch_cuda, oracle, rng, boundary):
+    t = torch_cuda
+    a = rng.uniform(-1, 1, (61, 203)).astype(np.float32)
+    out = t.zeros(a.shape, dtype=t.float32, device="cuda")
+    ctx.stencil(P.BOX5, dev(t, a), out, boundary=boundary, constant=np.float32(-2.0))
+    ctx.sync()
+    close(out.cpu().numpy(), oracle.stencil2d(a, np.full((5, 5), 0.04), boundary, -2.0), 2e-6)
+    lap = np.array([[0, 1, 0], [1, -4, 1], [0, 1, 0]], np.float64)
+    ctx.stencil(P.LAPLACE, dev(t, a), out, boundary=boundary, constant=np.float32(0.0))
+    ctx.sync()
+    close(out.cpu().numpy(), oracle.stencil2d(a, lap, boundary, 0.0), 2e-6)
+
+
+@pytest.mark.parametrize("n", [1, 2, 5, 129, 10007])
+@pytest.mark.parametrize("boundary", ["clamp", "wrap", "constant"])
+def test_stencil_rank1(ctx, P, torch_cuda, oracle, rng, n, boundary):
+    t = torch_cuda
+    if boundary == "wrap" and n < 2:
+        pytest.skip("wrap needs an array at least as large as the stencil radius")
+    a = rng.uniform(0, 1, n).astype(np.float32)
+    out = t.zeros(n, dtype=t.float32, device="cuda")
+    ctx.stencil(P.SMOOTH1D, dev(t, a), out, boundary=boundary, constant=np.float32(1.0))
+    ctx.sync()
+    ref = oracle.stencil2d(a.reshape(1, n), np.array([[0.25, 0.5, 0.25]]), boundary, 1.0).reshape(n)
+    close(out.cpu().numpy(), ref, 1e-6)
+
+
+def test_stencil_iterated_blur_matches_float64_recurrence(ctx, P, torch_cuda, oracle, workloads, rng):
+    t = torch_cuda
+    a = rng.uniform(0, 1, (256, 512)).astype(np.float32)
+    A, B = dev(t, a), t.zeros(a.shape, dtype=t.float32, device="cuda")
+    res = ctx.stencil_iterate(P.BLUR, A, B, 10, boundary="clamp")
+    ctx.sync()
+    close(res.cpu().numpy(), oracle.stencil2d_iter(a, workloads.BLUR_WEIGHTS, 10, "clamp"), 1e-6)
+
+
+def test_stencil2_on_different_extents_uses_the_intersection(ctx, P, torch_cuda, oracle, rng):
+    t = torch_cuda
+    a = rng.uniform(0, 1, (40, 100)).astype(np.float32)
+    b = rng.uniform(0, 1, (37, 120)).astype(np.float32)
+    out = t.zeros((37, 100), dtype=t.float32, device="cuda")
+    ctx.stencil2(P.STENCIL2_SUM, dev(t, a), dev(t, b), out, boundary="clamp")
+    ctx.sync()
+    w1 = np.array([[0, 0, 0], [0.5, 1, 0.5], [0, 0, 0]], np.float64)
+    w2 = np.array([[0, 0.25, 0], [0, -1, 0], [0, 0.25, 0]], np.float64)
+    close(out.cpu().numpy(), oracle.stencil2_2d(a, b, w1, w2, "clamp"), 1e-6)
+
+
+# ------------------------------------------------- generators and programs
+def test_device_generators_match_the_host_definition(ctx, torch_cuda, workloads):
+    t = torch_cuda
+    W = workloads
+    n, first = 100003, 12345
+    f = t.empty(n, dtype=t.float32, device="cuda")
+    ctx.gen_uniform_f32(f, n, first, W.SEED, W.S_SPOT, 5.0, 30.0)
+    i = t.empty(n, dtype=t.int32, device="cuda")
+    ctx.gen_uniform_i32(i, n, first, W.SEED, W.S_SCAN, 16)
+    cdf = W.zipf_cdf()
+    k = t.empty(n, dtype=t.int32, device="cuda")
+    ctx.gen_zipf_mix_i32(k, n, first, W.SEED, dev(t, cdf), cdf.size)
+    ctx.sync()
+    assert np.array_equal(f.cpu().numpy(), W.uniform_f32(W.SEED, W.S_SPOT, n, 5.0, 30.0, first))
+    assert np.array_equal(i.cpu().numpy(), W.uniform_i32(W.SEED, W.S_SCAN, n, 16, first))
+    assert np.array_equal(k.cpu().numpy(), W.zipf_mix_keys(W.SEED, n, cdf, first))
