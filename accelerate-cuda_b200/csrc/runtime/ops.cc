@@ -175,6 +175,8 @@ int accb_map(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_a
              const void *scalars, size_t scalar_bytes, const accb_array *out) {
     LOCK(ctx);
     TRY(check_skeleton(ctx, k, {SK_MAP}, "map"));
+    if (!out) return fail(ctx, ACCB_EINVAL, "null output array");
+    if (array_size(out) == 0) return ACCB_OK; /* nothing to compute; an empty array may have no storage */
     accb_kparams p;
     memset(&p, 0, sizeof p);
     TRY(fill_env(ctx, p, env, nenv));
@@ -342,9 +344,14 @@ int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_
     p.aux[0] = sc->status;
     p.aux[1] = sc->words + 1;
     p.aux[2] = sc->words + 2;
+    /* how the kernel assigns tiles: 0 = by block index, 2 = one ticket per block */
+    const int mode = pr.meta.v[5];
     const int grid = (int)std::max(1LL, ntiles);
-    if (n > 0) sc->scan_ticket += (unsigned)grid; /* every block of the launch takes exactly one ticket */
-    return launch(ctx, pr.fn, entry, grid, pr.block, 0, s, p);
+    /* keep the host's copy of the ticket counter in step with what the launch will draw */
+    if (n > 0 && mode == 2) sc->scan_ticket += (unsigned)grid;
+    /* full tiles are staged in dynamic shared memory by the TMA engine */
+    const size_t smem = (size_t)pr.meta.v[6];
+    return launch(ctx, pr.fn, entry, grid, pr.block, smem, s, p);
 }
 
 /* -------------------------------------------------------------- permute */
@@ -445,7 +452,7 @@ static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, 
     TRY(prepare(ctx, k, entry, 0, &pr));
     int txw = 32;
     while (txw < pr.block && txw * 4 < W) txw *= 2;
-    int rb = 32;
+    int rb = 64;
     if (const char *e = getenv("ACCB_STENCIL_ROWS")) rb = std::max(1, atoi(e));
     const int ty = pr.block / txw;
     p.ip[0] = H;

@@ -85,8 +85,12 @@ __device__ __forceinline__ void map_body(const accb_kparams &p) {
 
 }  // namespace accb
 
+#ifndef ACCB_MAP_CTA
 #define ACCB_MAP_CTA 256
-#define ACCB_MAP_U 2
+#endif
+#ifndef ACCB_MAP_U
+#define ACCB_MAP_U 2 /* vectors per input per thread per trip */
+#endif
 
 /* Entry point named after the reference's kernel (Mapping.hs:53). */
 #define ACCB_INSTANTIATE_MAP(Fn)                                                        \

@@ -6,7 +6,7 @@
  * interval totals, scan of the totals, down-sweep that reads the input a
  * second time; host side scanOp/scan1Op/scan'Op/scanCore, Execute.hs:328-392)
  * by ONE single-pass kernel with decoupled look-back: every element is read
- * once and written once (8 bytes per Int32 element instead of 12).
+ * from DRAM once and written once (8 bytes per Int32 element instead of 12).
  *
  * Semantics (PrefixSum.hs:137-198, Execute.hs:326-362), with all body writes
  * aligned to the input index so that 128-bit stores stay aligned:
@@ -27,14 +27,33 @@
  *   static T get(env, i, in-values...);  static T combine(T, T);
  *   using Out = accb::types<...>;  static void put(T, out-references...);
  *
- * Tile = CTA * ROWS * 4 elements.  A warp owns ROWS "rows" of 128 consecutive
- * elements; lane l of row j holds the 4 elements at 128*j + 4*l, so every
- * load and store instruction of a warp covers 512 contiguous bytes.
- * Tiles are handed out by an atomic ticket (never by blockIdx) so a tile's
- * predecessors are always already running: look-back cannot deadlock however
- * the hardware orders blocks.  The wait on a predecessor is nevertheless
- * bounded: after ACCB_SCAN_SPIN_LIMIT polls the kernel raises the error word
- * and carries on, so the launch always terminates.
+ * One tile of CTA * ROWS * 4 elements per block.  What bounds the kernel is
+ * not the arithmetic but the wait for the predecessors' totals (without it
+ * the same kernel runs at copy speed), so the design keeps as many bytes as
+ * possible in flight per SM while tiles wait:
+ *   - a full, 16-byte aligned tile is brought into SHARED memory by the TMA
+ *     engine (cp.async.bulk, completion on an mbarrier) as the block's first
+ *     action; no registers hold data while the copy or the look-back is
+ *     pending, so six 32 KB tiles are resident per SM;
+ *   - pass 1 over shared memory: thread sums, warp scans, block aggregate,
+ *     which warp 0 publishes at once;
+ *   - warp 0 looks back over its predecessors' status words (each in its own
+ *     128-byte line: hundreds of warps poll them while their owners write);
+ *   - pass 2 over shared memory: final values, 128-bit streaming stores.
+ * A warp owns ROWS "rows" of 128 consecutive elements; lane l of row j holds
+ * the 4 elements at 128*j + 4*l, so shared-memory accesses are conflict-free
+ * and every global store instruction of a warp covers 512 contiguous bytes.
+ * The ragged last tile (first for right scans) and unaligned arrays take a
+ * slower block-scan path with scalar accesses.
+ *
+ * A tile only ever waits for tiles earlier in scan order.  A block's tile is
+ * its block index (blocks of a 1-D grid are dispatched in index order, so the
+ * tiles waited for are resident or done); with ACCB_SCAN_TICKET tiles are
+ * drawn from an atomic counter instead, which makes that order explicit at
+ * the price of an L2 round trip per tile.  Every wait is bounded: after
+ * ACCB_SCAN_SPIN_LIMIT polls (look-back) or ACCB_SCAN_TMA_SPIN_LIMIT tries
+ * (mbarrier) the kernel raises the error word and carries on, so a launch
+ * always terminates.
  *
  * Runtime-owned scratch (never cleared between launches):
  *   aux[0] tile status words, aux[1] ticket counter, aux[2] error word.
@@ -48,16 +67,40 @@
 #pragma once
 #include "../cubits/accb_vec.cuh"
 #include "../cubits/accb_warp.cuh"
+#include "../cubits/accb_tma.cuh"
 #include "fold.cuh"
 
+#ifndef ACCB_SCAN_TMA
+#define ACCB_SCAN_TMA 1 /* 0: hold the tile in registers instead of shared memory */
+#endif
 #ifndef ACCB_SCAN_CTA
-#define ACCB_SCAN_CTA 512
+#define ACCB_SCAN_CTA (ACCB_SCAN_TMA ? 256 : 128)
 #endif
 #ifndef ACCB_SCAN_ROWS
-#define ACCB_SCAN_ROWS 4
+#define ACCB_SCAN_ROWS (ACCB_SCAN_TMA ? 8 : 4)
+#endif
+#ifndef ACCB_SCAN_STATUS_STRIDE
+#define ACCB_SCAN_STATUS_STRIDE 16 /* distance between tile status words, in 8-byte units */
+#endif
+#ifndef ACCB_SCAN_TICKET
+#define ACCB_SCAN_TICKET 0 /* 1: draw tiles from an atomic counter instead of the block index */
+#endif
+#ifndef ACCB_SCAN_DELAY_NS
+#define ACCB_SCAN_DELAY_NS 0 /* pause between two polls of a tile that is not published yet */
+#endif
+/* resident blocks per SM the compiler must leave registers for */
+#ifdef ACCB_SCAN_MINB
+#define ACCB_SCAN_MINB_FOR(Fn) ACCB_SCAN_MINB
+#elif ACCB_SCAN_TMA
+#define ACCB_SCAN_MINB_FOR(Fn) (sizeof(Fn::elem) <= 4 ? 6 : (sizeof(Fn::elem) <= 8 ? 4 : 2))
+#else
+#define ACCB_SCAN_MINB_FOR(Fn) (sizeof(Fn::elem) <= 4 ? 12 : (sizeof(Fn::elem) <= 8 ? 6 : 3))
 #endif
 #ifndef ACCB_SCAN_SPIN_LIMIT
 #define ACCB_SCAN_SPIN_LIMIT (1 << 20)
+#endif
+#ifndef ACCB_SCAN_TMA_SPIN_LIMIT
+#define ACCB_SCAN_TMA_SPIN_LIMIT (1 << 16)
 #endif
 
 namespace accb {
@@ -74,25 +117,30 @@ enum : unsigned { ST_AGG = 1u, ST_PREFIX = 2u };
 
 /* ---- tile status: one 64-bit word {flag, value} when the value fits 32 bits,
  * otherwise {flag | aggregate | prefix} records published with release /
- * acquire ordering. ---- */
+ * acquire ordering.  Neighbouring tiles' words are ACCB_SCAN_STATUS_STRIDE * 8
+ * bytes apart. ---- */
 template <class T, bool PACKED = (sizeof(T) <= 4)>
 struct TileStatus;
 
 template <class T>
 struct TileStatus<T, true> {
-    static constexpr int kBytes = 8;
+    static constexpr int kBytes = 8 * ACCB_SCAN_STATUS_STRIDE;
     unsigned long long *w;
     __device__ __forceinline__ explicit TileStatus(void *base) : w(static_cast<unsigned long long *>(base)) {}
     __device__ __forceinline__ void publish(long long t, unsigned flag, T v) const {
         unsigned bits = 0;
         memcpy(&bits, &v, sizeof(T));
         const unsigned long long word = ((unsigned long long)flag << 32) | bits;
-        asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(w + t), "l"(word) : "memory");
+        asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(w + t * ACCB_SCAN_STATUS_STRIDE), "l"(word)
+                     : "memory");
     }
     /* returns the flag word; value valid when the flag's epoch matches */
     __device__ __forceinline__ unsigned peek(long long t, T &v) const {
         unsigned long long word;
-        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word) : "l"(w + t) : "memory");
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];"
+                     : "=l"(word)
+                     : "l"(w + t * ACCB_SCAN_STATUS_STRIDE)
+                     : "memory");
         const unsigned bits = (unsigned)word;
         memcpy(&v, &bits, sizeof(T));
         return (unsigned)(word >> 32);
@@ -102,7 +150,7 @@ struct TileStatus<T, true> {
 template <class T>
 struct TileStatus<T, false> {
     static_assert(sizeof(T) % 4 == 0 && sizeof(T) <= 32, "scan value types are at most 32 bytes");
-    struct Rec {
+    struct alignas(128) Rec {
         unsigned flag;
         unsigned pad;
         T agg;
@@ -139,6 +187,12 @@ struct ScanOp {
         else
             return Fn::combine(a, b);
     }
+    __device__ __forceinline__ Opt<T> operator()(Opt<T> a, Opt<T> b) const {
+        Opt<T> r;
+        r.have = a.have | b.have;
+        r.v = (a.have && b.have) ? (*this)(a.v, b.v) : (a.have ? a.v : b.v);
+        return r;
+    }
 };
 
 template <class Fn, int... O>
@@ -156,13 +210,140 @@ __device__ __forceinline__ void scan_put_vec(typename Fn::elem (&y)[N], regs<N, 
     for (int k = 0; k < N; ++k) Fn::put(y[k], comp<O>(b)[k]...);
 }
 
-/* One tile, from load to store.  FT: the tile is full and vector-aligned, so
- * every "have" flag below is known at compile time and the warp scans run on
- * bare values. */
-template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL, bool FT>
-__device__ __forceinline__ void scan_tile(const accb_kparams &p, long long t, long long ntiles, long long base,
-                                          long long len, typename Fn::elem *s_warp,
-                                          Opt<typename Fn::elem> *s_prefix) {
+/* ---- decoupled look-back, run by warp 0 of the block that owns tile t.
+ * `agg` is the tile's aggregate.  Publishes the aggregate, gathers the
+ * exclusive prefix of the tile from its predecessors, publishes the inclusive
+ * prefix, writes the total / seed where the host asked for them, and returns
+ * the exclusive prefix (have == 0: the first tile of an unseeded scan). ---- */
+template <class Fn, bool RIGHT>
+__device__ __forceinline__ Opt<typename Fn::elem> scan_lookback(const accb_kparams &p, long long t,
+                                                                long long ntiles, typename Fn::elem agg) {
+    typedef typename Fn::elem T;
+    typedef Opt<T> O;
+    const ScanOp<Fn, RIGHT> op;
+    const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
+    const bool seeded = (p.flags & ACCB_F_HAS_SEED) != 0;
+    const unsigned epoch = (unsigned)p.ip[2];
+    const TileStatus<T> status(p.aux[0]);
+    unsigned int *err = static_cast<unsigned int *>(p.aux[2]);
+    const int lane = lane_id();
+    O pre;
+    pre.have = 0;
+    if (t == 0) {
+        if (seeded) {
+            pre.v = fold_seed<Fn>(p);
+            pre.have = 1;
+        }
+    } else {
+        if (lane == 0) status.publish(t, (epoch << 2) | ST_AGG, agg);
+        long long look = t - 1; /* lane l examines tile look - l */
+        int spins = 0;
+        bool done = false;
+#ifdef ACCB_SCAN_EXPERIMENT_NO_LOOKBACK
+        done = true; /* timing experiment only: results are wrong */
+#endif
+        while (!done) {
+            const long long idx = look - lane;
+            T v;
+            unsigned flag = 0;
+            bool ready = idx < 0;
+            /* every lane polls its own predecessor until it is published */
+            while (true) {
+                if (!ready) {
+                    flag = status.peek(idx, v);
+                    ready = (flag >> 2) == epoch && (flag & 3u) != 0;
+                }
+                if (__all_sync(FULL, ready)) break;
+                __nanosleep(ACCB_SCAN_DELAY_NS);
+                /* give up after the limit, or at once when another tile already gave up */
+                if (++spins > ACCB_SCAN_SPIN_LIMIT ||
+                    ((spins & 255) == 0 && *static_cast<volatile unsigned int *>(err) != 0u)) {
+                    if (lane == 0) atomicExch(err, 1u);
+                    if (!ready) flag = (epoch << 2) | ST_PREFIX; /* the result is flagged invalid */
+                    ready = true;
+                }
+            }
+            const bool is_pre = idx >= 0 && (flag & 3u) == ST_PREFIX;
+            const unsigned pm = __ballot_sync(FULL, is_pre);
+            const int first = pm ? __ffs(pm) - 1 : 32; /* nearest tile with a full prefix */
+            O win;
+            win.v = v;
+            win.have = (idx >= 0) && (lane <= first);
+            /* lanes hold ever earlier tiles: combine far-to-near */
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                O o = shfl_down(win, d);
+                if (lane + d < 32) win = op(o, win);
+            }
+            win = shfl_idx(win, 0);
+            pre = op(win, pre);
+            done = pm != 0 || look < 32;
+            look -= 32;
+        }
+    }
+    if (lane == 0) {
+        const T incl = pre.have ? op(pre.v, agg) : agg;
+        status.publish(t, (epoch << 2) | ST_PREFIX, incl);
+        if (t == ntiles - 1 && p.ip[3] >= 0) scan_put_sum<Fn>(p, p.ip[3], incl, oseq);
+        if (t == 0 && p.ip[4] >= 0 && seeded) scan_put_sum<Fn>(p, p.ip[4], fold_seed<Fn>(p), oseq);
+    }
+    return pre;
+}
+
+/* warp prefix and block aggregate from the per-warp totals in shared memory
+ * (all NW warps hold data) */
+template <class Fn, bool RIGHT, int NW>
+__device__ __forceinline__ void scan_block_level(const typename Fn::elem *s_warp, int w,
+                                                 Opt<typename Fn::elem> &wpre, typename Fn::elem &agg) {
+    const ScanOp<Fn, RIGHT> op;
+    wpre.have = 0;
+    agg = s_warp[0];
+#pragma unroll
+    for (int k = 0; k < NW; ++k) {
+        if (k < w) {
+            wpre.v = wpre.have ? op(wpre.v, s_warp[k]) : s_warp[k];
+            wpre.have = 1;
+        }
+        if (k > 0) agg = op(agg, s_warp[k]);
+    }
+}
+
+/* ---- full, aligned tile.  SMEM: the raw inputs sit in shared memory (put
+ * there by the TMA engine) and are read twice; otherwise they are loaded into
+ * registers once and kept there. ---- */
+template <class L, int I, int TILE>
+struct smem_offset {
+    static constexpr int value = smem_offset<L, I - 1, TILE>::value +
+                                 ((TILE * (int)sizeof(typename type_at<I - 1, L>::type) + 127) / 128) * 128;
+};
+template <class L, int TILE>
+struct smem_offset<L, 0, TILE> {
+    static constexpr int value = 0;
+};
+
+template <class L, int TILE, int... I>
+__device__ __forceinline__ void smem_load_row(const unsigned char *s, int vi, regs<V, L> &r,
+                                              std::integer_sequence<int, I...>) {
+    (load4<Cache::Default>(reinterpret_cast<const typename type_at<I, L>::type *>(s + smem_offset<L, I, TILE>::value),
+                           vi, comp<I>(r)),
+     ...);
+}
+
+template <class L, int TILE, int... I>
+__device__ __forceinline__ void smem_issue_tma(unsigned char *s, const void *const *slots, long long base,
+                                               unsigned long long *bar, std::integer_sequence<int, I...>) {
+    constexpr unsigned total = (unsigned)((TILE * (int)sizeof(typename type_at<I, L>::type)) + ... + 0);
+    mbar_expect_tx(bar, total);
+    (bulk_g2s(s + smem_offset<L, I, TILE>::value,
+              static_cast<const typename type_at<I, L>::type *>(slots[I]) + base,
+              (unsigned)(TILE * sizeof(typename type_at<I, L>::type)), bar),
+     ...);
+}
+
+template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL, bool SMEM>
+__device__ __forceinline__ void scan_tile_full(const accb_kparams &p, long long t, long long ntiles, long long base,
+                                               typename Fn::elem *s_warp, Opt<typename Fn::elem> *s_prefix,
+                                               const unsigned char *s_data) {
     typedef typename Fn::elem T;
     typedef typename Fn::In In;
     typedef typename Fn::Out Out;
@@ -174,233 +355,190 @@ __device__ __forceinline__ void scan_tile(const accb_kparams &p, long long t, lo
     const Env env(p);
     const auto iseq = std::make_integer_sequence<int, In::size>();
     const auto oseq = std::make_integer_sequence<int, Out::size>();
-    const bool seeded = (p.flags & ACCB_F_HAS_SEED) != 0;
-    const unsigned epoch = (unsigned)p.ip[2];
-    const TileStatus<T> status(p.aux[0]);
-    unsigned int *err = static_cast<unsigned int *>(p.aux[2]);
     const int lane = lane_id(), w = warp_id();
-    auto oc = [&](O a, O b) {
-        O r;
-        r.have = a.have | b.have;
-        r.v = (a.have && b.have) ? op(a.v, b.v) : (a.have ? a.v : b.v);
-        return r;
+
+    /* x(j) = the 4 values of row j in scan order: logical element
+     * (w*ROWS*128 + j*128 + lane*4 + k) of the tile */
+    regs<V, In> a[SMEM ? 1 : ROWS];
+    if constexpr (!SMEM) {
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            const int lv = w * (ROWS * 32) + j * 32 + lane;
+            load_all(p.in, base / V + (RIGHT ? (TILE_VECS - 1 - lv) : lv), a[j]);
+        }
+    }
+    auto row = [&](int j, T (&x)[V]) {
+        const int lv = w * (ROWS * 32) + j * 32 + lane;
+        const int tv = RIGHT ? (TILE_VECS - 1 - lv) : lv; /* vector index inside the tile, in memory order */
+        T tmp[V];
+        if constexpr (SMEM) {
+            smem_load_row<In, TILE>(s_data, tv, a[0], iseq);
+            fold_get<Fn>(env, base + (long long)tv * V, a[0], tmp, iseq);
+        } else {
+            fold_get<Fn>(env, base + (long long)tv * V, a[j], tmp, iseq);
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) x[k] = RIGHT ? tmp[V - 1 - k] : tmp[k];
     };
 
-    /* ---- load: x[j][k] is logical element (w*ROWS*128 + j*128 + lane*4 + k) of the tile ---- */
-    T x[ROWS][V];
-    int valid[ROWS][V];
-    if constexpr (FT) {
-        regs<V, In> a[ROWS];
-#pragma unroll
-        for (int j = 0; j < ROWS; ++j) {
-            const int lv = w * (ROWS * 32) + j * 32 + lane;
-            const long long pv = base / V + (RIGHT ? (TILE_VECS - 1 - lv) : lv);
-            load_all(p.in, pv, a[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < ROWS; ++j) {
-            const int lv = w * (ROWS * 32) + j * 32 + lane;
-            const long long pv = base / V + (RIGHT ? (TILE_VECS - 1 - lv) : lv);
-            T tmp[V];
-            fold_get<Fn>(env, pv * V, a[j], tmp, iseq);
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                x[j][k] = RIGHT ? tmp[V - 1 - k] : tmp[k];
-                valid[j][k] = 1;
-            }
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < ROWS; ++j)
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                const int q = (w * (ROWS * 32) + j * 32 + lane) * V + k;
-                /* right scans walk the tile backwards; a ragged tile is then
-                 * the first in scan order and its valid part sits at the low
-                 * physical offsets */
-                const long long off = RIGHT ? (long long)(TILE - 1 - q) : (long long)q;
-                valid[j][k] = off < len;
-                if (valid[j][k]) {
-                    regs<1, In> a;
-                    T tmp[1];
-                    load_one(p.in, base + off, a);
-                    fold_get<Fn>(env, base + off, a, tmp, iseq);
-                    x[j][k] = tmp[0];
-                }
-            }
-    }
-
-    /* ---- thread-local sums, then a warp scan per row ---- */
-    O ex[ROWS]; /* exclusive prefix of this thread's vector inside the warp chunk */
-    O wtot;     /* total of the warp chunk */
-    wtot.have = 0;
+    /* ---- pass 1: thread sums, a warp scan per row ---- */
+    T ex[ROWS]; /* exclusive prefix of this thread's vector inside the warp chunk; none for (j, lane) == (0, 0) */
+    T wtot;     /* total of the warp chunk */
 #pragma unroll
     for (int j = 0; j < ROWS; ++j) {
-        if constexpr (FT) {
-            const T s = op(op(x[j][0], x[j][1]), op(x[j][2], x[j][3]));
-            const T inc = warp_scan_inclusive(s, op);
-            const T up = shfl_up(inc, 1);
-            const T last = shfl_idx(inc, 31);
-            if (j == 0) {
-                ex[j].v = up;
-                ex[j].have = lane > 0;
-                wtot.v = last;
-            } else {
-                ex[j].v = lane > 0 ? op(wtot.v, up) : wtot.v;
-                ex[j].have = 1;
-                wtot.v = op(wtot.v, last);
-            }
-            wtot.have = 1;
+        T x[V];
+        row(j, x);
+        const T s = op(op(x[0], x[1]), op(x[2], x[3]));
+        const T inc = warp_scan_inclusive(s, op);
+        const T up = shfl_up(inc, 1);
+        const T last = shfl_idx(inc, 31);
+        if (j == 0) {
+            ex[j] = up;
+            wtot = last;
         } else {
-            O s;
-            s.have = 0;
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                O e;
-                e.v = x[j][k];
-                e.have = valid[j][k];
-                s = oc(s, e);
-            }
-            O inc = warp_scan_inclusive(s, oc);
-            O up = shfl_up(inc, 1);
-            if (lane == 0) up.have = 0;
-            ex[j] = oc(wtot, up);
-            wtot = oc(wtot, shfl_idx(inc, 31));
+            ex[j] = lane > 0 ? op(wtot, up) : wtot;
+            wtot = op(wtot, last);
         }
     }
 
-    /* ---- block level ---- */
-    if (lane == 0) s_warp[w] = wtot.v;
+    /* ---- block level, look-back ---- */
+    if (lane == 0) s_warp[w] = wtot;
     __syncthreads();
-    /* warps holding data: the first nwv for a left scan; for a right scan of
-     * a ragged tile the EARLY logical positions are the empty ones */
-    const int nwv = FT ? NW : (int)((len + ROWS * 128 - 1) / (ROWS * 128));
-    const int w_lo = RIGHT ? NW - nwv : 0, w_hi = RIGHT ? NW : nwv;
-    O wpre, agg;
-    wpre.have = 0;
-    agg.have = 0;
-#pragma unroll
-    for (int k = 0; k < NW; ++k) {
-        O e;
-        e.v = s_warp[k];
-        e.have = FT ? 1 : (k >= w_lo && k < w_hi);
-        if (k < w) wpre = oc(wpre, e);
-        agg = oc(agg, e);
-    }
-
-    /* ---- decoupled look-back (warp 0) ---- */
+    O wpre;
+    T agg;
+    scan_block_level<Fn, RIGHT, NW>(s_warp, w, wpre, agg);
     if (w == 0) {
-        O pre;
-        pre.have = 0;
-        if (t == 0) {
-            if (seeded) {
-                pre.v = fold_seed<Fn>(p);
-                pre.have = 1;
-            }
-            if (lane == 0) status.publish(0, (epoch << 2) | ST_PREFIX, oc(pre, agg).v);
-        } else {
-            if (lane == 0) status.publish(t, (epoch << 2) | ST_AGG, agg.v);
-            long long look = t - 1;
-            int spins = 0;
-            bool done = false;
-            while (!done) {
-                const long long idx = look - lane;
-                T v;
-                unsigned flag = 0;
-                bool ready = idx < 0;
-                /* every lane polls its own predecessor until it is published */
-                while (true) {
-                    if (!ready) {
-                        flag = status.peek(idx, v);
-                        ready = (flag >> 2) == epoch && (flag & 3u) != 0;
-                    }
-                    if (__all_sync(FULL, ready)) break;
-                    /* give up after the limit, or at once when another tile already gave up */
-                    if (++spins > ACCB_SCAN_SPIN_LIMIT ||
-                        ((spins & 255) == 0 && *static_cast<volatile unsigned int *>(err) != 0u)) {
-                        if (lane == 0) atomicExch(err, 1u);
-                        if (!ready) flag = (epoch << 2) | ST_PREFIX; /* give up; the result is flagged invalid */
-                        ready = true;
-                    }
-                }
-                const bool is_pre = idx >= 0 && (flag & 3u) == ST_PREFIX;
-                const unsigned pm = __ballot_sync(FULL, is_pre);
-                const int first = pm ? __ffs(pm) - 1 : 32; /* nearest tile with a full prefix */
-                O win;
-                win.v = v;
-                win.have = (idx >= 0) && (lane <= first);
-                /* lanes hold tiles look, look-1, ...: combine far-to-near */
-#pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    O o = shfl_down(win, d);
-                    if (lane + d < 32) win = oc(o, win);
-                }
-                win = shfl_idx(win, 0);
-                pre = oc(win, pre);
-                done = pm != 0 || look < 32;
-                look -= 32;
-            }
-            if (lane == 0) status.publish(t, (epoch << 2) | ST_PREFIX, oc(pre, agg).v);
-        }
-        if (lane == 0) {
-            *s_prefix = pre;
-            if (t == ntiles - 1 && p.ip[3] >= 0) scan_put_sum<Fn>(p, p.ip[3], oc(pre, agg).v, oseq);
-            if (t == 0 && p.ip[4] >= 0 && seeded) scan_put_sum<Fn>(p, p.ip[4], fold_seed<Fn>(p), oseq);
-        }
+        const O pre = scan_lookback<Fn, RIGHT>(p, t, ntiles, agg);
+        if (lane == 0) *s_prefix = pre;
     }
     __syncthreads();
-    const O tile_pre = oc(*s_prefix, wpre);
+    const O tile_pre = op(*s_prefix, wpre);
 
-    /* ---- final values and store ---- */
+    /* ---- pass 2: final values and store ---- */
 #pragma unroll
     for (int j = 0; j < ROWS; ++j) {
-        O run = oc(tile_pre, ex[j]);
-        if constexpr (FT) {
-            T y[V];
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                const T nxt = run.have ? op(run.v, x[j][k]) : x[j][k];
-                y[RIGHT ? V - 1 - k : k] = INCL ? nxt : run.v;
-                run.v = nxt;
-                run.have = 1;
-            }
-            regs<V, Out> b;
-            scan_put_vec<Fn>(y, b, oseq);
-            const int lv = w * (ROWS * 32) + j * 32 + lane;
-            const long long pv = base / V + (RIGHT ? (TILE_VECS - 1 - lv) : lv);
-            store_all(p.out, pv, b);
-        } else {
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                const int q = (w * (ROWS * 32) + j * 32 + lane) * V + k;
-                const long long off = RIGHT ? (long long)(TILE - 1 - q) : (long long)q;
-                if (valid[j][k]) {
-                    const T nxt = run.have ? op(run.v, x[j][k]) : x[j][k];
-                    regs<1, Out> b;
-                    T y[1] = {INCL ? nxt : run.v};
-                    scan_put_vec<Fn>(y, b, oseq);
-                    store_one(p.out, base + off, b);
-                    run.v = nxt;
-                    run.have = 1;
-                }
-            }
+        T x[V];
+        row(j, x);
+        O run = tile_pre;
+        if (j > 0 || lane > 0) {
+            run.v = run.have ? op(run.v, ex[j]) : ex[j];
+            run.have = 1;
         }
+        T y[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            const T nxt = run.have ? op(run.v, x[k]) : x[k];
+            y[RIGHT ? V - 1 - k : k] = INCL ? nxt : run.v;
+            run.v = nxt;
+            run.have = 1;
+        }
+        regs<V, Out> b;
+        scan_put_vec<Fn>(y, b, oseq);
+        const int lv = w * (ROWS * 32) + j * 32 + lane;
+        store_all(p.out, base / V + (RIGHT ? (TILE_VECS - 1 - lv) : lv), b);
     }
 }
 
+/* ---- ragged tile (len <= TILE valid elements at `base`) or unaligned
+ * arrays: scalar accesses, the tile walked twice in chunks of CTA elements
+ * (once for the aggregate, once -- after the look-back -- for the values). ---- */
 template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL>
+__device__ __forceinline__ void scan_tile_ragged(const accb_kparams &p, long long t, long long ntiles,
+                                                 long long base, long long len,
+                                                 Opt<typename Fn::elem> *s_opt /* CTA/32 + 1 slots */) {
+    typedef typename Fn::elem T;
+    typedef typename Fn::In In;
+    typedef typename Fn::Out Out;
+    typedef Opt<T> O;
+    constexpr int NW = CTA / 32;
+    const ScanOp<Fn, RIGHT> op;
+    const Env env(p);
+    const auto iseq = std::make_integer_sequence<int, In::size>();
+    const auto oseq = std::make_integer_sequence<int, Out::size>();
+    const int lane = lane_id(), w = warp_id();
+    /* logical position q (scan order) <-> memory offset */
+    auto fetch = [&](long long q) {
+        O e;
+        e.have = q < len;
+        if (e.have) {
+            const long long i = base + (RIGHT ? len - 1 - q : q);
+            regs<1, In> a;
+            T tmp[1];
+            load_one(p.in, i, a);
+            fold_get<Fn>(env, i, a, tmp, iseq);
+            e.v = tmp[0];
+        }
+        return e;
+    };
+
+    /* aggregate of the tile, chunk by chunk so that value order is kept */
+    O carry;
+    carry.have = 0;
+    const long long nchunk = (len + CTA - 1) / CTA;
+    for (long long c = 0; c < nchunk; ++c) {
+        O e = fetch(c * CTA + threadIdx.x);
+        O inc = warp_scan_inclusive(e, op);
+        if (lane == 31) s_opt[w] = inc;
+        __syncthreads();
+        O tot;
+        tot.have = 0;
+#pragma unroll
+        for (int k = 0; k < NW; ++k) tot = op(tot, s_opt[k]);
+        carry = op(carry, tot);
+        __syncthreads();
+    }
+    if (w == 0) {
+        const O pre = scan_lookback<Fn, RIGHT>(p, t, ntiles, carry.v); /* len >= 1, so carry.have */
+        if (lane == 0) s_opt[NW] = pre;
+    }
+    __syncthreads();
+    O run = s_opt[NW]; /* exclusive prefix of the chunk being written */
+    __syncthreads();
+    for (long long c = 0; c < nchunk; ++c) {
+        const long long q = c * CTA + threadIdx.x;
+        O e = fetch(q);
+        O inc = warp_scan_inclusive(e, op);
+        if (lane == 31) s_opt[w] = inc;
+        __syncthreads();
+        O before = run; /* everything ahead of this warp */
+        O tot;
+        tot.have = 0;
+#pragma unroll
+        for (int k = 0; k < NW; ++k) {
+            if (k < w) before = op(before, s_opt[k]);
+            tot = op(tot, s_opt[k]);
+        }
+        O up = shfl_up(inc, 1);
+        if (lane == 0) up.have = 0;
+        const O excl = op(before, up);
+        if (e.have) {
+            const T incl = excl.have ? op(excl.v, e.v) : e.v;
+            T y[1] = {INCL ? incl : excl.v};
+            regs<1, Out> b;
+            scan_put_vec<Fn>(y, b, oseq);
+            store_one(p.out, base + (RIGHT ? len - 1 - q : q), b);
+        }
+        run = op(run, tot);
+        __syncthreads();
+    }
+}
+
+template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL, bool SMEM>
 __device__ __forceinline__ void scan_body(const accb_kparams &p) {
     typedef typename Fn::elem T;
+    typedef typename Fn::In In;
     constexpr int NW = CTA / 32;
     constexpr int TILE = CTA * ROWS * V;
+    const auto iseq = std::make_integer_sequence<int, In::size>();
     const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
     __shared__ T s_warp[NW];
-    __shared__ Opt<T> s_prefix;
+    __shared__ Opt<T> s_opt[NW + 1];
     __shared__ long long s_tile;
+    __shared__ __align__(8) unsigned long long s_bar;
+    extern __shared__ __align__(128) unsigned char s_data[];
 
     const long long n = p.n;
     const long long ntiles = p.ip[0];
-    unsigned int *ticket = static_cast<unsigned int *>(p.aux[1]);
 
     if (n == 0) { /* empty input: only the seed survives */
         if (blockIdx.x == 0 && threadIdx.x == 0 && (p.flags & ACCB_F_HAS_SEED)) {
@@ -411,39 +549,62 @@ __device__ __forceinline__ void scan_body(const accb_kparams &p) {
         return;
     }
 
-    if (threadIdx.x == 0) s_tile = (long long)(unsigned)(atomicAdd(ticket, 1u) - (unsigned)p.ip[1]);
-    __syncthreads();
-    const long long t = s_tile; /* position in scan order */
+    long long t; /* position in scan order */
+    if constexpr (ACCB_SCAN_TICKET != 0) {
+        unsigned int *ticket = static_cast<unsigned int *>(p.aux[1]);
+        if (threadIdx.x == 0) s_tile = (long long)(unsigned)(atomicAdd(ticket, 1u) - (unsigned)p.ip[1]);
+        __syncthreads();
+        t = s_tile;
+    } else {
+        t = blockIdx.x;
+    }
     if (t >= ntiles) return;
-    const long long pt = RIGHT ? ntiles - 1 - t : t; /* position in memory */
-    const long long base = pt * TILE;
-    const long long len = (n - base) < TILE ? (n - base) : TILE;
-    if ((p.flags & ACCB_F_VEC) && len == TILE)
-        scan_tile<Fn, CTA, ROWS, RIGHT, INCL, true>(p, t, ntiles, base, len, s_warp, &s_prefix);
-    else
-        scan_tile<Fn, CTA, ROWS, RIGHT, INCL, false>(p, t, ntiles, base, len, s_warp, &s_prefix);
+    const long long base = (RIGHT ? ntiles - 1 - t : t) * TILE; /* position in memory */
+    const long long len = (n - base) < TILE ? (n - base) : (long long)TILE;
+    const bool full = (p.flags & ACCB_F_VEC) != 0 && len == TILE;
+
+    if (!full) {
+        scan_tile_ragged<Fn, CTA, ROWS, RIGHT, INCL>(p, t, ntiles, base, len, s_opt);
+        return;
+    }
+    if constexpr (SMEM) {
+        unsigned int *err = static_cast<unsigned int *>(p.aux[2]);
+        /* the whole tile by TMA, completion counted in bytes on the mbarrier */
+        if (threadIdx.x == 0) {
+            mbar_init(&s_bar, 1);
+            fence_mbar_init();
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) smem_issue_tma<In, TILE>(s_data, p.in, base, &s_bar, iseq);
+        int tries = 0;
+        while (!mbar_try_wait(&s_bar, 0)) {
+            if (++tries > ACCB_SCAN_TMA_SPIN_LIMIT) { /* bounded: flag the result invalid and go on */
+                atomicExch(err, 1u);
+                break;
+            }
+        }
+    }
+    scan_tile_full<Fn, CTA, ROWS, RIGHT, INCL, SMEM>(p, t, ntiles, base, s_warp, &s_opt[NW], s_data);
 }
 
 }  // namespace accb
 
 /* Entry points named after the reference's kernels (PrefixSum.hs:208,313):
  * exclusive and inclusive, left and right. */
-#define ACCB_INSTANTIATE_SCAN(Fn)                                                              \
-    ACCB_META(5, ACCB_SCAN_CTA, accb::TileStatus<Fn::elem>::kBytes,                            \
-              ACCB_SCAN_CTA * ACCB_SCAN_ROWS * 4, ACCB_SCAN_ROWS, 0)                           \
-    extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA)                                \
-        scanl(const __grid_constant__ accb_kparams p) {                                        \
-        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS, false, false>(p);                   \
-    }                                                                                          \
-    extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA)                                \
-        scanl1(const __grid_constant__ accb_kparams p) {                                       \
-        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS, false, true>(p);                    \
-    }                                                                                          \
-    extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA)                                \
-        scanr(const __grid_constant__ accb_kparams p) {                                        \
-        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS, true, false>(p);                    \
-    }                                                                                          \
-    extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA)                                \
-        scanr1(const __grid_constant__ accb_kparams p) {                                       \
-        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS, true, true>(p);                     \
+#define ACCB_SCAN_ENTRY(Fn, name, right, incl)                                                 \
+    extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA, ACCB_SCAN_MINB_FOR(Fn))        \
+        name(const __grid_constant__ accb_kparams p) {                                         \
+        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS, right, incl, ACCB_SCAN_TMA != 0>(p); \
     }
+
+/* metadata: record bytes, tile elements, rows, ticket mode, dynamic shared memory */
+#define ACCB_INSTANTIATE_SCAN(Fn)                                                              \
+    ACCB_META7(5, ACCB_SCAN_CTA, accb::TileStatus<Fn::elem>::kBytes,                           \
+               ACCB_SCAN_CTA * ACCB_SCAN_ROWS * 4, ACCB_SCAN_ROWS, ACCB_SCAN_TICKET ? 2 : 0,   \
+               ACCB_SCAN_TMA ? (accb::smem_offset<Fn::In, Fn::In::size,                        \
+                                                  ACCB_SCAN_CTA * ACCB_SCAN_ROWS * 4>::value)  \
+                             : 0)                                                              \
+    ACCB_SCAN_ENTRY(Fn, scanl, false, false)                                                   \
+    ACCB_SCAN_ENTRY(Fn, scanl1, false, true)                                                   \
+    ACCB_SCAN_ENTRY(Fn, scanr, true, false)                                                    \
+    ACCB_SCAN_ENTRY(Fn, scanr1, true, true)

@@ -40,6 +40,12 @@
 #ifndef ACCB_STENCIL_CTA
 #define ACCB_STENCIL_CTA 256
 #endif
+#ifndef ACCB_STENCIL_MINB
+#define ACCB_STENCIL_MINB 4 /* resident blocks per SM the compiler must leave registers for */
+#endif
+#ifndef ACCB_STENCIL_ROWS_IN_FLIGHT
+#define ACCB_STENCIL_ROWS_IN_FLIGHT 2 /* rows whose loads are issued before the first is used */
+#endif
 
 namespace accb {
 
@@ -82,37 +88,184 @@ struct Source {
     }
 };
 
-/* Load this thread's piece of row y (raw index) of `src`: the 4 centre columns
- * x0..x0+3 in r[RX..RX+3], halos in r[0..RX) and r[RX+4..]. */
+/* What a thread reads from memory for one row: its 4 centre columns and, only
+ * for lanes whose neighbour cannot supply them (warp edge, array edge), the
+ * halo columns.  Issuing is kept apart from using so that the loads of several
+ * rows can be in flight at once. */
 template <class T, int RX>
-__device__ __forceinline__ void load_row(const Source<T> &s, int y, int x0, T (&r)[4 + 2 * RX]) {
-    const int yy = bound_coord(y, s.h, s.mode);
+struct RowRaw {
     T c[V];
-    const bool inside = x0 + V <= s.w;
-    if (yy >= 0 && inside && s.vec_ok) {
-        load4<Cache::Default>(s.base, ((long long)yy * s.w + x0) / V, c);
+    T l[RX > 0 ? RX : 1], r[RX > 0 ? RX : 1];
+};
+
+/* A thread's columns, fixed for a whole band: where its halo columns come
+ * from is decided once here (boundary mapping in x included), not per row. */
+template <int RX>
+struct Cols {
+    int x0;
+    bool active;  /* x0 < w */
+    bool vec;     /* the 4 centre columns are one aligned 16-byte load */
+    bool l_ok;    /* left halo comes from lane-1 */
+    bool r_ok;    /* right halo comes from lane+1 */
+    int xl[RX > 0 ? RX : 1], xr[RX > 0 ? RX : 1]; /* mapped halo columns when read from memory (-1: constant) */
+    int xc[V];    /* mapped centre columns for a ragged or unaligned vector */
+};
+
+template <class T, int RX>
+__device__ __forceinline__ Cols<RX> make_cols(const Source<T> &s, int x0) {
+    Cols<RX> c;
+    const int lane = lane_id();
+    c.x0 = x0;
+    c.active = x0 < s.w;
+    c.vec = s.vec_ok && x0 + V <= s.w;
+    c.l_ok = lane > 0 && x0 > 0;
+    c.r_ok = lane < 31 && x0 + 2 * V <= s.w;
+#pragma unroll
+    for (int k = 0; k < V; ++k) c.xc[k] = bound_coord(x0 + k, s.w, s.mode);
+#pragma unroll
+    for (int d = 0; d < RX; ++d) {
+        c.xl[d] = bound_coord(x0 - RX + d, s.w, s.mode);
+        c.xr[d] = bound_coord(x0 + V + d, s.w, s.mode);
+    }
+    return c;
+}
+
+template <class T, int RX>
+__device__ __forceinline__ void issue_row(const Source<T> &s, int y, const Cols<RX> &c, RowRaw<T, RX> &raw) {
+    const int yy = bound_coord(y, s.h, s.mode);
+    const T *row = s.base + (long long)(yy < 0 ? 0 : yy) * s.w;
+    if (yy >= 0 && c.vec) {
+        load4<Cache::Default>(row, c.x0 / V, raw.c);
     } else {
 #pragma unroll
-        for (int k = 0; k < V; ++k) c[k] = x0 < s.w ? s.at(yy, x0 + k) : s.cval;
+        for (int k = 0; k < V; ++k) raw.c[k] = (c.active && yy >= 0 && c.xc[k] >= 0) ? row[c.xc[k]] : s.cval;
     }
-#pragma unroll
-    for (int k = 0; k < V; ++k) r[RX + k] = c[k];
     if constexpr (RX > 0) {
-        const int lane = lane_id();
-        /* neighbours' centre vectors; every lane takes part in the shuffles */
-        T lf[RX], rt[RX];
-#pragma unroll
-        for (int d = 0; d < RX; ++d) {
-            lf[d] = shfl_up(c[V - RX + d], 1);   /* columns x0-RX+d */
-            rt[d] = shfl_down(c[d], 1);          /* columns x0+4+d */
-        }
-        const bool l_ok = lane > 0 && x0 > 0;
-        const bool r_ok = lane < 31 && x0 + 2 * V <= s.w;
-        if (x0 < s.w) {
+        if (c.active && !(c.l_ok && c.r_ok)) { /* only warp-edge and array-edge lanes */
 #pragma unroll
             for (int d = 0; d < RX; ++d) {
-                r[d] = l_ok ? lf[d] : s.at(yy, x0 - RX + d);
-                r[RX + V + d] = r_ok ? rt[d] : s.at(yy, x0 + V + d);
+                if (!c.l_ok) raw.l[d] = (yy >= 0 && c.xl[d] >= 0) ? row[c.xl[d]] : s.cval;
+                if (!c.r_ok) raw.r[d] = (yy >= 0 && c.xr[d] >= 0) ? row[c.xr[d]] : s.cval;
+            }
+        }
+    }
+}
+
+/* Complete a row: centre columns x0..x0+3 in r[RX..RX+3], halos in r[0..RX)
+ * and r[RX+4..], taken from the neighbouring lanes where they hold them.
+ * Every lane of the warp takes part in the shuffles. */
+template <class T, int RX>
+__device__ __forceinline__ void finish_row(const Cols<RX> &c, const RowRaw<T, RX> &raw, T (&r)[4 + 2 * RX]) {
+#pragma unroll
+    for (int k = 0; k < V; ++k) r[RX + k] = raw.c[k];
+    if constexpr (RX > 0) {
+#pragma unroll
+        for (int d = 0; d < RX; ++d) {
+            const T lf = shfl_up(raw.c[V - RX + d], 1); /* columns x0-RX+d */
+            const T rt = shfl_down(raw.c[d], 1);        /* columns x0+4+d */
+            r[d] = c.l_ok ? lf : raw.l[d];
+            r[RX + V + d] = c.r_ok ? rt : raw.r[d];
+        }
+    }
+}
+
+/* One thread's walk down a band of rows [y_begin, y_end). */
+template <class Fn, int NARR, bool FAST>
+__device__ __forceinline__ void stencil_band(const Env &env, const Source<typename Fn::in_t> (&src)[NARR],
+                                             const Cols<Fn::RX> (&cols)[NARR], typename Fn::out_t *out, int W,
+                                             int x0, int y_begin, int y_end, bool out_vec) {
+    typedef typename Fn::in_t Tin;
+    typedef typename Fn::out_t Tout;
+    constexpr int RY = Fn::RY, RX = Fn::RX;
+    constexpr int WIN = 2 * RY + 1;
+    constexpr int RW = 4 + 2 * RX;
+    constexpr int CH = WIN * ((ACCB_STENCIL_ROWS_IN_FLIGHT + WIN - 1) / WIN);
+
+    /* FAST: pointers to this thread's vector in the next row to load / store */
+    const Tin *rp[NARR];
+#pragma unroll
+    for (int a = 0; a < NARR; ++a)
+        rp[a] = src[a].base + (FAST ? ((long long)(y_begin - RY) * src[a].w + x0) : 0LL);
+    Tout *op = out + (FAST ? ((long long)y_begin * W + x0) : 0LL);
+
+    auto issue = [&](int a, int y, RowRaw<Tin, RX> &raw) {
+        if constexpr (FAST) {
+            load4<Cache::Default>(rp[a], 0, raw.c);
+            if constexpr (RX > 0) {
+#pragma unroll
+                for (int d = 0; d < RX; ++d) {
+                    if (!cols[a].l_ok) raw.l[d] = cols[a].xl[d] >= 0 ? rp[a][cols[a].xl[d] - x0] : src[a].cval;
+                    if (!cols[a].r_ok) raw.r[d] = cols[a].xr[d] >= 0 ? rp[a][cols[a].xr[d] - x0] : src[a].cval;
+                }
+            }
+            rp[a] += src[a].w;
+        } else {
+            issue_row<Tin, RX>(src[a], y, cols[a], raw);
+        }
+    };
+
+    Tin win[NARR][WIN][RW];
+    /* preload rows y_begin-RY .. y_begin+RY-1 into slots 0 .. 2RY-1 */
+    if constexpr (WIN > 1) {
+        RowRaw<Tin, RX> pre[NARR][WIN - 1];
+#pragma unroll
+        for (int s = 0; s < WIN - 1; ++s)
+#pragma unroll
+            for (int a = 0; a < NARR; ++a) issue(a, y_begin - RY + s, pre[a][s]);
+#pragma unroll
+        for (int a = 0; a < NARR; ++a)
+#pragma unroll
+            for (int s = 0; s < WIN - 1; ++s) finish_row<Tin, RX>(cols[a], pre[a][s], win[a][s]);
+    }
+
+    /* CH output rows per trip (a multiple of WIN, so window slots are
+     * compile-time): first issue the loads of all CH new rows, then complete
+     * and use them one by one */
+    for (int y = y_begin; y < y_end; y += CH) {
+        RowRaw<Tin, RX> raw[NARR][CH];
+#pragma unroll
+        for (int u = 0; u < CH; ++u)
+            if (y + u < y_end) {
+#pragma unroll
+                for (int a = 0; a < NARR; ++a) issue(a, y + u + RY, raw[a][u]);
+            }
+#pragma unroll
+        for (int u = 0; u < CH; ++u) {
+            const int s = u % WIN; /* (yo - y_begin) % WIN */
+            const int yo = y + u;  /* output row */
+            if (yo < y_end) {
+                /* newest row yo+RY goes to slot (s + 2RY) % WIN */
+#pragma unroll
+                for (int a = 0; a < NARR; ++a)
+                    finish_row<Tin, RX>(cols[a], raw[a][u], win[a][(s + 2 * RY) % WIN]);
+                if (FAST || x0 < W) {
+                    Tout o[V];
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        Tin t[NARR][WIN][2 * RX + 1];
+#pragma unroll
+                        for (int a = 0; a < NARR; ++a)
+#pragma unroll
+                            for (int dy = 0; dy < WIN; ++dy)
+#pragma unroll
+                                for (int dx = 0; dx < 2 * RX + 1; ++dx)
+                                    t[a][dy][dx] = win[a][(s + dy) % WIN][k + dx];
+                        if constexpr (NARR == 1)
+                            o[k] = Fn::apply(env, t[0]);
+                        else
+                            o[k] = Fn::apply(env, t[0], t[1]);
+                    }
+                    if constexpr (FAST) {
+                        store4<Cache::Stream>(op, 0, o);
+                        op += W;
+                    } else if (out_vec && x0 + V <= W) {
+                        store4<Cache::Stream>(out, ((long long)yo * W + x0) / V, o);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < V; ++k)
+                            if (x0 + k < W) out[(long long)yo * W + x0 + k] = o[k];
+                    }
+                }
             }
         }
     }
@@ -123,8 +276,6 @@ __device__ __forceinline__ void stencil_body(const accb_kparams &p) {
     typedef typename Fn::in_t Tin;
     typedef typename Fn::out_t Tout;
     constexpr int RY = Fn::RY, RX = Fn::RX;
-    constexpr int WIN = 2 * RY + 1;
-    constexpr int RW = 4 + 2 * RX;
     const Env env(p);
     const int H = (int)p.ip[0], W = (int)p.ip[1];
     const int RB = (int)p.ip[2], TXW = (int)p.ip[3];
@@ -151,54 +302,23 @@ __device__ __forceinline__ void stencil_body(const accb_kparams &p) {
     for (long long b = blockIdx.x; b < (long long)ncg * nbands; b += gridDim.x) {
         const int cg = (int)(b % ncg), band = (int)(b / ncg);
         const int x0 = (cg * TXW + tx) * V;
+        Cols<RX> cols[NARR];
+#pragma unroll
+        for (int a = 0; a < NARR; ++a) cols[a] = make_cols<Tin, RX>(src[a], x0);
         const int y_begin = (band * TY + ty) * RB;
         const int y_end = min(H, y_begin + RB);
         if (y_begin >= H) continue; /* whole warps share ty, so a warp leaves together */
 
-        Tin win[NARR][WIN][RW];
-        /* preload rows y_begin-RY .. y_begin+RY-1 into slots 0 .. 2RY-1 */
+        /* Fast band: every row the band touches is inside every source and the
+         * whole warp moves aligned vectors, so rows are reached by pointer
+         * increments and no per-row boundary test is needed. */
+        bool fast = out_vec && x0 + V <= W && y_begin - RY >= 0;
 #pragma unroll
-        for (int a = 0; a < NARR; ++a)
-#pragma unroll
-            for (int s = 0; s < WIN - 1; ++s) load_row<Tin, RX>(src[a], y_begin - RY + s, x0, win[a][s]);
-
-        for (int y = y_begin; y < y_end; y += WIN) {
-#pragma unroll
-            for (int s = 0; s < WIN; ++s) {
-                const int yo = y + s; /* output row; (yo - y_begin) % WIN == s */
-                if (yo < y_end) {
-                    /* newest row yo+RY goes to slot (s + 2RY) % WIN */
-#pragma unroll
-                    for (int a = 0; a < NARR; ++a)
-                        load_row<Tin, RX>(src[a], yo + RY, x0, win[a][(s + 2 * RY) % WIN]);
-                    if (x0 < W) {
-                        Tout o[V];
-#pragma unroll
-                        for (int k = 0; k < V; ++k) {
-                            Tin t[NARR][WIN][2 * RX + 1];
-#pragma unroll
-                            for (int a = 0; a < NARR; ++a)
-#pragma unroll
-                                for (int dy = 0; dy < WIN; ++dy)
-#pragma unroll
-                                    for (int dx = 0; dx < 2 * RX + 1; ++dx)
-                                        t[a][dy][dx] = win[a][(s + dy) % WIN][k + dx];
-                            if constexpr (NARR == 1)
-                                o[k] = Fn::apply(env, t[0]);
-                            else
-                                o[k] = Fn::apply(env, t[0], t[1]);
-                        }
-                        if (out_vec && x0 + V <= W) {
-                            store4<Cache::Stream>(out, ((long long)yo * W + x0) / V, o);
-                        } else {
-#pragma unroll
-                            for (int k = 0; k < V; ++k)
-                                if (x0 + k < W) out[(long long)yo * W + x0 + k] = o[k];
-                        }
-                    }
-                }
-            }
-        }
+        for (int a = 0; a < NARR; ++a) fast = fast && cols[a].vec && y_end + RY <= src[a].h;
+        if (__all_sync(FULL, fast))
+            stencil_band<Fn, NARR, true>(env, src, cols, out, W, x0, y_begin, y_end, out_vec);
+        else
+            stencil_band<Fn, NARR, false>(env, src, cols, out, W, x0, y_begin, y_end, out_vec);
     }
 }
 
@@ -207,14 +327,14 @@ __device__ __forceinline__ void stencil_body(const accb_kparams &p) {
 /* Entry points named after the reference's kernels (Stencil.hs:67,158). */
 #define ACCB_INSTANTIATE_STENCIL(Fn)                                                           \
     ACCB_META(8, ACCB_STENCIL_CTA, sizeof(Fn::in_t), 0, 1, 0)                                  \
-    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA)                             \
+    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_MINB)                      \
         stencil(const __grid_constant__ accb_kparams p) {                                      \
         accb::stencil_body<Fn, 1, ACCB_STENCIL_CTA>(p);                                        \
     }
 
 #define ACCB_INSTANTIATE_STENCIL2(Fn)                                                          \
     ACCB_META(9, ACCB_STENCIL_CTA, sizeof(Fn::in_t), 0, 1, 0)                                  \
-    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA)                             \
+    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_MINB)                      \
         stencil2(const __grid_constant__ accb_kparams p) {                                     \
         accb::stencil_body<Fn, 2, ACCB_STENCIL_CTA>(p);                                        \
     }

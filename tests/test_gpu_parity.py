@@ -34,8 +34,9 @@ def close(got, ref, atol):
 def test_map_saxpy(ctx, P, torch_cuda, rng, n):
     t = torch_cuda
     x, y = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
-    out = t.empty(n, dtype=t.float32, device="cuda")
-    ctx.map(P.SAXPY, [dev(t, x), dev(t, y)], out, scalars=np.float32(2.5))
+    out = t.empty(max(n, 1), dtype=t.float32, device="cuda")[:n]  # an empty array still has an allocation (Prim.hs:167)
+    pad = lambda a: dev(t, np.concatenate([a, np.zeros(1, a.dtype)]))[:n]
+    ctx.map(P.SAXPY, [pad(x), pad(y)], out, scalars=np.float32(2.5))
     ctx.sync()
     ref = np.float32(2.5) * x + y  # one rounding per op, fma contraction aside
     close(out.cpu().numpy(), ref.astype(np.float64), 1e-6)
@@ -145,7 +146,6 @@ def test_fold_all_int_with_seed(ctx, P, torch_cuda, rng, n):
     out = t.zeros(1, dtype=t.int32, device="cuda")
     ctx.fold_all(P.SUM_I32, [dev(t, x)], n, out, seed=np.int32(17))
     ctx.sync()
-    ref = np.int32((int(x.astype(np.int64).sum()) + 17) & 0xffffffff if True else 0)
     assert out.cpu().numpy()[0] == np.array((int(x.astype(np.int64).sum()) + 17) & 0xffffffff, np.uint32).astype(np.int32)
 
 
