@@ -192,6 +192,32 @@ ACCB_API int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, co
                        long long n, int direction, int kind, const void *seed, size_t seed_bytes,
                        const accb_array *out, const accb_array *total);
 
+/* Int32 `scanl (+) seed` for callers that cannot allocate device memory.  It has
+ * no counterpart in the reference, whose every scan allocates its block-sum
+ * array (scanCore, CUDA/Execute.hs:364-392).  Meant for code that runs with a
+ * memory budget fixed in advance or in a place where touching the allocator is
+ * forbidden (a real-time loop, a callback of another library, a process whose
+ * pool is fully handed out): the call performs no cudaMalloc / cudaFree and
+ * needs no accb_context.  The tile status words live in a 1 MiB array that is
+ * part of the library image and stays resident on every GPU that loads the
+ * library until the process exits.
+ *   - `in` (n elements) and `out` (n + 1 elements: out[0] = seed, out[n] = the
+ *     total) are device pointers on `device`; the launch is asynchronous on
+ *     `stream`.
+ *   - n may be at most 2^28 (268 435 456) elements; larger inputs are refused
+ *     with ACCB_EINVAL and a message in accb_last_error(NULL).
+ *   - `status` is NULL or a device word the caller owns: it is cleared on the
+ *     stream and set to 1 if a bounded device-side wait gave up.
+ *   - The first call on a device looks up the array's device address (which
+ *     makes the CUDA runtime load the library's code there); make that first
+ *     call before any stream capture begins.
+ *   - All calls on a device share the one array, which keeps the previous
+ *     call's contents; each call clears on `stream` what it will read.  Two
+ *     calls that overlap on the GPU (different streams, no dependency between
+ *     them) race on it: order them. */
+ACCB_API int accb_scanl_add_i32_noalloc(int device, accb_stream stream, const int32_t *in, long long n,
+                                        int32_t seed, int32_t *out, unsigned int *status);
+
 /* out must already hold the default values (the reference copies them first,
  * Execute.hs:405-407); use accb_permute_defaults to do that copy. */
 ACCB_API int accb_permute_defaults(accb_context *ctx, accb_stream stream, const accb_array *defaults,
