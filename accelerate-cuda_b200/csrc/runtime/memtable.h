@@ -97,6 +97,12 @@ public:
         return &it->second;
     }
 
+    /* look without touching (does not count as a use) */
+    const Entry *peek(uint64_t key) const {
+        auto it = map_.find(key);
+        return it == map_.end() ? nullptr : &it->second;
+    }
+
     /* Bring an evicted entry back; *needs_upload tells the caller to copy
      * `host` to the device again. */
     Entry *ensure_resident(uint64_t key, bool *needs_upload) {

@@ -1,0 +1,146 @@
+"""Multi-GPU execution of the skeletons: one process per GPU, ``torch.distributed``
+for the exchange steps (NCCL on GPUs; the same code runs on CPU tensors with
+the gloo backend, which is how it is tested without GPUs).
+
+The reference has no multi-device code; its only primitive is an uncalled peer
+copy (``Data/Array/Accelerate/CUDA/Array/Prim.hs:306-335``).  Here every
+collective operation shards by contiguous slabs of the outermost index space:
+
+* map, fold over rows  -- no exchange, results stay sharded;
+* foldAll              -- one partial per rank, all-gathered and combined in rank order;
+* scan                 -- slab totals all-gathered; each rank continues from the
+                          exclusive sum of the lower ranks' totals (the carry);
+* permute (+)          -- full-size partial destinations, one all-reduce;
+* iterated stencil     -- row slabs with RY halo rows each way, refreshed before
+                          every application by neighbour send/recv into the
+                          rank's OWN halo rows (no kernel reads a peer's memory).
+
+Only the partitioning and exchange logic lives here; the local work is done by
+whatever ``local_*`` callables the caller passes (the skeleton launches of
+``Context`` on a GPU).
+"""
+from __future__ import annotations
+
+from typing import Callable, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def slab(n: int, rank: int, world: int) -> Tuple[int, int]:
+    """[lo, hi) of rank's contiguous slab of n items; sizes differ by at most one
+    and are multiples of 4 wherever possible so that slabs stay 16-byte aligned."""
+    q = (n // 4) // world * 4  # aligned base size
+    lo = rank * q
+    hi = (rank + 1) * q if rank < world - 1 else n
+    return lo, hi
+
+
+def scan_carry(local_total: torch.Tensor, group=None) -> torch.Tensor:
+    """Exclusive sum over the lower ranks of each rank's slab total (wrapping
+    integer addition): the seed the rank's local scan continues from."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    gathered = torch.empty(world, dtype=local_total.dtype, device=local_total.device)
+    dist.all_gather_into_tensor(gathered, local_total.reshape(1), group=group)
+    carry = gathered[:rank].sum(dtype=local_total.dtype) if rank else torch.zeros((), dtype=local_total.dtype,
+                                                                                  device=local_total.device)
+    return carry.reshape(1)
+
+
+def sharded_scanl(x_local: torch.Tensor, seed: int, local_total: Callable, local_scan: Callable, group=None):
+    """scanl (+) seed over the concatenation of the ranks' slabs.
+
+    ``local_total(x) -> 1-element tensor`` and ``local_scan(x, seed_tensor) ->
+    tensor of len(x)+1`` (exclusive body + running total) do the local work.
+    Returns the rank's part of the result: len(x) values (len(x)+1 on the last
+    rank, whose final element is the grand total)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    carry = scan_carry(local_total(x_local), group) + seed
+    out = local_scan(x_local, carry.to(x_local.dtype))
+    return out if rank == world - 1 else out[:-1]
+
+
+def sharded_fold_all(local_partial: torch.Tensor, combine: Callable, group=None) -> torch.Tensor:
+    """All ranks get the combination of the per-rank partials, taken in rank order
+    so that the result does not depend on arrival order."""
+    world = dist.get_world_size(group)
+    gathered = torch.empty(world, dtype=local_partial.dtype, device=local_partial.device)
+    dist.all_gather_into_tensor(gathered, local_partial.reshape(1), group=group)
+    acc = gathered[0]
+    for r in range(1, world):
+        acc = combine(acc, gathered[r])
+    return acc.reshape(1)
+
+
+def sharded_histogram(local_hist: torch.Tensor, defaults: torch.Tensor, group=None) -> torch.Tensor:
+    """permute (+): each rank scattered its slab of keys into a zero-initialised
+    full-size partial; the partials are summed by one all-reduce and the
+    defaults added once."""
+    total = local_hist.clone()
+    dist.all_reduce(total, op=dist.ReduceOp.SUM, group=group)
+    return total + defaults
+
+
+def exchange_halos(grid: torch.Tensor, ry: int, boundary: str = "clamp", group=None):
+    """Refresh the halo rows of a row-slab.
+
+    ``grid`` has ry halo rows above and below the rank's interior rows.  Interior
+    edge rows go to the neighbours' halos; at the global top and bottom the halo
+    is filled locally according to the boundary mode (clamp: replicate the edge
+    row; wrap: taken from the other end of the ring; constant: left untouched,
+    the caller keeps the constant there; mirror: reflected interior rows)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    interior = grid[ry:grid.shape[0] - ry]
+    top, bottom = interior[:ry].contiguous(), interior[-ry:].contiguous()
+    up, down = rank - 1, rank + 1
+    ring = boundary == "wrap"
+    if ring:
+        up, down = up % world, down % world
+    ops, recv_top, recv_bot = [], torch.empty_like(top), torch.empty_like(bottom)
+    has_up, has_down = up >= 0, down < world
+    if world > 1:
+        # Rows travelling up carry tag 0, rows travelling down tag 1.  NCCL matches the messages
+        # between two ranks by order, not by tag, so the order matters when both neighbours are the
+        # same rank (a ring of two): each side sends [up, down] and receives [from below, from above].
+        if has_up:
+            ops.append(dist.P2POp(dist.isend, top, up, group, 0))
+        if has_down:
+            ops.append(dist.P2POp(dist.isend, bottom, down, group, 1))
+        if has_down:
+            ops.append(dist.P2POp(dist.irecv, recv_bot, down, group, 0))
+        if has_up:
+            ops.append(dist.P2POp(dist.irecv, recv_top, up, group, 1))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+    if world == 1 and ring:
+        recv_top, recv_bot, has_up, has_down = bottom, top, True, True
+    if has_up:
+        grid[:ry] = recv_top
+    elif boundary == "clamp":
+        grid[:ry] = interior[:1].expand(ry, -1)
+    elif boundary == "mirror":
+        grid[:ry] = interior[1:ry + 1].flip(0)
+    if has_down:
+        grid[-ry:] = recv_bot
+    elif boundary == "clamp":
+        grid[-ry:] = interior[-1:].expand(ry, -1)
+    elif boundary == "mirror":
+        grid[-ry:] = interior[-ry - 1:-1].flip(0)
+    return grid
+
+
+def sharded_stencil_iterate(grid_local: torch.Tensor, iters: int, ry: int, local_apply: Callable,
+                            boundary: str = "clamp", group=None) -> torch.Tensor:
+    """``iters`` stencil applications on a row-slab.  ``grid_local`` holds only the
+    rank's interior rows; ``local_apply(padded) -> padded`` applies the stencil
+    to a slab with halo rows (any boundary treatment in x is the kernel's; rows
+    beyond the halo are never read because the halo already carries the
+    boundary)."""
+    h, w = grid_local.shape
+    a = torch.empty((h + 2 * ry, w), dtype=grid_local.dtype, device=grid_local.device)
+    a[ry:ry + h] = grid_local
+    for _ in range(iters):
+        exchange_halos(a, ry, boundary, group)
+        a = local_apply(a)
+    return a[ry:ry + h]

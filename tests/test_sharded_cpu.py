@@ -1,0 +1,99 @@
+"""The multi-GPU host logic (slab partitioning, scan carry, histogram all-reduce,
+stencil halo exchange) run as gloo ranks on CPU tensors.  The local work is done
+by the CPU oracle here -- on a GPU it is the skeleton launches."""
+import importlib
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, case, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sh = importlib.import_module("accelerate-cuda_b200.sharded")
+        W = importlib.import_module("accelerate-cuda_b200.workloads")
+        oracle = importlib.import_module("oracle")
+        ok = True
+        if case == "scan":
+            n = 100003
+            x = W.uniform_i32(W.SEED, W.S_SCAN, n, 16)
+            lo, hi = sh.slab(n, rank, world)
+            # each rank generates only its slab: the generator is index-addressable
+            xl = torch.from_numpy(W.uniform_i32(W.SEED, W.S_SCAN, hi - lo, 16, first=lo))
+            total = lambda t: torch.tensor([int(t.sum(dtype=torch.int64)) & 0xffffffff], dtype=torch.int64).to(torch.int32)
+            scan = lambda t, seed: torch.from_numpy(oracle.scanl_i32(t.numpy(), int(seed[0])))
+            out = sh.sharded_scanl(xl, 7, total, scan)
+            ref = oracle.scanl_i32(x, 7)
+            hi_ref = hi + 1 if rank == world - 1 else hi
+            ok = np.array_equal(out.numpy(), ref[lo:hi_ref])
+        elif case == "hist":
+            n = 50001
+            cdf = W.zipf_cdf()
+            lo, hi = sh.slab(n, rank, world)
+            keys = W.zipf_mix_keys(W.SEED, hi - lo, cdf, first=lo)
+            part = torch.from_numpy(oracle.permute_add_i32(keys, W.HIST_BINS))
+            defaults = torch.arange(W.HIST_BINS, dtype=torch.int32)
+            got = sh.sharded_histogram(part, defaults)
+            ref = oracle.permute_add_i32(W.zipf_mix_keys(W.SEED, n, cdf), W.HIST_BINS, defaults=defaults.numpy())
+            ok = np.array_equal(got.numpy(), ref)
+        elif case == "dot":
+            n = 70001
+            lo, hi = sh.slab(n, rank, world)
+            xs = W.uniform_f32(W.SEED, W.S_XS, hi - lo, -1, 1, first=lo)
+            ys = W.uniform_f32(W.SEED, W.S_YS, hi - lo, -1, 1, first=lo)
+            part = torch.tensor([oracle.dot_f32(xs, ys)], dtype=torch.float64)
+            got = sh.sharded_fold_all(part, lambda a, b: a + b)
+            ref = oracle.dot_f32(W.uniform_f32(W.SEED, W.S_XS, n, -1, 1), W.uniform_f32(W.SEED, W.S_YS, n, -1, 1))
+            ok = abs(float(got[0]) - ref) <= 1e-12 * abs(ref)
+        elif case.startswith("stencil"):
+            mode = case.split("-")[1]
+            h, w, iters = 12 * world + 5, 40, 4
+            g = W.uniform_f32(W.SEED, W.S_GRID, h * w, 0, 1).reshape(h, w).astype(np.float64)
+            lo, hi = (rank * (h // world), (rank + 1) * (h // world) if rank < world - 1 else h)
+            def apply(a, mode=mode):
+                # the boundary in x is the kernel's; in y the halo rows already hold the right neighbours, so
+                # what the kernel does beyond them only lands in halo rows, which the next exchange overwrites
+                return torch.from_numpy(oracle.stencil2d(a.numpy(), W.BLUR_WEIGHTS, mode))
+            got = sh.sharded_stencil_iterate(torch.from_numpy(g[lo:hi].copy()), iters, 1, apply, boundary=mode)
+            ref = g
+            for _ in range(iters):
+                ref = oracle.stencil2d(ref, W.BLUR_WEIGHTS, mode)
+            ok = np.allclose(got.numpy(), ref[lo:hi], rtol=0, atol=1e-14)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("case", ["scan", "hist", "dot", "stencil-clamp", "stencil-mirror", "stencil-wrap"])
+def test_sharded_paths_match_the_single_device_oracle(case, world):
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), case, ret), nprocs=world, join=True)
+    assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def test_slabs_partition_the_index_space_and_stay_aligned():
+    sh = importlib.import_module("accelerate-cuda_b200.sharded")
+    for n in (0, 1, 7, 1000, 1 << 20, (1 << 20) + 3):
+        for world in (1, 2, 3, 8):
+            edges = [sh.slab(n, r, world) for r in range(world)]
+            assert edges[0][0] == 0 and edges[-1][1] == n
+            assert all(edges[i][1] == edges[i + 1][0] for i in range(world - 1))
+            assert all(lo % 4 == 0 for lo, _ in edges)
