@@ -450,6 +450,26 @@ static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, 
             return fail(ctx, ACCB_EINVAL, "stencil result larger than source %d", a);
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
+    StreamScratch *sc = scratch_for(ctx, s);
+    if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+    p.aux[1] = sc->words + 2; /* error word of the bounded waits */
+    p.ip[4] = boundary;
+    /* Tile form (input tile staged in shared memory by TMA): needs 4-byte elements (the kernel
+     * reports 0 bytes of shared memory otherwise), 16-byte aligned arrays, widths that are
+     * multiples of 4 and enough rows to fill a tile. */
+    bool tiled = pr.meta.v[6] > 0 && (p.flags & ACCB_F_VEC) && W % 4 == 0 && H >= 16 && !getenv("ACCB_STENCIL_NO_TILE");
+    for (int a = 0; a < nsrc; ++a) tiled = tiled && p.ip[6 + 2 * a] % 4 == 0;
+    if (tiled) {
+        const std::string tentry = std::string(entry) + "_tile";
+        const size_t smem = (size_t)pr.meta.v[6];
+        Prep pt;
+        TRY(prepare(ctx, k, tentry.c_str(), smem, &pt));
+        p.ip[0] = H;
+        p.ip[1] = W;
+        const long long tiles = ceil_div(W, pt.meta.v[4]) * ceil_div(H, pt.meta.v[3]);
+        if (tiles > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one stencil launch");
+        return launch(ctx, pt.fn, tentry.c_str(), (int)tiles, pt.block, smem, s, p);
+    }
     int txw = 32;
     while (txw < pr.block && txw * 4 < W) txw *= 2;
     int rb = 64;

@@ -10,8 +10,12 @@
  * vs border per warp with __all; it also launches the kernel twice
  * (Execute.hs:422-423), which is not reproduced.
  *
- * Here each thread owns 4 adjacent columns and walks down a band of rows
- * keeping the (2*RY+1) x (4+2*RX) window in registers: per output row it
+ * Two forms.  The TILE form (second half of this file, `stencil_tile`) stages
+ * each block's input tile in shared memory with the TMA engine and is what
+ * runs for 4-byte elements on aligned arrays whose width is a multiple of 4.
+ * The REGISTER form below takes every other case (any element size, ragged
+ * widths, rank 1): each thread owns 4 adjacent columns and walks down a band
+ * of rows keeping the (2*RY+1) x (4+2*RX) window in registers: per output row it
  * issues ONE 128-bit load, gets the RX halo columns from the neighbouring
  * lanes with shuffles (only the lanes at a warp edge or at the array edge
  * read the halo from memory, through the boundary function) and writes one
@@ -36,7 +40,17 @@
 #pragma once
 #include "../cubits/accb_vec.cuh"
 #include "../cubits/accb_warp.cuh"
+#include "../cubits/accb_tma.cuh"
 
+#ifndef ACCB_STENCIL_TILE_RPT
+#define ACCB_STENCIL_TILE_RPT 8 /* tile form: output rows per thread */
+#endif
+#ifndef ACCB_STENCIL_TILE_MINB
+#define ACCB_STENCIL_TILE_MINB 6 /* tile form: resident blocks per SM to leave registers for */
+#endif
+#ifndef ACCB_STENCIL_TMA_SPIN_LIMIT
+#define ACCB_STENCIL_TMA_SPIN_LIMIT (1 << 16)
+#endif
 #ifndef ACCB_STENCIL_CTA
 #define ACCB_STENCIL_CTA 256
 #endif
@@ -322,19 +336,220 @@ __device__ __forceinline__ void stencil_body(const accb_kparams &p) {
     }
 }
 
+/* ------------------------------------------------------------------------
+ * Tile form: the (RB + 2RY) x (TW + 8) input tile of a block is brought into
+ * shared memory by the TMA engine, one cp.async.bulk per tile row, all
+ * completing on one mbarrier.  Nothing holds registers while the copies are
+ * in flight, so the bytes in flight per SM are bounded by shared memory (six
+ * 36 KB tiles), not by the register file -- the same reason as in scan.cuh.
+ * Rows outside the array are fetched from their boundary-mapped row; the few
+ * halo columns that fall outside the array (first / last column tile only)
+ * and the rows of a Constant boundary are patched by the threads afterwards.
+ * Then each thread walks RPT rows of 4 columns with the usual register
+ * window, reading shared memory only.
+ * Needs 4-byte elements, source widths that are multiples of 4 and 16-byte
+ * aligned arrays (checked by the host, which otherwise launches `stencil`).
+ * ---------------------------------------------------------------------- */
+template <class Fn, int NARR, int CTA>
+struct StencilTile {
+    static constexpr int RY = Fn::RY, RX = Fn::RX;
+    static constexpr int TXW = 64;                     /* threads along x */
+    static constexpr int TY = CTA / TXW;               /* thread rows */
+    static constexpr int RPT = ACCB_STENCIL_TILE_RPT;  /* output rows per thread */
+    static constexpr int RB = TY * RPT;                /* output rows per tile */
+    static constexpr int TW = TXW * V;                 /* output columns per tile */
+    static constexpr int HX = 4;                       /* halo columns kept each side (16 bytes) */
+    static constexpr int PW = TW + 2 * HX;             /* pitch of a tile row in elements */
+    static constexpr int SR = RB + 2 * RY;             /* tile rows */
+    static constexpr int kSmemBytes = NARR * SR * PW * 4;
+    static_assert(RX <= HX, "stencil radius in x is at most 4 in the tile form");
+};
+
+template <class Fn, int NARR, int CTA>
+__device__ __forceinline__ void stencil_tile_body(const accb_kparams &p) {
+    typedef typename Fn::in_t Tin;
+    typedef typename Fn::out_t Tout;
+    typedef StencilTile<Fn, NARR, CTA> G;
+    static_assert(sizeof(Tin) == 4 && sizeof(Tout) == 4, "tile form: 4-byte elements");
+    constexpr int RY = G::RY, RX = G::RX, WIN = 2 * RY + 1, RW = 4 + 2 * RX;
+    extern __shared__ __align__(128) unsigned char s_raw[];
+    __shared__ __align__(8) unsigned long long s_bar;
+    Tin(*tile)[G::SR][G::PW] = reinterpret_cast<Tin(*)[G::SR][G::PW]>(s_raw);
+
+    const Env env(p);
+    const int H = (int)p.ip[0], W = (int)p.ip[1];
+    const int mode = (int)p.ip[4];
+    Source<Tin> src[NARR];
+#pragma unroll
+    for (int a = 0; a < NARR; ++a) {
+        src[a].base = static_cast<const Tin *>(p.in[a]);
+        src[a].h = (int)p.ip[5 + 2 * a];
+        src[a].w = (int)p.ip[6 + 2 * a];
+        src[a].mode = mode;
+        src[a].cval = env.scalar<Tin>(0);
+        src[a].vec_ok = true;
+    }
+    Tout *out = static_cast<Tout *>(p.out[0]);
+    unsigned int *err = static_cast<unsigned int *>(p.aux[1]);
+
+    const int ncg = (W + G::TW - 1) / G::TW;
+    const int x0t = (int)(blockIdx.x % ncg) * G::TW, y0t = (int)(blockIdx.x / ncg) * G::RB;
+    /* columns [xs, xe) of source a are copied to tile columns [xs - (x0t - HX), ...) */
+    auto col_range = [&](int a, int &xs, int &xe) {
+        xs = max(0, x0t - G::HX);
+        xe = min(src[a].w, x0t + G::TW + G::HX);
+    };
+
+    if (threadIdx.x == 0) {
+        mbar_init(&s_bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (warp_id() == 0) {
+        if (lane_id() == 0) {
+            unsigned total = 0;
+#pragma unroll
+            for (int a = 0; a < NARR; ++a) {
+                int xs, xe;
+                col_range(a, xs, xe);
+                for (int r = 0; r < G::SR; ++r)
+                    if (bound_coord(y0t - RY + r, src[a].h, mode) >= 0) total += (unsigned)(xe - xs) * 4u;
+            }
+            mbar_expect_tx(&s_bar, total);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int a = 0; a < NARR; ++a) {
+            int xs, xe;
+            col_range(a, xs, xe);
+            for (int r = lane_id(); r < G::SR; r += 32) {
+                const int yy = bound_coord(y0t - RY + r, src[a].h, mode);
+                if (yy >= 0)
+                    bulk_g2s(&tile[a][r][xs - (x0t - G::HX)], src[a].base + (long long)yy * src[a].w + xs,
+                             (unsigned)(xe - xs) * 4u, &s_bar);
+            }
+        }
+    }
+    int tries = 0;
+    while (!mbar_try_wait(&s_bar, 0)) {
+        if (++tries > ACCB_STENCIL_TMA_SPIN_LIMIT) { /* bounded: flag the result invalid and go on */
+            atomicExch(err, 1u);
+            break;
+        }
+    }
+    /* patch what the copies could not bring: columns outside the array, rows of a Constant boundary */
+#pragma unroll
+    for (int a = 0; a < NARR; ++a) {
+        int xs, xe;
+        col_range(a, xs, xe);
+        const int lo = x0t - RX, hi = min(x0t + G::TW, W) + RX; /* columns any tap of this tile may touch */
+        const int nleft = max(0, xs - lo), nright = max(0, hi - xe);
+        const int per_row = nleft + nright;
+        for (int i = threadIdx.x; i < G::SR * per_row; i += CTA) {
+            const int r = i / per_row, j = i - r * per_row;
+            const int c = j < nleft ? lo + j : xe + (j - nleft);
+            const int yy = bound_coord(y0t - RY + r, src[a].h, mode);
+            tile[a][r][c - (x0t - G::HX)] = src[a].at(yy, c);
+        }
+        if (mode == B_CONSTANT) {
+            for (int r = 0; r < G::SR; ++r) {
+                if (bound_coord(y0t - RY + r, src[a].h, mode) >= 0) continue; /* uniform per block */
+                for (int c = threadIdx.x; c < G::PW; c += CTA) tile[a][r][c] = src[a].cval;
+            }
+        }
+    }
+    __syncthreads();
+
+    /* each thread: 4 columns, RPT rows, window in registers, shared-memory reads only */
+    const int tx = threadIdx.x % G::TXW, ty = threadIdx.x / G::TXW;
+    const int x = x0t + tx * V;
+    if (x >= W) return;
+    const int sc = G::HX + tx * V; /* tile column of the thread's first centre column */
+    auto row = [&](int a, int r, Tin(&d)[RW]) {
+        const Tin *q = &tile[a][r][sc];
+        Tin c[V];
+        load4<Cache::Default>(q, 0, c);
+#pragma unroll
+        for (int k = 0; k < V; ++k) d[RX + k] = c[k];
+#pragma unroll
+        for (int k = 0; k < RX; ++k) {
+            d[k] = q[k - RX];
+            d[RX + V + k] = q[V + k];
+        }
+    };
+    Tin win[NARR][WIN][RW];
+#pragma unroll
+    for (int a = 0; a < NARR; ++a)
+#pragma unroll
+        for (int s = 0; s < WIN - 1; ++s) row(a, ty * G::RPT + s, win[a][s]);
+    const bool vec_store = x + V <= W;
+#pragma unroll
+    for (int u = 0; u < G::RPT; ++u) {
+        const int yo = y0t + ty * G::RPT + u;
+        if (yo >= H) break;
+#pragma unroll
+        for (int a = 0; a < NARR; ++a) row(a, ty * G::RPT + u + 2 * RY, win[a][(u + 2 * RY) % WIN]);
+        Tout o[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            Tin t[NARR][WIN][2 * RX + 1];
+#pragma unroll
+            for (int a = 0; a < NARR; ++a)
+#pragma unroll
+                for (int dy = 0; dy < WIN; ++dy)
+#pragma unroll
+                    for (int dx = 0; dx < 2 * RX + 1; ++dx) t[a][dy][dx] = win[a][(u + dy) % WIN][k + dx];
+            if constexpr (NARR == 1)
+                o[k] = Fn::apply(env, t[0]);
+            else
+                o[k] = Fn::apply(env, t[0], t[1]);
+        }
+        if (vec_store) {
+            store4<Cache::Stream>(out + (long long)yo * W + x, 0, o);
+        } else {
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                if (x + k < W) out[(long long)yo * W + x + k] = o[k];
+        }
+    }
+}
+
+/* element types the tile form does not take still need a body to instantiate */
+template <class Fn, int NARR, int CTA>
+__device__ __forceinline__ void stencil_tile_or_nothing(const accb_kparams &p) {
+    if constexpr (sizeof(typename Fn::in_t) == 4 && sizeof(typename Fn::out_t) == 4 && Fn::RX <= 4)
+        stencil_tile_body<Fn, NARR, CTA>(p);
+}
+/* which: 0 dynamic shared memory, 1 rows per tile, 2 columns per tile; 0 when the tile form does not apply */
+template <class Fn, int NARR, int CTA>
+__host__ __device__ constexpr int stencil_tile_dim(int which) {
+    if constexpr (sizeof(typename Fn::in_t) == 4 && sizeof(typename Fn::out_t) == 4 && Fn::RX <= 4) {
+        typedef StencilTile<Fn, NARR, CTA> G;
+        return which == 0 ? G::kSmemBytes : (which == 1 ? G::RB : G::TW);
+    } else {
+        return 0;
+    }
+}
+
 }  // namespace accb
 
-/* Entry points named after the reference's kernels (Stencil.hs:67,158). */
-#define ACCB_INSTANTIATE_STENCIL(Fn)                                                           \
-    ACCB_META(8, ACCB_STENCIL_CTA, sizeof(Fn::in_t), 0, 1, 0)                                  \
-    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_MINB)                      \
-        stencil(const __grid_constant__ accb_kparams p) {                                      \
-        accb::stencil_body<Fn, 1, ACCB_STENCIL_CTA>(p);                                        \
+/* Entry points: `stencil` / `stencil2` as in the reference (Stencil.hs:67,158)
+ * are the register form, which takes any shape and element type; the host
+ * launches `stencil_tile` / `stencil2_tile` instead when their conditions hold.
+ * Metadata: {.., element bytes, rows per tile, columns per tile, 0, dynamic shared memory}. */
+#define ACCB_STENCIL_ENTRIES(Fn, id, narr, name, tname)                                        \
+    ACCB_META7(id, ACCB_STENCIL_CTA, sizeof(Fn::in_t),                                         \
+               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(1)),                        \
+               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(2)), 0,                     \
+               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(0)))                        \
+    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_MINB)          \
+        name(const __grid_constant__ accb_kparams p) {                                         \
+        accb::stencil_body<Fn, narr, ACCB_STENCIL_CTA>(p);                                     \
+    }                                                                                          \
+    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_TILE_MINB)     \
+        tname(const __grid_constant__ accb_kparams p) {                                        \
+        accb::stencil_tile_or_nothing<Fn, narr, ACCB_STENCIL_CTA>(p);                          \
     }
 
-#define ACCB_INSTANTIATE_STENCIL2(Fn)                                                          \
-    ACCB_META(9, ACCB_STENCIL_CTA, sizeof(Fn::in_t), 0, 1, 0)                                  \
-    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_MINB)                      \
-        stencil2(const __grid_constant__ accb_kparams p) {                                     \
-        accb::stencil_body<Fn, 2, ACCB_STENCIL_CTA>(p);                                        \
-    }
+#define ACCB_INSTANTIATE_STENCIL(Fn) ACCB_STENCIL_ENTRIES(Fn, 8, 1, stencil, stencil_tile)
+#define ACCB_INSTANTIATE_STENCIL2(Fn) ACCB_STENCIL_ENTRIES(Fn, 9, 2, stencil2, stencil2_tile)

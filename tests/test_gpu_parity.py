@@ -432,6 +432,33 @@ def test_stencil_blur_all_boundaries(ctx, P, torch_cuda, oracle, workloads, rng,
 
 
 @pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
+@pytest.mark.parametrize("shape", [(16, 8), (17, 260), (64, 1024), (100, 516), (33, 256), (300, 252)])
+def test_stencil_tile_form_shapes(ctx, P, torch_cuda, oracle, workloads, rng, boundary, shape):
+    """Widths that are multiples of 4 with at least 16 rows take the TMA-staged tile kernel: one and
+    several column tiles, ragged last tiles in both directions, radius 1 and 2."""
+    t = torch_cuda
+    a = rng.uniform(0, 1, shape).astype(np.float32)
+    out = t.zeros(shape, dtype=t.float32, device="cuda")
+    ctx.stencil(P.BLUR, dev(t, a), out, boundary=boundary, constant=np.float32(-1.5))
+    ctx.sync()
+    close(out.cpu().numpy(), oracle.stencil2d(a, workloads.BLUR_WEIGHTS, boundary, -1.5), 1e-6)
+    ctx.stencil(P.BOX5, dev(t, a), out, boundary=boundary, constant=np.float32(0.25))
+    ctx.sync()
+    close(out.cpu().numpy(), oracle.stencil2d(a, np.full((5, 5), 0.04), boundary, 0.25), 2e-6)
+
+
+def test_stencil_tile_and_register_forms_agree_bit_for_bit(ctx, P, torch_cuda, rng, monkeypatch):
+    t = torch_cuda
+    a = dev(t, rng.uniform(0, 1, (200, 1028)).astype(np.float32))
+    tiled, plain = t.zeros_like(a), t.zeros_like(a)
+    ctx.stencil(P.BLUR, a, tiled, boundary="mirror")
+    monkeypatch.setenv("ACCB_STENCIL_NO_TILE", "1")
+    ctx.stencil(P.BLUR, a, plain, boundary="mirror")
+    ctx.sync()
+    assert t.equal(tiled, plain)
+
+
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
 def test_stencil_radius2_and_laplace(ctx, P, torch_cuda, oracle, rng, boundary):
     t = torch_cuda
     a = rng.uniform(-1, 1, (61, 203)).astype(np.float32)
