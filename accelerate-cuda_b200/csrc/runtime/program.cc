@@ -58,6 +58,8 @@ struct accb_program {
     std::vector<std::vector<PoolBuf>> pool; /* per value id, per component (stencil uses 2x) */
     std::vector<std::vector<PoolBuf>> in_pool;
     cudaStream_t host_stream = nullptr;
+    cudaStream_t pipe_stream[3] = {nullptr, nullptr, nullptr}; /* upload, compute, download */
+    std::vector<cudaEvent_t> pipe_events;
     int status = ACCB_OK;
 };
 
@@ -340,10 +342,92 @@ int accb_program_run(accb_program *p, accb_stream stream, const accb_array *inpu
     return run_internal(p, (cudaStream_t)stream, inputs, outputs, false);
 }
 
+/* A program that is one left exclusive scan of its only input is run in chunks: while chunk k
+ * is scanned, chunk k+1 is on its way up and chunk k-1 on its way down, so both directions of
+ * the host link stay busy.  Chunk k continues from the running total that chunk k-1 left in
+ * out[start of k] (read on the device: ACCB_SEED_ON_DEVICE), which is also the value chunk k
+ * must write there.  Returns 1 if it handled the run, 0 if the program has another shape. */
+static int run_host_pipelined_scan(accb_program *p, const accb_array *host_in, accb_array *host_out, int *status) {
+    *status = ACCB_OK;
+    if (p->nodes.size() != 1 || p->ninputs != 1 || p->outputs.size() != 1) return 0;
+    Node &nd = p->nodes[0];
+    if (nd.kind != N_SCAN || nd.direction != ACCB_SCAN_LEFT || nd.scan_kind != ACCB_SCAN_EXCLUSIVE || !nd.has_seed ||
+        nd.env.size() != 1 || nd.env[0] != 0 || p->outputs[0] != nd.out_id || host_in[0].rank != 1)
+        return 0;
+    const long long n = host_in[0].shape[0];
+    const long long chunk = 1LL << 24;
+    if (n < 2 * chunk || getenv("ACCB_NO_PIPELINE")) return 0;
+    accb_context *ctx = p->ctx;
+    const accb_value_type &tin = p->types[0], &tout = p->types[nd.out_id];
+    auto run = [&]() -> int {
+        for (int i = 0; i < 3; ++i)
+            if (!p->pipe_stream[i])
+                TRY(check_cuda(ctx, cudaStreamCreateWithFlags(&p->pipe_stream[i], cudaStreamNonBlocking), "cudaStreamCreate"));
+        cudaStream_t up = p->pipe_stream[0], comp = p->pipe_stream[1], down = p->pipe_stream[2];
+        const long long nchunks = (n + chunk - 1) / chunk;
+        while ((long long)p->pipe_events.size() < 2 * nchunks) {
+            cudaEvent_t e;
+            TRY(check_cuda(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate"));
+            p->pipe_events.push_back(e);
+        }
+        accb_array din, dout;
+        memset(&din, 0, sizeof din);
+        memset(&dout, 0, sizeof dout);
+        din.rank = dout.rank = 1;
+        din.ncomp = tin.ncomp;
+        dout.ncomp = tout.ncomp;
+        auto &islots = p->in_pool[0];
+        if ((int)islots.size() < tin.ncomp) islots.resize(tin.ncomp);
+        for (int c = 0; c < tin.ncomp; ++c) TRY(pool_get(p, islots[c], (size_t)n * tin.comp_bytes[c], &din.ptr[c]));
+        dout.shape[0] = (int)(n + 1);
+        TRY(alloc_value(p, nd.out_id, dout, false));
+        for (long long k = 0; k < nchunks; ++k) {
+            const long long off = k * chunk, len = std::min(chunk, n - off);
+            accb_array ci = din, co = dout;
+            ci.shape[0] = (int)len;
+            co.shape[0] = (int)len + 1;
+            for (int c = 0; c < tin.ncomp; ++c) {
+                ci.ptr[c] = static_cast<char *>(din.ptr[c]) + off * tin.comp_bytes[c];
+                TRY(check_cuda(ctx, cudaMemcpyAsync(ci.ptr[c], static_cast<const char *>(host_in[0].ptr[c]) + off * tin.comp_bytes[c],
+                                                    (size_t)len * tin.comp_bytes[c], cudaMemcpyHostToDevice, up), "upload"));
+            }
+            for (int c = 0; c < tout.ncomp; ++c) co.ptr[c] = static_cast<char *>(dout.ptr[c]) + off * tout.comp_bytes[c];
+            TRY(check_cuda(ctx, cudaEventRecord(p->pipe_events[2 * k], up), "cudaEventRecord"));
+            TRY(check_cuda(ctx, cudaStreamWaitEvent(comp, p->pipe_events[2 * k], 0), "cudaStreamWaitEvent"));
+            if (k == 0 || tout.ncomp != 1) {
+                if (k > 0) return fail(ctx, ACCB_EINVAL, "pipelined scan: tuple carries are not supported");
+                TRY(accb_scan(ctx, nd.k, comp, &ci, 1, len, ACCB_SCAN_LEFT, ACCB_SCAN_EXCLUSIVE, nd.scalars.data(),
+                              nd.scalars.size(), &co, nullptr));
+            } else {
+                TRY(accb_scan(ctx, nd.k, comp, &ci, 1, len, ACCB_SCAN_LEFT, ACCB_SCAN_EXCLUSIVE | ACCB_SEED_ON_DEVICE,
+                              co.ptr[0], tout.comp_bytes[0], &co, nullptr));
+            }
+            TRY(check_cuda(ctx, cudaEventRecord(p->pipe_events[2 * k + 1], comp), "cudaEventRecord"));
+            TRY(check_cuda(ctx, cudaStreamWaitEvent(down, p->pipe_events[2 * k + 1], 0), "cudaStreamWaitEvent"));
+            const long long take = len + (k == nchunks - 1 ? 1 : 0); /* the last chunk also brings the total */
+            for (int c = 0; c < tout.ncomp; ++c)
+                TRY(check_cuda(ctx, cudaMemcpyAsync(static_cast<char *>(host_out[0].ptr[c]) + off * tout.comp_bytes[c], co.ptr[c],
+                                                    (size_t)take * tout.comp_bytes[c], cudaMemcpyDeviceToHost, down), "download"));
+        }
+        TRY(check_cuda(ctx, cudaStreamSynchronize(down), "cudaStreamSynchronize"));
+        host_out[0].rank = 1;
+        host_out[0].shape[0] = (int)(n + 1);
+        host_out[0].ncomp = tout.ncomp;
+        return ACCB_OK;
+    };
+    if (tout.ncomp != 1) return 0;
+    *status = run();
+    return 1;
+}
+
 int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array *host_out) {
     PLOCK(p);
     if ((p->ninputs && !host_in) || !host_out || p->outputs.empty()) return fail(p->ctx, ACCB_EINVAL, "bad argument");
     accb_context *ctx = p->ctx;
+    {
+        int st = ACCB_OK;
+        if (run_host_pipelined_scan(p, host_in, host_out, &st)) return st;
+    }
     if (!p->host_stream) TRY(check_cuda(ctx, cudaStreamCreateWithFlags(&p->host_stream, cudaStreamNonBlocking), "cudaStreamCreate"));
     cudaStream_t s = p->host_stream;
     /* upload (useArrayAsync, Execute.hs:151-154) */
@@ -393,6 +477,9 @@ int accb_program_destroy(accb_program *p) {
             for (auto &b : v)
                 if (b.ptr) cudaFree(b.ptr);
         if (p->host_stream) cudaStreamDestroy(p->host_stream);
+        for (auto s : p->pipe_stream)
+            if (s) cudaStreamDestroy(s);
+        for (auto e : p->pipe_events) cudaEventDestroy(e);
     }
     delete p;
     return ACCB_OK;

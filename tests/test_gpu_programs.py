@@ -1,0 +1,118 @@
+"""Whole programs: run / run1 / runWith on host arrays (upload, launch, download) and the
+AccFFI.h surface (accelerateCreate, runProgram, freeOutput, freeProgram) on device arrays."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_run1_scan_small_and_pipelined(accb, P, ctx, oracle, rng):
+    """run1 compiles once and is applied to several host arrays (CUDA.hs:307-330); inputs of at
+    least two 2^24-element chunks take the pipelined upload / scan / download path."""
+    scan = accb.run1With(ctx, lambda v: accb.scan(P.SCAN_ADD_I32, [v], np.int32, seed=np.int32(3)),
+                         accb.ArrayType(1, np.int32))
+    for n in (10, 100003, (1 << 25) + 12345):
+        x = rng.integers(0, 16, n).astype(np.int32)
+        assert np.array_equal(scan(x), oracle.scanl_i32(x, 3))
+    scan.destroy()
+
+
+def test_run1_scan_prime_returns_body_and_total(accb, P, ctx, oracle, rng):
+    f = accb.run1With(ctx, lambda v: accb.scan(P.SCAN_ADD_I32, [v], np.int32, kind=accb.SCAN_PRIME, seed=np.int32(0)),
+                      accb.ArrayType(1, np.int32))
+    x = rng.integers(-50, 50, 70001).astype(np.int32)
+    body, total = f(x)
+    rb, rt = oracle.scanl_prime_i32(x, 0)
+    assert np.array_equal(body, rb) and total.shape == () and int(total) == rt
+    f.destroy()
+
+
+def test_runWith_dot_product_program(accb, P, ctx, oracle, rng):
+    """foldAll (+) 0 (zipWith (*) xs ys) arrives as ONE fold over a fused producer (CodeGen.hs:104)."""
+    xs = rng.uniform(-1, 1, 1 << 20).astype(np.float32)
+    ys = rng.uniform(-1, 1, 1 << 20).astype(np.float32)
+    r = accb.runWith(ctx, lambda a, b: accb.fold(P.DOT, [a, b], np.float32, seed=np.float32(0), all=True), xs, ys)
+    ref = oracle.dot_f32(xs, ys)
+    assert r.shape == () and abs(float(r) - ref) <= 1e-5 * abs(ref)
+
+
+def test_program_chain_map_then_row_fold(accb, P, ctx, oracle, rng):
+    """let-bound chain: an intermediate array lives on the device only."""
+    def prog(x, y):
+        z = accb.map_(P.SAXPY, [x, y], accb.ArrayType(2, np.float32), scalars=np.float32(2.0))
+        return accb.fold(P.ROWSUM, [z], np.float32, seed=np.float32(0))
+    x = rng.uniform(-1, 1, (33, 2100)).astype(np.float32)
+    y = rng.uniform(-1, 1, (33, 2100)).astype(np.float32)
+    r = accb.runWith(ctx, prog, x, y)
+    ref = oracle.fold_rows_f32((np.float32(2.0) * x + y).astype(np.float32))
+    assert r.shape == (33,) and np.all(np.abs(r - ref) <= 1e-5 * np.abs(ref) + 1e-5)
+
+
+def test_program_histogram_and_iterated_stencil(accb, P, ctx, oracle, workloads, rng):
+    W = workloads
+    keys = W.zipf_mix_keys(W.SEED, 200001, W.zipf_cdf())
+    zeros = np.zeros(W.HIST_BINS, np.int32)
+    h = accb.runWith(ctx, lambda k, d: accb.permute(P.HIST, [k], d), keys, zeros)
+    assert np.array_equal(h, oracle.permute_add_i32(keys, W.HIST_BINS))
+    g = rng.uniform(0, 1, (96, 260)).astype(np.float32)
+    for iters in (1, 2, 5):
+        r = accb.runWith(ctx, lambda a: accb.stencil(P.BLUR, a, boundary="clamp", iters=iters), g)
+        ref = oracle.stencil2d_iter(g, W.BLUR_WEIGHTS, iters, "clamp")
+        assert np.all(np.abs(r - ref) <= 1e-5 * np.abs(ref) + 1e-6)
+
+
+def test_blackscholes_program_with_tuple_input_and_output(accb, P, ctx, oracle, workloads):
+    W = workloads
+    n = 50000
+    s = W.uniform_f32(W.SEED, W.S_SPOT, n, 5, 30)
+    k = W.uniform_f32(W.SEED, W.S_STRIKE, n, 1, 100)
+    y = W.uniform_f32(W.SEED, W.S_YEARS, n, 0.25, 10)
+    f = accb.run1With(ctx, lambda o: accb.map_(P.BLACKSCHOLES, [o], accb.ArrayType(1, [np.float32, np.float32])),
+                      accb.ArrayType(1, [np.float32] * 3))
+    call, put = f((s, k, y))
+    rc, rp = oracle.blackscholes(s, k, y)
+    assert np.all(np.abs(call - rc) <= 1e-5 * np.abs(rc) + 2e-5) and np.all(np.abs(put - rp) <= 1e-5 * np.abs(rp) + 2e-5)
+    ca, pa = accb.runWith(ctx, lambda o: accb.map_(P.BLACKSCHOLES_ACCURATE, [o], accb.ArrayType(1, [np.float32] * 2)), (s, k, y))
+    assert np.all(np.abs(ca - rc) <= 1e-5 * np.abs(rc) + 2e-5) and np.all(np.abs(pa - rp) <= 1e-5 * np.abs(rp) + 2e-5)
+    f.destroy()
+
+
+def test_accffi_surface_runProgram_on_device_arrays(accb, P, torch_cuda, oracle, rng):
+    """accelerateCreate / runProgram / freeOutput / freeProgram / accelerateDestroy with the struct
+    layouts of include/AccFFI.h:10-19: borrowed input pointers, library-owned outputs."""
+    t = torch_cuda
+    L = accb.lib()
+    h = L.accelerateCreate(0, None)
+    assert h
+    cctx = L.accelerateContext(h)
+    shim = accb.Context.__new__(accb.Context)  # a Context object around the handle's context
+    shim.handle, shim.device, shim._kernels = C.c_void_p(cctx), 0, {}
+    prog = accb.run1With(shim, lambda v: accb.scan(P.SCAN_ADD_I32, [v], np.int32, seed=np.int32(0)),
+                         accb.ArrayType(1, np.int32))
+    n = 123457
+    x = rng.integers(0, 16, n).astype(np.int32)
+    xd = t.from_numpy(x).cuda()
+    shape = (C.c_int * 1)(n)
+    ptrs = (C.c_void_p * 1)(xd.data_ptr())
+    inp = accb.InputArray(C.cast(shape, C.POINTER(C.c_int)), C.cast(ptrs, C.POINTER(C.c_void_p)))
+    out = accb.OutputArray()
+    L.runProgram(h, prog.handle, C.byref(inp), C.byref(out))
+    assert L.accelerateStatus(h) == accb.OK
+    assert out.shape[0] == n + 1
+    host = np.empty(n + 1, np.int32)
+    acc = accb.lib()
+    # read the library-owned result through the memory table API: register the pointer as
+    # unmanaged (insertUnmanaged, Array/Remote.hs:168-184), then peek
+    key = 0xABCDEF
+    assert acc.accb_insert_unmanaged(cctx, key, C.c_void_p(out.adata[0]), (n + 1) * 4) == accb.OK
+    assert acc.accb_peek(cctx, key, 0, host.ctypes.data_as(C.c_void_p), (n + 1) * 4, None) == accb.OK
+    assert acc.accb_context_sync(cctx) == accb.OK
+    assert acc.accb_free(cctx, key) == accb.OK
+    assert np.array_equal(host, oracle.scanl_i32(x, 0))
+    L.freeOutput(C.byref(out))
+    assert not out.adata
+    L.freeProgram(prog.handle)
+    prog.handle = None
+    L.accelerateDestroy(h)
