@@ -38,6 +38,21 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "effective HBM GB/s per skeleton at 2^28 elems"
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per unit of work, from the ncu captures
+# summarised under profiles/: (kernel, bytes per unit).  A unit is an element (scan, dot, hist,
+# rowsum), an option (blackscholes) or a grid point of one application (stencil).  Dirty lines still
+# in L2 when a kernel ends are not counted as DRAM writes by the profiler.
+NCU_TRAFFIC = {
+    "scan": ("scanl", 479.6e6 / (1 << 26)),
+    "dot": ("foldAll", 541.1e6 / (1 << 26)),
+    "hist": ("permute_smem", 272.4e6 / (1 << 26)),
+    "stencil": ("stencil_tile", 245.8e6 / (6144 * 6144)),
+    "blackscholes": ("map", 293.3e6 / (1 << 24)),
+    "rowsum": ("fold", 271.9e6 / (8192 * 8192)),
+}
+# algorithmic bytes per unit (see accelerate-cuda_b200/workloads.py)
+BYTES_PER_UNIT = {"scan": 8, "dot": 8, "hist": 4, "stencil": 8, "blackscholes": 20, "rowsum": 4}
 SPEC_PEAK_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 
@@ -416,10 +431,15 @@ def main():
         "clocks": clocks.summary(),
         "pct_of_spec_peak_8TBs": 100.0 * per_gpu / SPEC_PEAK_GBS,
     }
-    # dominant kernel = the skeleton's kernel; one launch per step moves the algorithmic bytes of a step
+    # dominant kernel = the skeleton's kernel; its launches in a step move the algorithmic bytes of the step.
+    # traffic: DRAM bytes per launch from one ncu capture of the same kernel on a smaller case (profiles/),
+    # scaled by the number of units a full launch processes (traffic grows in proportion to them).
+    kernel_name, traffic_per_unit = NCU_TRAFFIC[args.workload]
+    dom = getattr(wl, 'iters', 1)  # launches of the dominant kernel per step (10 for the iterated stencil)
+    units_per_launch = wl.bytes / BYTES_PER_UNIT[args.workload] / dom
     line["roofline"] = {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                        "traffic": None, "peak_kind": peak_kind,
-                        "kernel": "scanl" if args.workload == "scan" else args.workload}
+                        "traffic": traffic_per_unit * units_per_launch, "peak_kind": peak_kind, "kernel": kernel_name,
+                        "algorithmic_bytes_per_launch": wl.bytes / dom}
 
     if rank == 0 and world == 1 and not args.no_extras:
         # ---- e2e: run1 on pinned host arrays (upload + launch + download inside the timed region)
