@@ -283,7 +283,13 @@ __device__ __forceinline__ Opt<typename Fn::elem> scan_lookback(const accb_kpara
     }
     if (lane == 0) {
         const T incl = pre.have ? op(pre.v, agg) : agg;
-        status.publish(t, (epoch << 2) | ST_PREFIX, incl);
+#ifdef ACCB_SCAN_TEST_DROP_TILE0
+        /* test hook: the first tile never publishes, so every other tile's wait runs
+         * into its bound; used to check that the error word is raised and the launch
+         * still terminates */
+        if (t != 0)
+#endif
+            status.publish(t, (epoch << 2) | ST_PREFIX, incl);
         if (t == ntiles - 1 && p.ip[3] >= 0) scan_put_sum<Fn>(p, p.ip[3], incl, oseq);
         if (t == 0 && p.ip[4] >= 0 && seeded) scan_put_sum<Fn>(p, p.ip[4], fold_seed<Fn>(p), oseq);
     }
