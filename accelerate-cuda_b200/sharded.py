@@ -91,12 +91,13 @@ def exchange_halos(grid: torch.Tensor, ry: int, boundary: str = "clamp", group=N
     the caller keeps the constant there; mirror: reflected interior rows)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     interior = grid[ry:grid.shape[0] - ry]
-    top, bottom = interior[:ry].contiguous(), interior[-ry:].contiguous()
+    # row blocks of a contiguous grid are contiguous: sent from and received into place, no staging copies
+    top, bottom = interior[:ry], interior[-ry:]
     up, down = rank - 1, rank + 1
     ring = boundary == "wrap"
     if ring:
         up, down = up % world, down % world
-    ops, recv_top, recv_bot = [], torch.empty_like(top), torch.empty_like(bottom)
+    ops, recv_top, recv_bot = [], grid[:ry], grid[grid.shape[0] - ry:]
     has_up, has_down = up >= 0, down < world
     if world > 1:
         # Rows travelling up carry tag 0, rows travelling down tag 1.  NCCL matches the messages
@@ -114,15 +115,17 @@ def exchange_halos(grid: torch.Tensor, ry: int, boundary: str = "clamp", group=N
         for w in dist.batch_isend_irecv(ops):
             w.wait()
     if world == 1 and ring:
-        recv_top, recv_bot, has_up, has_down = bottom, top, True, True
+        grid[:ry] = bottom
+        grid[-ry:] = top
+        return grid
     if has_up:
-        grid[:ry] = recv_top
+        pass  # received in place
     elif boundary == "clamp":
         grid[:ry] = interior[:1].expand(ry, -1)
     elif boundary == "mirror":
         grid[:ry] = interior[1:ry + 1].flip(0)
     if has_down:
-        grid[-ry:] = recv_bot
+        pass  # received in place
     elif boundary == "clamp":
         grid[-ry:] = interior[-1:].expand(ry, -1)
     elif boundary == "mirror":

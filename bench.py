@@ -189,20 +189,30 @@ class DotWorkload(Workload):
         self.n = n or W.N28
         self.x = t.empty(self.n, dtype=t.float32, device="cuda")
         self.y = t.empty(self.n, dtype=t.float32, device="cuda")
-        self.ctx.gen_uniform_f32(self.x, self.n, 0, W.SEED, W.S_XS, -1.0, 1.0)
-        self.ctx.gen_uniform_f32(self.y, self.n, 0, W.SEED, W.S_YS, -1.0, 1.0)
+        first = self.rank * self.n  # each rank holds its own slab of one world*n vector
+        self.ctx.gen_uniform_f32(self.x, self.n, first, W.SEED, W.S_XS, -1.0, 1.0)
+        self.ctx.gen_uniform_f32(self.y, self.n, first, W.SEED, W.S_YS, -1.0, 1.0)
         self.out = t.zeros(1, dtype=t.float32, device="cuda")
         self.k = self.ctx.kernel(self.P.DOT).wait()
         self.bytes = W.bytes_dot(self.n)
+        if self.world > 1:
+            self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
         self.ctx.sync()
 
     def step(self):
         self.ctx.fold_all(self.k, [self.x, self.y], self.n, self.out, seed=np.float32(0))
+        if self.world > 1:  # partials all-gathered and combined in rank order
+            self.result = self.sh.sharded_fold_all(self.out, lambda a, b: a + b)
         return 1
 
     def verify(self):
         ref = float((self.x.double() * self.y.double()).sum())
-        return abs(float(self.out[0]) - ref) <= 1e-5 * abs(ref)
+        ok = abs(float(self.out[0]) - ref) <= 1e-5 * abs(ref)
+        if self.world > 1:
+            tot = self.t.tensor([ref], dtype=self.t.float64, device="cuda")
+            self.sh.dist.all_reduce(tot)
+            ok = ok and abs(float(self.result[0]) - float(tot[0])) <= 1e-5 * abs(float(tot[0]))
+        return ok
 
 
 class HistWorkload(Workload):
@@ -213,21 +223,29 @@ class HistWorkload(Workload):
         self.n = n or W.N28
         self.keys = t.empty(self.n, dtype=t.int32, device="cuda")
         cdf = t.from_numpy(W.zipf_cdf()).cuda()
-        self.ctx.gen_zipf_mix_i32(self.keys, self.n, 0, W.SEED, cdf, W.HIST_BINS)
+        self.ctx.gen_zipf_mix_i32(self.keys, self.n, self.rank * self.n, W.SEED, cdf, W.HIST_BINS)
         self.defaults = t.zeros(W.HIST_BINS, dtype=t.int32, device="cuda")
         self.out = t.zeros(W.HIST_BINS, dtype=t.int32, device="cuda")
         self.k = self.ctx.kernel(self.P.HIST).wait()
         self.bytes = W.bytes_hist(self.n)
+        if self.world > 1:
+            self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
         self.ctx.sync()
 
     def step(self):
         self.ctx.permute(self.k, [self.keys], self.n, self.out, defaults=self.defaults)
+        if self.world > 1:  # per-GPU partial histograms, one all-reduce of 16 KiB
+            self.result = self.sh.sharded_histogram(self.out, self.defaults)
         return 1
 
     def verify(self):
         t = self.t
         ref = t.bincount(self.keys.long(), minlength=self.W.HIST_BINS).int()
-        return bool(t.equal(ref, self.out)) and int(self.out.sum()) == self.n
+        ok = bool(t.equal(ref, self.out)) and int(self.out.sum()) == self.n
+        if self.world > 1:
+            self.sh.dist.all_reduce(ref)
+            ok = ok and bool(t.equal(ref, self.result)) and int(self.result.sum()) == self.n * self.world
+        return ok
 
 
 class StencilWorkload(Workload):
@@ -237,18 +255,33 @@ class StencilWorkload(Workload):
         t, W = self.t, self.W
         self.h = self.w = n or 8192
         self.iters = 10
-        self.a = t.empty((self.h, self.w), dtype=t.float32, device="cuda")
+        # with several GPUs each rank owns a slab of h rows of a (world*h) x w grid, plus one halo row
+        # above and below that its neighbours refresh before every application
+        halo = 1 if self.world > 1 else 0
+        rows = self.h + 2 * halo
+        self.a = t.empty((rows, self.w), dtype=t.float32, device="cuda")
         self.b = t.empty_like(self.a)
-        self.src = t.empty_like(self.a)
-        self.ctx.gen_uniform_f32(self.src, self.h * self.w, 0, W.SEED, W.S_GRID, 0.0, 1.0)
+        self.src = t.zeros_like(self.a)
+        self.ctx.gen_uniform_f32(self.src[halo:halo + self.h], self.h * self.w, self.rank * self.h * self.w, W.SEED,
+                                 W.S_GRID, 0.0, 1.0)
         self.k = self.ctx.kernel(self.P.BLUR).wait()
         self.bytes = W.bytes_stencil(self.h, self.w, self.iters)
+        if self.world > 1:
+            self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
         self.ctx.sync()
 
     def step(self):
-        # first application reads the pristine source, so every step does identical work
-        self.ctx.stencil(self.k, self.src, self.a, boundary="clamp")
-        self.res = self.ctx.stencil_iterate(self.k, self.a, self.b, self.iters - 1, boundary="clamp")
+        if self.world == 1:
+            # first application reads the pristine source, so every step does identical work
+            self.ctx.stencil(self.k, self.src, self.a, boundary="clamp")
+            self.res = self.ctx.stencil_iterate(self.k, self.a, self.b, self.iters - 1, boundary="clamp")
+            return self.iters
+        cur, nxt = self.src, self.a
+        for _ in range(self.iters):
+            self.sh.exchange_halos(cur, 1, "clamp")  # one 32 KiB row each way, into this rank's own halo rows
+            self.ctx.stencil(self.k, cur, nxt, boundary="clamp")
+            cur, nxt = nxt, (self.b if nxt is self.a else self.a)
+        self.res = cur[1:-1]
         return self.iters
 
     def verify(self):
