@@ -97,13 +97,17 @@ struct accb_event {
 
 namespace accb_rt {
 
+constexpr int kRowCounterBase = 16; /* first row counter in StreamScratch::words */
+constexpr int kRowCounters = 4096;  /* most rows a split fold takes */
+
 struct StreamScratch {
     void *status = nullptr;       /* scan tile status */
     size_t status_bytes = 0;
     int status_layout = 0;        /* bytes per tile record of the last scan */
     void *partial = nullptr;      /* fold partials */
     size_t partial_bytes = 0;
-    unsigned *words = nullptr;    /* [0] fold ticket, [1] scan ticket, [2] error word */
+    unsigned *words = nullptr;    /* [0] fold ticket, [1] scan ticket, [2] error word,
+                                     [kRowCounterBase..] per-row arrival counters of a split fold */
     unsigned scan_ticket = 0;     /* host mirror of words[1] */
     unsigned epoch = 0;
 };

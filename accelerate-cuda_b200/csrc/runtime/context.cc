@@ -131,8 +131,9 @@ StreamScratch *scratch_for(accb_context *ctx, cudaStream_t s) {
     auto it = ctx->scratch.find(s);
     if (it != ctx->scratch.end()) return &it->second;
     StreamScratch sc;
-    if (cudaMalloc((void **)&sc.words, 64) != cudaSuccess) return nullptr;
-    if (cudaMemsetAsync(sc.words, 0, 64, s) != cudaSuccess) return nullptr;
+    const size_t bytes = (kRowCounterBase + kRowCounters) * sizeof(unsigned);
+    if (cudaMalloc((void **)&sc.words, bytes) != cudaSuccess) return nullptr;
+    if (cudaMemsetAsync(sc.words, 0, bytes, s) != cudaSuccess) return nullptr;
     return &(ctx->scratch[s] = sc);
 }
 

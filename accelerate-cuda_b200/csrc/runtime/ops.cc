@@ -135,6 +135,16 @@ static int check_skeleton(accb_context *ctx, accb_kernel *k, std::initializer_li
 
 static long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
 
+/* Threads that share one range of `items` loads (vectors or scalars) when `units` ranges are
+ * reduced: 4, 8, 16 or 32 lanes, or 256 (a block) once a range has at least `block_from` loads or
+ * there are too few ranges to fill the GPU with warps. */
+static int pick_group(long long items, long long units, long long block_from) {
+    if (items >= block_from || (items >= 512 && units < 8192)) return 256;
+    int g = 4;
+    while (g < 32 && (long long)g * 8 < items) g *= 2;
+    return g;
+}
+
 }  // namespace accb_rt
 
 using namespace accb_rt;
@@ -239,12 +249,34 @@ int accb_fold_dim(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     p.n = rows * cols;
     p.ip[0] = rows;
     p.ip[1] = cols;
-    /* threads per row: a whole block for long rows, a warp, or 4 lanes */
-    const char *entry = cols >= 2048 ? "fold" : (cols >= 32 ? "fold_warp" : "fold_sub");
+    /* threads per row (the reference always uses one block per row, Launch.hs:120): a whole block
+     * for long rows, else an aligned group of 32 / 16 / 8 / 4 lanes sized so that a lane gets
+     * about 8 vectors of the row */
+    const int group = pick_group(cols % 4 == 0 ? cols / 4 : cols, rows, 2048);
+    const char *entry = group > 32 ? "fold" : group == 32 ? "fold_warp" : group == 16 ? "fold_g16" : group == 8 ? "fold_g8" : "fold_g4";
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
-    const int group = cols >= 2048 ? pr.block : (cols >= 32 ? 32 : 4);
-    const long long units = ceil_div(rows, pr.block / group);
+    const long long resident = (long long)ctx->sm_count * pr.per_sm;
+    const long long quantum = (long long)pr.block * pr.meta.v[4] * 4; /* elements a block takes per trip */
+    if (group > 32 && rows <= kRowCounters && rows < 4 * resident && cols >= 8 * quantum) {
+        /* too few rows to occupy the GPU evenly: cut every row into pieces, one block each, so
+         * that there are many more pieces than resident blocks */
+        long long pieces = std::min<long long>(ceil_div(16 * resident, rows), cols / (4 * quantum));
+        const long long chunk = ceil_div(ceil_div(cols, pieces), quantum) * quantum;
+        pieces = ceil_div(cols, chunk);
+        TRY(prepare(ctx, k, "fold_split", 0, &pr));
+        cudaStream_t s = (cudaStream_t)stream;
+        StreamScratch *sc = scratch_for(ctx, s);
+        if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+        TRY(grow(ctx, &sc->partial, &sc->partial_bytes, (size_t)(rows * pieces) * std::max(8, pr.meta.v[2]), s, false));
+        p.ip[2] = pieces;
+        p.ip[3] = chunk;
+        p.aux[0] = sc->partial;
+        p.aux[1] = sc->words + kRowCounterBase;
+        const int grid = (int)std::min<long long>(rows * pieces, (long long)ctx->sm_count * pr.per_sm);
+        return launch(ctx, pr.fn, "fold_split", grid, pr.block, 0, s, p);
+    }
+    const long long units = ceil_div(rows, pr.block / std::min(group, pr.block));
     const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * pr.per_sm);
     return launch(ctx, pr.fn, entry, grid, pr.block, 0, (cudaStream_t)stream, p);
 }
@@ -267,12 +299,15 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     p.ip[1] = cols;
     p.ip[2] = nseg;
     p.aux[0] = const_cast<int *>(offsets);
+    /* the reference gives every segment one warp (Launch.hs:118); here the group follows the
+     * average segment length (accesses are scalar, so a lane should get about 8 elements) */
+    const int group = pick_group(cols / std::max(1LL, nseg), rows * nseg, 8192);
+    const char *entry = group > 32 ? "foldSeg_block" : group == 32 ? "foldSeg" : group == 16 ? "foldSeg_g16" : group == 8 ? "foldSeg_g8" : "foldSeg_g4";
     Prep pr;
-    TRY(prepare(ctx, k, "foldSeg", 0, &pr));
-    /* one warp per segment (Launch.hs:118) */
-    const long long units = ceil_div(rows * nseg, pr.block / 32);
+    TRY(prepare(ctx, k, entry, 0, &pr));
+    const long long units = ceil_div(rows * nseg, pr.block / std::min(group, pr.block));
     const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * pr.per_sm);
-    return launch(ctx, pr.fn, "foldSeg", grid, pr.block, 0, (cudaStream_t)stream, p);
+    return launch(ctx, pr.fn, entry, grid, pr.block, 0, (cudaStream_t)stream, p);
 }
 
 /* ----------------------------------------------------------------- scan */
@@ -457,8 +492,19 @@ static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, 
     /* Tile form (input tile staged in shared memory by TMA): needs 4-byte elements (the kernel
      * reports 0 bytes of shared memory otherwise), 16-byte aligned arrays, widths that are
      * multiples of 4 and enough rows to fill a tile. */
-    bool tiled = pr.meta.v[6] > 0 && (p.flags & ACCB_F_VEC) && W % 4 == 0 && H >= 16 && !getenv("ACCB_STENCIL_NO_TILE");
-    for (int a = 0; a < nsrc; ++a) tiled = tiled && p.ip[6 + 2 * a] % 4 == 0;
+    bool staged = (p.flags & ACCB_F_VEC) && W % 4 == 0 && !getenv("ACCB_STENCIL_NO_TILE");
+    for (int a = 0; a < nsrc; ++a) staged = staged && p.ip[6 + 2 * a] % 4 == 0;
+    const bool tiled = staged && pr.meta.v[6] > 0 && H >= 16;
+    if (staged && out->rank == 1 && pr.meta.v[5] > 0 && W >= 4096) {
+        /* line form: one bulk copy of (tile + 8 halo elements) x 4 bytes per source */
+        const std::string lentry = std::string(entry) + "_line";
+        const size_t smem = (size_t)nsrc * (pr.meta.v[5] + 8) * 4;
+        Prep pl;
+        TRY(prepare(ctx, k, lentry.c_str(), smem, &pl));
+        p.ip[0] = 1;
+        p.ip[1] = W;
+        return launch(ctx, pl.fn, lentry.c_str(), (int)ceil_div(W, pl.meta.v[5]), pl.block, smem, s, p);
+    }
     if (tiled) {
         const std::string tentry = std::string(entry) + "_tile";
         const size_t smem = (size_t)pr.meta.v[6];

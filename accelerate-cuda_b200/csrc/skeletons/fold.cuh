@@ -129,6 +129,7 @@ __device__ __forceinline__ void fold_range(const accb_kparams &p, const Env &env
         acc.v = acc.have ? Fn::combine(acc.v, s) : s;
         acc.have = 1;
     }
+#pragma unroll 4
     for (long long i = lo + nvec * V + g; i < lo + len; i += G) {
         regs<1, In> a;
         T x[1];
@@ -198,104 +199,173 @@ __device__ __forceinline__ void fold_all_body(const accb_kparams &p) {
     }
 }
 
-/* ------------------------------------------------------ fold over inner dim */
-/* ip[0] = rows (outer size), ip[1] = cols (innermost extent).
- * GROUP = threads cooperating on one row: CTA (block per row) or 32/16/8/... */
-template <class Fn, int CTA, int GROUP, int U>
-__device__ __forceinline__ void fold_dim_body(const accb_kparams &p) {
+/* ---------------------------------------- fold over inner dim and foldSeg */
+/* Both reduce many independent ranges ("units": a row, or a segment of a row).
+ * GROUP threads cooperate on one unit: the whole block (long ranges), a warp,
+ * or an aligned sub-warp group of 16 / 8 / 4 lanes (short ranges, so that the
+ * lanes of a warp still read one contiguous stretch of memory).  A group
+ * takes KR units per trip so that short ranges still leave several loads in
+ * flight per lane.  `range(w, lo, len, vec)` describes unit w. */
+template <class Fn, int CTA, int GROUP, int U, int KR, class Range>
+__device__ __forceinline__ void fold_units(const accb_kparams &p, long long units, Range range) {
     typedef typename Fn::acc A;
     typedef Opt<A> O;
     __shared__ O s_red[CTA / 32];
     const Env env(p);
     const OptCombine<Fn> oc;
     const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
-    const long long rows = p.ip[0], cols = p.ip[1];
-    const bool vec_ok = (p.flags & ACCB_F_VEC) != 0 && (cols % V) == 0;
     const bool seeded = (p.flags & ACCB_F_HAS_SEED) != 0;
+    auto finish = [&](long long w, O acc) {
+        if (seeded) {
+            const A z = Fn::lift(fold_seed<Fn>(p));
+            acc.v = acc.have ? Fn::combine(acc.v, z) : z;
+            acc.have = 1;
+        }
+        if (acc.have) fold_put<Fn>(p, w, Fn::lower(acc.v), oseq);
+    };
 
     if constexpr (GROUP == CTA) {
-        for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+        for (long long w = blockIdx.x; w < units; w += gridDim.x) {
+            long long lo, len;
+            bool vec;
+            range(w, lo, len, vec);
             O acc;
             acc.have = 0;
-            fold_range<Fn, U>(p, env, r * cols, cols, threadIdx.x, CTA, vec_ok, acc);
+            fold_range<Fn, U>(p, env, lo, len, threadIdx.x, CTA, vec, acc);
             acc = block_reduce<CTA>(acc, oc, s_red);
-            if (threadIdx.x == 0) {
-                if (seeded) {
-                    const A z = Fn::lift(fold_seed<Fn>(p));
-                    acc.v = acc.have ? Fn::combine(acc.v, z) : z;
-                    acc.have = 1;
-                }
-                if (acc.have) fold_put<Fn>(p, r, Fn::lower(acc.v), oseq);
-            }
+            if (threadIdx.x == 0) finish(w, acc);
         }
     } else {
-        constexpr int PER = CTA / GROUP; /* rows per block per trip */
+        constexpr int PER = CTA / GROUP; /* units per block per sweep */
         const int g = threadIdx.x % GROUP;
-        for (long long r = (long long)blockIdx.x * PER + threadIdx.x / GROUP; r < rows;
-             r += (long long)gridDim.x * PER) {
-            O acc;
-            acc.have = 0;
-            fold_range<Fn, U>(p, env, r * cols, cols, g, GROUP, vec_ok, acc);
-            /* reduce inside the aligned group of GROUP lanes; a group's lanes
-             * share r, so they leave the loop together */
-            const unsigned gmask =
-                GROUP == 32 ? FULL : (((1u << GROUP) - 1u) << ((threadIdx.x & 31) / GROUP * GROUP));
+        const long long sweep = (long long)gridDim.x * PER;
+        /* the lanes of a group share their unit, so they leave the loops together */
+        const unsigned gmask = GROUP == 32 ? FULL : (((1u << GROUP) - 1u) << ((threadIdx.x & 31) / GROUP * GROUP));
+        for (long long w0 = (long long)blockIdx.x * PER + threadIdx.x / GROUP; w0 < units; w0 += sweep * KR) {
+            O acc[KR];
 #pragma unroll
-            for (int m = GROUP / 2; m > 0; m >>= 1) {
-                O o;
-                o.have = __shfl_xor_sync(gmask, acc.have, m);
-                constexpr int W = (sizeof(A) + 3) / 4;
-                unsigned w[W] = {};
-                memcpy(w, &acc.v, sizeof(A));
-#pragma unroll
-                for (int k = 0; k < W; ++k) w[k] = __shfl_xor_sync(gmask, w[k], m);
-                memcpy(&o.v, w, sizeof(A));
-                acc = oc(acc, o);
-            }
-            if (g == 0) {
-                if (seeded) {
-                    const A z = Fn::lift(fold_seed<Fn>(p));
-                    acc.v = acc.have ? Fn::combine(acc.v, z) : z;
-                    acc.have = 1;
+            for (int k = 0; k < KR; ++k) {
+                acc[k].have = 0;
+                const long long w = w0 + k * sweep;
+                if (w < units) {
+                    long long lo, len;
+                    bool vec;
+                    range(w, lo, len, vec);
+                    fold_range<Fn, U>(p, env, lo, len, g, GROUP, vec, acc[k]);
                 }
-                if (acc.have) fold_put<Fn>(p, r, Fn::lower(acc.v), oseq);
+            }
+#pragma unroll
+            for (int k = 0; k < KR; ++k) {
+                const long long w = w0 + k * sweep;
+                if (w < units) {
+#pragma unroll
+                    for (int m = GROUP / 2; m > 0; m >>= 1) {
+                        O o;
+                        o.have = __shfl_xor_sync(gmask, acc[k].have, m);
+                        constexpr int W = (sizeof(A) + 3) / 4;
+                        unsigned wd[W] = {};
+                        memcpy(wd, &acc[k].v, sizeof(A));
+#pragma unroll
+                        for (int q = 0; q < W; ++q) wd[q] = __shfl_xor_sync(gmask, wd[q], m);
+                        memcpy(&o.v, wd, sizeof(A));
+                        acc[k] = oc(acc[k], o);
+                    }
+                    if (g == 0) finish(w, acc[k]);
+                }
             }
         }
     }
 }
 
-/* ------------------------------------------------------------------ foldSeg */
-/* One warp per (row, segment).  aux[0] = Int32 offsets, length nseg+1: the
- * exclusive scan of the segment lengths (Execute.hs:320-324).
- * ip[0] = rows, ip[1] = cols (innermost extent of the source), ip[2] = nseg. */
-template <class Fn, int CTA>
-__device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
+/* fold / fold1 over the innermost dimension: ip[0] = rows (outer size),
+ * ip[1] = cols (innermost extent); unit = row. */
+template <class Fn, int CTA, int GROUP, int U, int KR>
+__device__ __forceinline__ void fold_dim_body(const accb_kparams &p) {
+    const long long rows = p.ip[0], cols = p.ip[1];
+    const bool vec_ok = (p.flags & ACCB_F_VEC) != 0 && (cols % V) == 0;
+    fold_units<Fn, CTA, GROUP, U, KR>(p, rows, [&](long long w, long long &lo, long long &len, bool &vec) {
+        lo = w * cols;
+        len = cols;
+        vec = vec_ok;
+    });
+}
+
+/* Few, very long rows: a row is cut into ip[2] pieces of ip[3] elements (a
+ * multiple of V; the last piece is shorter) so that all SMs get work.  One
+ * block per (row, piece); the block that completes a row last (arrival counter
+ * per row in aux[1], which it resets) combines the row's partials from aux[0]
+ * in piece order and applies the seed -- the scheme of foldAll, per row. */
+template <class Fn, int CTA, int U>
+__device__ __forceinline__ void fold_split_body(const accb_kparams &p) {
     typedef typename Fn::acc A;
     typedef Opt<A> O;
+    __shared__ O s_red[CTA / 32];
+    __shared__ int s_last;
     const Env env(p);
     const OptCombine<Fn> oc;
     const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
-    const long long rows = p.ip[0], cols = p.ip[1], nseg = p.ip[2];
-    const int *offs = static_cast<const int *>(p.aux[0]);
-    const bool seeded = (p.flags & ACCB_F_HAS_SEED) != 0;
-    const long long total = rows * nseg;
-    constexpr int WPB = CTA / 32;
-    for (long long w = (long long)blockIdx.x * WPB + warp_id(); w < total; w += (long long)gridDim.x * WPB) {
-        const long long r = w / nseg, s = w - r * nseg;
-        const long long lo = offs[s], hi = offs[s + 1];
+    const long long rows = p.ip[0], cols = p.ip[1], pieces = p.ip[2], chunk = p.ip[3];
+    const bool vec_ok = (p.flags & ACCB_F_VEC) != 0 && (cols % V) == 0;
+    O *partial = static_cast<O *>(p.aux[0]);
+    unsigned int *arrived = static_cast<unsigned int *>(p.aux[1]);
+    for (long long w = blockIdx.x; w < rows * pieces; w += gridDim.x) {
+        const long long r = w / pieces, pc = w - r * pieces;
+        const long long lo = pc * chunk, len = min(chunk, cols - lo);
         O acc;
         acc.have = 0;
-        fold_range<Fn, 1>(p, env, r * cols + lo, hi - lo, lane_id(), 32, false, acc);
-        acc = warp_reduce_xor(acc, oc);
-        if (lane_id() == 0) {
-            if (seeded) {
-                const A z = Fn::lift(fold_seed<Fn>(p));
-                acc.v = acc.have ? Fn::combine(acc.v, z) : z;
-                acc.have = 1;
-            }
-            if (acc.have) fold_put<Fn>(p, w, Fn::lower(acc.v), oseq);
+        fold_range<Fn, U>(p, env, r * cols + lo, len, threadIdx.x, CTA, vec_ok, acc);
+        acc = block_reduce<CTA>(acc, oc, s_red);
+        if (threadIdx.x == 0) {
+            partial[w] = acc;
+            __threadfence();
+            s_last = atomicAdd(arrived + r, 1u) == (unsigned)pieces - 1u;
         }
+        __syncthreads();
+        if (s_last) { /* uniform over the block */
+            __threadfence();
+            O tot;
+            tot.have = 0;
+            for (long long b = threadIdx.x; b < pieces; b += CTA) tot = oc(tot, ld_cg(partial + r * pieces + b));
+            tot = block_reduce<CTA>(tot, oc, s_red);
+            if (threadIdx.x == 0) {
+                arrived[r] = 0u;
+                if (p.flags & ACCB_F_HAS_SEED) {
+                    const A z = Fn::lift(fold_seed<Fn>(p));
+                    tot.v = tot.have ? Fn::combine(tot.v, z) : z;
+                    tot.have = 1;
+                }
+                if (tot.have) fold_put<Fn>(p, r, Fn::lower(tot.v), oseq);
+            }
+        }
+        __syncthreads(); /* s_last and s_red are reused by the next unit */
     }
+}
+
+/* foldSeg / fold1Seg: unit = (row, segment).  aux[0] = Int32 offsets, length
+ * nseg+1: the exclusive scan of the segment lengths (Execute.hs:320-324).
+ * ip[0] = rows, ip[1] = cols (innermost extent of the source), ip[2] = nseg.
+ * Segments start anywhere, so accesses are scalar. */
+template <class Fn, int CTA, int GROUP, int KR>
+__device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
+    const long long rows = p.ip[0], cols = p.ip[1], nseg = p.ip[2];
+    const int *offs = static_cast<const int *>(p.aux[0]);
+    fold_units<Fn, CTA, GROUP, 1, KR>(p, rows * nseg, [&](long long w, long long &lo, long long &len, bool &vec) {
+        /* a 64-bit division per segment would cost more than a short segment's loads */
+        long long r = 0, sgm = w;
+        if (rows != 1) {
+            if (rows * nseg <= 0xffffffffLL) {
+                r = (unsigned)w / (unsigned)nseg;
+                sgm = w - r * nseg;
+            } else {
+                r = w / nseg;
+                sgm = w - r * nseg;
+            }
+        }
+        const long long b = offs[sgm];
+        lo = r * cols + b;
+        len = offs[sgm + 1] - b;
+        vec = false;
+    });
 }
 
 }  // namespace accb
@@ -312,24 +382,37 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
         accb::fold_all_body<Fn, ACCB_FOLD_CTA, ACCB_FOLD_U>(p);                         \
     }
 
-#define ACCB_INSTANTIATE_FOLD_DIM(Fn)                                                   \
-    ACCB_META(3, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, ACCB_FOLD_U, 0)           \
+#define ACCB_FOLD_DIM_ENTRY(Fn, name, group, u, kr)                                      \
     extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
-        fold(const __grid_constant__ accb_kparams p) {                                  \
-        accb::fold_dim_body<Fn, ACCB_FOLD_CTA, ACCB_FOLD_CTA, ACCB_FOLD_U>(p);          \
-    }                                                                                   \
-    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
-        fold_warp(const __grid_constant__ accb_kparams p) {                             \
-        accb::fold_dim_body<Fn, ACCB_FOLD_CTA, 32, 2>(p);                               \
-    }                                                                                   \
-    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
-        fold_sub(const __grid_constant__ accb_kparams p) {                              \
-        accb::fold_dim_body<Fn, ACCB_FOLD_CTA, 4, 1>(p);                                \
+        name(const __grid_constant__ accb_kparams p) {                                  \
+        accb::fold_dim_body<Fn, ACCB_FOLD_CTA, group, u, kr>(p);                        \
     }
 
+/* one entry per group size; the host picks by row length */
+#define ACCB_INSTANTIATE_FOLD_DIM(Fn)                                                   \
+    ACCB_META(3, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, ACCB_FOLD_U, 0)           \
+    ACCB_FOLD_DIM_ENTRY(Fn, fold, ACCB_FOLD_CTA, ACCB_FOLD_U, 1)                        \
+    ACCB_FOLD_DIM_ENTRY(Fn, fold_warp, 32, 4, 1)                                        \
+    ACCB_FOLD_DIM_ENTRY(Fn, fold_g16, 16, 4, 1)                                         \
+    ACCB_FOLD_DIM_ENTRY(Fn, fold_g8, 8, 4, 2)                                           \
+    ACCB_FOLD_DIM_ENTRY(Fn, fold_g4, 4, 4, 4)                                           \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
+        fold_split(const __grid_constant__ accb_kparams p) {                            \
+        accb::fold_split_body<Fn, ACCB_FOLD_CTA, ACCB_FOLD_U>(p);                       \
+    }
+
+#define ACCB_FOLD_SEG_ENTRY(Fn, name, group, kr)                                        \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
+        name(const __grid_constant__ accb_kparams p) {                                  \
+        accb::fold_seg_body<Fn, ACCB_FOLD_CTA, group, kr>(p);                           \
+    }
+
+/* `foldSeg` is the reference's warp-per-segment form (Reduction.hs:430); the
+ * others serve shorter and longer segments */
 #define ACCB_INSTANTIATE_FOLD_SEG(Fn)                                                   \
     ACCB_META(4, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, 1, 0)                     \
-    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
-        foldSeg(const __grid_constant__ accb_kparams p) {                               \
-        accb::fold_seg_body<Fn, ACCB_FOLD_CTA>(p);                                      \
-    }
+    ACCB_FOLD_SEG_ENTRY(Fn, foldSeg, 32, 1)                                             \
+    ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g16, 16, 2)                                         \
+    ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g8, 8, 2)                                           \
+    ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g4, 4, 4)                                           \
+    ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_block, ACCB_FOLD_CTA, 1)

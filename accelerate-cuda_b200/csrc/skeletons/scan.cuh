@@ -76,8 +76,14 @@
 #ifndef ACCB_SCAN_CTA
 #define ACCB_SCAN_CTA (ACCB_SCAN_TMA ? 256 : 128)
 #endif
-#ifndef ACCB_SCAN_ROWS
-#define ACCB_SCAN_ROWS (ACCB_SCAN_TMA ? 8 : 4)
+/* rows of CTA x 4 elements per tile.  With the tile in shared memory the row count follows the bytes
+ * of one element over all input components, so that a tile stays at 32 KB and six blocks fit an SM */
+#ifdef ACCB_SCAN_ROWS
+#define ACCB_SCAN_ROWS_FOR(Fn) ACCB_SCAN_ROWS
+#elif ACCB_SCAN_TMA
+#define ACCB_SCAN_ROWS_FOR(Fn) (accb::scan_rows_for<Fn::In>::value)
+#else
+#define ACCB_SCAN_ROWS_FOR(Fn) 4
 #endif
 #ifndef ACCB_SCAN_STATUS_STRIDE
 #define ACCB_SCAN_STATUS_STRIDE 16 /* distance between tile status words, in 8-byte units */
@@ -92,7 +98,7 @@
 #ifdef ACCB_SCAN_MINB
 #define ACCB_SCAN_MINB_FOR(Fn) ACCB_SCAN_MINB
 #elif ACCB_SCAN_TMA
-#define ACCB_SCAN_MINB_FOR(Fn) (sizeof(Fn::elem) <= 4 ? 6 : (sizeof(Fn::elem) <= 8 ? 4 : 2))
+#define ACCB_SCAN_MINB_FOR(Fn) (sizeof(Fn::elem) <= 4 ? 6 : (sizeof(Fn::elem) <= 8 ? 5 : 3))
 #else
 #define ACCB_SCAN_MINB_FOR(Fn) (sizeof(Fn::elem) <= 4 ? 12 : (sizeof(Fn::elem) <= 8 ? 6 : 3))
 #endif
@@ -115,15 +121,22 @@ struct Scan {
 
 enum : unsigned { ST_AGG = 1u, ST_PREFIX = 2u };
 
-/* ---- tile status: one 64-bit word {flag, value} when the value fits 32 bits,
- * otherwise {flag | aggregate | prefix} records published with release /
- * acquire ordering.  Neighbouring tiles' words are ACCB_SCAN_STATUS_STRIDE * 8
- * bytes apart. ---- */
-template <class T, bool PACKED = (sizeof(T) <= 4)>
+/* ---- tile status.  A tile's record is kBytes long and starts with a 64-bit
+ * head whose upper half is the flag {epoch << 2 | state} in every layout, so a
+ * record left behind by a scan of another value type reads as an earlier
+ * epoch, i.e. "not ready".
+ *   values up to 4 bytes : the value sits in the lower half of the head; one
+ *                          relaxed 64-bit store / load carries flag and value;
+ *   values of 8 bytes    : {head, value} as one 128-bit store / load;
+ *   larger values        : {head, aggregate, prefix}, the flag published with
+ *                          release and read with acquire ordering.
+ * Neighbouring tiles' records are at least ACCB_SCAN_STATUS_STRIDE * 8 bytes
+ * apart. ---- */
+template <class T, int LAYOUT = (sizeof(T) <= 4 ? 0 : (sizeof(T) == 8 ? 1 : 2))>
 struct TileStatus;
 
 template <class T>
-struct TileStatus<T, true> {
+struct TileStatus<T, 0> {
     static constexpr int kBytes = 8 * ACCB_SCAN_STATUS_STRIDE;
     unsigned long long *w;
     __device__ __forceinline__ explicit TileStatus(void *base) : w(static_cast<unsigned long long *>(base)) {}
@@ -148,11 +161,36 @@ struct TileStatus<T, true> {
 };
 
 template <class T>
-struct TileStatus<T, false> {
+struct TileStatus<T, 1> {
+    static constexpr int kStride = ACCB_SCAN_STATUS_STRIDE < 2 ? 2 : (ACCB_SCAN_STATUS_STRIDE + 1) / 2 * 2;
+    static constexpr int kBytes = 8 * kStride; /* 16-byte aligned records */
+    unsigned long long *w;
+    __device__ __forceinline__ explicit TileStatus(void *base) : w(static_cast<unsigned long long *>(base)) {}
+    __device__ __forceinline__ void publish(long long t, unsigned flag, T v) const {
+        unsigned long long bits;
+        memcpy(&bits, &v, 8);
+        const unsigned long long head = (unsigned long long)flag << 32;
+        asm volatile("{ .reg .b128 q; mov.b128 q, {%1, %2}; st.relaxed.gpu.global.b128 [%0], q; }" ::"l"(w + t * kStride),
+                     "l"(head), "l"(bits)
+                     : "memory");
+    }
+    __device__ __forceinline__ unsigned peek(long long t, T &v) const {
+        unsigned long long head, bits;
+        asm volatile("{ .reg .b128 q; ld.relaxed.gpu.global.b128 q, [%2]; mov.b128 {%0, %1}, q; }"
+                     : "=l"(head), "=l"(bits)
+                     : "l"(w + t * kStride)
+                     : "memory");
+        memcpy(&v, &bits, 8);
+        return (unsigned)(head >> 32);
+    }
+};
+
+template <class T>
+struct TileStatus<T, 2> {
     static_assert(sizeof(T) % 4 == 0 && sizeof(T) <= 32, "scan value types are at most 32 bytes");
     struct alignas(128) Rec {
-        unsigned flag;
         unsigned pad;
+        unsigned flag;
         T agg;
         T pre;
     };
@@ -327,11 +365,36 @@ struct smem_offset<L, 0, TILE> {
     static constexpr int value = 0;
 };
 
+/* tile rows for a 32 KB tile: 8 for up to 4 bytes per element (all components), 4 up to 8, else 2 */
+template <class L>
+struct scan_rows_for {
+    static constexpr int bpe = smem_offset<L, L::size, 128>::value / 128;
+    static constexpr int value = bpe <= 4 ? 8 : (bpe <= 8 ? 4 : 2);
+};
+
+/* 4 consecutive values of one component from shared memory.  8-byte values make 32 bytes per
+ * thread: read as two 16-byte halves at a 32-byte thread stride, threads l and l+4 of a quarter warp
+ * would hit the same banks, so every other group of 4 threads takes its halves in the opposite
+ * order (and swaps them back in registers). */
+template <class T>
+__device__ __forceinline__ void smem_load4(const T *base, int vi, T (&r)[V]) {
+    if constexpr (sizeof(T) == 8) {
+        const uint4 *q = reinterpret_cast<const uint4 *>(base) + 2 * vi;
+        const int flip = (vi >> 2) & 1;
+        const uint4 a = q[flip], b = q[flip ^ 1];
+        const uint4 lo = flip ? b : a, hi = flip ? a : b;
+        memcpy(&r[0], &lo, 16);
+        memcpy(&r[2], &hi, 16);
+    } else {
+        load4<Cache::Default>(base, vi, r);
+    }
+}
+
 template <class L, int TILE, int... I>
 __device__ __forceinline__ void smem_load_row(const unsigned char *s, int vi, regs<V, L> &r,
                                               std::integer_sequence<int, I...>) {
-    (load4<Cache::Default>(reinterpret_cast<const typename type_at<I, L>::type *>(s + smem_offset<L, I, TILE>::value),
-                           vi, comp<I>(r)),
+    (smem_load4(reinterpret_cast<const typename type_at<I, L>::type *>(s + smem_offset<L, I, TILE>::value), vi,
+                comp<I>(r)),
      ...);
 }
 
@@ -600,15 +663,15 @@ __device__ __forceinline__ void scan_body(const accb_kparams &p) {
 #define ACCB_SCAN_ENTRY(Fn, name, right, incl)                                                 \
     extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA, ACCB_SCAN_MINB_FOR(Fn))        \
         name(const __grid_constant__ accb_kparams p) {                                         \
-        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS, right, incl, ACCB_SCAN_TMA != 0>(p); \
+        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS_FOR(Fn), right, incl, ACCB_SCAN_TMA != 0>(p); \
     }
 
 /* metadata: record bytes, tile elements, rows, ticket mode, dynamic shared memory */
 #define ACCB_INSTANTIATE_SCAN(Fn)                                                              \
     ACCB_META7(5, ACCB_SCAN_CTA, accb::TileStatus<Fn::elem>::kBytes,                           \
-               ACCB_SCAN_CTA * ACCB_SCAN_ROWS * 4, ACCB_SCAN_ROWS, ACCB_SCAN_TICKET ? 2 : 0,   \
+               ACCB_SCAN_CTA * ACCB_SCAN_ROWS_FOR(Fn) * 4, ACCB_SCAN_ROWS_FOR(Fn), ACCB_SCAN_TICKET ? 2 : 0,   \
                ACCB_SCAN_TMA ? (accb::smem_offset<Fn::In, Fn::In::size,                        \
-                                                  ACCB_SCAN_CTA * ACCB_SCAN_ROWS * 4>::value)  \
+                                                  ACCB_SCAN_CTA * ACCB_SCAN_ROWS_FOR(Fn) * 4>::value)  \
                              : 0)                                                              \
     ACCB_SCAN_ENTRY(Fn, scanl, false, false)                                                   \
     ACCB_SCAN_ENTRY(Fn, scanl1, false, true)                                                   \

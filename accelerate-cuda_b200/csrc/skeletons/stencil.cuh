@@ -45,8 +45,15 @@
 #ifndef ACCB_STENCIL_TILE_RPT
 #define ACCB_STENCIL_TILE_RPT 8 /* tile form: output rows per thread */
 #endif
-#ifndef ACCB_STENCIL_TILE_MINB
-#define ACCB_STENCIL_TILE_MINB 6 /* tile form: resident blocks per SM to leave registers for */
+/* tile form: resident blocks per SM to leave registers for.  The register window of a thread is
+ * arrays x (2RY+1) x (4+2RX) values: six blocks (40 registers) hold a 3x3 window, larger windows
+ * get four (64) or three (80) so that they do not spill. */
+#ifdef ACCB_STENCIL_TILE_MINB
+#define ACCB_STENCIL_TILE_MINB_FOR(Fn, narr) ACCB_STENCIL_TILE_MINB
+#else
+#define ACCB_STENCIL_TILE_MINB_FOR(Fn, narr)                                   \
+    ((narr) * (2 * Fn::RY + 1) * (4 + 2 * Fn::RX) <= 20 ? 6                    \
+                                                        : ((narr) * (2 * Fn::RY + 1) * (4 + 2 * Fn::RX) <= 40 ? 4 : 3))
 #endif
 #ifndef ACCB_STENCIL_TMA_SPIN_LIMIT
 #define ACCB_STENCIL_TMA_SPIN_LIMIT (1 << 16)
@@ -514,6 +521,149 @@ __device__ __forceinline__ void stencil_tile_body(const accb_kparams &p) {
     }
 }
 
+/* ----------------------------------------------------------------------
+ * Line form: rank-1 arrays.  A block's tile is a run of CTA * 4 * RPT
+ * elements plus 4 halo elements each side, brought into shared memory by ONE
+ * bulk copy per source; a warp then walks RPT rows of 128 consecutive
+ * elements (lane l takes 4 of them), as in the scan.  Same conditions as the
+ * tile form: 4-byte elements, aligned arrays, lengths that are multiples of 4.
+ * ---------------------------------------------------------------------- */
+#ifndef ACCB_STENCIL_LINE_RPT
+#define ACCB_STENCIL_LINE_RPT 8
+#endif
+template <int CTA>
+struct StencilLine {
+    static constexpr int HX = 4;
+    static constexpr int L = CTA * V * ACCB_STENCIL_LINE_RPT; /* outputs per tile */
+    static constexpr int PW = L + 2 * HX;
+};
+
+template <class Fn, int NARR, int CTA>
+__device__ __forceinline__ void stencil_line_body(const accb_kparams &p) {
+    typedef typename Fn::in_t Tin;
+    typedef typename Fn::out_t Tout;
+    typedef StencilLine<CTA> G;
+    static_assert(Fn::RY == 0 && Fn::RX <= G::HX, "line form: rank-1 stencil of radius at most 4");
+    constexpr int RX = Fn::RX, RW = V + 2 * RX, RPT = ACCB_STENCIL_LINE_RPT;
+    extern __shared__ __align__(128) unsigned char s_raw[];
+    __shared__ __align__(8) unsigned long long s_bar;
+    Tin(*tile)[G::PW] = reinterpret_cast<Tin(*)[G::PW]>(s_raw);
+
+    const Env env(p);
+    const int W = (int)p.ip[1], mode = (int)p.ip[4];
+    Source<Tin> src[NARR];
+#pragma unroll
+    for (int a = 0; a < NARR; ++a) {
+        src[a].base = static_cast<const Tin *>(p.in[a]);
+        src[a].h = 1;
+        src[a].w = (int)p.ip[6 + 2 * a];
+        src[a].mode = mode;
+        src[a].cval = env.scalar<Tin>(0);
+        src[a].vec_ok = true;
+    }
+    Tout *out = static_cast<Tout *>(p.out[0]);
+    unsigned int *err = static_cast<unsigned int *>(p.aux[1]);
+    const long long x0t = (long long)blockIdx.x * G::L;
+    auto col_range = [&](int a, long long &xs, long long &xe) {
+        xs = max(0LL, x0t - G::HX);
+        xe = min((long long)src[a].w, x0t + G::L + G::HX);
+    };
+
+    if (threadIdx.x == 0) {
+        mbar_init(&s_bar, 1);
+        fence_mbar_init();
+        unsigned total = 0;
+#pragma unroll
+        for (int a = 0; a < NARR; ++a) {
+            long long xs, xe;
+            col_range(a, xs, xe);
+            total += (unsigned)(xe - xs) * 4u;
+        }
+        mbar_expect_tx(&s_bar, total);
+#pragma unroll
+        for (int a = 0; a < NARR; ++a) {
+            long long xs, xe;
+            col_range(a, xs, xe);
+            bulk_g2s(&tile[a][xs - (x0t - G::HX)], src[a].base + xs, (unsigned)(xe - xs) * 4u, &s_bar);
+        }
+    }
+    __syncthreads(); /* the barrier is initialised before anybody polls it */
+    int tries = 0;
+    while (!mbar_try_wait(&s_bar, 0)) {
+        if (++tries > ACCB_STENCIL_TMA_SPIN_LIMIT) { /* bounded: flag the result invalid and go on */
+            atomicExch(err, 1u);
+            break;
+        }
+    }
+    /* halo elements outside the array: at most RX each side, first / last tile only */
+    if (threadIdx.x < 2 * RX) {
+#pragma unroll
+        for (int a = 0; a < NARR; ++a) {
+            long long xs, xe;
+            col_range(a, xs, xe);
+            const long long hi = min(x0t + G::L, (long long)W);
+            const long long c = threadIdx.x < RX ? x0t - RX + threadIdx.x : hi + (threadIdx.x - RX);
+            if (c < xs || c >= xe) tile[a][c - (x0t - G::HX)] = src[a].at(0, (int)c);
+        }
+    }
+    __syncthreads();
+
+    const int base = warp_id() * (RPT * 32 * V) + lane_id() * V;
+#pragma unroll
+    for (int j = 0; j < RPT; ++j) {
+        const int e = base + j * 32 * V;
+        const long long x = x0t + e;
+        if (x >= W) break;
+        Tout o[V];
+        Tin d[NARR][RW];
+#pragma unroll
+        for (int a = 0; a < NARR; ++a) {
+            const Tin *q = &tile[a][G::HX + e];
+            Tin c[V];
+            load4<Cache::Default>(q, 0, c);
+#pragma unroll
+            for (int k = 0; k < V; ++k) d[a][RX + k] = c[k];
+#pragma unroll
+            for (int k = 0; k < RX; ++k) {
+                d[a][k] = q[k - RX];
+                d[a][RX + V + k] = q[V + k];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            Tin t[NARR][1][2 * RX + 1];
+#pragma unroll
+            for (int a = 0; a < NARR; ++a)
+#pragma unroll
+                for (int dx = 0; dx < 2 * RX + 1; ++dx) t[a][0][dx] = d[a][k + dx];
+            if constexpr (NARR == 1)
+                o[k] = Fn::apply(env, t[0]);
+            else
+                o[k] = Fn::apply(env, t[0], t[1]);
+        }
+        if (x + V <= W) {
+            store4<Cache::Stream>(out + x, 0, o);
+        } else {
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                if (x + k < W) out[x + k] = o[k];
+        }
+    }
+}
+
+template <class Fn, int NARR, int CTA>
+__device__ __forceinline__ void stencil_line_or_nothing(const accb_kparams &p) {
+    if constexpr (sizeof(typename Fn::in_t) == 4 && sizeof(typename Fn::out_t) == 4 && Fn::RY == 0 && Fn::RX <= 4)
+        stencil_line_body<Fn, NARR, CTA>(p);
+}
+/* outputs per tile of the line form; 0 when it does not apply */
+template <class Fn, int CTA>
+__host__ __device__ constexpr int stencil_line_len() {
+    return (sizeof(typename Fn::in_t) == 4 && sizeof(typename Fn::out_t) == 4 && Fn::RY == 0 && Fn::RX <= 4)
+               ? StencilLine<CTA>::L
+               : 0;
+}
+
 /* element types the tile form does not take still need a body to instantiate */
 template <class Fn, int NARR, int CTA>
 __device__ __forceinline__ void stencil_tile_or_nothing(const accb_kparams &p) {
@@ -535,21 +685,28 @@ __host__ __device__ constexpr int stencil_tile_dim(int which) {
 
 /* Entry points: `stencil` / `stencil2` as in the reference (Stencil.hs:67,158)
  * are the register form, which takes any shape and element type; the host
- * launches `stencil_tile` / `stencil2_tile` instead when their conditions hold.
- * Metadata: {.., element bytes, rows per tile, columns per tile, 0, dynamic shared memory}. */
-#define ACCB_STENCIL_ENTRIES(Fn, id, narr, name, tname)                                        \
+ * launches `stencil_tile` / `stencil2_tile` (rank 2) or `stencil_line` /
+ * `stencil2_line` (rank 1) instead when their conditions hold.
+ * Metadata: {.., element bytes, rows per tile, columns per tile, outputs per
+ * tile of the line form, dynamic shared memory of the tile form}. */
+#define ACCB_STENCIL_ENTRIES(Fn, id, narr, name, tname, lname)                                 \
     ACCB_META7(id, ACCB_STENCIL_CTA, sizeof(Fn::in_t),                                         \
                (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(1)),                        \
-               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(2)), 0,                     \
+               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(2)),                        \
+               (accb::stencil_line_len<Fn, ACCB_STENCIL_CTA>()),                               \
                (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(0)))                        \
     extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_MINB)          \
         name(const __grid_constant__ accb_kparams p) {                                         \
         accb::stencil_body<Fn, narr, ACCB_STENCIL_CTA>(p);                                     \
     }                                                                                          \
-    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_TILE_MINB)     \
+    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_TILE_MINB_FOR(Fn, narr)) \
         tname(const __grid_constant__ accb_kparams p) {                                        \
         accb::stencil_tile_or_nothing<Fn, narr, ACCB_STENCIL_CTA>(p);                          \
+    }                                                                                          \
+    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, 6)                          \
+        lname(const __grid_constant__ accb_kparams p) {                                        \
+        accb::stencil_line_or_nothing<Fn, narr, ACCB_STENCIL_CTA>(p);                          \
     }
 
-#define ACCB_INSTANTIATE_STENCIL(Fn) ACCB_STENCIL_ENTRIES(Fn, 8, 1, stencil, stencil_tile)
-#define ACCB_INSTANTIATE_STENCIL2(Fn) ACCB_STENCIL_ENTRIES(Fn, 9, 2, stencil2, stencil2_tile)
+#define ACCB_INSTANTIATE_STENCIL(Fn) ACCB_STENCIL_ENTRIES(Fn, 8, 1, stencil, stencil_tile, stencil_line)
+#define ACCB_INSTANTIATE_STENCIL2(Fn) ACCB_STENCIL_ENTRIES(Fn, 9, 2, stencil2, stencil2_tile, stencil2_line)

@@ -172,7 +172,11 @@ def test_fold_all_tuple_argmax(ctx, P, torch_cuda, rng):
 
 
 @pytest.mark.parametrize("rows,cols", [(1, 1), (7, 3), (5, 31), (100, 32), (33, 100), (64, 1000), (9, 2048),
-                                       (17, 4099), (3, 16384), (300, 516)])
+                                       (17, 4099), (3, 16384), (300, 516),
+                                       # many short rows: groups of 4 / 8 / 16 / 32 lanes per row
+                                       (20000, 8), (20001, 20), (9000, 48), (9000, 200), (10000, 516), (8200, 2052),
+                                       # few long rows: every row cut into pieces across the SMs
+                                       (3, 200000), (2, 70001), (5, 1 << 20), (40, 140000)])
 def test_fold_rows(ctx, P, torch_cuda, oracle, rng, rows, cols):
     t = torch_cuda
     m = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
@@ -199,11 +203,12 @@ def test_fold_rows_empty_inner_dimension_yields_seed(ctx, P, accb, torch_cuda):
     assert e.value.status == accb.EBOUNDS
 
 
-def test_fold1_rows_min(ctx, P, torch_cuda, rng):
+@pytest.mark.parametrize("rows,cols", [(50, 777), (30000, 12), (3, 300000)])
+def test_fold1_rows_min(ctx, P, torch_cuda, rng, rows, cols):
     t = torch_cuda
-    m = rng.integers(-10**6, 10**6, (50, 777)).astype(np.int32)
-    out = t.zeros(50, dtype=t.int32, device="cuda")
-    ctx.fold_dim(P.ROWMIN_I32, [dev(t, m)], 50, 777, out)
+    m = rng.integers(-10**6, 10**6, (rows, cols)).astype(np.int32)
+    out = t.zeros(rows, dtype=t.int32, device="cuda")
+    ctx.fold_dim(P.ROWMIN_I32, [dev(t, m)], rows, cols, out)
     ctx.sync()
     assert np.array_equal(out.cpu().numpy(), m.min(axis=1))
 
@@ -223,6 +228,19 @@ def test_fold_seg(ctx, P, torch_cuda, oracle, rng):
     ctx.fold_seg(P.SEGSUM_F32, [dev(t, xf)], 1, x.size, dev(t, offs), lens.size, of, seed=np.float32(0))
     ctx.sync()
     close(of.cpu().numpy(), oracle.fold_seg_f32(xf, offs), 1e-7)
+
+
+@pytest.mark.parametrize("nseg,mean", [(60000, 3), (30000, 12), (9000, 40), (9000, 100), (300, 3000), (12, 20000)])
+def test_fold_seg_by_segment_length(ctx, P, torch_cuda, oracle, rng, nseg, mean):
+    """4, 8, 16 and 32 lanes or a whole block per segment, chosen by the average segment length."""
+    t = torch_cuda
+    lens = rng.integers(0, 2 * mean + 1, nseg)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    x = rng.integers(-1000, 1000, int(offs[-1])).astype(np.int32)
+    out = t.zeros(nseg, dtype=t.int32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_I32, [dev(t, x)], 1, x.size, dev(t, offs), nseg, out, seed=np.int32(-9))
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), oracle.fold_seg_i32(x, offs, -9))
 
 
 def test_fold_seg_rank2(ctx, P, torch_cuda, rng):
@@ -472,12 +490,13 @@ def test_stencil_radius2_and_laplace(ctx, P, torch_cuda, oracle, rng, boundary):
     close(out.cpu().numpy(), oracle.stencil2d(a, lap, boundary, 0.0), 2e-6)
 
 
-@pytest.mark.parametrize("n", [1, 2, 5, 129, 10007])
-@pytest.mark.parametrize("boundary", ["clamp", "wrap", "constant"])
+@pytest.mark.parametrize("n", [1, 2, 5, 129, 10007,
+                               4096, 8192, 8196, 100000, 1 << 20])  # multiples of 4 from 4096 up: the staged line form
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
 def test_stencil_rank1(ctx, P, torch_cuda, oracle, rng, n, boundary):
     t = torch_cuda
-    if boundary == "wrap" and n < 2:
-        pytest.skip("wrap needs an array at least as large as the stencil radius")
+    if boundary in ("wrap", "mirror") and n < 2:
+        pytest.skip("wrap and mirror need an array larger than the stencil radius")
     a = rng.uniform(0, 1, n).astype(np.float32)
     out = t.zeros(n, dtype=t.float32, device="cuda")
     ctx.stencil(P.SMOOTH1D, dev(t, a), out, boundary=boundary, constant=np.float32(1.0))
