@@ -42,6 +42,19 @@ struct type_at<0, types<T, Ts...>> {
     typedef T type;
 };
 
+/* byte offset of component I when TILE elements of every component of a type list are staged in
+ * shared memory one after the other, each component starting on a 128-byte boundary;
+ * smem_offset<L, L::size, TILE> is the total */
+template <class L, int I, int TILE>
+struct smem_offset {
+    static constexpr int value = smem_offset<L, I - 1, TILE>::value +
+                                 ((TILE * (int)sizeof(typename type_at<I - 1, L>::type) + 127) / 128) * 128;
+};
+template <class L, int TILE>
+struct smem_offset<L, 0, TILE> {
+    static constexpr int value = 0;
+};
+
 /* registers for V consecutive elements of every component in a type list */
 template <int V, class L>
 struct regs;

@@ -21,6 +21,7 @@
 #include <map>
 #include <memory>
 #include <mutex>
+#include <set>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -135,6 +136,7 @@ struct accb_context {
     void *l2_flush = nullptr;
     size_t l2_flush_bytes = 0;
     unsigned long long launches = 0;
+    std::set<CUfunction> carveout_set; /* entries already told to prefer shared memory over L1 */
     size_t mem_hits = 0, disk_hits = 0, compiles = 0;
     bool trace_exec = false, trace_gc = false, trace_cc = false;
 };
@@ -170,7 +172,7 @@ bool trace_enabled(const char *family);
 int get_function(accb_context *ctx, accb_kernel *k, const char *entry, CUfunction *fn, KernelMeta *meta);
 int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blocks_per_sm);
 int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, size_t smem,
-           cudaStream_t stream, const accb_kparams &p);
+           cudaStream_t stream, const accb_kparams &p, bool prefer_smem = true);
 
 /* host fault injection: ACCB_FAIL=<site>[:N] makes the N-th call at <site>
  * fail (sites: malloc, nvcc, cache_io) */

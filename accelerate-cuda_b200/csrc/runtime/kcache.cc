@@ -346,8 +346,6 @@ int get_function(accb_context *ctx, accb_kernel *k, const char *entry, CUfunctio
             return fail(ctx, ACCB_ENOTFOUND, "kernel %s has no entry point '%s'", k->key.c_str(), entry);
         /* allow the full 227 KB of dynamic shared memory */
         d.FuncSetAttribute(f, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, 227 * 1024 - 1024);
-        /* kernels that ask for dynamic shared memory want it at the expense of L1 */
-        if (m.meta.v[6] > 0) d.FuncSetAttribute(f, CU_FUNC_ATTRIBUTE_PREFERRED_SHARED_MEMORY_CARVEOUT, 100);
         it = m.fn.emplace(entry, f).first;
     }
     *fn = it->second;

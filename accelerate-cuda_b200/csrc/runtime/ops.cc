@@ -32,10 +32,14 @@ int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blo
 }
 
 int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, size_t smem, cudaStream_t stream,
-           const accb_kparams &p) {
+           const accb_kparams &p, bool prefer_smem) {
     void *args[] = {const_cast<accb_kparams *>(&p)};
     if (ctx->trace_exec)
         fprintf(stderr, "[accb exec] %s<<<%d,%d,%zu>>> n=%lld\n", name, grid, block, smem, p.n);
+    /* an entry that stages tiles in dynamic shared memory wants several of them per SM at the
+     * expense of L1; the other entries of the same module keep the default split */
+    if (smem > 0 && prefer_smem && ctx->carveout_set.insert(fn).second)
+        driver().FuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_PREFERRED_SHARED_MEMORY_CARVEOUT, 100);
     int st = check_cu(ctx, driver().LaunchKernel(fn, (unsigned)grid, 1, 1, (unsigned)block, 1, 1, (unsigned)smem,
                                                  (CUstream)stream, args, nullptr),
                       name);
@@ -143,6 +147,12 @@ static int pick_group(long long items, long long units, long long block_from) {
     int g = 4;
     while (g < 32 && (long long)g * 8 < items) g *= 2;
     return g;
+}
+
+/* longest row (fold) / average segment (foldSeg) the staged thread-per-unit form is used for */
+static long long stage_len_max(const char *env_name, long long dflt) {
+    if (const char *e = getenv(env_name)) return atoll(e);
+    return dflt;
 }
 
 }  // namespace accb_rt
@@ -256,6 +266,24 @@ int accb_fold_dim(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     const char *entry = group > 32 ? "fold" : group == 32 ? "fold_warp" : group == 16 ? "fold_g16" : group == 8 ? "fold_g8" : "fold_g4";
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
+    if (cols >= 1 && cols <= stage_len_max("ACCB_FOLD_STAGE_MAX", 128) && rows * cols >= (1 << 16) && rows * cols < (1LL << 40) && pr.meta.v[6] > 0 &&
+        (p.flags & ACCB_F_VEC) && !getenv("ACCB_FOLD_NO_STAGE")) {
+        /* many short rows: a block stages a run of whole rows (the matrix read as one long
+         * vector) in shared memory and every thread reduces whole rows */
+        const size_t smem = (size_t)pr.meta.v[6];
+        Prep ps;
+        TRY(get_function(ctx, k, "fold_staged", &ps.fn, &ps.meta)); /* its block size is meta.v[5] */
+        StreamScratch *sc = scratch_for(ctx, (cudaStream_t)stream);
+        if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+        const long long run = std::max(1LL, (ps.meta.v[3] - 16) / cols); /* rows per block */
+        p.ip[0] = 1;
+        p.ip[1] = rows * cols;
+        p.ip[2] = rows;
+        p.ip[3] = cols;
+        p.ip[4] = run;
+        p.aux[1] = sc->words + 2;
+        return launch(ctx, ps.fn, "fold_staged", (int)ceil_div(rows, run), ps.meta.v[5], smem, (cudaStream_t)stream, p);
+    }
     const long long resident = (long long)ctx->sm_count * pr.per_sm;
     const long long quantum = (long long)pr.block * pr.meta.v[4] * 4; /* elements a block takes per trip */
     if (group > 32 && rows <= kRowCounters && rows < 4 * resident && cols >= 8 * quantum) {
@@ -301,10 +329,28 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     p.aux[0] = const_cast<int *>(offsets);
     /* the reference gives every segment one warp (Launch.hs:118); here the group follows the
      * average segment length (accesses are scalar, so a lane should get about 8 elements) */
-    const int group = pick_group(cols / std::max(1LL, nseg), rows * nseg, 8192);
+    const long long avg = cols / std::max(1LL, nseg);
+    const int group = pick_group(avg, rows * nseg, 8192);
     const char *entry = group > 32 ? "foldSeg_block" : group == 32 ? "foldSeg" : group == 16 ? "foldSeg_g16" : group == 8 ? "foldSeg_g8" : "foldSeg_g4";
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
+    if (avg <= stage_len_max("ACCB_FOLDSEG_STAGE_MAX", 64) && rows * nseg >= 4096 && (rows == 1 || cols % 16 == 0) && pr.meta.v[6] > 0 &&
+        (p.flags & ACCB_F_VEC)) {
+        /* short segments: a block stages a run of consecutive segments in shared memory and every
+         * thread reduces whole segments; the run is sized to fill 3/4 of the window on average */
+        const size_t smem = (size_t)pr.meta.v[6];
+        Prep ps;
+        TRY(get_function(ctx, k, "foldSeg_staged", &ps.fn, &ps.meta)); /* its block size is meta.v[5] */
+        StreamScratch *sc = scratch_for(ctx, (cudaStream_t)stream);
+        if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+        const long long run =
+            std::min<long long>(std::max(32LL, (ps.meta.v[3] - 32) * 3 / 4 / std::max(1LL, avg)), 16LL * ps.meta.v[5]);
+        p.ip[4] = run;
+        p.aux[1] = sc->words + 2;
+        const long long blocks = rows * ceil_div(nseg, run);
+        if (blocks > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one foldSeg launch");
+        return launch(ctx, ps.fn, "foldSeg_staged", (int)blocks, ps.meta.v[5], smem, (cudaStream_t)stream, p);
+    }
     const long long units = ceil_div(rows * nseg, pr.block / std::min(group, pr.block));
     const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * pr.per_sm);
     return launch(ctx, pr.fn, entry, grid, pr.block, 0, (cudaStream_t)stream, p);
@@ -444,7 +490,8 @@ int accb_permute(accb_context *ctx, accb_kernel *k, accb_stream stream, const ac
         p.ip[1] = R;
         const long long units = ceil_div(n_src, (long long)ps.block * ps.meta.v[4] * 4);
         const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * ps.per_sm);
-        return launch(ctx, ps.fn, "permute_smem", grid, ps.block, smem, s, p);
+        /* the replicas take what they need; the driver's own split measured faster than the maximum */
+        return launch(ctx, ps.fn, "permute_smem", grid, ps.block, smem, s, p, false);
     }
     if (needs_lock) {
         /* one lock word per destination element, cleared for every launch (Execute.hs:402-405) */

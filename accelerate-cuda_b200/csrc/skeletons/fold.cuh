@@ -31,6 +31,7 @@
 #pragma once
 #include "../cubits/accb_vec.cuh"
 #include "../cubits/accb_warp.cuh"
+#include "../cubits/accb_tma.cuh"
 
 namespace accb {
 
@@ -370,6 +371,8 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
 
 }  // namespace accb
 
+#include "fold_staged.cuh" /* short rows and segments */
+
 #define ACCB_FOLD_CTA 256
 #define ACCB_FOLD_U 4
 
@@ -388,9 +391,20 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
         accb::fold_dim_body<Fn, ACCB_FOLD_CTA, group, u, kr>(p);                        \
     }
 
-/* one entry per group size; the host picks by row length */
+#define ACCB_FOLD_STAGED_ENTRY(Fn, name, seg)                                           \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_STAGE_CTA, 12)               \
+        name(const __grid_constant__ accb_kparams p) {                                  \
+        accb::fold_staged_or_nothing<Fn, seg>(p);                                       \
+    }
+
+/* One entry per group size; the host picks by row length.
+ * Metadata: {.., bytes of a partial, elements per window of the staged form, U, block size of the
+ * staged form, its shared memory} */
 #define ACCB_INSTANTIATE_FOLD_DIM(Fn)                                                   \
-    ACCB_META(3, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, ACCB_FOLD_U, 0)           \
+    ACCB_META7(3, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>),                            \
+               accb::fold_stage_window<Fn::In>::value, ACCB_FOLD_U, ACCB_FOLD_STAGE_CTA, \
+               (accb::fold_stage_smem<Fn>()))                                           \
+    ACCB_FOLD_STAGED_ENTRY(Fn, fold_staged, false)                                      \
     ACCB_FOLD_DIM_ENTRY(Fn, fold, ACCB_FOLD_CTA, ACCB_FOLD_U, 1)                        \
     ACCB_FOLD_DIM_ENTRY(Fn, fold_warp, 32, 4, 1)                                        \
     ACCB_FOLD_DIM_ENTRY(Fn, fold_g16, 16, 4, 1)                                         \
@@ -410,7 +424,10 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
 /* `foldSeg` is the reference's warp-per-segment form (Reduction.hs:430); the
  * others serve shorter and longer segments */
 #define ACCB_INSTANTIATE_FOLD_SEG(Fn)                                                   \
-    ACCB_META(4, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, 1, 0)                     \
+    ACCB_META7(4, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>),                            \
+               accb::fold_stage_window<Fn::In>::value, 1, ACCB_FOLD_STAGE_CTA,          \
+               (accb::fold_stage_smem<Fn>()))                                           \
+    ACCB_FOLD_STAGED_ENTRY(Fn, foldSeg_staged, true)                                    \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg, 32, 1)                                             \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g16, 16, 2)                                         \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g8, 8, 2)                                           \

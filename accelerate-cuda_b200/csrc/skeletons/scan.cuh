@@ -98,7 +98,7 @@
 #ifdef ACCB_SCAN_MINB
 #define ACCB_SCAN_MINB_FOR(Fn) ACCB_SCAN_MINB
 #elif ACCB_SCAN_TMA
-#define ACCB_SCAN_MINB_FOR(Fn) (sizeof(Fn::elem) <= 4 ? 6 : (sizeof(Fn::elem) <= 8 ? 5 : 3))
+#define ACCB_SCAN_MINB_FOR(Fn) (sizeof(Fn::elem) <= 8 ? 6 : 3)
 #else
 #define ACCB_SCAN_MINB_FOR(Fn) (sizeof(Fn::elem) <= 4 ? 12 : (sizeof(Fn::elem) <= 8 ? 6 : 3))
 #endif
@@ -355,16 +355,6 @@ __device__ __forceinline__ void scan_block_level(const typename Fn::elem *s_warp
 /* ---- full, aligned tile.  SMEM: the raw inputs sit in shared memory (put
  * there by the TMA engine) and are read twice; otherwise they are loaded into
  * registers once and kept there. ---- */
-template <class L, int I, int TILE>
-struct smem_offset {
-    static constexpr int value = smem_offset<L, I - 1, TILE>::value +
-                                 ((TILE * (int)sizeof(typename type_at<I - 1, L>::type) + 127) / 128) * 128;
-};
-template <class L, int TILE>
-struct smem_offset<L, 0, TILE> {
-    static constexpr int value = 0;
-};
-
 /* tile rows for a 32 KB tile: 8 for up to 4 bytes per element (all components), 4 up to 8, else 2 */
 template <class L>
 struct scan_rows_for {

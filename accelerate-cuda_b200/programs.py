@@ -133,8 +133,27 @@ struct SegSumF : accb::Fold<float, double> {{
 }};
 """)
 
+# sparse matrix x dense vector in CSR form: foldSeg (+) 0 (zipWith (*) vals (gather cols vec)) rowOffsets.
+# Environment: (vals, cols) zipped element-wise, then the dense vector as a free array variable.
+SMVM = KernelSpec("fold_seg", "Smvm", f"""
+struct Smvm : accb::Fold<float, double> {{
+    using In = accb::types<float, int>;
+    {_D} float get(const accb::Env &env, long long, float v, int c) {{ return v * env.in<float>(2)[c]; }}
+    {_D} double combine(double a, double b) {{ return a + b; }}
+}};
+""")
+
+# row-wise dot products of two matrices: fold (+) 0 (zipWith (*) a b)
+ROWDOT = KernelSpec("fold_dim", "RowDot", f"""
+struct RowDot : accb::Fold<float, double> {{
+    using In = accb::types<float, float>;
+    {_D} float get(const accb::Env &, long long, float x, float y) {{ return x * y; }}
+    {_D} double combine(double a, double b) {{ return a + b; }}
+}};
+""")
+
 # --------------------------------------------------------------------- scans
-SCAN_ADD_I32 = KernelSpec("scan", "AddI", f"""
+SCAN_ADD_I32 =KernelSpec("scan", "AddI", f"""
 struct AddI : accb::Scan<int> {{
     using In = accb::types<int>;
     {_D} int get(const accb::Env &, long long, int x) {{ return x; }}

@@ -175,6 +175,8 @@ def test_fold_all_tuple_argmax(ctx, P, torch_cuda, rng):
                                        (17, 4099), (3, 16384), (300, 516),
                                        # many short rows: groups of 4 / 8 / 16 / 32 lanes per row
                                        (20000, 8), (20001, 20), (9000, 48), (9000, 200), (10000, 516), (8200, 2052),
+                                       # ... of which rows up to 128 elements go thread-per-row out of shared memory
+                                       (70000, 1), (40001, 3), (5003, 100), (600, 128), (3000, 127),
                                        # few long rows: every row cut into pieces across the SMs
                                        (3, 200000), (2, 70001), (5, 1 << 20), (40, 140000)])
 def test_fold_rows(ctx, P, torch_cuda, oracle, rng, rows, cols):
@@ -241,6 +243,72 @@ def test_fold_seg_by_segment_length(ctx, P, torch_cuda, oracle, rng, nseg, mean)
     ctx.fold_seg(P.SEGSUM_I32, [dev(t, x)], 1, x.size, dev(t, offs), nseg, out, seed=np.int32(-9))
     ctx.sync()
     assert np.array_equal(out.cpu().numpy(), oracle.fold_seg_i32(x, offs, -9))
+
+
+def test_fold_seg_short_segments_with_outliers(ctx, P, torch_cuda, oracle, rng):
+    """The windowed form: mostly short segments, runs of empty ones, a few that span several windows,
+    a source length that is not a multiple of 4, and trailing empty segments."""
+    t = torch_cuda
+    lens = rng.integers(0, 9, 50000)
+    lens[1000:1400] = 0
+    lens[[5, 20000, 49990]] = [30000, 70, 9001]
+    lens[-3:] = 0
+    lens[7] += (-int(lens.sum())) % 4 + 1  # total = 1 (mod 4)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    x = rng.integers(-1000, 1000, int(offs[-1])).astype(np.int32)
+    out = t.full((lens.size,), 77, dtype=t.int32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_I32, [dev(t, x)], 1, x.size, dev(t, offs), lens.size, out, seed=np.int32(5))
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), oracle.fold_seg_i32(x, offs, 5))
+    xf = rng.uniform(-1, 1, x.size).astype(np.float32)
+    of = t.zeros(lens.size, dtype=t.float32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_F32, [dev(t, xf)], 1, x.size, dev(t, offs), lens.size, of, seed=np.float32(0))
+    ctx.sync()
+    ref = np.array([xf[offs[s]:offs[s + 1]].astype(np.float64).sum() for s in range(lens.size)])
+    close(of.cpu().numpy(), ref, 1e-5)
+
+
+@pytest.mark.parametrize("nrows,mean_nnz", [(300, 7), (40000, 5), (20000, 30), (3000, 400)])
+def test_fold_seg_sparse_matrix_vector_product(ctx, P, torch_cuda, rng, nrows, mean_nnz):
+    """CSR smvm: two zipped inputs of different types plus a gathered free array variable."""
+    t = torch_cuda
+    ncols = 5000
+    nnz = rng.integers(0, 2 * mean_nnz + 1, nrows)
+    offs = np.concatenate([[0], np.cumsum(nnz)]).astype(np.int32)
+    vals = rng.uniform(-1, 1, int(offs[-1])).astype(np.float32)
+    cols = rng.integers(0, ncols, int(offs[-1])).astype(np.int32)
+    vec = rng.uniform(-1, 1, ncols).astype(np.float32)
+    out = t.zeros(nrows, dtype=t.float32, device="cuda")
+    ctx.fold_seg(P.SMVM, [(dev(t, vals), dev(t, cols)), dev(t, vec)], 1, vals.size, dev(t, offs), nrows, out,
+                 seed=np.float32(0))
+    ctx.sync()
+    prod = np.concatenate([(vals * vec[cols]).astype(np.float64), [0.0]])  # products rounded to float32 as on the device
+    ref = np.add.reduceat(prod, offs[:-1]) * (nnz > 0)
+    close(out.cpu().numpy(), ref, 1e-6)
+
+
+@pytest.mark.parametrize("rows,cols", [(30000, 10), (900, 3000)])
+def test_fold_rows_of_two_zipped_inputs(ctx, P, torch_cuda, rng, rows, cols):
+    t = torch_cuda
+    a = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    b = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    out = t.zeros(rows, dtype=t.float32, device="cuda")
+    ctx.fold_dim(P.ROWDOT, [(dev(t, a), dev(t, b))], rows, cols, out, seed=np.float32(0))
+    ctx.sync()
+    close(out.cpu().numpy(), ((a * b).astype(np.float64)).sum(axis=1), 1e-6)
+
+
+def test_fold_seg_short_segments_rank2(ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    lens = rng.integers(0, 13, 3000)
+    lens[0] += (-int(lens.sum())) % 16  # row length a multiple of 16: the windowed form applies per row
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    m = rng.integers(-50, 50, (3, int(offs[-1]))).astype(np.int32)
+    out = t.zeros((3, lens.size), dtype=t.int32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_I32, [dev(t, m)], 3, m.shape[1], dev(t, offs), lens.size, out, seed=np.int32(0))
+    ctx.sync()
+    ref = np.stack([np.add.reduceat(np.concatenate([m[r], [0]]), offs[:-1])[:lens.size] * (lens > 0) for r in range(3)])
+    assert np.array_equal(out.cpu().numpy(), ref.astype(np.int32))
 
 
 def test_fold_seg_rank2(ctx, P, torch_cuda, rng):
