@@ -339,6 +339,71 @@ class RowSumWorkload(Workload):
         return bool(((self.out.double() - ref).abs() <= 1e-5 * ref.abs() + 1e-6).all())
 
 
+# ---- the reference's own algorithms on the same GPU and the same device inputs (baseline/refskel)
+def ref_algorithm(torch, wl, sm_count):
+    """Times the reference's algorithm for wl's program; returns {"GB/s", "ms", "check", "note"}.
+    Call after wl has run and verified: its result is what the baseline's result is checked against."""
+    R = importlib.import_module("baseline.refskel")
+    t = torch
+    scratch = R.scratch_elems(sm_count)
+    nbytes, note = wl.bytes, None
+    if isinstance(wl, ScanWorkload):
+        out2, blk = t.empty_like(wl.out), t.empty(scratch, dtype=t.int32, device="cuda")
+        fn = lambda: R.scanl(wl.x, 0, out2, blk)
+        check = lambda: bool(t.equal(out2, wl.out))
+        note = "3 launches: interval totals, scan of totals, second pass over the input"
+    elif isinstance(wl, DotWorkload):
+        out2, part = t.zeros(1, device="cuda"), t.empty(scratch, dtype=t.float32, device="cuda")
+        fn = lambda: R.dot(wl.x, wl.y, 0.0, part, out2)
+        check = lambda: abs(float(out2[0]) - float(wl.out[0])) <= 1e-6 * wl.n  # float32 accumulation, as the reference
+        note = "foldAll relaunched on the partials until one block is left; float32 accumulator"
+    elif isinstance(wl, HistWorkload):
+        # Every update of a hot bin is serialised by its lock while hundreds of thousands of threads
+        # spin on it (measured: ~0.2 ms per update of one shared bin), so a small bounded sample.
+        m = min(wl.n, 1 << 16)
+        keys = wl.keys[:m]
+        out2, lock = t.zeros_like(wl.out), t.zeros_like(wl.out)
+        err = t.zeros(1, dtype=t.int32, device="cuda")
+        fn = lambda: R.histogram(keys, wl.defaults, out2, lock, err)
+        check = lambda: bool(t.equal(out2, t.bincount(keys.long(), minlength=out2.numel()).int())) and int(err[0]) == 0
+        nbytes = wl.W.bytes_hist(m)
+        note = "spin lock per destination element; first 2^16 of the keys"
+    elif isinstance(wl, StencilWorkload):
+        a2, b2 = t.empty_like(wl.a), t.empty_like(wl.a)
+        def fn():
+            R.stencil_blur(wl.src, a2)
+            cur, nxt = a2, b2
+            for _ in range(wl.iters - 1):
+                R.stencil_blur(cur, nxt)
+                cur, nxt = nxt, cur
+            fn.res = cur
+        check = lambda: bool(((fn.res - wl.res).abs() <= 1e-5).all())
+        note = "one element per thread, nine global loads; one launch per application (the reference launches each twice)"
+    elif isinstance(wl, BlackScholesWorkload):
+        c2, p2 = t.empty_like(wl.call), t.empty_like(wl.put)
+        fn = lambda: R.map_blackscholes(wl.s, wl.k_, wl.y, c2, p2)
+        check = lambda: bool(((c2 - wl.call).abs() <= 1e-4).all()) and bool(((p2 - wl.put).abs() <= 1e-4).all())
+        note = "one element per thread per trip, scalar accesses; same functor and math flags"
+    elif isinstance(wl, RowSumWorkload):
+        out2 = t.empty_like(wl.out)
+        fn = lambda: R.fold_rows(wl.m, 0.0, out2)
+        check = lambda: bool(((out2 - wl.out).abs() <= 1e-2).all())  # float32 accumulation, as the reference
+        note = "one block per row, shared-memory tree"
+    else:
+        return None
+    fn()
+    t.cuda.synchronize()
+    e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+    steps = 3
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    t.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"GB/s": nbytes / (ms * 1e-3) / 1e9, "ms": ms, "check": check(), "note": note}
+
+
 WORKLOADS = {"scan": ScanWorkload, "dot": DotWorkload, "hist": HistWorkload, "stencil": StencilWorkload,
              "blackscholes": BlackScholesWorkload, "rowsum": RowSumWorkload}
 
@@ -501,10 +566,23 @@ def main():
         gbs, secs = cpu_scan_sample(1, 1 << 26, 3)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port",
                                 "sample": "sequential scanl (+) 0 over a 2^26-element Int32 slice, best of 3"}
+        # ---- the reference's own algorithm for the same program on this GPU (baseline/refskel), then
         # ---- the other skeletons, each on its configuration
+        def with_ref(entry, w):
+            try:
+                ra = ref_algorithm(torch, w, ctx.sm_count)
+            except (OSError, RuntimeError) as e:  # baseline library not built
+                ra = {"unavailable": str(e)}
+            if ra and "GB/s" in ra:
+                ra["speedup"] = entry["GB/s"] / ra["GB/s"]
+            entry["ref_algorithm"] = ra
+            return entry
+
+        table = {args.workload: with_ref({"GB/s": per_gpu, "frac_of_measured": per_gpu / peak, "ms": ms_step,
+                                          "parity_check": ok}, wl)}
+        line["ref_algorithm"] = table[args.workload]["ref_algorithm"]
         del wl
         torch.cuda.empty_cache()
-        table = {args.workload: {"GB/s": per_gpu, "frac_of_measured": per_gpu / peak, "ms": ms_step, "parity_check": ok}}
         for name, cls in WORKLOADS.items():
             if name == args.workload:
                 continue
@@ -512,8 +590,8 @@ def main():
             w2.setup(None)
             ms2, _ = time_steps(torch, w2, 10, 3)
             g = w2.bytes / (ms2 / 10 * 1e-3) / 1e9
-            table[name] = {"GB/s": g, "frac_of_measured": g / peak, "ms": ms2 / 10, "parity_check": bool(w2.verify()),
-                           "workload": w2.name}
+            table[name] = with_ref({"GB/s": g, "frac_of_measured": g / peak, "ms": ms2 / 10,
+                                    "parity_check": bool(w2.verify()), "workload": w2.name}, w2)
             del w2
             torch.cuda.empty_cache()
         line["skeletons"] = table
