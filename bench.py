@@ -339,6 +339,120 @@ class RowSumWorkload(Workload):
         return bool(((self.out.double() - ref).abs() <= 1e-5 * ref.abs() + 1e-6).all())
 
 
+# ---- secondary shapes and types of the same skeletons (not BASELINE configurations; --workload selects them
+# ---- for profiling, and the default run reports them in a table of their own)
+class Scan64Workload(Workload):
+    """Accelerate's Int is 64 bits wide: the default integer scan."""
+    name, dtype = "scanl (+) 0, Int64, 2^27", "int64"
+
+    def setup(self, n=None):
+        t = self.t
+        self.n = n or (1 << 27)
+        x32 = t.empty(self.n, dtype=t.int32, device="cuda")
+        self.ctx.gen_uniform_i32(x32, self.n, 0, self.W.SEED, self.W.S_SCAN, 16)
+        self.x = x32.long()
+        del x32
+        self.out = t.empty(self.n + 1, dtype=t.int64, device="cuda")
+        self.k = self.ctx.kernel(self.P.SCAN_ADD_I64).wait()
+        self.bytes = 16 * self.n + 8
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.scan(self.k, [self.x], self.n, self.out, seed=np.int64(0))
+        return 1
+
+    def verify(self):
+        return bool(self.t.equal(self.out[1:] - self.out[:-1], self.x)) and int(self.out[0]) == 0
+
+
+class ShortRowsWorkload(Workload):
+    name, dtype = "fold (+) 0 over rows, Float32 2^24 x 16", "f32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.rows, self.cols = n or (1 << 24), 16
+        self.m = t.empty((self.rows, self.cols), dtype=t.float32, device="cuda")
+        self.ctx.gen_uniform_f32(self.m, self.rows * self.cols, 0, W.SEED, W.S_MATRIX, -1.0, 1.0)
+        self.out = t.zeros(self.rows, dtype=t.float32, device="cuda")
+        self.k = self.ctx.kernel(self.P.ROWSUM).wait()
+        self.bytes = W.bytes_rowsum(self.rows, self.cols)
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.fold_dim(self.k, [self.m], self.rows, self.cols, self.out, seed=np.float32(0))
+        return 1
+
+    def verify(self):
+        ref = self.m.double().sum(dim=1)
+        return bool(((self.out.double() - ref).abs() <= 1e-5 * ref.abs() + 1e-6).all())
+
+
+class SmvmWorkload(Workload):
+    """Sparse matrix x dense vector, CSR: foldSeg (+) 0 (zipWith (*) vals (gather cols vec)) offsets; 2^24 rows of
+    0..16 non-zeros (mean 8), 2^20 columns."""
+    name, dtype = "smvm: foldSeg over 2^24 rows, mean 8 non-zeros, Float32", "f32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.rows, self.ncols = n or (1 << 24), 1 << 20
+        lens = t.empty(self.rows, dtype=t.int32, device="cuda")
+        self.ctx.gen_uniform_i32(lens, self.rows, 0, W.SEED, W.S_SCAN, 17)
+        self.offs = t.zeros(self.rows + 1, dtype=t.int32, device="cuda")
+        self.offs[1:] = t.cumsum(lens, 0)
+        self.nnz = int(self.offs[-1])
+        self.vals = t.empty(self.nnz, dtype=t.float32, device="cuda")
+        self.colidx = t.empty(self.nnz, dtype=t.int32, device="cuda")
+        self.vec = t.empty(self.ncols, dtype=t.float32, device="cuda")
+        self.ctx.gen_uniform_f32(self.vals, self.nnz, 0, W.SEED, W.S_XS, -1.0, 1.0)
+        self.ctx.gen_uniform_i32(self.colidx, self.nnz, 0, W.SEED, W.S_YS, self.ncols)
+        self.ctx.gen_uniform_f32(self.vec, self.ncols, 0, W.SEED, W.S_MATRIX, -1.0, 1.0)
+        self.out = t.zeros(self.rows, dtype=t.float32, device="cuda")
+        self.k = self.ctx.kernel(self.P.SMVM).wait()
+        # values + column indices + offsets in, one Float per row out; the gathered vector (4 MiB) lives in L2
+        self.bytes = 8 * self.nnz + 4 * (self.rows + 1) + 4 * self.rows
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.fold_seg(self.k, [(self.vals, self.colidx), self.vec], 1, self.nnz, self.offs, self.rows, self.out,
+                          seed=np.float32(0))
+        return 1
+
+    def verify(self):
+        t = self.t
+        prod = (self.vals * self.vec[self.colidx.long()]).double()
+        csum = t.cat([t.zeros(1, dtype=t.float64, device="cuda"), t.cumsum(prod, 0)])
+        ref = csum[self.offs[1:].long()] - csum[self.offs[:-1].long()]
+        return bool(((self.out.double() - ref).abs() <= 1e-5 * ref.abs() + 1e-4).all())
+
+
+class Smooth1dWorkload(Workload):
+    name, dtype = "stencil 3-tap smoothing Clamp, Float32 vector of 2^28", "f32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.n = n or W.N28
+        self.v = t.empty(self.n, dtype=t.float32, device="cuda")
+        self.ctx.gen_uniform_f32(self.v, self.n, 0, W.SEED, W.S_GRID, 0.0, 1.0)
+        self.out = t.empty_like(self.v)
+        self.k = self.ctx.kernel(self.P.SMOOTH1D).wait()
+        self.bytes = 8 * self.n
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.stencil(self.k, self.v, self.out, boundary="clamp")
+        return 1
+
+    def verify(self):
+        v, o = self.v, self.out
+        ref = 0.25 * v[:-2] + 0.5 * v[1:-1] + 0.25 * v[2:]
+        edge = abs(float(o[0]) - (0.75 * float(v[0]) + 0.25 * float(v[1]))) <= 1e-6
+        return bool(((o[1:-1] - ref).abs() <= 1e-6).all()) and edge
+
+
+SECONDARY_KERNEL = {"scan64": "scanl", "shortrows": "fold_staged", "smvm": "foldSeg_staged", "smooth1d": "stencil_line"}
+SECONDARY = {"scan64": Scan64Workload, "shortrows": ShortRowsWorkload, "smvm": SmvmWorkload, "smooth1d": Smooth1dWorkload}
+
+
 # ---- the reference's own algorithms on the same GPU and the same device inputs (baseline/refskel)
 def ref_algorithm(torch, wl, sm_count):
     """Times the reference's algorithm for wl's program; returns {"GB/s", "ms", "check", "note"}.
@@ -472,7 +586,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="scan", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="scan", choices=sorted(WORKLOADS) + sorted(SECONDARY))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--size", type=int, default=None, help="override the problem size (profiling small cases)")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-skeleton table, e2e and CPU baseline")
@@ -497,7 +611,9 @@ def main():
     ctx = accb.Context(local)
     peak, peak_kind = measured_peak()
 
-    wl = WORKLOADS[args.workload](accb, ctx, torch, rank, world)
+    if args.workload in SECONDARY and world > 1:
+        raise SystemExit("the secondary workloads run on one GPU")
+    wl = {**WORKLOADS, **SECONDARY}[args.workload](accb, ctx, torch, rank, world)
     wl.setup(args.size)
     if dist:
         dist.barrier()
@@ -532,11 +648,14 @@ def main():
     # dominant kernel = the skeleton's kernel; its launches in a step move the algorithmic bytes of the step.
     # traffic: DRAM bytes per launch from one ncu capture of the same kernel on a smaller case (profiles/),
     # scaled by the number of units a full launch processes (traffic grows in proportion to them).
-    kernel_name, traffic_per_unit = NCU_TRAFFIC[args.workload]
     dom = getattr(wl, 'iters', 1)  # launches of the dominant kernel per step (10 for the iterated stencil)
-    units_per_launch = wl.bytes / BYTES_PER_UNIT[args.workload] / dom
+    if args.workload in NCU_TRAFFIC:
+        kernel_name, traffic_per_unit = NCU_TRAFFIC[args.workload]
+        traffic = traffic_per_unit * wl.bytes / BYTES_PER_UNIT[args.workload] / dom
+    else:  # secondary workloads: no scaled ncu figure
+        kernel_name, traffic = SECONDARY_KERNEL[args.workload], None
     line["roofline"] = {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                        "traffic": traffic_per_unit * units_per_launch, "peak_kind": peak_kind, "kernel": kernel_name,
+                        "traffic": traffic, "peak_kind": peak_kind, "kernel": kernel_name,
                         "algorithmic_bytes_per_launch": wl.bytes / dom}
 
     if rank == 0 and world == 1 and not args.no_extras:
@@ -583,7 +702,7 @@ def main():
         line["ref_algorithm"] = table[args.workload]["ref_algorithm"]
         del wl
         torch.cuda.empty_cache()
-        for name, cls in WORKLOADS.items():
+        for name, cls in {**WORKLOADS, **SECONDARY}.items():
             if name == args.workload:
                 continue
             w2 = cls(accb, ctx, torch, 0, 1)
@@ -594,7 +713,8 @@ def main():
                                     "parity_check": bool(w2.verify()), "workload": w2.name}, w2)
             del w2
             torch.cuda.empty_cache()
-        line["skeletons"] = table
+        line["skeletons"] = {k: v for k, v in table.items() if k in WORKLOADS}    # the BASELINE configurations
+        line["secondary"] = {k: v for k, v in table.items() if k in SECONDARY}    # other shapes and types
     elif rank == 0:
         line["e2e"] = None
     ctx.sync()
