@@ -135,6 +135,9 @@ def lib() -> C.CDLL:
             "accb_program_scan": [vp, vp, C.POINTER(i32), i32, i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
             "accb_program_permute": [vp, vp, C.POINTER(i32), i32, i32, i32, C.POINTER(accb_value_type)],
             "accb_program_stencil": [vp, vp, i32, i32, vp, sz, i32, C.POINTER(accb_value_type)],
+            "accb_program_generate": [vp, vp, C.POINTER(i32), i32, i32, C.POINTER(i32), C.POINTER(accb_value_type), vp, sz],
+            "accb_program_fold_seg": [vp, vp, C.POINTER(i32), i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
+            "accb_program_stencil2": [vp, vp, i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
             "accb_program_outputs": [vp, C.POINTER(i32), i32],
             "accb_program_run": [vp, vp, arrp, arrp],
             "accb_program_run_host": [vp, arrp, arrp],
@@ -526,11 +529,12 @@ def fold(spec: KernelSpec, env: Sequence[Acc], out_dtypes, seed=None, all=False,
     return r
 
 
-def scan(spec: KernelSpec, env: Sequence[Acc], out_dtypes, direction=SCAN_LEFT, kind=SCAN_EXCLUSIVE, seed=None):
+def scan(spec: KernelSpec, env: Sequence[Acc], out_dtypes, direction=SCAN_LEFT, kind=SCAN_EXCLUSIVE, seed=None,
+         shape_like: Acc = None):
     """scanl / scanl1 / scanl' / scanr / scanr1 / scanr' node (Execute.hs:205-210,328-392).
     Returns the result array, or (body, total) for the primed forms."""
     p = _prog(*env)
-    like = env[0]
+    like = shape_like or env[0]
     out_type = ArrayType(1, out_dtypes)
     ids, n = p._ids(env)
     sb, sn = _seed_bytes(seed, out_type)
@@ -546,12 +550,12 @@ def scan(spec: KernelSpec, env: Sequence[Acc], out_dtypes, direction=SCAN_LEFT, 
     return r
 
 
-def permute(spec: KernelSpec, env: Sequence[Acc], defaults: Acc) -> Acc:
+def permute(spec: KernelSpec, env: Sequence[Acc], defaults: Acc, shape_like: Acc = None) -> Acc:
     """permute node: defaults copied first, then the scatter-combine (Execute.hs:211,396-408)."""
     p = _prog(*env)
     ids, n = p._ids(env)
     t = defaults.type.ctype()
-    vid = lib().accb_program_permute(p.handle, p.ctx._k(spec), ids, n, env[0].id, defaults.id, C.byref(t))
+    vid = lib().accb_program_permute(p.handle, p.ctx._k(spec), ids, n, (shape_like or env[0]).id, defaults.id, C.byref(t))
     r = p._new(vid, defaults.type)
     r.shape_fn = defaults.shape_fn
     return r
@@ -566,6 +570,45 @@ def stencil(spec: KernelSpec, src: Acc, out_dtype=None, boundary="clamp", consta
     vid = lib().accb_program_stencil(p.handle, p.ctx._k(spec), src.id, BOUNDARY[boundary], cb, cn, iters, C.byref(t))
     r = p._new(vid, out_type)
     r.shape_fn = src.shape_fn
+    return r
+
+
+def generate(prog: Afun, spec: KernelSpec, env: Sequence[Acc], shape, out_type: ArrayType, scalars=None) -> Acc:
+    """generate node with a literal shape (outermost extent first, as numpy writes shapes)."""
+    shape = tuple(int(e) for e in shape)
+    ids, n = prog._ids(env)
+    sb, sn = _bytes_of(scalars)
+    t = out_type.ctype()
+    inner_first = (C.c_int * max(1, len(shape)))(*reversed(shape))
+    vid = lib().accb_program_generate(prog.handle, prog.ctx._k(spec), ids, n, len(shape), inner_first, C.byref(t), sb, sn)
+    r = prog._new(vid, out_type)
+    r.shape_fn = lambda s: shape
+    return r
+
+
+def fold_seg(spec: KernelSpec, env: Sequence[Acc], offsets: Acc, out_dtypes, seed=None, shape_like: Acc = None) -> Acc:
+    """foldSeg / fold1Seg node; ``offsets`` is the Int32 vector of segments + 1 offsets (Execute.hs:320-324)."""
+    p = _prog(*env)
+    like = shape_like or env[0]
+    out_type = ArrayType(like.type.rank, out_dtypes)
+    ids, n = p._ids(env)
+    sb, sn = _seed_bytes(seed, out_type)
+    t = out_type.ctype()
+    vid = lib().accb_program_fold_seg(p.handle, p.ctx._k(spec), ids, n, like.id, offsets.id, sb, sn, C.byref(t))
+    r = p._new(vid, out_type)
+    r.shape_fn = lambda s, f=like.shape_fn, g=offsets.shape_fn: tuple(f(s)[:-1]) + (g(s)[0] - 1,)
+    return r
+
+
+def stencil2(spec: KernelSpec, src1: Acc, src2: Acc, out_dtype, boundary="clamp", constant=None) -> Acc:
+    """stencil2 node: result over the intersection of the sources (Execute.hs:427-450)."""
+    p = src1.prog
+    out_type = ArrayType(src1.type.rank, out_dtype)
+    cb, cn = _bytes_of(constant)
+    t = out_type.ctype()
+    vid = lib().accb_program_stencil2(p.handle, p.ctx._k(spec), src1.id, src2.id, BOUNDARY[boundary], cb, cn, C.byref(t))
+    r = p._new(vid, out_type)
+    r.shape_fn = lambda s, f=src1.shape_fn, g=src2.shape_fn: tuple(min(a, b) for a, b in zip(f(s), g(s)))
     return r
 
 

@@ -25,13 +25,16 @@ using namespace accb_rt;
 
 namespace {
 
-enum NodeKind { N_MAP, N_FOLD, N_SCAN, N_PERMUTE, N_STENCIL };
+enum NodeKind { N_MAP, N_FOLD, N_SCAN, N_PERMUTE, N_STENCIL, N_FOLDSEG, N_STENCIL2 };
 
 struct Node {
     NodeKind kind;
     accb_kernel *k = nullptr;
     std::vector<int> env;
-    int shape_like = 0;
+    int shape_like = 0;   /* value whose shape the result takes; -1: the literal shape below (generate) */
+    int lit_rank = 0;
+    int lit_shape[ACCB_MAX_RANK] = {0};
+    int offsets_id = -1;  /* foldSeg: Int32 vector of segment offsets, length segments + 1 */
     int all = 0;          /* fold: reduce everything */
     int direction = 0, scan_kind = 0;
     int defaults_id = -1; /* permute */
@@ -125,7 +128,11 @@ int run_internal(accb_program *p, cudaStream_t s, const accb_array *inputs, accb
     for (Node &nd : p->nodes) {
         std::vector<accb_array> env;
         for (int e : nd.env) env.push_back(val[e]);
-        const accb_array &like = val[nd.shape_like];
+        accb_array literal;
+        memset(&literal, 0, sizeof literal);
+        literal.rank = nd.lit_rank;
+        memcpy(literal.shape, nd.lit_shape, sizeof nd.lit_shape);
+        const accb_array &like = nd.shape_like >= 0 ? val[nd.shape_like] : literal;
         accb_array out;
         memset(&out, 0, sizeof out);
         const bool fresh = fresh_outputs && is_output(nd.out_id);
@@ -183,6 +190,35 @@ int run_internal(accb_program *p, cudaStream_t s, const accb_array *inputs, accb
                 TRY(accb_permute(ctx, nd.k, s, env.data(), (int)env.size(), size_of(like), nullptr, 0, &out));
                 break;
             }
+            case N_FOLDSEG: {
+                /* the innermost extent becomes the number of segments (Execute.hs:320-324) */
+                const accb_array &offs = val[nd.offsets_id];
+                if (offs.rank != 1 || offs.shape[0] < 1 || like.rank < 1)
+                    return fail(ctx, ACCB_EINVAL, "foldSeg needs a vector of segments + 1 offsets and a source of rank >= 1");
+                const long long nseg = offs.shape[0] - 1;
+                out.rank = like.rank;
+                out.shape[0] = (int)nseg;
+                long long rows = 1;
+                for (int d = 1; d < like.rank; ++d) {
+                    out.shape[d] = like.shape[d];
+                    rows *= like.shape[d];
+                }
+                TRY(alloc_value(p, nd.out_id, out, fresh));
+                TRY(accb_fold_seg(ctx, nd.k, s, env.data(), (int)env.size(), rows, like.shape[0],
+                                  static_cast<const int *>(offs.ptr[0]), nseg, nd.has_seed ? sc : nullptr,
+                                  nd.scalars.size(), &out));
+                break;
+            }
+            case N_STENCIL2: {
+                /* the result covers the intersection of the two sources (Execute.hs:433-435) */
+                const accb_array &a = val[nd.env[0]], &b = val[nd.env[1]];
+                if (a.rank != b.rank) return fail(ctx, ACCB_EINVAL, "stencil2 sources differ in rank");
+                out.rank = a.rank;
+                for (int d = 0; d < a.rank; ++d) out.shape[d] = std::min(a.shape[d], b.shape[d]);
+                TRY(alloc_value(p, nd.out_id, out, fresh));
+                TRY(accb_stencil2(ctx, nd.k, s, &a, &b, nd.boundary, sc, nd.scalars.size(), &out));
+                break;
+            }
             case N_STENCIL: {
                 out.rank = like.rank;
                 memcpy(out.shape, like.shape, sizeof out.shape);
@@ -214,7 +250,8 @@ int add_node(accb_program *p, Node &nd, const accb_value_type *out_type, int nva
         return -fail(p->ctx, ACCB_EINVAL, "bad result type");
     for (int e : nd.env)
         if (e < 0 || e >= (int)p->types.size()) return -fail(p->ctx, ACCB_EINVAL, "unknown value id %d", e);
-    if (nd.shape_like < 0 || nd.shape_like >= (int)p->types.size()) return -fail(p->ctx, ACCB_EINVAL, "unknown value id");
+    if (nd.shape_like >= (int)p->types.size() || (nd.shape_like < 0 && !(nd.kind == N_MAP && nd.shape_like == -1)))
+        return -fail(p->ctx, ACCB_EINVAL, "unknown value id");
     nd.out_id = (int)p->types.size();
     nd.out_type = *out_type;
     p->types.push_back(*out_type);
@@ -324,6 +361,56 @@ int accb_program_stencil(accb_program *p, accb_kernel *k, int src_id, int bounda
     nd.shape_like = src_id;
     nd.boundary = boundary;
     nd.iters = std::max(1, iters);
+    if (constant) nd.scalars.assign((const unsigned char *)constant, (const unsigned char *)constant + constant_bytes);
+    return add_node(p, nd, out_type, 1);
+}
+
+/* generate: a map whose result shape is given literally (innermost extent first) */
+int accb_program_generate(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank, const int *shape,
+                          const accb_value_type *out_type, const void *scalars, size_t scalar_bytes) {
+    if (!p || !k) return -ACCB_EINVAL;
+    if (rank < 0 || rank > ACCB_ARRAY_MAX_RANK || (rank > 0 && !shape)) return -fail(p->ctx, ACCB_EINVAL, "bad shape");
+    Node nd;
+    nd.kind = N_MAP;
+    nd.k = k;
+    if (nenv > 0) nd.env.assign(env_ids, env_ids + nenv);
+    nd.shape_like = -1;
+    nd.lit_rank = rank;
+    for (int d = 0; d < rank; ++d) {
+        if (shape[d] < 0) return -fail(p->ctx, ACCB_EINVAL, "negative extent");
+        nd.lit_shape[d] = shape[d];
+    }
+    if (scalars) nd.scalars.assign((const unsigned char *)scalars, (const unsigned char *)scalars + scalar_bytes);
+    return add_node(p, nd, out_type, 1);
+}
+
+int accb_program_fold_seg(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like, int offsets_id,
+                          const void *seed, size_t seed_bytes, const accb_value_type *out_type) {
+    if (!p || !k) return -ACCB_EINVAL;
+    if (offsets_id < 0 || offsets_id >= (int)p->types.size()) return -fail(p->ctx, ACCB_EINVAL, "unknown offsets id");
+    if (p->types[offsets_id].ncomp != 1 || p->types[offsets_id].comp_bytes[0] != 4)
+        return -fail(p->ctx, ACCB_EINVAL, "segment offsets are Int32");
+    Node nd;
+    nd.kind = N_FOLDSEG;
+    nd.k = k;
+    nd.env.assign(env_ids, env_ids + nenv);
+    nd.shape_like = shape_like;
+    nd.offsets_id = offsets_id;
+    nd.has_seed = seed != nullptr;
+    if (seed) nd.scalars.assign((const unsigned char *)seed, (const unsigned char *)seed + seed_bytes);
+    return add_node(p, nd, out_type, 1);
+}
+
+int accb_program_stencil2(accb_program *p, accb_kernel *k, int src1_id, int src2_id, int boundary, const void *constant,
+                          size_t constant_bytes, const accb_value_type *out_type) {
+    if (!p || !k) return -ACCB_EINVAL;
+    Node nd;
+    nd.kind = N_STENCIL2;
+    nd.k = k;
+    nd.env.push_back(src1_id);
+    nd.env.push_back(src2_id);
+    nd.shape_like = src1_id;
+    nd.boundary = boundary;
     if (constant) nd.scalars.assign((const unsigned char *)constant, (const unsigned char *)constant + constant_bytes);
     return add_node(p, nd, out_type, 1);
 }

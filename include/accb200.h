@@ -287,6 +287,19 @@ ACCB_API int accb_program_permute(accb_program *p, accb_kernel *k, const int *en
 ACCB_API int accb_program_stencil(accb_program *p, accb_kernel *k, int src_id, int boundary,
                                   const void *constant, size_t constant_bytes, int iters,
                                   const accb_value_type *out_type);
+/* generate: a map node whose result shape is given literally, innermost extent first
+ * (`generate (constant sh) f`, CUDA/Execute.hs:194-195) */
+ACCB_API int accb_program_generate(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,
+                                   const int *shape, const accb_value_type *out_type, const void *scalars,
+                                   size_t scalar_bytes);
+/* foldSeg / fold1Seg: offsets_id names an Int32 vector of segments + 1 offsets, the exclusive scan of the
+ * segment lengths (foldSegOp, CUDA/Execute.hs:320-324); the innermost extent of the result is the segment count */
+ACCB_API int accb_program_fold_seg(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like,
+                                   int offsets_id, const void *seed, size_t seed_bytes,
+                                   const accb_value_type *out_type);
+/* stencil2: the result covers the intersection of the two sources (stencil2Op, CUDA/Execute.hs:427-450) */
+ACCB_API int accb_program_stencil2(accb_program *p, accb_kernel *k, int src1_id, int src2_id, int boundary,
+                                   const void *constant, size_t constant_bytes, const accb_value_type *out_type);
 ACCB_API int accb_program_outputs(accb_program *p, const int *ids, int nout);
 /* run with DEVICE arrays (what runProgram does) */
 ACCB_API int accb_program_run(accb_program *p, accb_stream stream, const accb_array *inputs,

@@ -1,0 +1,286 @@
+"""The embedded array language (accelerate-cuda_b200/lang.py): what it prints (no device needed), that
+what it prints compiles for sm_100a, and -- on a GPU -- that whole programs written like Accelerate programs
+compute what numpy computes."""
+import ctypes as C
+import importlib
+
+import numpy as np
+import pytest
+
+A = importlib.import_module("accelerate-cuda_b200.lang")
+f32, f64, i32, i64, u32 = np.float32, np.float64, np.int32, np.int64, np.uint32
+
+add = lambda a, b: a + b  # noqa: E731
+
+
+# ------------------------------------------------------------------ programs shared by the tests
+def dotp(xs, ys):
+    return A.fold(add, 0.0, A.zipWith(lambda a, b: a * b, xs, ys))
+
+
+def histogram(keys):
+    return A.permute(add, A.fill(4096, 0, i32), lambda i: keys[i], A.fill(A.shape_of(keys), 1, i32))
+
+
+def blur(g):
+    w = [[1, 2, 1], [2, 4, 2], [1, 2, 1]]
+    return A.stencil(lambda t: sum((t[y][x] * (w[y][x] / 16.0) for y in range(3) for x in range(3)), A.constant(0, f32)),
+                     "clamp", g)
+
+
+def blackscholes(spot, strike, years):
+    def price(s, k, t):
+        r, v = 0.02, 0.30
+        vsq = v * A.sqrt(t)
+        d1 = (A.log(s / k) + (r + 0.5 * v * v) * t) / vsq
+        d2 = d1 - vsq
+        cnd = lambda d: 0.5 + 0.5 * A.erf(0.70710678 * d)  # noqa: E731
+        kexp = k * A.exp(-r * t)
+        return s * cnd(d1) - kexp * cnd(d2), kexp * (1.0 - cnd(d2)) - s * (1.0 - cnd(d1))
+    return A.zipWith(price, spot, strike, years)
+
+
+def smvm(vals, cols, vec, seglens):
+    return A.foldSeg(add, 0.0, A.zipWith(lambda v, c: v * vec[c], vals, cols), seglens)
+
+
+def argmax(xs):
+    pairs = A.generate(A.shape_of(xs), lambda i: (xs[i], i))
+    return A.fold1(lambda a, b: A.cond((b[0] > a[0]) | ((b[0] == a[0]) & (b[1] < a[1])), b, a), pairs)
+
+
+# ------------------------------------------------------------------ what is printed (CPU)
+def test_a_fold_over_a_zipwith_is_one_kernel_reading_both_vectors_elementwise():
+    specs = A.specs(dotp, A.vector(f32), A.vector(f32))
+    assert [s.skeleton for s in specs] == ["fold_all"]
+    src = specs[0].source
+    assert "using In = accb::types<float, float>;" in src and "in0 * in1" in src
+    assert "accb::Fold<float, double>" in src  # a recognised (+) on Float accumulates in double
+
+
+def test_fill_sources_cost_no_traffic_and_the_combiner_picks_the_atomic():
+    specs = A.specs(histogram, A.vector(i32))
+    assert [s.skeleton for s in specs] == ["map", "permute_smem"]  # the defaults are generated, the ones are fused
+    src = specs[1].source
+    assert "accb::Atomic::Add" in src and "using In = accb::types<int>;" in src and "identity()" in src
+    mx = A.specs(lambda k, v: A.permute(A.maximum, A.fill(16, 0.0, f32), lambda i: k[i], v), A.vector(i32), A.vector(f32))
+    assert "accb::Atomic::Cas" in mx[-1].source and mx[-1].skeleton == "permute"
+    last = A.specs(lambda k, v: A.permute(lambda x, y: x, A.fill(16, 0, i32), lambda i: k[i], v), A.vector(i32), A.vector(i32))
+    assert "accb::Atomic::None" in last[-1].source
+
+
+def test_integer_arithmetic_follows_the_reference_c_forms():
+    def f(x):
+        return A.map(lambda a: (a // 3, a % 3, A.quot(a, 3), A.rem(a, 3), -a, abs(a), a << 2), x)
+    src = A.specs(f, A.vector(i32))[0].source
+    for piece in ["accb::idiv<int>(in0, 3)", "accb::imod<int>(in0, 3)", "in0 / 3", "in0 % 3",
+                  "(int)(0 - (unsigned int)in0)", "(int)(in0 << 2)"]:
+        assert piece in src, piece
+    g = A.specs(lambda x: A.map(lambda a: (A.round_(a), A.floor(a), A.minimum(a, 2.0), a ** 2.0), x), A.vector(f32))[0].source
+    for piece in ["(int)roundf(in0)", "(int)floorf(in0)", "fminf(in0, 2.0f)", "powf(in0, 2.0f)"]:
+        assert piece in g, piece
+
+
+def test_the_language_is_typed_like_accelerate():
+    with pytest.raises(TypeError):
+        A.specs(lambda x, y: A.zipWith(add, x, y), A.vector(f32), A.vector(i32))  # Float + Int
+    with pytest.raises(TypeError):
+        A.specs(lambda x: A.map(lambda a: a + 0.5, x), A.vector(i32))  # fractional literal at Int
+    with pytest.raises(TypeError):
+        A.specs(lambda x: A.map(lambda a: a / 2, x), A.vector(i32))  # (/) on Int
+    with pytest.raises(TypeError):
+        A.specs(lambda x: A.map(lambda a: 1 if a > 0 else 0, x), A.vector(i32))  # Python `if` on an Exp
+    ok = A.specs(lambda x, y: A.zipWith(lambda a, b: a + A.fromIntegral(b, f32), x, y), A.vector(f32), A.vector(i32))
+    assert "(float)in1" in ok[0].source
+
+
+def test_backpermute_is_a_gather_and_indices_are_row_major():
+    src = A.specs(lambda m: A.backpermute((4, 6), lambda ix: (ix[1], ix[0]), m), A.matrix(f32))[0].source
+    assert "using In = accb::types<>;" in src and "env.in<float>(0)" in src
+    assert "accb::from_index2(6, i," in src and "* env.dim(0, 0) +" in src
+
+
+def test_an_array_read_at_its_own_index_and_elsewhere_appears_twice():
+    f = lambda v: A.generate(A.shape_of(v), lambda i: v[i] - v[A.maximum(i - 1, 0)])  # noqa: E731
+    src = A.specs(f, A.vector(i32))[0].source
+    assert "using In = accb::types<int>;" in src and "env.in<int>(1)" in src
+
+
+def test_tuples_become_structs_with_soa_outputs():
+    specs = A.specs(argmax, A.vector(f32))
+    assert [s.skeleton for s in specs] == ["fold_all"]
+    src = specs[0].source
+    assert "struct E { float c0; int c1; };" in src and "using Out = accb::types<float, int>;" in src
+    assert "void put(E r, float &o0, int &o1)" in src
+
+
+def test_segments_are_lengths_scanned_to_offsets_as_in_the_reference():
+    specs = A.specs(smvm, A.vector(f32), A.vector(i32), A.vector(f32), A.vector(i32))
+    assert [s.skeleton for s in specs] == ["scan", "fold_seg"]
+    assert "using In = accb::types<float, int>;" in specs[1].source and "env.in<float>(2)" in specs[1].source
+
+
+def test_everything_printed_compiles_for_sm_100a(accb):
+    """nvcc -arch=sm_100a on a sample of generated functors (no device needed)."""
+    import os
+    import tempfile
+    lib = accb.lib()
+    programs = [
+        (dotp, [A.vector(f32), A.vector(f32)]), (histogram, [A.vector(i32)]), (blur, [A.matrix(f32)]),
+        (blackscholes, [A.vector(f32)] * 3), (smvm, [A.vector(f32), A.vector(i32), A.vector(f32), A.vector(i32)]),
+        (argmax, [A.vector(f32)]),
+        (lambda m: A.backpermute((4, 6), lambda ix: (ix[1], ix[0]), m), [A.matrix(f32)]),
+        (lambda a, b: A.stencil2(lambda s, t: s[1][1] + 0.5 * (t[0][1] + t[2][1]), ("constant", 0.0), a, b),
+         [A.matrix(f32), A.matrix(f32)]),
+        (lambda ab: A.scanl1(lambda f, g: (g[0] * f[0], g[0] * f[1] + g[1]), ab), [A.vector(u32, u32)]),
+        (lambda x: A.map(lambda a: (a // 3, a % 3, A.cast(a, i64) * 5, A.cast(a, f64) / 3.0, a > 2), x), [A.vector(i32)]),
+        (lambda k, v: A.permute(lambda x, y: (x[0] + y[0], x[1] + y[1]), A.zip(A.fill(64, 0, i32), A.fill(64, 0, i32)),
+                                lambda i: k[i], A.zip(v, A.fill(A.shape_of(v), 1, i32))),
+         [A.vector(i32), A.vector(i32)]),
+    ]
+    specs = {}
+    for f, ts in programs:
+        for s in A.specs(f, *ts):
+            specs[s.functor] = s
+    from concurrent.futures import ThreadPoolExecutor
+    with tempfile.TemporaryDirectory() as cache:
+        def one(s):
+            log = C.create_string_buffer(1 << 16)
+            st = lib.accb_kernel_precompile(s.skeleton.encode(), s.source.encode(), s.functor.encode(), None,
+                                            cache.encode(), log, len(log))
+            return st, s, log.value.decode(errors="replace")
+        with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
+            for st, s, log in ex.map(one, specs.values()):
+                assert st == 0, f"{s.skeleton} {s.functor}:\n{s.source}\n{log}"
+
+
+# ------------------------------------------------------------------ whole programs on a GPU
+def close(got, ref, atol, rtol=1e-5):
+    got, ref = np.asarray(got, f64), np.asarray(ref, f64)
+    assert np.all(np.abs(got - ref) <= rtol * np.abs(ref) + atol), float(np.max(np.abs(got - ref)))
+
+
+@pytest.mark.gpu
+def test_dot_product_and_row_sums(ctx, rng):
+    x, y = rng.uniform(-1, 1, 300001).astype(f32), rng.uniform(-1, 1, 300001).astype(f32)
+    close(A.runWith(ctx, dotp, x, y), np.dot(x.astype(f64), y.astype(f64)), 1e-6)
+    m = rng.uniform(-1, 1, (700, 1300)).astype(f32)
+    close(A.runWith(ctx, lambda a: A.fold(add, 0.0, a), m), m.astype(f64).sum(axis=1), 1e-6)
+    close(A.runWith(ctx, lambda a: A.foldAll(A.maximum, -1e30, a), m), m.max(), 0)
+    with pytest.raises(ValueError):
+        A.runWith(ctx, dotp, x, y[:-1])  # zipped arrays of different length
+
+
+@pytest.mark.gpu
+def test_the_six_scans(ctx, rng):
+    x = rng.integers(-100, 100, 100003).astype(i32)
+    c = np.cumsum(x.astype(i64)).astype(i32)
+    assert np.array_equal(A.runWith(ctx, lambda v: A.scanl(add, 7, v), x), np.concatenate([[7], c + 7]).astype(i32))
+    assert np.array_equal(A.runWith(ctx, lambda v: A.scanl1(add, v), x), c)
+    body, tot = A.runWith(ctx, lambda v: A.scanl_(add, 0, v), x)
+    assert np.array_equal(body, np.concatenate([[0], c[:-1]]).astype(i32)) and tot == c[-1]
+    r = np.cumsum(x[::-1].astype(i64))[::-1].astype(i32)
+    assert np.array_equal(A.runWith(ctx, lambda v: A.scanr1(add, v), x), r)
+    assert np.array_equal(A.runWith(ctx, lambda v: A.scanr(add, 0, v), x), np.concatenate([r, [0]]).astype(i32))
+    body, tot = A.runWith(ctx, lambda v: A.scanr_(add, 0, v), x)
+    assert np.array_equal(body, np.concatenate([r[1:], [0]]).astype(i32)) and tot == r[0]
+    # a scan over a fused producer and a non-commutative tuple combiner (composition of affine maps)
+    a, b = rng.integers(1, 5, 5000).astype(u32), rng.integers(0, 9, 5000).astype(u32)
+    ga, gb = A.runWith(ctx, lambda ab: A.scanl1(lambda f, g: (g[0] * f[0], g[0] * f[1] + g[1]), ab), (a, b))
+    ra, rb = np.empty_like(a), np.empty_like(b)
+    fa, fb = np.uint32(1), np.uint32(0)
+    with np.errstate(over="ignore"):
+        for i in range(a.size):
+            fa, fb = a[i] * fa, a[i] * fb + b[i]
+            ra[i], rb[i] = fa, fb
+    assert np.array_equal(ga, ra) and np.array_equal(gb, rb)
+
+
+@pytest.mark.gpu
+def test_histogram_and_scatter_with_ignore(ctx, rng):
+    keys = rng.integers(0, 4096, 200000).astype(i32)
+    assert np.array_equal(A.runWith(ctx, histogram, keys), np.bincount(keys, minlength=4096).astype(i32))
+    vals = rng.uniform(0, 1, keys.size).astype(f32)
+    got = A.runWith(ctx, lambda k, v: A.permute(A.maximum, A.fill(4096, -1.0, f32),
+                                                lambda i: A.cond_index(k[i] % 2 == 0, k[i]), v), keys, vals)
+    ref = np.full(4096, -1.0, f32)
+    even = keys % 2 == 0
+    np.maximum.at(ref, keys[even], vals[even])
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", ("constant", 0.5)])
+def test_stencils(ctx, oracle, rng, boundary):
+    g = rng.uniform(0, 1, (300, 520)).astype(f32)
+    w = np.array([[1, 2, 1], [2, 4, 2], [1, 2, 1]]) / 16.0
+    f = lambda a: A.stencil(lambda t: sum((t[y][x] * float(w[y][x]) for y in range(3) for x in range(3)),  # noqa: E731
+                                          A.constant(0, f32)), boundary, a)
+    mode, cval = boundary if isinstance(boundary, tuple) else (boundary, 0.0)
+    close(A.runWith(ctx, f, g), oracle.stencil2d(g, w, mode, cval), 1e-6)
+    v = rng.uniform(0, 1, 10007).astype(f32)
+    s1 = A.runWith(ctx, lambda a: A.stencil(lambda t: 0.25 * t[0] + 0.5 * t[1] + 0.25 * t[2], boundary, a), v)
+    close(s1, oracle.stencil2d(v.reshape(1, -1), np.array([[0.25, 0.5, 0.25]]), mode, cval).reshape(-1), 1e-6)
+
+
+@pytest.mark.gpu
+def test_iterated_stencil_and_stencil2(ctx, rng):
+    g = rng.uniform(0, 1, (64, 128)).astype(f32)
+    five = lambda t: 0.2 * (t[0][1] + t[1][0] + t[1][1] + t[1][2] + t[2][1])  # noqa: E731
+    once = A.run1With(ctx, lambda a: A.stencil(five, "clamp", a), A.matrix(f32))
+    ref = g
+    for _ in range(4):
+        ref = once(ref)
+    close(A.runWith(ctx, lambda a: A.stencil(five, "clamp", a, iterate=4), g), ref, 1e-6)
+    h = rng.uniform(0, 1, (60, 128)).astype(f32)  # the result covers the intersection: 60 rows
+    got = A.runWith(ctx, lambda a, b: A.stencil2(lambda s, t: s[1][1] - t[1][1] + 0.5 * t[0][1], "clamp", a, b), g, h)
+    up = np.vstack([h[:1], h[:-1]])
+    close(got, g[:60] - h + 0.5 * up, 1e-6)
+
+
+@pytest.mark.gpu
+def test_black_scholes_is_one_map_with_two_outputs(ctx, workloads, oracle):
+    n = 50000
+    W = workloads
+    s, k, t = W.uniform_f32(W.SEED, W.S_SPOT, n, 5, 30), W.uniform_f32(W.SEED, W.S_STRIKE, n, 1, 100), \
+        W.uniform_f32(W.SEED, W.S_YEARS, n, 0.25, 10)
+    assert [x.skeleton for x in A.specs(blackscholes, *[A.vector(f32)] * 3)] == ["map"]
+    call, put = A.runWith(ctx, blackscholes, s, k, t)
+    rc, rp = oracle.blackscholes(s, k, t)
+    close(call, rc, 2e-5)
+    close(put, rp, 2e-5)
+
+
+@pytest.mark.gpu
+def test_sparse_matrix_vector_product(ctx, rng):
+    nrows, ncols = 20000, 3000
+    nnz = rng.integers(0, 13, nrows).astype(i32)
+    vals = rng.uniform(-1, 1, int(nnz.sum())).astype(f32)
+    cols = rng.integers(0, ncols, vals.size).astype(i32)
+    vec = rng.uniform(-1, 1, ncols).astype(f32)
+    got = A.runWith(ctx, smvm, vals, cols, vec, nnz)
+    offs = np.concatenate([[0], np.cumsum(nnz)])
+    prod = np.concatenate([(vals * vec[cols]).astype(f64), [0.0]])
+    close(got, np.add.reduceat(prod, offs[:-1]) * (nnz > 0), 1e-6)
+
+
+@pytest.mark.gpu
+def test_generate_backpermute_tuples_and_index_arithmetic(ctx, rng):
+    m = rng.uniform(-1, 1, (37, 53)).astype(f32)
+    assert np.array_equal(A.runWith(ctx, lambda a: A.backpermute((53, 37), lambda ix: (ix[1], ix[0]), a), m), m.T)
+    x = rng.uniform(-1, 1, 100001).astype(f32)
+    v, i = A.runWith(ctx, argmax, x)
+    assert i == int(np.argmax(x)) and v == x.max()
+    a = rng.integers(-50, 50, 10000).astype(i32)
+    d, r, q, t, big, frac, pos = A.runWith(
+        ctx, lambda z: A.map(lambda e: (e // 7, e % 7, A.quot(e, 7), A.rem(e, 7), A.cast(e, i64) * (1 << 33),
+                                        A.cast(e, f64) / 3.0, e > 2), z), a)
+    assert np.array_equal(d, a // 7) and np.array_equal(r, a % 7)  # numpy's // and % floor like Haskell's div and mod
+    assert np.array_equal(q, np.trunc(a / 7).astype(i32)) and np.array_equal(t, a - 7 * np.trunc(a / 7).astype(i32))
+    assert np.array_equal(big, a.astype(i64) << 33) and np.array_equal(frac, a / 3.0) and np.array_equal(pos.astype(bool), a > 2)
+    iota = A.runWith(ctx, lambda z: A.generate((3, 5), lambda ix: ix[0] * 10 + ix[1] + A.the(A.fold(add, 0, z))), a)
+    assert np.array_equal(iota, np.arange(3)[:, None] * 10 + np.arange(5)[None, :] + a.sum(dtype=i64).astype(i32))
+    f = A.run1With(ctx, lambda z: A.map(lambda e: A.cond(e < 0.0, -e, A.sqrt(e)), z), A.vector(f32))
+    for n in (5, 70000):  # one compiled function, several shapes
+        y = rng.uniform(-1, 1, n).astype(f32)
+        close(f(y), np.where(y < 0, -y, np.sqrt(np.abs(y))), 1e-7)
