@@ -44,10 +44,14 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
 
 def preseed_cache(verbose: bool = False) -> int:
-    """Compile every program of programs.py into kcache/ (skips cache hits)."""
+    """Compile every program of programs.py, and the kernels the embedded language prints for the example
+    programs of examples.py, into kcache/ (skips cache hits)."""
     sys.path.insert(0, os.path.dirname(HERE))
     import importlib
-    programs = importlib.import_module("accelerate-cuda_b200.programs")
+    import types
+    hand = importlib.import_module("accelerate-cuda_b200.programs")
+    generated = importlib.import_module("accelerate-cuda_b200.examples").generated_specs()
+    programs = types.SimpleNamespace(ALL={**hand.ALL, **{"lang:" + k: s for k, s in generated.items()}})
     lib = C.CDLL(LIB)
     lib.accb_kernel_precompile.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.c_size_t]
     lib.accb_last_error.restype = C.c_char_p

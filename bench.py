@@ -130,6 +130,13 @@ class Workload:
         self.P = importlib.import_module("accelerate-cuda_b200.programs")
         self.W = importlib.import_module("accelerate-cuda_b200.workloads")
 
+    functors = "hand"  # "lang": the kernels the embedded language prints for the same programs (examples.py)
+
+    def functor(self, name):
+        if self.functors == "lang":
+            return importlib.import_module("accelerate-cuda_b200.examples").generated_specs()[name]
+        return getattr(self.P, name)
+
 
 class ScanWorkload(Workload):
     """scanl (+) 0 over Int32, values uniform in [0,16); 2^28 elements per GPU."""
@@ -142,7 +149,7 @@ class ScanWorkload(Workload):
         self.ctx.gen_uniform_i32(self.x, self.n, self.rank * self.n, W.SEED, W.S_SCAN, 16)
         # rank r writes its slab of the global result; the last rank also owns out[n_total]
         self.out = t.empty(self.n + 1, dtype=t.int32, device="cuda")
-        self.k = self.ctx.kernel(self.P.SCAN_ADD_I32).wait()
+        self.k = self.ctx.kernel(self.functor("SCAN_ADD_I32")).wait()
         self.bytes = W.bytes_scan(self.n)
         if self.world > 1:
             import torch.distributed as dist
@@ -193,7 +200,7 @@ class DotWorkload(Workload):
         self.ctx.gen_uniform_f32(self.x, self.n, first, W.SEED, W.S_XS, -1.0, 1.0)
         self.ctx.gen_uniform_f32(self.y, self.n, first, W.SEED, W.S_YS, -1.0, 1.0)
         self.out = t.zeros(1, dtype=t.float32, device="cuda")
-        self.k = self.ctx.kernel(self.P.DOT).wait()
+        self.k = self.ctx.kernel(self.functor("DOT")).wait()
         self.bytes = W.bytes_dot(self.n)
         if self.world > 1:
             self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
@@ -226,7 +233,7 @@ class HistWorkload(Workload):
         self.ctx.gen_zipf_mix_i32(self.keys, self.n, self.rank * self.n, W.SEED, cdf, W.HIST_BINS)
         self.defaults = t.zeros(W.HIST_BINS, dtype=t.int32, device="cuda")
         self.out = t.zeros(W.HIST_BINS, dtype=t.int32, device="cuda")
-        self.k = self.ctx.kernel(self.P.HIST).wait()
+        self.k = self.ctx.kernel(self.functor("HIST")).wait()
         self.bytes = W.bytes_hist(self.n)
         if self.world > 1:
             self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
@@ -264,7 +271,7 @@ class StencilWorkload(Workload):
         self.src = t.zeros_like(self.a)
         self.ctx.gen_uniform_f32(self.src[halo:halo + self.h], self.h * self.w, self.rank * self.h * self.w, W.SEED,
                                  W.S_GRID, 0.0, 1.0)
-        self.k = self.ctx.kernel(self.P.BLUR).wait()
+        self.k = self.ctx.kernel(self.functor("BLUR")).wait()
         self.bytes = W.bytes_stencil(self.h, self.w, self.iters)
         if self.world > 1:
             self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
@@ -301,7 +308,7 @@ class BlackScholesWorkload(Workload):
         self.ctx.gen_uniform_f32(self.s, self.n, 0, W.SEED, W.S_SPOT, 5.0, 30.0)
         self.ctx.gen_uniform_f32(self.k_, self.n, 0, W.SEED, W.S_STRIKE, 1.0, 100.0)
         self.ctx.gen_uniform_f32(self.y, self.n, 0, W.SEED, W.S_YEARS, 0.25, 10.0)
-        self.k = self.ctx.kernel(self.P.BLACKSCHOLES).wait()
+        self.k = self.ctx.kernel(self.functor("BLACKSCHOLES")).wait()
         self.bytes = W.bytes_blackscholes(self.n)
         self.ctx.sync()
 
@@ -326,7 +333,7 @@ class RowSumWorkload(Workload):
         self.m = t.empty((self.rows, self.cols), dtype=t.float32, device="cuda")
         self.ctx.gen_uniform_f32(self.m, self.rows * self.cols, 0, W.SEED, W.S_MATRIX, -1.0, 1.0)
         self.out = t.zeros(self.rows, dtype=t.float32, device="cuda")
-        self.k = self.ctx.kernel(self.P.ROWSUM).wait()
+        self.k = self.ctx.kernel(self.functor("ROWSUM")).wait()
         self.bytes = W.bytes_rowsum(self.rows, self.cols)
         self.ctx.sync()
 
@@ -353,7 +360,7 @@ class Scan64Workload(Workload):
         self.x = x32.long()
         del x32
         self.out = t.empty(self.n + 1, dtype=t.int64, device="cuda")
-        self.k = self.ctx.kernel(self.P.SCAN_ADD_I64).wait()
+        self.k = self.ctx.kernel(self.functor("SCAN_ADD_I64")).wait()
         self.bytes = 16 * self.n + 8
         self.ctx.sync()
 
@@ -374,7 +381,7 @@ class ShortRowsWorkload(Workload):
         self.m = t.empty((self.rows, self.cols), dtype=t.float32, device="cuda")
         self.ctx.gen_uniform_f32(self.m, self.rows * self.cols, 0, W.SEED, W.S_MATRIX, -1.0, 1.0)
         self.out = t.zeros(self.rows, dtype=t.float32, device="cuda")
-        self.k = self.ctx.kernel(self.P.ROWSUM).wait()
+        self.k = self.ctx.kernel(self.functor("ROWSUM")).wait()
         self.bytes = W.bytes_rowsum(self.rows, self.cols)
         self.ctx.sync()
 
@@ -407,7 +414,7 @@ class SmvmWorkload(Workload):
         self.ctx.gen_uniform_i32(self.colidx, self.nnz, 0, W.SEED, W.S_YS, self.ncols)
         self.ctx.gen_uniform_f32(self.vec, self.ncols, 0, W.SEED, W.S_MATRIX, -1.0, 1.0)
         self.out = t.zeros(self.rows, dtype=t.float32, device="cuda")
-        self.k = self.ctx.kernel(self.P.SMVM).wait()
+        self.k = self.ctx.kernel(self.functor("SMVM")).wait()
         # values + column indices + offsets in, one Float per row out; the gathered vector (4 MiB) lives in L2
         self.bytes = 8 * self.nnz + 4 * (self.rows + 1) + 4 * self.rows
         self.ctx.sync()
@@ -434,7 +441,7 @@ class Smooth1dWorkload(Workload):
         self.v = t.empty(self.n, dtype=t.float32, device="cuda")
         self.ctx.gen_uniform_f32(self.v, self.n, 0, W.SEED, W.S_GRID, 0.0, 1.0)
         self.out = t.empty_like(self.v)
-        self.k = self.ctx.kernel(self.P.SMOOTH1D).wait()
+        self.k = self.ctx.kernel(self.functor("SMOOTH1D")).wait()
         self.bytes = 8 * self.n
         self.ctx.sync()
 
@@ -588,6 +595,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="scan", choices=sorted(WORKLOADS) + sorted(SECONDARY))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--functors", default="hand", choices=["hand", "lang"],
+                    help="hand-written functor snippets (programs.py) or the ones the embedded language prints (examples.py)")
     ap.add_argument("--size", type=int, default=None, help="override the problem size (profiling small cases)")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-skeleton table, e2e and CPU baseline")
     args = ap.parse_args()
@@ -613,6 +622,7 @@ def main():
 
     if args.workload in SECONDARY and world > 1:
         raise SystemExit("the secondary workloads run on one GPU")
+    Workload.functors = args.functors
     wl = {**WORKLOADS, **SECONDARY}[args.workload](accb, ctx, torch, rank, world)
     wl.setup(args.size)
     if dist:
@@ -640,7 +650,7 @@ def main():
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
         "data": "synthetic",
         "config": {"workload": wl.name, "l2": "inputs larger than L2 (1 GiB read per step)", "parity_check": ok,
-                   "elements_per_gpu": getattr(wl, "n", None), "seed": hex(wl.W.SEED)},
+                   "elements_per_gpu": getattr(wl, "n", None), "seed": hex(wl.W.SEED), "functors": args.functors},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
         "pct_of_spec_peak_8TBs": 100.0 * per_gpu / SPEC_PEAK_GBS,
@@ -715,6 +725,21 @@ def main():
             torch.cuda.empty_cache()
         line["skeletons"] = {k: v for k, v in table.items() if k in WORKLOADS}    # the BASELINE configurations
         line["secondary"] = {k: v for k, v in table.items() if k in SECONDARY}    # other shapes and types
+        # ---- the same programs written in the embedded language: the kernels it prints against the hand-written ones
+        if args.functors == "hand":
+            Workload.functors = "lang"
+            gen = {}
+            for name, cls in WORKLOADS.items():
+                w3 = cls(accb, ctx, torch, 0, 1)
+                w3.setup(None)
+                ms3, _ = time_steps(torch, w3, 10, 3)
+                g = w3.bytes / (ms3 / 10 * 1e-3) / 1e9
+                gen[name] = {"GB/s": g, "frac_of_measured": g / peak, "vs_hand_written": g / table[name]["GB/s"],
+                             "parity_check": bool(w3.verify())}
+                del w3
+                torch.cuda.empty_cache()
+            Workload.functors = "hand"
+            line["generated_functors"] = gen
     elif rank == 0:
         line["e2e"] = None
     ctx.sync()
