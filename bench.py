@@ -44,12 +44,12 @@ METRIC = "effective HBM GB/s per skeleton at 2^28 elems"
 # rowsum), an option (blackscholes) or a grid point of one application (stencil).  Dirty lines still
 # in L2 when a kernel ends are not counted as DRAM writes by the profiler.
 NCU_TRAFFIC = {
-    "scan": ("scanl", 479.6e6 / (1 << 26)),
-    "dot": ("foldAll", 541.1e6 / (1 << 26)),
-    "hist": ("permute_smem", 272.4e6 / (1 << 26)),
-    "stencil": ("stencil_tile", 245.8e6 / (6144 * 6144)),
-    "blackscholes": ("map", 293.3e6 / (1 << 24)),
-    "rowsum": ("fold", 271.9e6 / (8192 * 8192)),
+    "scan": ("scanl", 480.0e6 / (1 << 26)),
+    "dot": ("foldAll", 541.0e6 / (1 << 26)),
+    "hist": ("permute_smem", 274.9e6 / (1 << 26)),
+    "stencil": ("stencil_tile", 245.4e6 / (6144 * 6144)),
+    "blackscholes": ("map", 292.9e6 / (1 << 24)),
+    "rowsum": ("fold", 276.4e6 / (8192 * 8192)),
 }
 # algorithmic bytes per unit (see accelerate-cuda_b200/workloads.py)
 BYTES_PER_UNIT = {"scan": 8, "dot": 8, "hist": 4, "stencil": 8, "blackscholes": 20, "rowsum": 4}
