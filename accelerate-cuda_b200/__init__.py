@@ -535,14 +535,16 @@ def scan(spec: KernelSpec, env: Sequence[Acc], out_dtypes, direction=SCAN_LEFT, 
     Returns the result array, or (body, total) for the primed forms."""
     p = _prog(*env)
     like = shape_like or env[0]
-    out_type = ArrayType(1, out_dtypes)
+    # an inclusive scan over the row-major sequence of a matrix keeps its shape (segmented / row scans)
+    out_type = ArrayType(like.type.rank if kind == SCAN_INCLUSIVE else 1, out_dtypes)
     ids, n = p._ids(env)
     sb, sn = _seed_bytes(seed, out_type)
     t = out_type.ctype()
     vid = lib().accb_program_scan(p.handle, p.ctx._k(spec), ids, n, like.id, direction, kind, sb, sn, C.byref(t))
     r = p._new(vid, out_type)
     extra = 1 if kind == SCAN_EXCLUSIVE else 0
-    r.shape_fn = lambda s, f=like.shape_fn: (f(s)[0] + extra,)
+    r.shape_fn = (lambda s, f=like.shape_fn: tuple(f(s))) if kind == SCAN_INCLUSIVE else (
+        lambda s, f=like.shape_fn: (f(s)[0] + extra,))
     if kind == SCAN_PRIME:
         tot = Acc(p, vid + 1, ArrayType(0, out_dtypes))
         tot.shape_fn = lambda s: ()

@@ -166,10 +166,17 @@ int run_internal(accb_program *p, cudaStream_t s, const accb_array *inputs, accb
                 break;
             }
             case N_SCAN: {
-                if (like.rank != 1) return fail(ctx, ACCB_EINVAL, "scans are defined on vectors only"); /* PrefixSum.hs:39-46 */
-                const long long n = like.shape[0];
-                out.rank = 1;
-                out.shape[0] = (int)(nd.scan_kind == ACCB_SCAN_EXCLUSIVE ? n + 1 : n);
+                /* The reference scans vectors only (PrefixSum.hs:39-46).  An INCLUSIVE scan is also taken over
+                 * the row-major sequence of an array of higher rank: the result keeps the shape, and a
+                 * combiner that restarts at row or segment heads makes it a scan along the innermost
+                 * dimension or a segmented scan. */
+                if (like.rank != 1 && !(like.rank > 1 && nd.scan_kind == ACCB_SCAN_INCLUSIVE))
+                    return fail(ctx, ACCB_EINVAL, "exclusive scans are defined on vectors only");
+                const long long n = size_of(like);
+                if (n > 0x7fffffffLL - 1) return fail(ctx, ACCB_EINVAL, "array too large for one scan");
+                out.rank = like.rank;
+                memcpy(out.shape, like.shape, sizeof out.shape);
+                if (like.rank == 1) out.shape[0] = (int)(nd.scan_kind == ACCB_SCAN_EXCLUSIVE ? n + 1 : n);
                 TRY(alloc_value(p, nd.out_id, out, fresh));
                 accb_array total;
                 memset(&total, 0, sizeof total);

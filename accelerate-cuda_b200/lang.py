@@ -90,8 +90,9 @@ class _DryBackend:
         return self._add(like.prog, spec, ArrayType(like.type.rank, out_dtypes))
 
     def scan(self, spec, env, out_dtypes, direction=0, kind=0, seed=None, shape_like=None):
-        prog = (shape_like or env[0]).prog
-        r = self._add(prog, spec, ArrayType(1, out_dtypes))
+        like = shape_like or env[0]
+        prog = like.prog
+        r = self._add(prog, spec, ArrayType(like.type.rank if kind == _pkg.SCAN_INCLUSIVE else 1, out_dtypes))
         return (r, prog.new(ArrayType(0, out_dtypes))) if kind == _pkg.SCAN_PRIME else r
 
     def permute(self, spec, env, defaults, shape_like=None):
@@ -1031,10 +1032,112 @@ def fold1Seg(f: Callable, arr: Array, segments: Array) -> Array:
     return foldSeg(f, None, arr, segments)
 
 
+def _same_shape(new: Array, old: Array) -> Array:
+    """The manifest array `new` has the shape of `old` by construction: reads of it at the index of a kernel that
+    iterates over `old` are element-wise."""
+    if old.extent.literal is None:
+        new.prog._same[new.node.id] = old.prog_find(old.extent.like.node.id)
+    return new
+
+
+def _segmented_scan(f: Callable, arr: Array, flag_of: Callable, direction) -> Array:
+    """Inclusive scan of the row-major sequence of arr that restarts wherever flag_of(kenv, ix) holds: at the
+    first element of a row or segment for a left scan, at the last one for a right scan.  The value type is
+    widened to (value, flag) with the usual segmented operator, which is associative whenever f is; only the
+    value components are written."""
+    if arr.extent.literal is not None and not arr.manifest:
+        arr = compute(arr)
+    prog, right = arr.prog, direction == _pkg.SCAN_RIGHT
+    kenv = _KernelEnv(prog, arr.extent)
+    nv = len(arr.dtypes)
+
+    def produce():
+        kenv.index = Index(Exp(I64, "i"), arr.extent.dims(kenv, False))
+        _kenvs.append(kenv)
+        try:
+            vals = arr.at(kenv, kenv.index)
+            flag = flag_of(kenv, kenv.index)
+            if flag.dt != BOOL:
+                raise TypeError("segment flags are Bool")
+            return vals + (flag,)
+        finally:
+            _kenvs.pop()
+    gbody, gvals = _trace(produce)
+    dtypes = arr.dtypes + [BOOL]
+    decl = _struct_for("E", dtypes)
+
+    def combine():
+        # left scans: a precedes b and b's flag restarts; right scans call combine(later, earlier): the later
+        # element is the first argument and its flag restarts (the new element is the left argument of f)
+        first = tuple(Exp(dt, f"a.c{c}") for c, dt in enumerate(arr.dtypes))
+        second = tuple(Exp(dt, f"b.c{c}") for c, dt in enumerate(arr.dtypes))
+        fa, fb = Exp(BOOL, f"a.c{nv}"), Exp(BOOL, f"b.c{nv}")
+        _kenvs.append(_NoEnv())
+        try:
+            both = _flat(f(_unflat1(first), _unflat1(second)))
+        finally:
+            _kenvs.pop()
+        restart, kept = (fa, first) if right else (fb, second)
+        return tuple(cond(restart, k, v) for k, v in _zip(kept, both)) + (fa | fb,)
+    cbody, cvals = _trace(combine)
+    get, = kenv.resolve(f"{gbody}\n        {_ret(dtypes, gvals, 'E')}")
+    refs = ", ".join(f"{ctype(dt)} &o{c}" for c, dt in enumerate(arr.dtypes))
+    puts = " ".join(f"o{c} = r.c{c};" for c in range(nv))
+    text = (f"{decl}\nstruct @N@ {{\n    typedef E elem; typedef E acc;\n    using In = {_types_list(kenv.in_types())};\n"
+            f"    using Out = {_types_list(arr.dtypes)};\n"
+            f"    {_D} E get(const accb::Env &env, long long i{kenv.in_params()}) {{\n        {get}\n    }}\n"
+            f"    {_D} E combine(E a, E b) {{\n        {cbody}\n        {_ret(dtypes, cvals, 'E')}\n    }}\n"
+            f"    {_D} void put(E r, {refs}) {{ {puts} }}\n}};\n")
+    name = _name("SegScan", text)
+    spec = KernelSpec("scan", name, text.replace("@N@", name))
+    nodes, like = _env_or_like(kenv, arr)
+    node = _be().scan(spec, nodes, arr.dtypes, direction=direction, kind=_pkg.SCAN_INCLUSIVE, seed=None, shape_like=like)
+    return _same_shape(Array(prog, arr.dtypes, node=node), arr)
+
+
+def _segment_flags(arr: Array, seglens: Array, right: bool) -> Array:
+    """A Bool array of arr's shape: True at the first (left scans) or last (right scans) element of every
+    non-empty segment."""
+    seglens = _as_array(seglens)
+    if seglens.dtypes != [I32] or seglens.rank != 1 or arr.rank != 1:
+        raise TypeError("segment lengths are a vector of Int32, the data a vector")
+    offs = scanl(lambda a, b: a + b, 0, seglens)
+    lens = seglens
+    where = (lambda s: cond_index(lens[s] > 0, offs[s + 1] - 1)) if right else (lambda s: cond_index(lens[s] > 0, offs[s]))
+    flags = permute(lambda x, y: x, fill(shape_of(arr), False, np.bool_), where, fill(shape_of(seglens), True, np.bool_))
+    return _same_shape(flags, arr)
+
+
+def scanl1Seg(f: Callable, arr: Array, seglens: Array) -> Array:
+    """``scanl1Seg f arr segs``: an inclusive left scan inside every segment (segs = segment lengths)."""
+    arr = _as_array(arr)
+    if not arr.manifest:
+        arr = compute(arr)
+    flags = _segment_flags(arr, seglens, False)
+    return _segmented_scan(f, arr, lambda kenv, ix: flags.at(kenv, ix)[0], _pkg.SCAN_LEFT)
+
+
+def scanr1Seg(f: Callable, arr: Array, seglens: Array) -> Array:
+    arr = _as_array(arr)
+    if not arr.manifest:
+        arr = compute(arr)
+    flags = _segment_flags(arr, seglens, True)
+    return _segmented_scan(f, arr, lambda kenv, ix: flags.at(kenv, ix)[0], _pkg.SCAN_RIGHT)
+
+
 def _scan(f, seed, arr: Array, direction, kind):
     arr = _as_array(arr)
     if arr.rank != 1:
-        raise TypeError("scans are defined on vectors (PrefixSum.hs:39-46)")
+        # Along the innermost dimension of a matrix or cube (the reference rejects these, PrefixSum.hs:39-46):
+        # an inclusive scan of the whole array that restarts at the start (end, for right scans) of every row.
+        if kind != _pkg.SCAN_INCLUSIVE:
+            raise NotImplementedError("scanl1 / scanr1 are defined along the innermost dimension; the seeded forms on vectors")
+        right = direction == _pkg.SCAN_RIGHT
+
+        def row_edge(kenv, ix):
+            x = ix.comps()[-1]
+            return (x == ix.dims[-1] - 1) if right else (x == 0)
+        return _segmented_scan(f, arr, row_edge, direction)
     if arr.extent.literal is not None and not arr.manifest:
         arr = compute(arr)
     spec, kenv = _fold_source("Scan", f, seed, arr, "Scan")

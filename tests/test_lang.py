@@ -120,6 +120,18 @@ def test_segments_are_lengths_scanned_to_offsets_as_in_the_reference():
     assert "using In = accb::types<float, int>;" in specs[1].source and "env.in<float>(2)" in specs[1].source
 
 
+def test_row_scans_and_segmented_scans_are_scans_of_value_flag_pairs():
+    """What the reference rejects (PrefixSum.hs:39-46): the scan skeleton over (value, restart flag)."""
+    rows = A.specs(lambda m: A.scanl1(add, m), A.matrix(i32))
+    assert [s.skeleton for s in rows] == ["scan"]
+    src = rows[0].source
+    assert "struct E { int c0; unsigned char c1; };" in src and "using Out = accb::types<int>;" in src
+    assert "accb::from_index2(" in src  # the flag is "first column", from the index
+    seg = A.specs(lambda v, lens: A.scanl1Seg(add, v, lens), A.vector(f32), A.vector(i32))
+    assert [s.skeleton for s in seg] == ["scan", "map", "permute", "scan"]  # offsets, cleared flags, heads, the scan
+    assert "accb::Atomic::None" in seg[2].source and "using In = accb::types<float, unsigned char>;" in seg[3].source
+
+
 def test_everything_printed_compiles_for_sm_100a(accb):
     """nvcc -arch=sm_100a on a sample of generated functors (no device needed)."""
     import os
@@ -134,6 +146,9 @@ def test_everything_printed_compiles_for_sm_100a(accb):
          [A.matrix(f32), A.matrix(f32)]),
         (lambda ab: A.scanl1(lambda f, g: (g[0] * f[0], g[0] * f[1] + g[1]), ab), [A.vector(u32, u32)]),
         (lambda x: A.map(lambda a: (a // 3, a % 3, A.cast(a, i64) * 5, A.cast(a, f64) / 3.0, a > 2), x), [A.vector(i32)]),
+        (lambda m: A.scanr1(add, m), [A.matrix(f32)]),
+        (lambda v, lens: A.scanl1Seg(add, v, lens), [A.vector(f32), A.vector(i32)]),
+        (lambda v, lens: A.scanr1Seg(A.maximum, v, lens), [A.vector(i64), A.vector(i32)]),
         (lambda k, v: A.permute(lambda x, y: (x[0] + y[0], x[1] + y[1]), A.zip(A.fill(64, 0, i32), A.fill(64, 0, i32)),
                                 lambda i: k[i], A.zip(v, A.fill(A.shape_of(v), 1, i32))),
          [A.vector(i32), A.vector(i32)]),
@@ -194,6 +209,28 @@ def test_the_six_scans(ctx, rng):
             fa, fb = a[i] * fa, a[i] * fb + b[i]
             ra[i], rb[i] = fa, fb
     assert np.array_equal(ga, ra) and np.array_equal(gb, rb)
+
+
+@pytest.mark.gpu
+def test_scans_along_rows_and_inside_segments(ctx, rng):
+    m = rng.integers(-100, 100, (300, 1237)).astype(i32)
+    assert np.array_equal(A.runWith(ctx, lambda a: A.scanl1(add, a), m), np.cumsum(m, axis=1, dtype=i64).astype(i32))
+    assert np.array_equal(A.runWith(ctx, lambda a: A.scanr1(add, a), m),
+                          np.cumsum(m[:, ::-1], axis=1, dtype=i64)[:, ::-1].astype(i32))
+    wide = rng.integers(-9, 9, (3, 40000)).astype(i32)  # rows longer than a tile: the restart crosses tiles
+    assert np.array_equal(A.runWith(ctx, lambda a: A.scanl1(A.maximum, a), wide), np.maximum.accumulate(wide, axis=1))
+    lens = rng.integers(0, 50, 4000).astype(i32)
+    lens[100:140] = 0
+    lens[7] = 30000
+    v = rng.uniform(-1, 1, int(lens.sum())).astype(f32)
+    offs = np.concatenate([[0], np.cumsum(lens)])
+    refl, refr = np.empty_like(v, dtype=f64), np.empty_like(v, dtype=f64)
+    for s in range(lens.size):
+        seg = v[offs[s]:offs[s + 1]].astype(f64)
+        refl[offs[s]:offs[s + 1]] = np.cumsum(seg)
+        refr[offs[s]:offs[s + 1]] = np.cumsum(seg[::-1])[::-1]
+    close(A.runWith(ctx, lambda a, l: A.scanl1Seg(add, a, l), v, lens), refl, 2e-3)  # float32 sums of up to 30000 terms
+    close(A.runWith(ctx, lambda a, l: A.scanr1Seg(add, a, l), v, lens), refr, 2e-3)
 
 
 @pytest.mark.gpu
