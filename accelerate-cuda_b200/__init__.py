@@ -140,6 +140,7 @@ def lib() -> C.CDLL:
             "accb_program_stencil2": [vp, vp, i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
             "accb_program_outputs": [vp, C.POINTER(i32), i32],
             "accb_program_run": [vp, vp, arrp, arrp],
+            "accb_program_run_graph": [vp, vp, arrp, arrp],
             "accb_program_run_host": [vp, arrp, arrp],
             "accb_program_destroy": [vp],
             "accb_gen_uniform_f32": [vp, vp, vp, ll, ll, u64, u64, C.c_float, C.c_float],
@@ -453,10 +454,13 @@ class Afun:
         self.output_types = [o.type for o in outs]
 
     # device arrays in, device arrays out (library-owned until the next run)
-    def run_device(self, inputs: Sequence, stream=None):
+    def run_device(self, inputs: Sequence, stream=None, graph: bool = False):
+        """graph=True: the whole op list as one CUDA graph launch, recorded at the first call for these
+        input arrays on this stream (which must not be the default stream) and replayed afterwards."""
         ins = _arr_list(inputs)
         outs = (accb_array * len(self.output_types))()
-        _check(lib().accb_program_run(self.handle, Context._stream(stream), ins, outs), self.ctx.handle)
+        run = lib().accb_program_run_graph if graph else lib().accb_program_run
+        _check(run(self.handle, Context._stream(stream), ins, outs), self.ctx.handle)
         return list(outs)
 
     # host arrays in, host arrays out: run1

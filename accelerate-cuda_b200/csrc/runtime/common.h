@@ -110,7 +110,8 @@ struct StreamScratch {
     unsigned *words = nullptr;    /* [0] fold ticket, [1] scan ticket, [2] error word,
                                      [kRowCounterBase..] per-row arrival counters of a split fold */
     unsigned scan_ticket = 0;     /* host mirror of words[1] */
-    unsigned epoch = 0;
+    unsigned epoch = 0;           /* scan launches so far (below 2^29) */
+    unsigned graph_epoch = 0;     /* scan launches recorded inside stream captures (offset by 2^29) */
 };
 
 struct CudaAllocator : DeviceAllocator {
@@ -137,6 +138,7 @@ struct accb_context {
     size_t l2_flush_bytes = 0;
     unsigned long long launches = 0;
     std::set<CUfunction> carveout_set; /* entries already told to prefer shared memory over L1 */
+    std::map<std::tuple<CUfunction, int, size_t>, int> occupancy_cache; /* resident blocks per SM */
     size_t mem_hits = 0, disk_hits = 0, compiles = 0;
     bool trace_exec = false, trace_gc = false, trace_cc = false;
 };

@@ -23,11 +23,20 @@
 namespace accb_rt {
 
 int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blocks_per_sm) {
+    /* asked on every launch: remember the answer per (entry point, block size, dynamic shared memory), as
+     * the reference keeps the occupancy with each compiled kernel (CUDA/AST.hs:51-59) */
+    const auto key = std::make_tuple(fn, block, smem);
+    auto it = ctx->occupancy_cache.find(key);
+    if (it != ctx->occupancy_cache.end()) {
+        *blocks_per_sm = it->second;
+        return ACCB_OK;
+    }
     int n = 0;
     int st = check_cu(ctx, driver().OccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, block, smem),
                       "cuOccupancyMaxActiveBlocksPerMultiprocessor");
     if (st != ACCB_OK) return st;
     *blocks_per_sm = std::max(1, n);
+    ctx->occupancy_cache[key] = *blocks_per_sm;
     return ACCB_OK;
 }
 
@@ -411,17 +420,29 @@ int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_
     if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
     const size_t need = (size_t)std::max(1LL, ntiles) * rec;
     const bool regrow = sc->status_bytes < need;
-    TRY(grow(ctx, &sc->status, &sc->status_bytes, need, s, true));
-    if (!regrow && (sc->status_layout != rec || sc->epoch >= (1u << 30) - 2)) {
-        /* another record layout or an exhausted epoch counter: old words could alias new flags */
-        TRY(check_cuda(ctx, cudaMemsetAsync(sc->status, 0, sc->status_bytes, s), "cudaMemsetAsync"));
-        if (sc->epoch >= (1u << 30) - 2) sc->epoch = 0;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(s, &cap);
+    unsigned epoch;
+    if (cap == cudaStreamCaptureStatusActive) {
+        /* Inside a stream capture the launch will be replayed with the epoch recorded now, so every replay
+         * clears the status words it uses first (a memset node), and takes its epoch from a range of
+         * its own (2^29 ..) that launches outside captures never reach. */
+        if (regrow) return fail(ctx, ACCB_EINVAL, "scan scratch must be sized by a run before the stream capture");
+        TRY(check_cuda(ctx, cudaMemsetAsync(sc->status, 0, need, s), "cudaMemsetAsync"));
+        epoch = (1u << 29) + (sc->graph_epoch++ & ((1u << 29) - 1u));
+    } else {
+        TRY(grow(ctx, &sc->status, &sc->status_bytes, need, s, true));
+        if (!regrow && (sc->status_layout != rec || sc->epoch >= (1u << 29) - 2)) {
+            /* another record layout or an exhausted epoch counter: old words could alias new flags */
+            TRY(check_cuda(ctx, cudaMemsetAsync(sc->status, 0, sc->status_bytes, s), "cudaMemsetAsync"));
+            if (sc->epoch >= (1u << 29) - 2) sc->epoch = 0;
+        }
+        sc->status_layout = rec;
+        epoch = ++sc->epoch;
     }
-    sc->status_layout = rec;
-    sc->epoch++;
     p.ip[0] = ntiles;
     p.ip[1] = sc->scan_ticket;
-    p.ip[2] = sc->epoch;
+    p.ip[2] = epoch;
     p.aux[0] = sc->status;
     p.aux[1] = sc->words + 1;
     p.aux[2] = sc->words + 2;

@@ -64,6 +64,10 @@ struct accb_program {
     cudaStream_t pipe_stream[3] = {nullptr, nullptr, nullptr}; /* upload, compute, download */
     std::vector<cudaEvent_t> pipe_events;
     int status = ACCB_OK;
+    /* the op list recorded as a CUDA graph for one set of input arrays on one stream */
+    cudaGraphExec_t graph_exec = nullptr;
+    cudaStream_t graph_stream = nullptr;
+    std::vector<accb_array> graph_inputs, graph_outputs;
 };
 
 namespace {
@@ -558,12 +562,62 @@ int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array
     return ACCB_OK;
 }
 
+/* Run the op list as ONE CUDA graph launch.  The first call for a given set of input arrays (pointers and
+ * shapes) on a given stream runs the program once the ordinary way -- which sizes every intermediate and
+ * scratch buffer and loads every kernel --, records a second run with stream capture and instantiates the
+ * graph; later calls with the same arrays replay it, whatever the arrays now contain.  The outputs are the
+ * program's pooled result arrays, as for accb_program_run.  Replaces the per-node launch loop of
+ * executeOpenAcc (CUDA/Execute.hs:164-219) for programs that are applied again and again to arrays in place. */
+int accb_program_run_graph(accb_program *p, accb_stream stream, const accb_array *inputs, accb_array *outputs) {
+    PLOCK(p);
+    if ((p->ninputs && !inputs) || !outputs || p->outputs.empty()) return fail(p->ctx, ACCB_EINVAL, "bad argument");
+    accb_context *ctx = p->ctx;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!s) return fail(ctx, ACCB_EINVAL, "graph runs need a stream of their own (the default stream cannot be captured)");
+    bool same = p->graph_exec && p->graph_stream == s && (int)p->graph_inputs.size() == p->ninputs;
+    for (int i = 0; same && i < p->ninputs; ++i) {
+        const accb_array &a = p->graph_inputs[i], &b = inputs[i];
+        same = a.rank == b.rank && a.ncomp == b.ncomp;
+        for (int d = 0; same && d < a.rank; ++d) same = a.shape[d] == b.shape[d];
+        for (int c = 0; same && c < a.ncomp; ++c) same = a.ptr[c] == b.ptr[c];
+    }
+    if (!same) {
+        if (p->graph_exec) {
+            cudaGraphExecDestroy(p->graph_exec);
+            p->graph_exec = nullptr;
+        }
+        std::vector<accb_array> outs(p->outputs.size());
+        TRY(run_internal(p, s, inputs, outs.data(), false));
+        TRY(check_cuda(ctx, cudaStreamSynchronize(s), "cudaStreamSynchronize"));
+        TRY(check_cuda(ctx, cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed), "cudaStreamBeginCapture"));
+        const int st = run_internal(p, s, inputs, outs.data(), false);
+        cudaGraph_t g = nullptr;
+        const cudaError_t ce = cudaStreamEndCapture(s, &g);
+        if (st != ACCB_OK) {
+            if (g) cudaGraphDestroy(g);
+            return st;
+        }
+        TRY(check_cuda(ctx, ce, "cudaStreamEndCapture"));
+        const cudaError_t ci = cudaGraphInstantiate(&p->graph_exec, g, 0);
+        cudaGraphDestroy(g);
+        if (ci != cudaSuccess) p->graph_exec = nullptr;
+        TRY(check_cuda(ctx, ci, "cudaGraphInstantiate"));
+        p->graph_stream = s;
+        p->graph_inputs.assign(inputs, inputs + p->ninputs);
+        p->graph_outputs = outs;
+    }
+    TRY(check_cuda(ctx, cudaGraphLaunch(p->graph_exec, s), "cudaGraphLaunch"));
+    for (size_t j = 0; j < p->graph_outputs.size(); ++j) outputs[j] = p->graph_outputs[j];
+    return ACCB_OK;
+}
+
 int accb_program_destroy(accb_program *p) {
     if (!p) return ACCB_OK;
     {
         std::lock_guard<std::recursive_mutex> lock_(p->ctx->mu);
         CtxGuard g(p->ctx);
         cudaDeviceSynchronize();
+        if (p->graph_exec) cudaGraphExecDestroy(p->graph_exec);
         for (auto &v : p->pool)
             for (auto &b : v)
                 if (b.ptr) cudaFree(b.ptr);

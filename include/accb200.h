@@ -304,6 +304,13 @@ ACCB_API int accb_program_outputs(accb_program *p, const int *ids, int nout);
 /* run with DEVICE arrays (what runProgram does) */
 ACCB_API int accb_program_run(accb_program *p, accb_stream stream, const accb_array *inputs,
                               accb_array *outputs);
+/* The same as ONE CUDA graph launch: the first call for a set of input arrays (pointers and shapes) on a
+ * stream runs the program once, records a second run by stream capture and instantiates the graph; later
+ * calls with the same arrays replay it on whatever the arrays then contain.  `stream` must not be the default
+ * stream.  No counterpart in the reference, whose executeOpenAcc launches node by node
+ * (CUDA/Execute.hs:164-219). */
+ACCB_API int accb_program_run_graph(accb_program *p, accb_stream stream, const accb_array *inputs,
+                                    accb_array *outputs);
 /* run1 with HOST arrays: upload, execute, download (CUDA.hs:307-330,382-389).
  * host_in[i] / host_out[j] point to one host buffer per component. */
 ACCB_API int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array *host_out);

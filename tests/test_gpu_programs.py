@@ -116,3 +116,54 @@ def test_accffi_surface_runProgram_on_device_arrays(accb, P, torch_cuda, oracle,
     L.freeProgram(prog.handle)
     prog.handle = None
     L.accelerateDestroy(h)
+
+
+class _DevView:
+    """A device pointer as something torch.as_tensor understands."""
+
+    def __init__(self, a, typestr):
+        shape = tuple(a.shape[d] for d in reversed(range(a.rank)))
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (int(a.ptr[0]), False), "version": 2}
+
+
+def test_program_as_one_cuda_graph_replays_on_new_contents(accb, ctx, torch_cuda, rng):
+    """accb_program_run_graph: recorded once per set of input arrays, replayed on whatever they contain;
+    the scan inside clears its tile status words in every replay."""
+    import importlib
+    t = torch_cuda
+    A = importlib.import_module("accelerate-cuda_b200.lang")
+    add = lambda a, b: a + b  # noqa: E731
+
+    def prog(v):
+        return (A.scanl1(add, A.map(lambda x: x * 2, v)), A.fold(add, 0, v),
+                A.permute(add, A.fill(64, 0, np.int32), lambda i: v[i] & 63, A.fill(A.shape_of(v), 1, np.int32)))
+    f = A.run1With(ctx, prog, A.vector(np.int32))
+    n = 300001
+    v = t.from_numpy(rng.integers(0, 1000, n).astype(np.int32)).cuda()
+    s = t.cuda.Stream()
+    launches = []
+    for rep in range(4):
+        if rep:
+            v.add_(rep)  # new contents, same array
+        t.cuda.synchronize()
+        before = ctx.launch_count()
+        outs = f.run_device([v], stream=s.cuda_stream, graph=True)
+        s.synchronize()
+        launches.append(ctx.launch_count() - before)
+        h = v.cpu().numpy()
+        got = [t.as_tensor(_DevView(o, "<i4"), device="cuda").cpu().numpy() for o in outs]
+        assert np.array_equal(got[0], np.cumsum(2 * h.astype(np.int64)).astype(np.int32))
+        assert got[1].reshape(-1)[0] == h.sum(dtype=np.int64).astype(np.int32)
+        assert np.array_equal(got[2], np.bincount(h & 63, minlength=64).astype(np.int32))
+    assert launches[0] > 0 and launches[1:] == [0, 0, 0]  # replays issue no launches of their own
+    # another array: recorded again; and the ordinary path still agrees
+    w = t.from_numpy(rng.integers(0, 1000, n).astype(np.int32)).cuda()
+    o1 = f.run_device([w], stream=s.cuda_stream, graph=True)
+    s.synchronize()
+    a = t.as_tensor(_DevView(o1[0], "<i4"), device="cuda").clone()
+    o2 = f.run_device([w], stream=s.cuda_stream)
+    s.synchronize()
+    assert t.equal(a, t.as_tensor(_DevView(o2[0], "<i4"), device="cuda"))
+    with pytest.raises(accb.AccbError):
+        f.run_device([w], stream=None, graph=True)  # the default stream cannot be captured
+    f.destroy()
