@@ -610,3 +610,35 @@ def test_device_generators_match_the_host_definition(ctx, torch_cuda, workloads)
     assert np.array_equal(f.cpu().numpy(), W.uniform_f32(W.SEED, W.S_SPOT, n, 5.0, 30.0, first))
     assert np.array_equal(i.cpu().numpy(), W.uniform_i32(W.SEED, W.S_SCAN, n, 16, first))
     assert np.array_equal(k.cpu().numpy(), W.zipf_mix_keys(W.SEED, n, cdf, first))
+
+
+# ------------------------------------------------------------------ maximum sizes
+def test_arrays_of_the_largest_size_the_abi_can_describe(ctx, P, torch_cuda):
+    """Extents are C ints: 2^31 - 2 elements is the largest vector whose scanl result (one longer) still has
+    an Int32 extent.  Positions inside the kernels are 64-bit (the reference's are 32-bit ints,
+    CodeGen/Base.hs:144-145)."""
+    t = torch_cuda
+    if t.cuda.mem_get_info()[0] < 40 << 30:
+        pytest.skip("needs 40 GB of free device memory")
+    n = (1 << 31) - 2
+    x = t.ones(n, dtype=t.int32, device="cuda")
+    x[12345] = 7
+    out = t.empty(n + 1, dtype=t.int32, device="cuda")
+    ctx.scan(P.SCAN_ADD_I32, [x], n, out, seed=np.int32(0))
+    tot = t.zeros(1, dtype=t.int32, device="cuda")
+    ctx.fold_all(P.SUM_I32, [x], n, tot, seed=np.int32(0))
+    ctx.sync()
+    wrapped = np.array((n + 6) & 0xffffffff, np.uint32).astype(np.int32)  # the sum wraps past 2^31
+    assert (int(out[0]), int(out[12345]), int(out[12346]), int(out[-1])) == (0, 12345, 12352, int(wrapped))
+    assert int(tot[0]) == int(wrapped)
+    del out
+    y = t.empty(n, dtype=t.int32, device="cuda")
+    ctx.map(P.IOTA_SQ, [], y)  # o = (int)(i * i + 1) with a 64-bit i
+    ctx.sync()
+    assert (int(y[0]), int(y[3]), int(y[-1])) == (1, 10, int(np.array(((n - 1) ** 2 + 1) & 0xffffffff, np.uint32).astype(np.int32)))
+    del y
+    keys = (t.arange(n, dtype=t.int64, device="cuda") % 4096).int()
+    h, z = t.zeros(4096, dtype=t.int32, device="cuda"), t.zeros(4096, dtype=t.int32, device="cuda")
+    ctx.permute(P.HIST, [keys], n, h, defaults=z)
+    ctx.sync()
+    assert int(h.sum(dtype=t.int64)) == n and int(h[0]) == 524288 and int(h[4095]) == 524287
