@@ -453,7 +453,8 @@ static int run_host_pipelined_scan(accb_program *p, const accb_array *host_in, a
         nd.env.size() != 1 || nd.env[0] != 0 || p->outputs[0] != nd.out_id || host_in[0].rank != 1)
         return 0;
     const long long n = host_in[0].shape[0];
-    const long long chunk = 1LL << 24;
+    long long chunk = 1LL << 23; /* elements per chunk: long enough for the copy engines, short ramps at both ends */
+    if (const char *e = getenv("ACCB_PIPELINE_CHUNK_LOG2")) chunk = 1LL << std::min(28, std::max(16, atoi(e)));
     if (n < 2 * chunk || getenv("ACCB_NO_PIPELINE")) return 0;
     accb_context *ctx = p->ctx;
     const accb_value_type &tin = p->types[0], &tout = p->types[nd.out_id];

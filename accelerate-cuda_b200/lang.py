@@ -461,7 +461,6 @@ class Index:
                 names = [f"ix{b.n}_{d}" for d in range(r)]
                 b.n += 1
                 b.raw("int " + ", ".join(names) + ";")
-                inner = ", ".join(d.code for d in reversed(self.dims[1:]))  # from_indexN takes sh_(N-2) .. sh_0
                 if r == 2:
                     b.raw(f"accb::from_index2({self.dims[1].code}, {self.lin.code}, {names[0]}, {names[1]});")
                 elif r == 3:
@@ -469,7 +468,6 @@ class Index:
                           f"{names[0]}, {names[1]}, {names[2]});")
                 else:
                     raise NotImplementedError("ranks above 3")
-                del inner
                 self._comps = tuple(Exp(I32, n) for n in names)
         return self._comps
 
