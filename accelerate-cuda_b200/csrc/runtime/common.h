@@ -137,6 +137,7 @@ struct accb_context {
     void *l2_flush = nullptr;
     size_t l2_flush_bytes = 0;
     unsigned long long launches = 0;
+    unsigned long long buffer_generation = 0; /* bumped whenever a scratch or pooled buffer is replaced */
     std::set<CUfunction> carveout_set; /* entries already told to prefer shared memory over L1 */
     std::map<std::tuple<CUfunction, int, size_t>, int> occupancy_cache; /* resident blocks per SM */
     size_t mem_hits = 0, disk_hits = 0, compiles = 0;

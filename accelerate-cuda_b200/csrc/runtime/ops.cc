@@ -111,6 +111,7 @@ static int grow(accb_context *ctx, void **buf, size_t *have, size_t want, cudaSt
     /* the old buffer may still be read by work enqueued earlier on this stream */
     int st = check_cuda(ctx, cudaStreamSynchronize(stream), "cudaStreamSynchronize");
     if (st != ACCB_OK) return st;
+    ctx->buffer_generation++; /* recorded graphs that name the old buffer are stale now */
     if (*buf) cudaFree(*buf);
     *buf = nullptr;
     *have = 0;

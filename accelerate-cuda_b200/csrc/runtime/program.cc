@@ -67,6 +67,7 @@ struct accb_program {
     /* the op list recorded as a CUDA graph for one set of input arrays on one stream */
     cudaGraphExec_t graph_exec = nullptr;
     cudaStream_t graph_stream = nullptr;
+    unsigned long long graph_generation = 0; /* the context's buffer_generation when it was recorded */
     std::vector<accb_array> graph_inputs, graph_outputs;
 };
 
@@ -81,6 +82,7 @@ long long size_of(const accb_array &a) {
 int pool_get(accb_program *p, PoolBuf &b, size_t bytes, void **out) {
     bytes = std::max<size_t>(bytes, 16);
     if (b.bytes < bytes) {
+        p->ctx->buffer_generation++; /* a recorded graph of this program names the old buffer */
         if (b.ptr) {
             cudaDeviceSynchronize(); /* earlier runs may still read it */
             cudaFree(b.ptr);
@@ -575,7 +577,9 @@ int accb_program_run_graph(accb_program *p, accb_stream stream, const accb_array
     accb_context *ctx = p->ctx;
     cudaStream_t s = (cudaStream_t)stream;
     if (!s) return fail(ctx, ACCB_EINVAL, "graph runs need a stream of their own (the default stream cannot be captured)");
-    bool same = p->graph_exec && p->graph_stream == s && (int)p->graph_inputs.size() == p->ninputs;
+    /* a scratch or pooled buffer replaced since the recording (by any launch of this context) makes it stale */
+    bool same = p->graph_exec && p->graph_stream == s && (int)p->graph_inputs.size() == p->ninputs &&
+                p->graph_generation == ctx->buffer_generation;
     for (int i = 0; same && i < p->ninputs; ++i) {
         const accb_array &a = p->graph_inputs[i], &b = inputs[i];
         same = a.rank == b.rank && a.ncomp == b.ncomp;
@@ -604,6 +608,7 @@ int accb_program_run_graph(accb_program *p, accb_stream stream, const accb_array
         if (ci != cudaSuccess) p->graph_exec = nullptr;
         TRY(check_cuda(ctx, ci, "cudaGraphInstantiate"));
         p->graph_stream = s;
+        p->graph_generation = ctx->buffer_generation;
         p->graph_inputs.assign(inputs, inputs + p->ninputs);
         p->graph_outputs = outs;
     }

@@ -164,6 +164,14 @@ def test_program_as_one_cuda_graph_replays_on_new_contents(accb, ctx, torch_cuda
     o2 = f.run_device([w], stream=s.cuda_stream)
     s.synchronize()
     assert t.equal(a, t.as_tensor(_DevView(o2[0], "<i4"), device="cuda"))
+    # a larger run replaces the pooled intermediates and the scan scratch the recording names: recorded again
+    big = t.from_numpy(rng.integers(0, 1000, 40 * n).astype(np.int32)).cuda()
+    f.run_device([big], stream=s.cuda_stream)
+    s.synchronize()
+    before = ctx.launch_count()
+    o3 = f.run_device([w], stream=s.cuda_stream, graph=True)
+    s.synchronize()
+    assert ctx.launch_count() > before and t.equal(a, t.as_tensor(_DevView(o3[0], "<i4"), device="cuda"))
     with pytest.raises(accb.AccbError):
         f.run_device([w], stream=None, graph=True)  # the default stream cannot be captured
     f.destroy()
