@@ -136,6 +136,8 @@ def lib() -> C.CDLL:
             "accb_program_permute": [vp, vp, C.POINTER(i32), i32, i32, i32, C.POINTER(accb_value_type)],
             "accb_program_stencil": [vp, vp, i32, i32, vp, sz, i32, C.POINTER(accb_value_type)],
             "accb_program_generate": [vp, vp, C.POINTER(i32), i32, i32, C.POINTER(i32), C.POINTER(accb_value_type), vp, sz],
+            "accb_program_generate_dims": [vp, vp, C.POINTER(i32), i32, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32),
+                                           C.POINTER(accb_value_type), vp, sz],
             "accb_program_fold_seg": [vp, vp, C.POINTER(i32), i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
             "accb_program_stencil2": [vp, vp, i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
             "accb_program_outputs": [vp, C.POINTER(i32), i32],
@@ -590,6 +592,24 @@ def generate(prog: Afun, spec: KernelSpec, env: Sequence[Acc], shape, out_type: 
     r = prog._new(vid, out_type)
     r.shape_fn = lambda s: shape
     return r
+
+
+def generate_dims(prog: Afun, spec: KernelSpec, env: Sequence[Acc], dims, out_type: ArrayType, scalars=None) -> Acc:
+    """generate node whose shape is computed when the program runs.  dims lists, outermost first, one
+    (source, dim, add) per extent: ``add`` plus -- when source is an Acc -- extent ``dim`` (outermost first) of it."""
+    dims = [(s, int(d), int(a)) for s, d, a in dims]
+    ids, n = prog._ids(env)
+    sb, sn = _bytes_of(scalars)
+    t = out_type.ctype()
+    r = len(dims)
+    inner = list(reversed(dims))  # the C side counts extents innermost first
+    src = (C.c_int * max(1, r))(*[(s.id if s is not None else -1) for s, _, _ in inner])
+    sdim = (C.c_int * max(1, r))(*[((s.type.rank - 1 - d) if s is not None else 0) for s, d, _ in inner])
+    add = (C.c_int * max(1, r))(*[a for _, _, a in inner])
+    vid = lib().accb_program_generate_dims(prog.handle, prog.ctx._k(spec), ids, n, r, src, sdim, add, C.byref(t), sb, sn)
+    node = prog._new(vid, out_type)
+    node.shape_fn = lambda s: tuple((src_.shape_fn(s)[d] if src_ is not None else 0) + a for src_, d, a in dims)
+    return node
 
 
 def fold_seg(spec: KernelSpec, env: Sequence[Acc], offsets: Acc, out_dtypes, seed=None, shape_like: Acc = None) -> Acc:

@@ -31,9 +31,11 @@ struct Node {
     NodeKind kind;
     accb_kernel *k = nullptr;
     std::vector<int> env;
-    int shape_like = 0;   /* value whose shape the result takes; -1: the literal shape below (generate) */
+    int shape_like = 0;   /* value whose shape the result takes; -1: the shape described below (generate) */
     int lit_rank = 0;
-    int lit_shape[ACCB_MAX_RANK] = {0};
+    int lit_shape[ACCB_MAX_RANK] = {0};           /* extent d = lit_shape[d] ... */
+    int dim_src[ACCB_MAX_RANK] = {-1, -1, -1, -1}; /* ... + extent dim_of[d] of value dim_src[d], if >= 0 */
+    int dim_of[ACCB_MAX_RANK] = {0};
     int offsets_id = -1;  /* foldSeg: Int32 vector of segment offsets, length segments + 1 */
     int all = 0;          /* fold: reduce everything */
     int direction = 0, scan_kind = 0;
@@ -137,7 +139,16 @@ int run_internal(accb_program *p, cudaStream_t s, const accb_array *inputs, accb
         accb_array literal;
         memset(&literal, 0, sizeof literal);
         literal.rank = nd.lit_rank;
-        memcpy(literal.shape, nd.lit_shape, sizeof nd.lit_shape);
+        for (int d = 0; d < nd.lit_rank && nd.shape_like < 0; ++d) {
+            long long e = nd.lit_shape[d];
+            if (nd.dim_src[d] >= 0) {
+                const accb_array &src = val[nd.dim_src[d]];
+                if (nd.dim_of[d] >= src.rank) return fail(ctx, ACCB_EINVAL, "shape refers to a dimension its source lacks");
+                e += src.shape[nd.dim_of[d]];
+            }
+            if (e < 0 || e > 0x7fffffffLL) return fail(ctx, ACCB_EBOUNDS, "computed extent %lld is out of range", e);
+            literal.shape[d] = (int)e;
+        }
         const accb_array &like = nd.shape_like >= 0 ? val[nd.shape_like] : literal;
         accb_array out;
         memset(&out, 0, sizeof out);
@@ -392,6 +403,31 @@ int accb_program_generate(accb_program *p, accb_kernel *k, const int *env_ids, i
     for (int d = 0; d < rank; ++d) {
         if (shape[d] < 0) return -fail(p->ctx, ACCB_EINVAL, "negative extent");
         nd.lit_shape[d] = shape[d];
+    }
+    if (scalars) nd.scalars.assign((const unsigned char *)scalars, (const unsigned char *)scalars + scalar_bytes);
+    return add_node(p, nd, out_type, 1);
+}
+
+/* generate whose extents are taken from other values: extent d (innermost first) of the result is
+ * add[d], plus extent src_dim[d] of value src_value[d] when src_value[d] >= 0 */
+int accb_program_generate_dims(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,
+                               const int *src_value, const int *src_dim, const int *add,
+                               const accb_value_type *out_type, const void *scalars, size_t scalar_bytes) {
+    if (!p || !k) return -ACCB_EINVAL;
+    if (rank < 0 || rank > ACCB_ARRAY_MAX_RANK || (rank > 0 && (!src_value || !src_dim || !add)))
+        return -fail(p->ctx, ACCB_EINVAL, "bad shape description");
+    Node nd;
+    nd.kind = N_MAP;
+    nd.k = k;
+    if (nenv > 0) nd.env.assign(env_ids, env_ids + nenv);
+    nd.shape_like = -1;
+    nd.lit_rank = rank;
+    for (int d = 0; d < rank; ++d) {
+        if (src_value[d] >= (int)p->types.size() || (src_value[d] >= 0 && (src_dim[d] < 0 || src_dim[d] >= ACCB_ARRAY_MAX_RANK)))
+            return -fail(p->ctx, ACCB_EINVAL, "shape refers to an unknown value or dimension");
+        nd.dim_src[d] = src_value[d] < 0 ? -1 : src_value[d];
+        nd.dim_of[d] = src_dim[d];
+        nd.lit_shape[d] = add[d];
     }
     if (scalars) nd.scalars.assign((const unsigned char *)scalars, (const unsigned char *)scalars + scalar_bytes);
     return add_node(p, nd, out_type, 1);

@@ -78,6 +78,9 @@ class _DryBackend:
     def generate(self, prog, spec, env, shape, out_type, scalars=None):
         return self._add(prog, spec, out_type)
 
+    def generate_dims(self, prog, spec, env, dims, out_type, scalars=None):
+        return self._add(prog, spec, out_type)
+
     def map_(self, spec, env, out_type, shape_like=None, scalars=None):
         return self._add(env[0].prog, spec, out_type)
 
@@ -536,7 +539,8 @@ class _KernelEnv:
             t = (idx,) if isinstance(idx, Exp) else (tuple(idx) if isinstance(idx, (tuple, list)) else None)
             if t is not None and len(t) == len(ki._comps) and all(a is b for a, b in _zip(t, ki._comps)):
                 idx = ki
-        if isinstance(idx, Index) and idx is ki and self.extent.same_as(arr.extent):
+        if isinstance(idx, Index) and ki is not None and idx.lin is ki.lin and (
+                (idx is ki and self.extent.same_as(arr.extent)) or getattr(idx, "same_position", False)):
             if not any(a is arr for a in self.elem):
                 self.elem.append(arr)
             return tuple(Exp(dt, f"@IN{arr.node.id}_{c}@") for c, dt in enumerate(arr.dtypes))
@@ -582,36 +586,73 @@ class _KernelEnv:
         return [a.node for a in self.elem + self.gath]
 
 
-class _Extent:
-    """The shape of an array as far as it is known while tracing: that of a manifest array, or literal."""
+class _Dim:
+    """One extent of a shape: a constant, plus -- when src is given -- extent `dim` (outermost first) of a
+    manifest array.  What Accelerate writes as an Exp Int inside a shape."""
 
-    def __init__(self, like: "Array" = None, literal: Tuple[int, ...] = None):
-        self.like, self.literal = like, literal
+    def __init__(self, src: "Array" = None, dim: int = 0, add: int = 0):
+        self.src, self.dim, self.add = src, dim, int(add)
+
+    def key(self):
+        return ("lit", self.add) if self.src is None else ("arr", self.src.prog_find(self.src.node.id), self.dim, self.add)
+
+    def code(self, kenv: "_KernelEnv") -> Exp:
+        if self.src is None:
+            return constant(self.add, I32)
+        e = kenv.dims_of(self.src)[self.dim]
+        return e if self.add == 0 else Exp(I32, f"({e.code} + {_literal(self.add, I32)})")
+
+    def value(self, s) -> int:
+        return self.add if self.src is None else self.src.node.shape_fn(s)[self.dim] + self.add
+
+    def __add__(self, n: int) -> "_Dim":
+        return _Dim(self.src, self.dim, self.add + int(n))
+
+    def __sub__(self, n: int) -> "_Dim":
+        return _Dim(self.src, self.dim, self.add - int(n))
+
+
+class _Extent:
+    """The shape of an array as far as it is known while tracing: that of a manifest array (`like`), a tuple of
+    constants (`literal`), or extent by extent (`parts`) from constants and the extents of manifest arrays."""
+
+    def __init__(self, like: "Array" = None, literal: Tuple[int, ...] = None, parts: Sequence[_Dim] = None):
+        if parts is not None:
+            parts = list(parts)
+            if all(p.src is None for p in parts):
+                literal, parts = tuple(p.add for p in parts), None
+            elif (parts[0].src is not None and len(parts) == parts[0].src.rank
+                  and all(p.src is parts[0].src and p.dim == d and p.add == 0 for d, p in enumerate(parts))):
+                like, parts = parts[0].src, None
+        self.like, self.literal, self.parts = like, literal, parts
 
     @property
     def rank(self):
+        if self.parts is not None:
+            return len(self.parts)
         return len(self.literal) if self.literal is not None else self.like.rank
 
+    def part(self, d: int) -> _Dim:
+        if self.parts is not None:
+            return self.parts[d]
+        return _Dim(None, 0, self.literal[d]) if self.literal is not None else _Dim(self.like, d, 0)
+
     def key(self):
-        return ("lit", self.literal) if self.literal is not None else ("arr", self.like.prog_find(self.like.node.id))
+        return tuple(self.part(d).key() for d in range(self.rank))
 
     def same_as(self, other: "_Extent") -> bool:
         return self.key() == other.key()
 
     def dims(self, kenv: _KernelEnv, own_out: bool) -> List[Exp]:
         """Extents as expressions inside a kernel whose iteration space this is."""
-        if self.literal is not None:
-            return [constant(e, I32) for e in self.literal]
-        if own_out:  # a map writes an array of exactly this shape
-            r = self.rank
+        r = self.rank
+        if own_out and self.literal is None:  # a map writes an array of exactly this shape
             return [Exp(I32, f"env.out_dim({r - 1 - d})") for d in range(r)]
-        return kenv.dims_of(self.like)
+        return [self.part(d).code(kenv) for d in range(r)]
 
     def shape_fn(self):
-        if self.literal is not None:
-            lit = self.literal
-            return lambda s: lit
-        return self.like.node.shape_fn
+        parts = [self.part(d) for d in range(self.rank)]
+        return lambda s: tuple(p.value(s) for p in parts)
 
 
 def _unify(prog, a: _Extent, b: _Extent) -> _Extent:
@@ -621,11 +662,10 @@ def _unify(prog, a: _Extent, b: _Extent) -> _Extent:
     if a.rank != b.rank:
         raise TypeError(f"arrays of rank {a.rank} and {b.rank} zipped")
     prog._shape_checks.append((a.shape_fn(), b.shape_fn()))
-    if a.literal is None and b.literal is None:
+    if a.like is not None and b.like is not None:
         ra, rb = a.like.prog_find(a.like.node.id), b.like.prog_find(b.like.node.id)
         prog._same[rb] = ra
-        return a
-    return a if a.literal is None else b
+    return a if (a.like is not None or b.like is None) else b
 
 
 # ------------------------------------------------------------------ arrays
@@ -726,10 +766,14 @@ def generate(shape, f: Callable, prog=None) -> Array:
     """``generate sh f``: shape is a tuple of ints (outermost first) or ``shape_of(arr)``."""
     if isinstance(shape, _ShapeOf):
         ext, prog = shape.arr.extent, shape.arr.prog
+    elif isinstance(shape, _Extent):
+        ext = shape
+        prog = prog or next((ext.part(d).src.prog for d in range(ext.rank) if ext.part(d).src is not None), None) or _tracing[-1]
     else:
-        shape = (int(shape),) if isinstance(shape, (int, np.integer)) else tuple(int(e) for e in shape)
-        ext = _Extent(literal=shape)
-        prog = prog or _tracing[-1]
+        shape = (shape,) if isinstance(shape, (int, np.integer, _Dim)) else tuple(shape)
+        parts = [e if isinstance(e, _Dim) else _Dim(None, 0, int(e)) for e in shape]
+        ext = _Extent(parts=parts)
+        prog = prog or next((p.src.prog for p in parts if p.src is not None), None) or _tracing[-1]
     with _probe(prog) as pr:
         out = _flat(f(pr.index(ext.rank)))
     return Array(prog, [e.dt for e in out], ext, fn=lambda kenv, ix: f(_user_index(ix)))
@@ -743,6 +787,99 @@ def backpermute(shape, perm: Callable, arr: Array) -> Array:
     """``backpermute sh p arr``: element ix of the result is ``arr ! p ix`` (a gather)."""
     arr = _as_array(arr)
     return generate(shape, lambda ix: arr[perm(ix)], prog=arr.prog)
+
+
+def _comps(u) -> Tuple[Exp, ...]:
+    """The components of what an index function receives (one Exp for vectors, an Index otherwise)."""
+    return (u,) if isinstance(u, Exp) else tuple(u)
+
+
+def dim(arr: Array, d: int) -> _Dim:
+    """Extent d (outermost first, negative from the end) of an array, for use in the shape of a ``generate``,
+    ``backpermute``, ``replicate`` or ``reshape``; ``dim(a, 0) - 1`` and ``dim(a, 1) + 2`` are shapes too."""
+    arr = _as_array(arr)
+    return arr.extent.part(d % arr.rank)
+
+
+def replicate(arr: Array, extent, axis: int = 0) -> Array:
+    """``replicate``: a new dimension at position ``axis`` (outermost = 0) of the given extent (an int or a
+    ``dim`` of another array) along which the array is repeated."""
+    arr = _as_array(arr)
+    parts = [arr.extent.part(d) for d in range(arr.rank)]
+    parts.insert(axis, extent if isinstance(extent, _Dim) else _Dim(None, 0, int(extent)))
+
+    def f(u):
+        c = list(_comps(u))
+        del c[axis]
+        return arr[tuple(c) if len(c) != 1 else c[0]]
+    return generate(_Extent(parts=parts), f, prog=arr.prog)
+
+
+def slice(arr: Array, axis: int, index) -> Array:  # noqa: A001
+    """``slice``: the sub-array at a fixed position of one dimension; index is an int or a function of no arguments
+    that returns an Exp (e.g. ``lambda: the(k)``)."""
+    arr = _as_array(arr)
+    parts = [arr.extent.part(d) for d in range(arr.rank) if d != axis]
+
+    def f(u):
+        c = list(_comps(u)) if parts else []
+        at = index() if callable(index) else constant(index, I32)
+        c.insert(axis, at)
+        return arr[tuple(c) if len(c) != 1 else c[0]]
+    return generate(_Extent(parts=parts) if parts else (), f, prog=arr.prog)
+
+
+def transpose(m: Array) -> Array:
+    m = _as_array(m)
+    if m.rank != 2:
+        raise TypeError("transpose of a matrix")
+    return generate(_Extent(parts=[m.extent.part(1), m.extent.part(0)]), lambda u: m[(u[1], u[0])], prog=m.prog)
+
+
+def reshape(shape, arr: Array) -> Array:
+    """``reshape``: the same elements in row-major order under another shape of the same size."""
+    arr = _as_array(arr)
+    new = generate(shape, lambda u: constant(0, I32), prog=arr.prog).extent  # only its extent is wanted
+    prog = arr.prog
+    size = lambda fn: (lambda s: (int(np.prod(fn(s), dtype=np.int64)),))  # noqa: E731
+    prog._shape_checks.append((size(new.shape_fn()), size(arr.extent.shape_fn())))
+
+    def fn(kenv, ix):
+        same = Index(ix.lin, arr.extent.dims(kenv, False))
+        same.same_position = True  # the element with the same row-major position
+        return _unflat1(arr.at(kenv, same))
+    return Array(prog, arr.dtypes, new, fn=fn)
+
+
+def reverse(v: Array) -> Array:
+    v = _as_array(v)
+    return generate(shape_of(v), lambda i: v[shape(v)[0] - 1 - i])
+
+
+def init(v: Array) -> Array:
+    v = _as_array(v)
+    return generate((dim(v, 0) - 1,), lambda i: v[i])
+
+
+def tail(v: Array) -> Array:
+    v = _as_array(v)
+    return generate((dim(v, 0) - 1,), lambda i: v[i + 1])
+
+
+def take(n: int, v: Array) -> Array:
+    """The first n elements (n a constant not larger than the length)."""
+    v = _as_array(v)
+    return generate((int(n),), lambda i: v[i], prog=v.prog)
+
+
+def drop(n: int, v: Array) -> Array:
+    v = _as_array(v)
+    return generate((dim(v, 0) - int(n),), lambda i: v[i + int(n)])
+
+
+def enumFromN(n, start, dtype=np.int32) -> Array:
+    """The vector start, start + 1, ... of n elements (n an int or a ``dim``)."""
+    return generate((n,), lambda i: cast(i, dtype) + start)
 
 
 class _ShapeOf:
@@ -931,10 +1068,14 @@ def compute(arr: Array) -> Array:
     env_nodes = kenv.nodes()
     if arr.extent.literal is not None:
         node = _be().generate(prog, spec, env_nodes, arr.extent.literal, out_type)
-    else:
+    elif arr.extent.like is not None:
         like = arr.extent.like.node
         node = _be().map_(spec, env_nodes or [like], out_type, shape_like=like)
-    return Array(prog, arr.dtypes, node=node)
+    else:  # extents taken one by one from other arrays: the host computes the shape when the program runs
+        parts = [arr.extent.part(d) for d in range(arr.rank)]
+        node = _be().generate_dims(prog, spec, env_nodes, [(p.src.node if p.src is not None else None, p.dim, p.add)
+                                                          for p in parts], out_type)
+    return _same_shape(Array(prog, arr.dtypes, node=node), arr)
 
 
 def _fold_source(kind: str, f, seed, arr: Array, base: str):
@@ -1003,7 +1144,7 @@ def fold1All(f: Callable, arr: Array) -> Array:
 
 def _fold(f, seed, arr: Array, all_: bool) -> Array:
     whole = all_ or arr.rank <= 1
-    if arr.extent.literal is not None and not arr.manifest:
+    if arr.extent.like is None and not arr.manifest:
         arr = compute(arr)  # the row structure of a generated array comes from a manifest shape
     spec, kenv = _fold_source("FoldAll" if whole else "FoldDim", f, seed, arr, "Fold")
     nodes, like = _env_or_like(kenv, arr)
@@ -1018,7 +1159,7 @@ def foldSeg(f: Callable, seed, arr: Array, segments: Array) -> Array:
     if segments.dtypes != [I32]:
         raise TypeError("segment lengths are Int32")
     offsets = scanl(lambda a, b: a + b, 0, segments)
-    if arr.extent.literal is not None and not arr.manifest:
+    if arr.extent.like is None and not arr.manifest:
         arr = compute(arr)
     spec, kenv = _fold_source("FoldSeg", f, seed, arr, "Fold")
     nodes, like = _env_or_like(kenv, arr)
@@ -1033,7 +1174,7 @@ def fold1Seg(f: Callable, arr: Array, segments: Array) -> Array:
 def _same_shape(new: Array, old: Array) -> Array:
     """The manifest array `new` has the shape of `old` by construction: reads of it at the index of a kernel that
     iterates over `old` are element-wise."""
-    if old.extent.literal is None:
+    if old.extent.like is not None and old.extent.like.node is not new.node:
         new.prog._same[new.node.id] = old.prog_find(old.extent.like.node.id)
     return new
 
@@ -1043,7 +1184,7 @@ def _segmented_scan(f: Callable, arr: Array, flag_of: Callable, direction) -> Ar
     first element of a row or segment for a left scan, at the last one for a right scan.  The value type is
     widened to (value, flag) with the usual segmented operator, which is associative whenever f is; only the
     value components are written."""
-    if arr.extent.literal is not None and not arr.manifest:
+    if arr.extent.like is None and not arr.manifest:
         arr = compute(arr)
     prog, right = arr.prog, direction == _pkg.SCAN_RIGHT
     kenv = _KernelEnv(prog, arr.extent)
@@ -1128,15 +1269,30 @@ def _scan(f, seed, arr: Array, direction, kind):
     if arr.rank != 1:
         # Along the innermost dimension of a matrix or cube (the reference rejects these, PrefixSum.hs:39-46):
         # an inclusive scan of the whole array that restarts at the start (end, for right scans) of every row.
-        if kind != _pkg.SCAN_INCLUSIVE:
-            raise NotImplementedError("scanl1 / scanr1 are defined along the innermost dimension; the seeded forms on vectors")
         right = direction == _pkg.SCAN_RIGHT
+        if kind == _pkg.SCAN_PRIME:
+            raise NotImplementedError("scanl' / scanr' along the innermost dimension: use scanl / scanr and slice the totals off")
+        if kind == _pkg.SCAN_EXCLUSIVE:
+            # every row grows by one element: the seed goes first (last, for scanr) and the inclusive scan of
+            # the widened rows is the exclusive scan of the original ones
+            zs = _seed_value(seed, arr.dtypes)
+            src, r = arr, arr.rank
+            parts = [src.extent.part(d) for d in range(r - 1)] + [src.extent.part(r - 1) + 1]
+
+            def widened(u):
+                c = list(_comps(u))
+                x, cols = c[-1], shape(src)[-1]
+                at_seed = (x == cols) if right else (x == 0)
+                inside = minimum(x, cols - 1) if right else maximum(x - 1, 0)
+                vals = _flat(src[tuple(c[:-1] + [inside])])
+                return _unflat1(tuple(cond(at_seed, constant(z, dt), v) for z, dt, v in _zip(zs, src.dtypes, vals)))
+            arr = generate(_Extent(parts=parts), widened, prog=src.prog)
 
         def row_edge(kenv, ix):
             x = ix.comps()[-1]
             return (x == ix.dims[-1] - 1) if right else (x == 0)
         return _segmented_scan(f, arr, row_edge, direction)
-    if arr.extent.literal is not None and not arr.manifest:
+    if arr.extent.like is None and not arr.manifest:
         arr = compute(arr)
     spec, kenv = _fold_source("Scan", f, seed, arr, "Scan")
     nodes, like = _env_or_like(kenv, arr)
@@ -1155,17 +1311,13 @@ def scanl_(f, seed, arr): return _scan(f, seed, arr, _pkg.SCAN_LEFT, _pkg.SCAN_P
 def scanr_(f, seed, arr): return _scan(f, seed, arr, _pkg.SCAN_RIGHT, _pkg.SCAN_PRIME)   # scanr'
 
 
-_IDENTITY = {"+": lambda dt: 0, "|": lambda dt: 0, "^": lambda dt: 0,
-             "&": lambda dt: np.iinfo(dt).max if dt.kind == "u" else -1}
-
-
 def permute(f: Callable, defaults: Array, perm: Callable, arr: Array) -> Array:
     """``permute f defaults p arr``: out[p ix] = f (arr ! ix) (out ! p ix); ``p`` may return ``ignore``."""
     defaults, arr = compute(_as_array(defaults)), _as_array(arr)
     if defaults.dtypes != arr.dtypes:
         raise TypeError("defaults and source differ in element type")
     prog = arr.prog
-    if arr.extent.literal is not None and not arr.manifest:
+    if arr.extent.like is None and not arr.manifest:
         arr = compute(arr)
     kenv = _KernelEnv(prog, arr.extent)
     gbody, gvals = _producer_body(arr, kenv, own_out=False)

@@ -292,6 +292,12 @@ ACCB_API int accb_program_stencil(accb_program *p, accb_kernel *k, int src_id, i
 ACCB_API int accb_program_generate(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,
                                    const int *shape, const accb_value_type *out_type, const void *scalars,
                                    size_t scalar_bytes);
+/* generate whose shape is computed from other values when the program runs: extent d (innermost first) is
+ * add[d], plus extent src_dim[d] of value src_value[d] where src_value[d] >= 0.  What the reference gets by
+ * evaluating the shape expression of a Generate / Backpermute on the host (executeOpenAcc, CUDA/Execute.hs:194-199). */
+ACCB_API int accb_program_generate_dims(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,
+                                        const int *src_value, const int *src_dim, const int *add,
+                                        const accb_value_type *out_type, const void *scalars, size_t scalar_bytes);
 /* foldSeg / fold1Seg: offsets_id names an Int32 vector of segments + 1 offsets, the exclusive scan of the
  * segment lengths (foldSegOp, CUDA/Execute.hs:320-324); the innermost extent of the result is the segment count */
 ACCB_API int accb_program_fold_seg(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like,

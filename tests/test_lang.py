@@ -132,6 +132,23 @@ def test_row_scans_and_segmented_scans_are_scans_of_value_flag_pairs():
     assert "accb::Atomic::None" in seg[2].source and "using In = accb::types<float, unsigned char>;" in seg[3].source
 
 
+def mvm(mat, vec):
+    """matrix x vector the Accelerate way: replicate the vector over the rows, zip, fold the rows"""
+    return A.fold(add, 0.0, A.zipWith(lambda a, b: a * b, mat, A.replicate(vec, A.dim(mat, 0), axis=0)))
+
+
+def test_shapes_computed_from_other_arrays():
+    specs = A.specs(mvm, A.matrix(f32), A.vector(f32))
+    assert [s.skeleton for s in specs] == ["fold_dim"]  # replicate is fused: the matrix element-wise, the vector gathered
+    assert "using In = accb::types<float>;" in specs[0].source and "env.in<float>(1)" in specs[0].source
+    t = A.specs(lambda m: A.transpose(m), A.matrix(i32))
+    assert [s.skeleton for s in t] == ["map"] and "env.out_dim(" in t[0].source
+    r = A.specs(lambda m: A.map(lambda x: x + 1, A.reshape((A.dim(m, 1), A.dim(m, 0)), m)), A.matrix(i32))
+    assert "using In = accb::types<int>;" in r[0].source  # same row-major position: still element-wise
+    ex = A.specs(lambda m: A.scanl(add, 0, m), A.matrix(i32))
+    assert [s.skeleton for s in ex] == ["map", "scan"]  # rows widened by the seed, then the row scan
+
+
 def test_everything_printed_compiles_for_sm_100a(accb):
     """nvcc -arch=sm_100a on a sample of generated functors (no device needed)."""
     import os
@@ -147,6 +164,9 @@ def test_everything_printed_compiles_for_sm_100a(accb):
         (lambda ab: A.scanl1(lambda f, g: (g[0] * f[0], g[0] * f[1] + g[1]), ab), [A.vector(u32, u32)]),
         (lambda x: A.map(lambda a: (a // 3, a % 3, A.cast(a, i64) * 5, A.cast(a, f64) / 3.0, a > 2), x), [A.vector(i32)]),
         (lambda m: A.scanr1(add, m), [A.matrix(f32)]),
+        (mvm, [A.matrix(f32), A.vector(f32)]), (lambda m: A.scanr(A.maximum, 0, m), [A.matrix(i32)]),
+        (lambda m: (A.transpose(m), A.slice(m, 0, 2), A.reshape((A.dim(m, 1), A.dim(m, 0)), m)), [A.matrix(i32)]),
+        (lambda v: (A.reverse(v), A.init(v), A.tail(v), A.take(3, v), A.drop(2, v), A.enumFromN(A.dim(v, 0), 5)), [A.vector(i32)]),
         (lambda v, lens: A.scanl1Seg(add, v, lens), [A.vector(f32), A.vector(i32)]),
         (lambda v, lens: A.scanr1Seg(A.maximum, v, lens), [A.vector(i64), A.vector(i32)]),
         (lambda k, v: A.permute(lambda x, y: (x[0] + y[0], x[1] + y[1]), A.zip(A.fill(64, 0, i32), A.fill(64, 0, i32)),
@@ -231,6 +251,32 @@ def test_scans_along_rows_and_inside_segments(ctx, rng):
         refr[offs[s]:offs[s + 1]] = np.cumsum(seg[::-1])[::-1]
     close(A.runWith(ctx, lambda a, l: A.scanl1Seg(add, a, l), v, lens), refl, 2e-3)  # float32 sums of up to 30000 terms
     close(A.runWith(ctx, lambda a, l: A.scanr1Seg(add, a, l), v, lens), refr, 2e-3)
+
+
+@pytest.mark.gpu
+def test_replicate_slice_reshape_and_friends(ctx, rng):
+    m = rng.uniform(-1, 1, (301, 517)).astype(f32)
+    v = rng.uniform(-1, 1, 517).astype(f32)
+    close(A.runWith(ctx, mvm, m, v), m.astype(f64) @ v.astype(f64), 1e-5)
+    with pytest.raises(ValueError):
+        A.runWith(ctx, mvm, m, v[:-1])
+    mi = rng.integers(-99, 99, (37, 53)).astype(i32)
+    t, row, col, rs = A.runWith(ctx, lambda a: (A.transpose(a), A.slice(a, 0, 5), A.slice(a, 1, 7),
+                                                A.reshape((A.dim(a, 1), A.dim(a, 0)), a)), mi)
+    assert np.array_equal(t, mi.T) and np.array_equal(row, mi[5]) and np.array_equal(col, mi[:, 7])
+    assert np.array_equal(rs, mi.reshape(53, 37))
+    x = rng.integers(-99, 99, 10001).astype(i32)
+    rv, ini, tl, tk, dr, en = A.runWith(ctx, lambda a: (A.reverse(a), A.init(a), A.tail(a), A.take(3, a), A.drop(2, a),
+                                                        A.enumFromN(A.dim(a, 0), 5)), x)
+    assert np.array_equal(rv, x[::-1]) and np.array_equal(ini, x[:-1]) and np.array_equal(tl, x[1:])
+    assert np.array_equal(tk, x[:3]) and np.array_equal(dr, x[2:]) and np.array_equal(en, np.arange(5, 5 + x.size, dtype=i32))
+    rep = A.runWith(ctx, lambda a: A.replicate(a, 4, axis=1), x[:9])
+    assert np.array_equal(rep, np.repeat(x[:9, None], 4, axis=1))
+    # exclusive scans along rows: one element longer per row, seed first (scanl) or last (scanr)
+    ex = A.runWith(ctx, lambda a: A.scanl(add, 10, a), mi)
+    assert np.array_equal(ex, np.concatenate([np.full((37, 1), 10), 10 + np.cumsum(mi, axis=1)], axis=1).astype(i32))
+    er = A.runWith(ctx, lambda a: A.scanr(add, 10, a), mi)
+    assert np.array_equal(er, np.concatenate([10 + np.cumsum(mi[:, ::-1], axis=1)[:, ::-1], np.full((37, 1), 10)], axis=1).astype(i32))
 
 
 @pytest.mark.gpu
