@@ -21,9 +21,16 @@ on floats are fminf/fmaxf (:322-336), integer arithmetic wraps, Bool is one byte
 Accelerate: both operands of an operator have the same type (Python numbers take the type of the other operand);
 ``fromIntegral`` / ``toFloating`` / ``cast`` convert.
 
+Shapes are known extent by extent as a constant plus, optionally, an extent of an argument or intermediate array
+(``dim(arr, d)``, ``shape_of(arr)``): enough for ``replicate``, ``slice``, ``transpose``, ``reshape``, ``init``,
+``tail``, ``take``, ``drop`` and for the exclusive scans along rows, whose rows grow by one; the host evaluates them
+when the program runs, as the reference evaluates shape expressions (Execute.hs:194-199).  Scans along the
+innermost dimension of matrices and the segmented ``scanl1Seg`` / ``scanr1Seg``, which the reference rejects
+(PrefixSum.hs:39-46), are the scan skeleton over (value, restart flag) pairs.
+
 Restrictions of this front end (not of the skeletons): ranks up to 3; stencils of rank 1 and 2 over single-component
 arrays; seeds and fill values are constants; a ``zipWith`` of arrays of different shape is an error at run time
-instead of the intersection.
+instead of the intersection; no ``awhile`` / ``acond`` (loop and branch in Python around compiled functions).
 """
 from __future__ import annotations
 
