@@ -740,6 +740,32 @@ def main():
                 torch.cuda.empty_cache()
             Workload.functors = "hand"
             line["generated_functors"] = gen
+    elif world > 1 and isinstance(wl, ScanWorkload) and not args.no_extras:
+        # ---- e2e at N GPUs: every rank uploads its slab from pinned host memory, takes part in the carry exchange,
+        # scans, and downloads its part of the result; wall clock between barriers, max over ranks
+        n = wl.n
+        hin = torch.empty(n, dtype=torch.int32).pin_memory()
+        hin.copy_(wl.x.cpu())
+        hout = torch.empty(n + 1, dtype=torch.int32).pin_memory()
+
+        def e2e_step():
+            wl.x.copy_(hin, non_blocking=True)
+            wl.step()
+            hout.copy_(wl.out, non_blocking=True)
+            torch.cuda.synchronize()
+        e2e_step()
+        reps = 3
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            e2e_step()
+        dt = torch.tensor([(time.perf_counter() - t0) / reps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        ok_e2e = torch.tensor([int(wl.verify() and bool(torch.equal(hout, wl.out.cpu())))], device="cuda")
+        dist.all_reduce(ok_e2e, op=dist.ReduceOp.MIN)
+        line["e2e"] = {"value": total_bytes / float(dt[0]) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n * world,
+                       "d2h_bytes_per_step": 4 * (n + 1) * world, "ms_per_step": float(dt[0]) * 1e3, "steps": reps,
+                       "parity_check": bool(ok_e2e[0]), "note": "upload, carry exchange, scan, download per rank; not pipelined"}
     elif rank == 0:
         line["e2e"] = None
     ctx.sync()
