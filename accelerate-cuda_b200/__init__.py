@@ -120,6 +120,7 @@ def lib() -> C.CDLL:
             "accb_launch_config": [vp, vp, C.c_char_p, ll, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)],
             "accb_launch_count": [vp, C.POINTER(C.c_ulonglong)],
             "accb_map": [vp, vp, vp, arrp, i32, vp, sz, arrp],
+            "accb_map_transposed": [vp, vp, vp, arrp, i32, vp, sz, arrp],
             "accb_fold_all": [vp, vp, vp, arrp, i32, ll, vp, sz, arrp],
             "accb_fold_dim": [vp, vp, vp, arrp, i32, ll, ll, vp, sz, arrp],
             "accb_fold_seg": [vp, vp, vp, arrp, i32, ll, ll, vp, ll, vp, sz, arrp],
@@ -135,6 +136,7 @@ def lib() -> C.CDLL:
             "accb_program_scan": [vp, vp, C.POINTER(i32), i32, i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
             "accb_program_permute": [vp, vp, C.POINTER(i32), i32, i32, i32, C.POINTER(accb_value_type)],
             "accb_program_stencil": [vp, vp, i32, i32, vp, sz, i32, C.POINTER(accb_value_type)],
+            "accb_program_map_transposed": [vp, vp, C.POINTER(i32), i32, i32, C.POINTER(accb_value_type), vp, sz],
             "accb_program_generate": [vp, vp, C.POINTER(i32), i32, i32, C.POINTER(i32), C.POINTER(accb_value_type), vp, sz],
             "accb_program_generate_dims": [vp, vp, C.POINTER(i32), i32, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32),
                                            C.POINTER(accb_value_type), vp, sz],
@@ -314,6 +316,13 @@ class Context:
         o = to_accb_array(out)
         _check(lib().accb_map(self.handle, self._k(kernel), self._stream(stream), _arr_list(env), len(env), sb, sn,
                               C.byref(o)), self.handle)
+
+    def map_transposed(self, kernel, env: Sequence, out, scalars=None, stream=None):
+        """``map f (transpose m)``: the element-wise inputs have the transposed shape of ``out``."""
+        sb, sn = _bytes_of(scalars)
+        o = to_accb_array(out)
+        _check(lib().accb_map_transposed(self.handle, self._k(kernel), self._stream(stream), _arr_list(env), len(env),
+                                         sb, sn, C.byref(o)), self.handle)
 
     def fold_all(self, kernel, env: Sequence, n: int, out, seed=None, stream=None):
         sb, sn = _bytes_of(seed)
@@ -578,6 +587,18 @@ def stencil(spec: KernelSpec, src: Acc, out_dtype=None, boundary="clamp", consta
     vid = lib().accb_program_stencil(p.handle, p.ctx._k(spec), src.id, BOUNDARY[boundary], cb, cn, iters, C.byref(t))
     r = p._new(vid, out_type)
     r.shape_fn = src.shape_fn
+    return r
+
+
+def map_transposed(spec: KernelSpec, env: Sequence[Acc], src: Acc, out_type: ArrayType, scalars=None) -> Acc:
+    """map over transposed matrices: the result has the transposed shape of ``src`` (one of the element-wise inputs)."""
+    p = src.prog
+    ids, n = p._ids(env)
+    sb, sn = _bytes_of(scalars)
+    t = out_type.ctype()
+    vid = lib().accb_program_map_transposed(p.handle, p.ctx._k(spec), ids, n, src.id, C.byref(t), sb, sn)
+    r = p._new(vid, out_type)
+    r.shape_fn = lambda s, f=src.shape_fn: tuple(reversed(f(s)))
     return r
 
 

@@ -221,6 +221,36 @@ int accb_map(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_a
     return launch(ctx, pr.fn, "map", grid, pr.block, 0, (cudaStream_t)stream, p);
 }
 
+int accb_map_transposed(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                        const void *scalars, size_t scalar_bytes, const accb_array *out) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_MAP}, "map"));
+    if (!out || out->rank != 2) return fail(ctx, ACCB_EINVAL, "the result of a transposed map is a matrix");
+    if (array_size(out) == 0) return ACCB_OK;
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    TRY(fill_env(ctx, p, env, nenv));
+    TRY(fill_out(ctx, p, out));
+    TRY(fill_scalars(ctx, p, scalars, scalar_bytes));
+    p.n = array_size(out);
+    Prep pr;
+    TRY(prepare(ctx, k, "map_transposed", 0, &pr));
+    const size_t smem = (size_t)pr.meta.v[6];
+    if (smem == 0) return fail(ctx, ACCB_EINVAL, "kernel %s reads no array element-wise: nothing to transpose", k->key.c_str());
+    /* the element-wise inputs are out's shape transposed: out has shape[1] rows of shape[0] columns */
+    const int H = out->shape[0], W = out->shape[1]; /* rows and columns of the sources */
+    /* the arrays that hold the first In::size components (metadata slot 5) are the element-wise ones */
+    for (int a = 0, slot = 0; a < nenv && slot < pr.meta.v[5]; slot += env[a].ncomp, ++a)
+        if (env[a].rank != 2 || env[a].shape[0] != W || env[a].shape[1] != H)
+            return fail(ctx, ACCB_EINVAL, "environment array %d is not the transposed shape of the result", a);
+    p.ip[0] = H;
+    p.ip[1] = W;
+    const long long tiles = ceil_div(W, 64) * ceil_div(H, 64); /* kTransTile of map.cuh */
+    TRY(occupancy(ctx, pr.fn, pr.block, smem, &pr.per_sm));
+    const int grid = (int)std::min<long long>(tiles, (long long)ctx->sm_count * pr.per_sm);
+    return launch(ctx, pr.fn, "map_transposed", grid, pr.block, smem, (cudaStream_t)stream, p);
+}
+
 /* ---------------------------------------------------------------- folds */
 static int set_seed(accb_context *ctx, accb_kparams &p, const void *seed, size_t seed_bytes) {
     if (!seed) return ACCB_OK;

@@ -37,6 +37,7 @@ struct Node {
     int dim_src[ACCB_MAX_RANK] = {-1, -1, -1, -1}; /* ... + extent dim_of[d] of value dim_src[d], if >= 0 */
     int dim_of[ACCB_MAX_RANK] = {0};
     int offsets_id = -1;  /* foldSeg: Int32 vector of segment offsets, length segments + 1 */
+    bool transposed = false; /* map: the element-wise inputs are read transposed; the result has shape_like's shape transposed */
     int all = 0;          /* fold: reduce everything */
     int direction = 0, scan_kind = 0;
     int defaults_id = -1; /* permute */
@@ -158,8 +159,15 @@ int run_internal(accb_program *p, cudaStream_t s, const accb_array *inputs, accb
             case N_MAP: {
                 out.rank = like.rank;
                 memcpy(out.shape, like.shape, sizeof out.shape);
+                if (nd.transposed) {
+                    if (like.rank != 2) return fail(ctx, ACCB_EINVAL, "transpose of an array of rank %d", like.rank);
+                    std::swap(out.shape[0], out.shape[1]);
+                }
                 TRY(alloc_value(p, nd.out_id, out, fresh));
-                TRY(accb_map(ctx, nd.k, s, env.data(), (int)env.size(), sc, nd.scalars.size(), &out));
+                if (nd.transposed)
+                    TRY(accb_map_transposed(ctx, nd.k, s, env.data(), (int)env.size(), sc, nd.scalars.size(), &out));
+                else
+                    TRY(accb_map(ctx, nd.k, s, env.data(), (int)env.size(), sc, nd.scalars.size(), &out));
                 break;
             }
             case N_FOLD: {
@@ -386,6 +394,20 @@ int accb_program_stencil(accb_program *p, accb_kernel *k, int src_id, int bounda
     nd.boundary = boundary;
     nd.iters = std::max(1, iters);
     if (constant) nd.scalars.assign((const unsigned char *)constant, (const unsigned char *)constant + constant_bytes);
+    return add_node(p, nd, out_type, 1);
+}
+
+int accb_program_map_transposed(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int src_id,
+                                const accb_value_type *out_type, const void *scalars, size_t scalar_bytes) {
+    if (!p || !k) return -ACCB_EINVAL;
+    if (src_id < 0) return -fail(p->ctx, ACCB_EINVAL, "unknown value id");
+    Node nd;
+    nd.kind = N_MAP;
+    nd.k = k;
+    nd.env.assign(env_ids, env_ids + nenv);
+    nd.shape_like = src_id;
+    nd.transposed = true;
+    if (scalars) nd.scalars.assign((const unsigned char *)scalars, (const unsigned char *)scalars + scalar_bytes);
     return add_node(p, nd, out_type, 1);
 }
 

@@ -83,6 +83,116 @@ __device__ __forceinline__ void map_body(const accb_kparams &p) {
     }
 }
 
+/* ----------------------------------------------------------------------
+ * map over a TRANSPOSED matrix: `map f (transpose m)`.  Through the generic
+ * kernel a transpose is a gather whose reads are a whole row apart between
+ * neighbouring threads (the reference's backpermute, IndexSpace.hs:96-141, has
+ * the same access pattern).  Here the element-wise inputs -- matrices of
+ * ip[0] rows and ip[1] columns -- go through shared memory in tiles of 64x64:
+ * read along their rows with 16-byte loads, handed to the functor along their
+ * columns four at a time, so that loads and stores are both contiguous
+ * vectors.  Ragged edge tiles and unaligned arrays take scalar accesses.  The functor is the one of the plain
+ * map: apply(env, i, in-values..., out-references...) with i the OUTPUT
+ * position, in an array of ip[1] rows and ip[0] columns.
+ * ---------------------------------------------------------------------- */
+constexpr int kTransTile = 64;                 /* tile edge, in elements */
+constexpr int kTransPitch = kTransTile + 1;    /* odd pitch: columns of a tile fall into different banks */
+constexpr int kTransElems = kTransTile * kTransPitch;
+
+template <class L, int I>
+__device__ __forceinline__ typename type_at<I, L>::type *trans_plane(unsigned char *s) {
+    return reinterpret_cast<typename type_at<I, L>::type *>(s + smem_offset<L, I, kTransElems>::value);
+}
+/* N consecutive elements of every component into row `row` of the tile, from column `col` */
+template <class L, int N, int... I>
+__device__ __forceinline__ void trans_put(unsigned char *s, int row, int col, regs<N, L> &r,
+                                          std::integer_sequence<int, I...>) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) ((trans_plane<L, I>(s)[row * kTransPitch + col + k] = comp<I>(r)[k]), ...);
+}
+/* N elements of every component down column `col` of the tile, from row `row` */
+template <class L, int N, int... I>
+__device__ __forceinline__ void trans_take(unsigned char *s, int row, int col, regs<N, L> &r,
+                                           std::integer_sequence<int, I...>) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) ((comp<I>(r)[k] = trans_plane<L, I>(s)[(row + k) * kTransPitch + col]), ...);
+}
+
+template <class Fn, int CTA>
+__device__ __forceinline__ void map_transposed_body(const accb_kparams &p) {
+    typedef typename Fn::In In;
+    typedef typename Fn::Out Out;
+    constexpr int T = kTransTile, VX = T / V, RY = CTA / VX; /* threads along a row, rows per pass */
+    extern __shared__ __align__(128) unsigned char s_tile[];
+    const Env env(p);
+    const auto iseq = std::make_integer_sequence<int, In::size>();
+    const auto oseq = std::make_integer_sequence<int, Out::size>();
+    const int H = (int)p.ip[0], W = (int)p.ip[1]; /* of the sources; the result has W rows of H columns */
+    const int tx = threadIdx.x % VX, ty = threadIdx.x / VX;
+    const bool vec = (p.flags & ACCB_F_VEC) != 0 && W % V == 0 && H % V == 0;
+    const long long tiles_x = (W + T - 1) / T, tiles_y = (H + T - 1) / T;
+    for (long long t = blockIdx.x; t < tiles_x * tiles_y; t += gridDim.x) {
+        const int y0 = (int)(t / tiles_x) * T, x0 = (int)(t % tiles_x) * T; /* source tile */
+        const bool full = vec && y0 + T <= H && x0 + T <= W;
+        if (full) { /* 4 rows x one 16-byte vector per component and thread in flight */
+            regs<V, In> a[T / RY];
+#pragma unroll
+            for (int q = 0; q < T / RY; ++q)
+                load_all(p.in, ((long long)(y0 + ty + q * RY) * W + x0) / V + tx, a[q]);
+#pragma unroll
+            for (int q = 0; q < T / RY; ++q) trans_put<In, V>(s_tile, ty + q * RY, tx * V, a[q], iseq);
+        } else {
+            for (int r = ty; r < T; r += RY)
+                for (int k = 0; k < V; ++k)
+                    if (y0 + r < H && x0 + tx * V + k < W) {
+                        regs<1, In> a;
+                        load_one(p.in, (long long)(y0 + r) * W + x0 + tx * V + k, a);
+                        trans_put<In, 1>(s_tile, r, tx * V + k, a, iseq);
+                    }
+        }
+        __syncthreads();
+        /* result row x0 + r holds source column x0 + r: elements y0 + 4 tx .. + 3 come from 4 tile rows */
+        if (full) {
+#pragma unroll
+            for (int q = 0; q < T / RY; ++q) {
+                const int r = ty + q * RY;
+                regs<V, In> a;
+                regs<V, Out> b;
+                trans_take<In, V>(s_tile, tx * V, r, a, iseq);
+                const long long i = (long long)(x0 + r) * H + y0 + tx * V;
+                map_apply<Fn>(env, i, a, b, iseq, oseq);
+                store_all(p.out, i / V, b);
+            }
+        } else {
+            for (int r = ty; r < T; r += RY)
+                for (int k = 0; k < V; ++k)
+                    if (x0 + r < W && y0 + tx * V + k < H) {
+                        regs<1, In> a;
+                        regs<1, Out> b;
+                        trans_take<In, 1>(s_tile, tx * V + k, r, a, iseq);
+                        const long long i = (long long)(x0 + r) * H + y0 + tx * V + k;
+                        map_apply<Fn>(env, i, a, b, iseq, oseq);
+                        store_one(p.out, i, b);
+                    }
+        }
+        __syncthreads(); /* the tile is overwritten by the next trip */
+    }
+}
+
+/* the transposed form needs element-wise inputs; without any it has nothing to do */
+template <class Fn, int CTA>
+__device__ __forceinline__ void map_transposed_or_nothing(const accb_kparams &p) {
+    if constexpr (Fn::In::size > 0) map_transposed_body<Fn, CTA>(p);
+}
+template <class Fn>
+__host__ __device__ constexpr int map_transposed_smem() {
+    typedef typename Fn::In In;
+    if constexpr (In::size > 0)
+        return smem_offset<In, In::size, kTransElems>::value;
+    else
+        return 0;
+}
+
 }  // namespace accb
 
 #ifndef ACCB_MAP_CTA
@@ -92,10 +202,16 @@ __device__ __forceinline__ void map_body(const accb_kparams &p) {
 #define ACCB_MAP_U 2 /* vectors per input per thread per trip */
 #endif
 
-/* Entry point named after the reference's kernel (Mapping.hs:53). */
+/* Entry point named after the reference's kernel (Mapping.hs:53), and the form for transposed
+ * inputs.  Metadata: {.., 0, 0, U, element-wise input components, shared memory of the transposed form}. */
 #define ACCB_INSTANTIATE_MAP(Fn)                                                        \
-    ACCB_META(1, ACCB_MAP_CTA, 0, 0, ACCB_MAP_U, 0)                                     \
+    ACCB_META7(1, ACCB_MAP_CTA, 0, 0, ACCB_MAP_U, Fn::In::size,                         \
+               (accb::map_transposed_smem<Fn>()))                                       \
     extern "C" __global__ void __launch_bounds__(ACCB_MAP_CTA)                          \
         map(const __grid_constant__ accb_kparams p) {                                   \
         accb::map_body<Fn, ACCB_MAP_CTA, ACCB_MAP_U>(p);                                \
+    }                                                                                   \
+    extern "C" __global__ void __launch_bounds__(ACCB_MAP_CTA)                          \
+        map_transposed(const __grid_constant__ accb_kparams p) {                        \
+        accb::map_transposed_or_nothing<Fn, ACCB_MAP_CTA>(p);                           \
     }

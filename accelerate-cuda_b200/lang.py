@@ -88,6 +88,9 @@ class _DryBackend:
     def generate_dims(self, prog, spec, env, dims, out_type, scalars=None):
         return self._add(prog, spec, out_type)
 
+    def map_transposed(self, spec, env, src, out_type, scalars=None):
+        return self._add(src.prog, spec, out_type)
+
     def map_(self, spec, env, out_type, shape_like=None, scalars=None):
         return self._add(env[0].prog, spec, out_type)
 
@@ -557,6 +560,12 @@ class _KernelEnv:
         lin = _to_linear(idx, self.dims_of(arr))
         return tuple(_b().emit(dt, f"@G{arr.node.id}_{c}@[{lin.code}]") for c, dt in enumerate(arr.dtypes))
 
+    def elementwise(self, arr: "Array") -> Tuple[Exp, ...]:
+        """The components of arr as element-wise inputs, whatever the index (the skeleton pairs the positions)."""
+        if not any(a is arr for a in self.elem):
+            self.elem.append(arr)
+        return tuple(Exp(dt, f"@IN{arr.node.id}_{c}@") for c, dt in enumerate(arr.dtypes))
+
     # -- final assembly
     def in_types(self) -> List[np.dtype]:
         return [dt for a in self.elem for dt in a.dtypes]
@@ -685,6 +694,8 @@ class Array:
         self.node = node
         self.fn = fn
         self.extent = extent if extent is not None else _Extent(like=self)
+        # (manifest sources, function of their elements): this array is a map over transposed matrices
+        self.transposed = None
 
     @property
     def rank(self):
@@ -744,8 +755,12 @@ def map(f: Callable, arr: Array) -> Array:  # noqa: A001 (the Accelerate name)
     arr = _as_array(arr)
     with _probe(arr.prog) as pr:
         out = _flat(f(_unflat1(pr.symbols(arr.dtypes))))
-    return Array(arr.prog, [e.dt for e in out], arr.extent,
-                 fn=lambda kenv, ix: f(_unflat1(arr.at(kenv, ix))))
+    res = Array(arr.prog, [e.dt for e in out], arr.extent,
+                fn=lambda kenv, ix: f(_unflat1(arr.at(kenv, ix))))
+    if arr.transposed is not None:  # a map over a transpose is still a tiled transpose
+        srcs, g = arr.transposed
+        res.transposed = (srcs, lambda vs: f(g(vs)))
+    return res
 
 
 def zipWith(f: Callable, *arrs: Array) -> Array:
@@ -756,8 +771,15 @@ def zipWith(f: Callable, *arrs: Array) -> Array:
         ext = _unify(prog, ext, a.extent)
     with _probe(prog) as pr:
         out = _flat(f(*[_unflat1(pr.symbols(a.dtypes)) for a in arrs]))
-    return Array(prog, [e.dt for e in out], ext,
-                 fn=lambda kenv, ix: f(*[_unflat1(a.at(kenv, ix)) for a in arrs]))
+    res = Array(prog, [e.dt for e in out], ext,
+                fn=lambda kenv, ix: f(*[_unflat1(a.at(kenv, ix)) for a in arrs]))
+    if all(a.transposed is not None for a in arrs):  # transposes zipped: their sources are read tile by tile
+        groups = [a.transposed for a in arrs]
+        counts = [len(srcs) for srcs, _ in groups]
+        starts = [sum(counts[:k]) for k in range(len(groups))]
+        res.transposed = ([s for srcs, _ in groups for s in srcs],
+                          lambda vs: f(*[g(vs[st:st + n]) for (_, g), st, n in _zip(groups, starts, counts)]))
+    return res
 
 
 def zip(*arrs: Array) -> Array:  # noqa: A001
@@ -840,7 +862,12 @@ def transpose(m: Array) -> Array:
     m = _as_array(m)
     if m.rank != 2:
         raise TypeError("transpose of a matrix")
-    return generate(_Extent(parts=[m.extent.part(1), m.extent.part(0)]), lambda u: m[(u[1], u[0])], prog=m.prog)
+    t = generate(_Extent(parts=[m.extent.part(1), m.extent.part(0)]), lambda u: m[(u[1], u[0])], prog=m.prog)
+    if m.manifest:
+        # When this array (or maps / zips over it) is made manifest, the source goes through shared-memory tiles
+        # instead of being gathered; fused into any other consumer it stays the gather above.
+        t.transposed = ([m], lambda vs: vs[0])
+    return t
 
 
 def reshape(shape, arr: Array) -> Array:
@@ -1063,7 +1090,20 @@ def compute(arr: Array) -> Array:
         return arr
     prog = arr.prog
     kenv = _KernelEnv(prog, arr.extent)
-    body, vals = _producer_body(arr, kenv, own_out=True)
+    if arr.transposed is not None:
+        # map f (transpose m): the same functor as map f m, launched so that m goes through shared-memory tiles
+        srcs, g = arr.transposed
+
+        def go():
+            kenv.index = Index(Exp(I64, "i"), arr.extent.dims(kenv, True))
+            _kenvs.append(kenv)
+            try:
+                return _flat(g([_unflat1(kenv.elementwise(s)) for s in srcs]))
+            finally:
+                _kenvs.pop()
+        body, vals = _trace(go)
+    else:
+        body, vals = _producer_body(arr, kenv, own_out=True)
     outs = "".join(f", {ctype(dt)} &out{c}" for c, dt in enumerate(arr.dtypes))
     sets = " ".join(f"out{c} = {v.code};" for c, v in enumerate(vals))
     text, = kenv.resolve(f"{body}\n        {sets}")
@@ -1073,6 +1113,9 @@ def compute(arr: Array) -> Array:
     spec = KernelSpec("map", name, src)
     out_type = ArrayType(arr.rank, arr.dtypes)
     env_nodes = kenv.nodes()
+    if arr.transposed is not None:
+        node = _be().map_transposed(spec, env_nodes, arr.transposed[0][0].node, out_type)
+        return Array(prog, arr.dtypes, node=node)
     if arr.extent.literal is not None:
         node = _be().generate(prog, spec, env_nodes, arr.extent.literal, out_type)
     elif arr.extent.like is not None:

@@ -167,6 +167,12 @@ ACCB_API int accb_launch_count(accb_context *ctx, unsigned long long *launches);
  * All launches are asynchronous on `stream`.                               */
 ACCB_API int accb_map(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
                       const void *scalars, size_t scalar_bytes, const accb_array *out);
+/* `map f (transpose m)` with the same kernel object as `map f m`: the environment arrays that the functor
+ * reads element-wise are matrices of the transposed shape of `out` and go through 32x32 shared-memory tiles, so
+ * that loads and stores are both contiguous.  In the reference a transpose is a backpermute, i.e. a gather
+ * (mkTransform, CUDA/CodeGen/IndexSpace.hs:96-141). */
+ACCB_API int accb_map_transposed(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
+                                 int nenv, const void *scalars, size_t scalar_bytes, const accb_array *out);
 
 /* seed == NULL selects fold1 / fold1All (no seed) */
 ACCB_API int accb_fold_all(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
@@ -287,6 +293,9 @@ ACCB_API int accb_program_permute(accb_program *p, accb_kernel *k, const int *en
 ACCB_API int accb_program_stencil(accb_program *p, accb_kernel *k, int src_id, int boundary,
                                   const void *constant, size_t constant_bytes, int iters,
                                   const accb_value_type *out_type);
+/* map over transposed matrices (accb_map_transposed): the result has the transposed shape of value src_id */
+ACCB_API int accb_program_map_transposed(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int src_id,
+                                         const accb_value_type *out_type, const void *scalars, size_t scalar_bytes);
 /* generate: a map node whose result shape is given literally, innermost extent first
  * (`generate (constant sh) f`, CUDA/Execute.hs:194-195) */
 ACCB_API int accb_program_generate(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,

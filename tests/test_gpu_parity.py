@@ -83,6 +83,29 @@ def test_transpose_by_index_arithmetic(ctx, P, torch_cuda, rng):
     assert np.array_equal(out.cpu().numpy(), a.T)
 
 
+@pytest.mark.parametrize("h,w", [(1, 1), (3, 70), (64, 64), (65, 127), (128, 192), (1000, 36), (257, 1028)])
+def test_map_over_transposed_inputs_through_shared_memory_tiles(ctx, P, accb, torch_cuda, rng, h, w):
+    """accb_map_transposed: the functor of `map f m` launched as `map f (transpose m)`; full 64x64 tiles take the
+    vector path, ragged edges and widths that are not multiples of 4 the scalar one."""
+    t = torch_cuda
+    x, y = rng.standard_normal((h, w)).astype(np.float32), rng.standard_normal((h, w)).astype(np.float32)
+    out = t.empty((w, h), dtype=t.float32, device="cuda")
+    ctx.map_transposed(P.SAXPY, [dev(t, x), dev(t, y)], out, scalars=np.float32(2.5))
+    ctx.sync()
+    close(out.cpu().numpy(), (np.float32(2.5) * x + y).T.astype(np.float64), 1e-6)
+    a = rng.integers(-128, 128, (h, w)).astype(np.int8)
+    b = rng.integers(-30000, 30000, (h, w)).astype(np.int16)
+    c = rng.standard_normal((h, w)) * 1000
+    o = t.empty((w, h), dtype=t.int64, device="cuda")
+    f = t.empty((w, h), dtype=t.uint8, device="cuda")
+    ctx.map_transposed(P.WIDEN, [(dev(t, a), dev(t, b), dev(t, c))], (o, f))  # components of 1, 2 and 8 bytes
+    ctx.sync()
+    assert np.array_equal(o.cpu().numpy(), (a.astype(np.int64) * b + c.astype(np.int64)).T)
+    assert np.array_equal(f.cpu().numpy(), (a > 0).astype(np.uint8).T)
+    with pytest.raises(accb.AccbError):
+        ctx.map_transposed(P.SAXPY, [dev(t, x), dev(t, y)], t.empty((h + 1, w), device="cuda"), scalars=np.float32(1))
+
+
 @pytest.mark.parametrize("n", [7, 4096, 12345])
 def test_map_mixed_widths(ctx, P, torch_cuda, rng, n):
     t = torch_cuda

@@ -142,7 +142,10 @@ def test_shapes_computed_from_other_arrays():
     assert [s.skeleton for s in specs] == ["fold_dim"]  # replicate is fused: the matrix element-wise, the vector gathered
     assert "using In = accb::types<float>;" in specs[0].source and "env.in<float>(1)" in specs[0].source
     t = A.specs(lambda m: A.transpose(m), A.matrix(i32))
-    assert [s.skeleton for s in t] == ["map"] and "env.out_dim(" in t[0].source
+    # a transpose made manifest is the plain map functor launched over shared-memory tiles, not a gather
+    assert [s.skeleton for s in t] == ["map"] and "using In = accb::types<int>;" in t[0].source
+    g = A.specs(lambda m: A.fold(add, 0, A.transpose(m)), A.matrix(i32))  # column sums: tiled transpose, then row sums
+    assert [s.skeleton for s in g] == ["map", "fold_dim"]
     r = A.specs(lambda m: A.map(lambda x: x + 1, A.reshape((A.dim(m, 1), A.dim(m, 0)), m)), A.matrix(i32))
     assert "using In = accb::types<int>;" in r[0].source  # same row-major position: still element-wise
     ex = A.specs(lambda m: A.scanl(add, 0, m), A.matrix(i32))
@@ -270,6 +273,13 @@ def test_replicate_slice_reshape_and_friends(ctx, rng):
                                                         A.enumFromN(A.dim(a, 0), 5)), x)
     assert np.array_equal(rv, x[::-1]) and np.array_equal(ini, x[:-1]) and np.array_equal(tl, x[1:])
     assert np.array_equal(tk, x[:3]) and np.array_equal(dr, x[2:]) and np.array_equal(en, np.arange(5, 5 + x.size, dtype=i32))
+    for shp in [(1, 1), (33, 1000), (1025, 257)]:  # tiled transposes: maps and zips over them, wide and tuple elements
+        a, b = rng.uniform(-1, 1, shp), rng.integers(-9, 9, shp).astype(i32)
+        t1, t2, t3 = A.runWith(ctx, lambda p, q: (A.map(lambda e: e * 2.0, A.transpose(p)),
+                                                  A.zipWith(lambda e, k: e + A.cast(k, f64), A.transpose(p), A.transpose(q)),
+                                                  A.transpose(A.compute(A.zip(p, q)))), a, b)
+        assert np.array_equal(t1, 2 * a.T) and np.array_equal(t2, a.T + b.T)
+        assert np.array_equal(t3[0], a.T) and np.array_equal(t3[1], b.T)
     rep = A.runWith(ctx, lambda a: A.replicate(a, 4, axis=1), x[:9])
     assert np.array_equal(rep, np.repeat(x[:9, None], 4, axis=1))
     # exclusive scans along rows: one element longer per row, seed first (scanl) or last (scanr)
