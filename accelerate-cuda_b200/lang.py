@@ -28,8 +28,8 @@ when the program runs, as the reference evaluates shape expressions (Execute.hs:
 innermost dimension of matrices and the segmented ``scanl1Seg`` / ``scanr1Seg``, which the reference rejects
 (PrefixSum.hs:39-46), are the scan skeleton over (value, restart flag) pairs.
 
-Restrictions of this front end (not of the skeletons): ranks up to 3; stencils of rank 1 and 2 over single-component
-arrays; seeds and fill values are constants; a ``zipWith`` of arrays of different shape is an error at run time
+Restrictions of this front end (not of the skeletons): ranks up to 3; the stencil skeleton serves vectors and matrices
+of one component (cubes and tuple elements fall back to a gathering ``generate``); seeds and fill values are constants; a ``zipWith`` of arrays of different shape is an error at run time
 instead of the intersection; no ``awhile`` / ``acond`` (loop and branch in Python around compiled functions).
 """
 from __future__ import annotations
@@ -1471,16 +1471,68 @@ def _stencil_spec(f: Callable, narr: int, tin, tout_probe, pattern, kind: str):
     return KernelSpec("stencil" if narr == 1 else "stencil2", name, text.replace("@N@", name)), out[0].dt
 
 
+def _bound(i: Exp, n: Exp, mode: str) -> Exp:
+    """One coordinate through the boundary function (Stencil/Extra.hs:200-226); Constant clamps, the caller
+    replaces the value."""
+    if mode in ("clamp", "constant"):
+        return maximum(minimum(i, n - 1), 0)
+    if mode == "mirror":
+        return cond(i < 0, -i, cond(i >= n, n - (i - n + 2), i))
+    if mode == "wrap":
+        return cond(i < 0, n + i, cond(i >= n, i - n, i))
+    raise ValueError(f"unknown boundary {mode!r}")
+
+
+def _stencil_by_gather(f: Callable, boundary, arr: Array, pattern) -> Array:
+    """A stencil of any rank and element type as a ``generate`` that gathers."""
+    mode, cval = (boundary[0], boundary[1]) if isinstance(boundary, tuple) else (boundary, None)
+    pattern = tuple(pattern)
+    if len(pattern) != arr.rank or any(w % 2 == 0 for w in pattern):
+        raise TypeError("the neighbourhood has one odd extent per dimension")
+    radii = [w // 2 for w in pattern]
+
+    def at(u):
+        centre, dims = _comps(u), shape(arr)
+
+        def tap(offs):
+            moved = [c + o if o else c for c, o in _zip(centre, offs)]
+            idx = tuple(_bound(m, n, mode) if o else m for m, n, o in _zip(moved, dims, offs))
+            vals = _flat(arr[idx if len(idx) != 1 else idx[0]])
+            if mode == "constant" and any(offs):
+                inside = None
+                for m, n, o in _zip(moved, dims, offs):
+                    if o:
+                        ok = (m >= 0) & (m < n)
+                        inside = ok if inside is None else inside & ok
+                consts = cval if isinstance(cval, (tuple, list)) else [cval]
+                vals = tuple(cond(inside, v, constant(c, v.dt)) for v, c in _zip(vals, consts))
+            return _unflat1(vals)
+
+        def nest(d, offs):
+            if d == arr.rank:
+                return tap(offs)
+            return [nest(d + 1, offs + [o]) for o in range(-radii[d], radii[d] + 1)]
+        return f(nest(0, []))
+    return generate(shape_of(arr), at)
+
+
 def stencil(f: Callable, boundary, arr: Array, pattern=None, iterate: int = 1) -> Array:
     """``stencil f boundary arr``.  f receives the neighbourhood as nested lists, ``t[dy][dx]`` for a matrix
-    (``t[dx]`` for a vector), centre in the middle; pattern = (rows, columns) of the neighbourhood, 3x3 / 3 by
-    default.  boundary: "clamp", "mirror", "wrap" or ("constant", value).  iterate > 1 applies it repeatedly."""
+    (``t[dx]`` for a vector, ``t[dz][dy][dx]`` for a cube), centre in the middle; pattern = the extents of the
+    neighbourhood, 3 per dimension by default.  boundary: "clamp", "mirror", "wrap" or ("constant", value).
+    iterate > 1 applies it repeatedly.  Vectors and matrices of one component go through the stencil skeleton
+    (tiles staged in shared memory); cubes and tuple elements gather, as every stencil of the reference does."""
     arr = compute(_as_array(arr))
-    if len(arr.dtypes) != 1 or arr.rank not in (1, 2):
-        raise NotImplementedError("stencils over vectors and matrices of one component")
-    pattern = pattern or ((1, 3) if arr.rank == 1 else (3, 3))
     if arr.rank == 1 and isinstance(pattern, int):
         pattern = (1, pattern)
+    if len(arr.dtypes) != 1 or arr.rank not in (1, 2) or (pattern is not None and pattern[-1] > 9):
+        # cubes, tuple elements, very wide neighbourhoods: the way the reference does every stencil -- each element
+        # gathers its neighbourhood through the boundary function (CodeGen/Stencil.hs:55-114, Stencil/Extra.hs:191-226)
+        out = arr
+        for _ in range(max(1, iterate)):
+            out = compute(_stencil_by_gather(f, boundary, out, pattern or (3,) * arr.rank))
+        return out
+    pattern = pattern or ((1, 3) if arr.rank == 1 else (3, 3))
     spec, tout = _stencil_spec(f, 1, arr.dtypes, "rank1" if arr.rank == 1 else "rank2", pattern, "Stencil")
     mode, const = (boundary[0], np.asarray(boundary[1], dtype=arr.dtypes[0])[()]) if isinstance(boundary, tuple) else (boundary, None)
     if iterate > 1 and tout != arr.dtypes[0]:

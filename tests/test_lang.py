@@ -317,6 +317,26 @@ def test_stencils(ctx, oracle, rng, boundary):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("boundary,padmode", [("clamp", "edge"), ("mirror", "reflect"), ("wrap", "wrap"),
+                                              (("constant", 2.0), "constant")])
+def test_stencil_over_a_cube_gathers_through_the_boundary_function(ctx, rng, boundary, padmode):
+    c = rng.uniform(0, 1, (9, 20, 33)).astype(f32)
+    mean27 = lambda t: sum((t[z][y][x] for z in range(3) for y in range(3) for x in range(3)), A.constant(0, f32)) / 27.0  # noqa: E731
+    got = A.runWith(ctx, lambda a: A.stencil(mean27, boundary, a), c)
+    kw = {"constant_values": 2.0} if padmode == "constant" else {}
+    p = np.pad(c.astype(f64), 1, mode=padmode, **kw)
+    ref = sum(p[z:z + 9, y:y + 20, x:x + 33] for z in range(3) for y in range(3) for x in range(3)) / 27.0
+    close(got, ref, 1e-6)
+    # elements that are pairs: the neighbourhood of a vector of (value, weight)
+    v, w = rng.uniform(0, 1, 5000).astype(f32), rng.uniform(1, 2, 5000).astype(f32)
+    sv, sw = A.runWith(ctx, lambda a: A.stencil(lambda t: (t[0][0] * t[0][1] + t[1][0] * t[1][1] + t[2][0] * t[2][1],
+                                                           t[0][1] + t[1][1] + t[2][1]), "clamp", a), (v, w))
+    pv, pw = np.pad(v.astype(f64), 1, mode="edge"), np.pad(w.astype(f64), 1, mode="edge")
+    close(sv, pv[:-2] * pw[:-2] + pv[1:-1] * pw[1:-1] + pv[2:] * pw[2:], 1e-6)
+    close(sw, pw[:-2] + pw[1:-1] + pw[2:], 1e-6)
+
+
+@pytest.mark.gpu
 def test_iterated_stencil_and_stencil2(ctx, rng):
     g = rng.uniform(0, 1, (64, 128)).astype(f32)
     five = lambda t: 0.2 * (t[0][1] + t[1][0] + t[1][1] + t[1][2] + t[2][1])  # noqa: E731
