@@ -11,9 +11,12 @@ collective operation shards by contiguous slabs of the outermost index space:
 * scan                 -- slab totals all-gathered; each rank continues from the
                           exclusive sum of the lower ranks' totals (the carry);
 * permute (+)          -- full-size partial destinations, one all-reduce;
-* iterated stencil     -- row slabs with RY halo rows each way, refreshed before
-                          every application by neighbour send/recv into the
-                          rank's OWN halo rows (no kernel reads a peer's memory).
+* iterated stencil     -- row slabs with halo rows towards each neighbour, refreshed
+                          by neighbour send/recv into the rank's OWN halo rows (no
+                          kernel reads a peer's memory): either RY rows before every
+                          application, or iters*RY rows ONCE, after which all the
+                          applications run on the padded slab (a few rows are
+                          computed twice instead of exchanging iters times).
 
 Only the partitioning and exchange logic lives here; the local work is done by
 whatever ``local_*`` callables the caller passes (the skeleton launches of
@@ -131,6 +134,65 @@ def exchange_halos(grid: torch.Tensor, ry: int, boundary: str = "clamp", group=N
     elif boundary == "mirror":
         grid[-ry:] = interior[-ry - 1:-1].flip(0)
     return grid
+
+
+def sharded_stencil_iterate_blocked(grid_local: torch.Tensor, iters: int, ry: int, local_iterate: Callable,
+                                    boundary: str = "clamp", group=None) -> torch.Tensor:
+    """``iters`` stencil applications on a row-slab with ONE exchange: the halo is iters*ry rows wide, the
+    applications run on the whole padded slab, and what the kernel's own boundary treatment does at the padded
+    edges creeps inwards by ry rows per application -- exactly as far as the halo reaches.  About iters^2*ry/2 rows
+    per side are computed redundantly instead of exchanging ry rows iters times.  Ranks at the global top and bottom
+    get no halo on that side (the kernel's boundary IS the global one there); with Wrap every rank has both.
+    ``local_iterate(padded, iters) -> padded`` applies the stencil iters times.  Falls back to one exchange per
+    application when some slab has fewer than iters*ry rows."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    k = iters * ry
+    h = grid_local.shape[0]
+    hmin = grid_local.new_tensor([float(h)])
+    if world > 1:
+        dist.all_reduce(hmin, op=dist.ReduceOp.MIN, group=group)
+    if world == 1:
+        return local_iterate(grid_local, iters)
+    if int(hmin[0]) < k:  # every rank takes the same path: the exchange is collective
+        out = grid_local
+        return sharded_stencil_iterate(out, iters, ry, lambda a: local_iterate(a, 1), boundary, group)
+    pt, pb = wide_halo_layout(k, boundary, group)
+    a = torch.empty((pt + h + pb, grid_local.shape[1]), dtype=grid_local.dtype, device=grid_local.device)
+    a[pt:pt + h] = grid_local
+    exchange_wide_halos(a, pt, pb, group)
+    return local_iterate(a, iters)[pt:pt + h]
+
+
+def wide_halo_layout(k: int, boundary: str = "clamp", group=None) -> Tuple[int, int]:
+    """Halo rows (above, below) of this rank's slab for k rows of reach: none at the global top and bottom, where
+    the kernel's boundary is the global one, except with Wrap, where the ranks form a ring."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    ring = boundary == "wrap" and world > 1
+    return (k if (rank > 0 or ring) else 0), (k if (rank < world - 1 or ring) else 0)
+
+
+def exchange_wide_halos(a: torch.Tensor, pt: int, pb: int, group=None) -> torch.Tensor:
+    """Fill the pt halo rows above and the pb halo rows below the interior of a padded slab from the neighbours'
+    interiors, in place (a caller that keeps its data in such a slab exchanges without any copy)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    h = a.shape[0] - pt - pb
+    interior = a[pt:pt + h]
+    up, down = (rank - 1) % world, (rank + 1) % world
+    ops = []
+    # rows travelling up carry tag 0, rows travelling down tag 1; between two ranks messages match by order, which
+    # matters when both neighbours are the same rank (a ring of two): send [up, down], receive [from below, from above]
+    if pt:
+        ops.append(dist.P2POp(dist.isend, interior[:pt], up, group, 0))
+    if pb:
+        ops.append(dist.P2POp(dist.isend, interior[h - pb:], down, group, 1))
+    if pb:
+        ops.append(dist.P2POp(dist.irecv, a[pt + h:], down, group, 0))
+    if pt:
+        ops.append(dist.P2POp(dist.irecv, a[:pt], up, group, 1))
+    if ops:
+        for wk in dist.batch_isend_irecv(ops):
+            wk.wait()
+    return a
 
 
 def sharded_stencil_iterate(grid_local: torch.Tensor, iters: int, ry: int, local_apply: Callable,

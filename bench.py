@@ -262,14 +262,20 @@ class StencilWorkload(Workload):
         t, W = self.t, self.W
         self.h = self.w = n or 8192
         self.iters = 10
-        # with several GPUs each rank owns a slab of h rows of a (world*h) x w grid, plus one halo row
-        # above and below that its neighbours refresh before every application
-        halo = 1 if self.world > 1 else 0
-        rows = self.h + 2 * halo
+        # With several GPUs each rank owns a slab of h rows of a (world*h) x w grid, plus `iters` halo rows towards
+        # each neighbour that ONE exchange per step refreshes (320 KiB each way): the ten applications then run on
+        # the padded slab, and what the kernel's Clamp does at the padded edges creeps in by a row per application,
+        # exactly as far as the halo reaches.
+        if self.world > 1:
+            self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
+            self.pt, self.pb = self.sh.wide_halo_layout(self.iters, "clamp")
+        else:
+            self.pt = self.pb = 0
+        rows = self.pt + self.h + self.pb
         self.a = t.empty((rows, self.w), dtype=t.float32, device="cuda")
         self.b = t.empty_like(self.a)
         self.src = t.zeros_like(self.a)
-        self.ctx.gen_uniform_f32(self.src[halo:halo + self.h], self.h * self.w, self.rank * self.h * self.w, W.SEED,
+        self.ctx.gen_uniform_f32(self.src[self.pt:self.pt + self.h], self.h * self.w, self.rank * self.h * self.w, W.SEED,
                                  W.S_GRID, 0.0, 1.0)
         self.k = self.ctx.kernel(self.functor("BLUR")).wait()
         self.bytes = W.bytes_stencil(self.h, self.w, self.iters)
@@ -283,18 +289,29 @@ class StencilWorkload(Workload):
             self.ctx.stencil(self.k, self.src, self.a, boundary="clamp")
             self.res = self.ctx.stencil_iterate(self.k, self.a, self.b, self.iters - 1, boundary="clamp")
             return self.iters
-        cur, nxt = self.src, self.a
-        for _ in range(self.iters):
-            self.sh.exchange_halos(cur, 1, "clamp")  # one 32 KiB row each way, into this rank's own halo rows
-            self.ctx.stencil(self.k, cur, nxt, boundary="clamp")
-            cur, nxt = nxt, (self.b if nxt is self.a else self.a)
-        self.res = cur[1:-1]
+        self.sh.exchange_wide_halos(self.src, self.pt, self.pb)  # in place: the data lives in the padded slab
+        self.ctx.stencil(self.k, self.src, self.a, boundary="clamp")
+        res = self.ctx.stencil_iterate(self.k, self.a, self.b, self.iters - 1, boundary="clamp")
+        self.res = res[self.pt:self.pt + self.h]
         return self.iters
 
     def verify(self):
         # blur with Clamp keeps values inside [min, max] of the source and (interior) preserves the mean
-        r = self.res
-        return bool(r.min() >= self.src.min()) and bool(r.max() <= self.src.max()) and abs(float(r.mean()) - float(self.src.mean())) < 1e-3
+        r, t = self.res, self.t
+        interior = self.src[self.pt:self.pt + self.h]
+        ok = bool(r.min() >= interior.min() - 1e-6) and bool(r.max() <= interior.max() + 1e-6)
+        if self.world == 1:
+            return ok and abs(float(r.mean()) - float(interior.mean())) < 1e-3
+        # several GPUs: the wide-halo scheme against one exchange of a single row per application, bit for bit
+        cur = t.zeros((self.h + 2, self.w), dtype=t.float32, device="cuda")
+        cur[1:-1] = interior
+        nxt = t.empty_like(cur)
+        for _ in range(self.iters):
+            self.sh.exchange_halos(cur, 1, "clamp")
+            self.ctx.stencil(self.k, cur, nxt, boundary="clamp")
+            cur, nxt = nxt, cur
+        self.ctx.sync()
+        return ok and bool(t.equal(cur[1:-1], r))
 
 
 class BlackScholesWorkload(Workload):

@@ -70,7 +70,17 @@ def _worker(rank, world, port, case, ret):
                 # the boundary in x is the kernel's; in y the halo rows already hold the right neighbours, so
                 # what the kernel does beyond them only lands in halo rows, which the next exchange overwrites
                 return torch.from_numpy(oracle.stencil2d(a.numpy(), W.BLUR_WEIGHTS, mode))
-            got = sh.sharded_stencil_iterate(torch.from_numpy(g[lo:hi].copy()), iters, 1, apply, boundary=mode)
+            def iterate(a, times):
+                for _ in range(times):
+                    a = apply(a)
+                return a
+            if case.startswith("stencilwide"):  # one exchange of iters rows each way, then iters applications
+                got = sh.sharded_stencil_iterate_blocked(torch.from_numpy(g[lo:hi].copy()), iters, 1, iterate, boundary=mode)
+            elif case.startswith("stencilshort"):  # slabs shorter than the wide halo: one exchange per application
+                iters = 14
+                got = sh.sharded_stencil_iterate_blocked(torch.from_numpy(g[lo:hi].copy()), iters, 1, iterate, boundary=mode)
+            else:
+                got = sh.sharded_stencil_iterate(torch.from_numpy(g[lo:hi].copy()), iters, 1, apply, boundary=mode)
             ref = g
             for _ in range(iters):
                 ref = oracle.stencil2d(ref, W.BLUR_WEIGHTS, mode)
@@ -81,7 +91,8 @@ def _worker(rank, world, port, case, ret):
 
 
 @pytest.mark.parametrize("world", [2, 3])
-@pytest.mark.parametrize("case", ["scan", "hist", "dot", "stencil-clamp", "stencil-mirror", "stencil-wrap"])
+@pytest.mark.parametrize("case", ["scan", "hist", "dot", "stencil-clamp", "stencil-mirror", "stencil-wrap",
+                                  "stencilwide-clamp", "stencilwide-mirror", "stencilwide-wrap", "stencilshort-clamp"])
 def test_sharded_paths_match_the_single_device_oracle(case, world):
     mgr = mp.Manager()
     ret = mgr.dict()
