@@ -257,6 +257,48 @@ def test_scans_along_rows_and_inside_segments(ctx, rng):
 
 
 @pytest.mark.gpu
+def test_every_scalar_operator_against_numpy(ctx, rng):
+    """The C forms of CodeGen/Arithmetic.hs, operator by operator, on negative and positive operands."""
+    a = rng.integers(-1000, 1000, 4096).astype(i32)
+    b = rng.integers(1, 50, 4096).astype(i32) * rng.choice([-1, 1], 4096).astype(i32)
+    with np.errstate(over="ignore"):
+        got = A.runWith(ctx, lambda x, y: A.zipWith(lambda p, q: (p + q, p - q, p * q, p // q, p % q, A.quot(p, q), A.rem(p, q), -p), x, y), a, b)
+        tq = np.trunc(a / b).astype(i32)
+        for g, r in zip(got, [a + b, a - b, a * b, a // b, a % b, tq, a - tq * b, -a]):
+            assert np.array_equal(g, r)
+        got = A.runWith(ctx, lambda x, y: A.zipWith(lambda p, q: (abs(p), A.signum(p), A.minimum(p, q), A.maximum(p, q), p & q, p | q, p ^ q, ~p), x, y), a, b)
+        for g, r in zip(got, [np.abs(a), np.sign(a), np.minimum(a, b), np.maximum(a, b), a & b, a | b, a ^ b, ~a]):
+            assert np.array_equal(g, r)
+        got = A.runWith(ctx, lambda x, y: A.zipWith(lambda p, q: (p << 3, p >> 2, p < q, p <= q, p == q, p != q, (p > 0) & (q > 0), (p > 0) | ~(q > 0)), x, y), a, b)
+        for g, r in zip(got, [a << 3, a >> 2, a < b, a <= b, a == b, a != b, (a > 0) & (b > 0), (a > 0) | ~(b > 0)]):
+            assert np.array_equal(g.astype(r.dtype), r)
+        # wrapping: Int32 arithmetic is modulo 2^32, unsigned division and shifts are logical
+        big = rng.integers(-2**31, 2**31 - 1, 4096).astype(i32)
+        w1, w2 = A.runWith(ctx, lambda x: A.map(lambda p: (p * p + p, A.cast(A.cast(p, u32) >> 1, i32)), x), big)
+        assert np.array_equal(w1, big * big + big) and np.array_equal(w2, (big.astype(u32) >> 1).astype(i32))
+    x = rng.uniform(-4, 4, 4096).astype(f32)
+    y = rng.uniform(0.1, 4, 4096).astype(f32)
+    got = A.runWith(ctx, lambda p, q: A.zipWith(lambda s, t: (s / t, s ** 2.0, A.sqrt(t), A.exp(s), A.log(t), A.sin(s), A.cos(s), A.atan2(s, t)), p, q), x, y)
+    for g, r in zip(got, [x / y, x ** 2, np.sqrt(y), np.exp(x), np.log(y), np.sin(x), np.cos(x), np.arctan2(x, y)]):
+        close(g, r.astype(f64), 1e-6, rtol=2e-6)
+    got = A.runWith(ctx, lambda p: A.map(lambda s: (A.floor(s), A.ceiling(s), A.round_(s), A.truncate(s), abs(s), A.signum(s), A.tanh(s), A.isnan(s / s)), p),
+                    np.concatenate([x, np.array([0.0, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5], f32)]))
+    xx = np.concatenate([x, np.array([0.0, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5], f32)])
+    half_away = np.where(xx >= 0, np.floor(xx + 0.5), np.ceil(xx - 0.5)).astype(i32)  # C round, not banker's
+    with np.errstate(invalid="ignore"):
+        refs = [np.floor(xx).astype(i32), np.ceil(xx).astype(i32), half_away, np.trunc(xx).astype(i32), np.abs(xx), np.sign(xx), np.tanh(xx), np.isnan(xx / xx)]
+    for k, (g, r) in enumerate(zip(got, refs)):
+        if r.dtype.kind == "f":
+            close(g, r.astype(f64), 1e-6, rtol=2e-6)
+        else:
+            assert np.array_equal(g.astype(r.dtype), r), k
+    # conversions and double precision
+    d = A.runWith(ctx, lambda p: A.map(lambda s: (A.cast(s, f64) * 1.0000000001, A.cast(A.cast(s, f64) * 1e10, i64), A.cond(s > 0.0, A.toFloating(A.floor(s), f32), s)), p), x)
+    assert np.array_equal(d[0], x.astype(f64) * 1.0000000001) and np.array_equal(d[1], (x.astype(f64) * 1e10).astype(i64))
+    assert np.array_equal(d[2], np.where(x > 0, np.floor(x), x))
+
+
+@pytest.mark.gpu
 def test_replicate_slice_reshape_and_friends(ctx, rng):
     m = rng.uniform(-1, 1, (301, 517)).astype(f32)
     v = rng.uniform(-1, 1, 517).astype(f32)
