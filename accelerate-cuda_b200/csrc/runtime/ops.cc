@@ -374,7 +374,7 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     const char *entry = group > 32 ? "foldSeg_block" : group == 32 ? "foldSeg" : group == 16 ? "foldSeg_g16" : group == 8 ? "foldSeg_g8" : "foldSeg_g4";
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
-    if (avg <= stage_len_max("ACCB_FOLDSEG_STAGE_MAX", 64) && rows * nseg >= 4096 && (rows == 1 || cols % 16 == 0) && pr.meta.v[6] > 0 &&
+    if (avg <= stage_len_max("ACCB_FOLDSEG_STAGE_MAX", 384) && rows * nseg >= 4096 && (rows == 1 || cols % 16 == 0) && pr.meta.v[6] > 0 &&
         (p.flags & ACCB_F_VEC)) {
         /* short segments: a block stages a run of consecutive segments in shared memory and every
          * thread reduces whole segments; the run is sized to fill 3/4 of the window on average */
@@ -383,9 +383,17 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
         TRY(get_function(ctx, k, "foldSeg_staged", &ps.fn, &ps.meta)); /* its block size is meta.v[5] */
         StreamScratch *sc = scratch_for(ctx, (cudaStream_t)stream);
         if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+        /* a run that overflows the window reads its last segments from global memory, so aim high */
+        long long fill = 6;
+        if (const char *e = getenv("ACCB_FOLDSEG_STAGE_FILL8")) fill = std::min(8, std::max(1, atoi(e)));
         const long long run =
-            std::min<long long>(std::max(32LL, (ps.meta.v[3] - 32) * 3 / 4 / std::max(1LL, avg)), 16LL * ps.meta.v[5]);
+            std::min<long long>(std::max(1LL, (ps.meta.v[3] - 32) * fill / 8 / std::max(1LL, avg)), 16LL * ps.meta.v[5]);
+        /* lanes per segment: a thread takes whole segments of up to ~100 elements; longer ones are shared by
+         * 8 lanes so that the few segments of a window still occupy the block */
+        long long lanes = avg <= 112 ? 1 : 8;
+        if (const char *e = getenv("ACCB_FOLDSEG_STAGE_LANES")) lanes = std::max(1, atoi(e));
         p.ip[4] = run;
+        p.ip[5] = lanes;
         p.aux[1] = sc->words + 2;
         const long long blocks = rows * ceil_div(nseg, run);
         if (blocks > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one foldSeg launch");

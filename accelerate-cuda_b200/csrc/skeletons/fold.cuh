@@ -33,6 +33,10 @@
 #include "../cubits/accb_warp.cuh"
 #include "../cubits/accb_tma.cuh"
 
+#ifndef ACCB_FOLD_SCALAR_UNROLL
+#define ACCB_FOLD_SCALAR_UNROLL 4 /* scalar loads in flight per lane where vector loads do not apply (segments) */
+#endif
+
 namespace accb {
 
 template <class T, class A = T>
@@ -130,7 +134,8 @@ __device__ __forceinline__ void fold_range(const accb_kparams &p, const Env &env
         acc.v = acc.have ? Fn::combine(acc.v, s) : s;
         acc.have = 1;
     }
-#pragma unroll 4
+    constexpr int kScalarUnroll = ACCB_FOLD_SCALAR_UNROLL;
+#pragma unroll kScalarUnroll
     for (long long i = lo + nvec * V + g; i < lo + len; i += G) {
         regs<1, In> a;
         T x[1];

@@ -24,7 +24,9 @@
  *   ip[0] rows, ip[1] cols (elements per row of the source), ip[2] units per
  *   row, ip[3] uniform unit length (fold over rows: the host passes the matrix
  *   as ONE row of rows x cols elements) or, with SEG, aux[0] = Int32 offsets of
- *   length units + 1; ip[4] = S.  aux[1] = error word of the bounded wait.
+ *   length units + 1; ip[4] = S; ip[5] = lanes per unit (1, or a power of two up to 32 for units of a few
+ *   hundred elements: then consecutive lanes read consecutive elements of their unit and combine by
+ *   shuffles).  aux[1] = error word of the bounded wait.
  * Segment offsets are Int32 (Execute.hs:320-324), so positions inside a row
  * are held in 32-bit registers.
  */
@@ -38,7 +40,7 @@
 #define ACCB_FOLD_STAGE_CTA 128
 #endif
 #ifndef ACCB_FOLD_STAGE_COOP
-#define ACCB_FOLD_STAGE_COOP 128 /* units longer than this are reduced by a whole warp */
+#define ACCB_FOLD_STAGE_COOP 512 /* where a thread owns whole units, longer ones are reduced by the whole warp */
 #endif
 #ifndef ACCB_FOLD_STAGE_BYTES
 #define ACCB_FOLD_STAGE_BYTES 16384 /* window size over all input components */
@@ -136,10 +138,10 @@ __device__ __forceinline__ void fold_staged_body(const accb_kparams &p) {
      * component size; the host checked that row starts are) */
     const int mis = (int)((org + d0) & 15);
     const int a0 = d0 - mis;
-    const bool fits = d1 - a0 <= WIN;
-    /* elements to stage: whole 16-byte units, but never beyond the end of the row */
+    /* elements to stage: whole 16-byte units, never beyond the end of the row, and as much of the run as the
+     * window holds (what does not fit -- a run with a few long segments -- is read from global memory) */
     const long long row_left = row0 + cols - (org + a0);
-    const int wlen = fits ? (int)min((long long)((d1 - a0 + 15) & ~15), row_left) : 0;
+    const int wlen = (int)min(min((long long)(d1 - a0 + 15) & ~15LL, (long long)WIN), row_left);
     const int w1 = a0 + wlen; /* positions in [a0, w1) are in shared memory */
 
     if (threadIdx.x == 0) {
@@ -158,6 +160,11 @@ __device__ __forceinline__ void fold_staged_body(const accb_kparams &p) {
         return (i >= a0 && i < w1) ? stage_get<Fn, WIN>(env, s_raw, i - a0, org + i, iseq)
                                    : global_get<Fn>(p, env, org + i, iseq);
     };
+    /* G lanes share a unit (ip[5]: 1 for short units, a power of two up to 32 for longer ones): lane g of the
+     * group takes elements g, g + G, ... -- consecutive lanes, consecutive words -- and the group's partial
+     * results are combined by shuffles.  With G = 1 a thread owns whole units and rotates its start. */
+    const int G = max(1, (int)p.ip[5]);
+    const int upw = 32 / G, g = lane % G, slot = lane / G; /* units per warp and pass; place in the group; group */
     int b = 0, e = 0;
     auto bounds = [&](int k) { /* of unit k of the run; (0, 0) beyond it */
         b = e = 0;
@@ -171,8 +178,8 @@ __device__ __forceinline__ void fold_staged_body(const accb_kparams &p) {
             }
         }
     };
-    bounds(warp * 32 + lane); /* fetched while the copy is in flight */
-    __syncthreads();          /* barrier initialised, tail elements written */
+    bounds(warp * upw + slot); /* fetched while the copy is in flight */
+    __syncthreads();           /* barrier initialised, tail elements written */
     {
         int tries = 0;
         while (!mbar_try_wait(&s_bar, 0)) {
@@ -182,45 +189,57 @@ __device__ __forceinline__ void fold_staged_body(const accb_kparams &p) {
             }
         }
     }
-    const int cta = blockDim.x;
-    for (int k0 = warp * 32; k0 < cnt; k0 += cta) {
-        const int k = k0 + lane;
+    const int per_pass = (blockDim.x / 32) * upw;
+    for (int k0 = warp * upw; k0 < cnt; k0 += per_pass) {
+        const int k = k0 + slot;
         const bool valid = k < cnt;
-        if (k0 != warp * 32) bounds(k);
+        if (k0 != warp * upw) bounds(k);
         const int len = e - b;
-        const bool coop = len > ACCB_FOLD_STAGE_COOP;
         O acc;
         acc.have = 0;
-        if (valid && !coop && len > 0) {
-            /* one loop of len trips for every lane (two loops, before and after the wrap, would
-             * have different trip counts per lane and run one after the other) */
-            int i = b + ((lane * len) >> 5);
-            if (b >= a0 && e <= w1) {
+        if (G == 1) {
+            const bool coop = len > ACCB_FOLD_STAGE_COOP;
+            if (valid && !coop && len > 0) {
+                /* one loop of len trips for every lane (two loops, before and after the wrap, would
+                 * have different trip counts per lane and run one after the other) */
+                int i = b + ((lane * len) >> 5);
+                if (b >= a0 && e <= w1) {
 #pragma unroll 4
-                for (int j = 0; j < len; ++j) {
-                    add(acc, stage_get<Fn, WIN>(env, s_raw, i - a0, org + i, iseq));
-                    if (++i == e) i = b;
-                }
-            } else {
-                for (int j = 0; j < len; ++j) {
-                    add(acc, at(i));
-                    if (++i == e) i = b;
+                    for (int j = 0; j < len; ++j) {
+                        add(acc, stage_get<Fn, WIN>(env, s_raw, i - a0, org + i, iseq));
+                        if (++i == e) i = b;
+                    }
+                } else {
+                    for (int j = 0; j < len; ++j) {
+                        add(acc, at(i));
+                        if (++i == e) i = b;
+                    }
                 }
             }
-        }
-        unsigned m = __ballot_sync(FULL, valid && coop);
-        while (m) { /* long units: the whole warp, lane-strided */
-            const int src = __ffs(m) - 1;
-            m &= m - 1;
-            const int bb = __shfl_sync(FULL, b, src), ee = __shfl_sync(FULL, e, src);
-            O part;
-            part.have = 0;
+            unsigned m = __ballot_sync(FULL, valid && coop);
+            while (m) { /* outliers: the whole warp, lane-strided */
+                const int src = __ffs(m) - 1;
+                m &= m - 1;
+                const int bb = __shfl_sync(FULL, b, src), ee = __shfl_sync(FULL, e, src);
+                O part;
+                part.have = 0;
 #pragma unroll 4
-            for (int i = bb + lane; i < ee; i += 32) add(part, at(i));
-            part = warp_reduce_xor(part, oc);
-            if (lane == src) acc = part;
+                for (int i = bb + lane; i < ee; i += 32) add(part, at(i));
+                part = warp_reduce_xor(part, oc);
+                if (lane == src) acc = part;
+            }
+        } else {
+            /* (units whose length is a multiple of 32 G put the groups of a warp on the same banks; walking
+             * them in rotated chunks of 32 elements cost more instructions than the conflicts do) */
+            if (valid && b >= a0 && e <= w1) {
+#pragma unroll 4
+                for (int i = b + g; i < e; i += G) add(acc, stage_get<Fn, WIN>(env, s_raw, i - a0, org + i, iseq));
+            } else if (valid) {
+                for (int i = b + g; i < e; i += G) add(acc, at(i));
+            }
+            for (int m = G >> 1; m > 0; m >>= 1) acc = oc(acc, shfl_xor(acc, m)); /* stays inside the aligned group */
         }
-        if (valid) {
+        if (valid && g == 0) {
             if (seeded) {
                 const A z = Fn::lift(fold_seed<Fn>(p));
                 acc.v = acc.have ? Fn::combine(acc.v, z) : z;

@@ -255,7 +255,8 @@ def test_fold_seg(ctx, P, torch_cuda, oracle, rng):
     close(of.cpu().numpy(), oracle.fold_seg_f32(xf, offs), 1e-7)
 
 
-@pytest.mark.parametrize("nseg,mean", [(60000, 3), (30000, 12), (9000, 40), (9000, 100), (300, 3000), (12, 20000)])
+@pytest.mark.parametrize("nseg,mean", [(60000, 3), (30000, 12), (9000, 40), (9000, 100), (300, 3000), (12, 20000),
+                                       (20000, 150), (6000, 300), (5000, 1000)])  # staged with 8 lanes per segment; groups
 def test_fold_seg_by_segment_length(ctx, P, torch_cuda, oracle, rng, nseg, mean):
     """4, 8, 16 and 32 lanes or a whole block per segment, chosen by the average segment length."""
     t = torch_cuda
