@@ -39,7 +39,7 @@ OK, EINVAL, ECUDA, ENOMEM, ECOMPILE, EIO, EBOUNDS, ETIMEOUT, ENOTFOUND, ENODRIVE
 _STATUS = ["OK", "EINVAL", "ECUDA", "ENOMEM", "ECOMPILE", "EIO", "EBOUNDS", "ETIMEOUT", "ENOTFOUND", "ENODRIVER"]
 
 SCAN_LEFT, SCAN_RIGHT = 0, 1
-SCAN_EXCLUSIVE, SCAN_INCLUSIVE, SCAN_PRIME = 0, 1, 2
+SCAN_EXCLUSIVE, SCAN_INCLUSIVE, SCAN_PRIME, SCAN_INCLUSIVE_SEEDED = 0, 1, 2, 3
 SEED_ON_DEVICE = 0x100
 CLAMP, MIRROR, WRAP, CONSTANT = 0, 1, 2, 3
 BOUNDARY = {"clamp": CLAMP, "mirror": MIRROR, "wrap": WRAP, "constant": CONSTANT}
@@ -147,6 +147,20 @@ def lib() -> C.CDLL:
             "accb_program_run_graph": [vp, vp, arrp, arrp],
             "accb_program_run_host": [vp, arrp, arrp],
             "accb_program_destroy": [vp],
+            "accb_group_create": [C.POINTER(i32), i32, C.POINTER(vp)],
+            "accb_group_destroy": [vp],
+            "accb_group_size": [vp, C.POINTER(i32)],
+            "accb_group_context": [vp, i32, C.POINTER(vp)],
+            "accb_group_stream": [vp, i32, C.POINTER(vp)],
+            "accb_group_sync": [vp],
+            "accb_group_map": [vp, vp, arrp, i32, vp, sz, arrp],
+            "accb_group_fold_dim": [vp, vp, arrp, i32, C.POINTER(ll), ll, vp, sz, arrp],
+            "accb_group_fold_all": [vp, vp, vp, arrp, i32, C.POINTER(ll), vp, sz, C.POINTER(i32), arrp],
+            "accb_group_scan": [vp, vp, vp, vp, arrp, i32, C.POINTER(ll), i32, i32, vp, sz, sz, arrp, arrp],
+            "accb_group_permute": [vp, vp, vp, arrp, i32, C.POINTER(ll), vp, sz, C.POINTER(i32), arrp, i32],
+            "accb_group_stencil_layout": [vp, i32, i32, i32, i32, C.POINTER(i32), C.POINTER(i32)],
+            "accb_group_stencil_iterate": [vp, vp, arrp, arrp, C.POINTER(i32), i32, i32, i32, vp, sz,
+                                           C.POINTER(i32), C.POINTER(i32)],
             "accb_gen_uniform_f32": [vp, vp, vp, ll, ll, u64, u64, C.c_float, C.c_float],
             "accb_gen_uniform_i32": [vp, vp, vp, ll, ll, u64, u64, i32],
             "accb_gen_zipf_mix_i32": [vp, vp, vp, ll, ll, u64, vp, i32],
@@ -165,6 +179,8 @@ def lib() -> C.CDLL:
             getattr(L, name).restype = None
         L.accb_last_error.argtypes = [vp]
         L.accb_last_error.restype = C.c_char_p
+        L.accb_group_last_error.argtypes = [vp]
+        L.accb_group_last_error.restype = C.c_char_p
         L.accb_version.restype = C.c_char_p
         L.accelerateCreate.argtypes = [C.c_int32, vp]
         L.accelerateCreate.restype = vp
@@ -404,6 +420,106 @@ class Context:
 
     def flush_l2(self, stream=None):
         _check(lib().accb_flush_l2(self.handle, self._stream(stream)), self.handle)
+
+
+class Group:
+    """Several GPUs driven from one process (``accb_group_*``): rank r owns the r-th contiguous slab of every
+    array.  Per-rank arguments are lists with one entry per rank.  The reference has no multi-device execution
+    (its peer copy, CUDA/Array/Prim.hs:306-335, is never called)."""
+
+    def __init__(self, devices: Sequence[int]):
+        h = C.c_void_p()
+        devs = (C.c_int * len(devices))(*devices)
+        st = lib().accb_group_create(devs, len(devices), C.byref(h))
+        if st != OK:
+            _check(st)
+        self.handle, self.devices, self.size = h, list(devices), len(devices)
+        self.contexts, self.streams = [], []
+        for r in range(self.size):
+            c, s = C.c_void_p(), C.c_void_p()
+            self._check(lib().accb_group_context(h, r, C.byref(c)))
+            self._check(lib().accb_group_stream(h, r, C.byref(s)))
+            ctx = Context.__new__(Context)  # borrowed: destroyed with the group
+            ctx.handle, ctx.device, ctx._kernels = c, devices[r], {}
+            self.contexts.append(ctx)
+            self.streams.append(s.value)
+
+    def _check(self, status: int):
+        if status != OK:
+            msg = lib().accb_group_last_error(self.handle)
+            raise AccbError(status, msg.decode(errors="replace") if msg else "")
+
+    def destroy(self):
+        if self.handle:
+            lib().accb_group_destroy(self.handle)
+            self.handle = None
+
+    def sync(self):
+        self._check(lib().accb_group_sync(self.handle))
+
+    def _k(self, k):
+        return self.contexts[0]._k(k)  # one kernel object serves every context
+
+    def _env(self, env):
+        flat = [a for rank_env in env for a in rank_env]
+        return _arr_list(flat), (len(env[0]) if env else 0)
+
+    def _lls(self, xs):
+        return (C.c_longlong * len(xs))(*[int(x) for x in xs])
+
+    @staticmethod
+    def _cb(arr):
+        cb = [c.element_size() for c in _components(arr)]
+        return (C.c_int * len(cb))(*cb)
+
+    def map(self, kernel, env, out, scalars=None):
+        sb, sn = _bytes_of(scalars)
+        e, nenv = self._env(env)
+        self._check(lib().accb_group_map(self.handle, self._k(kernel), e, nenv, sb, sn, _arr_list(out)))
+
+    def fold_dim(self, kernel, env, rows, cols: int, out, seed=None):
+        sb, sn = _bytes_of(seed)
+        e, nenv = self._env(env)
+        self._check(lib().accb_group_fold_dim(self.handle, self._k(kernel), e, nenv, self._lls(rows), cols, sb, sn,
+                                              _arr_list(out)))
+
+    def fold_all(self, kernel, combine_kernel, env, n, out, seed=None):
+        sb, sn = _bytes_of(seed)
+        e, nenv = self._env(env)
+        outs = (accb_array * self.size)(*[to_accb_array(o, shape=()) for o in out])
+        self._check(lib().accb_group_fold_all(self.handle, self._k(kernel), self._k(combine_kernel), e, nenv,
+                                              self._lls(n), sb, sn, self._cb(out[0]), outs))
+
+    def scan(self, kernel, total_kernel, carry_kernel, env, n, out, direction=SCAN_LEFT, kind=SCAN_EXCLUSIVE,
+             seed=None, total=None):
+        sb, sn = _bytes_of(seed)
+        e, nenv = self._env(env)
+        tot = (accb_array * self.size)(*[to_accb_array(t, shape=()) for t in total]) if total is not None else None
+        self._check(lib().accb_group_scan(self.handle, self._k(kernel), self._k(total_kernel), self._k(carry_kernel),
+                                          e, nenv, self._lls(n), direction, kind, sb, sn,
+                                          _components(out[0])[0].element_size(), _arr_list(out), tot))
+
+    def permute(self, kernel, merge_kernel, env, n_src, out, scalars=None, broadcast=False):
+        sb, sn = _bytes_of(scalars)
+        e, nenv = self._env(env)
+        self._check(lib().accb_group_permute(self.handle, self._k(kernel), self._k(merge_kernel), e, nenv,
+                                             self._lls(n_src), sb, sn, self._cb(out[0]), _arr_list(out),
+                                             1 if broadcast else 0))
+
+    def stencil_layout(self, rank: int, iters: int, ry: int, boundary="clamp"):
+        t, b = C.c_int(), C.c_int()
+        self._check(lib().accb_group_stencil_layout(self.handle, rank, iters, ry, BOUNDARY[boundary], C.byref(t),
+                                                    C.byref(b)))
+        return t.value, b.value
+
+    def stencil_iterate(self, kernel, a, b, rows, iters: int, ry: int, boundary="clamp", constant=None):
+        """Returns the list of slabs (``a`` or ``b``) that hold the result in their own rows."""
+        cb, cn = _bytes_of(constant)
+        in_b = C.c_int()
+        self._check(lib().accb_group_stencil_iterate(self.handle, self._k(kernel), _arr_list(a), _arr_list(b),
+                                                     (C.c_int * len(rows))(*rows), iters, ry, BOUNDARY[boundary],
+                                                     cb, cn, self._cb(a[0]), C.byref(in_b)))
+        return b if in_b.value else a
 
 
 # ------------------------------------------------------------------ programs

@@ -414,6 +414,7 @@ int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_
     const bool right = direction == ACCB_SCAN_RIGHT;
     const bool seed_on_device = (kind & ACCB_SEED_ON_DEVICE) != 0;
     kind &= ~ACCB_SEED_ON_DEVICE;
+    if (kind < ACCB_SCAN_EXCLUSIVE || kind > ACCB_SCAN_INCLUSIVE_SEEDED) return fail(ctx, ACCB_EINVAL, "unknown scan kind %d", kind);
     if (kind != ACCB_SCAN_INCLUSIVE && !seed) return fail(ctx, ACCB_EINVAL, "scanl/scanr/scan' need a seed");
     if (kind == ACCB_SCAN_INCLUSIVE && seed) return fail(ctx, ACCB_EINVAL, "scanl1/scanr1 take no seed");
     if (kind == ACCB_SCAN_PRIME && !total) return fail(ctx, ACCB_EINVAL, "scan' needs a total array");
@@ -432,8 +433,8 @@ int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_
     p.ip[3] = -1;
     p.ip[4] = -1;
     const char *entry;
-    if (kind == ACCB_SCAN_INCLUSIVE) {
-        entry = right ? "scanr1" : "scanl1";
+    if (kind == ACCB_SCAN_INCLUSIVE || kind == ACCB_SCAN_INCLUSIVE_SEEDED) {
+        entry = right ? "scanr1" : "scanl1"; /* with a seed: the look-back of the first tile starts from it */
     } else if (kind == ACCB_SCAN_PRIME) {
         entry = right ? "scanr" : "scanl";
         TRY(fill_out(ctx, p, total, out->ncomp));

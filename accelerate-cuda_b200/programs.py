@@ -372,6 +372,15 @@ struct Saxpy {{
 }};
 """)
 
+# zipWith (+) on Int32: merges the partial destinations of a permute (+) that ran on several GPUs
+ZIP_ADD_I32 = KernelSpec("map", "ZipAddI", f"""
+struct ZipAddI {{
+    using In = accb::types<int, int>;
+    using Out = accb::types<int>;
+    {_D} void apply(const accb::Env &, long long, int x, int y, int &o) {{ o = (int)((unsigned)x + (unsigned)y); }}
+}};
+""")
+
 # generate: a function of the index only
 IOTA_SQ = KernelSpec("map", "IotaSq", f"""
 struct IotaSq {{

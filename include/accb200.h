@@ -189,7 +189,11 @@ enum { ACCB_SCAN_LEFT = 0, ACCB_SCAN_RIGHT = 1 };
 enum {
     ACCB_SCAN_EXCLUSIVE = 0, /* scanl / scanr : out has n+1 elements            */
     ACCB_SCAN_INCLUSIVE = 1, /* scanl1 / scanr1: out has n elements, no seed    */
-    ACCB_SCAN_PRIME = 2      /* scanl' / scanr': out has n elements + `total`   */
+    ACCB_SCAN_PRIME = 2,     /* scanl' / scanr': out has n elements + `total`   */
+    /* scanl1 / scanr1 continuing from a seed: out[i] = seed (+) x0 (+) .. (+) xi,
+     * n elements.  How a later slab of a sharded scan1 continues from the carry
+     * of the earlier slabs; the reference has no such form. */
+    ACCB_SCAN_INCLUSIVE_SEEDED = 3
 };
 /* OR into `kind`: `seed` is a DEVICE pointer to the seed value, written by
  * earlier work on the same stream (the carry of a sharded scan). */
@@ -330,6 +334,71 @@ ACCB_API int accb_program_run_graph(accb_program *p, accb_stream stream, const a
  * host_in[i] / host_out[j] point to one host buffer per component. */
 ACCB_API int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array *host_out);
 ACCB_API int accb_program_destroy(accb_program *p);
+
+/* ------------------------------------------ several GPUs from one process
+ * A group is an ordered list of devices ("ranks"), each with its own context
+ * and stream.  Arrays are sharded by contiguous slabs of the outermost index
+ * space, rank 0 holding the first slab.  Every accb_group_* launch enqueues
+ * work on all ranks' streams and returns; ordering between devices is done
+ * with events; exchanged data is copied into the receiving device's OWN memory
+ * (peer copy) before a kernel reads it, and no kernel waits for another device.
+ * The reference drives one device per context; its only multi-device primitive
+ * is the peer copy of CUDA/Array/Prim.hs:306-335, which nothing calls.
+ * Per-rank arguments are rank-major: env[r * nenv + j], out[r], n[r].  A device
+ * may appear more than once in the list (its ranks then share that GPU).  The
+ * caller orders its own work against the group's streams (accb_group_stream,
+ * accb_group_sync).                                                         */
+typedef struct accb_group accb_group;
+ACCB_API int accb_group_create(const int *devices, int n, accb_group **grp);
+ACCB_API int accb_group_destroy(accb_group *grp);
+ACCB_API int accb_group_size(accb_group *grp, int *n);
+ACCB_API int accb_group_context(accb_group *grp, int rank, accb_context **ctx); /* borrowed */
+ACCB_API int accb_group_stream(accb_group *grp, int rank, accb_stream *stream); /* borrowed */
+ACCB_API int accb_group_sync(accb_group *grp); /* waits for every rank; reports bounded-wait failures */
+ACCB_API const char *accb_group_last_error(accb_group *grp);
+/* map / generate / transform over slabs: no exchange */
+ACCB_API int accb_group_map(accb_group *grp, accb_kernel *k, const accb_array *env, int nenv, const void *scalars,
+                            size_t scalar_bytes, const accb_array *out);
+/* fold over the innermost dimension, rows[r] rows on rank r: no exchange */
+ACCB_API int accb_group_fold_dim(accb_group *grp, accb_kernel *k, const accb_array *env, int nenv,
+                                 const long long *rows, long long cols, const void *seed, size_t seed_bytes,
+                                 const accb_array *out);
+/* foldAll / fold1All (seed NULL): each rank reduces its n[r] >= 1 elements with `k`; the partials are copied to
+ * rank 0 and reduced IN RANK ORDER, with the seed, by `k_combine` -- a fold_all kernel with the same combiner whose
+ * functor reads one plain array of elements; every out[r] (a Scalar on rank r) receives the result. */
+ACCB_API int accb_group_fold_all(accb_group *grp, accb_kernel *k, accb_kernel *k_combine, const accb_array *env,
+                                 int nenv, const long long *n, const void *seed, size_t seed_bytes,
+                                 const int *comp_bytes, const accb_array *out);
+/* All six scans over the concatenation of the slabs (n[r] >= 1 elements on rank r; one-component elements of
+ * elt_bytes).  `k` scans a slab; `k_total` is the fold_all kernel of the same producer and combiner (the slab
+ * totals: one extra read of the slab); `k_carry` a scan kernel with the same combiner over a plain array, run on
+ * rank 0 over the totals.  Each rank then continues from the carry of the slabs before it (after it, for right
+ * scans), read from its own memory.  out[r] has n[r] elements; for ACCB_SCAN_EXCLUSIVE the LAST rank's has
+ * n[r] + 1 (scanl: the total; scanr: the seed).  total[r] (needed for ACCB_SCAN_PRIME, else may be NULL) receives
+ * the running total at the end of rank r's slab: the grand total is on the last rank (left) or rank 0 (right). */
+ACCB_API int accb_group_scan(accb_group *grp, accb_kernel *k, accb_kernel *k_total, accb_kernel *k_carry,
+                             const accb_array *env, int nenv, const long long *n, int direction, int kind,
+                             const void *seed, size_t seed_bytes, size_t elt_bytes, const accb_array *out,
+                             const accb_array *total);
+/* permute with an associative and commutative combiner: every out[r] is a full-size destination; out[0] must hold
+ * the defaults and out[r > 0] the combiner's neutral element.  Each rank scatters its n_src[r] source elements;
+ * the partial destinations are copied to rank 0 one after another and merged into out[0] by `k_merge`, a map
+ * kernel computing combine(a, b) of two plain arrays.  With `broadcast` every out[r] then receives the result. */
+ACCB_API int accb_group_permute(accb_group *grp, accb_kernel *k, accb_kernel *k_merge, const accb_array *env,
+                                int nenv, const long long *n_src, const void *scalars, size_t scalar_bytes,
+                                const int *comp_bytes, const accb_array *out, int broadcast);
+/* `iters` applications of a stencil on row slabs with ONE exchange: a[r] and b[r] are slabs of
+ * pad_top + rows[r] + pad_bottom rows (accb_group_stencil_layout: iters * ry rows towards each neighbouring
+ * rank, none at the global top and bottom unless the boundary is ACCB_WRAP), the rank's rows[r] >= iters * ry
+ * own rows in the middle of a[r].  The halos are filled from the neighbours' rows by peer copies, then all
+ * applications run on the padded slab: what the kernel's boundary treatment does at a padded edge creeps inwards
+ * by ry rows per application, exactly as far as the halo reaches.  *result_in_b tells which buffer holds the
+ * result (own rows only; the halos hold garbage).  `ry` is the stencil's reach along the outermost dimension. */
+ACCB_API int accb_group_stencil_layout(accb_group *grp, int rank, int iters, int ry, int boundary, int *pad_top,
+                                       int *pad_bottom);
+ACCB_API int accb_group_stencil_iterate(accb_group *grp, accb_kernel *k, const accb_array *a, const accb_array *b,
+                                        const int *rows, int iters, int ry, int boundary, const void *constant,
+                                        size_t constant_bytes, const int *comp_bytes, int *result_in_b);
 
 /* -------------------------------------------- synthetic benchmark inputs
  * Index-addressable generators (any shard can produce its own slice).      */

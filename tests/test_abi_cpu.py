@@ -55,6 +55,19 @@ def test_no_cpu_fallback_without_a_driver(accb):
         accb.Context(0)
     assert e.value.status == accb.ENODRIVER
     assert L.accelerateCreate(0, None) is None
+    with pytest.raises(accb.AccbError) as e:
+        accb.Group([0, 0])
+    assert e.value.status == accb.ENODRIVER
+
+
+def test_header_is_plain_c_and_the_library_links_from_c(tmp_path):
+    """What a cgo / hsc2hs stub needs: `include/accb200.h` under -std=c99 -pedantic, and -laccb200 from a C program."""
+    exe = tmp_path / "abi_smoke"
+    subprocess.run(["gcc", "-std=c99", "-pedantic", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "cpp", "abi_smoke.c"), "-L", PKG, "-laccb200",
+                    f"-Wl,-rpath,{PKG}", "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.strip() == "OK", out.stdout + out.stderr
 
 
 def test_product_never_touches_the_oracle():
