@@ -173,6 +173,7 @@ bool trace_enabled(const char *family);
 
 /* launching */
 int get_function(accb_context *ctx, accb_kernel *k, const char *entry, CUfunction *fn, KernelMeta *meta);
+void forget_context(accb_context *ctx); /* unload the modules loaded for a context that is being destroyed */
 int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blocks_per_sm);
 int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, size_t smem,
            cudaStream_t stream, const accb_kparams &p, bool prefer_smem = true);

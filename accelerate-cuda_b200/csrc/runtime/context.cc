@@ -203,6 +203,7 @@ int accb_context_destroy(accb_context *ctx) {
         std::lock_guard<std::recursive_mutex> lock_(ctx->mu);
         CtxGuard g(ctx);
         cudaDeviceSynchronize();
+        forget_context(ctx);
         ctx->mem.clear();
         for (auto &kv : ctx->scratch) {
             cudaFree(kv.second.status);

@@ -353,6 +353,20 @@ int get_function(accb_context *ctx, accb_kernel *k, const char *entry, CUfunctio
     return ACCB_OK;
 }
 
+/* A context is going away: unload the modules loaded for it and drop their entries, which are keyed by the
+ * context's address -- a later context may be allocated at the same address, on another device. */
+void forget_context(accb_context *ctx) {
+    std::lock_guard<std::mutex> l(g_table_mu);
+    for (auto &kv : g_table) {
+        accb_kernel *k = kv.second;
+        std::lock_guard<std::mutex> lk(k->mu);
+        auto it = k->loaded.find(ctx);
+        if (it == k->loaded.end()) continue;
+        if (it->second.mod) driver().ModuleUnload(it->second.mod);
+        k->loaded.erase(it);
+    }
+}
+
 }  // namespace accb_rt
 
 using namespace accb_rt;
