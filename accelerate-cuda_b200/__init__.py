@@ -147,6 +147,7 @@ def lib() -> C.CDLL:
             "accb_program_run_graph": [vp, vp, arrp, arrp],
             "accb_program_run_host": [vp, arrp, arrp],
             "accb_program_destroy": [vp],
+            "accb_awhile": [vp, vp, vp, arrp, i32, ll, C.POINTER(ll)],
             "accb_group_create": [C.POINTER(i32), i32, C.POINTER(vp)],
             "accb_group_destroy": [vp],
             "accb_group_size": [vp, C.POINTER(i32)],
@@ -623,6 +624,20 @@ class Afun:
         if self.handle:
             lib().accb_program_destroy(self.handle)
             self.handle = None
+
+
+def awhile(cond: Afun, body: Afun, state: Sequence, device: bool = True, max_iters: int = 1 << 20, stream=None,
+           count: bool = False):
+    """``awhile cond body`` on device arrays, in place: while ``cond(*state)`` (one Scalar Bool) holds, ``state``
+    is replaced by ``body(*state)``.  ``device=True`` runs the whole loop as one CUDA graph with a conditional
+    WHILE node -- the flag never reaches the host and the call returns at once; ``device=False`` is the
+    reference's scheme, one read-back of the flag per iteration (Awhile, CUDA/Execute.hs:236-244).
+    ``count=True`` waits and returns how often the body ran."""
+    it = C.c_longlong(0)
+    _check(lib().accb_awhile(cond.handle, body.handle, Context._stream(stream), _arr_list(state),
+                             1 if device else 0, max_iters, C.byref(it) if (count or not device) else None),
+           body.ctx.handle)
+    return it.value if (count or not device) else None
 
 
 # builder functions used inside a traced function --------------------------------

@@ -72,6 +72,14 @@ struct accb_program {
     cudaStream_t graph_stream = nullptr;
     unsigned long long graph_generation = 0; /* the context's buffer_generation when it was recorded */
     std::vector<accb_array> graph_inputs, graph_outputs;
+    /* awhile with this program as the body, recorded as a graph with a conditional WHILE node */
+    cudaGraphExec_t loop_exec = nullptr;
+    cudaStream_t loop_stream = nullptr;
+    accb_program *loop_cond = nullptr;
+    unsigned long long loop_generation = 0;
+    long long loop_max_iters = 0;
+    std::vector<accb_array> loop_state;
+    unsigned long long *loop_words = nullptr; /* device: [0] times the body ran, [1] stopped by the limit */
 };
 
 namespace {
@@ -675,6 +683,201 @@ int accb_program_run_graph(accb_program *p, accb_stream stream, const accb_array
     return ACCB_OK;
 }
 
+}  // extern "C"
+
+/* ---------------------------------------------------------------- awhile */
+namespace {
+
+/* Decides whether the loop goes on.  Runs once ahead of the WHILE node (in_body = 0: resets the counters) and
+ * once at the end of every pass through its body.  The limit keeps a loop whose condition never turns false
+ * from occupying the GPU for ever. */
+__global__ void awhile_step(cudaGraphConditionalHandle handle, const unsigned char *flag, unsigned long long *words,
+                            unsigned long long max_iters, int in_body) {
+    unsigned long long done = 0;
+    if (in_body) {
+        done = words[0] + 1;
+        words[0] = done;
+    } else {
+        words[0] = 0;
+        words[1] = 0;
+    }
+    unsigned go = *flag != 0;
+    if (go && done >= max_iters) {
+        go = 0;
+        words[1] = 1;
+    }
+    cudaGraphSetConditional(handle, go);
+}
+
+bool same_shape(const accb_array &a, const accb_array &b) {
+    if (a.rank != b.rank || a.ncomp != b.ncomp) return false;
+    for (int d = 0; d < a.rank; ++d)
+        if (a.shape[d] != b.shape[d]) return false;
+    return true;
+}
+
+/* state <- the body's results, on the stream */
+int copy_back(accb_program *body, cudaStream_t s, const accb_array *state, const std::vector<accb_array> &outs) {
+    accb_context *ctx = body->ctx;
+    for (int i = 0; i < body->ninputs; ++i) {
+        if (!same_shape(state[i], outs[i]))
+            return fail(ctx, ACCB_EINVAL, "awhile: result %d of the body differs in shape from the state it replaces", i);
+        const accb_value_type &t = body->types[body->outputs[i]];
+        const long long n = size_of(state[i]);
+        for (int c = 0; c < t.ncomp; ++c) {
+            if (outs[i].ptr[c] == state[i].ptr[c] || n == 0) continue; /* passed through unchanged */
+            TRY(check_cuda(ctx, cudaMemcpyAsync(state[i].ptr[c], outs[i].ptr[c], (size_t)n * t.comp_bytes[c],
+                                                cudaMemcpyDeviceToDevice, s), "cudaMemcpyAsync"));
+        }
+    }
+    return ACCB_OK;
+}
+
+int awhile_check(accb_program *cond, accb_program *body, const accb_array *state, long long max_iters) {
+    accb_context *ctx = body->ctx;
+    if (cond->ctx != ctx) return fail(ctx, ACCB_EINVAL, "awhile: condition and body belong to different contexts");
+    if (!state || body->ninputs < 1 || cond->ninputs != body->ninputs || (int)body->outputs.size() != body->ninputs)
+        return fail(ctx, ACCB_EINVAL, "awhile: the condition takes, and the body takes and returns, the state arrays");
+    if (cond->outputs.size() != 1) return fail(ctx, ACCB_EINVAL, "awhile: the condition has one result");
+    const accb_value_type &ft = cond->types[cond->outputs[0]];
+    if (ft.ncomp != 1 || ft.comp_bytes[0] != 1) return fail(ctx, ACCB_EINVAL, "awhile: the condition yields a Scalar Bool");
+    for (int i = 0; i < body->ninputs; ++i) {
+        const accb_value_type &a = body->types[i], &b = body->types[body->outputs[i]], &c = cond->types[i];
+        bool ok = a.ncomp == b.ncomp && a.ncomp == c.ncomp && a.rank == b.rank;
+        for (int k = 0; ok && k < a.ncomp; ++k) ok = a.comp_bytes[k] == b.comp_bytes[k] && a.comp_bytes[k] == c.comp_bytes[k];
+        if (!ok) return fail(ctx, ACCB_EINVAL, "awhile: state array %d changes type", i);
+    }
+    if (max_iters < 1) return fail(ctx, ACCB_EINVAL, "awhile: max_iters must be positive");
+    return ACCB_OK;
+}
+
+/* one graph: [cond, decide] -> WHILE { body, copy back, cond, decide } */
+int awhile_record(accb_program *cond, accb_program *body, cudaStream_t s, const accb_array *state, long long max_iters) {
+    accb_context *ctx = body->ctx;
+    if (body->loop_exec) {
+        cudaGraphExecDestroy(body->loop_exec);
+        body->loop_exec = nullptr;
+    }
+    if (!body->loop_words)
+        TRY(check_cuda(ctx, cudaMalloc((void **)&body->loop_words, 2 * sizeof(unsigned long long)), "cudaMalloc"));
+    /* a run outside any capture sizes every pooled and scratch buffer and loads the kernels; the body's results
+     * are not copied back, so the state is untouched */
+    accb_array flag;
+    std::vector<accb_array> outs(body->outputs.size());
+    TRY(run_internal(cond, s, state, &flag, false));
+    TRY(run_internal(body, s, state, outs.data(), false));
+    TRY(check_cuda(ctx, cudaStreamSynchronize(s), "cudaStreamSynchronize"));
+
+    cudaGraph_t g = nullptr;
+    TRY(check_cuda(ctx, cudaGraphCreate(&g, 0), "cudaGraphCreate"));
+    struct Guard {
+        cudaGraph_t g;
+        ~Guard() { cudaGraphDestroy(g); }
+    } guard{g};
+    cudaGraphConditionalHandle handle;
+    TRY(check_cuda(ctx, cudaGraphConditionalHandleCreate(&handle, g, 0, cudaGraphCondAssignDefault),
+                   "cudaGraphConditionalHandleCreate"));
+    /* ahead of the loop */
+    TRY(check_cuda(ctx, cudaStreamBeginCaptureToGraph(s, g, nullptr, nullptr, 0, cudaStreamCaptureModeRelaxed),
+                   "cudaStreamBeginCaptureToGraph"));
+    int st = run_internal(cond, s, state, &flag, false);
+    std::vector<cudaGraphNode_t> deps;
+    if (st == ACCB_OK) {
+        awhile_step<<<1, 1, 0, s>>>(handle, static_cast<const unsigned char *>(flag.ptr[0]), body->loop_words,
+                                    (unsigned long long)max_iters, 0);
+        cudaStreamCaptureStatus cs;
+        const cudaGraphNode_t *d = nullptr;
+        size_t nd = 0;
+        st = check_cuda(ctx, cudaStreamGetCaptureInfo(s, &cs, nullptr, nullptr, &d, &nd), "cudaStreamGetCaptureInfo");
+        if (st == ACCB_OK) deps.assign(d, d + nd);
+    }
+    cudaGraph_t ended = nullptr;
+    cudaError_t ce = cudaStreamEndCapture(s, &ended);
+    TRY(st);
+    TRY(check_cuda(ctx, ce, "cudaStreamEndCapture"));
+    /* the loop */
+    cudaGraphNodeParams params = {cudaGraphNodeTypeConditional}; /* the remaining members zero */
+    params.type = cudaGraphNodeTypeConditional;
+    params.conditional.handle = handle;
+    params.conditional.type = cudaGraphCondTypeWhile;
+    params.conditional.size = 1;
+    cudaGraphNode_t loop;
+    TRY(check_cuda(ctx, cudaGraphAddNode(&loop, g, deps.data(), deps.size(), &params), "cudaGraphAddNode (while)"));
+    cudaGraph_t inside = params.conditional.phGraph_out[0];
+    TRY(check_cuda(ctx, cudaStreamBeginCaptureToGraph(s, inside, nullptr, nullptr, 0, cudaStreamCaptureModeRelaxed),
+                   "cudaStreamBeginCaptureToGraph"));
+    st = run_internal(body, s, state, outs.data(), false);
+    if (st == ACCB_OK) st = copy_back(body, s, state, outs);
+    if (st == ACCB_OK) st = run_internal(cond, s, state, &flag, false);
+    if (st == ACCB_OK)
+        awhile_step<<<1, 1, 0, s>>>(handle, static_cast<const unsigned char *>(flag.ptr[0]), body->loop_words,
+                                    (unsigned long long)max_iters, 1);
+    ce = cudaStreamEndCapture(s, &ended);
+    TRY(st);
+    TRY(check_cuda(ctx, ce, "cudaStreamEndCapture"));
+    const cudaError_t ci = cudaGraphInstantiate(&body->loop_exec, g, 0);
+    if (ci != cudaSuccess) body->loop_exec = nullptr;
+    TRY(check_cuda(ctx, ci, "cudaGraphInstantiate"));
+    body->loop_stream = s;
+    body->loop_cond = cond;
+    body->loop_generation = ctx->buffer_generation;
+    body->loop_max_iters = max_iters;
+    body->loop_state.assign(state, state + body->ninputs);
+    return ACCB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int accb_awhile(accb_program *cond, accb_program *body, accb_stream stream, const accb_array *state, int mode,
+                long long max_iters, long long *iterations) {
+    if (!cond) return fail(nullptr, ACCB_EINVAL, "null program");
+    PLOCK(body);
+    accb_context *ctx = body->ctx;
+    TRY(awhile_check(cond, body, state, max_iters));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (mode == ACCB_AWHILE_HOST) {
+        long long done = 0;
+        accb_array flag;
+        std::vector<accb_array> outs(body->outputs.size());
+        for (;;) {
+            TRY(run_internal(cond, s, state, &flag, false));
+            unsigned char go = 0;
+            TRY(check_cuda(ctx, cudaMemcpyAsync(&go, flag.ptr[0], 1, cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync"));
+            TRY(check_cuda(ctx, cudaStreamSynchronize(s), "cudaStreamSynchronize"));
+            if (!go) break;
+            if (done >= max_iters) {
+                if (iterations) *iterations = done;
+                return fail(ctx, ACCB_ETIMEOUT, "awhile: still true after %lld iterations", done);
+            }
+            TRY(run_internal(body, s, state, outs.data(), false));
+            TRY(copy_back(body, s, state, outs));
+            ++done;
+        }
+        if (iterations) *iterations = done;
+        return ACCB_OK;
+    }
+    if (mode != ACCB_AWHILE_DEVICE) return fail(ctx, ACCB_EINVAL, "awhile: unknown mode %d", mode);
+    if (!s) return fail(ctx, ACCB_EINVAL, "a device-resident loop needs a stream of its own (the default stream cannot be captured)");
+    bool same = body->loop_exec && body->loop_stream == s && body->loop_cond == cond &&
+                body->loop_generation == ctx->buffer_generation && body->loop_max_iters == max_iters;
+    for (int i = 0; same && i < body->ninputs; ++i) {
+        same = same_shape(body->loop_state[i], state[i]);
+        for (int c = 0; same && c < state[i].ncomp; ++c) same = body->loop_state[i].ptr[c] == state[i].ptr[c];
+    }
+    if (!same) TRY(awhile_record(cond, body, s, state, max_iters));
+    TRY(check_cuda(ctx, cudaGraphLaunch(body->loop_exec, s), "cudaGraphLaunch"));
+    if (iterations) {
+        unsigned long long w[2] = {0, 0};
+        TRY(check_cuda(ctx, cudaMemcpyAsync(w, body->loop_words, sizeof w, cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync"));
+        TRY(check_cuda(ctx, cudaStreamSynchronize(s), "cudaStreamSynchronize"));
+        *iterations = (long long)w[0];
+        if (w[1]) return fail(ctx, ACCB_ETIMEOUT, "awhile: still true after %lld iterations", (long long)w[0]);
+    }
+    return ACCB_OK;
+}
+
 int accb_program_destroy(accb_program *p) {
     if (!p) return ACCB_OK;
     {
@@ -682,6 +885,8 @@ int accb_program_destroy(accb_program *p) {
         CtxGuard g(p->ctx);
         cudaDeviceSynchronize();
         if (p->graph_exec) cudaGraphExecDestroy(p->graph_exec);
+        if (p->loop_exec) cudaGraphExecDestroy(p->loop_exec);
+        if (p->loop_words) cudaFree(p->loop_words);
         for (auto &v : p->pool)
             for (auto &b : v)
                 if (b.ptr) cudaFree(b.ptr);

@@ -1615,3 +1615,50 @@ def runWith(ctx, f: Callable, *arrays):
 
 def run(f: Callable, *arrays):
     return runWith(_pkg.default_context(), f, *arrays)
+
+
+_awhile_keys = iter(range(0x7A000000, 0x7FFFFFFF))
+
+
+def awhile(cond: Callable, body: Callable, *arrays, ctx=None, device: bool = True, max_iters: int = 1 << 20):
+    """``awhile cond body init`` on numpy arrays: while ``cond(*state)`` (a Scalar Bool) holds, the state becomes
+    ``body(*state)``, which must keep every array's type and shape.  The state stays on the device throughout;
+    with ``device=True`` so does the flag (one CUDA graph with a conditional WHILE node), otherwise it is read
+    back once per iteration as the reference does (Awhile, CUDA/Execute.hs:236-244).
+    Returns ``(final_state, iterations)``."""
+    import ctypes as C
+    ctx = ctx or _pkg.default_context()
+    types = _pkg._types_of(arrays)
+    L, h = _pkg.lib(), ctx.handle
+    progs, keys, state, hosts = [], [], [], []
+    stream = C.c_void_p()
+    _pkg._check(L.accb_stream_acquire(h, C.byref(stream)), h)
+    try:
+        progs.append(run1With(ctx, cond, *types))
+        progs.append(run1With(ctx, body, *types))
+        for x, t in builtins.zip(arrays, types):
+            comps = [np.array(c, dtype=d, order="C", copy=True) for c, d in builtins.zip(_pkg._components(x), t.dtypes)]
+            dev = []  # the copies receive the final state
+            for c in comps:
+                key, p = next(_awhile_keys), C.c_void_p()
+                _pkg._check(L.accb_malloc(h, key, builtins.max(c.nbytes, 16), C.byref(p)), h)
+                keys.append(key)
+                _pkg._check(L.accb_poke(h, key, 0, c.ctypes.data, c.nbytes, stream), h)
+                dev.append(_pkg.DeviceArray(p.value, c.shape, c.dtype))
+            hosts.append(comps)
+            state.append(tuple(dev) if len(dev) > 1 else dev[0])
+        n = _pkg.awhile(progs[0], progs[1], state, device=device, max_iters=max_iters, stream=stream.value, count=True)
+        k = iter(keys)
+        for comps in hosts:
+            for c in comps:
+                _pkg._check(L.accb_peek(h, next(k), 0, c.ctypes.data, c.nbytes, stream), h)
+        _pkg._check(L.accb_stream_sync(h, stream), h)
+        res = [c[0] if len(c) == 1 else tuple(c) for c in hosts]
+        return (res[0] if len(res) == 1 else tuple(res)), n
+    finally:
+        L.accb_stream_sync(h, stream)
+        for p in progs:
+            p.destroy()
+        for key in keys:
+            L.accb_free(h, key)
+        L.accb_stream_release(h, stream)

@@ -330,6 +330,23 @@ ACCB_API int accb_program_run(accb_program *p, accb_stream stream, const accb_ar
  * (CUDA/Execute.hs:164-219). */
 ACCB_API int accb_program_run_graph(accb_program *p, accb_stream stream, const accb_array *inputs,
                                     accb_array *outputs);
+/* awhile: while `cond` holds of the state, replace the state by `body` of it.  `cond` takes the state arrays as
+ * its inputs and has ONE output, a Scalar of one 1-byte component (Bool); `body` takes the same inputs and has one
+ * output per input, of the same type and -- when it runs -- the same shape.  `state` are body's-input-many device
+ * arrays that hold the initial state and receive the final one (each iteration's results are copied back into
+ * them on the stream).
+ *   ACCB_AWHILE_HOST    the reference's scheme (Awhile of executeOpenAcc, CUDA/Execute.hs:236-244): the flag is
+ *                       copied to the host and the stream synchronised once per iteration.
+ *   ACCB_AWHILE_DEVICE  the whole loop is ONE CUDA graph launch: a conditional WHILE node whose body holds the
+ *                       launches of `body`, the copies and `cond`; the flag never leaves the device and the call
+ *                       returns without waiting.  Recorded at the first call for these arrays on this stream
+ *                       (not the default stream) and replayed afterwards.
+ * max_iters > 0 bounds the loop on the device as well: when it stops the loop, the call (host mode) or the first
+ * call that passes a non-NULL `iterations` (which waits for the stream) returns ACCB_ETIMEOUT.  `iterations`, if
+ * not NULL, receives the number of times the body ran. */
+enum { ACCB_AWHILE_HOST = 0, ACCB_AWHILE_DEVICE = 1 };
+ACCB_API int accb_awhile(accb_program *cond, accb_program *body, accb_stream stream, const accb_array *state,
+                         int mode, long long max_iters, long long *iterations);
 /* run1 with HOST arrays: upload, execute, download (CUDA.hs:307-330,382-389).
  * host_in[i] / host_out[j] point to one host buffer per component. */
 ACCB_API int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array *host_out);

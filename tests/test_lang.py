@@ -439,3 +439,39 @@ def test_generate_backpermute_tuples_and_index_arithmetic(ctx, rng):
     for n in (5, 70000):  # one compiled function, several shapes
         y = rng.uniform(-1, 1, n).astype(f32)
         close(f(y), np.where(y < 0, -y, np.sqrt(np.abs(y))), 1e-7)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("device", [False, True])
+def test_awhile_keeps_the_loop_on_the_device(ctx, accb, rng, device):
+    """awhile: doubling until the largest element passes a bound (the trip count depends on the data), and a
+    smoothing loop that carries a counter as a second state array.  The device-resident loop (a conditional
+    WHILE node) and the host-driven one agree with the same loop written in numpy."""
+    x = rng.integers(1, 50, 10001).astype(i32)
+    small = lambda v: A.map(lambda m: m < 100000, A.foldAll(A.maximum, 0, v))  # noqa: E731
+    got, n = A.awhile(small, lambda v: A.map(lambda e: e * 2 + 1, v), x, ctx=ctx, device=device)
+    ref, k = x.copy(), 0
+    while ref.max() < 100000:
+        ref, k = ref * 2 + 1, k + 1
+    assert n == k and k > 5 and np.array_equal(got, ref)
+
+    g = rng.uniform(0, 1, 4099).astype(f32)
+    three = lambda t: (t[0] + t[1] + t[2]) / 3.0  # noqa: E731
+    (gg, kk), n = A.awhile(lambda a, c: A.map(lambda v: v < 9, c),
+                           lambda a, c: (A.stencil(three, "clamp", a), A.map(lambda v: v + 1, c)),
+                           g, np.array(0, i32), ctx=ctx, device=device)
+    ref = g.astype(f64)
+    for _ in range(9):
+        p = np.concatenate([ref[:1], ref, ref[-1:]])
+        ref = (p[:-2] + p[1:-1] + p[2:]) / 3.0
+    assert n == 9 and int(kk) == 9
+    close(gg, ref, 1e-6)
+    # a condition that is false from the start: the body never runs and the state comes back untouched
+    got, n = A.awhile(lambda v: A.map(lambda m: m < 0, A.foldAll(A.maximum, 0, v)), lambda v: A.map(lambda e: e + 1, v),
+                      x, ctx=ctx, device=device)
+    assert n == 0 and np.array_equal(got, x)
+    # a condition that never turns false is stopped by the iteration limit, on the device as well
+    with pytest.raises(accb.AccbError) as e:
+        A.awhile(lambda v: A.map(lambda m: m > -1, A.foldAll(A.maximum, 0, v)), lambda v: A.map(lambda e: e // 2, v),
+                 x, ctx=ctx, device=device, max_iters=6)
+    assert e.value.status == accb.ETIMEOUT
