@@ -1314,6 +1314,30 @@ def scanr1Seg(f: Callable, arr: Array, seglens: Array) -> Array:
     return _segmented_scan(f, arr, lambda kenv, ix: flags.at(kenv, ix)[0], _pkg.SCAN_RIGHT)
 
 
+def _scan_prime_seg(f: Callable, seed, arr: Array, seglens: Array, right: bool):
+    """scanl'Seg / scanr'Seg: inside every segment the exclusive scan (same length as the data), and one total per
+    segment.  The exclusive scan is the inclusive segmented scan of the data shifted by one element, the seed
+    entering at each segment's first (last, for right scans) position; the totals are a foldSeg."""
+    arr = _as_array(arr)
+    if not arr.manifest:
+        arr = compute(arr)
+    flags = _segment_flags(arr, seglens, right)
+    zs = _seed_value(seed, arr.dtypes)
+    src = arr
+
+    def shifted(i):
+        j = minimum(i + 1, shape(src)[0] - 1) if right else maximum(i - 1, 0)
+        vals = _flat(src[j])
+        return _unflat1(tuple(cond(flags[i], constant(z, dt), v) for z, dt, v in _zip(zs, src.dtypes, vals)))
+    moved = generate(shape_of(src), shifted)
+    body = _segmented_scan(f, moved, lambda kenv, ix: flags.at(kenv, ix)[0], _pkg.SCAN_RIGHT if right else _pkg.SCAN_LEFT)
+    return body, foldSeg(f, seed, src, seglens)
+
+
+def scanl_Seg(f, seed, arr, seglens): return _scan_prime_seg(f, seed, arr, seglens, False)   # scanl'Seg
+def scanr_Seg(f, seed, arr, seglens): return _scan_prime_seg(f, seed, arr, seglens, True)    # scanr'Seg
+
+
 def _scan(f, seed, arr: Array, direction, kind):
     arr = _as_array(arr)
     if arr.rank != 1:

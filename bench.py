@@ -546,6 +546,37 @@ WORKLOADS = {"scan": ScanWorkload, "dot": DotWorkload, "hist": HistWorkload, "st
              "blackscholes": BlackScholesWorkload, "rowsum": RowSumWorkload}
 
 
+def awhile_sample(accb, ctx, torch, side=128, iters=200):
+    """`awhile` around a 5-point stencil and a counter, the loop driven from the host (the flag read back every
+    iteration, as the reference does) and resident on the device (one graph launch with a conditional WHILE
+    node): wall-clock microseconds per iteration, the host being part of what is measured."""
+    A = importlib.import_module("accelerate-cuda_b200.lang")
+    f32, i32 = np.float32, np.int32
+    five = lambda t: 0.2 * (t[0][1] + t[1][0] + t[1][1] + t[1][2] + t[2][1])  # noqa: E731
+    types = (A.matrix(f32), A.scalar(i32))
+    cond = A.run1With(ctx, lambda a, c: A.map(lambda v: v < iters, c), *types)
+    body = A.run1With(ctx, lambda a, c: (A.stencil(five, "clamp", a), A.map(lambda v: v + 1, c)), *types)
+    grid = torch.rand((side, side), device="cuda")
+    count = torch.zeros((), dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    out = {"program": f"{iters} x 5-point stencil on {side}x{side} Float32 + counter", "unit": "us per iteration"}
+    for mode, device in (("host_loop", False), ("device_loop", True)):
+        best = None
+        for _ in range(4):
+            count.zero_()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            n = accb.awhile(cond, body, [grid, count], device=device, max_iters=10 * iters, stream=stream.cuda_stream,
+                            count=True)
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        out[mode] = best / max(n, 1) * 1e6
+        out["iterations_ok"] = out.get("iterations_ok", True) and n == iters
+    cond.destroy()
+    body.destroy()
+    return out
+
+
 def time_steps(torch, wl, steps, warmup):
     """K steps between two CUDA events on the launching (current) stream; returns (ms total, launches)."""
     for _ in range(warmup):
@@ -757,6 +788,7 @@ def main():
                 torch.cuda.empty_cache()
             Workload.functors = "hand"
             line["generated_functors"] = gen
+        line["awhile"] = awhile_sample(accb, ctx, torch)
     elif world > 1 and isinstance(wl, ScanWorkload) and not args.no_extras:
         # ---- e2e at N GPUs: every rank uploads its slab from pinned host memory, takes part in the carry exchange,
         # scans, and downloads its part of the result; wall clock between barriers, max over ranks

@@ -254,6 +254,18 @@ def test_scans_along_rows_and_inside_segments(ctx, rng):
         refr[offs[s]:offs[s + 1]] = np.cumsum(seg[::-1])[::-1]
     close(A.runWith(ctx, lambda a, l: A.scanl1Seg(add, a, l), v, lens), refl, 2e-3)  # float32 sums of up to 30000 terms
     close(A.runWith(ctx, lambda a, l: A.scanr1Seg(add, a, l), v, lens), refr, 2e-3)
+    # scanl'Seg / scanr'Seg: the exclusive scan inside every segment plus one total per segment (empty ones: the seed)
+    w = rng.integers(-100, 100, int(lens.sum())).astype(i32)
+    exl, exr, tot = np.empty_like(w), np.empty_like(w), np.empty(lens.size, i32)
+    for s in range(lens.size):
+        seg = w[offs[s]:offs[s + 1]].astype(i64)
+        exl[offs[s]:offs[s + 1]] = 5 + np.concatenate([[0], np.cumsum(seg)])[:seg.size]
+        exr[offs[s]:offs[s + 1]] = 5 + np.concatenate([np.cumsum(seg[::-1])[::-1], [0]])[1:]
+        tot[s] = 5 + seg.sum()
+    body, totals = A.runWith(ctx, lambda a, l: A.scanl_Seg(add, 5, a, l), w, lens)
+    assert np.array_equal(body, exl) and np.array_equal(totals, tot)
+    body, totals = A.runWith(ctx, lambda a, l: A.scanr_Seg(add, 5, a, l), w, lens)
+    assert np.array_equal(body, exr) and np.array_equal(totals, tot)
 
 
 @pytest.mark.gpu
