@@ -95,9 +95,6 @@ __device__ __forceinline__ void map_body(const accb_kparams &p) {
  * map: apply(env, i, in-values..., out-references...) with i the OUTPUT
  * position, in an array of ip[1] rows and ip[0] columns.
  * ---------------------------------------------------------------------- */
-#ifndef ACCB_TRANS_GROUP
-#define ACCB_TRANS_GROUP 8 /* tiles along each side of a group of tiles that blocks work on together */
-#endif
 constexpr int kTransTile = 64;                 /* tile edge, in elements */
 constexpr int kTransPitch = kTransTile + 1;    /* odd pitch: columns of a tile fall into different banks */
 constexpr int kTransElems = kTransTile * kTransPitch;
@@ -134,19 +131,8 @@ __device__ __forceinline__ void map_transposed_body(const accb_kparams &p) {
     const int tx = threadIdx.x % VX, ty = threadIdx.x / VX;
     const bool vec = (p.flags & ACCB_F_VEC) != 0 && W % V == 0 && H % V == 0;
     const long long tiles_x = (W + T - 1) / T, tiles_y = (H + T - 1) / T;
-    /* Tiles are numbered in square groups of G x G: the blocks running at the same time then read runs of
-     * G * T contiguous elements of the source rows AND write runs of the same length of the result rows, instead
-     * of long runs on one side and isolated tile rows on the other. */
-    constexpr int G = ACCB_TRANS_GROUP;
-    const bool grouped = tiles_x % G == 0 && tiles_y % G == 0;
     for (long long t = blockIdx.x; t < tiles_x * tiles_y; t += gridDim.x) {
-        long long tile_y = t / tiles_x, tile_x = t % tiles_x;
-        if (grouped) {
-            const long long group = t / (G * G), in = t % (G * G), groups_x = tiles_x / G;
-            tile_y = (group / groups_x) * G + in / G;
-            tile_x = (group % groups_x) * G + in % G;
-        }
-        const int y0 = (int)tile_y * T, x0 = (int)tile_x * T; /* source tile */
+        const int y0 = (int)(t / tiles_x) * T, x0 = (int)(t % tiles_x) * T; /* source tile */
         const bool full = vec && y0 + T <= H && x0 + T <= W;
         if (full) { /* 4 rows x one 16-byte vector per component and thread in flight */
             regs<V, In> a[T / RY];
