@@ -197,3 +197,63 @@ def test_group_stencil_refuses_a_slab_smaller_than_its_halo(group, accb, P, torc
     with pytest.raises(accb.AccbError):
         group.stencil_iterate(P.BLUR, A, B, rows, iters, 1, "clamp")
     group.sync()
+
+
+_D = "static __device__ __forceinline__"
+MINMAX_BODY = f"""
+    typedef LH elem; typedef LH acc;
+    using Out = accb::types<float, float>;
+    {_D} LH lift(LH x) {{ return x; }}
+    {_D} LH lower(LH x) {{ return x; }}
+    {_D} LH combine(LH a, LH b) {{ LH r; r.lo = fminf(a.lo, b.lo); r.hi = fmaxf(a.hi, b.hi); return r; }}
+    {_D} void put(LH r, float &lo, float &hi) {{ lo = r.lo; hi = r.hi; }}
+"""
+
+
+def test_group_fold_of_pairs_and_permute_with_max(group, accb, P, torch_cuda, rng):
+    """A two-component value (min, max) through the partial exchange, and a permute whose combiner is not (+):
+    partial destinations start from the combiner's neutral element and are merged with a zipWith of the combiner."""
+    t, G = torch_cuda, group.size
+    minmax = accb.KernelSpec("fold_all", "MinMax", f"""
+struct LH {{ float lo, hi; }};
+struct MinMax {{
+    using In = accb::types<float>;
+    {_D} LH get(const accb::Env &, long long, float x) {{ LH r; r.lo = x; r.hi = x; return r; }}
+{MINMAX_BODY}}};
+""")
+    minmax_pairs = accb.KernelSpec("fold_all", "MinMaxP", f"""
+struct LH {{ float lo, hi; }};
+struct MinMaxP {{
+    using In = accb::types<float, float>;
+    {_D} LH get(const accb::Env &, long long, float lo, float hi) {{ LH r; r.lo = lo; r.hi = hi; return r; }}
+{MINMAX_BODY}}};
+""")
+    n = 200003
+    x = rng.standard_normal(n).astype(np.float32)
+    c = cuts(n, G, rng)
+    env = [[put(t, x[c[r]:c[r + 1]], group.devices[r])] for r in range(G)]
+    out = [(t.zeros(1, device=f"cuda:{group.devices[r]}"), t.zeros(1, device=f"cuda:{group.devices[r]}")) for r in range(G)]
+    sync_all(t)
+    group.fold_all(minmax, minmax_pairs, env, [c[r + 1] - c[r] for r in range(G)], out)  # fold1All: no seed
+    group.sync()
+    for lo, hi in out:
+        assert float(lo.cpu()[0]) == x.min() and float(hi.cpu()[0]) == x.max()
+
+    zip_max = accb.KernelSpec("map", "ZipMaxF", f"""
+struct ZipMaxF {{
+    using In = accb::types<float, float>;
+    using Out = accb::types<float>;
+    {_D} void apply(const accb::Env &, long long, float a, float b, float &o) {{ o = fmaxf(a, b); }}
+}};
+""")
+    bins = 1000
+    keys = rng.integers(0, bins, n).astype(np.int32)
+    defaults = rng.standard_normal(bins).astype(np.float32)
+    env = [[(put(t, keys[c[r]:c[r + 1]], group.devices[r]), put(t, x[c[r]:c[r + 1]], group.devices[r]))] for r in range(G)]
+    dst = [put(t, defaults if r == 0 else np.full(bins, -np.inf, np.float32), group.devices[r]) for r in range(G)]
+    sync_all(t)
+    group.permute(P.SCATTER_MAX_F32, zip_max, env, [c[r + 1] - c[r] for r in range(G)], dst)
+    group.sync()
+    ref = defaults.copy()
+    np.maximum.at(ref, keys, x)
+    assert np.array_equal(dst[0].cpu().numpy(), ref)
