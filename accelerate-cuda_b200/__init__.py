@@ -140,6 +140,8 @@ def lib() -> C.CDLL:
             "accb_program_generate": [vp, vp, C.POINTER(i32), i32, i32, C.POINTER(i32), C.POINTER(accb_value_type), vp, sz],
             "accb_program_generate_dims": [vp, vp, C.POINTER(i32), i32, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32),
                                            C.POINTER(accb_value_type), vp, sz],
+            "accb_program_generate_dims2": [vp, vp, C.POINTER(i32), i32, i32] + [C.POINTER(i32)] * 5 +
+                                           [C.POINTER(accb_value_type), vp, sz],
             "accb_program_fold_seg": [vp, vp, C.POINTER(i32), i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
             "accb_program_stencil2": [vp, vp, i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
             "accb_program_outputs": [vp, C.POINTER(i32), i32],
@@ -749,18 +751,24 @@ def generate(prog: Afun, spec: KernelSpec, env: Sequence[Acc], shape, out_type: 
 def generate_dims(prog: Afun, spec: KernelSpec, env: Sequence[Acc], dims, out_type: ArrayType, scalars=None) -> Acc:
     """generate node whose shape is computed when the program runs.  dims lists, outermost first, one
     (source, dim, add) per extent: ``add`` plus -- when source is an Acc -- extent ``dim`` (outermost first) of it."""
-    dims = [(s, int(d), int(a)) for s, d, a in dims]
+    # an entry may name a second source, (source, dim, add, source2, dim2): the extents of both are added
+    dims = [(e[0], int(e[1]), int(e[2]), e[3] if len(e) > 3 else None, int(e[4]) if len(e) > 3 else 0) for e in dims]
     ids, n = prog._ids(env)
     sb, sn = _bytes_of(scalars)
     t = out_type.ctype()
     r = len(dims)
     inner = list(reversed(dims))  # the C side counts extents innermost first
-    src = (C.c_int * max(1, r))(*[(s.id if s is not None else -1) for s, _, _ in inner])
-    sdim = (C.c_int * max(1, r))(*[((s.type.rank - 1 - d) if s is not None else 0) for s, d, _ in inner])
-    add = (C.c_int * max(1, r))(*[a for _, _, a in inner])
-    vid = lib().accb_program_generate_dims(prog.handle, prog.ctx._k(spec), ids, n, r, src, sdim, add, C.byref(t), sb, sn)
+    ints = lambda xs: (C.c_int * max(1, r))(*xs)  # noqa: E731
+    src = ints([(e[0].id if e[0] is not None else -1) for e in inner])
+    sdim = ints([((e[0].type.rank - 1 - e[1]) if e[0] is not None else 0) for e in inner])
+    src2 = ints([(e[3].id if e[3] is not None else -1) for e in inner])
+    sdim2 = ints([((e[3].type.rank - 1 - e[4]) if e[3] is not None else 0) for e in inner])
+    add = ints([e[2] for e in inner])
+    vid = lib().accb_program_generate_dims2(prog.handle, prog.ctx._k(spec), ids, n, r, src, sdim, src2, sdim2, add,
+                                            C.byref(t), sb, sn)
     node = prog._new(vid, out_type)
-    node.shape_fn = lambda s: tuple((src_.shape_fn(s)[d] if src_ is not None else 0) + a for src_, d, a in dims)
+    node.shape_fn = lambda s: tuple((a.shape_fn(s)[d] if a is not None else 0) + k + (b.shape_fn(s)[d2] if b is not None else 0)
+                                    for a, d, k, b, d2 in dims)
     return node
 
 

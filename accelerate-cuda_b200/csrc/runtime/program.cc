@@ -36,6 +36,8 @@ struct Node {
     int lit_shape[ACCB_MAX_RANK] = {0};           /* extent d = lit_shape[d] ... */
     int dim_src[ACCB_MAX_RANK] = {-1, -1, -1, -1}; /* ... + extent dim_of[d] of value dim_src[d], if >= 0 */
     int dim_of[ACCB_MAX_RANK] = {0};
+    int dim_src2[ACCB_MAX_RANK] = {-1, -1, -1, -1}; /* ... + a second such extent, if >= 0 (appended arrays) */
+    int dim_of2[ACCB_MAX_RANK] = {0};
     int offsets_id = -1;  /* foldSeg: Int32 vector of segment offsets, length segments + 1 */
     bool transposed = false; /* map: the element-wise inputs are read transposed; the result has shape_like's shape transposed */
     int all = 0;          /* fold: reduce everything */
@@ -154,6 +156,11 @@ int run_internal(accb_program *p, cudaStream_t s, const accb_array *inputs, accb
                 const accb_array &src = val[nd.dim_src[d]];
                 if (nd.dim_of[d] >= src.rank) return fail(ctx, ACCB_EINVAL, "shape refers to a dimension its source lacks");
                 e += src.shape[nd.dim_of[d]];
+            }
+            if (nd.dim_src2[d] >= 0) {
+                const accb_array &src = val[nd.dim_src2[d]];
+                if (nd.dim_of2[d] >= src.rank) return fail(ctx, ACCB_EINVAL, "shape refers to a dimension its source lacks");
+                e += src.shape[nd.dim_of2[d]];
             }
             if (e < 0 || e > 0x7fffffffLL) return fail(ctx, ACCB_EBOUNDS, "computed extent %lld is out of range", e);
             literal.shape[d] = (int)e;
@@ -440,11 +447,13 @@ int accb_program_generate(accb_program *p, accb_kernel *k, const int *env_ids, i
 
 /* generate whose extents are taken from other values: extent d (innermost first) of the result is
  * add[d], plus extent src_dim[d] of value src_value[d] when src_value[d] >= 0 */
-int accb_program_generate_dims(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,
-                               const int *src_value, const int *src_dim, const int *add,
-                               const accb_value_type *out_type, const void *scalars, size_t scalar_bytes) {
+int accb_program_generate_dims2(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,
+                                const int *src_value, const int *src_dim, const int *src_value2, const int *src_dim2,
+                                const int *add, const accb_value_type *out_type, const void *scalars,
+                                size_t scalar_bytes) {
     if (!p || !k) return -ACCB_EINVAL;
-    if (rank < 0 || rank > ACCB_ARRAY_MAX_RANK || (rank > 0 && (!src_value || !src_dim || !add)))
+    if (rank < 0 || rank > ACCB_ARRAY_MAX_RANK || (rank > 0 && (!src_value || !src_dim || !add)) ||
+        ((src_value2 == nullptr) != (src_dim2 == nullptr)))
         return -fail(p->ctx, ACCB_EINVAL, "bad shape description");
     Node nd;
     nd.kind = N_MAP;
@@ -452,15 +461,27 @@ int accb_program_generate_dims(accb_program *p, accb_kernel *k, const int *env_i
     if (nenv > 0) nd.env.assign(env_ids, env_ids + nenv);
     nd.shape_like = -1;
     nd.lit_rank = rank;
+    auto known = [&](int v, int d) { return v < (int)p->types.size() && (v < 0 || (d >= 0 && d < ACCB_ARRAY_MAX_RANK)); };
     for (int d = 0; d < rank; ++d) {
-        if (src_value[d] >= (int)p->types.size() || (src_value[d] >= 0 && (src_dim[d] < 0 || src_dim[d] >= ACCB_ARRAY_MAX_RANK)))
+        if (!known(src_value[d], src_dim[d]) || (src_value2 && !known(src_value2[d], src_dim2[d])))
             return -fail(p->ctx, ACCB_EINVAL, "shape refers to an unknown value or dimension");
         nd.dim_src[d] = src_value[d] < 0 ? -1 : src_value[d];
         nd.dim_of[d] = src_dim[d];
+        if (src_value2) {
+            nd.dim_src2[d] = src_value2[d] < 0 ? -1 : src_value2[d];
+            nd.dim_of2[d] = src_dim2[d];
+        }
         nd.lit_shape[d] = add[d];
     }
     if (scalars) nd.scalars.assign((const unsigned char *)scalars, (const unsigned char *)scalars + scalar_bytes);
     return add_node(p, nd, out_type, 1);
+}
+
+int accb_program_generate_dims(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,
+                               const int *src_value, const int *src_dim, const int *add,
+                               const accb_value_type *out_type, const void *scalars, size_t scalar_bytes) {
+    return accb_program_generate_dims2(p, k, env_ids, nenv, rank, src_value, src_dim, nullptr, nullptr, add, out_type,
+                                       scalars, scalar_bytes);
 }
 
 int accb_program_fold_seg(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like, int offsets_id,

@@ -606,26 +606,43 @@ class _Dim:
     """One extent of a shape: a constant, plus -- when src is given -- extent `dim` (outermost first) of a
     manifest array.  What Accelerate writes as an Exp Int inside a shape."""
 
-    def __init__(self, src: "Array" = None, dim: int = 0, add: int = 0):
-        self.src, self.dim, self.add = src, dim, int(add)
+    def __init__(self, src: "Array" = None, dim: int = 0, add: int = 0, src2: "Array" = None, dim2: int = 0):
+        # src2 / dim2: a second extent added to the first (the length of `xs ++ ys`)
+        self.src, self.dim, self.add, self.src2, self.dim2 = src, dim, int(add), src2, dim2
 
     def key(self):
-        return ("lit", self.add) if self.src is None else ("arr", self.src.prog_find(self.src.node.id), self.dim, self.add)
+        if self.src is None:
+            return ("lit", self.add)
+        k = ("arr", self.src.prog_find(self.src.node.id), self.dim, self.add)
+        return k if self.src2 is None else k + (self.src2.prog_find(self.src2.node.id), self.dim2)
 
     def code(self, kenv: "_KernelEnv") -> Exp:
         if self.src is None:
             return constant(self.add, I32)
         e = kenv.dims_of(self.src)[self.dim]
+        if self.src2 is not None:
+            e = Exp(I32, f"({e.code} + {kenv.dims_of(self.src2)[self.dim2].code})")
         return e if self.add == 0 else Exp(I32, f"({e.code} + {_literal(self.add, I32)})")
 
     def value(self, s) -> int:
-        return self.add if self.src is None else self.src.node.shape_fn(s)[self.dim] + self.add
+        if self.src is None:
+            return self.add
+        second = self.src2.node.shape_fn(s)[self.dim2] if self.src2 is not None else 0
+        return self.src.node.shape_fn(s)[self.dim] + second + self.add
 
-    def __add__(self, n: int) -> "_Dim":
-        return _Dim(self.src, self.dim, self.add + int(n))
+    def __add__(self, n) -> "_Dim":
+        if isinstance(n, _Dim):
+            if n.src is None:
+                return self + n.add
+            if self.src is None:
+                return n + self.add
+            if self.src2 is not None or n.src2 is not None:
+                raise NotImplementedError("an extent that adds up more than two array extents")
+            return _Dim(self.src, self.dim, self.add + n.add, n.src, n.dim)
+        return _Dim(self.src, self.dim, self.add + int(n), self.src2, self.dim2)
 
     def __sub__(self, n: int) -> "_Dim":
-        return _Dim(self.src, self.dim, self.add - int(n))
+        return _Dim(self.src, self.dim, self.add - int(n), self.src2, self.dim2)
 
 
 class _Extent:
@@ -638,7 +655,8 @@ class _Extent:
             if all(p.src is None for p in parts):
                 literal, parts = tuple(p.add for p in parts), None
             elif (parts[0].src is not None and len(parts) == parts[0].src.rank
-                  and all(p.src is parts[0].src and p.dim == d and p.add == 0 for d, p in enumerate(parts))):
+                  and all(p.src is parts[0].src and p.dim == d and p.add == 0 and p.src2 is None
+                          for d, p in enumerate(parts))):
                 like, parts = parts[0].src, None
         self.like, self.literal, self.parts = like, literal, parts
 
@@ -1123,8 +1141,9 @@ def compute(arr: Array) -> Array:
         node = _be().map_(spec, env_nodes or [like], out_type, shape_like=like)
     else:  # extents taken one by one from other arrays: the host computes the shape when the program runs
         parts = [arr.extent.part(d) for d in range(arr.rank)]
-        node = _be().generate_dims(prog, spec, env_nodes, [(p.src.node if p.src is not None else None, p.dim, p.add)
-                                                          for p in parts], out_type)
+        node = _be().generate_dims(prog, spec, env_nodes,
+                                   [(p.src.node if p.src is not None else None, p.dim, p.add,
+                                     p.src2.node if p.src2 is not None else None, p.dim2) for p in parts], out_type)
     return _same_shape(Array(prog, arr.dtypes, node=node), arr)
 
 
@@ -1334,6 +1353,50 @@ def _scan_prime_seg(f: Callable, seed, arr: Array, seglens: Array, right: bool):
     return body, foldSeg(f, seed, src, seglens)
 
 
+def concat(xs: Array, ys: Array) -> Array:
+    """``xs ++ ys`` on vectors: a generate over the sum of the two lengths."""
+    xs, ys = _as_array(xs), _as_array(ys)
+    if xs.rank != 1 or ys.rank != 1 or xs.dtypes != ys.dtypes:
+        raise TypeError("(++) here joins two vectors of one element type")
+
+    def pick(i):
+        nx, ny = shape(xs)[0], shape(ys)[0]
+        a = _flat(xs[maximum(minimum(i, nx - 1), 0)])
+        b = _flat(ys[maximum(minimum(i - nx, ny - 1), 0)])
+        return _unflat1(tuple(cond(i < nx, u, v) for u, v in _zip(a, b)))
+    return generate(_Extent(parts=[xs.extent.part(0) + ys.extent.part(0)]), pick, prog=xs.prog)
+
+
+def _scan_seg_exclusive(f: Callable, seed, arr: Array, seglens: Array, right: bool) -> Array:
+    """scanlSeg / scanrSeg: every segment grows by one element, the seed in front (behind, for right scans), so the
+    result has length(data) + length(segments) elements.  The seed positions are marked in the widened index
+    space, a running count of the marks tells every other position which element of the data it holds, and the
+    inclusive segmented scan of that widened vector, restarting at the marks, is the result."""
+    arr, seglens = _as_array(arr), _as_array(seglens)
+    if seglens.dtypes != [I32] or seglens.rank != 1 or arr.rank != 1:
+        raise TypeError("segment lengths are a vector of Int32, the data a vector")
+    if not arr.manifest:
+        arr = compute(arr)
+    if not seglens.manifest:
+        seglens = compute(seglens)
+    zs = _seed_value(seed, arr.dtypes)
+    wide = _Extent(parts=[arr.extent.part(0) + seglens.extent.part(0)])
+    offs = compute(scanl(lambda a, b: a + b, 0, seglens))
+    marks = permute(lambda x, y: x, fill(wide, False, np.bool_), lambda s: (offs[s + 1] if right else offs[s]) + s,
+                    fill(shape_of(seglens), True, np.bool_))
+    counts = _same_shape(compute(scanl1(lambda a, b: a + b, map(lambda m: cond(m, constant(1, I32), constant(0, I32)), marks))), marks)
+    src = arr
+
+    def widened(j):
+        at = maximum(minimum(j - counts[j], shape(src)[0] - 1), 0)  # marks up to here are not data
+        vals = _flat(src[at])
+        return _unflat1(tuple(cond(marks[j], constant(z, dt), v) for z, dt, v in _zip(zs, src.dtypes, vals)))
+    moved = generate(shape_of(marks), widened)  # fused into the scan
+    return _segmented_scan(f, moved, lambda kenv, ix: marks.at(kenv, ix)[0], _pkg.SCAN_RIGHT if right else _pkg.SCAN_LEFT)
+
+
+def scanlSeg(f, seed, arr, seglens): return _scan_seg_exclusive(f, seed, arr, seglens, False)
+def scanrSeg(f, seed, arr, seglens): return _scan_seg_exclusive(f, seed, arr, seglens, True)
 def scanl_Seg(f, seed, arr, seglens): return _scan_prime_seg(f, seed, arr, seglens, False)   # scanl'Seg
 def scanr_Seg(f, seed, arr, seglens): return _scan_prime_seg(f, seed, arr, seglens, True)    # scanr'Seg
 

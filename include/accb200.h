@@ -311,6 +311,13 @@ ACCB_API int accb_program_generate(accb_program *p, accb_kernel *k, const int *e
 ACCB_API int accb_program_generate_dims(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,
                                         const int *src_value, const int *src_dim, const int *add,
                                         const accb_value_type *out_type, const void *scalars, size_t scalar_bytes);
+/* the same with up to two sources per extent: add[d] + extent src_dim[d] of src_value[d] + extent src_dim2[d] of
+ * src_value2[d] (each where the value id is >= 0): the shape of `xs ++ ys` and of segmented scans whose segments
+ * grow by one element. */
+ACCB_API int accb_program_generate_dims2(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int rank,
+                                         const int *src_value, const int *src_dim, const int *src_value2,
+                                         const int *src_dim2, const int *add, const accb_value_type *out_type,
+                                         const void *scalars, size_t scalar_bytes);
 /* foldSeg / fold1Seg: offsets_id names an Int32 vector of segments + 1 offsets, the exclusive scan of the
  * segment lengths (foldSegOp, CUDA/Execute.hs:320-324); the innermost extent of the result is the segment count */
 ACCB_API int accb_program_fold_seg(accb_program *p, accb_kernel *k, const int *env_ids, int nenv, int shape_like,

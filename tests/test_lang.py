@@ -266,6 +266,17 @@ def test_scans_along_rows_and_inside_segments(ctx, rng):
     assert np.array_equal(body, exl) and np.array_equal(totals, tot)
     body, totals = A.runWith(ctx, lambda a, l: A.scanr_Seg(add, 5, a, l), w, lens)
     assert np.array_equal(body, exr) and np.array_equal(totals, tot)
+    # scanlSeg / scanrSeg: every segment one element longer, the seed first (last); length = data + segments
+    refl, refr = [], []
+    for s in range(lens.size):
+        seg = w[offs[s]:offs[s + 1]].astype(i64)
+        refl.append(5 + np.concatenate([[0], np.cumsum(seg)]))
+        refr.append(5 + np.concatenate([np.cumsum(seg[::-1])[::-1], [0]]))
+    assert np.array_equal(A.runWith(ctx, lambda a, l: A.scanlSeg(add, 5, a, l), w, lens), np.concatenate(refl).astype(i32))
+    assert np.array_equal(A.runWith(ctx, lambda a, l: A.scanrSeg(add, 5, a, l), w, lens), np.concatenate(refr).astype(i32))
+    # (++): the extent of the result is the sum of two arrays' extents
+    assert np.array_equal(A.runWith(ctx, lambda a, b: A.concat(A.map(lambda e: e + 1, a), b), w, lens),
+                          np.concatenate([w + 1, lens]))
 
 
 @pytest.mark.gpu
