@@ -1528,6 +1528,28 @@ class _CondIndex:
         self.c, self.ix = c, ix
 
 
+def compact(pred: Callable, arr: Array):
+    """Stream compaction, the core of Accelerate's ``filter``: the elements of a vector that satisfy ``pred``, in
+    order, at the front of a vector of the ORIGINAL length, and their number as a Scalar Int32.  (``filter`` itself
+    returns a vector whose length is that number: a shape known only once the device has computed it, which a
+    caller obtains by slicing with the count.)  An exclusive scan of the flags gives every kept element its
+    position; a permute without atomics moves it there."""
+    arr = _as_array(arr)
+    if arr.rank != 1:
+        raise TypeError("compact takes a vector")
+    if not arr.manifest:
+        arr = compute(arr)
+    src = arr
+    keep = compute(map(lambda e: pred(e), src))
+    if keep.dtypes != [BOOL]:
+        raise TypeError("the predicate yields a Bool")
+    where, count = scanl_(lambda a, b: a + b, 0, map(lambda k: cond(k, constant(1, I32), constant(0, I32)), keep))
+    where = _same_shape(compute(where), src)
+    zeros = generate(shape_of(src), lambda i: _unflat1(tuple(constant(0, dt) for dt in src.dtypes)))
+    moved = permute(lambda x, y: x, zeros, lambda i: cond_index(keep[i], where[i]), src)
+    return moved, count
+
+
 def cond_index(c: Exp, ix) -> _CondIndex:
     """A destination that is ``ix`` when c holds and ``ignore`` otherwise."""
     return _CondIndex(c, ix)

@@ -365,6 +365,13 @@ def test_histogram_and_scatter_with_ignore(ctx, rng):
     even = keys % 2 == 0
     np.maximum.at(ref, keys[even], vals[even])
     assert np.array_equal(got, ref)
+    # stream compaction (the core of `filter`): kept elements in order at the front, and how many there are
+    front, count = A.runWith(ctx, lambda v: A.compact(lambda e: e > 0.5, v), vals)
+    kept = vals[vals > 0.5]
+    assert int(count) == kept.size and np.array_equal(front[:kept.size], kept) and not front[kept.size:].any()
+    pairs, count = A.runWith(ctx, lambda kv: A.compact(lambda e: e[0] % 3 == 0, kv), (keys, vals))
+    sel = keys % 3 == 0
+    assert int(count) == sel.sum() and np.array_equal(pairs[0][:sel.sum()], keys[sel]) and np.array_equal(pairs[1][:sel.sum()], vals[sel])
 
 
 @pytest.mark.gpu
