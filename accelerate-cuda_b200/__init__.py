@@ -164,6 +164,16 @@ def lib() -> C.CDLL:
             "accb_group_stencil_layout": [vp, i32, i32, i32, i32, C.POINTER(i32), C.POINTER(i32)],
             "accb_group_stencil_iterate": [vp, vp, arrp, arrp, C.POINTER(i32), i32, i32, i32, vp, sz,
                                            C.POINTER(i32), C.POINTER(i32)],
+            "accb_peer_create": [vp, i32, i32, sz, C.POINTER(vp)],
+            "accb_peer_handle": [vp, vp],
+            "accb_peer_connect": [vp, vp],
+            "accb_peer_data": [vp, C.POINTER(vp), C.POINTER(sz)],
+            "accb_peer_barrier": [vp, vp],
+            "accb_peer_gather": [vp, vp, sz, sz, vp],
+            "accb_peer_allreduce": [vp, vp, sz, ll, i32, i32, vp],
+            "accb_peer_pull": [vp, vp, i32, sz, sz, vp],
+            "accb_peer_status": [vp, vp, C.POINTER(i32)],
+            "accb_peer_destroy": [vp],
             "accb_gen_uniform_f32": [vp, vp, vp, ll, ll, u64, u64, C.c_float, C.c_float],
             "accb_gen_uniform_i32": [vp, vp, vp, ll, ll, u64, u64, i32],
             "accb_gen_zipf_mix_i32": [vp, vp, vp, ll, ll, u64, vp, i32],
@@ -256,6 +266,70 @@ class DeviceArray:
 
     def __init__(self, ptr: int, shape, dtype):
         self.ptr, self.shape, self.dtype = int(ptr), tuple(shape), np.dtype(dtype)
+
+    def element_size(self) -> int:
+        return self.dtype.itemsize
+
+    @property
+    def __cuda_array_interface__(self):
+        """Lets ``torch.as_tensor(device_array, device="cuda")`` (or cupy) view the memory without a copy."""
+        return {"shape": self.shape, "typestr": self.dtype.str, "data": (self.ptr, False), "version": 3, "strides": None}
+
+
+PEER_TYPES = {np.dtype(np.int32): 0, np.dtype(np.uint32): 1, np.dtype(np.int64): 2, np.dtype(np.float32): 3,
+              np.dtype(np.float64): 4}
+PEER_OPS = {"add": 0, "min": 1, "max": 2, "and": 3, "or": 4, "xor": 5}
+
+
+class Peer:
+    """This rank's exchange buffer and its mappings of the other ranks' buffers (``accb_peer_*``): exchanges
+    between processes, one per GPU, done by the library's own kernels over NVLink.  ``all_gather_bytes(b)`` is the
+    host's way to hand every rank's 64-byte handle to every rank, e.g. built on ``torch.distributed``."""
+
+    def __init__(self, ctx: "Context", rank: int, world: int, nbytes: int, all_gather_bytes: Callable):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        h = C.c_void_p()
+        _check(lib().accb_peer_create(ctx.handle, rank, world, nbytes, C.byref(h)), ctx.handle)
+        self.handle = h
+        mine = C.create_string_buffer(64)
+        self._check(lib().accb_peer_handle(h, mine))
+        handles = all_gather_bytes(mine.raw)  # list of `world` bytes objects, in rank order
+        blob = C.create_string_buffer(b"".join(handles), 64 * world)
+        self._check(lib().accb_peer_connect(h, blob))
+        p, n = C.c_void_p(), C.c_size_t()
+        self._check(lib().accb_peer_data(h, C.byref(p), C.byref(n)))
+        self.data_ptr, self.nbytes = p.value, n.value
+
+    def _check(self, status: int):
+        _check(status, self.ctx.handle)
+
+    def array(self, offset: int, shape, dtype) -> "DeviceArray":
+        """A region of this rank's own buffer as a device array that skeleton launches can write."""
+        return DeviceArray(self.data_ptr + offset, shape, dtype)
+
+    def barrier(self, stream=None):
+        self._check(lib().accb_peer_barrier(self.handle, Context._stream(stream)))
+
+    def gather(self, offset: int, nbytes: int, dst, stream=None):
+        self._check(lib().accb_peer_gather(self.handle, Context._stream(stream), offset, nbytes, C.c_void_p(_ptr(dst))))
+
+    def allreduce(self, offset: int, count: int, dtype, op: str, dst, stream=None):
+        self._check(lib().accb_peer_allreduce(self.handle, Context._stream(stream), offset, count,
+                                              PEER_TYPES[np.dtype(dtype)], PEER_OPS[op], C.c_void_p(_ptr(dst))))
+
+    def pull(self, from_rank: int, offset: int, nbytes: int, dst_ptr: int, stream=None):
+        self._check(lib().accb_peer_pull(self.handle, Context._stream(stream), from_rank, offset, nbytes,
+                                         C.c_void_p(int(dst_ptr))))
+
+    def status(self, stream=None):
+        """Waits for the stream; raises ETIMEOUT if a rank did not reach some exchange in time."""
+        t = C.c_int()
+        self._check(lib().accb_peer_status(self.handle, Context._stream(stream), C.byref(t)))
+
+    def destroy(self):
+        if self.handle:
+            lib().accb_peer_destroy(self.handle)
+            self.handle = None
 
 
 class Kernel:

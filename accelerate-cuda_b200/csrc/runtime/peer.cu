@@ -1,0 +1,293 @@
+/*
+ * peer.cu -- the small exchanges of the sharded skeletons done by the library's own kernels over NVLink, one
+ * process per GPU: every rank owns an exchange buffer that the other ranks map (CUDA IPC, plain peer mappings,
+ * no multicast objects), and a kernel that first synchronises the ranks through flags in those buffers and
+ * then moves or combines the data with peer loads.
+ *
+ *   scan      slab totals       barrier + gather of one element per rank          (accb_peer_gather)
+ *   foldAll   partials          the same
+ *   permute   partial results   barrier + element-wise combination in rank order   (accb_peer_allreduce)
+ *   stencil   halo rows         barrier, pull from the neighbours' slabs, barrier   (accb_peer_barrier / _pull)
+ *
+ * The reference has no multi-device execution; its peer copy (CUDA/Array/Prim.hs:306-335) is never called.
+ *
+ * Flags: rank r's buffer starts with one 32-bit word per rank.  Barrier number e: every rank stores e into word
+ * [own rank] of EVERY rank's buffer (release, system scope), then waits until all words of its own buffer have
+ * reached e (acquire).  The ranks run on different GPUs; a wait gives up after about two seconds, sets the
+ * buffer's error word and lets the kernel finish, so a rank that never arrives cannot hang the others.
+ */
+#include <type_traits>
+
+#include "common.h"
+
+using namespace accb_rt;
+
+namespace {
+constexpr int kMaxWorld = 64;
+constexpr size_t kHeader = 1024;           /* flags [0..64), error word at [64], padding */
+constexpr int kErrorWord = kMaxWorld;
+constexpr unsigned kSpinLimit = 1u << 23;  /* x ~250 ns */
+
+struct PeerPtrs {
+    unsigned char *base[kMaxWorld];
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+template <class T>
+__device__ __forceinline__ T ld_peer(const T *p) { /* not through this GPU's L1 */
+    return __ldcg(p);
+}
+
+/* all threads of ONE block call this; threads 0..world-1 do the signalling */
+__device__ void block_barrier(const PeerPtrs &pp, int rank, int world, unsigned epoch) {
+    __syncthreads();
+    const int r = threadIdx.x;
+    if (r < world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<unsigned *>(pp.base[r]) + rank, epoch);
+        const unsigned *mine = reinterpret_cast<const unsigned *>(pp.base[rank]) + r;
+        unsigned spins = 0;
+        while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
+            __nanosleep(250);
+            if (++spins > kSpinLimit) {
+                atomicExch(reinterpret_cast<unsigned *>(pp.base[rank]) + kErrorWord, 1u);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void peer_barrier_kernel(PeerPtrs pp, int rank, int world, unsigned epoch) { block_barrier(pp, rank, world, epoch); }
+
+/* dst[r * bytes ..] = rank r's data[offset .. offset + bytes), bytes a multiple of 4 */
+__global__ void peer_gather_kernel(PeerPtrs pp, int rank, int world, unsigned epoch, size_t offset, size_t bytes,
+                                   unsigned *dst) {
+    block_barrier(pp, rank, world, epoch);
+    const size_t words = bytes / 4;
+    for (size_t i = threadIdx.x; i < words * world; i += blockDim.x) {
+        const int r = (int)(i / words);
+        const unsigned *src = reinterpret_cast<const unsigned *>(pp.base[r] + kHeader + offset);
+        dst[i] = ld_peer(src + i % words);
+    }
+}
+
+enum { OP_ADD = 0, OP_MIN = 1, OP_MAX = 2, OP_AND = 3, OP_OR = 4, OP_XOR = 5 };
+
+template <class T>
+__device__ __forceinline__ T combine(int op, T a, T b) {
+    if (op == OP_MIN) return b < a ? b : a;
+    if (op == OP_MAX) return b > a ? b : a;
+    if constexpr (std::is_integral<T>::value) {
+        typedef typename std::make_unsigned<T>::type U;
+        if (op == OP_AND) return a & b;
+        if (op == OP_OR) return a | b;
+        if (op == OP_XOR) return a ^ b;
+        return (T)((U)a + (U)b); /* wrapping, as the skeletons add */
+    } else {
+        return a + b;
+    }
+}
+
+/* dst[i] = data_0[i] (op) data_1[i] (op) ... in rank order: every rank computes the same bits */
+template <class T>
+__global__ void peer_allreduce_kernel(PeerPtrs pp, int rank, int world, unsigned epoch, size_t offset, long long count,
+                                      int op, T *dst) {
+    block_barrier(pp, rank, world, epoch);
+    for (long long i = threadIdx.x; i < count; i += blockDim.x) {
+        T acc = ld_peer(reinterpret_cast<const T *>(pp.base[0] + kHeader + offset) + i);
+        for (int r = 1; r < world; ++r) {
+            const T v = ld_peer(reinterpret_cast<const T *>(pp.base[r] + kHeader + offset) + i);
+            acc = combine<T>(op, acc, v);
+        }
+        dst[i] = acc;
+    }
+}
+
+/* dst[0 .. bytes) = rank `from`'s data[offset ..), 16 bytes per thread and trip; no barrier of its own */
+__global__ void peer_pull_kernel(PeerPtrs pp, int from, size_t offset, size_t bytes, uint4 *dst) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(pp.base[from] + kHeader + offset);
+    const size_t n = bytes / 16;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = ld_peer(src + i);
+}
+
+}  // namespace
+
+struct accb_peer {
+    accb_context *ctx = nullptr;
+    int rank = 0, world = 1;
+    size_t bytes = 0;              /* of the data area */
+    unsigned char *local = nullptr;
+    PeerPtrs pp;
+    bool connected = false;
+    unsigned epoch = 0;
+};
+
+#define PLOCKP(p)                                                   \
+    if (!(p)) return fail(nullptr, ACCB_EINVAL, "null peer object"); \
+    std::lock_guard<std::recursive_mutex> lock_((p)->ctx->mu);      \
+    CtxGuard guard_((p)->ctx)
+
+extern "C" {
+
+int accb_peer_create(accb_context *ctx, int rank, int world, size_t bytes, accb_peer **out) {
+    if (!ctx || !out) return fail(ctx, ACCB_EINVAL, "null argument");
+    *out = nullptr;
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return fail(ctx, ACCB_EINVAL, "rank %d of %d", rank, world);
+    std::lock_guard<std::recursive_mutex> lock_(ctx->mu);
+    CtxGuard guard_(ctx);
+    accb_peer *p = new accb_peer;
+    p->ctx = ctx;
+    p->rank = rank;
+    p->world = world;
+    p->bytes = (bytes + 255) / 256 * 256;
+    memset(&p->pp, 0, sizeof p->pp);
+    /* a plain cudaMalloc block of its own: that is what an IPC handle names */
+    int st = check_cuda(ctx, cudaMalloc((void **)&p->local, kHeader + p->bytes), "cudaMalloc");
+    if (st == ACCB_OK) st = check_cuda(ctx, cudaMemset(p->local, 0, kHeader), "cudaMemset");
+    if (st != ACCB_OK) {
+        if (p->local) cudaFree(p->local);
+        delete p;
+        return st;
+    }
+    p->pp.base[rank] = p->local;
+    p->connected = world == 1;
+    *out = p;
+    return ACCB_OK;
+}
+
+int accb_peer_handle(accb_peer *p, unsigned char *handle) {
+    PLOCKP(p);
+    if (!handle) return fail(p->ctx, ACCB_EINVAL, "null handle buffer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == ACCB_PEER_HANDLE_BYTES, "handle size");
+    cudaIpcMemHandle_t h;
+    int st = check_cuda(p->ctx, cudaIpcGetMemHandle(&h, p->local), "cudaIpcGetMemHandle");
+    if (st == ACCB_OK) memcpy(handle, &h, sizeof h);
+    return st;
+}
+
+int accb_peer_connect(accb_peer *p, const unsigned char *handles) {
+    PLOCKP(p);
+    if (!handles) return fail(p->ctx, ACCB_EINVAL, "null handles");
+    for (int r = 0; r < p->world; ++r) {
+        if (r == p->rank || p->pp.base[r]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * sizeof h, sizeof h);
+        void *q = nullptr;
+        int st = check_cuda(p->ctx, cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+        if (st != ACCB_OK) return st;
+        p->pp.base[r] = static_cast<unsigned char *>(q);
+    }
+    p->connected = true;
+    return ACCB_OK;
+}
+
+int accb_peer_data(accb_peer *p, void **data, size_t *bytes) {
+    PLOCKP(p);
+    if (data) *data = p->local + kHeader;
+    if (bytes) *bytes = p->bytes;
+    return ACCB_OK;
+}
+
+/* 1 when a wait of some earlier exchange gave up (the word is cleared); waits for the stream */
+int accb_peer_status(accb_peer *p, accb_stream stream, int *timed_out) {
+    PLOCKP(p);
+    unsigned w = 0;
+    int st = check_cuda(p->ctx, cudaStreamSynchronize((cudaStream_t)stream), "cudaStreamSynchronize");
+    if (st == ACCB_OK)
+        st = check_cuda(p->ctx, cudaMemcpy(&w, p->local + kErrorWord * 4, 4, cudaMemcpyDeviceToHost), "cudaMemcpy");
+    if (st != ACCB_OK) return st;
+    if (w) cudaMemset(p->local + kErrorWord * 4, 0, 4);
+    if (timed_out) *timed_out = w != 0;
+    return w ? fail(p->ctx, ACCB_ETIMEOUT, "a rank did not reach an exchange in time") : ACCB_OK;
+}
+
+static int ready(accb_peer *p, size_t offset, size_t bytes) {
+    if (!p->connected) return fail(p->ctx, ACCB_EINVAL, "peer buffers are not connected yet");
+    if (offset % 16 || offset + bytes > p->bytes) return fail(p->ctx, ACCB_EINVAL, "range outside the exchange buffer");
+    return ACCB_OK;
+}
+
+int accb_peer_barrier(accb_peer *p, accb_stream stream) {
+    PLOCKP(p);
+    int st = ready(p, 0, 0);
+    if (st != ACCB_OK) return st;
+    if (p->world == 1) return ACCB_OK;
+    peer_barrier_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(p->pp, p->rank, p->world, ++p->epoch);
+    p->ctx->launches++;
+    return check_cuda(p->ctx, cudaGetLastError(), "peer barrier");
+}
+
+int accb_peer_gather(accb_peer *p, accb_stream stream, size_t offset, size_t bytes, void *dst) {
+    PLOCKP(p);
+    int st = ready(p, offset, bytes);
+    if (st != ACCB_OK) return st;
+    if (!dst || bytes % 4) return fail(p->ctx, ACCB_EINVAL, "gather moves multiples of 4 bytes");
+    peer_gather_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(p->pp, p->rank, p->world, ++p->epoch, offset, bytes,
+                                                           static_cast<unsigned *>(dst));
+    p->ctx->launches++;
+    return check_cuda(p->ctx, cudaGetLastError(), "peer gather");
+}
+
+int accb_peer_allreduce(accb_peer *p, accb_stream stream, size_t offset, long long count, int type, int op, void *dst) {
+    PLOCKP(p);
+    const size_t eb = (type == ACCB_PEER_I64 || type == ACCB_PEER_F64) ? 8 : 4;
+    int st = ready(p, offset, (size_t)count * eb);
+    if (st != ACCB_OK) return st;
+    if (!dst || count < 0 || op < OP_ADD || op > OP_XOR) return fail(p->ctx, ACCB_EINVAL, "bad all-reduce arguments");
+    const bool real = type == ACCB_PEER_F32 || type == ACCB_PEER_F64;
+    if (real && op > OP_MAX) return fail(p->ctx, ACCB_EINVAL, "bitwise combination of floating-point values");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (type < ACCB_PEER_I32 || type > ACCB_PEER_F64) return fail(p->ctx, ACCB_EINVAL, "unknown element type %d", type);
+    const unsigned e = ++p->epoch;
+#define ACCB_PEER_LAUNCH(T) \
+    peer_allreduce_kernel<T><<<1, 1024, 0, s>>>(p->pp, p->rank, p->world, e, offset, count, op, static_cast<T *>(dst))
+    switch (type) {
+        case ACCB_PEER_I32: ACCB_PEER_LAUNCH(int); break;
+        case ACCB_PEER_U32: ACCB_PEER_LAUNCH(unsigned); break;
+        case ACCB_PEER_I64: ACCB_PEER_LAUNCH(long long); break;
+        case ACCB_PEER_F32: ACCB_PEER_LAUNCH(float); break;
+        case ACCB_PEER_F64: ACCB_PEER_LAUNCH(double); break;
+        default: return fail(p->ctx, ACCB_EINVAL, "unknown element type %d", type);
+    }
+#undef ACCB_PEER_LAUNCH
+    p->ctx->launches++;
+    return check_cuda(p->ctx, cudaGetLastError(), "peer all-reduce");
+}
+
+int accb_peer_pull(accb_peer *p, accb_stream stream, int from_rank, size_t offset, size_t bytes, void *dst) {
+    PLOCKP(p);
+    int st = ready(p, offset, bytes);
+    if (st != ACCB_OK) return st;
+    if (from_rank < 0 || from_rank >= p->world || !dst || bytes % 16 || (reinterpret_cast<uintptr_t>(dst) & 15))
+        return fail(p->ctx, ACCB_EINVAL, "pull moves 16-byte aligned multiples of 16 bytes from an existing rank");
+    if (bytes == 0) return ACCB_OK;
+    const int grid = (int)std::min<size_t>((bytes / 16 + 255) / 256, (size_t)p->ctx->sm_count * 4);
+    peer_pull_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p->pp, from_rank, offset, bytes, static_cast<uint4 *>(dst));
+    p->ctx->launches++;
+    return check_cuda(p->ctx, cudaGetLastError(), "peer pull");
+}
+
+int accb_peer_destroy(accb_peer *p) {
+    if (!p) return ACCB_OK;
+    {
+        std::lock_guard<std::recursive_mutex> lock_(p->ctx->mu);
+        CtxGuard guard_(p->ctx);
+        cudaDeviceSynchronize();
+        for (int r = 0; r < p->world; ++r)
+            if (r != p->rank && p->pp.base[r]) cudaIpcCloseMemHandle(p->pp.base[r]);
+        if (p->local) cudaFree(p->local);
+    }
+    delete p;
+    return ACCB_OK;
+}
+
+}  // extern "C"

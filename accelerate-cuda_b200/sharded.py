@@ -209,3 +209,47 @@ def sharded_stencil_iterate(grid_local: torch.Tensor, iters: int, ry: int, local
         exchange_halos(a, ry, boundary, group)
         a = local_apply(a)
     return a[ry:ry + h]
+
+
+# ------------------------------------------------------------------ exchanges by the library's own kernels
+def peer_buffer(ctx, nbytes: int, group=None):
+    """This rank's exchange buffer, connected to the other ranks' buffers (``Peer``): the 64-byte IPC handles travel
+    through the process group once; afterwards the exchanges below are single kernels over NVLink peer mappings and
+    involve neither the collective library nor the host."""
+    from . import Peer
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+
+    def all_gather_bytes(b: bytes):
+        out = [None] * world
+        dist.all_gather_object(out, b, group=group)
+        return out
+    return Peer(ctx, rank, world, nbytes, all_gather_bytes)
+
+
+def peer_scan_carry(peer, offset: int, gathered: torch.Tensor) -> torch.Tensor:
+    """The carry of a sharded scan when the slab total was written at ``offset`` of the rank's exchange buffer: one
+    kernel synchronises the ranks and gathers the totals; the exclusive sum of the lower ranks follows."""
+    peer.gather(offset, gathered.element_size(), gathered)
+    r = peer.rank
+    return gathered[:r].sum(dtype=gathered.dtype).reshape(1) if r else torch.zeros(1, dtype=gathered.dtype,
+                                                                                  device=gathered.device)
+
+
+def peer_wide_halos(peer, slab_offset: int, rows: int, row_bytes: int, reach: int, boundary: str = "clamp"):
+    """Fill the halo rows of a padded slab that lives at ``slab_offset`` of the exchange buffer (every rank: the same
+    offset and ``rows`` own rows) from the neighbours' own rows: barrier, two pulls over NVLink, barrier -- the
+    second so that no rank overwrites rows a neighbour is still reading."""
+    world, rank = peer.world, peer.rank
+    ring = boundary == "wrap" and world > 1
+    pads = [((reach if (r > 0 or ring) else 0), (reach if (r < world - 1 or ring) else 0)) for r in range(world)]
+    pt, pb = pads[rank]
+    up, down = (rank - 1) % world, (rank + 1) % world
+    peer.barrier()
+    if pt:  # the last rows of the rank above
+        peer.pull(up, slab_offset + (pads[up][0] + rows - reach) * row_bytes, reach * row_bytes,
+                  peer.data_ptr + slab_offset)
+    if pb:  # the first rows of the rank below
+        peer.pull(down, slab_offset + pads[down][0] * row_bytes, reach * row_bytes,
+                  peer.data_ptr + slab_offset + (pt + rows) * row_bytes)
+    peer.barrier()
+    return pt, pb

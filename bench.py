@@ -131,6 +131,20 @@ class Workload:
         self.W = importlib.import_module("accelerate-cuda_b200.workloads")
 
     functors = "hand"  # "lang": the kernels the embedded language prints for the same programs (examples.py)
+    exchange = "peer"  # several GPUs: "peer" = the library's own exchange kernels over NVLink, "nccl" = collectives
+
+    def peer_views(self, nbytes_each, shape, dtype):
+        """Two regions of a fresh exchange buffer as torch tensors (used alternately: a rank may overwrite what it
+        exchanged only after the next exchange) -- or None when the exchanges go through NCCL."""
+        if self.world == 1 or self.exchange != "peer":
+            self.peer = None
+            return None
+        sh = importlib.import_module("accelerate-cuda_b200.sharded")
+        pitch = (nbytes_each + 255) // 256 * 256
+        self.peer = sh.peer_buffer(self.ctx, 2 * pitch)
+        self.parity = 0
+        self.peer_offsets = (0, pitch)
+        return [self.t.as_tensor(self.peer.array(o, shape, dtype), device="cuda") for o in self.peer_offsets]
 
     def functor(self, name):
         if self.functors == "lang":
@@ -159,13 +173,22 @@ class ScanWorkload(Workload):
             self.gathered = t.zeros(self.world, dtype=t.int32, device="cuda")
             self.carry = t.zeros(1, dtype=t.int32, device="cuda")
             self.bytes = W.bytes_scan(self.n)  # algorithmic bytes stay 8 B/element; the reduce pass is overhead
+            self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
+            self.totals = self.peer_views(4, (1,), np.int32)
         self.ctx.sync()
 
     def step(self):
         if self.world == 1:
             self.ctx.scan(self.k, [self.x], self.n, self.out, seed=np.int32(0))
             return 1
-        # carry pass: slab totals -> all-gather -> exclusive sum of the lower ranks -> seeded local scan
+        # carry pass: slab totals -> gathered -> exclusive sum of the lower ranks -> seeded local scan
+        if self.peer is not None:  # the total goes straight into the exchange buffer; one kernel syncs and gathers
+            p = self.parity
+            self.parity ^= 1
+            self.ctx.fold_all(self.ksum, [self.x], self.n, self.totals[p], seed=np.int32(0))
+            self.carry.copy_(self.sh.peer_scan_carry(self.peer, self.peer_offsets[p], self.gathered))
+            self.ctx.scan(self.k, [self.x], self.n, self.out, seed=self.carry)
+            return 3
         self.ctx.fold_all(self.ksum, [self.x], self.n, self.total, seed=np.int32(0))
         self.dist.all_gather_into_tensor(self.gathered, self.total)
         self.carry.copy_(self.gathered[: self.rank].sum(dtype=self.t.int32).reshape(1)) if self.rank else self.carry.zero_()
@@ -204,9 +227,18 @@ class DotWorkload(Workload):
         self.bytes = W.bytes_dot(self.n)
         if self.world > 1:
             self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
+            self.partials = self.peer_views(4, (1,), np.float32)
+            self.result = t.zeros(1, dtype=t.float32, device="cuda")
         self.ctx.sync()
 
     def step(self):
+        if self.world > 1 and self.peer is not None:  # partials combined in rank order by one kernel over NVLink
+            p = self.parity
+            self.parity ^= 1
+            self.out = self.partials[p]
+            self.ctx.fold_all(self.k, [self.x, self.y], self.n, self.out, seed=np.float32(0))
+            self.peer.allreduce(self.peer_offsets[p], 1, np.float32, "add", self.result)
+            return 2
         self.ctx.fold_all(self.k, [self.x, self.y], self.n, self.out, seed=np.float32(0))
         if self.world > 1:  # partials all-gathered and combined in rank order
             self.result = self.sh.sharded_fold_all(self.out, lambda a, b: a + b)
@@ -237,9 +269,18 @@ class HistWorkload(Workload):
         self.bytes = W.bytes_hist(self.n)
         if self.world > 1:
             self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
+            self.parts = self.peer_views(4 * W.HIST_BINS, (W.HIST_BINS,), np.int32)
+            self.result = t.zeros(W.HIST_BINS, dtype=t.int32, device="cuda")
         self.ctx.sync()
 
     def step(self):
+        if self.world > 1 and self.peer is not None:  # partial histograms summed in rank order by one kernel over NVLink
+            p = self.parity
+            self.parity ^= 1
+            self.out = self.parts[p]
+            self.ctx.permute(self.k, [self.keys], self.n, self.out, defaults=self.defaults)
+            self.peer.allreduce(self.peer_offsets[p], self.W.HIST_BINS, np.int32, "add", self.result)
+            return 2
         self.ctx.permute(self.k, [self.keys], self.n, self.out, defaults=self.defaults)
         if self.world > 1:  # per-GPU partial histograms, one all-reduce of 16 KiB
             self.result = self.sh.sharded_histogram(self.out, self.defaults)
@@ -274,7 +315,14 @@ class StencilWorkload(Workload):
         rows = self.pt + self.h + self.pb
         self.a = t.empty((rows, self.w), dtype=t.float32, device="cuda")
         self.b = t.empty_like(self.a)
-        self.src = t.zeros_like(self.a)
+        self.peer = None
+        if self.world > 1 and self.exchange == "peer":
+            # the source slab lives in the exchange buffer: the neighbours pull their halo rows out of it
+            self.peer = self.sh.peer_buffer(self.ctx, rows * self.w * 4)
+            self.src = t.as_tensor(self.peer.array(0, (rows, self.w), np.float32), device="cuda")
+            self.src.zero_()
+        else:
+            self.src = t.zeros_like(self.a)
         self.ctx.gen_uniform_f32(self.src[self.pt:self.pt + self.h], self.h * self.w, self.rank * self.h * self.w, W.SEED,
                                  W.S_GRID, 0.0, 1.0)
         self.k = self.ctx.kernel(self.functor("BLUR")).wait()
@@ -289,11 +337,14 @@ class StencilWorkload(Workload):
             self.ctx.stencil(self.k, self.src, self.a, boundary="clamp")
             self.res = self.ctx.stencil_iterate(self.k, self.a, self.b, self.iters - 1, boundary="clamp")
             return self.iters
-        self.sh.exchange_wide_halos(self.src, self.pt, self.pb)  # in place: the data lives in the padded slab
+        if self.peer is not None:  # barrier, two pulls over NVLink, barrier: the library's own kernels
+            self.sh.peer_wide_halos(self.peer, 0, self.h, self.w * 4, self.iters, "clamp")
+        else:
+            self.sh.exchange_wide_halos(self.src, self.pt, self.pb)  # in place: the data lives in the padded slab
         self.ctx.stencil(self.k, self.src, self.a, boundary="clamp")
         res = self.ctx.stencil_iterate(self.k, self.a, self.b, self.iters - 1, boundary="clamp")
         self.res = res[self.pt:self.pt + self.h]
-        return self.iters
+        return self.iters + (2 + bool(self.pt) + bool(self.pb) if self.peer is not None else 0)
 
     def verify(self):
         # blur with Clamp keeps values inside [min, max] of the source and (interior) preserves the mean
@@ -645,6 +696,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--functors", default="hand", choices=["hand", "lang"],
                     help="hand-written functor snippets (programs.py) or the ones the embedded language prints (examples.py)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="several GPUs: the library's own exchange kernels over NVLink peer mappings, or NCCL collectives")
     ap.add_argument("--size", type=int, default=None, help="override the problem size (profiling small cases)")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-skeleton table, e2e and CPU baseline")
     args = ap.parse_args()
@@ -671,6 +724,7 @@ def main():
     if args.workload in SECONDARY and world > 1:
         raise SystemExit("the secondary workloads run on one GPU")
     Workload.functors = args.functors
+    Workload.exchange = args.exchange
     wl = {**WORKLOADS, **SECONDARY}[args.workload](accb, ctx, torch, rank, world)
     wl.setup(args.size)
     if dist:
@@ -698,7 +752,8 @@ def main():
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
         "data": "synthetic",
         "config": {"workload": wl.name, "l2": "inputs larger than L2 (1 GiB read per step)", "parity_check": ok,
-                   "elements_per_gpu": getattr(wl, "n", None), "seed": hex(wl.W.SEED), "functors": args.functors},
+                   "elements_per_gpu": getattr(wl, "n", None), "seed": hex(wl.W.SEED), "functors": args.functors,
+                   **({"exchange": args.exchange} if world > 1 else {})},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
         "pct_of_spec_peak_8TBs": 100.0 * per_gpu / SPEC_PEAK_GBS,
@@ -821,6 +876,13 @@ def main():
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist:
+        dist.barrier()  # every rank is done with the others' exchange buffers
+        try:
+            if getattr(wl, "peer", None) is not None:
+                wl.peer.status()
+                wl.peer.destroy()
+        except NameError:
+            pass
         dist.barrier()
         dist.destroy_process_group()
 

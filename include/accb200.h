@@ -424,6 +424,39 @@ ACCB_API int accb_group_stencil_iterate(accb_group *grp, accb_kernel *k, const a
                                         const int *rows, int iters, int ry, int boundary, const void *constant,
                                         size_t constant_bytes, const int *comp_bytes, int *result_in_b);
 
+/* ------------------------- exchanges between processes, one per GPU
+ * For hosts that run one process per GPU (torchrun, MPI): the small exchanges of the sharded skeletons -- slab
+ * totals of a scan, partials of a foldAll, partial destinations of a permute, halo rows of a stencil -- done by
+ * the library's own kernels over NVLink instead of a collective library.  Every rank creates an exchange buffer
+ * of the same size, passes its 64-byte handle to the others by whatever channel the host has (the Python mirror
+ * uses torch.distributed), and connects; the buffers are plain CUDA IPC peer mappings (no multicast objects).
+ * Ranks write what they want to exchange into their OWN buffer (accb_peer_data: a device pointer any skeleton
+ * launch can write to) and then call, all of them and in the same order:
+ *   accb_peer_gather     one kernel: synchronise the ranks, then dst[r * bytes ..] = rank r's data[offset ..]
+ *   accb_peer_allreduce  one kernel: synchronise, then dst[i] = data_0[i] (op) data_1[i] (op) .., in rank order,
+ *                        so that every rank gets the same bits
+ *   accb_peer_barrier    synchronise only;  accb_peer_pull copies from ONE rank's buffer without synchronising
+ * The synchronisation is a flag per rank in every buffer (release stores to the peers, acquire polling of the own
+ * buffer); a wait gives up after about two seconds and accb_peer_status then reports ACCB_ETIMEOUT.  A rank may
+ * overwrite data it exchanged only after the NEXT synchronising call has returned on its stream, since slower
+ * ranks may still be reading: callers alternate between two offsets.  No counterpart in the reference. */
+typedef struct accb_peer accb_peer;
+#define ACCB_PEER_HANDLE_BYTES 64
+enum { ACCB_PEER_I32 = 0, ACCB_PEER_U32 = 1, ACCB_PEER_I64 = 2, ACCB_PEER_F32 = 3, ACCB_PEER_F64 = 4 };
+enum { ACCB_PEER_ADD = 0, ACCB_PEER_MIN = 1, ACCB_PEER_MAX = 2, ACCB_PEER_AND = 3, ACCB_PEER_OR = 4, ACCB_PEER_XOR = 5 };
+ACCB_API int accb_peer_create(accb_context *ctx, int rank, int world, size_t bytes, accb_peer **peer);
+ACCB_API int accb_peer_handle(accb_peer *peer, unsigned char *handle /* ACCB_PEER_HANDLE_BYTES */);
+ACCB_API int accb_peer_connect(accb_peer *peer, const unsigned char *handles /* world x ACCB_PEER_HANDLE_BYTES */);
+ACCB_API int accb_peer_data(accb_peer *peer, void **data, size_t *bytes);
+ACCB_API int accb_peer_barrier(accb_peer *peer, accb_stream stream);
+ACCB_API int accb_peer_gather(accb_peer *peer, accb_stream stream, size_t offset, size_t bytes, void *dst);
+ACCB_API int accb_peer_allreduce(accb_peer *peer, accb_stream stream, size_t offset, long long count, int type,
+                                 int op, void *dst);
+ACCB_API int accb_peer_pull(accb_peer *peer, accb_stream stream, int from_rank, size_t offset, size_t bytes,
+                            void *dst);
+ACCB_API int accb_peer_status(accb_peer *peer, accb_stream stream, int *timed_out);
+ACCB_API int accb_peer_destroy(accb_peer *peer); /* after every rank has finished using the buffers */
+
 /* -------------------------------------------- synthetic benchmark inputs
  * Index-addressable generators (any shard can produce its own slice).      */
 ACCB_API int accb_gen_uniform_f32(accb_context *ctx, accb_stream stream, float *dst, long long n,

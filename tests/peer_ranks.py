@@ -1,0 +1,74 @@
+"""Child program of tests/test_gpu_peer.py: run under torchrun with one rank per GPU.  Every exchange kernel of
+accb_peer_* is compared with the corresponding NCCL collective over many rounds, regions alternating as the API
+asks; prints PEER-OK on every rank that saw no difference."""
+import importlib
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    accb = importlib.import_module("accelerate-cuda_b200")
+    sh = importlib.import_module("accelerate-cuda_b200.sharded")
+    ctx = accb.Context(local)
+    n = 4096
+    pitch = 4 * n
+    peer = sh.peer_buffer(ctx, 2 * pitch + 1024 * 1024)
+    views = [torch.as_tensor(peer.array(o, (n,), np.int32), device="cuda") for o in (0, pitch)]
+    big = torch.as_tensor(peer.array(2 * pitch, (262144,), np.float32), device="cuda")  # pulled by the next rank
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    ok = True
+    for it in range(40):
+        p = it & 1
+        views[p].copy_(torch.randint(-1000, 1000, (n,), generator=gen, device="cuda", dtype=torch.int32))
+        # all-reduce (+) in rank order against NCCL
+        got = torch.empty(n, dtype=torch.int32, device="cuda")
+        peer.allreduce((0, pitch)[p], n, np.int32, "add", got)
+        ref = views[p].clone()
+        dist.all_reduce(ref)
+        ok = ok and bool(torch.equal(got, ref))
+        # max
+        peer.allreduce((0, pitch)[p], n, np.int32, "max", got)
+        ref = views[p].clone()
+        dist.all_reduce(ref, op=dist.ReduceOp.MAX)
+        ok = ok and bool(torch.equal(got, ref))
+        # gather of the first 4 elements of every rank
+        g = torch.empty(4 * world, dtype=torch.int32, device="cuda")
+        peer.gather((0, pitch)[p], 16, g)
+        ref = torch.empty(4 * world, dtype=torch.int32, device="cuda")
+        dist.all_gather_into_tensor(ref, views[p][:4].contiguous())
+        ok = ok and bool(torch.equal(g, ref))
+        carry = sh.peer_scan_carry(peer, (0, pitch)[p], torch.empty(world, dtype=torch.int32, device="cuda"))
+        ok = ok and int(carry[0]) == int(ref[0::4][:rank].sum())
+    # pull: every rank fetches the previous rank's block between two barriers
+    big.copy_(torch.rand(262144, generator=gen, device="cuda"))
+    mine = torch.empty_like(big)
+    peer.barrier()
+    peer.pull((rank - 1) % world, 2 * pitch, big.numel() * 4, mine.data_ptr())
+    peer.barrier()
+    blocks = [torch.empty_like(big) for _ in range(world)]
+    dist.all_gather(blocks, big)
+    ok = ok and bool(torch.equal(mine, blocks[(rank - 1) % world]))
+    peer.status()
+    flag = torch.tensor([int(ok)], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.barrier()
+    peer.destroy()
+    dist.barrier()
+    if int(flag[0]) == 1:
+        print(f"PEER-OK rank {rank} of {world}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
