@@ -216,14 +216,23 @@ def peer_buffer(ctx, nbytes: int, group=None):
     """This rank's exchange buffer, connected to the other ranks' buffers (``Peer``): the 64-byte IPC handles travel
     through the process group once; afterwards the exchanges below are single kernels over NVLink peer mappings and
     involve neither the collective library nor the host."""
-    from . import Peer
+    from . import AccbError, ECUDA, Peer
     world, rank = dist.get_world_size(group), dist.get_rank(group)
+    gathered = [False]
 
-    def all_gather_bytes(b: bytes):
+    def all_gather_bytes(b):
         out = [None] * world
+        gathered[0] = True
         dist.all_gather_object(out, b, group=group)
+        if any(h is None for h in out):
+            raise AccbError(ECUDA, "a rank could not create its exchange buffer")
         return out
-    return Peer(ctx, rank, world, nbytes, all_gather_bytes)
+    try:
+        return Peer(ctx, rank, world, nbytes, all_gather_bytes)
+    except AccbError:
+        if not gathered[0]:  # failed before the handles were exchanged: the other ranks are waiting in the gather
+            dist.all_gather_object([None] * world, None, group=group)
+        raise
 
 
 def peer_scan_carry(peer, offset: int, gathered: torch.Tensor) -> torch.Tensor:

@@ -133,23 +133,37 @@ class Workload:
     functors = "hand"  # "lang": the kernels the embedded language prints for the same programs (examples.py)
     exchange = "peer"  # several GPUs: "peer" = the library's own exchange kernels over NVLink, "nccl" = collectives
 
+    def make_peer(self, nbytes):
+        """This rank's exchange buffer connected to the others', or None when the exchanges go through NCCL: by
+        request, or because some rank could not map the buffers (all ranks then agree to fall back)."""
+        if self.world == 1 or Workload.exchange != "peer":
+            return None
+        import torch.distributed as dist
+        sh = importlib.import_module("accelerate-cuda_b200.sharded")
+        peer, why = None, ""
+        try:
+            peer = sh.peer_buffer(self.ctx, nbytes)
+        except self.accb.AccbError as e:
+            why = str(e)
+        ok = self.t.tensor([int(peer is not None)], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok[0]) == 0:
+            if peer is not None:
+                peer.destroy()
+            Workload.exchange = "nccl (peer mapping unavailable" + (": " + why.splitlines()[0][:80] if why else "") + ")"
+            return None
+        return peer
+
     def peer_views(self, nbytes_each, shape, dtype):
         """Two regions of a fresh exchange buffer as torch tensors (used alternately: a rank may overwrite what it
         exchanged only after the next exchange) -- or None when the exchanges go through NCCL."""
-        if self.world == 1 or self.exchange != "peer":
-            self.peer = None
-            return None
-        sh = importlib.import_module("accelerate-cuda_b200.sharded")
         pitch = (nbytes_each + 255) // 256 * 256
-        self.peer = sh.peer_buffer(self.ctx, 2 * pitch)
+        self.peer = self.make_peer(2 * pitch)
+        if self.peer is None:
+            return None
         self.parity = 0
         self.peer_offsets = (0, pitch)
         return [self.t.as_tensor(self.peer.array(o, shape, dtype), device="cuda") for o in self.peer_offsets]
-
-    def functor(self, name):
-        if self.functors == "lang":
-            return importlib.import_module("accelerate-cuda_b200.examples").generated_specs()[name]
-        return getattr(self.P, name)
 
 
 class ScanWorkload(Workload):
@@ -316,9 +330,9 @@ class StencilWorkload(Workload):
         self.a = t.empty((rows, self.w), dtype=t.float32, device="cuda")
         self.b = t.empty_like(self.a)
         self.peer = None
-        if self.world > 1 and self.exchange == "peer":
+        self.peer = self.make_peer(rows * self.w * 4)
+        if self.peer is not None:
             # the source slab lives in the exchange buffer: the neighbours pull their halo rows out of it
-            self.peer = self.sh.peer_buffer(self.ctx, rows * self.w * 4)
             self.src = t.as_tensor(self.peer.array(0, (rows, self.w), np.float32), device="cuda")
             self.src.zero_()
         else:
@@ -753,7 +767,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": wl.name, "l2": "inputs larger than L2 (1 GiB read per step)", "parity_check": ok,
                    "elements_per_gpu": getattr(wl, "n", None), "seed": hex(wl.W.SEED), "functors": args.functors,
-                   **({"exchange": args.exchange} if world > 1 else {})},
+                   **({"exchange": Workload.exchange} if world > 1 else {})},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
         "pct_of_spec_peak_8TBs": 100.0 * per_gpu / SPEC_PEAK_GBS,
