@@ -96,17 +96,37 @@ __device__ __forceinline__ T combine(int op, T a, T b) {
     }
 }
 
-/* dst[i] = data_0[i] (op) data_1[i] (op) ... in rank order: every rank computes the same bits */
+/* dst[i] = data_0[i] (op) data_1[i] (op) ... in rank order: every rank computes the same bits.  A thread takes
+ * 16 bytes of every rank's data at a time and issues the loads of up to eight ranks before it combines any of
+ * them: the loads cross NVLink, and one after the other their latencies would add up. */
 template <class T>
 __global__ void peer_allreduce_kernel(PeerPtrs pp, int rank, int world, unsigned epoch, size_t offset, long long count,
                                       int op, T *dst) {
     block_barrier(pp, rank, world, epoch);
-    for (long long i = threadIdx.x; i < count; i += blockDim.x) {
-        T acc = ld_peer(reinterpret_cast<const T *>(pp.base[0] + kHeader + offset) + i);
-        for (int r = 1; r < world; ++r) {
-            const T v = ld_peer(reinterpret_cast<const T *>(pp.base[r] + kHeader + offset) + i);
-            acc = combine<T>(op, acc, v);
+    constexpr int VEC = 16 / sizeof(T), BATCH = 8;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(dst) & 15u) == 0; /* `offset` is a multiple of 16 */
+    const long long nvec = vec_ok ? count / VEC : 0;
+    for (long long i = threadIdx.x; i < nvec; i += blockDim.x) {
+        __align__(16) T acc[VEC];
+        for (int r0 = 0; r0 < world; r0 += BATCH) {
+            uint4 v[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j)
+                if (r0 + j < world) v[j] = ld_peer(reinterpret_cast<const uint4 *>(pp.base[r0 + j] + kHeader + offset) + i);
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j)
+                if (r0 + j < world) {
+                    const T *e = reinterpret_cast<const T *>(&v[j]);
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) acc[k] = (r0 + j == 0) ? e[k] : combine<T>(op, acc[k], e[k]);
+                }
         }
+        reinterpret_cast<uint4 *>(dst)[i] = *reinterpret_cast<const uint4 *>(acc);
+    }
+    for (long long i = nvec * VEC + threadIdx.x; i < count; i += blockDim.x) {
+        T acc = ld_peer(reinterpret_cast<const T *>(pp.base[0] + kHeader + offset) + i);
+        for (int r = 1; r < world; ++r)
+            acc = combine<T>(op, acc, ld_peer(reinterpret_cast<const T *>(pp.base[r] + kHeader + offset) + i));
         dst[i] = acc;
     }
 }

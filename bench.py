@@ -165,6 +165,11 @@ class Workload:
         self.peer_offsets = (0, pitch)
         return [self.t.as_tensor(self.peer.array(o, shape, dtype), device="cuda") for o in self.peer_offsets]
 
+    def functor(self, name):
+        if self.functors == "lang":
+            return importlib.import_module("accelerate-cuda_b200.examples").generated_specs()[name]
+        return getattr(self.P, name)
+
 
 class ScanWorkload(Workload):
     """scanl (+) 0 over Int32, values uniform in [0,16); 2^28 elements per GPU."""

@@ -39,3 +39,14 @@ def test_algorithmic_bytes(workloads):
     assert W.bytes_dot(W.N24) == 134217732 and W.bytes_scan(W.N28) == 2147483652
     assert W.bytes_hist(W.N28) == 1073774592 and W.bytes_stencil(8192, 8192, 10) == 5368709120
     assert W.bytes_blackscholes(W.N26) == 1342177280 and W.bytes_rowsum(16384, 16384) == 1073807360
+
+
+def test_bench_workloads_have_the_methods_the_driver_loop_calls():
+    """bench.py only runs on a GPU; this catches a workload class that lost a method in an edit."""
+    import importlib
+    bench = importlib.import_module("bench")
+    classes = list(bench.WORKLOADS.values()) + list(bench.SECONDARY.values())
+    assert len(classes) >= 10
+    for cls in classes:
+        for m in ("setup", "step", "verify", "functor", "make_peer", "peer_views"):
+            assert callable(getattr(cls, m, None)), f"{cls.__name__}.{m}"
