@@ -171,6 +171,7 @@ def lib() -> C.CDLL:
             "accb_peer_barrier": [vp, vp],
             "accb_peer_gather": [vp, vp, sz, sz, vp],
             "accb_peer_allreduce": [vp, vp, sz, ll, i32, i32, vp],
+            "accb_peer_exscan": [vp, vp, sz, ll, i32, i32, vp, vp],
             "accb_peer_pull": [vp, vp, i32, sz, sz, vp],
             "accb_peer_status": [vp, vp, C.POINTER(i32)],
             "accb_peer_destroy": [vp],
@@ -316,6 +317,12 @@ class Peer:
     def allreduce(self, offset: int, count: int, dtype, op: str, dst, stream=None):
         self._check(lib().accb_peer_allreduce(self.handle, Context._stream(stream), offset, count,
                                               PEER_TYPES[np.dtype(dtype)], PEER_OPS[op], C.c_void_p(_ptr(dst))))
+
+    def exscan(self, offset: int, count: int, dtype, op: str, first, dst, stream=None):
+        """dst = first (op) the data of every LOWER rank, in rank order: the carry of a sharded scan."""
+        self._check(lib().accb_peer_exscan(self.handle, Context._stream(stream), offset, count,
+                                           PEER_TYPES[np.dtype(dtype)], PEER_OPS[op], C.c_void_p(_ptr(first)),
+                                           C.c_void_p(_ptr(dst))))
 
     def pull(self, from_rank: int, offset: int, nbytes: int, dst_ptr: int, stream=None):
         self._check(lib().accb_peer_pull(self.handle, Context._stream(stream), from_rank, offset, nbytes,

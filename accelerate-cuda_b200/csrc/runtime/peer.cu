@@ -131,6 +131,27 @@ __global__ void peer_allreduce_kernel(PeerPtrs pp, int rank, int world, unsigned
     }
 }
 
+/* dst[i] = first[i] (op) data_0[i] (op) .. (op) data_{rank-1}[i]: what the slabs before this rank's add up to, the
+ * carry its scan continues from (`first` = the seed of the whole scan, in this rank's memory) */
+template <class T>
+__global__ void peer_exscan_kernel(PeerPtrs pp, int rank, int world, unsigned epoch, size_t offset, long long count,
+                                   int op, const T *first, T *dst) {
+    block_barrier(pp, rank, world, epoch);
+    for (long long i = threadIdx.x; i < count; i += blockDim.x) {
+        T acc = first[i];
+        for (int r0 = 0; r0 < rank; r0 += 8) {
+            T v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (r0 + j < rank) v[j] = ld_peer(reinterpret_cast<const T *>(pp.base[r0 + j] + kHeader + offset) + i);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (r0 + j < rank) acc = combine<T>(op, acc, v[j]);
+        }
+        dst[i] = acc;
+    }
+}
+
 /* dst[0 .. bytes) = rank `from`'s data[offset ..), 16 bytes per thread and trip; no barrier of its own */
 __global__ void peer_pull_kernel(PeerPtrs pp, int from, size_t offset, size_t bytes, uint4 *dst) {
     const uint4 *src = reinterpret_cast<const uint4 *>(pp.base[from] + kHeader + offset);
@@ -281,6 +302,33 @@ int accb_peer_allreduce(accb_peer *p, accb_stream stream, size_t offset, long lo
 #undef ACCB_PEER_LAUNCH
     p->ctx->launches++;
     return check_cuda(p->ctx, cudaGetLastError(), "peer all-reduce");
+}
+
+int accb_peer_exscan(accb_peer *p, accb_stream stream, size_t offset, long long count, int type, int op,
+                     const void *first, void *dst) {
+    PLOCKP(p);
+    if (type < ACCB_PEER_I32 || type > ACCB_PEER_F64) return fail(p->ctx, ACCB_EINVAL, "unknown element type %d", type);
+    const size_t eb = (type == ACCB_PEER_I64 || type == ACCB_PEER_F64) ? 8 : 4;
+    int st = ready(p, offset, (size_t)count * eb);
+    if (st != ACCB_OK) return st;
+    if (!dst || !first || count < 0 || op < OP_ADD || op > OP_XOR) return fail(p->ctx, ACCB_EINVAL, "bad scan arguments");
+    if ((type == ACCB_PEER_F32 || type == ACCB_PEER_F64) && op > OP_MAX)
+        return fail(p->ctx, ACCB_EINVAL, "bitwise combination of floating-point values");
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned e = ++p->epoch;
+#define ACCB_PEER_LAUNCH(T)                                                                                      \
+    peer_exscan_kernel<T><<<1, 256, 0, s>>>(p->pp, p->rank, p->world, e, offset, count, op, static_cast<const T *>(first), \
+                                            static_cast<T *>(dst))
+    switch (type) {
+        case ACCB_PEER_I32: ACCB_PEER_LAUNCH(int); break;
+        case ACCB_PEER_U32: ACCB_PEER_LAUNCH(unsigned); break;
+        case ACCB_PEER_I64: ACCB_PEER_LAUNCH(long long); break;
+        case ACCB_PEER_F32: ACCB_PEER_LAUNCH(float); break;
+        default: ACCB_PEER_LAUNCH(double); break;
+    }
+#undef ACCB_PEER_LAUNCH
+    p->ctx->launches++;
+    return check_cuda(p->ctx, cudaGetLastError(), "peer exclusive scan");
 }
 
 int accb_peer_pull(accb_peer *p, accb_stream stream, int from_rank, size_t offset, size_t bytes, void *dst) {

@@ -194,6 +194,7 @@ class ScanWorkload(Workload):
             self.bytes = W.bytes_scan(self.n)  # algorithmic bytes stay 8 B/element; the reduce pass is overhead
             self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
             self.totals = self.peer_views(4, (1,), np.int32)
+            self.zero = t.zeros(1, dtype=t.int32, device="cuda")  # the seed of the whole scan
         self.ctx.sync()
 
     def step(self):
@@ -205,7 +206,7 @@ class ScanWorkload(Workload):
             p = self.parity
             self.parity ^= 1
             self.ctx.fold_all(self.ksum, [self.x], self.n, self.totals[p], seed=np.int32(0))
-            self.carry.copy_(self.sh.peer_scan_carry(self.peer, self.peer_offsets[p], self.gathered))
+            self.peer.exscan(self.peer_offsets[p], 1, np.int32, "add", self.zero, self.carry)  # sync + carry: one kernel
             self.ctx.scan(self.k, [self.x], self.n, self.out, seed=self.carry)
             return 3
         self.ctx.fold_all(self.ksum, [self.x], self.n, self.total, seed=np.int32(0))

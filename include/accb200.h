@@ -452,6 +452,10 @@ ACCB_API int accb_peer_barrier(accb_peer *peer, accb_stream stream);
 ACCB_API int accb_peer_gather(accb_peer *peer, accb_stream stream, size_t offset, size_t bytes, void *dst);
 ACCB_API int accb_peer_allreduce(accb_peer *peer, accb_stream stream, size_t offset, long long count, int type,
                                  int op, void *dst);
+/* one kernel: synchronise, then dst[i] = first[i] (op) data_0[i] (op) .. (op) data_{rank-1}[i] -- the carry a
+ * sharded scan continues from on this rank (`first`: the seed of the whole scan, a device pointer on this rank) */
+ACCB_API int accb_peer_exscan(accb_peer *peer, accb_stream stream, size_t offset, long long count, int type, int op,
+                              const void *first, void *dst);
 ACCB_API int accb_peer_pull(accb_peer *peer, accb_stream stream, int from_rank, size_t offset, size_t bytes,
                             void *dst);
 ACCB_API int accb_peer_status(accb_peer *peer, accb_stream stream, int *timed_out);

@@ -50,6 +50,9 @@ def main():
         ok = ok and bool(torch.equal(g, ref))
         carry = sh.peer_scan_carry(peer, (0, pitch)[p], torch.empty(world, dtype=torch.int32, device="cuda"))
         ok = ok and int(carry[0]) == int(ref[0::4][:rank].sum())
+        seed, c2 = torch.full((4,), 7, dtype=torch.int32, device="cuda"), torch.empty(4, dtype=torch.int32, device="cuda")
+        peer.exscan((0, pitch)[p], 4, np.int32, "add", seed, c2)  # 7 + the lower ranks' elements, in one kernel
+        ok = ok and bool(torch.equal(c2, 7 + ref.view(world, 4)[:rank].sum(dim=0, dtype=torch.int32)))
     # pull: every rank fetches the previous rank's block between two barriers
     big.copy_(torch.rand(262144, generator=gen, device="cuda"))
     mine = torch.empty_like(big)
