@@ -14,12 +14,10 @@ def device_lists(torch):
     n = torch.cuda.device_count()
     if n >= 2:
         lists.append([0, 1])
-    if n >= 4:
-        lists.append([0, 1, 2, 3])
     return lists
 
 
-@pytest.fixture(scope="module", params=range(5))
+@pytest.fixture(scope="module", params=range(4))
 def group(request, accb, torch_cuda):
     lists = device_lists(torch_cuda)
     if request.param >= len(lists):
