@@ -108,3 +108,61 @@ def test_slabs_partition_the_index_space_and_stay_aligned():
             assert edges[0][0] == 0 and edges[-1][1] == n
             assert all(edges[i][1] == edges[i + 1][0] for i in range(world - 1))
             assert all(lo % 4 == 0 for lo, _ in edges)
+
+
+class _FakePeers:
+    """The exchange buffers of all ranks as numpy arrays in one process: what peer_wide_halos asks of accb_peer_*
+    (barrier, pull) replayed on the CPU, so that the offsets it computes can be checked without GPUs."""
+
+    def __init__(self, world, nbytes):
+        self.world, self.bufs = world, [np.zeros(nbytes, np.uint8) for _ in range(world)]
+        self.base = [1 << 20] * world  # pretend device address of every rank's data area
+
+    def view(self, rank):
+        outer = self
+
+        class Peer:
+            world, data_ptr = outer.world, outer.base[rank]
+
+            def __init__(self):
+                self.rank, self.barriers, self.pulls = rank, 0, []
+
+            def barrier(self):
+                self.barriers += 1
+
+            def pull(self, from_rank, offset, nbytes, dst_ptr):
+                self.pulls.append((from_rank, offset, nbytes, dst_ptr - outer.base[rank]))
+        return Peer()
+
+
+@pytest.mark.parametrize("world", [2, 3, 4])
+@pytest.mark.parametrize("boundary", ["clamp", "wrap"])
+def test_peer_halo_pulls_name_the_neighbours_own_rows(world, boundary):
+    """peer_wide_halos on fake exchange buffers: after replaying the pulls every halo row holds the row of the global
+    grid it stands for (clamp: ranks at the global edges have no halo there; wrap: the ranks form a ring)."""
+    sh = importlib.import_module("accelerate-cuda_b200.sharded")
+    rows, w, reach = 6, 4, 2
+    row_bytes = 4 * w
+    ring = boundary == "wrap"
+    pads = [((reach if (r > 0 or ring) else 0), (reach if (r < world - 1 or ring) else 0)) for r in range(world)]
+    fake = _FakePeers(world, (rows + 2 * reach) * row_bytes)
+    grid = np.arange(world * rows * w, dtype=np.float32).reshape(world * rows, w)
+    slabs = []
+    for r in range(world):  # own rows in the middle of the padded slab, halos marked -1
+        pt, pb = pads[r]
+        slab = fake.bufs[r][:(pt + rows + pb) * row_bytes].view(np.float32).reshape(pt + rows + pb, w)
+        slab[:] = -1
+        slab[pt:pt + rows] = grid[r * rows:(r + 1) * rows]
+        slabs.append(slab)
+    peers = [fake.view(r) for r in range(world)]
+    for r in range(world):
+        assert sh.peer_wide_halos(peers[r], 0, rows, row_bytes, reach, boundary) == pads[r]
+        assert peers[r].barriers == 2  # before the pulls, and after them
+    for r in range(world):
+        for src, off, n, dst in peers[r].pulls:
+            fake.bufs[r][dst:dst + n] = fake.bufs[src][off:off + n]
+    total = world * rows
+    for r in range(world):
+        pt, pb = pads[r]
+        want = [(r * rows - pt + i) % total for i in range(pt + rows + pb)]
+        assert np.array_equal(slabs[r], grid[want])
