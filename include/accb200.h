@@ -447,6 +447,8 @@ enum { ACCB_PEER_ADD = 0, ACCB_PEER_MIN = 1, ACCB_PEER_MAX = 2, ACCB_PEER_AND = 
 ACCB_API int accb_peer_create(accb_context *ctx, int rank, int world, size_t bytes, accb_peer **peer);
 ACCB_API int accb_peer_handle(accb_peer *peer, unsigned char *handle /* ACCB_PEER_HANDLE_BYTES */);
 ACCB_API int accb_peer_connect(accb_peer *peer, const unsigned char *handles /* world x ACCB_PEER_HANDLE_BYTES */);
+/* instead of accb_peer_connect, for tests of the time limit: the other ranks never arrive */
+ACCB_API int accb_peer_loopback(accb_peer *peer);
 ACCB_API int accb_peer_data(accb_peer *peer, void **data, size_t *bytes);
 ACCB_API int accb_peer_barrier(accb_peer *peer, accb_stream stream);
 ACCB_API int accb_peer_gather(accb_peer *peer, accb_stream stream, size_t offset, size_t bytes, void *dst);

@@ -32,6 +32,23 @@ def test_peer_single_rank_forms(accb, ctx, torch_cuda, rng):
     peer.destroy()
 
 
+def test_a_rank_that_never_arrives_runs_the_wait_into_its_limit(accb, ctx, torch_cuda, monkeypatch):
+    """The failure is made on the host: this process claims to be rank 0 of 2 and nobody plays rank 1, so rank 1's
+    flag is never set.  The barrier kernel gives up after its limit (one second here), finishes normally, and the
+    status call reports ETIMEOUT; the context stays usable."""
+    t = torch_cuda
+    monkeypatch.setenv("ACCB_PEER_TIMEOUT_MS", "1000")
+    peer = accb.Peer(ctx, 0, 2, 4096, None)
+    peer.barrier()
+    with pytest.raises(accb.AccbError) as e:
+        peer.status()
+    assert e.value.status == accb.ETIMEOUT
+    peer.status()  # the error word was cleared
+    x = t.arange(10, device="cuda")
+    assert int(x.sum()) == 45  # the device still answers
+    peer.destroy()
+
+
 def test_peer_exchanges_match_nccl_on_two_or_more_gpus(torch_cuda):
     n = torch_cuda.cuda.device_count()
     if n < 2:
