@@ -118,11 +118,65 @@ __device__ __forceinline__ void trans_take(unsigned char *s, int row, int col, r
     for (int k = 0; k < N; ++k) ((comp<I>(r)[k] = trans_plane<L, I>(s)[(row + k) * kTransPitch + col]), ...);
 }
 
+/* Tiles of 4-byte components take a second layout, in which every shared-memory access is a 16-byte vector: a
+ * thread that holds a 4x4 block (four consecutive rows, four consecutive columns) transposes it in registers and
+ * stores each column piece as one vector into the TRANSPOSED tile (row = source column, 16 vectors of 4 source
+ * rows each); the result rows are then read back as vectors.  Vector j of row c sits at position j ^ ((c >> 2) & 7),
+ * which spreads the eight lanes of a quarter warp over all banks both when they store (consecutive column
+ * groups, one row group) and when they load (one row, consecutive vectors).  With scalar accesses the kernel
+ * spent its time waiting for the shared-memory instruction queue (32 instructions per thread and tile, half of
+ * them replayed for bank conflicts). */
+template <class L, int... I>
+__host__ __device__ constexpr bool trans_all4(std::integer_sequence<int, I...>) {
+    return ((sizeof(typename type_at<I, L>::type) == 4) && ...);
+}
+template <class E>
+__device__ __forceinline__ unsigned trans_bits(E v) {
+    return *reinterpret_cast<const unsigned *>(&v);
+}
+template <class E>
+__device__ __forceinline__ E trans_unbits(unsigned u) {
+    return *reinterpret_cast<const E *>(&u);
+}
+template <class L, int I>
+__device__ __forceinline__ void trans_put4_one(unsigned char *s, int ty, int tx, regs<V, L> (&a)[4]) {
+    uint4 *plane = reinterpret_cast<uint4 *>(trans_plane<L, I>(s));
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        uint4 w;
+        w.x = trans_bits(comp<I>(a[0])[k]);
+        w.y = trans_bits(comp<I>(a[1])[k]);
+        w.z = trans_bits(comp<I>(a[2])[k]);
+        w.w = trans_bits(comp<I>(a[3])[k]);
+        plane[(4 * tx + k) * (kTransTile / 4) + (ty ^ (tx & 7))] = w;
+    }
+}
+template <class L, int... I>
+__device__ __forceinline__ void trans_put4(unsigned char *s, int ty, int tx, regs<V, L> (&a)[4],
+                                           std::integer_sequence<int, I...>) {
+    (trans_put4_one<L, I>(s, ty, tx, a), ...);
+}
+template <class L, int I>
+__device__ __forceinline__ void trans_take4_one(unsigned char *s, int r, int tx, regs<V, L> &c) {
+    typedef typename type_at<I, L>::type E;
+    const uint4 w = reinterpret_cast<const uint4 *>(trans_plane<L, I>(s))[r * (kTransTile / 4) + (tx ^ ((r >> 2) & 7))];
+    comp<I>(c)[0] = trans_unbits<E>(w.x);
+    comp<I>(c)[1] = trans_unbits<E>(w.y);
+    comp<I>(c)[2] = trans_unbits<E>(w.z);
+    comp<I>(c)[3] = trans_unbits<E>(w.w);
+}
+template <class L, int... I>
+__device__ __forceinline__ void trans_take4(unsigned char *s, int r, int tx, regs<V, L> &c, std::integer_sequence<int, I...>) {
+    (trans_take4_one<L, I>(s, r, tx, c), ...);
+}
+
 template <class Fn, int CTA>
 __device__ __forceinline__ void map_transposed_body(const accb_kparams &p) {
     typedef typename Fn::In In;
     typedef typename Fn::Out Out;
     constexpr int T = kTransTile, VX = T / V, RY = CTA / VX; /* threads along a row, rows per pass */
+    /* all components 4 bytes wide, 16 x 16 threads, 4-element vectors: the all-vector tile layout */
+    constexpr bool fast = trans_all4<In>(std::make_integer_sequence<int, In::size>()) && V == 4 && VX == 16 && RY == 16;
     extern __shared__ __align__(128) unsigned char s_tile[];
     const Env env(p);
     const auto iseq = std::make_integer_sequence<int, In::size>();
@@ -136,11 +190,17 @@ __device__ __forceinline__ void map_transposed_body(const accb_kparams &p) {
         const bool full = vec && y0 + T <= H && x0 + T <= W;
         if (full) { /* 4 rows x one 16-byte vector per component and thread in flight */
             regs<V, In> a[T / RY];
+            if constexpr (fast) { /* four consecutive rows: a 4x4 block per thread */
 #pragma unroll
-            for (int q = 0; q < T / RY; ++q)
-                load_all(p.in, ((long long)(y0 + ty + q * RY) * W + x0) / V + tx, a[q]);
+                for (int q = 0; q < 4; ++q) load_all(p.in, ((long long)(y0 + 4 * ty + q) * W + x0) / V + tx, a[q]);
+                trans_put4<In>(s_tile, ty, tx, a, iseq);
+            } else {
 #pragma unroll
-            for (int q = 0; q < T / RY; ++q) trans_put<In, V>(s_tile, ty + q * RY, tx * V, a[q], iseq);
+                for (int q = 0; q < T / RY; ++q)
+                    load_all(p.in, ((long long)(y0 + ty + q * RY) * W + x0) / V + tx, a[q]);
+#pragma unroll
+                for (int q = 0; q < T / RY; ++q) trans_put<In, V>(s_tile, ty + q * RY, tx * V, a[q], iseq);
+            }
         } else {
             for (int r = ty; r < T; r += RY)
                 for (int k = 0; k < V; ++k)
@@ -158,7 +218,10 @@ __device__ __forceinline__ void map_transposed_body(const accb_kparams &p) {
                 const int r = ty + q * RY;
                 regs<V, In> a;
                 regs<V, Out> b;
-                trans_take<In, V>(s_tile, tx * V, r, a, iseq);
+                if constexpr (fast)
+                    trans_take4<In>(s_tile, r, tx, a, iseq);
+                else
+                    trans_take<In, V>(s_tile, tx * V, r, a, iseq);
                 const long long i = (long long)(x0 + r) * H + y0 + tx * V;
                 map_apply<Fn>(env, i, a, b, iseq, oseq);
                 store_all(p.out, i / V, b);

@@ -98,5 +98,6 @@ def generated_specs():
             "SMVM": A.specs(smvm, v(f32), v(i32), v(f32), v(i32))[1],   # [0] scans the segment lengths
             "SCAN_ADD_I64": A.specs(prefix_sum64, v(i64))[0],
             "SMOOTH1D": A.specs(smooth, v(f32))[0],
+            "TRANSPOSE_TILED": A.specs(lambda a: A.transpose(a), A.matrix(f32))[0],  # launched with map_transposed
         }
     return _specs

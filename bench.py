@@ -544,8 +544,35 @@ class Smooth1dWorkload(Workload):
         return bool(((o[1:-1] - ref).abs() <= 1e-6).all()) and edge
 
 
-SECONDARY_KERNEL = {"scan64": "scanl", "shortrows": "fold_staged", "smvm": "foldSeg_staged", "smooth1d": "stencil_line"}
-SECONDARY = {"scan64": Scan64Workload, "shortrows": ShortRowsWorkload, "smvm": SmvmWorkload, "smooth1d": Smooth1dWorkload}
+class TransposeWorkload(Workload):
+    """`transpose m` made manifest: the map skeleton over 64x64 shared-memory tiles (the reference runs a transpose
+    as a backpermute, i.e. a gather)."""
+    name, dtype = "transpose, Float32 8192 x 8192 (map over shared-memory tiles)", "f32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.side = n or 8192
+        self.m = t.empty((self.side, self.side), dtype=t.float32, device="cuda")
+        self.ctx.gen_uniform_f32(self.m, self.side * self.side, 0, W.SEED, W.S_MATRIX, -1.0, 1.0)
+        self.out = t.empty_like(self.m)
+        # the plain map functor (out = in) that the embedded language prints for `transpose`
+        spec = importlib.import_module("accelerate-cuda_b200.examples").generated_specs()["TRANSPOSE_TILED"]
+        self.k = self.ctx.kernel(spec).wait()
+        self.bytes = 8 * self.side * self.side
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.map_transposed(self.k, [self.m], self.out)
+        return 1
+
+    def verify(self):
+        return bool(self.t.equal(self.out, self.m.T))
+
+
+SECONDARY_KERNEL = {"scan64": "scanl", "shortrows": "fold_staged", "smvm": "foldSeg_staged", "smooth1d": "stencil_line",
+                    "transpose": "map_transposed"}
+SECONDARY = {"scan64": Scan64Workload, "shortrows": ShortRowsWorkload, "smvm": SmvmWorkload, "smooth1d": Smooth1dWorkload,
+             "transpose": TransposeWorkload}
 
 
 # ---- the reference's own algorithms on the same GPU and the same device inputs (baseline/refskel)
