@@ -261,6 +261,9 @@ __host__ __device__ constexpr int map_transposed_smem() {
 #ifndef ACCB_MAP_CTA
 #define ACCB_MAP_CTA 256
 #endif
+#ifndef ACCB_TRANS_MINB
+#define ACCB_TRANS_MINB 8 /* resident blocks per SM the transposed form is compiled for: one 16 KB tile each */
+#endif
 #ifndef ACCB_MAP_U
 #define ACCB_MAP_U 2 /* vectors per input per thread per trip */
 #endif
@@ -274,7 +277,7 @@ __host__ __device__ constexpr int map_transposed_smem() {
         map(const __grid_constant__ accb_kparams p) {                                   \
         accb::map_body<Fn, ACCB_MAP_CTA, ACCB_MAP_U>(p);                                \
     }                                                                                   \
-    extern "C" __global__ void __launch_bounds__(ACCB_MAP_CTA)                          \
+    extern "C" __global__ void __launch_bounds__(ACCB_MAP_CTA, ACCB_TRANS_MINB)         \
         map_transposed(const __grid_constant__ accb_kparams p) {                        \
         accb::map_transposed_or_nothing<Fn, ACCB_MAP_CTA>(p);                           \
     }
