@@ -95,41 +95,53 @@ __device__ __forceinline__ void map_body(const accb_kparams &p) {
  * map: apply(env, i, in-values..., out-references...) with i the OUTPUT
  * position, in an array of ip[1] rows and ip[0] columns.
  * ---------------------------------------------------------------------- */
-constexpr int kTransTile = 64;                 /* tile edge, in elements */
-constexpr int kTransPitch = kTransTile + 1;    /* odd pitch: columns of a tile fall into different banks */
-constexpr int kTransElems = kTransTile * kTransPitch;
+#ifndef ACCB_TRANS_TILE_4B
+#define ACCB_TRANS_TILE_4B 64 /* tile edge when every element-wise input is 4 bytes wide (64 or 128) */
+#endif
+constexpr int kTransTileAny = 64; /* tile edge otherwise */
+
+template <class L, int... I>
+__host__ __device__ constexpr bool trans_all4(std::integer_sequence<int, I...>) {
+    return ((sizeof(typename type_at<I, L>::type) == 4) && ...);
+}
+/* tile edge in elements; the scalar layout pads every row by one element (odd pitch: the columns of a tile fall
+ * into different banks) and the vector layout below fits into the same space */
+template <class L>
+__host__ __device__ constexpr int trans_tile() {
+    return trans_all4<L>(std::make_integer_sequence<int, L::size>()) ? ACCB_TRANS_TILE_4B : kTransTileAny;
+}
+template <class L>
+__host__ __device__ constexpr int trans_elems() {
+    return trans_tile<L>() * (trans_tile<L>() + 1);
+}
 
 template <class L, int I>
 __device__ __forceinline__ typename type_at<I, L>::type *trans_plane(unsigned char *s) {
-    return reinterpret_cast<typename type_at<I, L>::type *>(s + smem_offset<L, I, kTransElems>::value);
+    return reinterpret_cast<typename type_at<I, L>::type *>(s + smem_offset<L, I, trans_elems<L>()>::value);
 }
 /* N consecutive elements of every component into row `row` of the tile, from column `col` */
 template <class L, int N, int... I>
 __device__ __forceinline__ void trans_put(unsigned char *s, int row, int col, regs<N, L> &r,
                                           std::integer_sequence<int, I...>) {
 #pragma unroll
-    for (int k = 0; k < N; ++k) ((trans_plane<L, I>(s)[row * kTransPitch + col + k] = comp<I>(r)[k]), ...);
+    for (int k = 0; k < N; ++k) ((trans_plane<L, I>(s)[row * (trans_tile<L>() + 1) + col + k] = comp<I>(r)[k]), ...);
 }
 /* N elements of every component down column `col` of the tile, from row `row` */
 template <class L, int N, int... I>
 __device__ __forceinline__ void trans_take(unsigned char *s, int row, int col, regs<N, L> &r,
                                            std::integer_sequence<int, I...>) {
 #pragma unroll
-    for (int k = 0; k < N; ++k) ((comp<I>(r)[k] = trans_plane<L, I>(s)[(row + k) * kTransPitch + col]), ...);
+    for (int k = 0; k < N; ++k) ((comp<I>(r)[k] = trans_plane<L, I>(s)[(row + k) * (trans_tile<L>() + 1) + col]), ...);
 }
 
 /* Tiles of 4-byte components take a second layout, in which every shared-memory access is a 16-byte vector: a
  * thread that holds a 4x4 block (four consecutive rows, four consecutive columns) transposes it in registers and
- * stores each column piece as one vector into the TRANSPOSED tile (row = source column, 16 vectors of 4 source
+ * stores each column piece as one vector into the TRANSPOSED tile (row = source column, T/4 vectors of 4 source
  * rows each); the result rows are then read back as vectors.  Vector j of row c sits at position j ^ ((c >> 2) & 7),
  * which spreads the eight lanes of a quarter warp over all banks both when they store (consecutive column
  * groups, one row group) and when they load (one row, consecutive vectors).  With scalar accesses the kernel
  * spent its time waiting for the shared-memory instruction queue (32 instructions per thread and tile, half of
  * them replayed for bank conflicts). */
-template <class L, int... I>
-__host__ __device__ constexpr bool trans_all4(std::integer_sequence<int, I...>) {
-    return ((sizeof(typename type_at<I, L>::type) == 4) && ...);
-}
 template <class E>
 __device__ __forceinline__ unsigned trans_bits(E v) {
     return *reinterpret_cast<const unsigned *>(&v);
@@ -138,8 +150,9 @@ template <class E>
 __device__ __forceinline__ E trans_unbits(unsigned u) {
     return *reinterpret_cast<const E *>(&u);
 }
+/* the 4x4 block of row group `j` and column group `tx` */
 template <class L, int I>
-__device__ __forceinline__ void trans_put4_one(unsigned char *s, int ty, int tx, regs<V, L> (&a)[4]) {
+__device__ __forceinline__ void trans_put4_one(unsigned char *s, int j, int tx, regs<V, L> (&a)[4]) {
     uint4 *plane = reinterpret_cast<uint4 *>(trans_plane<L, I>(s));
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -148,18 +161,19 @@ __device__ __forceinline__ void trans_put4_one(unsigned char *s, int ty, int tx,
         w.y = trans_bits(comp<I>(a[1])[k]);
         w.z = trans_bits(comp<I>(a[2])[k]);
         w.w = trans_bits(comp<I>(a[3])[k]);
-        plane[(4 * tx + k) * (kTransTile / 4) + (ty ^ (tx & 7))] = w;
+        plane[(4 * tx + k) * (trans_tile<L>() / 4) + (j ^ (tx & 7))] = w;
     }
 }
 template <class L, int... I>
-__device__ __forceinline__ void trans_put4(unsigned char *s, int ty, int tx, regs<V, L> (&a)[4],
+__device__ __forceinline__ void trans_put4(unsigned char *s, int j, int tx, regs<V, L> (&a)[4],
                                            std::integer_sequence<int, I...>) {
-    (trans_put4_one<L, I>(s, ty, tx, a), ...);
+    (trans_put4_one<L, I>(s, j, tx, a), ...);
 }
 template <class L, int I>
 __device__ __forceinline__ void trans_take4_one(unsigned char *s, int r, int tx, regs<V, L> &c) {
     typedef typename type_at<I, L>::type E;
-    const uint4 w = reinterpret_cast<const uint4 *>(trans_plane<L, I>(s))[r * (kTransTile / 4) + (tx ^ ((r >> 2) & 7))];
+    const uint4 w =
+        reinterpret_cast<const uint4 *>(trans_plane<L, I>(s))[r * (trans_tile<L>() / 4) + (tx ^ ((r >> 2) & 7))];
     comp<I>(c)[0] = trans_unbits<E>(w.x);
     comp<I>(c)[1] = trans_unbits<E>(w.y);
     comp<I>(c)[2] = trans_unbits<E>(w.z);
@@ -174,9 +188,9 @@ template <class Fn, int CTA>
 __device__ __forceinline__ void map_transposed_body(const accb_kparams &p) {
     typedef typename Fn::In In;
     typedef typename Fn::Out Out;
-    constexpr int T = kTransTile, VX = T / V, RY = CTA / VX; /* threads along a row, rows per pass */
-    /* all components 4 bytes wide, 16 x 16 threads, 4-element vectors: the all-vector tile layout */
-    constexpr bool fast = trans_all4<In>(std::make_integer_sequence<int, In::size>()) && V == 4 && VX == 16 && RY == 16;
+    constexpr int T = trans_tile<In>(), VX = T / V, RY = CTA / VX; /* threads along a row, rows per pass */
+    /* all components 4 bytes wide and 4-element vectors: the all-vector tile layout, T/4 x T/4 blocks of 4x4 */
+    constexpr bool fast = trans_all4<In>(std::make_integer_sequence<int, In::size>()) && V == 4 && (T / 4) % RY == 0;
     extern __shared__ __align__(128) unsigned char s_tile[];
     const Env env(p);
     const auto iseq = std::make_integer_sequence<int, In::size>();
@@ -188,13 +202,18 @@ __device__ __forceinline__ void map_transposed_body(const accb_kparams &p) {
     for (long long t = blockIdx.x; t < tiles_x * tiles_y; t += gridDim.x) {
         const int y0 = (int)(t / tiles_x) * T, x0 = (int)(t % tiles_x) * T; /* source tile */
         const bool full = vec && y0 + T <= H && x0 + T <= W;
-        if (full) { /* 4 rows x one 16-byte vector per component and thread in flight */
-            regs<V, In> a[T / RY];
-            if constexpr (fast) { /* four consecutive rows: a 4x4 block per thread */
+        if (full) {
+            if constexpr (fast) { /* four consecutive rows at a time: a 4x4 block per thread and pass */
 #pragma unroll
-                for (int q = 0; q < 4; ++q) load_all(p.in, ((long long)(y0 + 4 * ty + q) * W + x0) / V + tx, a[q]);
-                trans_put4<In>(s_tile, ty, tx, a, iseq);
-            } else {
+                for (int s = 0; s < (T / 4) / RY; ++s) {
+                    const int j = ty + s * RY;
+                    regs<V, In> a[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) load_all(p.in, ((long long)(y0 + 4 * j + q) * W + x0) / V + tx, a[q]);
+                    trans_put4<In>(s_tile, j, tx, a, iseq);
+                }
+            } else { /* T / RY rows x one 16-byte vector per component and thread in flight */
+                regs<V, In> a[T / RY];
 #pragma unroll
                 for (int q = 0; q < T / RY; ++q)
                     load_all(p.in, ((long long)(y0 + ty + q * RY) * W + x0) / V + tx, a[q]);
@@ -213,7 +232,7 @@ __device__ __forceinline__ void map_transposed_body(const accb_kparams &p) {
         __syncthreads();
         /* result row x0 + r holds source column x0 + r: elements y0 + 4 tx .. + 3 come from 4 tile rows */
         if (full) {
-#pragma unroll
+#pragma unroll 4
             for (int q = 0; q < T / RY; ++q) {
                 const int r = ty + q * RY;
                 regs<V, In> a;
@@ -251,7 +270,7 @@ template <class Fn>
 __host__ __device__ constexpr int map_transposed_smem() {
     typedef typename Fn::In In;
     if constexpr (In::size > 0)
-        return smem_offset<In, In::size, kTransElems>::value;
+        return smem_offset<In, In::size, trans_elems<In>()>::value;
     else
         return 0;
 }
