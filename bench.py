@@ -890,7 +890,8 @@ def main():
                 torch.cuda.empty_cache()
             Workload.functors = "hand"
             line["generated_functors"] = gen
-        line["awhile"] = awhile_sample(accb, ctx, torch)
+        if not os.environ.get("ACCB_BENCH_SKIP_AWHILE"):  # set for profiler runs: the loop is a graph with a WHILE node
+            line["awhile"] = awhile_sample(accb, ctx, torch)
     elif world > 1 and isinstance(wl, ScanWorkload) and not args.no_extras:
         # ---- e2e at N GPUs: every rank uploads its slab from pinned host memory, takes part in the carry exchange,
         # scans, and downloads its part of the result; wall clock between barriers, max over ranks
