@@ -709,7 +709,12 @@ def run_reference(args):
     if rank != 0:
         return
     oracle = importlib.import_module("oracle")
-    threads = oracle.max_threads()
+    # all the host threads this process may use: torchrun sets OMP_NUM_THREADS=1, which is not a property of the host
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    threads = max(oracle.max_threads(), cores)
     n = 1 << 26
     W = importlib.import_module("accelerate-cuda_b200.workloads")
     x = W.uniform_i32(W.SEED, W.S_SCAN, n, 16)
