@@ -714,6 +714,12 @@ def run_reference(args):
         cores = len(os.sched_getaffinity(0))
     except AttributeError:
         cores = os.cpu_count() or 1
+    try:  # a container's CPU quota, where there is one
+        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()
+        if quota != "max":
+            cores = min(cores, max(1, int(quota) // int(period)))
+    except (OSError, ValueError):
+        pass
     threads = max(oracle.max_threads(), cores)
     n = 1 << 26
     W = importlib.import_module("accelerate-cuda_b200.workloads")
