@@ -50,6 +50,7 @@ struct Driver {
     CUresult (*CtxPopCurrent)(CUcontext *) = nullptr;
     CUresult (*GetErrorString)(CUresult, const char **) = nullptr;
     CUresult (*MemcpyDtoH)(void *, CUdeviceptr, size_t) = nullptr;
+    CUresult (*DevicePrimaryCtxGetState)(CUdevice, unsigned *, int *) = nullptr;
 };
 const Driver &driver();
 
@@ -122,6 +123,26 @@ struct CudaAllocator : DeviceAllocator {
 
 }  // namespace accb_rt
 
+namespace accb_rt {
+/* Tuning knobs, read from the environment ONCE when a context is created (never on the launch path):
+ *   ACCB_FOLD_STAGE_MAX, ACCB_FOLD_NO_STAGE, ACCB_FOLDSEG_STAGE_MAX, ACCB_FOLDSEG_STAGE_FILL8,
+ *   ACCB_FOLDSEG_STAGE_LANES, ACCB_PERMUTE_REPLICAS, ACCB_STENCIL_NO_TILE, ACCB_STENCIL_ROWS,
+ *   ACCB_PIPELINE_CHUNK_LOG2, ACCB_NO_PIPELINE. */
+struct Tuning {
+    long long fold_stage_max = 128;    /* longest row the staged thread-per-row fold takes */
+    bool fold_no_stage = false;
+    long long foldseg_stage_max = 384; /* longest average segment the staged foldSeg takes */
+    int foldseg_fill8 = 6;             /* eighths of the shared-memory window a run of segments aims to fill */
+    int foldseg_lanes = 0;             /* lanes per segment of the staged foldSeg; 0: by segment length */
+    int permute_replicas = 4;          /* shared-memory copies of a privatised permute destination */
+    bool stencil_no_tile = false;
+    int stencil_rows = 64;             /* band height of the register-form stencil */
+    int pipeline_chunk_log2 = 0;       /* chunk of the host pipeline; 0: default */
+    bool no_pipeline = false;
+    void read_environment();
+};
+}  // namespace accb_rt
+
 struct accb_context {
     int device = 0;
     CUcontext foreign = nullptr; /* non-null: a context the caller owns */
@@ -142,6 +163,8 @@ struct accb_context {
     std::map<std::tuple<CUfunction, int, size_t>, int> occupancy_cache; /* resident blocks per SM */
     size_t mem_hits = 0, disk_hits = 0, compiles = 0;
     bool trace_exec = false, trace_gc = false, trace_cc = false;
+    accb_rt::Tuning tune;
+    std::set<void *> loops_unchecked; /* counter words of device-resident awhile loops whose overrun flag nobody has read yet */
 };
 
 namespace accb_rt {
@@ -150,6 +173,7 @@ namespace accb_rt {
 struct CtxGuard {
     accb_context *c;
     bool pushed = false;
+    int previous = -1; /* the device to make current again when the scope ends, or -1 */
     explicit CtxGuard(accb_context *ctx);
     ~CtxGuard();
 };

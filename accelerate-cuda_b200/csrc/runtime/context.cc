@@ -8,6 +8,7 @@
  */
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cstdlib>
 
 #include "common.h"
@@ -48,6 +49,7 @@ const Driver &driver() {
         d.CtxPopCurrent = (decltype(d.CtxPopCurrent))sym("cuCtxPopCurrent_v2");
         d.GetErrorString = (decltype(d.GetErrorString))sym("cuGetErrorString");
         d.MemcpyDtoH = (decltype(d.MemcpyDtoH))sym("cuMemcpyDtoH_v2");
+        d.DevicePrimaryCtxGetState = (decltype(d.DevicePrimaryCtxGetState))sym("cuDevicePrimaryCtxGetState");
         d.ok = ok;
     });
     return d;
@@ -97,12 +99,38 @@ bool inject_failure(const char *site) {
     return ++counts[site] == nth;
 }
 
+void Tuning::read_environment() {
+    auto num = [](const char *name, long long dflt) {
+        const char *e = getenv(name);
+        return e ? atoll(e) : dflt;
+    };
+    fold_stage_max = num("ACCB_FOLD_STAGE_MAX", fold_stage_max);
+    fold_no_stage = getenv("ACCB_FOLD_NO_STAGE") != nullptr;
+    foldseg_stage_max = num("ACCB_FOLDSEG_STAGE_MAX", foldseg_stage_max);
+    foldseg_fill8 = (int)std::min(8LL, std::max(1LL, num("ACCB_FOLDSEG_STAGE_FILL8", foldseg_fill8)));
+    foldseg_lanes = (int)std::max(0LL, num("ACCB_FOLDSEG_STAGE_LANES", 0));
+    permute_replicas = (int)std::max(1LL, num("ACCB_PERMUTE_REPLICAS", permute_replicas));
+    stencil_no_tile = getenv("ACCB_STENCIL_NO_TILE") != nullptr;
+    stencil_rows = (int)std::max(1LL, num("ACCB_STENCIL_ROWS", stencil_rows));
+    pipeline_chunk_log2 = (int)num("ACCB_PIPELINE_CHUNK_LOG2", 0);
+    no_pipeline = getenv("ACCB_NO_PIPELINE") != nullptr;
+}
+
 CtxGuard::CtxGuard(accb_context *ctx) : c(ctx) {
     if (!c) return;
     if (c->foreign) {
         pushed = driver().CtxPushCurrent(c->foreign) == CUDA_SUCCESS;
     } else {
-        cudaSetDevice(c->device);
+        /* the caller's current device comes back when the scope ends -- but only if that device already has a
+         * primary context: making a device current creates one, and a process that never touched, say,
+         * device 0 must not start holding memory there because a library call passed through */
+        int cur = -1;
+        if (cudaGetDevice(&cur) == cudaSuccess && cur != c->device) {
+            unsigned flags = 0;
+            int active = 0;
+            if (driver().DevicePrimaryCtxGetState((CUdevice)cur, &flags, &active) == CUDA_SUCCESS && active) previous = cur;
+        }
+        if (cur != c->device) cudaSetDevice(c->device);
     }
 }
 CtxGuard::~CtxGuard() {
@@ -110,6 +138,7 @@ CtxGuard::~CtxGuard() {
         CUcontext old;
         driver().CtxPopCurrent(&old);
     }
+    if (previous >= 0) cudaSetDevice(previous);
 }
 
 void *CudaAllocator::alloc(size_t bytes) {
@@ -190,6 +219,7 @@ int accb_context_create(int device, void *cu_context, accb_context **out) {
     c->trace_exec = trace_enabled("exec");
     c->trace_gc = trace_enabled("gc");
     c->trace_cc = trace_enabled("cc");
+    c->tune.read_environment();
     if (c->cc_major != 10)
         return fail(nullptr, ACCB_EINVAL, "device %d is sm_%d%d; this library only carries sm_100a code", device,
                     prop.major, prop.minor);
@@ -230,6 +260,15 @@ int accb_context_sync(accb_context *ctx) {
             cudaMemset(kv.second.words + 2, 0, sizeof(unsigned));
             return fail(ctx, ACCB_ETIMEOUT, "a bounded device-side wait (scan look-back or permute lock) gave up");
         }
+    }
+    /* device-resident awhile loops started without an iteration count: were they cut off at max_iters? */
+    std::set<void *> loops;
+    loops.swap(ctx->loops_unchecked);
+    for (void *words : loops) {
+        unsigned long long w[2] = {0, 0};
+        st = check_cuda(ctx, cudaMemcpy(w, words, sizeof w, cudaMemcpyDeviceToHost), "reading loop words");
+        if (st != ACCB_OK) return st;
+        if (w[1]) return fail(ctx, ACCB_ETIMEOUT, "awhile: still true after %lld iterations", (long long)w[0]);
     }
     return ACCB_OK;
 }

@@ -191,7 +191,7 @@ int accb_group_create(const int *devices, int n, accb_group **out) {
                 cudaGetLastError();
                 continue;
             }
-            cudaSetDevice(g->dev[i]);
+            CtxGuard on_i(g->ctx[i]); /* makes dev[i] current and hands the caller's device back afterwards */
             if (cudaDeviceEnablePeerAccess(g->dev[j], 0) != cudaSuccess) cudaGetLastError(); /* already enabled */
         }
     if (st != ACCB_OK) {

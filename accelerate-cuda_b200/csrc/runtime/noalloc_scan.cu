@@ -16,10 +16,9 @@
  *
  * The array's name is only meaningful in device code; on the host it is a
  * stand-in symbol, so the address the kernel gets is looked up with
- * cudaGetSymbolAddress, once per device, with that device current.
+ * cudaGetSymbolAddress with that device current (on every call: the answer
+ * belongs to the current CUDA context, not to the device ordinal).
  */
-#include <mutex>
-
 #include "common.h"
 
 /* 32-byte status records instead of 128-byte ones keep the resident array at
@@ -49,10 +48,6 @@ __global__ void __launch_bounds__(kCta, 6) noalloc_scanl_add_i32(const __grid_co
     accb::scan_body<AddI32, kCta, kRows, false, false, true>(p);
 }
 
-/* device address of g_noalloc_scratch per device, looked up on first use */
-std::mutex g_mu;
-void *g_addr[64] = {nullptr};
-
 }  // namespace
 
 using namespace accb_rt;
@@ -78,20 +73,17 @@ extern "C" int accb_scanl_add_i32_noalloc(int device, accb_stream stream, const 
         if (previous != device) cudaSetDevice(previous);
     };
 
-    /* set-up, once per device: the device address of the resident scratch array */
+    /* The device address of the resident scratch array, asked for on EVERY call with `device` current.  The
+     * array has one instance per CUDA context, so an address remembered per device ordinal would be wrong for a
+     * caller that switches between the primary context and a context of its own on the same GPU, or that
+     * resets the device.  Only the first call on a device does real work here (it loads the library's
+     * image onto that device, which is why that call belongs before any stream capture); later calls are a
+     * table look-up and allocate nothing. */
     void *scratch = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(g_mu);
-        if (!g_addr[device]) {
-            void *ptr = nullptr;
-            st = check_cuda(nullptr, cudaGetSymbolAddress(&ptr, g_noalloc_scratch), "cudaGetSymbolAddress(scratch)");
-            if (st != ACCB_OK) {
-                restore();
-                return st;
-            }
-            g_addr[device] = ptr;
-        }
-        scratch = g_addr[device];
+    st = check_cuda(nullptr, cudaGetSymbolAddress(&scratch, g_noalloc_scratch), "cudaGetSymbolAddress(scratch)");
+    if (st != ACCB_OK) {
+        restore();
+        return st;
     }
 
     cudaStream_t s = (cudaStream_t)stream;

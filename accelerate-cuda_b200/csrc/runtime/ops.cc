@@ -159,12 +159,6 @@ static int pick_group(long long items, long long units, long long block_from) {
     return g;
 }
 
-/* longest row (fold) / average segment (foldSeg) the staged thread-per-unit form is used for */
-static long long stage_len_max(const char *env_name, long long dflt) {
-    if (const char *e = getenv(env_name)) return atoll(e);
-    return dflt;
-}
-
 }  // namespace accb_rt
 
 using namespace accb_rt;
@@ -306,8 +300,8 @@ int accb_fold_dim(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     const char *entry = group > 32 ? "fold" : group == 32 ? "fold_warp" : group == 16 ? "fold_g16" : group == 8 ? "fold_g8" : "fold_g4";
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
-    if (cols >= 1 && cols <= stage_len_max("ACCB_FOLD_STAGE_MAX", 128) && rows * cols >= (1 << 16) && rows * cols < (1LL << 40) && pr.meta.v[6] > 0 &&
-        (p.flags & ACCB_F_VEC) && !getenv("ACCB_FOLD_NO_STAGE")) {
+    if (cols >= 1 && cols <= ctx->tune.fold_stage_max && rows * cols >= (1 << 16) && rows * cols < (1LL << 40) && pr.meta.v[6] > 0 &&
+        (p.flags & ACCB_F_VEC) && !ctx->tune.fold_no_stage) {
         /* many short rows: a block stages a run of whole rows (the matrix read as one long
          * vector) in shared memory and every thread reduces whole rows */
         const size_t smem = (size_t)pr.meta.v[6];
@@ -374,7 +368,7 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     const char *entry = group > 32 ? "foldSeg_block" : group == 32 ? "foldSeg" : group == 16 ? "foldSeg_g16" : group == 8 ? "foldSeg_g8" : "foldSeg_g4";
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
-    if (avg <= stage_len_max("ACCB_FOLDSEG_STAGE_MAX", 384) && rows * nseg >= 4096 && (rows == 1 || cols % 16 == 0) && pr.meta.v[6] > 0 &&
+    if (avg <= ctx->tune.foldseg_stage_max && rows * nseg >= 4096 && (rows == 1 || cols % 16 == 0) && pr.meta.v[6] > 0 &&
         (p.flags & ACCB_F_VEC)) {
         /* short segments: a block stages a run of consecutive segments in shared memory and every
          * thread reduces whole segments; the run is sized to fill 3/4 of the window on average */
@@ -384,14 +378,12 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
         StreamScratch *sc = scratch_for(ctx, (cudaStream_t)stream);
         if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
         /* a run that overflows the window reads its last segments from global memory, so aim high */
-        long long fill = 6;
-        if (const char *e = getenv("ACCB_FOLDSEG_STAGE_FILL8")) fill = std::min(8, std::max(1, atoi(e)));
+        const long long fill = ctx->tune.foldseg_fill8;
         const long long run =
             std::min<long long>(std::max(1LL, (ps.meta.v[3] - 32) * fill / 8 / std::max(1LL, avg)), 16LL * ps.meta.v[5]);
         /* lanes per segment: a thread takes whole segments of up to ~100 elements; longer ones are shared by
          * 8 lanes so that the few segments of a window still occupy the block */
-        long long lanes = avg <= 112 ? 1 : 8;
-        if (const char *e = getenv("ACCB_FOLDSEG_STAGE_LANES")) lanes = std::max(1, atoi(e));
+        const long long lanes = ctx->tune.foldseg_lanes > 0 ? ctx->tune.foldseg_lanes : (avg <= 112 ? 1 : 8);
         p.ip[4] = run;
         p.ip[5] = lanes;
         p.aux[1] = sc->words + 2;
@@ -541,8 +533,7 @@ int accb_permute(accb_context *ctx, accb_kernel *k, accb_stream stream, const ac
     const bool needs_lock = pr.meta.v[5] != 0;
     /* privatise in shared memory when R skewed copies of the destination fit */
     if (k->skeleton == SK_PERMUTE_SMEM && (nout + 1) * elem <= 96 * 1024) {
-        int R = 4;
-        if (const char *e = getenv("ACCB_PERMUTE_REPLICAS")) R = std::max(1, atoi(e));
+        int R = ctx->tune.permute_replicas;
         while (R > 1 && (R & (R - 1))) R &= R - 1; /* power of two */
         while (R > 1 && (long long)R * (nout + 1) * elem > 200 * 1024) R >>= 1;
         const size_t smem = (size_t)R * (nout + 1) * elem;
@@ -600,7 +591,7 @@ static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, 
     /* Tile form (input tile staged in shared memory by TMA): needs 4-byte elements (the kernel
      * reports 0 bytes of shared memory otherwise), 16-byte aligned arrays, widths that are
      * multiples of 4 and enough rows to fill a tile. */
-    bool staged = (p.flags & ACCB_F_VEC) && W % 4 == 0 && !getenv("ACCB_STENCIL_NO_TILE");
+    bool staged = (p.flags & ACCB_F_VEC) && W % 4 == 0 && !ctx->tune.stencil_no_tile;
     for (int a = 0; a < nsrc; ++a) staged = staged && p.ip[6 + 2 * a] % 4 == 0;
     const bool tiled = staged && pr.meta.v[6] > 0 && H >= 16;
     if (staged && out->rank == 1 && pr.meta.v[5] > 0 && W >= 4096) {
@@ -626,8 +617,7 @@ static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, 
     }
     int txw = 32;
     while (txw < pr.block && txw * 4 < W) txw *= 2;
-    int rb = 64;
-    if (const char *e = getenv("ACCB_STENCIL_ROWS")) rb = std::max(1, atoi(e));
+    const int rb = ctx->tune.stencil_rows;
     const int ty = pr.block / txw;
     p.ip[0] = H;
     p.ip[1] = W;

@@ -543,9 +543,9 @@ static int run_host_pipelined_scan(accb_program *p, const accb_array *host_in, a
         return 0;
     const long long n = host_in[0].shape[0];
     long long chunk = 1LL << 23; /* elements per chunk: long enough for the copy engines, short ramps at both ends */
-    if (const char *e = getenv("ACCB_PIPELINE_CHUNK_LOG2")) chunk = 1LL << std::min(28, std::max(16, atoi(e)));
-    if (n < 2 * chunk || getenv("ACCB_NO_PIPELINE")) return 0;
     accb_context *ctx = p->ctx;
+    if (ctx->tune.pipeline_chunk_log2 > 0) chunk = 1LL << std::min(28, std::max(16, ctx->tune.pipeline_chunk_log2));
+    if (n < 2 * chunk || ctx->tune.no_pipeline) return 0;
     const accb_value_type &tin = p->types[0], &tout = p->types[nd.out_id];
     auto run = [&]() -> int {
         for (int i = 0; i < 3; ++i)
@@ -895,6 +895,10 @@ int accb_awhile(accb_program *cond, accb_program *body, accb_stream stream, cons
         TRY(check_cuda(ctx, cudaStreamSynchronize(s), "cudaStreamSynchronize"));
         *iterations = (long long)w[0];
         if (w[1]) return fail(ctx, ACCB_ETIMEOUT, "awhile: still true after %lld iterations", (long long)w[0]);
+    } else {
+        /* nobody waits here: a loop cut off at max_iters is reported by the next accb_context_sync, as the
+         * bounded waits of scans and permutes are */
+        ctx->loops_unchecked.insert(body->loop_words);
     }
     return ACCB_OK;
 }
@@ -907,7 +911,10 @@ int accb_program_destroy(accb_program *p) {
         cudaDeviceSynchronize();
         if (p->graph_exec) cudaGraphExecDestroy(p->graph_exec);
         if (p->loop_exec) cudaGraphExecDestroy(p->loop_exec);
-        if (p->loop_words) cudaFree(p->loop_words);
+        if (p->loop_words) {
+            p->ctx->loops_unchecked.erase(p->loop_words);
+            cudaFree(p->loop_words);
+        }
         for (auto &v : p->pool)
             for (auto &b : v)
                 if (b.ptr) cudaFree(b.ptr);

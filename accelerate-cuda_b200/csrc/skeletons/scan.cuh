@@ -277,9 +277,6 @@ __device__ __forceinline__ Opt<typename Fn::elem> scan_lookback(const accb_kpara
         long long look = t - 1; /* lane l examines tile look - l */
         int spins = 0;
         bool done = false;
-#ifdef ACCB_SCAN_EXPERIMENT_NO_LOOKBACK
-        done = true; /* timing experiment only: results are wrong */
-#endif
         while (!done) {
             const long long idx = look - lane;
             T v;

@@ -30,7 +30,8 @@ innermost dimension of matrices and the segmented ``scanl1Seg`` / ``scanr1Seg``,
 
 Restrictions of this front end (not of the skeletons): ranks up to 3; the stencil skeleton serves vectors and matrices
 of one component (cubes and tuple elements fall back to a gathering ``generate``); seeds and fill values are constants; a ``zipWith`` of arrays of different shape is an error at run time
-instead of the intersection; no ``awhile`` / ``acond`` (loop and branch in Python around compiled functions).
+instead of the intersection; no ``acond`` (branch in Python around compiled functions; ``awhile`` exists, see the
+end of this file).
 """
 from __future__ import annotations
 

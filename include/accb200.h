@@ -168,7 +168,7 @@ ACCB_API int accb_launch_count(accb_context *ctx, unsigned long long *launches);
 ACCB_API int accb_map(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
                       const void *scalars, size_t scalar_bytes, const accb_array *out);
 /* `map f (transpose m)` with the same kernel object as `map f m`: the environment arrays that the functor
- * reads element-wise are matrices of the transposed shape of `out` and go through 32x32 shared-memory tiles, so
+ * reads element-wise are matrices of the transposed shape of `out` and go through 64x64 shared-memory tiles, so
  * that loads and stores are both contiguous.  In the reference a transpose is a backpermute, i.e. a gather
  * (mkTransform, CUDA/CodeGen/IndexSpace.hs:96-141). */
 ACCB_API int accb_map_transposed(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
@@ -217,10 +217,14 @@ ACCB_API int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, co
  *   - n may be at most 2^28 (268 435 456) elements; larger inputs are refused
  *     with ACCB_EINVAL and a message in accb_last_error(NULL).
  *   - `status` is NULL or a device word the caller owns: it is cleared on the
- *     stream and set to 1 if a bounded device-side wait gave up.
- *   - The first call on a device looks up the array's device address (which
- *     makes the CUDA runtime load the library's code there); make that first
- *     call before any stream capture begins.
+ *     stream and set to 1 if a bounded device-side wait gave up.  With
+ *     status == NULL such a failure cannot be observed: the output is then
+ *     wrong without any signal, so pass a word unless the result is checked
+ *     by other means.
+ *   - Every call looks up the array's device address in the current CUDA
+ *     context.  The first call on a device makes the CUDA runtime load the
+ *     library's code there; make that first call before any stream capture
+ *     begins.
  *   - All calls on a device share the one array, which keeps the previous
  *     call's contents; each call clears on `stream` what it will read.  Two
  *     calls that overlap on the GPU (different streams, no dependency between
@@ -266,6 +270,14 @@ typedef struct {
 } OutputArray;
 
 ACCB_API AccHandle accelerateCreate(int32_t device, void *cu_context);
+/* AccFFI.h:27-30 defines accelerateInit in the header itself: it starts the Haskell run-time system (hs_init) and
+ * calls accelerateCreate.  There is no run-time system to start here, so argc / argv are ignored; C code written
+ * against AccFFI.h compiles unchanged. */
+static inline AccHandle accelerateInit(int argc, char **argv, int device, void *cu_context) {
+    (void)argc;
+    (void)argv;
+    return accelerateCreate((int32_t)device, cu_context);
+}
 ACCB_API void accelerateDestroy(AccHandle hndl);
 ACCB_API void runProgram(AccHandle hndl, AccProgram p, InputArray *in, OutputArray *out);
 ACCB_API void freeOutput(OutputArray *out);
@@ -348,9 +360,10 @@ ACCB_API int accb_program_run_graph(accb_program *p, accb_stream stream, const a
  *                       launches of `body`, the copies and `cond`; the flag never leaves the device and the call
  *                       returns without waiting.  Recorded at the first call for these arrays on this stream
  *                       (not the default stream) and replayed afterwards.
- * max_iters > 0 bounds the loop on the device as well: when it stops the loop, the call (host mode) or the first
- * call that passes a non-NULL `iterations` (which waits for the stream) returns ACCB_ETIMEOUT.  `iterations`, if
- * not NULL, receives the number of times the body ran. */
+ * max_iters > 0 bounds the loop on the device as well.  When it stops the loop, ACCB_ETIMEOUT is returned by the
+ * call itself in host mode; in device mode by the call itself when `iterations` is not NULL (the call then waits
+ * for the stream), otherwise by the next accb_context_sync.  `iterations`, if not NULL, receives the number of
+ * times the body ran. */
 enum { ACCB_AWHILE_HOST = 0, ACCB_AWHILE_DEVICE = 1 };
 ACCB_API int accb_awhile(accb_program *cond, accb_program *body, accb_stream stream, const accb_array *state,
                          int mode, long long max_iters, long long *iterations);
@@ -437,7 +450,8 @@ ACCB_API int accb_group_stencil_iterate(accb_group *grp, accb_kernel *k, const a
  *                        so that every rank gets the same bits
  *   accb_peer_barrier    synchronise only;  accb_peer_pull copies from ONE rank's buffer without synchronising
  * The synchronisation is a flag per rank in every buffer (release stores to the peers, acquire polling of the own
- * buffer); a wait gives up after about two seconds and accb_peer_status then reports ACCB_ETIMEOUT.  A rank may
+ * buffer); a wait gives up after five seconds (ACCB_PEER_TIMEOUT_MS, read when the buffer is created, changes that)
+ * and accb_peer_status then reports ACCB_ETIMEOUT.  A rank may
  * overwrite data it exchanged only after the NEXT synchronising call has returned on its stream, since slower
  * ranks may still be reading: callers alternate between two offsets.  No counterpart in the reference. */
 typedef struct accb_peer accb_peer;

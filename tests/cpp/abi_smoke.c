@@ -29,6 +29,8 @@ int main(void) {
             if (accb_group_create(devs, 2, &grp) == ACCB_OK || grp != NULL) return 5;
             if (!accb_last_error(NULL) || !accb_last_error(NULL)[0]) return 6;
             if (accelerateCreate(0, NULL) != NULL) return 7;
+            /* the AccFFI.h spelling: argc / argv are accepted and ignored */
+            if (accelerateInit(0, NULL, 0, NULL) != NULL) return 8;
         }
     }
     puts("OK");
