@@ -20,7 +20,7 @@
 #define ACCB_MAX_ARR 8   /* environment arrays */
 #define ACCB_MAX_RANK 4
 #define ACCB_MAX_AUX 6
-#define ACCB_MAX_IP 10
+#define ACCB_MAX_IP 12
 #define ACCB_SCALAR_BYTES 64
 
 /* accb_kparams.flags */

@@ -139,9 +139,10 @@ __device__ __forceinline__ T imod(T a, T b) {
  * 0, 0}.  It stands in for the (entry name, occupancy, block size, shared
  * memory) record the reference keeps per kernel
  * (Data/Array/Accelerate/CUDA/AST.hs:51-59). */
-#define ACCB_META7(id, cta, rec, tile, u, extra, smem)                         \
+#define ACCB_META8(id, cta, rec, tile, u, extra, smem, last)                   \
     extern "C" __global__ void accb_meta_query(int *out) {                     \
-        const int m[8] = {(id), (cta), (int)(rec), (int)(tile), (u), (extra), (int)(smem), 0}; \
+        const int m[8] = {(id), (cta), (int)(rec), (int)(tile), (u), (extra), (int)(smem), (int)(last)}; \
         for (int i = 0; i < 8; ++i) out[i] = m[i];                             \
     }
+#define ACCB_META7(id, cta, rec, tile, u, extra, smem) ACCB_META8(id, cta, rec, tile, u, extra, smem, 0)
 #define ACCB_META(id, cta, rec, tile, u, extra) ACCB_META7(id, cta, rec, tile, u, extra, 0)

@@ -55,6 +55,24 @@
  * (mbarrier) the kernel raises the error word and carries on, so a launch
  * always terminates.
  *
+ * Several GPUs (entries scanl_bc, scanl1_bc; host side accb_peer_scan).  The
+ * vector is dealt to the G GPUs in blocks of TPB tiles: global block j lives
+ * on GPU j mod G, which holds its blocks one after the other.  Every GPU runs
+ * this same single-pass kernel over its own blocks, so every element still
+ * crosses DRAM twice (a scan over contiguous slabs needs each slab's total
+ * before it can start, i.e. a third pass).  Inside a block the look-back is
+ * the one above, stopped at the block's first tile.  That first tile takes its
+ * exclusive prefix from a second, much shorter chain: one status record per
+ * BLOCK, of which every GPU keeps a full copy in memory the other GPUs can
+ * write.  The last tile of a block stores the block's aggregate -- and later
+ * its inclusive prefix -- into every GPU's copy with plain peer stores over
+ * NVLink (no multicast); the first tile of a block polls only its own GPU's
+ * copy.  All blocks of one round (one per GPU) publish their aggregates at
+ * about the same time and independently of one another, so a round costs one
+ * NVLink store latency, not G of them, and several blocks per GPU are in
+ * flight to hide it.  Waits that depend on another GPU are bounded by the
+ * global timer (ip[9] nanoseconds).
+ *
  * Runtime-owned scratch (never cleared between launches):
  *   aux[0] tile status words, aux[1] ticket counter, aux[2] error word.
  * Status words carry the launch epoch (ip[2]); words of earlier launches read
@@ -63,6 +81,10 @@
  *   ip[0] tiles, ip[1] ticket base, ip[2] epoch, ip[3] index of the total in
  *   the "sum" slots out[Out::size..] (or -1), ip[4] index at which the seed is
  *   stored in the sum slots (or -1).
+ * Block-cyclic entries in addition: ip[5] tiles per block, ip[6] number of GPUs,
+ * ip[7] this GPU's rank, ip[8] epoch of the block records (the same on every
+ * GPU), ip[9] time limit in ns, ip[10] byte offset of the block records in
+ * every GPU's exchange buffer; aux[3] device table of the G buffers' addresses.
  */
 #pragma once
 #include "../cubits/accb_vec.cuh"
@@ -331,6 +353,212 @@ __device__ __forceinline__ Opt<typename Fn::elem> scan_lookback(const accb_kpara
     return pre;
 }
 
+/* ---- block records of the block-cyclic scan: one per global block, dense, read and written with system
+ * scope because the writers are other GPUs.  Flag {epoch << 2 | state} and value travel in one store: a 64-bit
+ * word for values up to 4 bytes, a 128-bit word for 8-byte values (16 bytes per record either way). ---- */
+constexpr int kBlockRecordBytes = 16;
+
+template <class T>
+struct BlockStatus {
+    static_assert(sizeof(T) <= 8, "block records carry values of up to 8 bytes");
+    static __device__ __forceinline__ void publish(unsigned char *base, long long j, unsigned flag, T v) {
+        unsigned char *rec = base + j * kBlockRecordBytes;
+        if constexpr (sizeof(T) <= 4) {
+            unsigned bits = 0;
+            memcpy(&bits, &v, sizeof(T));
+            const unsigned long long word = ((unsigned long long)flag << 32) | bits;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(rec), "l"(word) : "memory");
+        } else {
+            unsigned long long bits;
+            memcpy(&bits, &v, 8);
+            const unsigned long long head = (unsigned long long)flag << 32;
+            asm volatile("{ .reg .b128 q; mov.b128 q, {%1, %2}; st.relaxed.sys.global.b128 [%0], q; }" ::"l"(rec), "l"(head),
+                         "l"(bits)
+                         : "memory");
+        }
+    }
+    static __device__ __forceinline__ unsigned peek(const unsigned char *base, long long j, T &v) {
+        const unsigned char *rec = base + j * kBlockRecordBytes;
+        if constexpr (sizeof(T) <= 4) {
+            unsigned long long word;
+            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(rec) : "memory");
+            const unsigned bits = (unsigned)word;
+            memcpy(&v, &bits, sizeof(T));
+            return (unsigned)(word >> 32);
+        } else {
+            unsigned long long head, bits;
+            asm volatile("{ .reg .b128 q; ld.relaxed.sys.global.b128 q, [%2]; mov.b128 {%0, %1}, q; }"
+                         : "=l"(head), "=l"(bits)
+                         : "l"(rec)
+                         : "memory");
+            memcpy(&v, &bits, 8);
+            return (unsigned)(head >> 32);
+        }
+    }
+};
+
+__device__ __forceinline__ unsigned long long scan_global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+/* combines a look-back window: lane l holds the record of the (l+1)-th nearest predecessor, `first` is the
+ * nearest lane whose record is a full prefix (32: none); returns, in every lane, the combination of the
+ * records up to and including that one, far to near */
+template <class Fn>
+__device__ __forceinline__ Opt<typename Fn::elem> scan_window(typename Fn::elem v, bool inside, int first) {
+    const ScanOp<Fn, false> op;
+    const int lane = lane_id();
+    Opt<typename Fn::elem> win;
+    win.v = v;
+    win.have = inside && (lane <= first);
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        Opt<typename Fn::elem> o = shfl_down(win, d);
+        if (lane + d < 32) win = op(o, win);
+    }
+    return shfl_idx(win, 0);
+}
+
+/* ---- look-back of the block-cyclic scan (left scans), run by warp 0 of the block that owns LOCAL tile t.
+ * Tile t is tile k = t mod TPB of local block t / TPB, i.e. of global block j = (t / TPB) * G + g.
+ *   k > 0: the look-back above over the earlier tiles of the same block.  The record of the block's first tile
+ *          counts only once it holds that tile's inclusive prefix (which includes everything before the block).
+ *          The LAST tile of a block first accepts that record as an aggregate too: when its walk reaches the
+ *          block's first tile without meeting a prefix it knows the block's aggregate, stores it into every
+ *          GPU's block records, and only then insists on the prefix.
+ *   k = 0: publishes its aggregate for the tiles behind it, then walks the block records of its own GPU's copy
+ *          from block j - 1 downwards (aggregates until a prefix; block 0 only ever publishes a prefix, which
+ *          contains the seed).
+ * The last tile of a block finally stores the block's inclusive prefix into every GPU's block records. ---- */
+template <class Fn>
+__device__ __forceinline__ Opt<typename Fn::elem> scan_lookback_bc(const accb_kparams &p, long long t,
+                                                                   long long ntiles, typename Fn::elem agg) {
+    typedef typename Fn::elem T;
+    typedef Opt<T> O;
+    const ScanOp<Fn, false> op;
+    const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
+    O pre;
+    pre.have = 0;
+    if constexpr (sizeof(T) <= 8) {
+        const bool seeded = (p.flags & ACCB_F_HAS_SEED) != 0;
+        const unsigned epoch = (unsigned)p.ip[2]; /* of this GPU's tile records */
+        const unsigned pe = (unsigned)p.ip[8];    /* of the block records */
+        const TileStatus<T> status(p.aux[0]);
+        unsigned int *err = static_cast<unsigned int *>(p.aux[2]);
+        const int lane = lane_id();
+        const long long TPB = p.ip[5];
+        const int G = (int)p.ip[6], g = (int)p.ip[7];
+        const unsigned long long limit_ns = (unsigned long long)p.ip[9];
+        const long long k = t % TPB, t0 = t - k;
+        const long long j = (t / TPB) * G + g;
+        const bool last_of_block = (k == TPB - 1) || (t == ntiles - 1);
+        unsigned char *const *bases = static_cast<unsigned char *const *>(p.aux[3]);
+        const long long boff = p.ip[10];
+        /* all lanes hold the same flag and value: lane l stores into GPU l's copy (l + 32, ...) */
+        auto publish_block = [&](unsigned state, T v) {
+            for (int r = lane; r < G; r += 32) BlockStatus<T>::publish(bases[r] + boff, j, (pe << 2) | state, v);
+        };
+        const unsigned long long t_start = scan_global_ns();
+        unsigned spins = 0;
+        /* bounded waits: true once the time limit has passed, another tile has given up, or the poll count
+         * says the timer itself cannot be trusted (called by all lanes alike) */
+        auto expired = [&]() -> bool {
+            if ((++spins & 63u) != 0) return false;
+            return spins > (1u << 24) || *static_cast<volatile unsigned int *>(err) != 0u ||
+                   scan_global_ns() - t_start > limit_ns;
+        };
+
+        if (k == 0) {
+            if (j == 0) {
+                if (seeded) {
+                    pre.v = fold_seed<Fn>(p);
+                    pre.have = 1;
+                }
+            } else {
+                if (lane == 0) status.publish(t, (epoch << 2) | ST_AGG, agg);
+                if (last_of_block) publish_block(ST_AGG, agg); /* a block of one tile */
+                const unsigned char *mine = bases[g] + boff;
+                long long look = j - 1; /* lane l examines block look - l */
+                bool done = false;
+                while (!done) {
+                    const long long idx = look - lane;
+                    T v;
+                    unsigned flag = 0;
+                    bool ready = idx < 0;
+                    while (true) {
+                        if (!ready) {
+                            flag = BlockStatus<T>::peek(mine, idx, v);
+                            ready = (flag >> 2) == pe && (flag & 3u) != 0;
+                        }
+                        if (__all_sync(FULL, ready)) break;
+                        __nanosleep(100);
+                        if (expired()) {
+                            if (lane == 0) atomicExch(err, 1u);
+                            if (!ready) flag = (pe << 2) | ST_PREFIX; /* the result is flagged invalid */
+                            ready = true;
+                        }
+                    }
+                    const bool is_pre = idx >= 0 && (flag & 3u) == ST_PREFIX;
+                    const unsigned pm = __ballot_sync(FULL, is_pre);
+                    const O win = scan_window<Fn>(v, idx >= 0, pm ? __ffs(pm) - 1 : 32);
+                    pre = op(win, pre);
+                    done = pm != 0 || look < 32;
+                    look -= 32;
+                }
+            }
+        } else {
+            if (lane == 0) status.publish(t, (epoch << 2) | ST_AGG, agg);
+            bool strict = !last_of_block; /* the first tile's record counts only as a prefix */
+            long long look = t - 1;
+            bool done = false;
+            while (!done) {
+                const long long idx = look - lane;
+                const bool inside = idx >= t0;
+                T v;
+                unsigned flag = 0;
+                bool ready = !inside;
+                while (true) {
+                    if (!ready) {
+                        flag = status.peek(idx, v);
+                        const unsigned st = (flag >> 2) == epoch ? (flag & 3u) : 0u;
+                        ready = st == ST_PREFIX || (st == ST_AGG && !(strict && idx == t0));
+                    }
+                    if (__all_sync(FULL, ready)) break;
+                    __nanosleep(ACCB_SCAN_DELAY_NS);
+                    if (expired()) {
+                        if (lane == 0) atomicExch(err, 1u);
+                        if (!ready) flag = (epoch << 2) | ST_PREFIX;
+                        ready = true;
+                    }
+                }
+                const bool is_pre = inside && (flag & 3u) == ST_PREFIX;
+                const unsigned pm = __ballot_sync(FULL, is_pre);
+                const O win = scan_window<Fn>(v, inside, pm ? __ffs(pm) - 1 : 32);
+                const bool reached = look - 31 <= t0;
+                if (pm == 0 && reached && !strict) {
+                    /* every earlier tile of the block has published its aggregate: the block's aggregate is
+                     * known before its prefix, and the blocks behind it on the other GPUs can use it at once */
+                    const O s = op(win, pre);
+                    publish_block(ST_AGG, op(s.v, agg));
+                    strict = true;
+                    continue; /* the same window again; the first tile now has to show its prefix */
+                }
+                pre = op(win, pre);
+                done = pm != 0 || reached;
+                look -= 32;
+            }
+        }
+        const T incl = pre.have ? op(pre.v, agg) : agg;
+        if (lane == 0) status.publish(t, (epoch << 2) | ST_PREFIX, incl);
+        if (last_of_block) publish_block(ST_PREFIX, incl);
+        /* the host passes a total index only to the GPU that owns the last block */
+        if (lane == 0 && t == ntiles - 1 && p.ip[3] >= 0) scan_put_sum<Fn>(p, p.ip[3], incl, oseq);
+    }
+    return pre;
+}
+
 /* warp prefix and block aggregate from the per-warp totals in shared memory
  * (all NW warps hold data) */
 template <class Fn, bool RIGHT, int NW>
@@ -396,7 +624,7 @@ __device__ __forceinline__ void smem_issue_tma(unsigned char *s, const void *con
      ...);
 }
 
-template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL, bool SMEM>
+template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL, bool SMEM, bool BC = false>
 __device__ __forceinline__ void scan_tile_full(const accb_kparams &p, long long t, long long ntiles, long long base,
                                                typename Fn::elem *s_warp, Opt<typename Fn::elem> *s_prefix,
                                                const unsigned char *s_data) {
@@ -464,7 +692,11 @@ __device__ __forceinline__ void scan_tile_full(const accb_kparams &p, long long 
     T agg;
     scan_block_level<Fn, RIGHT, NW>(s_warp, w, wpre, agg);
     if (w == 0) {
-        const O pre = scan_lookback<Fn, RIGHT>(p, t, ntiles, agg);
+        O pre;
+        if constexpr (BC)
+            pre = scan_lookback_bc<Fn>(p, t, ntiles, agg);
+        else
+            pre = scan_lookback<Fn, RIGHT>(p, t, ntiles, agg);
         if (lane == 0) *s_prefix = pre;
     }
     __syncthreads();
@@ -498,7 +730,7 @@ __device__ __forceinline__ void scan_tile_full(const accb_kparams &p, long long 
 /* ---- ragged tile (len <= TILE valid elements at `base`) or unaligned
  * arrays: scalar accesses, the tile walked twice in chunks of CTA elements
  * (once for the aggregate, once -- after the look-back -- for the values). ---- */
-template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL>
+template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL, bool BC = false>
 __device__ __forceinline__ void scan_tile_ragged(const accb_kparams &p, long long t, long long ntiles,
                                                  long long base, long long len,
                                                  Opt<typename Fn::elem> *s_opt /* CTA/32 + 1 slots */) {
@@ -544,7 +776,11 @@ __device__ __forceinline__ void scan_tile_ragged(const accb_kparams &p, long lon
         __syncthreads();
     }
     if (w == 0) {
-        const O pre = scan_lookback<Fn, RIGHT>(p, t, ntiles, carry.v); /* len >= 1, so carry.have */
+        O pre; /* len >= 1, so carry.have */
+        if constexpr (BC)
+            pre = scan_lookback_bc<Fn>(p, t, ntiles, carry.v);
+        else
+            pre = scan_lookback<Fn, RIGHT>(p, t, ntiles, carry.v);
         if (lane == 0) s_opt[NW] = pre;
     }
     __syncthreads();
@@ -579,8 +815,9 @@ __device__ __forceinline__ void scan_tile_ragged(const accb_kparams &p, long lon
     }
 }
 
-template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL, bool SMEM>
+template <class Fn, int CTA, int ROWS, bool RIGHT, bool INCL, bool SMEM, bool BC = false>
 __device__ __forceinline__ void scan_body(const accb_kparams &p) {
+    static_assert(!(BC && RIGHT), "the block-cyclic form serves left scans");
     typedef typename Fn::elem T;
     typedef typename Fn::In In;
     constexpr int NW = CTA / 32;
@@ -620,7 +857,7 @@ __device__ __forceinline__ void scan_body(const accb_kparams &p) {
     const bool full = (p.flags & ACCB_F_VEC) != 0 && len == TILE;
 
     if (!full) {
-        scan_tile_ragged<Fn, CTA, ROWS, RIGHT, INCL>(p, t, ntiles, base, len, s_opt);
+        scan_tile_ragged<Fn, CTA, ROWS, RIGHT, INCL, BC>(p, t, ntiles, base, len, s_opt);
         return;
     }
     if constexpr (SMEM) {
@@ -640,27 +877,30 @@ __device__ __forceinline__ void scan_body(const accb_kparams &p) {
             }
         }
     }
-    scan_tile_full<Fn, CTA, ROWS, RIGHT, INCL, SMEM>(p, t, ntiles, base, s_warp, &s_opt[NW], s_data);
+    scan_tile_full<Fn, CTA, ROWS, RIGHT, INCL, SMEM, BC>(p, t, ntiles, base, s_warp, &s_opt[NW], s_data);
 }
 
 }  // namespace accb
 
 /* Entry points named after the reference's kernels (PrefixSum.hs:208,313):
  * exclusive and inclusive, left and right. */
-#define ACCB_SCAN_ENTRY(Fn, name, right, incl)                                                 \
+#define ACCB_SCAN_ENTRY(Fn, name, right, incl, bc)                                             \
     extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA, ACCB_SCAN_MINB_FOR(Fn))        \
         name(const __grid_constant__ accb_kparams p) {                                         \
-        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS_FOR(Fn), right, incl, ACCB_SCAN_TMA != 0>(p); \
+        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS_FOR(Fn), right, incl, ACCB_SCAN_TMA != 0, bc>(p); \
     }
 
-/* metadata: record bytes, tile elements, rows, ticket mode, dynamic shared memory */
+/* metadata: record bytes, tile elements, rows, ticket mode, dynamic shared memory, bytes of a value */
 #define ACCB_INSTANTIATE_SCAN(Fn)                                                              \
-    ACCB_META7(5, ACCB_SCAN_CTA, accb::TileStatus<Fn::elem>::kBytes,                           \
+    ACCB_META8(5, ACCB_SCAN_CTA, accb::TileStatus<Fn::elem>::kBytes,                           \
                ACCB_SCAN_CTA * ACCB_SCAN_ROWS_FOR(Fn) * 4, ACCB_SCAN_ROWS_FOR(Fn), ACCB_SCAN_TICKET ? 2 : 0,   \
                ACCB_SCAN_TMA ? (accb::smem_offset<Fn::In, Fn::In::size,                        \
                                                   ACCB_SCAN_CTA * ACCB_SCAN_ROWS_FOR(Fn) * 4>::value)  \
-                             : 0)                                                              \
-    ACCB_SCAN_ENTRY(Fn, scanl, false, false)                                                   \
-    ACCB_SCAN_ENTRY(Fn, scanl1, false, true)                                                   \
-    ACCB_SCAN_ENTRY(Fn, scanr, true, false)                                                    \
-    ACCB_SCAN_ENTRY(Fn, scanr1, true, true)
+                             : 0,                                                              \
+               sizeof(Fn::elem))                                                               \
+    ACCB_SCAN_ENTRY(Fn, scanl, false, false, false)                                            \
+    ACCB_SCAN_ENTRY(Fn, scanl1, false, true, false)                                            \
+    ACCB_SCAN_ENTRY(Fn, scanr, true, false, false)                                             \
+    ACCB_SCAN_ENTRY(Fn, scanr1, true, true, false)                                             \
+    ACCB_SCAN_ENTRY(Fn, scanl_bc, false, false, true)                                          \
+    ACCB_SCAN_ENTRY(Fn, scanl1_bc, false, true, true)

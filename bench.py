@@ -120,6 +120,28 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def host_threads():
+    """All the host threads this process may use (torchrun sets OMP_NUM_THREADS=1, which is not a property of the
+    host), bounded by the container's CPU quota where there is one."""
+    oracle = importlib.import_module("oracle")
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    try:
+        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()
+        if quota != "max":
+            cores = min(cores, max(1, int(quota) // int(period)))
+    except (OSError, ValueError):
+        pass
+    return max(oracle.max_threads(), cores)
+
+
+def close_to(got, ref, atol, rtol=1e-5):
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    return bool(np.all(np.abs(got - ref) <= rtol * np.abs(ref) + atol))
+
+
 # -------------------------------------------------------------- workloads
 class Workload:
     name = ""
@@ -216,12 +238,24 @@ class ScanWorkload(Workload):
         return 2
 
     def verify(self):
-        """out[i+1] - out[i] == x[i] everywhere and out[0] == carry: a size-independent property."""
+        """out[i+1] - out[i] == x[i] everywhere, out[0] == the wrapped sum of the lower ranks' slabs and out[n] ==
+        out[0] + this slab's sum: with the first two, every element is pinned.  On one GPU the whole result is
+        also compared with the oracle."""
         t = self.t
         d = self.out[1:] - self.out[:-1]
         ok = bool(t.equal(d, self.x))
-        if self.world == 1:
-            ok = ok and int(self.out[0]) == 0 and int(self.out[-1]) == int(self.x.sum(dtype=t.int64) & 0xffffffff)
+        mine = self.x.sum(dtype=t.int64).reshape(1)
+        lower = 0
+        if self.world > 1:
+            totals = t.zeros(self.world, dtype=t.int64, device="cuda")
+            self.dist.all_gather_into_tensor(totals, mine)
+            lower = int(totals[: self.rank].sum())
+        wrap = lambda v: int(np.array(v & 0xffffffff, np.uint32).astype(np.int32))  # noqa: E731
+        ok = ok and int(self.out[0]) == wrap(lower) and int(self.out[-1]) == wrap(lower + int(mine[0]))
+        if self.world == 1 and self.functors == "hand":
+            oracle = importlib.import_module("oracle")
+            ref = oracle.scanl_i32(self.x.cpu().numpy(), 0, nthreads=host_threads())
+            ok = ok and bool(t.equal(self.out, t.from_numpy(ref).cuda()))
         return ok
 
     def program(self):
@@ -233,15 +267,21 @@ class ScanWorkload(Workload):
 
 class DotWorkload(Workload):
     name, dtype = "foldAll (+) 0 (zipWith (*) xs ys), Float32, 2^28", "f32"
+    sets = 1  # buffer sets the steps rotate through (inputs smaller than L2 need several)
 
     def setup(self, n=None):
         t, W = self.t, self.W
         self.n = n or W.N28
-        self.x = t.empty(self.n, dtype=t.float32, device="cuda")
-        self.y = t.empty(self.n, dtype=t.float32, device="cuda")
         first = self.rank * self.n  # each rank holds its own slab of one world*n vector
-        self.ctx.gen_uniform_f32(self.x, self.n, first, W.SEED, W.S_XS, -1.0, 1.0)
-        self.ctx.gen_uniform_f32(self.y, self.n, first, W.SEED, W.S_YS, -1.0, 1.0)
+        self.pairs = []
+        for _ in range(self.sets):  # every set holds the same values: one reference serves all of them
+            x = t.empty(self.n, dtype=t.float32, device="cuda")
+            y = t.empty(self.n, dtype=t.float32, device="cuda")
+            self.ctx.gen_uniform_f32(x, self.n, first, W.SEED, W.S_XS, -1.0, 1.0)
+            self.ctx.gen_uniform_f32(y, self.n, first, W.SEED, W.S_YS, -1.0, 1.0)
+            self.pairs.append((x, y))
+        self.turn = 0
+        self.x, self.y = self.pairs[0]
         self.out = t.zeros(1, dtype=t.float32, device="cuda")
         self.k = self.ctx.kernel(self.functor("DOT")).wait()
         self.bytes = W.bytes_dot(self.n)
@@ -252,6 +292,9 @@ class DotWorkload(Workload):
         self.ctx.sync()
 
     def step(self):
+        if self.sets > 1:
+            self.turn = (self.turn + 1) % self.sets
+            self.x, self.y = self.pairs[self.turn]
         if self.world > 1 and self.peer is not None:  # partials combined in rank order by one kernel over NVLink
             p = self.parity
             self.parity ^= 1
@@ -266,12 +309,27 @@ class DotWorkload(Workload):
 
     def verify(self):
         ref = float((self.x.double() * self.y.double()).sum())
-        ok = abs(float(self.out[0]) - ref) <= 1e-5 * abs(ref)
+        atol = 1e-9 * self.n ** 0.5  # the sum of mean-zero products may land near zero
+        ok = abs(float(self.out[0]) - ref) <= 1e-5 * abs(ref) + atol
+        if self.world == 1:
+            oracle = importlib.import_module("oracle")
+            ref2 = oracle.dot_f32(self.x.cpu().numpy(), self.y.cpu().numpy(), nthreads=host_threads())
+            ok = ok and abs(float(self.out[0]) - ref2) <= 1e-5 * abs(ref2) + atol
         if self.world > 1:
             tot = self.t.tensor([ref], dtype=self.t.float64, device="cuda")
             self.sh.dist.all_reduce(tot)
             ok = ok and abs(float(self.result[0]) - float(tot[0])) <= 1e-5 * abs(float(tot[0]))
         return ok
+
+
+class Dot24Workload(DotWorkload):
+    """Configuration 1 at its own size: 128 MiB of input per step is about the size of L2, so the steps rotate
+    through four disjoint buffer sets (512 MiB)."""
+    name, dtype = "foldAll (+) 0 (zipWith (*) xs ys), Float32, 2^24, 4 rotating buffer sets", "f32"
+    sets = 4
+
+    def setup(self, n=None):
+        super().setup(n or self.W.N24)
 
 
 class HistWorkload(Workload):
@@ -310,6 +368,10 @@ class HistWorkload(Workload):
         t = self.t
         ref = t.bincount(self.keys.long(), minlength=self.W.HIST_BINS).int()
         ok = bool(t.equal(ref, self.out)) and int(self.out.sum()) == self.n
+        if self.world == 1:
+            oracle = importlib.import_module("oracle")
+            ref2 = oracle.permute_add_i32(self.keys.cpu().numpy(), self.W.HIST_BINS, nthreads=host_threads())
+            ok = ok and bool(np.array_equal(self.out.cpu().numpy(), ref2))
         if self.world > 1:
             self.sh.dist.all_reduce(ref)
             ok = ok and bool(t.equal(ref, self.result)) and int(self.result.sum()) == self.n * self.world
@@ -367,10 +429,24 @@ class StencilWorkload(Workload):
         return self.iters + (2 + bool(self.pt) + bool(self.pb) if self.peer is not None else 0)
 
     def verify(self):
-        # blur with Clamp keeps values inside [min, max] of the source and (interior) preserves the mean
-        r, t = self.res, self.t
+        """Bands of 48 result rows at the top, the middle and the bottom of this rank's slab against the oracle's
+        ten-step recurrence (float64 state).  The oracle's input is a band of the GLOBAL (world*h) x w grid widened
+        by ten rows each way, made on the host by the numpy generator: it shares neither the device generator nor
+        the halo exchange with what it checks.  Where the widened band is cut inside the grid the oracle's Clamp
+        is wrong there, which reaches ten rows inwards: exactly the widening."""
+        r, t, W = self.res, self.t, self.W
+        oracle = importlib.import_module("oracle")
+        H, band, reach = self.h * self.world, 48, self.iters
+        ok = True
+        for local0 in (0, self.h // 2 - band // 2, self.h - band):
+            g0 = self.rank * self.h + local0  # first global row of the band
+            lo, hi = max(0, g0 - reach), min(H, g0 + band + reach)
+            src = W.uniform_f32(W.SEED, W.S_GRID, (hi - lo) * self.w, 0.0, 1.0, first=lo * self.w).reshape(hi - lo, self.w)
+            ref = oracle.stencil2d_iter(src, W.BLUR_WEIGHTS, self.iters, "clamp", nthreads=host_threads())
+            ok = ok and close_to(r[local0:local0 + band].cpu().numpy(), ref[g0 - lo:g0 - lo + band], 1e-6)
+        # everywhere: blur with Clamp keeps values inside [min, max] of the source
         interior = self.src[self.pt:self.pt + self.h]
-        ok = bool(r.min() >= interior.min() - 1e-6) and bool(r.max() <= interior.max() + 1e-6)
+        ok = ok and bool(r.min() >= interior.min() - 1e-6) and bool(r.max() <= interior.max() + 1e-6)
         if self.world == 1:
             return ok and abs(float(r.mean()) - float(interior.mean())) < 1e-3
         # several GPUs: the wide-halo scheme against one exchange of a single row per application, bit for bit
@@ -393,9 +469,10 @@ class BlackScholesWorkload(Workload):
         self.n = n or W.N26
         mk = lambda: t.empty(self.n, dtype=t.float32, device="cuda")
         self.s, self.k_, self.y, self.call, self.put = mk(), mk(), mk(), mk(), mk()
-        self.ctx.gen_uniform_f32(self.s, self.n, 0, W.SEED, W.S_SPOT, 5.0, 30.0)
-        self.ctx.gen_uniform_f32(self.k_, self.n, 0, W.SEED, W.S_STRIKE, 1.0, 100.0)
-        self.ctx.gen_uniform_f32(self.y, self.n, 0, W.SEED, W.S_YEARS, 0.25, 10.0)
+        self.first = self.rank * self.n  # each rank prices its own slice of world*n options: no exchange
+        self.ctx.gen_uniform_f32(self.s, self.n, self.first, W.SEED, W.S_SPOT, 5.0, 30.0)
+        self.ctx.gen_uniform_f32(self.k_, self.n, self.first, W.SEED, W.S_STRIKE, 1.0, 100.0)
+        self.ctx.gen_uniform_f32(self.y, self.n, self.first, W.SEED, W.S_YEARS, 0.25, 10.0)
         self.k = self.ctx.kernel(self.functor("BLACKSCHOLES")).wait()
         self.bytes = W.bytes_blackscholes(self.n)
         self.ctx.sync()
@@ -405,11 +482,23 @@ class BlackScholesWorkload(Workload):
         return 1
 
     def verify(self):
-        # put-call parity: call - put = S - K exp(-rT)
-        t = self.t
+        """Every option: put-call parity, call - put = S - K exp(-rT).  Every 1024th option (2^16 of them): both
+        prices against the oracle's float64 closed form on inputs made by the numpy generator."""
+        t, W = self.t, self.W
         lhs = (self.call - self.put).double()
         rhs = self.s.double() - self.k_.double() * t.exp(-0.02 * self.y.double())
-        return bool(((lhs - rhs).abs() <= 1e-5 * rhs.abs() + 1e-4).all())
+        ok = bool(((lhs - rhs).abs() <= 1e-5 * rhs.abs() + 1e-4).all())
+        oracle = importlib.import_module("oracle")
+        stride = max(1, self.n >> 16)
+        idx = np.arange(0, self.n, stride)
+        gen = lambda stream, lo, hi: np.concatenate(  # noqa: E731
+            [W.uniform_f32(W.SEED, stream, 1, lo, hi, first=self.first + int(i)) for i in idx[:64]])
+        # the strided sample comes from the device arrays; its first 64 entries are also regenerated on the host
+        pick = t.from_numpy(idx).cuda()
+        s, k, y = (a[pick].cpu().numpy() for a in (self.s, self.k_, self.y))
+        ok = ok and np.array_equal(s[:64], gen(W.S_SPOT, 5.0, 30.0)) and np.array_equal(k[:64], gen(W.S_STRIKE, 1.0, 100.0))
+        rc, rp = oracle.blackscholes(s, k, y, nthreads=host_threads())
+        return ok and close_to(self.call[pick].cpu().numpy(), rc, 2e-5) and close_to(self.put[pick].cpu().numpy(), rp, 2e-5)
 
 
 class RowSumWorkload(Workload):
@@ -419,7 +508,9 @@ class RowSumWorkload(Workload):
         t, W = self.t, self.W
         self.rows = self.cols = n or 16384
         self.m = t.empty((self.rows, self.cols), dtype=t.float32, device="cuda")
-        self.ctx.gen_uniform_f32(self.m, self.rows * self.cols, 0, W.SEED, W.S_MATRIX, -1.0, 1.0)
+        # each rank sums its own slab of rows of a (world*rows) x cols matrix: no exchange, results stay sharded
+        self.ctx.gen_uniform_f32(self.m, self.rows * self.cols, self.rank * self.rows * self.cols, W.SEED, W.S_MATRIX,
+                                 -1.0, 1.0)
         self.out = t.zeros(self.rows, dtype=t.float32, device="cuda")
         self.k = self.ctx.kernel(self.functor("ROWSUM")).wait()
         self.bytes = W.bytes_rowsum(self.rows, self.cols)
@@ -431,7 +522,37 @@ class RowSumWorkload(Workload):
 
     def verify(self):
         ref = self.m.double().sum(dim=1)
-        return bool(((self.out.double() - ref).abs() <= 1e-5 * ref.abs() + 1e-6).all())
+        ok = bool(((self.out.double() - ref).abs() <= 1e-5 * ref.abs() + 1e-6).all())
+        # every 64th row against the oracle's float64 row sums
+        oracle = importlib.import_module("oracle")
+        rows = self.m[::64].contiguous().cpu().numpy()
+        return ok and close_to(self.out[::64].cpu().numpy(), oracle.fold_rows_f32(rows, nthreads=host_threads()), 1e-6)
+
+
+class ScanPrimeWorkload(Workload):
+    """scanl' (+) 0: the n-element body plus the total as a separate scalar (the second half of configuration 2)."""
+    name, dtype = "scanl' (+) 0, Int32, 2^28", "int32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.n = n or W.N28
+        self.x = t.empty(self.n, dtype=t.int32, device="cuda")
+        self.ctx.gen_uniform_i32(self.x, self.n, 0, W.SEED, W.S_SCAN, 16)
+        self.out = t.empty(self.n, dtype=t.int32, device="cuda")
+        self.total = t.zeros(1, dtype=t.int32, device="cuda")
+        self.k = self.ctx.kernel(self.functor("SCAN_ADD_I32")).wait()
+        self.bytes = W.bytes_scan(self.n)
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.scan(self.k, [self.x], self.n, self.out, kind=self.accb.SCAN_PRIME, seed=np.int32(0), total=self.total)
+        return 1
+
+    def verify(self):
+        t = self.t
+        oracle = importlib.import_module("oracle")
+        ref = oracle.scanl_i32(self.x.cpu().numpy(), 0, nthreads=host_threads())
+        return bool(t.equal(self.out, t.from_numpy(ref[:-1]).cuda())) and int(self.total[0]) == int(ref[-1])
 
 
 # ---- secondary shapes and types of the same skeletons (not BASELINE configurations; --workload selects them
@@ -569,9 +690,30 @@ class TransposeWorkload(Workload):
         return bool(self.t.equal(self.out, self.m.T))
 
 
-SECONDARY_KERNEL = {"scan64": "scanl", "shortrows": "fold_staged", "smvm": "foldSeg_staged", "smooth1d": "stencil_line",
+class HistEqualWorkload(HistWorkload):
+    """The adversarial histogram: every key is the same, so every update of a warp meets in one bin."""
+    name = "permute (+) histogram, 2^28 Int32 keys, all keys equal"
+
+    def setup(self, n=None):
+        super().setup(n)
+        self.keys.fill_(1234)
+        self.ctx.sync()
+
+
+class HistHotWorkload(HistWorkload):
+    """Sixteen hot bins (uniform over bins 0, 256, 512, ..): a warp's 32 updates fall on 16 addresses."""
+    name = "permute (+) histogram, 2^28 Int32 keys, 16 hot bins"
+
+    def setup(self, n=None):
+        super().setup(n)
+        self.ctx.gen_uniform_i32(self.keys, self.n, 0, self.W.SEED, self.W.S_UNIF, 16)
+        self.keys.mul_(256)
+        self.ctx.sync()
+
+
+SECONDARY_KERNEL = {"hist_equal": "permute_smem", "hist_hot16": "permute_smem", "scan64": "scanl", "shortrows": "fold_staged", "smvm": "foldSeg_staged", "smooth1d": "stencil_line",
                     "transpose": "map_transposed"}
-SECONDARY = {"scan64": Scan64Workload, "shortrows": ShortRowsWorkload, "smvm": SmvmWorkload, "smooth1d": Smooth1dWorkload,
+SECONDARY = {"hist_equal": HistEqualWorkload, "hist_hot16": HistHotWorkload, "scan64": Scan64Workload, "shortrows": ShortRowsWorkload, "smvm": SmvmWorkload, "smooth1d": Smooth1dWorkload,
              "transpose": TransposeWorkload}
 
 
@@ -593,7 +735,7 @@ def ref_algorithm(torch, wl, sm_count):
         fn = lambda: R.dot(wl.x, wl.y, 0.0, part, out2)
         check = lambda: abs(float(out2[0]) - float(wl.out[0])) <= 1e-6 * wl.n  # float32 accumulation, as the reference
         note = "foldAll relaunched on the partials until one block is left; float32 accumulator"
-    elif isinstance(wl, HistWorkload):
+    elif type(wl) is HistWorkload:  # not the adversarial variants: a lock that every key shares serialises the whole sample
         # Every update of a hot bin is serialised by its lock while hundreds of thousands of threads
         # spin on it (measured: ~0.2 ms per update of one shared bin), so a small bounded sample.
         m = min(wl.n, 1 << 16)
@@ -642,6 +784,8 @@ def ref_algorithm(torch, wl, sm_count):
 
 WORKLOADS = {"scan": ScanWorkload, "dot": DotWorkload, "hist": HistWorkload, "stencil": StencilWorkload,
              "blackscholes": BlackScholesWorkload, "rowsum": RowSumWorkload}
+# the configurations' own sizes and forms where they differ from the 2^28 headline (one GPU)
+CONFIG_EXTRAS = {"dot_n24": Dot24Workload, "scan_prime": ScanPrimeWorkload}
 
 
 def awhile_sample(accb, ctx, torch, side=128, iters=200):
@@ -709,39 +853,114 @@ def run_reference(args):
     if rank != 0:
         return
     oracle = importlib.import_module("oracle")
-    # all the host threads this process may use: torchrun sets OMP_NUM_THREADS=1, which is not a property of the host
-    try:
-        cores = len(os.sched_getaffinity(0))
-    except AttributeError:
-        cores = os.cpu_count() or 1
-    try:  # a container's CPU quota, where there is one
-        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()
-        if quota != "max":
-            cores = min(cores, max(1, int(quota) // int(period)))
-    except (OSError, ValueError):
-        pass
-    threads = max(oracle.max_threads(), cores)
-    n = 1 << 26
+    threads = host_threads()
+    # the GPU arm's size: 2^28 elements per step (1 GiB in, 1 GiB out; a step takes tens of milliseconds).  The
+    # values repeat with period 2^24 -- the time of an integer prefix sum does not depend on them -- so that
+    # generating the input does not take longer than the measurement.
+    n = 1 << 28
     W = importlib.import_module("accelerate-cuda_b200.workloads")
-    x = W.uniform_i32(W.SEED, W.S_SCAN, n, 16)
+    x = np.tile(W.uniform_i32(W.SEED, W.S_SCAN, 1 << 24, 16), n >> 24)
     for _ in range(args.warmup):
         oracle.scanl_i32(x, 0, nthreads=threads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.scanl_i32(x, 0, nthreads=threads)
+        out = oracle.scanl_i32(x, 0, nthreads=threads)
     dt = time.perf_counter() - t0
+    assert int(out[-1]) == int(x.astype(np.int64).sum() & 0xffffffff)
     gbs = W.bytes_scan(n) * args.steps / dt / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int32", "data": "synthetic",
-        "config": {"workload": ScanWorkload.name, "sample": "2^26-element slice per step"},
+        "config": {"workload": ScanWorkload.name, "threads": threads,
+                   "sample": "the full 2^28 elements per step (one GPU's share; the values repeat with period 2^24)"},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": "scanl (+) 0 over a 2^26-element Int32 slice per step, blocked two-pass OpenMP scan"},
+                         "sample": "scanl (+) 0 over 2^28 Int32 per step, blocked two-pass OpenMP scan on %d threads" % threads},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference's own CPU path (Accelerate's interpreter) cannot be built here (no GHC); this is the C oracle port",
     }
     print(json.dumps(line), flush=True)
+
+
+def measure(torch, dist, wl, steps, warmup):
+    """(ms per step as the max over ranks, launches per step, parity as the min over ranks) of a workload that has
+    been set up; every rank calls this."""
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms, launches = time_steps(torch, wl, steps, warmup)
+    if dist:
+        tm = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ms = float(tm[0])
+        dist.barrier()
+    ok = bool(wl.verify())
+    if dist:
+        okt = torch.tensor([int(ok)], device="cuda")
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        ok = bool(okt[0])
+    return ms / steps, launches // steps, ok
+
+
+def release(torch, dist, wl):
+    """Frees a workload; with several ranks its exchange buffer only after every rank is done with the others'."""
+    peer = getattr(wl, "peer", None)
+    if dist:
+        dist.barrier()
+    if peer is not None:
+        peer.status()
+        peer.destroy()
+        dist.barrier()
+    torch.cuda.empty_cache()
+
+
+def e2e_single(torch, wl, steps):
+    """The scan through run1 on pinned HOST arrays: upload, launches and download inside the timed region."""
+    prog = wl.program()
+    n = wl.n
+    hin = torch.empty(n, dtype=torch.int32).pin_memory()
+    hin.copy_(wl.x.cpu())
+    hout = torch.empty(n + 1, dtype=torch.int32).pin_memory()
+    xin, xout = hin.numpy(), hout.numpy()
+    for _ in range(2):
+        prog(xin, out=[[xout]])
+    reps = max(3, min(steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        prog(xin, out=[[xout]])
+    dt = (time.perf_counter() - t0) / reps
+    ok = bool(torch.equal(hout, wl.out.cpu()))
+    prog.destroy()
+    return {"value": wl.bytes / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4 * (n + 1),
+            "ms_per_step": dt * 1e3, "steps": reps, "parity_check": ok}
+
+
+def e2e_sharded(torch, dist, wl, world):
+    """The scan end to end on N GPUs: every rank uploads its share from pinned host memory, takes part in the
+    exchange, scans, and downloads its part of the result; wall clock between barriers, max over ranks."""
+    n = wl.n
+    hin = torch.empty(n, dtype=torch.int32).pin_memory()
+    hin.copy_(wl.x.cpu())
+    hout = torch.empty(n + 1, dtype=torch.int32).pin_memory()
+
+    def step():
+        wl.x.copy_(hin, non_blocking=True)
+        wl.step()
+        hout.copy_(wl.out, non_blocking=True)
+        torch.cuda.synchronize()
+    step()
+    reps = 3
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        step()
+    dt = torch.tensor([(time.perf_counter() - t0) / reps], device="cuda", dtype=torch.float64)
+    dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    ok = torch.tensor([int(wl.verify() and bool(torch.equal(hout, wl.out.cpu())))], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return {"value": wl.bytes * world / float(dt[0]) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n * world,
+            "d2h_bytes_per_step": 4 * (n + 1) * world, "ms_per_step": float(dt[0]) * 1e3, "steps": reps,
+            "parity_check": bool(ok[0]), "note": "upload, exchange, scan, download per rank; not pipelined"}
 
 
 # -------------------------------------------------------------------- main
@@ -750,7 +969,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="scan", choices=sorted(WORKLOADS) + sorted(SECONDARY))
+    ap.add_argument("--workload", default="scan", choices=sorted(WORKLOADS) + sorted(SECONDARY) + sorted(CONFIG_EXTRAS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--functors", default="hand", choices=["hand", "lang"],
                     help="hand-written functor snippets (programs.py) or the ones the embedded language prints (examples.py)")
@@ -779,11 +998,12 @@ def main():
     ctx = accb.Context(local)
     peak, peak_kind = measured_peak()
 
-    if args.workload in SECONDARY and world > 1:
+    everything = {**WORKLOADS, **SECONDARY, **CONFIG_EXTRAS}
+    if args.workload not in WORKLOADS and world > 1:
         raise SystemExit("the secondary workloads run on one GPU")
     Workload.functors = args.functors
     Workload.exchange = args.exchange
-    wl = {**WORKLOADS, **SECONDARY}[args.workload](accb, ctx, torch, rank, world)
+    wl = everything[args.workload](accb, ctx, torch, rank, world)
     wl.setup(args.size)
     if dist:
         dist.barrier()
@@ -811,7 +1031,8 @@ def main():
         "data": "synthetic",
         "config": {"workload": wl.name, "l2": "inputs larger than L2 (1 GiB read per step)", "parity_check": ok,
                    "elements_per_gpu": getattr(wl, "n", None), "seed": hex(wl.W.SEED), "functors": args.functors,
-                   **({"exchange": Workload.exchange} if world > 1 else {})},
+                   **({"exchange": Workload.exchange, "distribution": getattr(wl, "distribution", "contiguous slabs")}
+                      if world > 1 else {})},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
         "pct_of_spec_peak_8TBs": 100.0 * per_gpu / SPEC_PEAK_GBS,
@@ -824,34 +1045,18 @@ def main():
         kernel_name, traffic_per_unit = NCU_TRAFFIC[args.workload]
         traffic = traffic_per_unit * wl.bytes / BYTES_PER_UNIT[args.workload] / dom
     else:  # secondary workloads: no scaled ncu figure
-        kernel_name, traffic = SECONDARY_KERNEL[args.workload], None
+        kernel_name, traffic = SECONDARY_KERNEL.get(args.workload, args.workload), None
     line["roofline"] = {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                         "traffic": traffic, "peak_kind": peak_kind, "kernel": kernel_name,
                         "algorithmic_bytes_per_launch": wl.bytes / dom}
 
-    if rank == 0 and world == 1 and not args.no_extras:
+    def entry_of(w, ms1, ok1):
+        g = w.bytes / (ms1 * 1e-3) / 1e9
+        return {"GB/s": g, "frac_of_measured": g / peak, "ms": ms1, "parity_check": ok1, "workload": w.name}
+
+    if world == 1 and not args.no_extras:
         # ---- e2e: run1 on pinned host arrays (upload + launch + download inside the timed region)
-        try:
-            prog = wl.program()
-            n = wl.n
-            hin = torch.empty(n, dtype=torch.int32).pin_memory()
-            hin.copy_(wl.x.cpu())
-            hout = torch.empty(n + 1, dtype=torch.int32).pin_memory()
-            xin, xout = hin.numpy(), hout.numpy()
-            for _ in range(2):
-                prog(xin, out=[[xout]])
-            reps = max(3, min(args.steps, 5))
-            t0 = time.perf_counter()
-            for _ in range(reps):
-                prog(xin, out=[[xout]])
-            dt = (time.perf_counter() - t0) / reps
-            assert int(xout[-1]) == int(wl.out[-1])
-            line["e2e"] = {"value": wl.bytes / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n,
-                           "d2h_bytes_per_step": 4 * (n + 1), "ms_per_step": dt * 1e3, "steps": reps}
-            prog.destroy()
-            del hin, hout
-        except AttributeError:
-            line["e2e"] = None
+        line["e2e"] = e2e_single(torch, wl, args.steps) if hasattr(wl, "program") else None
         # ---- CPU baseline on a bounded sample, one core
         gbs, secs = cpu_scan_sample(1, 1 << 26, 3)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port",
@@ -868,24 +1073,21 @@ def main():
             entry["ref_algorithm"] = ra
             return entry
 
-        table = {args.workload: with_ref({"GB/s": per_gpu, "frac_of_measured": per_gpu / peak, "ms": ms_step,
-                                          "parity_check": ok}, wl)}
+        table = {args.workload: with_ref(entry_of(wl, ms_step, ok), wl)}
         line["ref_algorithm"] = table[args.workload]["ref_algorithm"]
         del wl
         torch.cuda.empty_cache()
-        for name, cls in {**WORKLOADS, **SECONDARY}.items():
+        for name, cls in everything.items():
             if name == args.workload:
                 continue
             w2 = cls(accb, ctx, torch, 0, 1)
             w2.setup(None)
-            ms2, _ = time_steps(torch, w2, 10, 3)
-            g = w2.bytes / (ms2 / 10 * 1e-3) / 1e9
-            table[name] = with_ref({"GB/s": g, "frac_of_measured": g / peak, "ms": ms2 / 10,
-                                    "parity_check": bool(w2.verify()), "workload": w2.name}, w2)
+            ms2, _, ok2 = measure(torch, None, w2, 10, 3)
+            table[name] = with_ref(entry_of(w2, ms2, ok2), w2)
             del w2
             torch.cuda.empty_cache()
-        line["skeletons"] = {k: v for k, v in table.items() if k in WORKLOADS}    # the BASELINE configurations
-        line["secondary"] = {k: v for k, v in table.items() if k in SECONDARY}    # other shapes and types
+        line["skeletons"] = {k: v for k, v in table.items() if k in WORKLOADS or k in CONFIG_EXTRAS}  # the BASELINE configurations
+        line["secondary"] = {k: v for k, v in table.items() if k in SECONDARY}                       # other shapes and types
         # ---- the same programs written in the embedded language: the kernels it prints against the hand-written ones
         if args.functors == "hand":
             Workload.functors = "lang"
@@ -893,56 +1095,56 @@ def main():
             for name, cls in WORKLOADS.items():
                 w3 = cls(accb, ctx, torch, 0, 1)
                 w3.setup(None)
-                ms3, _ = time_steps(torch, w3, 10, 3)
-                g = w3.bytes / (ms3 / 10 * 1e-3) / 1e9
+                ms3, _, ok3 = measure(torch, None, w3, 10, 3)
+                g = w3.bytes / (ms3 * 1e-3) / 1e9
                 gen[name] = {"GB/s": g, "frac_of_measured": g / peak, "vs_hand_written": g / table[name]["GB/s"],
-                             "parity_check": bool(w3.verify())}
+                             "parity_check": ok3}
                 del w3
                 torch.cuda.empty_cache()
             Workload.functors = "hand"
             line["generated_functors"] = gen
         if not os.environ.get("ACCB_BENCH_SKIP_AWHILE"):  # set for profiler runs: the loop is a graph with a WHILE node
             line["awhile"] = awhile_sample(accb, ctx, torch)
-    elif world > 1 and isinstance(wl, ScanWorkload) and not args.no_extras:
-        # ---- e2e at N GPUs: every rank uploads its slab from pinned host memory, takes part in the carry exchange,
-        # scans, and downloads its part of the result; wall clock between barriers, max over ranks
-        n = wl.n
-        hin = torch.empty(n, dtype=torch.int32).pin_memory()
-        hin.copy_(wl.x.cpu())
-        hout = torch.empty(n + 1, dtype=torch.int32).pin_memory()
-
-        def e2e_step():
-            wl.x.copy_(hin, non_blocking=True)
-            wl.step()
-            hout.copy_(wl.out, non_blocking=True)
-            torch.cuda.synchronize()
-        e2e_step()
-        reps = 3
-        dist.barrier()
-        t0 = time.perf_counter()
-        for _ in range(reps):
-            e2e_step()
-        dt = torch.tensor([(time.perf_counter() - t0) / reps], device="cuda", dtype=torch.float64)
-        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-        ok_e2e = torch.tensor([int(wl.verify() and bool(torch.equal(hout, wl.out.cpu())))], device="cuda")
-        dist.all_reduce(ok_e2e, op=dist.ReduceOp.MIN)
-        line["e2e"] = {"value": total_bytes / float(dt[0]) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * n * world,
-                       "d2h_bytes_per_step": 4 * (n + 1) * world, "ms_per_step": float(dt[0]) * 1e3, "steps": reps,
-                       "parity_check": bool(ok_e2e[0]), "note": "upload, carry exchange, scan, download per rank; not pipelined"}
+    elif world > 1 and not args.no_extras:
+        # ---- e2e of the timed workload at N GPUs
+        line["e2e"] = e2e_sharded(torch, dist, wl, world) if isinstance(wl, ScanWorkload) else None
+        # ---- every skeleton through its sharded path: aggregate GB/s, parity, and efficiency against the SAME
+        # ---- program run unsharded on every GPU at once in this run (no exchange: what N independent GPUs give)
+        table = {args.workload: entry_of(wl, ms_step, ok)}
+        release(torch, dist, wl)
+        del wl
+        torch.cuda.empty_cache()
+        for name, cls in WORKLOADS.items():
+            if name != args.workload:
+                w2 = cls(accb, ctx, torch, rank, world)
+                w2.setup(None)
+                ms2, _, ok2 = measure(torch, dist, w2, 10, 3)
+                table[name] = entry_of(w2, ms2, ok2)
+                release(torch, dist, w2)
+                del w2
+                torch.cuda.empty_cache()
+            w1 = cls(accb, ctx, torch, 0, 1)  # unsharded, on every rank at the same time
+            w1.setup(None)
+            ms1, _, ok1 = measure(torch, dist, w1, 10, 3)
+            del w1
+            torch.cuda.empty_cache()
+            e = table[name]
+            e["GB/s_per_gpu"] = e["GB/s"]
+            e["GB/s"] = e["GB/s_per_gpu"] * world
+            e["unsharded_ms"] = ms1
+            e["efficiency"] = ms1 / e["ms"]
+            e["parity_check"] = e["parity_check"] and ok1
+        line["skeletons"] = table
     elif rank == 0:
         line["e2e"] = None
     ctx.sync()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist:
-        dist.barrier()  # every rank is done with the others' exchange buffers
         try:
-            if getattr(wl, "peer", None) is not None:
-                wl.peer.status()
-                wl.peer.destroy()
+            release(torch, dist, wl)
         except NameError:
-            pass
-        dist.barrier()
+            dist.barrier()
         dist.destroy_process_group()
 
 
