@@ -174,6 +174,8 @@ def lib() -> C.CDLL:
             "accb_peer_allreduce": [vp, vp, sz, ll, i32, i32, vp],
             "accb_peer_exscan": [vp, vp, sz, ll, i32, i32, vp, vp],
             "accb_peer_pull": [vp, vp, i32, sz, sz, vp],
+            "accb_peer_scan_layout": [i32, i32, ll, ll, C.POINTER(ll), C.POINTER(i32), C.POINTER(sz)],
+            "accb_peer_scan": [vp, vp, vp, arrp, i32, ll, ll, i32, vp, sz, sz, arrp, arrp],
             "accb_peer_status": [vp, vp, C.POINTER(i32)],
             "accb_peer_destroy": [vp],
             "accb_gen_uniform_f32": [vp, vp, vp, ll, ll, u64, u64, C.c_float, C.c_float],
@@ -332,6 +334,17 @@ class Peer:
         self._check(lib().accb_peer_pull(self.handle, Context._stream(stream), from_rank, offset, nbytes,
                                          C.c_void_p(int(dst_ptr))))
 
+    def scan(self, kernel, env: Sequence, n_global: int, out, kind=SCAN_EXCLUSIVE, seed=None, total=None,
+             block_elems: int = 0, scratch_offset: int = 0, stream=None):
+        """scanl / scanl1 / scanl' over one vector dealt to the ranks in blocks (``accb_peer_scan``): ``env`` and
+        ``out`` are this rank's blocks, one after the other (``scan_layout`` gives their length)."""
+        sb, sn = _bytes_of(seed)
+        o = to_accb_array(out)
+        t = to_accb_array(total, shape=()) if total is not None else None
+        self._check(lib().accb_peer_scan(self.handle, self.ctx._k(kernel), Context._stream(stream), _arr_list(env),
+                                         len(env), n_global, block_elems, kind, sb, sn, scratch_offset, C.byref(o),
+                                         C.byref(t) if t is not None else None))
+
     def status(self, stream=None):
         """Waits for the stream; raises ETIMEOUT if a rank did not reach some exchange in time."""
         t = C.c_int()
@@ -341,6 +354,14 @@ class Peer:
         if self.handle:
             lib().accb_peer_destroy(self.handle)
             self.handle = None
+
+
+def scan_layout(world: int, rank: int, n_global: int, block_elems: int):
+    """(elements this rank holds, rank that owns the last block and with it the total, bytes of exchange-buffer
+    scratch) of a block-cyclic scan (``accb_peer_scan_layout``)."""
+    n, owner, scratch = C.c_longlong(), C.c_int(), C.c_size_t()
+    _check(lib().accb_peer_scan_layout(world, rank, n_global, block_elems, C.byref(n), C.byref(owner), C.byref(scratch)))
+    return n.value, owner.value, scratch.value
 
 
 class Kernel:

@@ -202,6 +202,18 @@ int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blo
 int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, size_t smem,
            cudaStream_t stream, const accb_kparams &p, bool prefer_smem = true);
 
+/* exchange buffers (peer.cu), as the block-cyclic scan driver sees them */
+struct PeerScanInfo {
+    accb_context *ctx = nullptr;
+    int rank = 0, world = 1;
+    void *dev_bases = nullptr;         /* device table: address of every rank's buffer */
+    size_t header_bytes = 0;           /* the data area starts this far into a buffer */
+    unsigned long long timeout_ns = 0; /* how long a rank waits for the others */
+    unsigned count = 0;                /* number of this scan on the buffer (the same on every rank) */
+};
+int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *info);
+accb_context *peer_context(accb_peer *p);
+
 /* host fault injection: ACCB_FAIL=<site>[:N] makes the N-th call at <site>
  * fail (sites: malloc, nvcc, cache_io) */
 bool inject_failure(const char *site);

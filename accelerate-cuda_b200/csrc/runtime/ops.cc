@@ -397,6 +397,39 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
 }
 
 /* ----------------------------------------------------------------- scan */
+/* Tile status records of a scan on stream s: sized for ntiles records of rec bytes, and the epoch that marks
+ * this launch's records (records of earlier launches read as "not ready", so nothing is cleared between
+ * launches). */
+static int scan_scratch(accb_context *ctx, cudaStream_t s, long long ntiles, int rec, StreamScratch **out, unsigned *epoch_out) {
+    StreamScratch *sc = scratch_for(ctx, s);
+    if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+    const size_t need = (size_t)std::max(1LL, ntiles) * rec;
+    const bool regrow = sc->status_bytes < need;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(s, &cap);
+    unsigned epoch;
+    if (cap == cudaStreamCaptureStatusActive) {
+        /* Inside a stream capture the launch will be replayed with the epoch recorded now, so every replay
+         * clears the status words it uses first (a memset node), and takes its epoch from a range of
+         * its own (2^29 ..) that launches outside captures never reach. */
+        if (regrow) return fail(ctx, ACCB_EINVAL, "scan scratch must be sized by a run before the stream capture");
+        TRY(check_cuda(ctx, cudaMemsetAsync(sc->status, 0, need, s), "cudaMemsetAsync"));
+        epoch = (1u << 29) + (sc->graph_epoch++ & ((1u << 29) - 1u));
+    } else {
+        TRY(grow(ctx, &sc->status, &sc->status_bytes, need, s, true));
+        if (!regrow && (sc->status_layout != rec || sc->epoch >= (1u << 29) - 2)) {
+            /* another record layout or an exhausted epoch counter: old words could alias new flags */
+            TRY(check_cuda(ctx, cudaMemsetAsync(sc->status, 0, sc->status_bytes, s), "cudaMemsetAsync"));
+            if (sc->epoch >= (1u << 29) - 2) sc->epoch = 0;
+        }
+        sc->status_layout = rec;
+        epoch = ++sc->epoch;
+    }
+    *out = sc;
+    *epoch_out = epoch;
+    return ACCB_OK;
+}
+
 int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv, long long n,
               int direction, int kind, const void *seed, size_t seed_bytes, const accb_array *out,
               const accb_array *total) {
@@ -448,30 +481,9 @@ int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_
     const long long ntiles = ceil_div(n, tile);
     if (ntiles > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one scan launch");
     cudaStream_t s = (cudaStream_t)stream;
-    StreamScratch *sc = scratch_for(ctx, s);
-    if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
-    const size_t need = (size_t)std::max(1LL, ntiles) * rec;
-    const bool regrow = sc->status_bytes < need;
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    cudaStreamIsCapturing(s, &cap);
-    unsigned epoch;
-    if (cap == cudaStreamCaptureStatusActive) {
-        /* Inside a stream capture the launch will be replayed with the epoch recorded now, so every replay
-         * clears the status words it uses first (a memset node), and takes its epoch from a range of
-         * its own (2^29 ..) that launches outside captures never reach. */
-        if (regrow) return fail(ctx, ACCB_EINVAL, "scan scratch must be sized by a run before the stream capture");
-        TRY(check_cuda(ctx, cudaMemsetAsync(sc->status, 0, need, s), "cudaMemsetAsync"));
-        epoch = (1u << 29) + (sc->graph_epoch++ & ((1u << 29) - 1u));
-    } else {
-        TRY(grow(ctx, &sc->status, &sc->status_bytes, need, s, true));
-        if (!regrow && (sc->status_layout != rec || sc->epoch >= (1u << 29) - 2)) {
-            /* another record layout or an exhausted epoch counter: old words could alias new flags */
-            TRY(check_cuda(ctx, cudaMemsetAsync(sc->status, 0, sc->status_bytes, s), "cudaMemsetAsync"));
-            if (sc->epoch >= (1u << 29) - 2) sc->epoch = 0;
-        }
-        sc->status_layout = rec;
-        epoch = ++sc->epoch;
-    }
+    StreamScratch *sc = nullptr;
+    unsigned epoch = 0;
+    TRY(scan_scratch(ctx, s, ntiles, rec, &sc, &epoch));
     p.ip[0] = ntiles;
     p.ip[1] = sc->scan_ticket;
     p.ip[2] = epoch;
@@ -486,6 +498,116 @@ int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_
     /* full tiles are staged in dynamic shared memory by the TMA engine */
     const size_t smem = (size_t)pr.meta.v[6];
     return launch(ctx, pr.fn, entry, grid, pr.block, smem, s, p);
+}
+
+/* ----------------------------------------- scan over several GPUs, block-cyclic */
+static int bc_layout(int world, int rank, long long n_global, long long block_elems, long long *n_local, int *total_owner) {
+    if (world < 1 || rank < 0 || rank >= world || n_global < 0 || block_elems < 1) return ACCB_EINVAL;
+    const long long full = n_global / block_elems, rem = n_global % block_elems;
+    const long long mine = full / world + (rank < full % world ? 1 : 0);
+    const long long blocks = full + (rem ? 1 : 0);
+    if (n_local) *n_local = mine * block_elems + ((rem && full % world == rank) ? rem : 0);
+    if (total_owner) *total_owner = blocks ? (int)((blocks - 1) % world) : 0;
+    return ACCB_OK;
+}
+
+int accb_peer_scan_layout(int world, int rank, long long n_global, long long block_elems, long long *n_local,
+                          int *total_owner, size_t *scratch_bytes) {
+    if (bc_layout(world, rank, n_global, block_elems, n_local, total_owner) != ACCB_OK)
+        return fail(nullptr, ACCB_EINVAL, "block-cyclic layout: rank %d of %d, %lld elements in blocks of %lld", rank, world,
+                    n_global, block_elems);
+    /* two sets of block records (launches alternate between them), 16 bytes per block */
+    if (scratch_bytes) *scratch_bytes = (size_t)(2 * std::max(1LL, ceil_div(n_global, block_elems)) * 16 + 255) / 256 * 256;
+    return ACCB_OK;
+}
+
+int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                   long long n_global, long long block_elems, int kind, const void *seed, size_t seed_bytes,
+                   size_t scratch_offset, const accb_array *out, const accb_array *total) {
+    accb_context *ctx = peer_context(peer);
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_SCAN}, "scan"));
+    if (kind != ACCB_SCAN_EXCLUSIVE && kind != ACCB_SCAN_INCLUSIVE && kind != ACCB_SCAN_PRIME)
+        return fail(ctx, ACCB_EINVAL, "the block-cyclic scan serves scanl, scanl1 and scanl' (kind %d)", kind);
+    if (kind != ACCB_SCAN_INCLUSIVE && !seed) return fail(ctx, ACCB_EINVAL, "scanl / scanl' need a seed");
+    if (kind == ACCB_SCAN_INCLUSIVE && seed) return fail(ctx, ACCB_EINVAL, "scanl1 takes no seed");
+    if (kind == ACCB_SCAN_PRIME && !total) return fail(ctx, ACCB_EINVAL, "scanl' needs a total array");
+    const char *entry = kind == ACCB_SCAN_INCLUSIVE ? "scanl1_bc" : "scanl_bc";
+    Prep pr;
+    TRY(prepare(ctx, k, entry, 0, &pr));
+    const int rec = pr.meta.v[2];
+    const long long tile = pr.meta.v[3];
+    if (rec <= 0 || tile <= 0) return fail(ctx, ACCB_EINVAL, "kernel %s carries no scan metadata", k->key.c_str());
+    if (pr.meta.v[7] < 1 || pr.meta.v[7] > 8)
+        return fail(ctx, ACCB_EINVAL, "the block-cyclic scan carries values of up to 8 bytes between GPUs (this kernel's have %d)",
+                    pr.meta.v[7]);
+    if (block_elems == 0) block_elems = 32 * tile; /* 1 MiB of 4-byte values */
+    if (n_global < 0 || block_elems < tile || block_elems % tile)
+        return fail(ctx, ACCB_EINVAL, "blocks are whole multiples of the kernel's tile of %lld elements", tile);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(s, &cap);
+    if (cap == cudaStreamCaptureStatusActive) return fail(ctx, ACCB_EINVAL, "a scan over several GPUs cannot be recorded in a stream capture");
+
+    const long long blocks = ceil_div(n_global, block_elems);
+    size_t scratch = 0;
+    TRY(accb_peer_scan_layout(1, 0, n_global, block_elems, nullptr, nullptr, &scratch));
+    PeerScanInfo info;
+    TRY(peer_scan_begin(peer, scratch_offset, scratch, &info)); /* counts the scan: every rank calls, with or without data */
+    long long n_local = 0;
+    int owner = 0;
+    bc_layout(info.world, info.rank, n_global, block_elems, &n_local, &owner);
+
+    /* With fewer than two blocks per GPU a rank could finish this scan and start the one after the next while a
+     * slower rank still reads this scan's block records (they alternate between two sets only): line the ranks
+     * up first.  With two or more blocks per GPU no rank can finish scan e+1 before every rank has begun it,
+     * i.e. has finished scan e. */
+    if (info.world > 1 && blocks < 2LL * info.world) TRY(accb_peer_barrier(peer, stream));
+
+    if (n_global == 0) { /* only the seed survives: scanl's single element and the total, on rank 0 */
+        if (info.rank != 0) return ACCB_OK;
+        return accb_scan(ctx, k, stream, env, nenv, 0, ACCB_SCAN_LEFT, kind, seed, seed_bytes, out, total);
+    }
+    if (n_local == 0) return ACCB_OK;
+
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    TRY(fill_env(ctx, p, env, nenv));
+    TRY(fill_out(ctx, p, out));
+    TRY(set_seed(ctx, p, seed, seed_bytes));
+    p.n = n_local;
+    p.ip[3] = -1;
+    p.ip[4] = -1;
+    if (info.rank == owner) {
+        if (kind == ACCB_SCAN_PRIME) {
+            TRY(fill_out(ctx, p, total, out->ncomp));
+            p.ip[3] = 0;
+        } else if (kind == ACCB_SCAN_EXCLUSIVE) { /* the total follows this rank's last element */
+            TRY(fill_out(ctx, p, out, out->ncomp));
+            p.ip[3] = n_local;
+        }
+    }
+    const long long ntiles = ceil_div(n_local, tile);
+    if (ntiles > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one scan launch");
+    StreamScratch *sc = nullptr;
+    unsigned epoch = 0;
+    TRY(scan_scratch(ctx, s, ntiles, rec, &sc, &epoch));
+    p.ip[0] = ntiles;
+    p.ip[1] = sc->scan_ticket;
+    p.ip[2] = epoch;
+    p.ip[5] = block_elems / tile;
+    p.ip[6] = info.world;
+    p.ip[7] = info.rank;
+    p.ip[8] = info.count & 0x3fffffffu;
+    p.ip[9] = (long long)info.timeout_ns;
+    p.ip[10] = (long long)(info.header_bytes + scratch_offset + (info.count & 1u) * (scratch / 2));
+    p.aux[0] = sc->status;
+    p.aux[1] = sc->words + 1;
+    p.aux[2] = sc->words + 2;
+    p.aux[3] = info.dev_bases;
+    const int grid = (int)ntiles;
+    if (pr.meta.v[5] == 2) sc->scan_ticket += (unsigned)grid;
+    return launch(ctx, pr.fn, entry, grid, pr.block, (size_t)pr.meta.v[6], s, p);
 }
 
 /* -------------------------------------------------------------- permute */

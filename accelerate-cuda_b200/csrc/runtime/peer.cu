@@ -179,7 +179,13 @@ struct accb_peer {
     PeerPtrs pp;
     bool connected = false;
     unsigned epoch = 0;
+    unsigned char **dev_bases = nullptr; /* the buffers' addresses in device memory, for kernels that take a table */
+    unsigned scans = 0;                  /* block-cyclic scans so far: the epoch of their block records */
 };
+
+extern "C" {
+static int make_table(accb_peer *p);
+}
 
 #define PLOCKP(p)                                                   \
     if (!(p)) return fail(nullptr, ACCB_EINVAL, "null peer object"); \
@@ -202,7 +208,11 @@ int accb_peer_create(accb_context *ctx, int rank, int world, size_t bytes, accb_
     memset(&p->pp, 0, sizeof p->pp);
     /* a plain cudaMalloc block of its own: that is what an IPC handle names */
     int st = check_cuda(ctx, cudaMalloc((void **)&p->local, kHeader + p->bytes), "cudaMalloc");
-    if (st == ACCB_OK) st = check_cuda(ctx, cudaMemset(p->local, 0, kHeader), "cudaMemset");
+    /* flags, error word and data all start at zero (records that kernels validate by an epoch must not hold
+     * leftovers of whoever owned the memory before), and the clearing is finished before any rank can learn
+     * this buffer's handle and write into it */
+    if (st == ACCB_OK) st = check_cuda(ctx, cudaMemset(p->local, 0, kHeader + p->bytes), "cudaMemset");
+    if (st == ACCB_OK) st = check_cuda(ctx, cudaDeviceSynchronize(), "cudaDeviceSynchronize");
     if (st != ACCB_OK) {
         if (p->local) cudaFree(p->local);
         delete p;
@@ -239,7 +249,7 @@ int accb_peer_connect(accb_peer *p, const unsigned char *handles) {
         p->pp.base[r] = static_cast<unsigned char *>(q);
     }
     p->connected = true;
-    return ACCB_OK;
+    return make_table(p);
 }
 
 /* Every other rank is stood in for by this rank's own buffer: nobody ever sets their flags, so the next
@@ -249,7 +259,7 @@ int accb_peer_loopback(accb_peer *p) {
     for (int r = 0; r < p->world; ++r)
         if (!p->pp.base[r]) p->pp.base[r] = p->local;
     p->connected = true;
-    return ACCB_OK;
+    return make_table(p);
 }
 
 int accb_peer_data(accb_peer *p, void **data, size_t *bytes) {
@@ -270,6 +280,16 @@ int accb_peer_status(accb_peer *p, accb_stream stream, int *timed_out) {
     if (w) cudaMemset(p->local + kErrorWord * 4, 0, 4);
     if (timed_out) *timed_out = w != 0;
     return w ? fail(p->ctx, ACCB_ETIMEOUT, "a rank did not reach an exchange in time") : ACCB_OK;
+}
+
+/* the table of buffer addresses that kernels index by rank, built once all buffers are mapped */
+static int make_table(accb_peer *p) {
+    if (p->dev_bases) return ACCB_OK;
+    int st = check_cuda(p->ctx, cudaMalloc((void **)&p->dev_bases, sizeof(unsigned char *) * kMaxWorld), "cudaMalloc");
+    if (st == ACCB_OK)
+        st = check_cuda(p->ctx, cudaMemcpy(p->dev_bases, p->pp.base, sizeof(unsigned char *) * kMaxWorld, cudaMemcpyHostToDevice),
+                        "cudaMemcpy");
+    return st;
 }
 
 static int ready(accb_peer *p, size_t offset, size_t bytes) {
@@ -365,6 +385,33 @@ int accb_peer_pull(accb_peer *p, accb_stream stream, int from_rank, size_t offse
     return check_cuda(p->ctx, cudaGetLastError(), "peer pull");
 }
 
+}  // extern "C"
+
+namespace accb_rt {
+/* what the block-cyclic scan driver (ops.cc) needs to know about an exchange buffer; counts the scan */
+int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *info) {
+    if (!p || !info) return fail(nullptr, ACCB_EINVAL, "null peer object");
+    int st = ready(p, offset, bytes);
+    if (st != ACCB_OK) return st;
+    if (p->world > 1 && !p->dev_bases) return fail(p->ctx, ACCB_EINVAL, "peer buffers are not connected yet");
+    if (!p->dev_bases) {
+        st = make_table(p);
+        if (st != ACCB_OK) return st;
+    }
+    info->ctx = p->ctx;
+    info->rank = p->rank;
+    info->world = p->world;
+    info->dev_bases = p->dev_bases;
+    info->header_bytes = kHeader;
+    info->timeout_ns = p->pp.timeout_ns;
+    info->count = ++p->scans;
+    return ACCB_OK;
+}
+accb_context *peer_context(accb_peer *p) { return p ? p->ctx : nullptr; }
+}  // namespace accb_rt
+
+extern "C" {
+
 int accb_peer_destroy(accb_peer *p) {
     if (!p) return ACCB_OK;
     {
@@ -374,6 +421,7 @@ int accb_peer_destroy(accb_peer *p) {
         for (int r = 0; r < p->world; ++r)
             if (r != p->rank && p->pp.base[r] && p->pp.base[r] != p->local) cudaIpcCloseMemHandle(p->pp.base[r]);
         if (p->local) cudaFree(p->local);
+        if (p->dev_bases) cudaFree(p->dev_bases);
     }
     delete p;
     return ACCB_OK;

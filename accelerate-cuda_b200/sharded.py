@@ -10,6 +10,9 @@ collective operation shards by contiguous slabs of the outermost index space:
 * foldAll              -- one partial per rank, all-gathered and combined in rank order;
 * scan                 -- slab totals all-gathered; each rank continues from the
                           exclusive sum of the lower ranks' totals (the carry);
+                          or, without the extra pass over the data that the slab
+                          total costs, dealt to the ranks in blocks (block j on rank
+                          j mod world) and scanned by ``Peer.scan`` in one pass;
 * permute (+)          -- full-size partial destinations, one all-reduce;
 * iterated stencil     -- row slabs with halo rows towards each neighbour, refreshed
                           by neighbour send/recv into the rank's OWN halo rows (no
@@ -37,6 +40,33 @@ def slab(n: int, rank: int, world: int) -> Tuple[int, int]:
     lo = rank * q
     hi = (rank + 1) * q if rank < world - 1 else n
     return lo, hi
+
+
+def block_cyclic_counts(n: int, world: int, block: int):
+    """Elements per rank when a vector of n elements is dealt in blocks of ``block``: block j goes to rank
+    j mod world; only the last block may be short.  The same arithmetic as ``accb_peer_scan_layout``."""
+    full, rem = divmod(n, block)
+    counts = [(full // world + (1 if r < full % world else 0)) * block for r in range(world)]
+    if rem:
+        counts[full % world] += rem
+    return counts
+
+
+def block_cyclic_take(x: torch.Tensor, rank: int, world: int, block: int) -> torch.Tensor:
+    """This rank's share of the vector x, its blocks one after the other."""
+    n = x.shape[0]
+    parts = [x[lo:min(lo + block, n)] for lo in range(rank * block, n, world * block)]
+    return torch.cat(parts) if parts else x[:0]
+
+
+def block_cyclic_put(dst: torch.Tensor, local: torch.Tensor, rank: int, world: int, block: int) -> torch.Tensor:
+    """The inverse of ``block_cyclic_take``: writes this rank's blocks to their places in the whole vector."""
+    n, at = dst.shape[0], 0
+    for lo in range(rank * block, n, world * block):
+        m = min(block, n - lo)
+        dst[lo:lo + m] = local[at:at + m]
+        at += m
+    return dst
 
 
 def scan_carry(local_total: torch.Tensor, group=None) -> torch.Tensor:

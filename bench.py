@@ -194,27 +194,51 @@ class Workload:
 
 
 class ScanWorkload(Workload):
-    """scanl (+) 0 over Int32, values uniform in [0,16); 2^28 elements per GPU."""
+    """scanl (+) 0 over Int32, values uniform in [0,16); 2^28 elements per GPU.
+
+    Several GPUs scan ONE vector of world * 2^28 elements.  By default it is dealt to the GPUs in blocks of 1 MiB
+    (block j on GPU j mod world) and scanned in one pass per GPU (accb_peer_scan); ``distribution = "slabs"``
+    gives every GPU a contiguous slab instead, which costs a second read of the slab for its total."""
     name, dtype = "scanl (+) 0, Int32, 2^28 per GPU", "int32"
+    distribution = "block-cyclic"  # or "slabs"
+    block = 32 * 8192               # elements per block of the block-cyclic distribution (1 MiB)
 
     def setup(self, n=None):
         t, W = self.t, self.W
         self.n = n or W.N28
         self.x = t.empty(self.n, dtype=t.int32, device="cuda")
-        self.ctx.gen_uniform_i32(self.x, self.n, self.rank * self.n, W.SEED, W.S_SCAN, 16)
-        # rank r writes its slab of the global result; the last rank also owns out[n_total]
+        self.cyclic = self.world > 1 and self.distribution == "block-cyclic" and Workload.exchange == "peer"
+        if self.world > 1 and not self.cyclic:
+            self.distribution = "contiguous slabs"
+        # rank r writes its share of the global result; the owner of the last element also holds out[n_total]
         self.out = t.empty(self.n + 1, dtype=t.int32, device="cuda")
         self.k = self.ctx.kernel(self.functor("SCAN_ADD_I32")).wait()
         self.bytes = W.bytes_scan(self.n)
+        self.peer = None
         if self.world > 1:
             import torch.distributed as dist
             self.dist = dist
+            self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
+        if self.cyclic:
+            self.n_global = self.n * self.world
+            n_local, self.owner, scratch = self.accb.scan_layout(self.world, self.rank, self.n_global, self.block)
+            if n_local != self.n:
+                raise SystemExit("the per-GPU size must be a multiple of the block size")
+            self.peer = self.make_peer(scratch)
+            self.cyclic = self.peer is not None
+        if self.cyclic:
+            # local block b is global block b * world + rank: generated in place from the index-addressable generator
+            for b in range(self.n // self.block):
+                self.ctx.gen_uniform_i32(self.x[b * self.block:(b + 1) * self.block], self.block,
+                                         (b * self.world + self.rank) * self.block, W.SEED, W.S_SCAN, 16)
+        else:
+            self.ctx.gen_uniform_i32(self.x, self.n, self.rank * self.n, W.SEED, W.S_SCAN, 16)
+        if self.world > 1 and not self.cyclic:
+            self.distribution = "contiguous slabs"
             self.ksum = self.ctx.kernel(self.P.SUM_I32).wait()
             self.total = t.zeros(1, dtype=t.int32, device="cuda")
             self.gathered = t.zeros(self.world, dtype=t.int32, device="cuda")
             self.carry = t.zeros(1, dtype=t.int32, device="cuda")
-            self.bytes = W.bytes_scan(self.n)  # algorithmic bytes stay 8 B/element; the reduce pass is overhead
-            self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
             self.totals = self.peer_views(4, (1,), np.int32)
             self.zero = t.zeros(1, dtype=t.int32, device="cuda")  # the seed of the whole scan
         self.ctx.sync()
@@ -222,6 +246,9 @@ class ScanWorkload(Workload):
     def step(self):
         if self.world == 1:
             self.ctx.scan(self.k, [self.x], self.n, self.out, seed=np.int32(0))
+            return 1
+        if self.cyclic:  # one pass: block records travel between the GPUs inside the scan kernel itself
+            self.peer.scan(self.k, [self.x], self.n_global, self.out, seed=np.int32(0), block_elems=self.block)
             return 1
         # carry pass: slab totals -> gathered -> exclusive sum of the lower ranks -> seeded local scan
         if self.peer is not None:  # the total goes straight into the exchange buffer; one kernel syncs and gathers
@@ -238,10 +265,28 @@ class ScanWorkload(Workload):
         return 2
 
     def verify(self):
-        """out[i+1] - out[i] == x[i] everywhere, out[0] == the wrapped sum of the lower ranks' slabs and out[n] ==
-        out[0] + this slab's sum: with the first two, every element is pinned.  On one GPU the whole result is
-        also compared with the oracle."""
+        """One GPU: the whole result against the oracle.  Contiguous slabs: out[i+1] - out[i] == x[i] everywhere,
+        out[0] == the wrapped sum of the lower ranks' slabs and out[n] == out[0] + this slab's sum, which pins every
+        element.  Block-cyclic: the whole local result against torch operators -- every block's exclusive prefix from
+        the all-gathered block sums (int64, wrapped) plus the cumulative sum inside the block."""
         t = self.t
+        wrap = lambda v: int(np.array(v & 0xffffffff, np.uint32).astype(np.int32))  # noqa: E731
+        if self.world > 1 and self.cyclic:
+            nb = self.n // self.block
+            xb = self.x.view(nb, self.block)
+            sums = xb.sum(dim=1, dtype=t.int64)
+            every = t.empty(self.world * nb, dtype=t.int64, device="cuda")
+            self.dist.all_gather_into_tensor(every, sums)
+            in_order = every.view(self.world, nb).t().reshape(-1)  # global block j = b * world + rank
+            before = t.cumsum(in_order, 0) - in_order
+            mine = before.view(nb, self.world)[:, self.rank]
+            inside = t.cumsum(xb, 1, dtype=t.int64)
+            inside -= xb
+            inside += mine[:, None]
+            ok = bool(t.equal(self.out[:self.n], inside.int().view(-1)))
+            if self.rank == self.owner:
+                ok = ok and int(self.out[self.n]) == wrap(int(in_order.sum()))
+            return ok
         d = self.out[1:] - self.out[:-1]
         ok = bool(t.equal(d, self.x))
         mine = self.x.sum(dtype=t.int64).reshape(1)
@@ -250,7 +295,6 @@ class ScanWorkload(Workload):
             totals = t.zeros(self.world, dtype=t.int64, device="cuda")
             self.dist.all_gather_into_tensor(totals, mine)
             lower = int(totals[: self.rank].sum())
-        wrap = lambda v: int(np.array(v & 0xffffffff, np.uint32).astype(np.int32))  # noqa: E731
         ok = ok and int(self.out[0]) == wrap(lower) and int(self.out[-1]) == wrap(lower + int(mine[0]))
         if self.world == 1 and self.functors == "hand":
             oracle = importlib.import_module("oracle")
@@ -975,6 +1019,9 @@ def main():
                     help="hand-written functor snippets (programs.py) or the ones the embedded language prints (examples.py)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="several GPUs: the library's own exchange kernels over NVLink peer mappings, or NCCL collectives")
+    ap.add_argument("--scan-distribution", default="block-cyclic", choices=["block-cyclic", "slabs"],
+                    help="several GPUs: the vector dealt in 1 MiB blocks and scanned in one pass, or contiguous slabs "
+                         "joined by a carry (one more read of every slab)")
     ap.add_argument("--size", type=int, default=None, help="override the problem size (profiling small cases)")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-skeleton table, e2e and CPU baseline")
     args = ap.parse_args()
@@ -1003,6 +1050,7 @@ def main():
         raise SystemExit("the secondary workloads run on one GPU")
     Workload.functors = args.functors
     Workload.exchange = args.exchange
+    ScanWorkload.distribution = args.scan_distribution
     wl = everything[args.workload](accb, ctx, torch, rank, world)
     wl.setup(args.size)
     if dist:
@@ -1134,6 +1182,20 @@ def main():
             e["unsharded_ms"] = ms1
             e["efficiency"] = ms1 / e["ms"]
             e["parity_check"] = e["parity_check"] and ok1
+        # ---- the scan over contiguous slabs joined by a carry, for comparison: one more read of every slab
+        if ScanWorkload.distribution == "block-cyclic" and "scan" in table:
+            ScanWorkload.distribution = "slabs"
+            w2 = ScanWorkload(accb, ctx, torch, rank, world)
+            w2.setup(None)
+            ms2, _, ok2 = measure(torch, dist, w2, 10, 3)
+            e = entry_of(w2, ms2, ok2)
+            e.update({"GB/s_per_gpu": e["GB/s"], "GB/s": e["GB/s"] * world, "unsharded_ms": table["scan"]["unsharded_ms"],
+                      "efficiency": table["scan"]["unsharded_ms"] / ms2, "distribution": "contiguous slabs"})
+            table["scan_slabs"] = e
+            release(torch, dist, w2)
+            del w2
+            torch.cuda.empty_cache()
+            ScanWorkload.distribution = "block-cyclic"
         line["skeletons"] = table
     elif rank == 0:
         line["e2e"] = None

@@ -474,6 +474,26 @@ ACCB_API int accb_peer_exscan(accb_peer *peer, accb_stream stream, size_t offset
                               const void *first, void *dst);
 ACCB_API int accb_peer_pull(accb_peer *peer, accb_stream stream, int from_rank, size_t offset, size_t bytes,
                             void *dst);
+/* scanl / scanl1 / scanl' over ONE vector of n_global elements that is dealt to the ranks in blocks: global block j
+ * (block_elems elements, a multiple of the kernel's tile; 0 picks 32 tiles) lives on rank j mod world, and every
+ * rank stores its blocks one after the other (accb_peer_scan_layout tells how many elements that is; only the last
+ * global block may be short).  `env` and `out` are the rank's own arrays in that layout.  One launch per rank of the
+ * same single-pass kernel as accb_scan: every element is read and written once, the ranks run at the same time, and
+ * what crosses NVLink is one 16-byte record per block and rank (the block's aggregate, later its prefix), stored
+ * into every rank's exchange buffer with plain peer stores -- `scratch_offset` names scratch_bytes of the data area
+ * (16-byte aligned, the same on every rank) that this call owns.  A scan over contiguous slabs must know a slab's
+ * total before it starts and therefore reads every element twice; the reference's scan reads twice on ONE GPU
+ * (CUDA/CodeGen/PrefixSum.hs:59-120).
+ *   ACCB_SCAN_EXCLUSIVE  out has n_local elements; the rank that owns the last block (total_owner) has one more:
+ *                        the total, right after its last element.  With n_global == 0 rank 0 writes the seed.
+ *   ACCB_SCAN_INCLUSIVE  scanl1, no seed.      ACCB_SCAN_PRIME  `total` is written on total_owner only.
+ * Values of up to 8 bytes (one component).  Every rank must call, in the same order, also one that holds no element.
+ * Waits on other ranks give up after the buffer's time limit; accb_context_sync then returns ACCB_ETIMEOUT. */
+ACCB_API int accb_peer_scan_layout(int world, int rank, long long n_global, long long block_elems, long long *n_local,
+                                   int *total_owner, size_t *scratch_bytes);
+ACCB_API int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                            long long n_global, long long block_elems, int kind, const void *seed, size_t seed_bytes,
+                            size_t scratch_offset, const accb_array *out, const accb_array *total);
 ACCB_API int accb_peer_status(accb_peer *peer, accb_stream stream, int *timed_out);
 ACCB_API int accb_peer_destroy(accb_peer *peer); /* after every rank has finished using the buffers */
 

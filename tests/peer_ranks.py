@@ -62,11 +62,39 @@ def main():
     blocks = [torch.empty_like(big) for _ in range(world)]
     dist.all_gather(blocks, big)
     ok = ok and bool(torch.equal(mine, blocks[(rank - 1) % world]))
+    # the scan over a vector dealt to the ranks in blocks, against a cumulative sum of the whole vector
+    P = importlib.import_module("accelerate-cuda_b200.programs")
+    tile = 8192
+    cases = ((world * 64 * tile + 12345, 4), (world * 8 * tile, 2), (3 * tile + 5, 1), (5, 1), (world * 300 * tile, 32))
+    scratch_max = max(accb.scan_layout(world, rank, n_g, tpb * tile)[2] for n_g, tpb in cases)
+    peer2 = sh.peer_buffer(ctx, scratch_max)
+    for n_g, tpb in cases:
+        block = tpb * tile
+        n_local, owner, _ = accb.scan_layout(world, rank, n_g, block)
+        same = torch.Generator(device="cuda").manual_seed(4321)  # every rank draws the same whole vector
+        whole = torch.randint(-9, 10, (n_g,), generator=same, device="cuda", dtype=torch.int32)
+        mine = sh.block_cyclic_take(whole, rank, world, block).contiguous()
+        ok = ok and mine.numel() == n_local == sh.block_cyclic_counts(n_g, world, block)[rank]
+        ref = torch.cat([torch.zeros(1, dtype=torch.int64, device="cuda"), torch.cumsum(whole, 0, dtype=torch.int64)]) + 3
+        ref = ref.int()  # wraps as the kernel's addition does
+        for rep in range(3):
+            out = torch.full((n_local + 1,), -77, dtype=torch.int32, device="cuda")
+            peer2.scan(P.SCAN_ADD_I32, [mine], n_g, out, seed=np.int32(3), block_elems=block)
+            ctx.sync()
+            ok = ok and bool(torch.equal(out[:n_local], sh.block_cyclic_take(ref[:n_g], rank, world, block)))
+            ok = ok and int(out[n_local]) == (int(ref[n_g]) if rank == owner else -77)
+            out.fill_(-77)
+            peer2.scan(P.SCAN_ADD_I32, [mine], n_g, out[:n_local], kind=accb.SCAN_INCLUSIVE, block_elems=block)
+            ctx.sync()
+            ok = ok and bool(torch.equal(out[:n_local], sh.block_cyclic_take(ref[1:] - 3, rank, world, block)))
+            ok = ok and int(out[n_local]) == -77
+    peer2.status()
     peer.status()
     flag = torch.tensor([int(ok)], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.barrier()
     peer.destroy()
+    peer2.destroy()
     dist.barrier()
     if int(flag[0]) == 1:
         print(f"PEER-OK rank {rank} of {world}", flush=True)

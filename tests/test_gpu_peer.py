@@ -32,6 +32,71 @@ def test_peer_single_rank_forms(accb, ctx, torch_cuda, rng):
     peer.destroy()
 
 
+TILE = 8192  # elements of a scan tile for 4-byte values (4096 for 8-byte values)
+
+
+@pytest.mark.parametrize("n,tiles_per_block", [(1, 1), (TILE, 1), (5 * TILE, 1), (5 * TILE + 17, 2), (40 * TILE, 8),
+                                               (100 * TILE + 4099, 32), (3 * TILE - 1, 4), (777, 2)])
+@pytest.mark.parametrize("kind", ["scanl", "scanl1", "scanl'"])
+def test_block_chained_scan_on_one_gpu(accb, ctx, P, oracle, torch_cuda, rng, n, tiles_per_block, kind):
+    """The scan over several GPUs with a world of one: every block record is written and read by the same GPU in
+    ONE launch (nothing waits for another launch), which exercises the chain of blocks -- aggregates published by
+    a block's last tile, prefixes taken up by the next block's first tile -- without a second GPU."""
+    t = torch_cuda
+    block = tiles_per_block * TILE
+    n_local, owner, scratch = accb.scan_layout(1, 0, n, block)
+    assert (n_local, owner) == (n, 0)
+    peer = accb.Peer(ctx, 0, 1, scratch + 256, lambda b: [b])
+    x = rng.integers(-9, 10, n).astype(np.int32)
+    xd = t.from_numpy(x).cuda()
+    for _ in range(3):  # launches alternate between the two sets of block records
+        out = t.full((n + 1,), -77, dtype=t.int32, device="cuda")
+        if kind == "scanl":
+            peer.scan(P.SCAN_ADD_I32, [xd], n, out, seed=np.int32(5), block_elems=block, scratch_offset=256)
+            ctx.sync()
+            assert np.array_equal(out.cpu().numpy(), oracle.scanl_i32(x, 5))
+        elif kind == "scanl1":
+            peer.scan(P.SCAN_ADD_I32, [xd], n, out[:n], kind=accb.SCAN_INCLUSIVE, block_elems=block, scratch_offset=256)
+            ctx.sync()
+            assert np.array_equal(out[:n].cpu().numpy(), oracle.scanl1_i32(x)) and int(out[n]) == -77
+        else:
+            tot = t.zeros(1, dtype=t.int32, device="cuda")
+            peer.scan(P.SCAN_ADD_I32, [xd], n, out[:n], kind=accb.SCAN_PRIME, seed=np.int32(-3), total=tot,
+                      block_elems=block, scratch_offset=256)
+            ctx.sync()
+            body, total = oracle.scanl_prime_i32(x, -3)
+            assert np.array_equal(out[:n].cpu().numpy(), body) and int(tot[0]) == total and int(out[n]) == -77
+    peer.status()
+    peer.destroy()
+
+
+def test_block_chained_scan_of_eight_byte_values_and_floats(accb, ctx, P, torch_cuda, rng):
+    t = torch_cuda
+    n = 9 * 4096 + 5  # Int64 tiles hold 4096 elements
+    n_local, owner, scratch = accb.scan_layout(1, 0, n, 2 * 4096)
+    peer = accb.Peer(ctx, 0, 1, scratch, lambda b: [b])
+    x = rng.integers(-(1 << 40), 1 << 40, n).astype(np.int64)
+    out = t.empty(n + 1, dtype=t.int64, device="cuda")
+    peer.scan(P.SCAN_ADD_I64, [t.from_numpy(x).cuda()], n, out, seed=np.int64(1), block_elems=2 * 4096)
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy(), np.concatenate([[1], 1 + np.cumsum(x)]))
+    with pytest.raises(accb.AccbError):  # blocks are whole tiles
+        peer.scan(P.SCAN_ADD_I64, [t.from_numpy(x).cuda()], n, out, seed=np.int64(1), block_elems=1000)
+    with pytest.raises(accb.AccbError):  # right scans are not dealt in blocks
+        peer.scan(P.SCAN_ADD_I64, [t.from_numpy(x).cuda()], n, out, kind=accb.SCAN_INCLUSIVE_SEEDED, seed=np.int64(1))
+    peer.destroy()
+
+
+def test_block_chained_scan_of_nothing(accb, ctx, P, torch_cuda):
+    t = torch_cuda
+    peer = accb.Peer(ctx, 0, 1, 4096, lambda b: [b])
+    out = t.full((1,), -1, dtype=t.int32, device="cuda")
+    peer.scan(P.SCAN_ADD_I32, [t.empty(1, dtype=t.int32, device="cuda")[:0]], 0, out, seed=np.int32(42))
+    ctx.sync()
+    assert int(out[0]) == 42  # scanl f z [] = [z]
+    peer.destroy()
+
+
 def test_a_rank_that_never_arrives_runs_the_wait_into_its_limit(accb, ctx, torch_cuda, monkeypatch):
     """The failure is made on the host: this process claims to be rank 0 of 2 and nobody plays rank 1, so rank 1's
     flag is never set.  The barrier kernel gives up after its limit (one second here), finishes normally, and the
@@ -46,6 +111,31 @@ def test_a_rank_that_never_arrives_runs_the_wait_into_its_limit(accb, ctx, torch
     peer.status()  # the error word was cleared
     x = t.arange(10, device="cuda")
     assert int(x.sum()) == 45  # the device still answers
+    peer.destroy()
+
+
+def test_a_scan_whose_other_rank_never_publishes_gives_up(accb, ctx, P, torch_cuda, monkeypatch):
+    """Rank 0 of a pretended world of two holds blocks 0, 2, 4, ..; block 2 needs block 1's record, which nobody
+    writes.  The failure is made on the host (no second rank exists); the kernel's waits run into the time limit,
+    the launch finishes, accb_context_sync reports ETIMEOUT and the device still answers."""
+    t = torch_cuda
+    monkeypatch.setenv("ACCB_PEER_TIMEOUT_MS", "500")
+    n_g = 6 * TILE
+    n_local, owner, scratch = accb.scan_layout(2, 0, n_g, TILE)
+    peer = accb.Peer(ctx, 0, 2, scratch, None)
+    x = t.ones(n_local, dtype=t.int32, device="cuda")
+    out = t.empty(n_local + 1, dtype=t.int32, device="cuda")
+    peer.scan(P.SCAN_ADD_I32, [x], n_g, out, seed=np.int32(0), block_elems=TILE)
+    with pytest.raises(accb.AccbError) as e:
+        ctx.sync()
+    assert e.value.status == accb.ETIMEOUT
+    assert int(out[TILE - 1]) == TILE - 1  # block 0 needed nobody and is right
+    ctx.sync()  # the error word was cleared
+    assert int(t.arange(10, device="cuda").sum()) == 45
+    try:
+        peer.status()
+    except accb.AccbError:
+        pass  # the barrier ahead of a scan with few blocks gave up as well
     peer.destroy()
 
 

@@ -166,3 +166,29 @@ def test_peer_halo_pulls_name_the_neighbours_own_rows(world, boundary):
         pt, pb = pads[r]
         want = [(r * rows - pt + i) % total for i in range(pt + rows + pb)]
         assert np.array_equal(slabs[r], grid[want])
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+@pytest.mark.parametrize("n,block", [(0, 8), (1, 8), (8, 8), (9, 8), (63, 8), (64, 8), (65, 8), (1000, 16), (12345, 32)])
+def test_block_cyclic_layout_of_the_sharded_scan(world, n, block):
+    """accb_peer_scan_layout (no device needed) against the Python helpers, and take/put as inverses: block j
+    lives on rank j mod world, only the last block may be short, and that block's owner holds the total."""
+    sys.path.insert(0, ROOT)
+    accb = importlib.import_module("accelerate-cuda_b200")
+    sh = importlib.import_module("accelerate-cuda_b200.sharded")
+    counts = sh.block_cyclic_counts(n, world, block)
+    assert sum(counts) == n
+    x = torch.arange(n, dtype=torch.int32)
+    back = torch.full((n,), -1, dtype=torch.int32)
+    nblocks = -(-n // block)
+    for r in range(world):
+        n_local, owner, scratch = accb.scan_layout(world, r, n, block)
+        mine = sh.block_cyclic_take(x, r, world, block)
+        assert n_local == counts[r] == mine.numel()
+        assert owner == ((nblocks - 1) % world if nblocks else 0)
+        assert scratch >= 2 * 16 * max(1, nblocks) and scratch % 256 == 0
+        # the rank's k-th element of local block b is element (b * world + r) * block + k of the whole vector
+        for b in range(0, mine.numel(), block):
+            assert int(mine[b]) == (b // block * world + r) * block
+        sh.block_cyclic_put(back, mine, r, world, block)
+    assert torch.equal(back, x)
