@@ -174,6 +174,7 @@ def lib() -> C.CDLL:
             "accb_peer_allreduce": [vp, vp, sz, ll, i32, i32, vp],
             "accb_peer_exscan": [vp, vp, sz, ll, i32, i32, vp, vp],
             "accb_peer_pull": [vp, vp, i32, sz, sz, vp],
+            "accb_peer_scan_tile": [vp, vp, C.POINTER(ll)],
             "accb_peer_scan_layout": [i32, i32, ll, ll, C.POINTER(ll), C.POINTER(i32), C.POINTER(sz)],
             "accb_peer_scan": [vp, vp, vp, arrp, i32, ll, ll, i32, vp, sz, sz, arrp, arrp],
             "accb_peer_status": [vp, vp, C.POINTER(i32)],
@@ -421,6 +422,12 @@ class Context:
                                          C.byref(h)), self.handle)
             k = self._kernels[spec] = Kernel(self, spec, h)
         return k
+
+    def scan_tile(self, kernel) -> int:
+        """Elements of one tile of the kernel's block-cyclic scan entries (``accb_peer_scan_tile``)."""
+        n = C.c_longlong()
+        _check(lib().accb_peer_scan_tile(self.handle, self._k(kernel), C.byref(n)), self.handle)
+        return n.value
 
     def cache_stats(self):
         a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()

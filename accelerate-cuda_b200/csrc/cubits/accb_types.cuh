@@ -139,10 +139,12 @@ __device__ __forceinline__ T imod(T a, T b) {
  * 0, 0}.  It stands in for the (entry name, occupancy, block size, shared
  * memory) record the reference keeps per kernel
  * (Data/Array/Accelerate/CUDA/AST.hs:51-59). */
-#define ACCB_META8(id, cta, rec, tile, u, extra, smem, last)                   \
+#define ACCB_META12(id, cta, rec, tile, u, extra, smem, last, m8, m9, m10, m11)     \
     extern "C" __global__ void accb_meta_query(int *out) {                     \
-        const int m[8] = {(id), (cta), (int)(rec), (int)(tile), (u), (extra), (int)(smem), (int)(last)}; \
-        for (int i = 0; i < 8; ++i) out[i] = m[i];                             \
+        const int m[12] = {(id), (cta), (int)(rec), (int)(tile), (u), (extra), (int)(smem), (int)(last), \
+                           (int)(m8), (int)(m9), (int)(m10), (int)(m11)};      \
+        for (int i = 0; i < 12; ++i) out[i] = m[i];                            \
     }
+#define ACCB_META8(id, cta, rec, tile, u, extra, smem, last) ACCB_META12(id, cta, rec, tile, u, extra, smem, last, 0, 0, 0, 0)
 #define ACCB_META7(id, cta, rec, tile, u, extra, smem) ACCB_META8(id, cta, rec, tile, u, extra, smem, 0)
 #define ACCB_META(id, cta, rec, tile, u, extra) ACCB_META7(id, cta, rec, tile, u, extra, 0)

@@ -73,7 +73,7 @@ struct CompileResult {
 };
 
 struct KernelMeta {
-    int v[8] = {0};
+    int v[12] = {0}; /* what accb_meta_query of the module reports (ACCB_META12 of cubits/accb_types.cuh) */
 };
 
 struct LoadedModule {
@@ -211,7 +211,7 @@ struct PeerScanInfo {
     unsigned long long timeout_ns = 0; /* how long a rank waits for the others */
     unsigned count = 0;                /* number of this scan on the buffer (the same on every rank) */
 };
-int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *info);
+int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *info, bool count);
 accb_context *peer_context(accb_peer *p);
 
 /* host fault injection: ACCB_FAIL=<site>[:N] makes the N-th call at <site>

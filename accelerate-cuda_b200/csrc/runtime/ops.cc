@@ -516,8 +516,19 @@ int accb_peer_scan_layout(int world, int rank, long long n_global, long long blo
     if (bc_layout(world, rank, n_global, block_elems, n_local, total_owner) != ACCB_OK)
         return fail(nullptr, ACCB_EINVAL, "block-cyclic layout: rank %d of %d, %lld elements in blocks of %lld", rank, world,
                     n_global, block_elems);
-    /* two sets of block records (launches alternate between them), 16 bytes per block */
-    if (scratch_bytes) *scratch_bytes = (size_t)(2 * std::max(1LL, ceil_div(n_global, block_elems)) * 16 + 255) / 256 * 256;
+    /* two sets of block records (launches alternate between them), one 128-byte line per block
+     * (ACCB_SCAN_BLOCK_RECORD of scan.cuh) */
+    if (scratch_bytes) *scratch_bytes = (size_t)(2 * std::max(1LL, ceil_div(n_global, block_elems)) * 128);
+    return ACCB_OK;
+}
+
+int accb_peer_scan_tile(accb_context *ctx, accb_kernel *k, long long *tile_elems) {
+    LOCK(ctx);
+    TRY(check_skeleton(ctx, k, {SK_SCAN}, "scan"));
+    Prep pr;
+    TRY(prepare(ctx, k, "scanl_bc", 0, &pr));
+    if (pr.meta.v[9] <= 0) return fail(ctx, ACCB_EINVAL, "kernel %s carries no scan metadata", k->key.c_str());
+    if (tile_elems) *tile_elems = pr.meta.v[9];
     return ACCB_OK;
 }
 
@@ -536,12 +547,13 @@ int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const ac
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
     const int rec = pr.meta.v[2];
-    const long long tile = pr.meta.v[3];
-    if (rec <= 0 || tile <= 0) return fail(ctx, ACCB_EINVAL, "kernel %s carries no scan metadata", k->key.c_str());
+    const long long tile = pr.meta.v[9]; /* the block-cyclic entries have a tile shape of their own */
+    pr.block = pr.meta.v[8];
+    if (rec <= 0 || tile <= 0 || pr.block <= 0) return fail(ctx, ACCB_EINVAL, "kernel %s carries no scan metadata", k->key.c_str());
     if (pr.meta.v[7] < 1 || pr.meta.v[7] > 8)
         return fail(ctx, ACCB_EINVAL, "the block-cyclic scan carries values of up to 8 bytes between GPUs (this kernel's have %d)",
                     pr.meta.v[7]);
-    if (block_elems == 0) block_elems = 32 * tile; /* 1 MiB of 4-byte values */
+    if (block_elems == 0) block_elems = 32 * tile; /* 1.1 MiB of input */
     if (n_global < 0 || block_elems < tile || block_elems % tile)
         return fail(ctx, ACCB_EINVAL, "blocks are whole multiples of the kernel's tile of %lld elements", tile);
     cudaStream_t s = (cudaStream_t)stream;
@@ -553,10 +565,17 @@ int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const ac
     size_t scratch = 0;
     TRY(accb_peer_scan_layout(1, 0, n_global, block_elems, nullptr, nullptr, &scratch));
     PeerScanInfo info;
-    TRY(peer_scan_begin(peer, scratch_offset, scratch, &info)); /* counts the scan: every rank calls, with or without data */
+    TRY(peer_scan_begin(peer, scratch_offset, scratch, &info, false));
     long long n_local = 0;
     int owner = 0;
     bc_layout(info.world, info.rank, n_global, block_elems, &n_local, &owner);
+    /* the caller's arrays must be as long as the layout says: a result array sized for another distribution
+     * would be written out of bounds */
+    const long long need_out = n_local + ((kind == ACCB_SCAN_EXCLUSIVE && info.rank == owner) ? 1 : 0);
+    if (n_global > 0 && n_local > 0 && (!out || array_size(out) < need_out))
+        return fail(ctx, ACCB_EINVAL, "rank %d holds %lld elements of this scan: the result array needs %lld elements, it has %lld",
+                    info.rank, n_local, need_out, out ? array_size(out) : 0LL);
+    TRY(peer_scan_begin(peer, scratch_offset, scratch, &info, true)); /* counts the scan: every rank calls, with or without data */
 
     /* With fewer than two blocks per GPU a rank could finish this scan and start the one after the next while a
      * slower rank still reads this scan's block records (they alternate between two sets only): line the ranks
@@ -607,7 +626,7 @@ int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const ac
     p.aux[3] = info.dev_bases;
     const int grid = (int)ntiles;
     if (pr.meta.v[5] == 2) sc->scan_ticket += (unsigned)grid;
-    return launch(ctx, pr.fn, entry, grid, pr.block, (size_t)pr.meta.v[6], s, p);
+    return launch(ctx, pr.fn, entry, grid, pr.block, (size_t)pr.meta.v[10], s, p);
 }
 
 /* -------------------------------------------------------------- permute */

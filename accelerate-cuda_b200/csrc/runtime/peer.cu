@@ -388,8 +388,9 @@ int accb_peer_pull(accb_peer *p, accb_stream stream, int from_rank, size_t offse
 }  // extern "C"
 
 namespace accb_rt {
-/* what the block-cyclic scan driver (ops.cc) needs to know about an exchange buffer; counts the scan */
-int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *info) {
+/* what the block-cyclic scan driver (ops.cc) needs to know about an exchange buffer; `count` makes this call
+ * the next scan on the buffer */
+int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *info, bool count) {
     if (!p || !info) return fail(nullptr, ACCB_EINVAL, "null peer object");
     int st = ready(p, offset, bytes);
     if (st != ACCB_OK) return st;
@@ -404,7 +405,7 @@ int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *inf
     info->dev_bases = p->dev_bases;
     info->header_bytes = kHeader;
     info->timeout_ns = p->pp.timeout_ns;
-    info->count = ++p->scans;
+    info->count = count ? ++p->scans : p->scans;
     return ACCB_OK;
 }
 accb_context *peer_context(accb_peer *p) { return p ? p->ctx : nullptr; }

@@ -124,6 +124,20 @@
 #else
 #define ACCB_SCAN_MINB_FOR(Fn) (sizeof(Fn::elem) <= 4 ? 12 : (sizeof(Fn::elem) <= 8 ? 6 : 3))
 #endif
+/* The block-cyclic entries (several GPUs) take tiles of 36 KB from 128 threads: six of them fill an SM's shared
+ * memory (216 KB in flight instead of 192), which buys back the longer wait of a tile whose predecessors sit on
+ * another GPU.  Measured on two GPUs, 2^28 Int32 each: 0.368 ms against 0.385 ms with the 32 KB tiles. */
+#ifndef ACCB_SCAN_BC_CTA
+#define ACCB_SCAN_BC_CTA 128
+#endif
+#ifdef ACCB_SCAN_BC_ROWS
+#define ACCB_SCAN_BC_ROWS_FOR(Fn) ACCB_SCAN_BC_ROWS
+#else
+#define ACCB_SCAN_BC_ROWS_FOR(Fn) (accb::scan_bc_rows_for<Fn::In>::value)
+#endif
+#ifndef ACCB_SCAN_BC_MINB
+#define ACCB_SCAN_BC_MINB 6
+#endif
 #ifndef ACCB_SCAN_SPIN_LIMIT
 #define ACCB_SCAN_SPIN_LIMIT (1 << 20)
 #endif
@@ -355,8 +369,14 @@ __device__ __forceinline__ Opt<typename Fn::elem> scan_lookback(const accb_kpara
 
 /* ---- block records of the block-cyclic scan: one per global block, dense, read and written with system
  * scope because the writers are other GPUs.  Flag {epoch << 2 | state} and value travel in one store: a 64-bit
- * word for values up to 4 bytes, a 128-bit word for 8-byte values (16 bytes per record either way). ---- */
-constexpr int kBlockRecordBytes = 16;
+ * word for values up to 4 bytes, a 128-bit word for 8-byte values.  Records are ACCB_SCAN_BLOCK_RECORD bytes apart. ---- */
+#ifndef ACCB_SCAN_BLOCK_RECORD
+#define ACCB_SCAN_BLOCK_RECORD 128 /* bytes from one block record to the next: a line of its own (the host sizes the scratch for this) */
+#endif
+#ifndef ACCB_SCAN_BLOCK_DELAY_NS
+#define ACCB_SCAN_BLOCK_DELAY_NS 100 /* pause between two polls of a block record that is not published yet */
+#endif
+constexpr int kBlockRecordBytes = ACCB_SCAN_BLOCK_RECORD;
 
 template <class T>
 struct BlockStatus {
@@ -422,16 +442,16 @@ __device__ __forceinline__ Opt<typename Fn::elem> scan_window(typename Fn::elem 
 }
 
 /* ---- look-back of the block-cyclic scan (left scans), run by warp 0 of the block that owns LOCAL tile t.
- * Tile t is tile k = t mod TPB of local block t / TPB, i.e. of global block j = (t / TPB) * G + g.
- *   k > 0: the look-back above over the earlier tiles of the same block.  The record of the block's first tile
- *          counts only once it holds that tile's inclusive prefix (which includes everything before the block).
- *          The LAST tile of a block first accepts that record as an aggregate too: when its walk reaches the
- *          block's first tile without meeting a prefix it knows the block's aggregate, stores it into every
- *          GPU's block records, and only then insists on the prefix.
- *   k = 0: publishes its aggregate for the tiles behind it, then walks the block records of its own GPU's copy
- *          from block j - 1 downwards (aggregates until a prefix; block 0 only ever publishes a prefix, which
- *          contains the seed).
- * The last tile of a block finally stores the block's inclusive prefix into every GPU's block records. ---- */
+ * Tile t is tile k = t mod TPB of local block t / TPB, i.e. of global block j = (t / TPB) * G + g.  Its
+ * predecessors in scan order are the earlier tiles of its own block and then the blocks j - 1, j - 2, ..:
+ *   1. the look-back above over the tile records t - 1 .. t - k (this GPU's); it ends early at a tile that
+ *      already knows its inclusive prefix (which contains everything before the block);
+ *   2. otherwise it goes on over the BLOCK records j - 1, j - 2, .. of this GPU's copy: aggregates until a
+ *      prefix (block 0 only ever publishes a prefix, which contains the seed).
+ * Every tile walks both chains by itself, so nobody waits for the block's first tile: a tile is two dependent
+ * polls behind the moment its predecessors' aggregates exist, wherever in the block it sits.  The LAST tile of
+ * a block knows the block's aggregate once step 1 has reached the block's first tile and stores it into every
+ * GPU's block records before step 2; at the end it stores the block's inclusive prefix there. ---- */
 template <class Fn>
 __device__ __forceinline__ Opt<typename Fn::elem> scan_lookback_bc(const accb_kparams &p, long long t,
                                                                    long long ntiles, typename Fn::elem agg) {
@@ -470,83 +490,71 @@ __device__ __forceinline__ Opt<typename Fn::elem> scan_lookback_bc(const accb_kp
                    scan_global_ns() - t_start > limit_ns;
         };
 
-        if (k == 0) {
-            if (j == 0) {
-                if (seeded) {
-                    pre.v = fold_seed<Fn>(p);
-                    pre.have = 1;
+        bool resolved = false; /* `pre` is the exclusive prefix of the tile */
+        if (t == 0 && j == 0) { /* nothing precedes the very first tile but the seed */
+            if (seeded) {
+                pre.v = fold_seed<Fn>(p);
+                pre.have = 1;
+            }
+            resolved = true;
+        } else if (lane == 0) {
+            status.publish(t, (epoch << 2) | ST_AGG, agg);
+        }
+        /* step 1: the earlier tiles of this block */
+        long long look = t - 1; /* lane l examines tile look - l */
+        while (!resolved && look >= t0) {
+            const long long idx = look - lane;
+            const bool inside = idx >= t0;
+            T v;
+            unsigned flag = 0;
+            bool ready = !inside;
+            while (true) {
+                if (!ready) {
+                    flag = status.peek(idx, v);
+                    ready = (flag >> 2) == epoch && (flag & 3u) != 0;
                 }
-            } else {
-                if (lane == 0) status.publish(t, (epoch << 2) | ST_AGG, agg);
-                if (last_of_block) publish_block(ST_AGG, agg); /* a block of one tile */
-                const unsigned char *mine = bases[g] + boff;
-                long long look = j - 1; /* lane l examines block look - l */
-                bool done = false;
-                while (!done) {
-                    const long long idx = look - lane;
-                    T v;
-                    unsigned flag = 0;
-                    bool ready = idx < 0;
-                    while (true) {
-                        if (!ready) {
-                            flag = BlockStatus<T>::peek(mine, idx, v);
-                            ready = (flag >> 2) == pe && (flag & 3u) != 0;
-                        }
-                        if (__all_sync(FULL, ready)) break;
-                        __nanosleep(100);
-                        if (expired()) {
-                            if (lane == 0) atomicExch(err, 1u);
-                            if (!ready) flag = (pe << 2) | ST_PREFIX; /* the result is flagged invalid */
-                            ready = true;
-                        }
-                    }
-                    const bool is_pre = idx >= 0 && (flag & 3u) == ST_PREFIX;
-                    const unsigned pm = __ballot_sync(FULL, is_pre);
-                    const O win = scan_window<Fn>(v, idx >= 0, pm ? __ffs(pm) - 1 : 32);
-                    pre = op(win, pre);
-                    done = pm != 0 || look < 32;
-                    look -= 32;
+                if (__all_sync(FULL, ready)) break;
+                __nanosleep(ACCB_SCAN_DELAY_NS);
+                if (expired()) {
+                    if (lane == 0) atomicExch(err, 1u);
+                    if (!ready) flag = (epoch << 2) | ST_PREFIX; /* the result is flagged invalid */
+                    ready = true;
                 }
             }
-        } else {
-            if (lane == 0) status.publish(t, (epoch << 2) | ST_AGG, agg);
-            bool strict = !last_of_block; /* the first tile's record counts only as a prefix */
-            long long look = t - 1;
-            bool done = false;
-            while (!done) {
+            const unsigned pm = __ballot_sync(FULL, inside && (flag & 3u) == ST_PREFIX);
+            pre = op(scan_window<Fn>(v, inside, pm ? __ffs(pm) - 1 : 32), pre);
+            resolved = pm != 0;
+            look -= 32;
+        }
+        if (!resolved) {
+            /* `pre` is what the block holds ahead of this tile.  The last tile now knows the block's aggregate,
+             * ahead of its prefix: the blocks behind it, on the other GPUs, can use it at once. */
+            if (last_of_block) publish_block(ST_AGG, pre.have ? op(pre.v, agg) : agg);
+            /* step 2: the blocks before this one (j > 0: block 0 starts with the very first tile, whose record is
+             * a prefix from the start, so step 1 cannot end here for it unless a wait gave up) */
+            const unsigned char *mine = bases[g] + boff;
+            look = j - 1; /* lane l examines block look - l */
+            while (!resolved && look >= 0) {
                 const long long idx = look - lane;
-                const bool inside = idx >= t0;
                 T v;
                 unsigned flag = 0;
-                bool ready = !inside;
+                bool ready = idx < 0;
                 while (true) {
                     if (!ready) {
-                        flag = status.peek(idx, v);
-                        const unsigned st = (flag >> 2) == epoch ? (flag & 3u) : 0u;
-                        ready = st == ST_PREFIX || (st == ST_AGG && !(strict && idx == t0));
+                        flag = BlockStatus<T>::peek(mine, idx, v);
+                        ready = (flag >> 2) == pe && (flag & 3u) != 0;
                     }
                     if (__all_sync(FULL, ready)) break;
-                    __nanosleep(ACCB_SCAN_DELAY_NS);
+                    __nanosleep(ACCB_SCAN_BLOCK_DELAY_NS);
                     if (expired()) {
                         if (lane == 0) atomicExch(err, 1u);
-                        if (!ready) flag = (epoch << 2) | ST_PREFIX;
+                        if (!ready) flag = (pe << 2) | ST_PREFIX;
                         ready = true;
                     }
                 }
-                const bool is_pre = inside && (flag & 3u) == ST_PREFIX;
-                const unsigned pm = __ballot_sync(FULL, is_pre);
-                const O win = scan_window<Fn>(v, inside, pm ? __ffs(pm) - 1 : 32);
-                const bool reached = look - 31 <= t0;
-                if (pm == 0 && reached && !strict) {
-                    /* every earlier tile of the block has published its aggregate: the block's aggregate is
-                     * known before its prefix, and the blocks behind it on the other GPUs can use it at once */
-                    const O s = op(win, pre);
-                    publish_block(ST_AGG, op(s.v, agg));
-                    strict = true;
-                    continue; /* the same window again; the first tile now has to show its prefix */
-                }
-                pre = op(win, pre);
-                done = pm != 0 || reached;
+                const unsigned pm = __ballot_sync(FULL, idx >= 0 && (flag & 3u) == ST_PREFIX);
+                pre = op(scan_window<Fn>(v, idx >= 0, pm ? __ffs(pm) - 1 : 32), pre);
+                resolved = pm != 0;
                 look -= 32;
             }
         }
@@ -585,6 +593,13 @@ template <class L>
 struct scan_rows_for {
     static constexpr int bpe = smem_offset<L, L::size, 128>::value / 128;
     static constexpr int value = bpe <= 4 ? 8 : (bpe <= 8 ? 4 : 2);
+};
+
+/* tile rows of the block-cyclic entries, 128 threads: 36 KB of input per tile */
+template <class L>
+struct scan_bc_rows_for {
+    static constexpr int bpe = smem_offset<L, L::size, 128>::value / 128;
+    static constexpr int value = bpe <= 4 ? 18 : (bpe <= 8 ? 9 : 4);
 };
 
 /* 4 consecutive values of one component from shared memory.  8-byte values make 32 bytes per
@@ -884,23 +899,30 @@ __device__ __forceinline__ void scan_body(const accb_kparams &p) {
 
 /* Entry points named after the reference's kernels (PrefixSum.hs:208,313):
  * exclusive and inclusive, left and right. */
-#define ACCB_SCAN_ENTRY(Fn, name, right, incl, bc)                                             \
+#define ACCB_SCAN_ENTRY(Fn, name, right, incl)                                                 \
     extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA, ACCB_SCAN_MINB_FOR(Fn))        \
         name(const __grid_constant__ accb_kparams p) {                                         \
-        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS_FOR(Fn), right, incl, ACCB_SCAN_TMA != 0, bc>(p); \
+        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS_FOR(Fn), right, incl, ACCB_SCAN_TMA != 0, false>(p); \
+    }
+#define ACCB_SCAN_BC_ENTRY(Fn, name, incl)                                                     \
+    extern "C" __global__ void __launch_bounds__(ACCB_SCAN_BC_CTA, ACCB_SCAN_BC_MINB)          \
+        name(const __grid_constant__ accb_kparams p) {                                         \
+        accb::scan_body<Fn, ACCB_SCAN_BC_CTA, ACCB_SCAN_BC_ROWS_FOR(Fn), false, incl, true, true>(p); \
     }
 
-/* metadata: record bytes, tile elements, rows, ticket mode, dynamic shared memory, bytes of a value */
+/* metadata: record bytes, tile elements, rows, ticket mode, dynamic shared memory, bytes of a value; of the
+ * block-cyclic entries: threads, tile elements, dynamic shared memory */
 #define ACCB_INSTANTIATE_SCAN(Fn)                                                              \
-    ACCB_META8(5, ACCB_SCAN_CTA, accb::TileStatus<Fn::elem>::kBytes,                           \
+    ACCB_META12(5, ACCB_SCAN_CTA, accb::TileStatus<Fn::elem>::kBytes,                          \
                ACCB_SCAN_CTA * ACCB_SCAN_ROWS_FOR(Fn) * 4, ACCB_SCAN_ROWS_FOR(Fn), ACCB_SCAN_TICKET ? 2 : 0,   \
                ACCB_SCAN_TMA ? (accb::smem_offset<Fn::In, Fn::In::size,                        \
                                                   ACCB_SCAN_CTA * ACCB_SCAN_ROWS_FOR(Fn) * 4>::value)  \
                              : 0,                                                              \
-               sizeof(Fn::elem))                                                               \
-    ACCB_SCAN_ENTRY(Fn, scanl, false, false, false)                                            \
-    ACCB_SCAN_ENTRY(Fn, scanl1, false, true, false)                                            \
-    ACCB_SCAN_ENTRY(Fn, scanr, true, false, false)                                             \
-    ACCB_SCAN_ENTRY(Fn, scanr1, true, true, false)                                             \
-    ACCB_SCAN_ENTRY(Fn, scanl_bc, false, false, true)                                          \
-    ACCB_SCAN_ENTRY(Fn, scanl1_bc, false, true, true)
+               sizeof(Fn::elem), ACCB_SCAN_BC_CTA, ACCB_SCAN_BC_CTA * ACCB_SCAN_BC_ROWS_FOR(Fn) * 4,  \
+               (accb::smem_offset<Fn::In, Fn::In::size, ACCB_SCAN_BC_CTA * ACCB_SCAN_BC_ROWS_FOR(Fn) * 4>::value), 0) \
+    ACCB_SCAN_ENTRY(Fn, scanl, false, false)                                                   \
+    ACCB_SCAN_ENTRY(Fn, scanl1, false, true)                                                   \
+    ACCB_SCAN_ENTRY(Fn, scanr, true, false)                                                    \
+    ACCB_SCAN_ENTRY(Fn, scanr1, true, true)                                                    \
+    ACCB_SCAN_BC_ENTRY(Fn, scanl_bc, false)                                                    \
+    ACCB_SCAN_BC_ENTRY(Fn, scanl1_bc, true)

@@ -201,7 +201,7 @@ class ScanWorkload(Workload):
     gives every GPU a contiguous slab instead, which costs a second read of the slab for its total."""
     name, dtype = "scanl (+) 0, Int32, 2^28 per GPU", "int32"
     distribution = "block-cyclic"  # or "slabs"
-    block = 32 * 8192               # elements per block of the block-cyclic distribution (1 MiB)
+    tiles_per_block = 32            # blocks of the block-cyclic distribution: 32 tiles (1.1 MiB)
 
     def setup(self, n=None):
         t, W = self.t, self.W
@@ -220,10 +220,15 @@ class ScanWorkload(Workload):
             self.dist = dist
             self.sh = importlib.import_module("accelerate-cuda_b200.sharded")
         if self.cyclic:
+            # every GPU holds the same number of whole blocks; what is left of its 2^28 elements (less than a block)
+            # stays outside the scan, and the algorithmic bytes count only what is scanned
+            self.block = self.tiles_per_block * self.ctx.scan_tile(self.k)
+            self.n = self.n // self.block * self.block
+            self.x, self.out = self.x[:self.n], self.out[:self.n + 1]
+            self.bytes = W.bytes_scan(self.n)
             self.n_global = self.n * self.world
             n_local, self.owner, scratch = self.accb.scan_layout(self.world, self.rank, self.n_global, self.block)
-            if n_local != self.n:
-                raise SystemExit("the per-GPU size must be a multiple of the block size")
+            assert n_local == self.n
             self.peer = self.make_peer(scratch)
             self.cyclic = self.peer is not None
         if self.cyclic:

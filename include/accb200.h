@@ -475,11 +475,11 @@ ACCB_API int accb_peer_exscan(accb_peer *peer, accb_stream stream, size_t offset
 ACCB_API int accb_peer_pull(accb_peer *peer, accb_stream stream, int from_rank, size_t offset, size_t bytes,
                             void *dst);
 /* scanl / scanl1 / scanl' over ONE vector of n_global elements that is dealt to the ranks in blocks: global block j
- * (block_elems elements, a multiple of the kernel's tile; 0 picks 32 tiles) lives on rank j mod world, and every
+ * (block_elems elements, a multiple of the kernel's tile, see accb_peer_scan_tile; 0 picks 32 tiles) lives on rank j mod world, and every
  * rank stores its blocks one after the other (accb_peer_scan_layout tells how many elements that is; only the last
  * global block may be short).  `env` and `out` are the rank's own arrays in that layout.  One launch per rank of the
  * same single-pass kernel as accb_scan: every element is read and written once, the ranks run at the same time, and
- * what crosses NVLink is one 16-byte record per block and rank (the block's aggregate, later its prefix), stored
+ * what crosses NVLink is one 16-byte store per block and rank (the block's aggregate, later its prefix), stored
  * into every rank's exchange buffer with plain peer stores -- `scratch_offset` names scratch_bytes of the data area
  * (16-byte aligned, the same on every rank) that this call owns.  A scan over contiguous slabs must know a slab's
  * total before it starts and therefore reads every element twice; the reference's scan reads twice on ONE GPU
@@ -489,6 +489,8 @@ ACCB_API int accb_peer_pull(accb_peer *peer, accb_stream stream, int from_rank, 
  *   ACCB_SCAN_INCLUSIVE  scanl1, no seed.      ACCB_SCAN_PRIME  `total` is written on total_owner only.
  * Values of up to 8 bytes (one component).  Every rank must call, in the same order, also one that holds no element.
  * Waits on other ranks give up after the buffer's time limit; accb_context_sync then returns ACCB_ETIMEOUT. */
+/* elements of one tile of kernel k's block-cyclic entries (blocks are whole multiples of it) */
+ACCB_API int accb_peer_scan_tile(accb_context *ctx, accb_kernel *k, long long *tile_elems);
 ACCB_API int accb_peer_scan_layout(int world, int rank, long long n_global, long long block_elems, long long *n_local,
                                    int *total_owner, size_t *scratch_bytes);
 ACCB_API int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,

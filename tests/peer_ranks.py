@@ -64,7 +64,7 @@ def main():
     ok = ok and bool(torch.equal(mine, blocks[(rank - 1) % world]))
     # the scan over a vector dealt to the ranks in blocks, against a cumulative sum of the whole vector
     P = importlib.import_module("accelerate-cuda_b200.programs")
-    tile = 8192
+    tile = ctx.scan_tile(P.SCAN_ADD_I32)
     cases = ((world * 64 * tile + 12345, 4), (world * 8 * tile, 2), (3 * tile + 5, 1), (5, 1), (world * 300 * tile, 32))
     scratch_max = max(accb.scan_layout(world, rank, n_g, tpb * tile)[2] for n_g, tpb in cases)
     peer2 = sh.peer_buffer(ctx, scratch_max)

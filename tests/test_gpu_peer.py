@@ -32,7 +32,7 @@ def test_peer_single_rank_forms(accb, ctx, torch_cuda, rng):
     peer.destroy()
 
 
-TILE = 8192  # elements of a scan tile for 4-byte values (4096 for 8-byte values)
+TILE = 9216  # elements of a tile of the block-cyclic scan for 4-byte values (4608 for 8-byte values)
 
 
 @pytest.mark.parametrize("n,tiles_per_block", [(1, 1), (TILE, 1), (5 * TILE, 1), (5 * TILE + 17, 2), (40 * TILE, 8),
@@ -43,6 +43,7 @@ def test_block_chained_scan_on_one_gpu(accb, ctx, P, oracle, torch_cuda, rng, n,
     ONE launch (nothing waits for another launch), which exercises the chain of blocks -- aggregates published by
     a block's last tile, prefixes taken up by the next block's first tile -- without a second GPU."""
     t = torch_cuda
+    assert ctx.scan_tile(P.SCAN_ADD_I32) == TILE
     block = tiles_per_block * TILE
     n_local, owner, scratch = accb.scan_layout(1, 0, n, block)
     assert (n_local, owner) == (n, 0)
@@ -72,14 +73,18 @@ def test_block_chained_scan_on_one_gpu(accb, ctx, P, oracle, torch_cuda, rng, n,
 
 def test_block_chained_scan_of_eight_byte_values_and_floats(accb, ctx, P, torch_cuda, rng):
     t = torch_cuda
-    n = 9 * 4096 + 5  # Int64 tiles hold 4096 elements
-    n_local, owner, scratch = accb.scan_layout(1, 0, n, 2 * 4096)
+    tile = ctx.scan_tile(P.SCAN_ADD_I64)  # half as many 8-byte values
+    assert tile == TILE // 2
+    n = 9 * tile + 5
+    n_local, owner, scratch = accb.scan_layout(1, 0, n, 2 * tile)
     peer = accb.Peer(ctx, 0, 1, scratch, lambda b: [b])
     x = rng.integers(-(1 << 40), 1 << 40, n).astype(np.int64)
     out = t.empty(n + 1, dtype=t.int64, device="cuda")
-    peer.scan(P.SCAN_ADD_I64, [t.from_numpy(x).cuda()], n, out, seed=np.int64(1), block_elems=2 * 4096)
+    peer.scan(P.SCAN_ADD_I64, [t.from_numpy(x).cuda()], n, out, seed=np.int64(1), block_elems=2 * tile)
     ctx.sync()
     assert np.array_equal(out.cpu().numpy(), np.concatenate([[1], 1 + np.cumsum(x)]))
+    with pytest.raises(accb.AccbError):  # a result array shorter than this rank's share of the vector
+        peer.scan(P.SCAN_ADD_I64, [t.from_numpy(x).cuda()], n, out[:n], seed=np.int64(1), block_elems=2 * tile)
     with pytest.raises(accb.AccbError):  # blocks are whole tiles
         peer.scan(P.SCAN_ADD_I64, [t.from_numpy(x).cuda()], n, out, seed=np.int64(1), block_elems=1000)
     with pytest.raises(accb.AccbError):  # right scans are not dealt in blocks
