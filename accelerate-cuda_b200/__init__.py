@@ -148,6 +148,7 @@ def lib() -> C.CDLL:
             "accb_program_run": [vp, vp, arrp, arrp],
             "accb_program_run_graph": [vp, vp, arrp, arrp],
             "accb_program_run_host": [vp, arrp, arrp],
+            "accb_program_stream_chunk": [vp, ll],
             "accb_program_destroy": [vp],
             "accb_awhile": [vp, vp, vp, arrp, i32, ll, C.POINTER(ll)],
             "accb_group_create": [C.POINTER(i32), i32, C.POINTER(vp)],
@@ -177,6 +178,7 @@ def lib() -> C.CDLL:
             "accb_peer_scan_tile": [vp, vp, C.POINTER(ll)],
             "accb_peer_scan_layout": [i32, i32, ll, ll, C.POINTER(ll), C.POINTER(i32), C.POINTER(sz)],
             "accb_peer_scan": [vp, vp, vp, arrp, i32, ll, ll, i32, vp, sz, sz, arrp, arrp],
+            "accb_peer_scan_piece": [vp, vp, vp, arrp, i32, ll, ll, i32, vp, sz, sz, arrp, arrp, ll, ll],
             "accb_peer_status": [vp, vp, C.POINTER(i32)],
             "accb_peer_destroy": [vp],
             "accb_gen_uniform_f32": [vp, vp, vp, ll, ll, u64, u64, C.c_float, C.c_float],
@@ -336,15 +338,16 @@ class Peer:
                                          C.c_void_p(int(dst_ptr))))
 
     def scan(self, kernel, env: Sequence, n_global: int, out, kind=SCAN_EXCLUSIVE, seed=None, total=None,
-             block_elems: int = 0, scratch_offset: int = 0, stream=None):
+             block_elems: int = 0, scratch_offset: int = 0, stream=None, first_block: int = 0, blocks: int = -1):
         """scanl / scanl1 / scanl' over one vector dealt to the ranks in blocks (``accb_peer_scan``): ``env`` and
-        ``out`` are this rank's blocks, one after the other (``scan_layout`` gives their length)."""
+        ``out`` are this rank's blocks, one after the other (``scan_layout`` gives their length).  ``first_block`` /
+        ``blocks`` launch only a piece of it (``accb_peer_scan_piece``): pieces follow one another on one stream."""
         sb, sn = _bytes_of(seed)
         o = to_accb_array(out)
         t = to_accb_array(total, shape=()) if total is not None else None
-        self._check(lib().accb_peer_scan(self.handle, self.ctx._k(kernel), Context._stream(stream), _arr_list(env),
-                                         len(env), n_global, block_elems, kind, sb, sn, scratch_offset, C.byref(o),
-                                         C.byref(t) if t is not None else None))
+        self._check(lib().accb_peer_scan_piece(self.handle, self.ctx._k(kernel), Context._stream(stream), _arr_list(env),
+                                               len(env), n_global, block_elems, kind, sb, sn, scratch_offset, C.byref(o),
+                                               C.byref(t) if t is not None else None, first_block, blocks))
 
     def status(self, stream=None):
         """Waits for the stream; raises ETIMEOUT if a rank did not reach some exchange in time."""
@@ -731,6 +734,12 @@ class Afun:
         _check(lib().accb_program_run_host(self.handle, ins, outs), self.ctx.handle)
         res = [r[0] if len(r) == 1 else tuple(r) for r in results]
         return res[0] if len(res) == 1 else tuple(res)
+
+    def stream_chunk(self, elements: int):
+        """Piece size, in elements, of the streamed host run (``accb_program_stream_chunk``): -1 the default,
+        0 never run in pieces."""
+        _check(lib().accb_program_stream_chunk(self.handle, elements), self.ctx.handle)
+        return self
 
     def _result_shapes(self, in_shapes):
         return [fn(in_shapes) for fn in self._shape_fns]

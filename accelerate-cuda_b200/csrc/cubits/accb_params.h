@@ -29,6 +29,7 @@
 #define ACCB_F_INCLUSIVE 4u  /* scan: inclusive result */
 #define ACCB_F_RIGHT 8u      /* scan: right-to-left */
 #define ACCB_F_SEED_PTR 16u  /* scalars[0..8) is a device pointer to the seed */
+#define ACCB_F_CARRY 32u     /* foldAll: aux[2] points to the result of the part of the array before this one */
 
 typedef struct accb_kparams {
     const void *in[ACCB_MAX_IN];
@@ -41,6 +42,8 @@ typedef struct accb_kparams {
     int out_shape[ACCB_MAX_RANK];
     unsigned int flags;
     int pad_;
+    long long base;                 /* index of this launch's first element in the whole array: what the functor
+                                       is told is base + position (a launch may cover a piece of a larger array) */
     unsigned char scalars[ACCB_SCALAR_BYTES]; /* user scalars, packed in declaration order */
 } accb_kparams;
 

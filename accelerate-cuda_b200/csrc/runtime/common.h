@@ -203,6 +203,7 @@ int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int blo
            cudaStream_t stream, const accb_kparams &p, bool prefer_smem = true);
 
 /* exchange buffers (peer.cu), as the block-cyclic scan driver sees them */
+struct PieceState;
 struct PeerScanInfo {
     accb_context *ctx = nullptr;
     int rank = 0, world = 1;
@@ -210,6 +211,14 @@ struct PeerScanInfo {
     size_t header_bytes = 0;           /* the data area starts this far into a buffer */
     unsigned long long timeout_ns = 0; /* how long a rank waits for the others */
     unsigned count = 0;                /* number of this scan on the buffer (the same on every rank) */
+    struct PieceState *piece = nullptr; /* the scan that is being launched piece by piece, if any */
+};
+/* a block-cyclic scan launched in pieces keeps its epochs from piece to piece */
+struct PieceState {
+    bool open = false;
+    unsigned count = 0, epoch = 0;
+    long long n_global = 0, block_elems = 0, next_block = 0;
+    cudaStream_t stream = nullptr;
 };
 int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *info, bool count);
 accb_context *peer_context(accb_peer *p);

@@ -197,6 +197,11 @@ int accb_launch_config(accb_context *ctx, accb_kernel *k, const char *entry, lon
 /* ------------------------------------------------------------------ map */
 int accb_map(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
              const void *scalars, size_t scalar_bytes, const accb_array *out) {
+    return accb_map_at(ctx, k, stream, env, nenv, scalars, scalar_bytes, out, 0);
+}
+
+int accb_map_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                const void *scalars, size_t scalar_bytes, const accb_array *out, long long index_base) {
     LOCK(ctx);
     TRY(check_skeleton(ctx, k, {SK_MAP}, "map"));
     if (!out) return fail(ctx, ACCB_EINVAL, "null output array");
@@ -207,6 +212,7 @@ int accb_map(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_a
     TRY(fill_out(ctx, p, out));
     TRY(fill_scalars(ctx, p, scalars, scalar_bytes));
     p.n = array_size(out);
+    p.base = index_base;
     if (p.n == 0) return ACCB_OK;
     Prep pr;
     TRY(prepare(ctx, k, "map", 0, &pr));
@@ -255,10 +261,16 @@ static int set_seed(accb_context *ctx, accb_kparams &p, const void *seed, size_t
 
 int accb_fold_all(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
                   long long n, const void *seed, size_t seed_bytes, const accb_array *out) {
+    return accb_fold_all_at(ctx, k, stream, env, nenv, n, seed, seed_bytes, out, 0, nullptr);
+}
+
+int accb_fold_all_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                     long long n, const void *seed, size_t seed_bytes, const accb_array *out, long long index_base,
+                     const void *carry) {
     LOCK(ctx);
     TRY(check_skeleton(ctx, k, {SK_FOLD_ALL}, "fold_all"));
     if (n < 0) return fail(ctx, ACCB_EINVAL, "negative size");
-    if (n == 0 && !seed) return fail(ctx, ACCB_EBOUNDS, "fold1: empty array");
+    if (n == 0 && !seed && !carry) return fail(ctx, ACCB_EBOUNDS, "fold1: empty array");
     accb_kparams p;
     memset(&p, 0, sizeof p);
     TRY(fill_env(ctx, p, env, nenv));
@@ -275,11 +287,22 @@ int accb_fold_all(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     TRY(grow(ctx, &sc->partial, &sc->partial_bytes, (size_t)grid * std::max(8, pr.meta.v[2]), s, false));
     p.aux[0] = sc->partial;
     p.aux[1] = sc->words + 0;
+    p.base = index_base;
+    if (carry) {
+        p.aux[2] = const_cast<void *>(carry);
+        p.flags |= ACCB_F_CARRY;
+    }
     return launch(ctx, pr.fn, "foldAll", grid, pr.block, 0, s, p);
 }
 
 int accb_fold_dim(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
                   long long rows, long long cols, const void *seed, size_t seed_bytes, const accb_array *out) {
+    return accb_fold_dim_at(ctx, k, stream, env, nenv, rows, cols, seed, seed_bytes, out, 0);
+}
+
+int accb_fold_dim_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                     long long rows, long long cols, const void *seed, size_t seed_bytes, const accb_array *out,
+                     long long index_base) {
     LOCK(ctx);
     TRY(check_skeleton(ctx, k, {SK_FOLD_DIM}, "fold_dim"));
     if (rows < 0 || cols < 0) return fail(ctx, ACCB_EINVAL, "negative extent");
@@ -291,6 +314,7 @@ int accb_fold_dim(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     TRY(fill_out(ctx, p, out));
     TRY(set_seed(ctx, p, seed, seed_bytes));
     p.n = rows * cols;
+    p.base = index_base;
     p.ip[0] = rows;
     p.ip[1] = cols;
     /* threads per row (the reference always uses one block per row, Launch.hs:120): a whole block
@@ -433,6 +457,12 @@ static int scan_scratch(accb_context *ctx, cudaStream_t s, long long ntiles, int
 int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv, long long n,
               int direction, int kind, const void *seed, size_t seed_bytes, const accb_array *out,
               const accb_array *total) {
+    return accb_scan_at(ctx, k, stream, env, nenv, n, direction, kind, seed, seed_bytes, out, total, 0);
+}
+
+int accb_scan_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv, long long n,
+                 int direction, int kind, const void *seed, size_t seed_bytes, const accb_array *out,
+                 const accb_array *total, long long index_base) {
     LOCK(ctx);
     TRY(check_skeleton(ctx, k, {SK_SCAN}, "scan"));
     if (n < 0) return fail(ctx, ACCB_EINVAL, "negative size");
@@ -455,6 +485,7 @@ int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_
         TRY(set_seed(ctx, p, seed, seed_bytes));
     }
     p.n = n;
+    p.base = index_base;
     p.ip[3] = -1;
     p.ip[4] = -1;
     const char *entry;
@@ -535,6 +566,14 @@ int accb_peer_scan_tile(accb_context *ctx, accb_kernel *k, long long *tile_elems
 int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
                    long long n_global, long long block_elems, int kind, const void *seed, size_t seed_bytes,
                    size_t scratch_offset, const accb_array *out, const accb_array *total) {
+    return accb_peer_scan_piece(peer, k, stream, env, nenv, n_global, block_elems, kind, seed, seed_bytes, scratch_offset, out,
+                                total, 0, -1);
+}
+
+int accb_peer_scan_piece(accb_peer *peer, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                         long long n_global, long long block_elems, int kind, const void *seed, size_t seed_bytes,
+                         size_t scratch_offset, const accb_array *out, const accb_array *total,
+                         long long first_local_block, long long local_blocks) {
     accb_context *ctx = peer_context(peer);
     LOCK(ctx);
     TRY(check_skeleton(ctx, k, {SK_SCAN}, "scan"));
@@ -543,6 +582,7 @@ int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const ac
     if (kind != ACCB_SCAN_INCLUSIVE && !seed) return fail(ctx, ACCB_EINVAL, "scanl / scanl' need a seed");
     if (kind == ACCB_SCAN_INCLUSIVE && seed) return fail(ctx, ACCB_EINVAL, "scanl1 takes no seed");
     if (kind == ACCB_SCAN_PRIME && !total) return fail(ctx, ACCB_EINVAL, "scanl' needs a total array");
+    if (first_local_block < 0) return fail(ctx, ACCB_EINVAL, "negative block number");
     const char *entry = kind == ACCB_SCAN_INCLUSIVE ? "scanl1_bc" : "scanl_bc";
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
@@ -575,19 +615,48 @@ int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const ac
     if (n_global > 0 && n_local > 0 && (!out || array_size(out) < need_out))
         return fail(ctx, ACCB_EINVAL, "rank %d holds %lld elements of this scan: the result array needs %lld elements, it has %lld",
                     info.rank, n_local, need_out, out ? array_size(out) : 0LL);
-    TRY(peer_scan_begin(peer, scratch_offset, scratch, &info, true)); /* counts the scan: every rank calls, with or without data */
-
-    /* With fewer than two blocks per GPU a rank could finish this scan and start the one after the next while a
-     * slower rank still reads this scan's block records (they alternate between two sets only): line the ranks
-     * up first.  With two or more blocks per GPU no rank can finish scan e+1 before every rank has begun it,
-     * i.e. has finished scan e. */
-    if (info.world > 1 && blocks < 2LL * info.world) TRY(accb_peer_barrier(peer, stream));
-
-    if (n_global == 0) { /* only the seed survives: scanl's single element and the total, on rank 0 */
-        if (info.rank != 0) return ACCB_OK;
-        return accb_scan(ctx, k, stream, env, nenv, 0, ACCB_SCAN_LEFT, kind, seed, seed_bytes, out, total);
+    PieceState &piece = *info.piece;
+    const bool begin = first_local_block == 0;
+    if (!begin) {
+        const bool same = piece.n_global == n_global && piece.block_elems == block_elems && piece.stream == s;
+        /* a rank that holds fewer blocks than the others is done earlier: its later pieces are empty */
+        if (same && !piece.open && first_local_block >= piece.next_block) return ACCB_OK;
+        if (!(same && piece.open && piece.next_block == first_local_block))
+            return fail(ctx, ACCB_EINVAL, "piece %lld does not continue the scan begun on this stream (next block %lld)",
+                        first_local_block, piece.open ? piece.next_block : -1LL);
     }
-    if (n_local == 0) return ACCB_OK;
+    const long long ntiles = ceil_div(n_local, tile);
+    if (ntiles > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one scan launch");
+    StreamScratch *sc = nullptr;
+    if (begin) {
+        TRY(peer_scan_begin(peer, scratch_offset, scratch, &info, true)); /* counts the scan: every rank calls, with or without data */
+        /* With fewer than two blocks per GPU a rank could finish this scan and start the one after the next while a
+         * slower rank still reads this scan's block records (they alternate between two sets only): line the ranks
+         * up first.  With two or more blocks per GPU no rank can finish scan e+1 before every rank has begun it,
+         * i.e. has finished scan e. */
+        if (info.world > 1 && blocks < 2LL * info.world) TRY(accb_peer_barrier(peer, stream));
+        if (n_global == 0) { /* only the seed survives: scanl's single element and the total, on rank 0 */
+            if (info.rank != 0) return ACCB_OK;
+            return accb_scan(ctx, k, stream, env, nenv, 0, ACCB_SCAN_LEFT, kind, seed, seed_bytes, out, total);
+        }
+        piece = PieceState();
+        piece.count = info.count;
+        piece.n_global = n_global;
+        piece.block_elems = block_elems;
+        piece.stream = s;
+        piece.open = true;
+        if (n_local > 0) TRY(scan_scratch(ctx, s, ntiles, rec, &sc, &piece.epoch));
+    } else if (n_local > 0) {
+        sc = scratch_for(ctx, s);
+        if (!sc || sc->epoch != piece.epoch)
+            return fail(ctx, ACCB_EINVAL, "another scan ran on this stream between the pieces of this one");
+    }
+    const long long tpb = block_elems / tile;
+    const long long local_all = ceil_div(n_local, block_elems);
+    const long long last_block = local_blocks < 0 ? local_all : std::min(local_all, first_local_block + local_blocks);
+    piece.next_block = last_block;
+    if (last_block >= local_all) piece.open = false;
+    if (n_local == 0 || last_block <= first_local_block) return ACCB_OK;
 
     accb_kparams p;
     memset(&p, 0, sizeof p);
@@ -606,25 +675,22 @@ int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const ac
             p.ip[3] = n_local;
         }
     }
-    const long long ntiles = ceil_div(n_local, tile);
-    if (ntiles > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one scan launch");
-    StreamScratch *sc = nullptr;
-    unsigned epoch = 0;
-    TRY(scan_scratch(ctx, s, ntiles, rec, &sc, &epoch));
+    const long long tile_first = first_local_block * tpb, tile_end = std::min(ntiles, last_block * tpb);
     p.ip[0] = ntiles;
     p.ip[1] = sc->scan_ticket;
-    p.ip[2] = epoch;
-    p.ip[5] = block_elems / tile;
+    p.ip[2] = piece.epoch;
+    p.ip[5] = tpb;
     p.ip[6] = info.world;
     p.ip[7] = info.rank;
-    p.ip[8] = info.count & 0x3fffffffu;
+    p.ip[8] = piece.count & 0x3fffffffu;
     p.ip[9] = (long long)info.timeout_ns;
-    p.ip[10] = (long long)(info.header_bytes + scratch_offset + (info.count & 1u) * (scratch / 2));
+    p.ip[10] = (long long)(info.header_bytes + scratch_offset + (piece.count & 1u) * (scratch / 2));
+    p.ip[11] = tile_first;
     p.aux[0] = sc->status;
     p.aux[1] = sc->words + 1;
     p.aux[2] = sc->words + 2;
     p.aux[3] = info.dev_bases;
-    const int grid = (int)ntiles;
+    const int grid = (int)(tile_end - tile_first);
     if (pr.meta.v[5] == 2) sc->scan_ticket += (unsigned)grid;
     return launch(ctx, pr.fn, entry, grid, pr.block, (size_t)pr.meta.v[10], s, p);
 }
@@ -648,6 +714,12 @@ int accb_permute_defaults(accb_context *ctx, accb_stream stream, const accb_arra
 
 int accb_permute(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
                  long long n_src, const void *scalars, size_t scalar_bytes, const accb_array *out) {
+    return accb_permute_at(ctx, k, stream, env, nenv, n_src, scalars, scalar_bytes, out, 0);
+}
+
+int accb_permute_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                    long long n_src, const void *scalars, size_t scalar_bytes, const accb_array *out,
+                    long long index_base) {
     LOCK(ctx);
     TRY(check_skeleton(ctx, k, {SK_PERMUTE, SK_PERMUTE_SMEM}, "permute"));
     if (n_src < 0) return fail(ctx, ACCB_EINVAL, "negative size");
@@ -660,6 +732,7 @@ int accb_permute(accb_context *ctx, accb_kernel *k, accb_stream stream, const ac
     p.flags |= vec;
     TRY(fill_scalars(ctx, p, scalars, scalar_bytes));
     p.n = n_src;
+    p.base = index_base;
     const long long nout = array_size(out);
     p.ip[0] = nout;
     if (n_src == 0 || nout == 0) return ACCB_OK;

@@ -181,6 +181,7 @@ struct accb_peer {
     unsigned epoch = 0;
     unsigned char **dev_bases = nullptr; /* the buffers' addresses in device memory, for kernels that take a table */
     unsigned scans = 0;                  /* block-cyclic scans so far: the epoch of their block records */
+    PieceState piece;                    /* a scan that is being launched piece by piece */
 };
 
 extern "C" {
@@ -406,6 +407,7 @@ int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *inf
     info->header_bytes = kHeader;
     info->timeout_ns = p->pp.timeout_ns;
     info->count = count ? ++p->scans : p->scans;
+    info->piece = &p->piece;
     return ACCB_OK;
 }
 accb_context *peer_context(accb_peer *p) { return p ? p->ctx : nullptr; }

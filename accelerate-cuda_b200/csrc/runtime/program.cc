@@ -69,6 +69,7 @@ struct accb_program {
     cudaStream_t pipe_stream[3] = {nullptr, nullptr, nullptr}; /* upload, compute, download */
     std::vector<cudaEvent_t> pipe_events;
     int status = ACCB_OK;
+    long long stream_chunk = -1; /* elements per piece of a streamed host run: -1 the default, 0 never stream */
     /* the op list recorded as a CUDA graph for one set of input arrays on one stream */
     cudaGraphExec_t graph_exec = nullptr;
     cudaStream_t graph_stream = nullptr;
@@ -529,83 +530,335 @@ int accb_program_run(accb_program *p, accb_stream stream, const accb_array *inpu
     return run_internal(p, (cudaStream_t)stream, inputs, outputs, false);
 }
 
-/* A program that is one left exclusive scan of its only input is run in chunks: while chunk k
- * is scanned, chunk k+1 is on its way up and chunk k-1 on its way down, so both directions of
- * the host link stay busy.  Chunk k continues from the running total that chunk k-1 left in
- * out[start of k] (read on the device: ACCB_SEED_ON_DEVICE), which is also the value chunk k
- * must write there.  Returns 1 if it handled the run, 0 if the program has another shape. */
-static int run_host_pipelined_scan(accb_program *p, const accb_array *host_in, accb_array *host_out, int *status) {
+/* ------------------------------------------------------------------------------------------------------
+ * Streamed host runs.  The reference uploads every input, runs, and downloads every result, one after the
+ * other (useArrayAsync / collect, CUDA.hs:307-330,382-389), so the host link idles while the kernels run and
+ * one direction idles while the other is used.  A program whose nodes work on their input piece by piece is
+ * run in pieces instead: while piece k is computed, piece k+1 is on its way up and the results of piece k-1 on
+ * their way down.  What makes a node fit:
+ *   map / zipWith   element-wise inputs are cut into the same pieces as the result (accb_map_at);
+ *   fold over rows  a piece is a run of rows (accb_fold_dim_at);
+ *   foldAll         every piece continues from what the pieces before it came to (accb_fold_all_at);
+ *   scanl, scanl1, scanl'   every piece continues from the previous piece's last value (seed on the device);
+ *   permute         every piece combines into the one result (accb_permute_at).
+ * Values are classed as STREAM (cut into pieces along the outermost dimension), WHOLE (an input that is not
+ * read element-wise -- a table that is gathered from, the defaults of a permute: uploaded once, ahead of the
+ * first piece) or ACC (built up over all pieces: a fold's scalar, a permute's result, a scan' total; downloaded
+ * at the end).  Stencils, transposed maps, right scans, segmented folds and nodes that read an ACC value do not
+ * fit; such programs run the reference's way. */
+enum StreamClass { SC_UNKNOWN = 0, SC_STREAM, SC_WHOLE, SC_ACC };
+
+struct StreamValue {
+    int cls = SC_UNKNOWN;
+    long long per_unit = 1; /* elements per unit of the outermost dimension */
+    int tail = 0;           /* elements beyond units * per_unit (the total of an exclusive scan) */
+    accb_array whole;       /* the device array (all pieces) */
+};
+
+/* number of leading components the kernel reads element-wise (In::size of its functor) */
+static int elementwise_components(accb_context *ctx, accb_kernel *k, const char *entry, int *n) {
+    CUfunction fn;
+    KernelMeta meta;
+    int st = get_function(ctx, k, entry, &fn, &meta);
+    if (st == ACCB_OK) *n = meta.v[11];
+    return st;
+}
+
+static long long outer_extent(const accb_array &a) { return a.rank >= 1 ? a.shape[a.rank - 1] : 1; }
+static long long inner_elems(const accb_array &a) {
+    long long n = 1;
+    for (int d = 0; d + 1 < a.rank; ++d) n *= a.shape[d];
+    return n;
+}
+
+/* Returns 1 if it handled the run (status in *status), 0 if the program does not fit. */
+static int run_host_streamed(accb_program *p, const accb_array *host_in, accb_array *host_out, int *status) {
     *status = ACCB_OK;
-    if (p->nodes.size() != 1 || p->ninputs != 1 || p->outputs.size() != 1) return 0;
-    Node &nd = p->nodes[0];
-    if (nd.kind != N_SCAN || nd.direction != ACCB_SCAN_LEFT || nd.scan_kind != ACCB_SCAN_EXCLUSIVE || !nd.has_seed ||
-        nd.env.size() != 1 || nd.env[0] != 0 || p->outputs[0] != nd.out_id || host_in[0].rank != 1)
-        return 0;
-    const long long n = host_in[0].shape[0];
-    long long chunk = 1LL << 23; /* elements per chunk: long enough for the copy engines, short ramps at both ends */
     accb_context *ctx = p->ctx;
-    if (ctx->tune.pipeline_chunk_log2 > 0) chunk = 1LL << std::min(28, std::max(16, ctx->tune.pipeline_chunk_log2));
-    if (n < 2 * chunk || ctx->tune.no_pipeline) return 0;
-    const accb_value_type &tin = p->types[0], &tout = p->types[nd.out_id];
+    if (ctx->tune.no_pipeline || p->stream_chunk == 0 || p->ninputs < 1) return 0;
+    const size_t nvalues = p->types.size();
+    std::vector<StreamValue> val(nvalues);
+    std::vector<int> first_ew(p->nodes.size(), 0); /* element-wise components per node */
+
+    /* ---- does every node fit, and which inputs are cut into pieces? ---- */
+    auto want = [&](int id, int cls) { /* an input takes the class its first reader needs; others must agree */
+        if (val[id].cls == SC_UNKNOWN && id < p->ninputs) val[id].cls = cls;
+        return val[id].cls == cls;
+    };
+    for (size_t ni = 0; ni < p->nodes.size(); ++ni) {
+        Node &nd = p->nodes[ni];
+        const char *entry = nullptr;
+        switch (nd.kind) {
+            case N_MAP: entry = nd.transposed ? nullptr : "map"; break;
+            case N_FOLD: entry = nullptr; break; /* decided below: foldAll or fold over rows */
+            case N_SCAN: entry = nd.direction == ACCB_SCAN_LEFT ? "scanl" : nullptr; break;
+            case N_PERMUTE: entry = "permute"; break;
+            default: return 0;
+        }
+        if (!entry && nd.kind != N_FOLD) return 0;
+        if (nd.shape_like < 0) return 0;
+        if (nd.kind == N_FOLD) entry = (nd.all || p->types[nd.shape_like].rank <= 1) ? "foldAll" : "fold";
+        int ew = 0;
+        if (elementwise_components(ctx, nd.k, entry, &ew) != ACCB_OK) return 0;
+        first_ew[ni] = ew;
+        int slot = 0;
+        for (int e : nd.env) { /* the arrays that hold the first `ew` components are read element-wise */
+            const bool elementwise = slot < ew;
+            slot += p->types[e].ncomp;
+            if (!want(e, elementwise ? SC_STREAM : SC_WHOLE)) return 0;
+        }
+        if (!want(nd.shape_like, SC_STREAM)) return 0;
+        const accb_value_type &to = p->types[nd.out_id];
+        switch (nd.kind) {
+            case N_MAP: val[nd.out_id].cls = SC_STREAM; break;
+            case N_FOLD:
+                if (!strcmp(entry, "foldAll")) {
+                    if (to.ncomp != 1) return 0; /* the carry between pieces is one value */
+                    val[nd.out_id].cls = SC_ACC;
+                } else {
+                    val[nd.out_id].cls = SC_STREAM;
+                }
+                break;
+            case N_SCAN:
+                if (to.ncomp != 1 || p->types[nd.shape_like].rank != 1) return 0;
+                if (nd.scan_kind != ACCB_SCAN_EXCLUSIVE && nd.scan_kind != ACCB_SCAN_INCLUSIVE && nd.scan_kind != ACCB_SCAN_PRIME) return 0;
+                val[nd.out_id].cls = SC_STREAM;
+                val[nd.out_id].tail = nd.scan_kind == ACCB_SCAN_EXCLUSIVE ? 1 : 0;
+                if (nd.scan_kind == ACCB_SCAN_PRIME) val[nd.out_id + 1].cls = SC_ACC;
+                break;
+            case N_PERMUTE:
+                if (!want(nd.defaults_id, SC_WHOLE)) return 0;
+                val[nd.out_id].cls = SC_ACC;
+                break;
+            default: return 0;
+        }
+    }
+    for (int id : p->outputs)
+        if (val[id].cls != SC_STREAM && val[id].cls != SC_ACC) return 0;
+
+    /* ---- the pieces: all streamed inputs share the outermost extent ---- */
+    long long units = -1, widest = 1;
+    for (int i = 0; i < p->ninputs; ++i) {
+        if (val[i].cls == SC_UNKNOWN) val[i].cls = SC_WHOLE; /* an input nobody reads */
+        if (val[i].cls != SC_STREAM) continue;
+        if (host_in[i].rank < 1) return 0;
+        if (units < 0) units = outer_extent(host_in[i]);
+        if (outer_extent(host_in[i]) != units) return 0;
+        val[i].per_unit = inner_elems(host_in[i]);
+        widest = std::max(widest, val[i].per_unit);
+    }
+    if (units < 0) return 0;
+    long long chunk_elems = 1LL << 23; /* long enough for the copy engines, short ramps at both ends */
+    if (ctx->tune.pipeline_chunk_log2 > 0) chunk_elems = 1LL << std::min(28, std::max(10, ctx->tune.pipeline_chunk_log2));
+    if (p->stream_chunk > 0) chunk_elems = p->stream_chunk;
+    /* pieces start on multiples of 16 units, so that every component of every piece stays 16-byte aligned */
+    const long long per_piece = std::max(16LL, chunk_elems / widest / 16 * 16);
+    if (units < 2 * per_piece) return 0;
+    const long long npieces = (units + per_piece - 1) / per_piece;
+
     auto run = [&]() -> int {
         for (int i = 0; i < 3; ++i)
             if (!p->pipe_stream[i])
                 TRY(check_cuda(ctx, cudaStreamCreateWithFlags(&p->pipe_stream[i], cudaStreamNonBlocking), "cudaStreamCreate"));
         cudaStream_t up = p->pipe_stream[0], comp = p->pipe_stream[1], down = p->pipe_stream[2];
-        const long long nchunks = (n + chunk - 1) / chunk;
-        while ((long long)p->pipe_events.size() < 2 * nchunks) {
+        while ((long long)p->pipe_events.size() < 2 * npieces + 1) {
             cudaEvent_t e;
             TRY(check_cuda(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate"));
             p->pipe_events.push_back(e);
         }
-        accb_array din, dout;
-        memset(&din, 0, sizeof din);
-        memset(&dout, 0, sizeof dout);
-        din.rank = dout.rank = 1;
-        din.ncomp = tin.ncomp;
-        dout.ncomp = tout.ncomp;
-        auto &islots = p->in_pool[0];
-        if ((int)islots.size() < tin.ncomp) islots.resize(tin.ncomp);
-        for (int c = 0; c < tin.ncomp; ++c) TRY(pool_get(p, islots[c], (size_t)n * tin.comp_bytes[c], &din.ptr[c]));
-        dout.shape[0] = (int)(n + 1);
-        TRY(alloc_value(p, nd.out_id, dout, false));
-        for (long long k = 0; k < nchunks; ++k) {
-            const long long off = k * chunk, len = std::min(chunk, n - off);
-            accb_array ci = din, co = dout;
-            ci.shape[0] = (int)len;
-            co.shape[0] = (int)len + 1;
-            for (int c = 0; c < tin.ncomp; ++c) {
-                ci.ptr[c] = static_cast<char *>(din.ptr[c]) + off * tin.comp_bytes[c];
-                TRY(check_cuda(ctx, cudaMemcpyAsync(ci.ptr[c], static_cast<const char *>(host_in[0].ptr[c]) + off * tin.comp_bytes[c],
-                                                    (size_t)len * tin.comp_bytes[c], cudaMemcpyHostToDevice, up), "upload"));
+        /* device arrays of the inputs (whole size); WHOLE inputs go up first */
+        for (int i = 0; i < p->ninputs; ++i) {
+            accb_array &d = val[i].whole;
+            d = host_in[i];
+            const accb_value_type &t = p->types[i];
+            auto &slots = p->in_pool[i];
+            if ((int)slots.size() < t.ncomp) slots.resize(t.ncomp);
+            const long long n = size_of(host_in[i]);
+            for (int c = 0; c < t.ncomp; ++c) {
+                TRY(pool_get(p, slots[c], (size_t)std::max(1LL, n) * t.comp_bytes[c], &d.ptr[c]));
+                if (val[i].cls == SC_WHOLE && n > 0)
+                    TRY(check_cuda(ctx, cudaMemcpyAsync(d.ptr[c], host_in[i].ptr[c], (size_t)n * t.comp_bytes[c],
+                                                        cudaMemcpyHostToDevice, up), "upload"));
             }
-            for (int c = 0; c < tout.ncomp; ++c) co.ptr[c] = static_cast<char *>(dout.ptr[c]) + off * tout.comp_bytes[c];
+        }
+        TRY(check_cuda(ctx, cudaEventRecord(p->pipe_events[2 * npieces], up), "cudaEventRecord"));
+        TRY(check_cuda(ctx, cudaStreamWaitEvent(comp, p->pipe_events[2 * npieces], 0), "cudaStreamWaitEvent"));
+
+        /* a piece [u0, u0 + len) of a streamed value */
+        auto piece = [&](int id, long long u0, long long len, int extra) {
+            const StreamValue &v = val[id];
+            accb_array a = v.whole;
+            a.shape[a.rank - 1] = (int)(len + (a.rank == 1 ? extra : 0));
+            for (int c = 0; c < a.ncomp; ++c)
+                a.ptr[c] = static_cast<char *>(v.whole.ptr[c]) + u0 * v.per_unit * p->types[id].comp_bytes[c];
+            return a;
+        };
+
+        for (long long k = 0; k < npieces; ++k) {
+            const long long u0 = k * per_piece, len = std::min(per_piece, units - u0);
+            const bool first = k == 0, last = k == npieces - 1;
+            for (int i = 0; i < p->ninputs; ++i) {
+                if (val[i].cls != SC_STREAM) continue;
+                const accb_value_type &t = p->types[i];
+                for (int c = 0; c < t.ncomp; ++c) {
+                    const size_t off = (size_t)(u0 * val[i].per_unit) * t.comp_bytes[c];
+                    TRY(check_cuda(ctx, cudaMemcpyAsync(static_cast<char *>(val[i].whole.ptr[c]) + off,
+                                                        static_cast<const char *>(host_in[i].ptr[c]) + off,
+                                                        (size_t)(len * val[i].per_unit) * t.comp_bytes[c], cudaMemcpyHostToDevice, up),
+                                   "upload"));
+                }
+            }
             TRY(check_cuda(ctx, cudaEventRecord(p->pipe_events[2 * k], up), "cudaEventRecord"));
             TRY(check_cuda(ctx, cudaStreamWaitEvent(comp, p->pipe_events[2 * k], 0), "cudaStreamWaitEvent"));
-            if (k == 0 || tout.ncomp != 1) {
-                if (k > 0) return fail(ctx, ACCB_EINVAL, "pipelined scan: tuple carries are not supported");
-                TRY(accb_scan(ctx, nd.k, comp, &ci, 1, len, ACCB_SCAN_LEFT, ACCB_SCAN_EXCLUSIVE, nd.scalars.data(),
-                              nd.scalars.size(), &co, nullptr));
-            } else {
-                TRY(accb_scan(ctx, nd.k, comp, &ci, 1, len, ACCB_SCAN_LEFT, ACCB_SCAN_EXCLUSIVE | ACCB_SEED_ON_DEVICE,
-                              co.ptr[0], tout.comp_bytes[0], &co, nullptr));
+
+            for (size_t ni = 0; ni < p->nodes.size(); ++ni) {
+                Node &nd = p->nodes[ni];
+                const StreamValue &like = val[nd.shape_like];
+                const void *sc = nd.scalars.empty() ? nullptr : nd.scalars.data();
+                std::vector<accb_array> env;
+                for (int e : nd.env) env.push_back(val[e].cls == SC_STREAM ? piece(e, u0, len, 0) : val[e].whole);
+                const long long base = u0 * like.per_unit; /* index of the piece's first element in the whole array */
+                StreamValue &ov = val[nd.out_id];
+                if (first) { /* size the result from the whole input */
+                    accb_array &o = ov.whole;
+                    memset(&o, 0, sizeof o);
+                    const accb_array &lw = like.whole;
+                    switch (nd.kind) {
+                        case N_MAP:
+                            o.rank = lw.rank;
+                            memcpy(o.shape, lw.shape, sizeof o.shape);
+                            ov.per_unit = like.per_unit;
+                            break;
+                        case N_FOLD:
+                            if (ov.cls == SC_ACC) {
+                                o.rank = 0;
+                            } else { /* the innermost extent goes */
+                                o.rank = lw.rank - 1;
+                                for (int d = 1; d < lw.rank; ++d) o.shape[d - 1] = lw.shape[d];
+                                ov.per_unit = lw.shape[0] ? like.per_unit / lw.shape[0] : 0;
+                            }
+                            break;
+                        case N_SCAN:
+                            o.rank = 1;
+                            o.shape[0] = (int)(units + ov.tail);
+                            ov.per_unit = 1;
+                            break;
+                        case N_PERMUTE: {
+                            const accb_array &dfl = val[nd.defaults_id].whole;
+                            o.rank = dfl.rank;
+                            memcpy(o.shape, dfl.shape, sizeof o.shape);
+                            break;
+                        }
+                        default: break;
+                    }
+                    if (nd.kind == N_SCAN && units + ov.tail > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one scan");
+                    TRY(alloc_value(p, nd.out_id, o, false));
+                    if (nd.kind == N_SCAN && nd.scan_kind == ACCB_SCAN_PRIME) {
+                        accb_array &t = val[nd.out_id + 1].whole;
+                        memset(&t, 0, sizeof t);
+                        TRY(alloc_value(p, nd.out_id + 1, t, false));
+                    }
+                    if (nd.kind == N_PERMUTE)
+                        TRY(accb_permute_defaults(ctx, comp, &val[nd.defaults_id].whole, &o, p->types[nd.out_id].comp_bytes));
+                }
+                switch (nd.kind) {
+                    case N_MAP: {
+                        accb_array o = piece(nd.out_id, u0, len, 0);
+                        TRY(accb_map_at(ctx, nd.k, comp, env.data(), (int)env.size(), sc, nd.scalars.size(), &o, base));
+                        break;
+                    }
+                    case N_FOLD: {
+                        if (ov.cls == SC_ACC) {
+                            const bool seed_now = nd.has_seed && last; /* f(.., seed) closes the fold: with the last piece */
+                            TRY(accb_fold_all_at(ctx, nd.k, comp, env.data(), (int)env.size(), len * like.per_unit,
+                                                 seed_now ? sc : nullptr, nd.scalars.size(), &ov.whole, base,
+                                                 first ? nullptr : ov.whole.ptr[0]));
+                        } else {
+                            accb_array o = piece(nd.out_id, u0, len, 0);
+                            const long long cols = like.whole.shape[0];
+                            TRY(accb_fold_dim_at(ctx, nd.k, comp, env.data(), (int)env.size(), cols ? len * like.per_unit / cols : 0,
+                                                 cols, nd.has_seed ? sc : nullptr, nd.scalars.size(), &o, base));
+                        }
+                        break;
+                    }
+                    case N_SCAN: {
+                        const int eb = p->types[nd.out_id].comp_bytes[0];
+                        accb_array o = piece(nd.out_id, u0, len, last ? ov.tail : ov.tail); /* every piece writes its running total behind itself */
+                        char *optr = static_cast<char *>(o.ptr[0]);
+                        if (nd.scan_kind == ACCB_SCAN_EXCLUSIVE) {
+                            /* piece k continues from the total piece k-1 left in the element it also starts with */
+                            TRY(accb_scan_at(ctx, nd.k, comp, env.data(), (int)env.size(), len, ACCB_SCAN_LEFT,
+                                             first ? ACCB_SCAN_EXCLUSIVE : (ACCB_SCAN_EXCLUSIVE | ACCB_SEED_ON_DEVICE),
+                                             first ? sc : static_cast<const void *>(optr), first ? nd.scalars.size() : (size_t)eb, &o,
+                                             nullptr, base));
+                        } else if (nd.scan_kind == ACCB_SCAN_INCLUSIVE) {
+                            TRY(accb_scan_at(ctx, nd.k, comp, env.data(), (int)env.size(), len, ACCB_SCAN_LEFT,
+                                             first ? ACCB_SCAN_INCLUSIVE : (ACCB_SCAN_INCLUSIVE_SEEDED | ACCB_SEED_ON_DEVICE),
+                                             first ? nullptr : static_cast<const void *>(optr - eb), first ? 0 : (size_t)eb, &o, nullptr,
+                                             base));
+                        } else { /* scanl': the total so far is the next piece's seed */
+                            accb_array &tot = val[nd.out_id + 1].whole;
+                            TRY(accb_scan_at(ctx, nd.k, comp, env.data(), (int)env.size(), len, ACCB_SCAN_LEFT,
+                                             first ? ACCB_SCAN_PRIME : (ACCB_SCAN_PRIME | ACCB_SEED_ON_DEVICE),
+                                             first ? sc : static_cast<const void *>(tot.ptr[0]), first ? nd.scalars.size() : (size_t)eb, &o,
+                                             &tot, base));
+                        }
+                        break;
+                    }
+                    case N_PERMUTE:
+                        TRY(accb_permute_at(ctx, nd.k, comp, env.data(), (int)env.size(), len * like.per_unit, nullptr, 0,
+                                            &ov.whole, base));
+                        break;
+                    default: break;
+                }
             }
             TRY(check_cuda(ctx, cudaEventRecord(p->pipe_events[2 * k + 1], comp), "cudaEventRecord"));
             TRY(check_cuda(ctx, cudaStreamWaitEvent(down, p->pipe_events[2 * k + 1], 0), "cudaStreamWaitEvent"));
-            const long long take = len + (k == nchunks - 1 ? 1 : 0); /* the last chunk also brings the total */
-            for (int c = 0; c < tout.ncomp; ++c)
-                TRY(check_cuda(ctx, cudaMemcpyAsync(static_cast<char *>(host_out[0].ptr[c]) + off * tout.comp_bytes[c], co.ptr[c],
-                                                    (size_t)take * tout.comp_bytes[c], cudaMemcpyDeviceToHost, down), "download"));
+            /* the piece's share of every streamed result goes down while the next piece is computed */
+            for (size_t j = 0; j < p->outputs.size(); ++j) {
+                const int id = p->outputs[j];
+                const StreamValue &v = val[id];
+                if (v.cls != SC_STREAM) continue;
+                const accb_value_type &t = p->types[id];
+                const long long take = len * v.per_unit + (last ? v.tail : 0);
+                for (int c = 0; c < t.ncomp; ++c) {
+                    const size_t off = (size_t)(u0 * v.per_unit) * t.comp_bytes[c];
+                    if (take > 0)
+                        TRY(check_cuda(ctx, cudaMemcpyAsync(static_cast<char *>(host_out[j].ptr[c]) + off,
+                                                            static_cast<const char *>(v.whole.ptr[c]) + off,
+                                                            (size_t)take * t.comp_bytes[c], cudaMemcpyDeviceToHost, down), "download"));
+                }
+            }
+        }
+        /* results built up over all pieces */
+        for (size_t j = 0; j < p->outputs.size(); ++j) {
+            const int id = p->outputs[j];
+            const StreamValue &v = val[id];
+            const accb_value_type &t = p->types[id];
+            void *host_ptr[ACCB_ARRAY_MAX_COMP];
+            for (int c = 0; c < t.ncomp; ++c) host_ptr[c] = host_out[j].ptr[c];
+            if (v.cls == SC_ACC) {
+                const long long n = size_of(v.whole);
+                for (int c = 0; c < t.ncomp; ++c)
+                    if (n > 0)
+                        TRY(check_cuda(ctx, cudaMemcpyAsync(host_ptr[c], v.whole.ptr[c], (size_t)n * t.comp_bytes[c],
+                                                            cudaMemcpyDeviceToHost, down), "download"));
+            }
+            host_out[j] = v.whole; /* rank and shape of the result */
+            for (int c = 0; c < t.ncomp; ++c) host_out[j].ptr[c] = host_ptr[c];
         }
         TRY(check_cuda(ctx, cudaStreamSynchronize(down), "cudaStreamSynchronize"));
-        host_out[0].rank = 1;
-        host_out[0].shape[0] = (int)(n + 1);
-        host_out[0].ncomp = tout.ncomp;
         return ACCB_OK;
     };
-    if (tout.ncomp != 1) return 0;
     *status = run();
     return 1;
+}
+
+int accb_program_stream_chunk(accb_program *p, long long elements) {
+    PLOCK(p);
+    if (elements < -1) return fail(p->ctx, ACCB_EINVAL, "piece size %lld", elements);
+    p->stream_chunk = elements;
+    return ACCB_OK;
 }
 
 int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array *host_out) {
@@ -614,7 +867,7 @@ int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array
     accb_context *ctx = p->ctx;
     {
         int st = ACCB_OK;
-        if (run_host_pipelined_scan(p, host_in, host_out, &st)) return st;
+        if (run_host_streamed(p, host_in, host_out, &st)) return st;
     }
     if (!p->host_stream) TRY(check_cuda(ctx, cudaStreamCreateWithFlags(&p->host_stream, cudaStreamNonBlocking), "cudaStreamCreate"));
     cudaStream_t s = p->host_stream;

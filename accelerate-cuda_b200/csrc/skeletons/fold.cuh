@@ -70,7 +70,7 @@ template <class Fn, int N, int... I>
 __device__ __forceinline__ void fold_get(const Env &env, long long i0, regs<N, typename Fn::In> &a,
                                          typename Fn::elem (&x)[N], std::integer_sequence<int, I...>) {
 #pragma unroll
-    for (int k = 0; k < N; ++k) x[k] = Fn::get(env, i0 + k, comp<I>(a)[k]...);
+    for (int k = 0; k < N; ++k) x[k] = Fn::get(env, env.p.base + i0 + k, comp<I>(a)[k]...);
 }
 
 template <class Fn, int... O>
@@ -196,6 +196,13 @@ __device__ __forceinline__ void fold_all_body(const accb_kparams &p) {
     tot = block_reduce<CTA>(tot, oc, s_red);
     if (threadIdx.x == 0) {
         *ticket = 0u;
+        if (p.flags & ACCB_F_CARRY) {
+            /* this launch folds a later piece of a larger array: what the pieces before it came to stands on
+             * the LEFT (the combiner need not commute) */
+            const A c = Fn::lift(*static_cast<const typename Fn::elem *>(p.aux[2]));
+            tot.v = tot.have ? Fn::combine(c, tot.v) : c;
+            tot.have = 1;
+        }
         if (p.flags & ACCB_F_HAS_SEED) {
             const A z = Fn::lift(fold_seed<Fn>(p));
             tot.v = tot.have ? Fn::combine(tot.v, z) : z;
@@ -384,7 +391,7 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
 /* Entry points named after the reference's kernels (Reduction.hs:111,229,430);
  * the seeded and seedless forms share a kernel (flag ACCB_F_HAS_SEED). */
 #define ACCB_INSTANTIATE_FOLD_ALL(Fn)                                                   \
-    ACCB_META(2, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, ACCB_FOLD_U, 0)           \
+    ACCB_META12(2, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>), 0, ACCB_FOLD_U, 0, 0, 0, 0, 0, 0, Fn::In::size) \
     extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
         foldAll(const __grid_constant__ accb_kparams p) {                               \
         accb::fold_all_body<Fn, ACCB_FOLD_CTA, ACCB_FOLD_U>(p);                         \
@@ -406,9 +413,9 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
  * Metadata: {.., bytes of a partial, elements per window of the staged form, U, block size of the
  * staged form, its shared memory} */
 #define ACCB_INSTANTIATE_FOLD_DIM(Fn)                                                   \
-    ACCB_META7(3, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>),                            \
-               accb::fold_stage_window<Fn::In>::value, ACCB_FOLD_U, ACCB_FOLD_STAGE_CTA, \
-               (accb::fold_stage_smem<Fn>()))                                           \
+    ACCB_META12(3, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>),                           \
+                accb::fold_stage_window<Fn::In>::value, ACCB_FOLD_U, ACCB_FOLD_STAGE_CTA, \
+                (accb::fold_stage_smem<Fn>()), 0, 0, 0, 0, Fn::In::size)                \
     ACCB_FOLD_STAGED_ENTRY(Fn, fold_staged, false)                                      \
     ACCB_FOLD_DIM_ENTRY(Fn, fold, ACCB_FOLD_CTA, ACCB_FOLD_U, 1)                        \
     ACCB_FOLD_DIM_ENTRY(Fn, fold_warp, 32, 4, 1)                                        \

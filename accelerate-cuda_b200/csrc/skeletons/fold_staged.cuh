@@ -59,14 +59,14 @@ template <class Fn, int WIN, int... I>
 __device__ __forceinline__ typename Fn::elem stage_get(const Env &env, const unsigned char *s, int j, long long i,
                                                        std::integer_sequence<int, I...>) {
     typedef typename Fn::In In;
-    return Fn::get(env, i,
+    return Fn::get(env, env.p.base + i,
                    reinterpret_cast<const typename type_at<I, In>::type *>(s + smem_offset<In, I, WIN>::value)[j]...);
 }
 template <class Fn, int... I>
 __device__ __forceinline__ typename Fn::elem global_get(const accb_kparams &p, const Env &env, long long i,
                                                         std::integer_sequence<int, I...>) {
     typedef typename Fn::In In;
-    return Fn::get(env, i, static_cast<const typename type_at<I, In>::type *>(p.in[I])[i]...);
+    return Fn::get(env, p.base + i, static_cast<const typename type_at<I, In>::type *>(p.in[I])[i]...);
 }
 
 /* bulk copy of `len` elements of every component starting at element `g` (a multiple of 16); the

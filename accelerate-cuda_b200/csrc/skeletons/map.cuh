@@ -36,7 +36,7 @@ __device__ __forceinline__ void map_apply(const Env &env, long long i0, regs<N, 
                                           regs<N, typename Fn::Out> &b, std::integer_sequence<int, I...>,
                                           std::integer_sequence<int, O...>) {
 #pragma unroll
-    for (int k = 0; k < N; ++k) Fn::apply(env, i0 + k, comp<I>(a)[k]..., comp<O>(b)[k]...);
+    for (int k = 0; k < N; ++k) Fn::apply(env, env.p.base + i0 + k, comp<I>(a)[k]..., comp<O>(b)[k]...);
 }
 
 template <class Fn, int CTA, int U>
@@ -290,8 +290,8 @@ __host__ __device__ constexpr int map_transposed_smem() {
 /* Entry point named after the reference's kernel (Mapping.hs:53), and the form for transposed
  * inputs.  Metadata: {.., 0, 0, U, element-wise input components, shared memory of the transposed form}. */
 #define ACCB_INSTANTIATE_MAP(Fn)                                                        \
-    ACCB_META7(1, ACCB_MAP_CTA, 0, 0, ACCB_MAP_U, Fn::In::size,                         \
-               (accb::map_transposed_smem<Fn>()))                                       \
+    ACCB_META12(1, ACCB_MAP_CTA, 0, 0, ACCB_MAP_U, Fn::In::size,                        \
+                (accb::map_transposed_smem<Fn>()), 0, 0, 0, 0, Fn::In::size)            \
     extern "C" __global__ void __launch_bounds__(ACCB_MAP_CTA)                          \
         map(const __grid_constant__ accb_kparams p) {                                   \
         accb::map_body<Fn, ACCB_MAP_CTA, ACCB_MAP_U>(p);                                \

@@ -158,9 +158,9 @@ __device__ __forceinline__ void permute_elems(const accb_kparams &p, const Env &
     const long long nout = p.ip[0];
 #pragma unroll
     for (int k = 0; k < N; ++k) {
-        const long long j = Fn::index(env, i0 + k, comp<I>(a)[k]...);
+        const long long j = Fn::index(env, env.p.base + i0 + k, comp<I>(a)[k]...);
         if (j >= 0 && j < nout) {
-            const T x = Fn::get(env, i0 + k, comp<I>(a)[k]...);
+            const T x = Fn::get(env, env.p.base + i0 + k, comp<I>(a)[k]...);
             if constexpr (Fn::atomic == Atomic::Lock)
                 permute_locked<Fn>(p, j, x, std::make_integer_sequence<int, Fn::Out::size>());
             else
@@ -210,9 +210,9 @@ __device__ __forceinline__ void permute_elems_smem(const accb_kparams &p, const 
     const long long nout = p.ip[0];
 #pragma unroll
     for (int k = 0; k < N; ++k) {
-        const long long j = Fn::index(env, i0 + k, comp<I>(a)[k]...);
+        const long long j = Fn::index(env, env.p.base + i0 + k, comp<I>(a)[k]...);
         if (j >= 0 && j < nout) {
-            const T x = Fn::get(env, i0 + k, comp<I>(a)[k]...);
+            const T x = Fn::get(env, env.p.base + i0 + k, comp<I>(a)[k]...);
             atomic_combine<Fn>(mine + j, x);
         }
     }
@@ -276,8 +276,8 @@ __device__ __forceinline__ void permute_smem_body(const accb_kparams &p) {
 /* Entry points: `permute` as in the reference (IndexSpace.hs:172); the
  * privatised form is selected by the host when the destination is small. */
 #define ACCB_INSTANTIATE_PERMUTE(Fn)                                                           \
-    ACCB_META(6, ACCB_PERMUTE_CTA, sizeof(Fn::elem), 0, ACCB_PERMUTE_U,                        \
-              Fn::atomic == accb::Atomic::Lock ? 1 : 0)                                        \
+    ACCB_META12(6, ACCB_PERMUTE_CTA, sizeof(Fn::elem), 0, ACCB_PERMUTE_U,                      \
+                Fn::atomic == accb::Atomic::Lock ? 1 : 0, 0, 0, 0, 0, 0, Fn::In::size)         \
     extern "C" __global__ void __launch_bounds__(ACCB_PERMUTE_CTA)                             \
         permute(const __grid_constant__ accb_kparams p) {                                      \
         accb::permute_body<Fn, ACCB_PERMUTE_CTA, ACCB_PERMUTE_U>(p);                           \

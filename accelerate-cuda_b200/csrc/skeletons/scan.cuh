@@ -84,7 +84,10 @@
  * Block-cyclic entries in addition: ip[5] tiles per block, ip[6] number of GPUs,
  * ip[7] this GPU's rank, ip[8] epoch of the block records (the same on every
  * GPU), ip[9] time limit in ns, ip[10] byte offset of the block records in
- * every GPU's exchange buffer; aux[3] device table of the G buffers' addresses.
+ * every GPU's exchange buffer, ip[11] first tile of this launch (the scan may be
+ * launched piece by piece, all pieces with the same epochs, so that a later
+ * piece finds the records of the earlier ones); aux[3] device table of the G
+ * buffers' addresses.
  */
 #pragma once
 #include "../cubits/accb_vec.cuh"
@@ -866,6 +869,7 @@ __device__ __forceinline__ void scan_body(const accb_kparams &p) {
     } else {
         t = blockIdx.x;
     }
+    if constexpr (BC) t += p.ip[11]; /* a launch may cover the tiles from ip[11] on: the scan launched piece by piece */
     if (t >= ntiles) return;
     const long long base = (RIGHT ? ntiles - 1 - t : t) * TILE; /* position in memory */
     const long long len = (n - base) < TILE ? (n - base) : (long long)TILE;
@@ -919,7 +923,7 @@ __device__ __forceinline__ void scan_body(const accb_kparams &p) {
                                                   ACCB_SCAN_CTA * ACCB_SCAN_ROWS_FOR(Fn) * 4>::value)  \
                              : 0,                                                              \
                sizeof(Fn::elem), ACCB_SCAN_BC_CTA, ACCB_SCAN_BC_CTA * ACCB_SCAN_BC_ROWS_FOR(Fn) * 4,  \
-               (accb::smem_offset<Fn::In, Fn::In::size, ACCB_SCAN_BC_CTA * ACCB_SCAN_BC_ROWS_FOR(Fn) * 4>::value), 0) \
+               (accb::smem_offset<Fn::In, Fn::In::size, ACCB_SCAN_BC_CTA * ACCB_SCAN_BC_ROWS_FOR(Fn) * 4>::value), Fn::In::size) \
     ACCB_SCAN_ENTRY(Fn, scanl, false, false)                                                   \
     ACCB_SCAN_ENTRY(Fn, scanl1, false, true)                                                   \
     ACCB_SCAN_ENTRY(Fn, scanr, true, false)                                                    \

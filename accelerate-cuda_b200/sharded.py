@@ -265,6 +265,54 @@ def peer_buffer(ctx, nbytes: int, group=None):
         raise
 
 
+class PeerScanFromHost:
+    """``scanl`` over one vector dealt to the ranks in blocks, from HOST arrays to HOST arrays: the counterpart of
+    ``run1`` (upload, run, download: CUDA.hs:307-330,382-389) for one process per GPU.  Every rank passes its own
+    blocks (pinned host memory) and receives its share of the result.  The scan is launched piece by piece
+    (``Peer.scan`` with ``first_block`` / ``blocks``): while piece k is scanned, piece k+1 is on its way to the
+    device and the result of piece k-1 on its way back, so both directions of every rank's host link and the GPUs
+    work at the same time."""
+
+    def __init__(self, ctx, peer, kernel, n_global: int, block_elems: int, dtype, seed, blocks_per_piece: int = 32,
+                 scratch_offset: int = 0):
+        from . import scan_layout
+        self.ctx, self.peer, self.kernel, self.seed = ctx, peer, kernel, seed
+        self.n_global, self.block, self.per, self.scratch_offset = n_global, block_elems, blocks_per_piece, scratch_offset
+        self.n_local, self.owner, _ = scan_layout(peer.world, peer.rank, n_global, block_elems)
+        self.has_total = peer.rank == self.owner
+        # every rank launches the same number of pieces: as many as the rank with the most blocks needs
+        most = -(-(-(-n_global // block_elems)) // peer.world)
+        self.pieces = max(1, -(-most // blocks_per_piece))
+        self.x = torch.empty(max(1, self.n_local), dtype=dtype, device="cuda")
+        self.out = torch.empty(self.n_local + 1, dtype=dtype, device="cuda")
+        self.up, self.comp, self.down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+
+    def __call__(self, host_in: torch.Tensor, host_out: torch.Tensor):
+        """host_in: this rank's n_local elements; host_out: n_local elements (+ 1 on the rank that owns the last
+        block: the total).  Returns when the result has arrived."""
+        n, blk = self.n_local, self.block
+        for k in range(self.pieces):
+            first = k * self.per
+            lo, hi = min(n, first * blk), min(n, (first + self.per) * blk)
+            arrived, scanned = torch.cuda.Event(), torch.cuda.Event()
+            with torch.cuda.stream(self.up):
+                if hi > lo:
+                    self.x[lo:hi].copy_(host_in[lo:hi], non_blocking=True)
+                arrived.record()
+            self.comp.wait_event(arrived)
+            self.peer.scan(self.kernel, [self.x[:max(1, n)]], self.n_global, self.out, seed=self.seed, block_elems=blk,
+                           scratch_offset=self.scratch_offset, stream=self.comp.cuda_stream, first_block=first,
+                           blocks=self.per)
+            scanned.record(self.comp)
+            self.down.wait_event(scanned)
+            with torch.cuda.stream(self.down):
+                top = hi + (1 if (hi == n and self.has_total and k == self.pieces - 1) else 0)
+                if top > lo:
+                    host_out[lo:top].copy_(self.out[lo:top], non_blocking=True)
+        self.down.synchronize()
+        return host_out
+
+
 def peer_scan_carry(peer, offset: int, gathered: torch.Tensor) -> torch.Tensor:
     """The carry of a sharded scan when the slab total was written at ``offset`` of the rank's exchange buffer: one
     kernel synchronises the ranks and gathers the totals; the exclusive sum of the lower ranks follows."""

@@ -202,6 +202,31 @@ ACCB_API int accb_scan(accb_context *ctx, accb_kernel *k, accb_stream stream, co
                        long long n, int direction, int kind, const void *seed, size_t seed_bytes,
                        const accb_array *out, const accb_array *total);
 
+/* The same launches over a PIECE of a larger array: `env` and `out` describe the piece, and the functor is told
+ * index_base + position, i.e. the element's index in the whole array.  This is how a program whose input does
+ * not fit, or has not arrived yet, is run piece by piece (accb_program_run_host streams host arrays this way:
+ * while piece k is computed, piece k+1 is on its way to the device and the result of piece k-1 on its way back).
+ *   fold_all  `carry` is NULL or a device pointer to what the pieces before this one came to (one value of the
+ *             result type): the result is carry (f) fold of this piece [(f) seed], the carry on the LEFT.  Pass
+ *             the seed with the last piece only.
+ *   scan      continue from the previous piece with ACCB_SEED_ON_DEVICE (and ACCB_SCAN_INCLUSIVE_SEEDED for scanl1).
+ *   permute   every piece combines into the same `out`; copy the defaults once, before the first piece.
+ * No counterpart in the reference, which uploads whole arrays before the first launch (CUDA.hs:307-330). */
+ACCB_API int accb_map_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                         const void *scalars, size_t scalar_bytes, const accb_array *out, long long index_base);
+ACCB_API int accb_fold_all_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
+                              int nenv, long long n, const void *seed, size_t seed_bytes, const accb_array *out,
+                              long long index_base, const void *carry);
+ACCB_API int accb_fold_dim_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
+                              int nenv, long long rows, long long cols, const void *seed, size_t seed_bytes,
+                              const accb_array *out, long long index_base);
+ACCB_API int accb_scan_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                          long long n, int direction, int kind, const void *seed, size_t seed_bytes,
+                          const accb_array *out, const accb_array *total, long long index_base);
+ACCB_API int accb_permute_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
+                             int nenv, long long n_src, const void *scalars, size_t scalar_bytes,
+                             const accb_array *out, long long index_base);
+
 /* Int32 `scanl (+) seed` for callers that cannot allocate device memory.  It has
  * no counterpart in the reference, whose every scan allocates its block-sum
  * array (scanCore, CUDA/Execute.hs:364-392).  Meant for code that runs with a
@@ -368,7 +393,11 @@ enum { ACCB_AWHILE_HOST = 0, ACCB_AWHILE_DEVICE = 1 };
 ACCB_API int accb_awhile(accb_program *cond, accb_program *body, accb_stream stream, const accb_array *state,
                          int mode, long long max_iters, long long *iterations);
 /* run1 with HOST arrays: upload, execute, download (CUDA.hs:307-330,382-389).
- * host_in[i] / host_out[j] point to one host buffer per component. */
+ * host_in[i] / host_out[j] point to one host buffer per component.  A program made of maps, folds, left scans
+ * and permutes over inputs of one outermost extent is run in pieces (see accb_map_at), so that both directions
+ * of the host link and the GPU work at the same time; accb_program_stream_chunk sets the piece size in elements
+ * (-1: the default of 2^23, 0: never run in pieces).  Use pinned host memory for the copies to overlap. */
+ACCB_API int accb_program_stream_chunk(accb_program *p, long long elements);
 ACCB_API int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array *host_out);
 ACCB_API int accb_program_destroy(accb_program *p);
 
@@ -496,6 +525,16 @@ ACCB_API int accb_peer_scan_layout(int world, int rank, long long n_global, long
 ACCB_API int accb_peer_scan(accb_peer *peer, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
                             long long n_global, long long block_elems, int kind, const void *seed, size_t seed_bytes,
                             size_t scratch_offset, const accb_array *out, const accb_array *total);
+/* The same scan launched piece by piece: this call covers the rank's blocks first_local_block .. first_local_block +
+ * local_blocks - 1 (local_blocks < 0: all the rest); `env`, `out` and every other argument are those of the whole
+ * scan in every call.  Piece 0 begins the scan, later pieces must follow in order on the same stream, with no other
+ * scan on that stream in between; every rank cuts its blocks at the same places.  A later piece finds the
+ * records of the earlier ones, so a rank can scan what has arrived while the rest of its input is still on its way
+ * from the host, and send results back while later pieces run. */
+ACCB_API int accb_peer_scan_piece(accb_peer *peer, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
+                                  long long n_global, long long block_elems, int kind, const void *seed,
+                                  size_t seed_bytes, size_t scratch_offset, const accb_array *out,
+                                  const accb_array *total, long long first_local_block, long long local_blocks);
 ACCB_API int accb_peer_status(accb_peer *peer, accb_stream stream, int *timed_out);
 ACCB_API int accb_peer_destroy(accb_peer *peer); /* after every rank has finished using the buffers */
 

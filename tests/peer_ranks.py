@@ -88,6 +88,20 @@ def main():
             ctx.sync()
             ok = ok and bool(torch.equal(out[:n_local], sh.block_cyclic_take(ref[1:] - 3, rank, world, block)))
             ok = ok and int(out[n_local]) == -77
+    # the same from pinned host arrays, the scan launched in pieces that overlap with the copies
+    n_g, block = world * 40 * tile + 999, 2 * tile
+    n_local, owner, _ = accb.scan_layout(world, rank, n_g, block)
+    same = torch.Generator(device="cuda").manual_seed(777)
+    whole = torch.randint(-9, 10, (n_g,), generator=same, device="cuda", dtype=torch.int32)
+    ref = (torch.cat([torch.zeros(1, dtype=torch.int64, device="cuda"), torch.cumsum(whole, 0, dtype=torch.int64)]) + 3).int()
+    run = sh.PeerScanFromHost(ctx, peer2, P.SCAN_ADD_I32, n_g, block, torch.int32, np.int32(3), blocks_per_piece=3)
+    hin = sh.block_cyclic_take(whole, rank, world, block).cpu().pin_memory()
+    hout = torch.full((n_local + 1,), -77, dtype=torch.int32).pin_memory()
+    for rep in range(2):
+        run(hin, hout)
+        ok = ok and bool(torch.equal(hout[:n_local], sh.block_cyclic_take(ref[:n_g], rank, world, block).cpu()))
+        ok = ok and int(hout[n_local]) == (int(ref[n_g]) if rank == owner else -77)
+    ctx.sync()
     peer2.status()
     peer.status()
     flag = torch.tensor([int(ok)], device="cuda")

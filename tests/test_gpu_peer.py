@@ -92,6 +92,28 @@ def test_block_chained_scan_of_eight_byte_values_and_floats(accb, ctx, P, torch_
     peer.destroy()
 
 
+@pytest.mark.parametrize("n,tiles_per_block,per", [(50 * TILE + 77, 2, 3), (7 * TILE, 1, 1), (33 * TILE, 4, 100)])
+def test_scan_launched_piece_by_piece_from_host_arrays(accb, ctx, P, oracle, torch_cuda, rng, n, tiles_per_block, per):
+    """PeerScanFromHost with a world of one: pinned host arrays in and out, the scan launched in pieces of `per`
+    blocks that find the records of the pieces before them; uploads, launches and downloads overlap."""
+    t = torch_cuda
+    sh = __import__("importlib").import_module("accelerate-cuda_b200.sharded")
+    block = tiles_per_block * TILE
+    _, _, scratch = accb.scan_layout(1, 0, n, block)
+    peer = accb.Peer(ctx, 0, 1, scratch, lambda b: [b])
+    run = sh.PeerScanFromHost(ctx, peer, P.SCAN_ADD_I32, n, block, t.int32, np.int32(9), blocks_per_piece=per)
+    for _ in range(2):
+        x = rng.integers(-9, 10, n).astype(np.int32)
+        hin = t.from_numpy(x).pin_memory()
+        hout = t.full((n + 1,), -1, dtype=t.int32).pin_memory()
+        run(hin, hout)
+        assert np.array_equal(hout.numpy(), oracle.scanl_i32(x, 9))
+    ctx.sync()
+    with pytest.raises(accb.AccbError):  # a piece out of order
+        peer.scan(P.SCAN_ADD_I32, [run.x], n, run.out, seed=np.int32(9), block_elems=block, first_block=5, blocks=1)
+    peer.destroy()
+
+
 def test_block_chained_scan_of_nothing(accb, ctx, P, torch_cuda):
     t = torch_cuda
     peer = accb.Peer(ctx, 0, 1, 4096, lambda b: [b])

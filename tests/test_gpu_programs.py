@@ -175,3 +175,136 @@ def test_program_as_one_cuda_graph_replays_on_new_contents(accb, ctx, torch_cuda
     with pytest.raises(accb.AccbError):
         f.run_device([w], stream=None, graph=True)  # the default stream cannot be captured
     f.destroy()
+
+
+# ------------------------------------------------------------- streamed host runs
+_D = "static __device__ __forceinline__"
+
+
+def _index_specs(accb):
+    KS = accb.KernelSpec
+    add_index = KS("map", "AddIndex", f"""
+struct AddIndex {{
+    using In = accb::types<int>;
+    using Out = accb::types<int>;
+    {_D} void apply(const accb::Env &, long long i, int x, int &o) {{ o = x + (int)(i % 1000003); }}
+}};
+""")
+    weighted = KS("fold_all", "IndexWeighted", f"""
+struct IndexWeighted : accb::Fold<int> {{
+    using In = accb::types<int>;
+    {_D} int get(const accb::Env &, long long i, int x) {{ return x * (int)(i % 7); }}
+    {_D} int combine(int a, int b) {{ return (int)((unsigned)a + (unsigned)b); }}
+}};
+""")
+    # not commutative: affine maps x -> a x + b composed left to right, packed into one 64-bit value
+    affine = KS("fold_all", "Affine", f"""
+struct Affine : accb::Fold<long long> {{
+    using In = accb::types<int>;
+    {_D} long long get(const accb::Env &, long long, int x) {{
+        return ((long long)(unsigned)(2 * (x & 1) + 1) << 32) | (unsigned)(x & 0xffff); }}
+    {_D} long long combine(long long f, long long g) {{ /* first f, then g */
+        const unsigned fa = (unsigned)(f >> 32), fb = (unsigned)f, ga = (unsigned)(g >> 32), gb = (unsigned)g;
+        return ((long long)(unsigned)(ga * fa) << 32) | (unsigned)(ga * fb + gb); }}
+}};
+""")
+    scatter = KS("permute", "IndexScatter", f"""
+struct IndexScatter : accb::Permute<int, accb::Atomic::Add> {{
+    using In = accb::types<int>;
+    {_D} long long index(const accb::Env &, long long i, int) {{ return i % 977; }}
+    {_D} int get(const accb::Env &, long long i, int x) {{ return x + (int)(i & 3); }}
+    {_D} int combine(int x, int y) {{ return (int)((unsigned)x + (unsigned)y); }}
+}};
+""")
+    return add_index, weighted, affine, scatter
+
+
+def _both_ways(accb, ctx, build, types, inputs, piece):
+    """The same program run whole (the reference's upload / run / download) and in pieces of `piece` elements."""
+    f = accb.run1With(ctx, build, *types)
+    whole = f.stream_chunk(0)(*inputs)
+    pieces = f.stream_chunk(piece)(*inputs)
+    f.destroy()
+    return whole, pieces
+
+
+@pytest.mark.parametrize("n,piece", [(100003, 4096), (65536, 16384), (1 << 20, 100000), (33, 16)])
+def test_streamed_runs_give_the_results_of_whole_runs(accb, P, ctx, oracle, workloads, rng, n, piece):
+    """Maps, folds, the three left scans and permutes on host arrays, cut into many small pieces: bit-identical to
+    the run that uploads everything first for integers, and the functor sees the same element indices."""
+    add_index, weighted, affine, scatter = _index_specs(accb)
+    i32 = accb.ArrayType(1, np.int32)
+    x = rng.integers(-100, 100, n).astype(np.int32)
+    y = rng.integers(-100, 100, n).astype(np.int32)
+    # map with the element index; zipWith of two streamed inputs
+    w, s = _both_ways(accb, ctx, lambda a: accb.map_(add_index, [a], i32), [i32], [x], piece)
+    assert np.array_equal(w, s) and np.array_equal(w, x + (np.arange(n) % 1000003).astype(np.int32))
+    f32 = accb.ArrayType(1, np.float32)
+    xf, yf = x.astype(np.float32) / 7, y.astype(np.float32) / 3
+    w, s = _both_ways(accb, ctx, lambda a, b: accb.map_(P.SAXPY, [a, b], f32, scalars=np.float32(2.5)), [f32, f32], [xf, yf], piece)
+    assert np.array_equal(w, s) and np.allclose(s, np.float32(2.5) * xf + yf, rtol=1e-6, atol=1e-4)
+    # foldAll: index-dependent, with a seed; fold1 (no seed); a combiner that does not commute
+    w, s = _both_ways(accb, ctx, lambda a: accb.fold(weighted, [a], np.int32, seed=np.int32(11), all=True), [i32], [x], piece)
+    assert int(w) == int(s) == int(np.int32((x.astype(np.int64) * (np.arange(n) % 7)).sum() + 11))
+    w, s = _both_ways(accb, ctx, lambda a: accb.fold(P.MAX_I32, [a], np.int32, all=True), [i32], [x], piece)
+    assert int(w) == int(s) == int(x.max())
+    w, s = _both_ways(accb, ctx, lambda a: accb.fold(affine, [a], np.int64, seed=np.int64(1 << 32), all=True), [i32], [x], piece)
+    assert int(w) == int(s)
+    # scans
+    for kind, ref in ((accb.SCAN_EXCLUSIVE, oracle.scanl_i32(x, 5)), (accb.SCAN_INCLUSIVE, oracle.scanl1_i32(x))):
+        seed = None if kind == accb.SCAN_INCLUSIVE else np.int32(5)
+        w, s = _both_ways(accb, ctx, lambda a: accb.scan(P.SCAN_ADD_I32, [a], np.int32, kind=kind, seed=seed), [i32], [x], piece)
+        assert np.array_equal(w, ref) and np.array_equal(s, ref)
+    w, s = _both_ways(accb, ctx, lambda a: accb.scan(P.SCAN_ADD_I32, [a], np.int32, kind=accb.SCAN_PRIME, seed=np.int32(-2)),
+                      [i32], [x], piece)
+    body, total = oracle.scanl_prime_i32(x, -2)
+    assert np.array_equal(s[0], body) and int(s[1]) == total and np.array_equal(w[0], body) and int(w[1]) == total
+    # permute: index-dependent scatter onto defaults that are uploaded once
+    d = rng.integers(-5, 5, 977).astype(np.int32)
+    w, s = _both_ways(accb, ctx, lambda a, dfl: accb.permute(scatter, [a], dfl), [i32, i32], [x, d], piece)
+    ref = d.astype(np.int64).copy()
+    np.add.at(ref, np.arange(n) % 977, x.astype(np.int64) + (np.arange(n) & 3))
+    assert np.array_equal(w, s) and np.array_equal(s, ref.astype(np.int32))
+    # a chain: the intermediate array never leaves the device
+    w, s = _both_ways(accb, ctx, lambda a: accb.fold(weighted, [accb.map_(add_index, [a], i32)], np.int32, seed=np.int32(0), all=True),
+                      [i32], [x], piece)
+    assert int(w) == int(s)
+
+
+def test_streamed_row_folds_and_tuple_maps(accb, P, ctx, oracle, workloads, rng):
+    W = workloads
+    m = rng.uniform(-1, 1, (4099, 260)).astype(np.float32)
+    mt = accb.ArrayType(2, np.float32)
+    w, s = _both_ways(accb, ctx, lambda a: accb.fold(P.ROWSUM, [a], np.float32, seed=np.float32(0)), [mt], [m], 260 * 64)
+    ref = oracle.fold_rows_f32(m)
+    assert s.shape == (4099,) and np.array_equal(w, s) and np.all(np.abs(s - ref) <= 1e-5 * np.abs(ref) + 1e-6)
+    n = 70001
+    opts = tuple(W.uniform_f32(W.SEED, st, n, lo, hi) for st, lo, hi in ((W.S_SPOT, 5, 30), (W.S_STRIKE, 1, 100), (W.S_YEARS, 0.25, 10)))
+    w, s = _both_ways(accb, ctx, lambda o: accb.map_(P.BLACKSCHOLES, [o], accb.ArrayType(1, [np.float32, np.float32])),
+                      [accb.ArrayType(1, [np.float32] * 3)], [opts], 8192)
+    assert np.array_equal(w[0], s[0]) and np.array_equal(w[1], s[1])
+    rc, _ = oracle.blackscholes(*opts)
+    assert np.all(np.abs(s[0] - rc) <= 1e-5 * np.abs(rc) + 2e-5)
+    # the dot product: float results of the two ways differ by the rounding of the carry between pieces only
+    xs, ys = rng.uniform(-1, 1, 1 << 18).astype(np.float32), rng.uniform(-1, 1, 1 << 18).astype(np.float32)
+    v = accb.ArrayType(1, np.float32)
+    w, s = _both_ways(accb, ctx, lambda a, b: accb.fold(P.DOT, [a, b], np.float32, seed=np.float32(0), all=True), [v, v], [xs, ys], 1 << 14)
+    ref = oracle.dot_f32(xs, ys)
+    assert abs(float(w) - ref) <= 1e-5 * abs(ref) + 1e-5 and abs(float(s) - ref) <= 1e-5 * abs(ref) + 1e-5
+
+
+def test_programs_that_do_not_fit_run_whole(accb, P, ctx, oracle, workloads, rng):
+    """A stencil needs its neighbours' rows and a right scan starts at the far end: such programs are not cut into
+    pieces, whatever the piece size, and give the same results as before."""
+    W = workloads
+    g = rng.uniform(0, 1, (512, 260)).astype(np.float32)
+    f = accb.run1With(ctx, lambda a: accb.stencil(P.BLUR, a, boundary="clamp", iters=3), accb.ArrayType(2, np.float32))
+    r = f.stream_chunk(4096)(g)
+    ref = oracle.stencil2d_iter(g, W.BLUR_WEIGHTS, 3, "clamp")
+    assert np.all(np.abs(r - ref) <= 1e-5 * np.abs(ref) + 1e-6)
+    f.destroy()
+    x = rng.integers(-9, 9, 100003).astype(np.int32)
+    f = accb.run1With(ctx, lambda a: accb.scan(P.SCAN_ADD_I32, [a], np.int32, direction=accb.SCAN_RIGHT, seed=np.int32(1)),
+                      accb.ArrayType(1, np.int32))
+    assert np.array_equal(f.stream_chunk(4096)(x), oracle.scanr_i32(x, 1))
+    f.destroy()
