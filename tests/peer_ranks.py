@@ -66,7 +66,8 @@ def main():
     P = importlib.import_module("accelerate-cuda_b200.programs")
     tile = ctx.scan_tile(P.SCAN_ADD_I32)
     cases = ((world * 64 * tile + 12345, 4), (world * 8 * tile, 2), (3 * tile + 5, 1), (5, 1), (world * 300 * tile, 32))
-    scratch_max = max(accb.scan_layout(world, rank, n_g, tpb * tile)[2] for n_g, tpb in cases)
+    host_case = (world * 40 * tile + 999, 2)  # scanned from host arrays further down
+    scratch_max = max(accb.scan_layout(world, rank, n_g, tpb * tile)[2] for n_g, tpb in cases + (host_case,))
     peer2 = sh.peer_buffer(ctx, scratch_max)
     for n_g, tpb in cases:
         block = tpb * tile
@@ -89,7 +90,7 @@ def main():
             ok = ok and bool(torch.equal(out[:n_local], sh.block_cyclic_take(ref[1:] - 3, rank, world, block)))
             ok = ok and int(out[n_local]) == -77
     # the same from pinned host arrays, the scan launched in pieces that overlap with the copies
-    n_g, block = world * 40 * tile + 999, 2 * tile
+    n_g, block = host_case[0], host_case[1] * tile
     n_local, owner, _ = accb.scan_layout(world, rank, n_g, block)
     same = torch.Generator(device="cuda").manual_seed(777)
     whole = torch.randint(-9, 10, (n_g,), generator=same, device="cuda", dtype=torch.int32)
