@@ -102,6 +102,7 @@ def lib() -> C.CDLL:
             "accb_insert_unmanaged": [vp, u64, vp, sz],
             "accb_with_ptr": [vp, u64, C.POINTER(vp), C.POINTER(sz)],
             "accb_release": [vp, u64],
+            "accb_release_after": [vp, u64, vp],
             "accb_peek": [vp, u64, sz, vp, sz, vp],
             "accb_poke": [vp, u64, sz, vp, sz, vp],
             "accb_copy": [vp, u64, u64, sz, vp],

@@ -119,6 +119,8 @@ struct CudaAllocator : DeviceAllocator {
     void *alloc(size_t bytes) override;
     void release(void *p) override;
     bool copy_to_host(void *host, const void *dev, size_t bytes) override;
+    void wait_token(void *token) override;    /* tokens are CUDA events */
+    void release_token(void *token) override;
 };
 
 }  // namespace accb_rt

@@ -156,6 +156,20 @@ bool CudaAllocator::copy_to_host(void *host, const void *dev, size_t bytes) {
     return cudaMemcpy(host, dev, bytes, cudaMemcpyDeviceToHost) == cudaSuccess;
 }
 
+void CudaAllocator::wait_token(void *token) { cudaEventSynchronize(static_cast<cudaEvent_t>(token)); }
+void CudaAllocator::release_token(void *token) { cudaEventDestroy(static_cast<cudaEvent_t>(token)); }
+
+/* an event recorded behind everything enqueued on `s` so far, as a memory-table waypoint */
+static void *waypoint_after(cudaStream_t s) {
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventRecord(ev, s) != cudaSuccess) {
+        cudaEventDestroy(ev);
+        return nullptr;
+    }
+    return ev;
+}
+
 StreamScratch *scratch_for(accb_context *ctx, cudaStream_t s) {
     auto it = ctx->scratch.find(s);
     if (it != ctx->scratch.end()) return &it->second;
@@ -390,6 +404,8 @@ int accb_use(accb_context *ctx, uint64_t key, const void *host, size_t bytes, ac
         int st = check_cuda(ctx, cudaMemcpyAsync(e->dptr, host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream),
                             "upload");
         if (st != ACCB_OK) return st;
+        /* the copy is asynchronous: eviction must not free the destination under it */
+        if (void *w = waypoint_after((cudaStream_t)stream)) ctx->mem.set_waypoint(key, w);
     }
     *dptr = e->dptr;
     return ACCB_OK;
@@ -419,6 +435,17 @@ int accb_with_ptr(accb_context *ctx, uint64_t key, void **dptr, size_t *bytes) {
 
 int accb_release(accb_context *ctx, uint64_t key) {
     LOCK(ctx);
+    if (!ctx->mem.unpin(key)) return fail(ctx, ACCB_ENOTFOUND, "key %llx is not pinned", (unsigned long long)key);
+    return ACCB_OK;
+}
+
+int accb_release_after(accb_context *ctx, uint64_t key, accb_stream stream) {
+    LOCK(ctx);
+    if (!ctx->mem.peek(key)) return fail(ctx, ACCB_ENOTFOUND, "unknown key %llx", (unsigned long long)key);
+    /* the waypoint first: once unpinned the entry may be chosen for eviction at any time */
+    void *w = waypoint_after((cudaStream_t)stream);
+    if (!w) return fail(ctx, ACCB_ECUDA, "cannot record an event on the stream");
+    ctx->mem.set_waypoint(key, w);
     if (!ctx->mem.unpin(key)) return fail(ctx, ACCB_ENOTFOUND, "key %llx is not pinned", (unsigned long long)key);
     return ACCB_OK;
 }

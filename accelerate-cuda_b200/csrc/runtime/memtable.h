@@ -9,7 +9,10 @@
  * bytes and are at least one element (Remote.hs:60-80, Prim.hs:167,186); a
  * failed allocation is not an error but the signal to evict and retry
  * (Remote.hs:63-67); entries in use by device work are pinned and cannot be
- * evicted (withRemote, Remote.hs:113-134); memory registered with
+ * evicted, and an entry remembers the last asynchronous work that used it
+ * (a "waypoint": an event recorded behind that work), which eviction and
+ * removal wait for before the memory is written back or freed (withRemote,
+ * Remote.hs:113-134); memory registered with
  * insertUnmanaged is never freed by the table (Remote.hs:168-184).
  *
  * The table is header-only and talks to the device through DeviceAllocator,
@@ -28,6 +31,9 @@ struct DeviceAllocator {
     virtual void *alloc(size_t bytes) = 0; /* nullptr when out of memory */
     virtual void release(void *p) = 0;
     virtual bool copy_to_host(void *host, const void *dev, size_t bytes) = 0;
+    /* waypoints: opaque tokens that stand for asynchronous work still using an entry */
+    virtual void wait_token(void *token) { (void)token; }    /* returns once that work has finished */
+    virtual void release_token(void *token) { (void)token; } /* the token is not needed any more */
 };
 
 class MemTable {
@@ -41,6 +47,7 @@ public:
         bool resident = true;    /* false: evicted, data lives in `host` */
         int pins = 0;
         uint64_t tick = 0;       /* last use */
+        void *waypoint = nullptr; /* token of the last asynchronous work that used the entry, or null */
     };
 
     static constexpr size_t kGranule = 1024;
@@ -133,6 +140,20 @@ public:
         return true;
     }
 
+    /* The entry was handed to asynchronous work that `token` stands for: the table takes the token over and waits
+     * for it before it writes the entry back, frees it or forgets it.  A newer token replaces an older one (work
+     * on one stream is ordered; callers that use several streams pass the token of a join). */
+    bool set_waypoint(uint64_t key, void *token) {
+        auto it = map_.find(key);
+        if (it == map_.end()) {
+            alloc_->release_token(token);
+            return false;
+        }
+        if (it->second.waypoint) alloc_->release_token(it->second.waypoint);
+        it->second.waypoint = token;
+        return true;
+    }
+
     bool remove(uint64_t key) {
         auto it = map_.find(key);
         if (it == map_.end()) return false;
@@ -159,7 +180,15 @@ public:
     size_t evictions() const { return evictions_; }
 
 private:
+    void settle(Entry &e) { /* no asynchronous work uses the entry after this */
+        if (!e.waypoint) return;
+        alloc_->wait_token(e.waypoint);
+        alloc_->release_token(e.waypoint);
+        e.waypoint = nullptr;
+    }
+
     void drop(Entry &e) {
+        settle(e);
         if (e.managed && e.resident && e.dptr) {
             alloc_->release(e.dptr);
             resident_bytes_ -= e.alloc_bytes;
@@ -176,6 +205,7 @@ private:
             if (!victim || e.tick < victim->tick) victim = &e;
         }
         if (!victim) return false;
+        settle(*victim); /* work enqueued earlier may still read or write it (Remote.hs:127-134) */
         if (!alloc_->copy_to_host(victim->host, victim->dptr, victim->bytes)) return false;
         alloc_->release(victim->dptr);
         resident_bytes_ -= victim->alloc_bytes;

@@ -110,6 +110,10 @@ ACCB_API int accb_insert_unmanaged(accb_context *ctx, uint64_t key, void *dptr, 
 /* pin / unpin an entry while device work uses it (withRemote, Remote.hs:113-134) */
 ACCB_API int accb_with_ptr(accb_context *ctx, uint64_t key, void **dptr, size_t *bytes);
 ACCB_API int accb_release(accb_context *ctx, uint64_t key);
+/* unpin, and remember that work enqueued on `stream` so far still uses the entry: the table waits for that work
+ * before it writes the entry back to the host, frees it or forgets it -- the waypoint event that withRemote
+ * attaches to every use (Remote.hs:127-134).  accb_release alone is for callers that have synchronised. */
+ACCB_API int accb_release_after(accb_context *ctx, uint64_t key, accb_stream stream);
 ACCB_API int accb_peek(accb_context *ctx, uint64_t key, size_t offset, void *host, size_t bytes,
                        accb_stream stream); /* device -> host (peekArrayAsync) */
 ACCB_API int accb_poke(accb_context *ctx, uint64_t key, size_t offset, const void *host, size_t bytes,

@@ -32,8 +32,16 @@ struct FakeDevice : DeviceAllocator {
     bool copy_to_host(void *host, const void *dev, size_t bytes) override {
         memcpy(host, dev, bytes);
         ++writebacks;
+        log.push_back('c');
         return true;
     }
+    // waypoints: a token is a pointer to an int that counts how often it was waited for
+    std::vector<char> log;  // 'w' wait, 'r' token released, 'c' copy to host
+    void wait_token(void *token) override {
+        ++*static_cast<int *>(token);
+        log.push_back('w');
+    }
+    void release_token(void *) override { log.push_back('r'); }
 };
 
 #define CHECK(c)                                                        \
@@ -89,6 +97,21 @@ int main() {
         CHECK(t.remove(10));
         CHECK(t.insert(30, 2000, host[0].data()) && t.insert(31, 2000, host[1].data()));
         CHECK(t.reclaim() == 2 && t.resident_bytes() == 0);
+        // an entry still used by asynchronous work carries a waypoint: eviction waits for it BEFORE the
+        // write-back (Remote.hs:127-134); a newer waypoint replaces the older one; removal waits as well
+        CHECK(t.remove(30) && t.remove(31));
+        int waits_a = 0, waits_b = 0, waits_c = 0;
+        CHECK(t.insert(40, 2000, host[0].data()) && t.insert(41, 2000, host[1].data()));
+        CHECK(t.set_waypoint(40, &waits_a));
+        CHECK(t.set_waypoint(40, &waits_b));  // releases token a unwaited
+        dev.log.clear();
+        CHECK(t.find(41));                    // 40 is the LRU entry
+        CHECK(t.insert(42, 8000, nullptr));   // needs 40's memory
+        CHECK(waits_a == 0 && waits_b == 1 && !t.peek(40)->resident);
+        CHECK(dev.log.size() >= 3 && dev.log[0] == 'w' && dev.log[1] == 'r' && dev.log[2] == 'c');
+        CHECK(t.set_waypoint(41, &waits_c) && t.remove(41) && waits_c == 1);
+        CHECK(!t.set_waypoint(99, &waits_c));  // unknown key: the token is handed back
+        CHECK(t.remove(42) && t.remove(40));
     }
     CHECK(dev.used == 0 && dev.live.empty());  // the destructor released what was left
     printf("OK\n");

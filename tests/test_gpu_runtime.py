@@ -121,6 +121,35 @@ def test_memory_table_on_the_device(accb, torch_cuda):
     ctx.destroy()
 
 
+def test_eviction_waits_for_work_that_still_uses_an_array(accb, P, torch_cuda):
+    """An array released while a kernel on another stream still writes it: accb_release_after leaves a waypoint
+    behind that kernel, and the write-back of an eviction waits for it (Array/Remote.hs:113-134), so the host copy
+    receives the finished result."""
+    t = torch_cuda
+    L = accb.lib()
+    ctx = accb.Context(0)
+    h = ctx.handle
+    n = 1 << 24
+    host = np.zeros(n, np.int32)
+    d, sz = C.c_void_p(), C.c_size_t()
+    assert L.accb_use(h, 7, host.ctypes.data_as(C.c_void_p), host.nbytes, None, C.byref(d)) == 0
+    assert L.accb_with_ptr(h, 7, C.byref(d), C.byref(sz)) == 0
+    stream = t.cuda.Stream()
+    out = t.as_tensor(accb.DeviceArray(d.value, (n,), np.int32), device="cuda")
+    x = t.ones(n, dtype=t.int32, device="cuda")
+    t.cuda.synchronize()
+    for _ in range(20):  # enough queued work that the last launch is still pending when the eviction starts
+        ctx.scan(P.SCAN_ADD_I32, [x], n - 1, out, seed=np.int32(1), stream=stream.cuda_stream)
+    assert L.accb_release_after(h, 7, C.c_void_p(stream.cuda_stream)) == 0
+    assert L.accb_reclaim(h) == 0  # writes key 7 back to `host` and frees it
+    ev, nn, b = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    assert L.accb_memory_stats(h, C.byref(nn), C.byref(b), C.byref(ev)) == 0 and ev.value == 1
+    assert np.array_equal(host, np.arange(1, n + 1, dtype=np.int32))
+    assert L.accb_release_after(h, 12345, None) == accb.ENOTFOUND
+    t.cuda.synchronize()
+    ctx.destroy()
+
+
 def test_streams_and_events(accb, P, torch_cuda):
     """A producer on one stream, a consumer on another, joined by an event (Execute/Stream.hs:66-74,
     Execute/Event.hs:112-115); streams and events are recycled through the reservoirs."""
