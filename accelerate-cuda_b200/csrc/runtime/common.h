@@ -62,7 +62,7 @@ struct SkeletonDesc {
     int id;
 };
 enum SkeletonId { SK_MAP = 1, SK_FOLD_ALL, SK_FOLD_DIM, SK_FOLD_SEG, SK_SCAN, SK_PERMUTE, SK_PERMUTE_SMEM,
-                  SK_STENCIL, SK_STENCIL2 };
+                  SK_STENCIL, SK_STENCIL2, SK_STENCIL3 };
 const SkeletonDesc *find_skeleton(const char *name);
 
 struct CompileResult {

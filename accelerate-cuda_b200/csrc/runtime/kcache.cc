@@ -45,6 +45,7 @@ static const SkeletonDesc kSkeletons[] = {
     {"permute_smem", "permute.cuh", "ACCB_INSTANTIATE_PERMUTE_SMEM", SK_PERMUTE_SMEM},
     {"stencil", "stencil.cuh", "ACCB_INSTANTIATE_STENCIL", SK_STENCIL},
     {"stencil2", "stencil.cuh", "ACCB_INSTANTIATE_STENCIL2", SK_STENCIL2},
+    {"stencil3", "stencil3.cuh", "ACCB_INSTANTIATE_STENCIL3", SK_STENCIL3}, /* stencil over a rank-3 array */
 };
 
 const SkeletonDesc *find_skeleton(const char *name) {

@@ -771,10 +771,53 @@ int accb_permute_at(accb_context *ctx, accb_kernel *k, accb_stream stream, const
 }
 
 /* -------------------------------------------------------------- stencil */
+/* rank 3: a block owns a column of the cube and marches along z (skeletons/stencil3.cuh) */
+static int stencil3_launch(accb_context *ctx, accb_kernel *k, cudaStream_t s, const accb_array *src, int boundary,
+                           const void *constant, size_t constant_bytes, const accb_array *out) {
+    if (k->skeleton != SK_STENCIL3) return fail(ctx, ACCB_EINVAL, "kernel %s was not built for the stencil3 skeleton (rank-3 arrays)", k->key.c_str());
+    if (!src || src->rank != 3 || src->ncomp != 1 || !src->ptr[0]) return fail(ctx, ACCB_EINVAL, "stencil source: rank / component mismatch");
+    if (boundary < ACCB_CLAMP || boundary > ACCB_CONSTANT) return fail(ctx, ACCB_EINVAL, "unknown boundary %d", boundary);
+    if (boundary == ACCB_CONSTANT && !constant) return fail(ctx, ACCB_EINVAL, "Constant boundary needs a value");
+    for (int d = 0; d < 3; ++d)
+        if (src->shape[d] != out->shape[d]) return fail(ctx, ACCB_EINVAL, "a stencil's result has the shape of its source");
+    accb_kparams p;
+    memset(&p, 0, sizeof p);
+    p.flags |= ACCB_F_VEC;
+    p.in[0] = src->ptr[0];
+    if (!aligned16(src->ptr[0])) p.flags &= ~ACCB_F_VEC;
+    TRY(fill_out(ctx, p, out));
+    if (constant) TRY(fill_scalars(ctx, p, constant, constant_bytes));
+    const long long W = out->shape[0], H = out->shape[1], D = out->shape[2];
+    p.n = W * H * D;
+    if (p.n == 0) return ACCB_OK;
+    Prep pr;
+    TRY(prepare(ctx, k, "stencil3", 0, &pr));
+    if (pr.meta.v[2] != 4) return fail(ctx, ACCB_EINVAL, "the rank-3 stencil skeleton takes 4-byte elements");
+    const size_t smem = (size_t)pr.meta.v[6];
+    TRY(occupancy(ctx, pr.fn, pr.block, smem, &pr.per_sm));
+    const long long columns = ceil_div(W, pr.meta.v[4]) * ceil_div(H, pr.meta.v[3]);
+    const long long resident = (long long)ctx->sm_count * pr.per_sm;
+    /* cut z so that there are a few times more tasks than resident blocks, but keep runs long: every run
+     * re-reads 2*RZ planes of its neighbours */
+    const long long min_run = std::max(8LL, 8LL * pr.meta.v[5]);
+    long long zchunks = std::max(1LL, std::min(ceil_div(D, min_run), ceil_div(4 * resident, columns)));
+    const long long zrun = ceil_div(D, zchunks);
+    zchunks = ceil_div(D, zrun);
+    p.ip[0] = D;
+    p.ip[1] = H;
+    p.ip[2] = W;
+    p.ip[3] = zrun;
+    p.ip[4] = boundary;
+    const int grid = (int)std::min(columns * zchunks, resident);
+    return launch(ctx, pr.fn, "stencil3", grid, pr.block, smem, s, p);
+}
+
 static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, cudaStream_t s,
                           const accb_array *const *src, int nsrc, int boundary, const void *constant,
                           size_t constant_bytes, const accb_array *out) {
-    if (!out || out->rank < 1 || out->rank > 2) return fail(ctx, ACCB_EINVAL, "stencils support rank 1 and 2");
+    if (out && out->rank == 3 && nsrc == 1) return stencil3_launch(ctx, k, s, src[0], boundary, constant, constant_bytes, out);
+    if (k->skeleton == SK_STENCIL3) return fail(ctx, ACCB_EINVAL, "kernel %s was built for rank-3 arrays", k->key.c_str());
+    if (!out || out->rank < 1 || out->rank > 2) return fail(ctx, ACCB_EINVAL, "stencil2 supports rank 1 and 2, stencil rank 1 to 3");
     if (boundary < ACCB_CLAMP || boundary > ACCB_CONSTANT) return fail(ctx, ACCB_EINVAL, "unknown boundary %d", boundary);
     if (boundary == ACCB_CONSTANT && !constant) return fail(ctx, ACCB_EINVAL, "Constant boundary needs a value");
     accb_kparams p;
@@ -846,7 +889,7 @@ static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, 
 int accb_stencil(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *src, int boundary,
                  const void *constant, size_t constant_bytes, const accb_array *out) {
     LOCK(ctx);
-    TRY(check_skeleton(ctx, k, {SK_STENCIL}, "stencil"));
+    TRY(check_skeleton(ctx, k, {SK_STENCIL, SK_STENCIL3}, "stencil"));
     const accb_array *srcs[1] = {src};
     return stencil_launch(ctx, k, "stencil", (cudaStream_t)stream, srcs, 1, boundary, constant, constant_bytes, out);
 }
@@ -864,7 +907,7 @@ int accb_stencil_iterate(accb_context *ctx, accb_kernel *k, accb_stream stream, 
                          const accb_array *b, int iters, int boundary, const void *constant, size_t constant_bytes,
                          int *result_in_b) {
     LOCK(ctx);
-    TRY(check_skeleton(ctx, k, {SK_STENCIL}, "stencil"));
+    TRY(check_skeleton(ctx, k, {SK_STENCIL, SK_STENCIL3}, "stencil"));
     if (!a || !b || iters < 0) return fail(ctx, ACCB_EINVAL, "bad argument");
     const accb_array *cur = a, *nxt = b;
     for (int i = 0; i < iters; ++i) {

@@ -1,0 +1,204 @@
+/*
+ * stencil3.cuh -- stencil over rank-3 arrays (cubes) with Clamp / Mirror /
+ * Wrap / Constant boundaries.
+ *
+ * The reference's mkStencil is rank-polymorphic
+ * (Data/Array/Accelerate/CUDA/CodeGen/Stencil.hs:55-114): whatever the rank,
+ * every output point gathers all its taps from global memory through
+ * stencilAccess (CodeGen/Stencil/Extra.hs:53-128), i.e. 27 loads with three
+ * boundary tests each for a 3x3x3 neighbourhood.  Here a block owns a column
+ * of the cube -- TY x TX points in (y, x), a run of planes in z -- and marches
+ * along z: the 2*RZ+1 input planes a z-step needs sit in a ring of tiles in
+ * shared memory, every z-step brings in ONE new plane tile (with its halo in
+ * y and x) and retires the oldest, so an input element is requested from
+ * memory once per block that needs it instead of once per tap.  The threads
+ * of a warp read and write 512 contiguous bytes per row; a thread computes 4
+ * adjacent x per row from 16-byte shared-memory reads.
+ *
+ * Boundary semantics as for the lower ranks (Extra.hs:200-226): every
+ * coordinate is mapped on its own; with Constant the whole tap is the constant
+ * as soon as one coordinate is outside (:122-128,191-196).  The mapping is
+ * done once, when a plane tile is filled, not per tap.
+ *
+ * Functor contract (derive from accb::Stencil3<Tin, Tout, RZ, RY, RX>; 4-byte
+ * Tin):
+ *   static Tout apply(env, const Tin (&t)[2*RZ+1][2*RY+1][2*RX+1]);
+ * with t[dz][dy][dx] the element at offset (dz-RZ, dy-RY, dx-RX), the order
+ * in which Accelerate's stencil patterns nest (outermost dimension first).
+ *
+ *   in[0] source, out[0] result; ip[0] D, ip[1] H, ip[2] W (planes, rows,
+ *   columns); ip[3] planes per block; ip[4] boundary; scalars[0..] the constant.
+ */
+#pragma once
+#include "../cubits/accb_vec.cuh"
+#include "../cubits/accb_warp.cuh"
+#include "stencil.cuh"
+
+#ifndef ACCB_STENCIL3_CTA
+#define ACCB_STENCIL3_CTA 256
+#endif
+#ifndef ACCB_STENCIL3_TY
+#define ACCB_STENCIL3_TY 16 /* rows of a block's column */
+#endif
+#define ACCB_STENCIL3_TX 128 /* columns of a block's column: one warp row */
+
+namespace accb {
+
+template <class Tin, class Tout, int RZ_, int RY_, int RX_>
+struct Stencil3 {
+    typedef Tin in_t;
+    typedef Tout out_t;
+    static constexpr int RZ = RZ_, RY = RY_, RX = RX_;
+};
+
+/* geometry of one plane tile in shared memory: TY + 2*RY rows of PITCH values; the TX centre columns start
+ * at value PAD (a multiple of 4, so that a thread's 4 columns are one aligned 16-byte read) */
+template <class Fn>
+struct Stencil3Tile {
+    static constexpr int TY = ACCB_STENCIL3_TY, TX = ACCB_STENCIL3_TX;
+    static constexpr int PAD = (Fn::RX + 3) / 4 * 4;
+    static constexpr int PITCH = TX + 2 * PAD;
+    static constexpr int ROWS = TY + 2 * Fn::RY;
+    static constexpr int PLANE = ROWS * PITCH;     /* values per plane tile */
+    static constexpr int RING = 2 * Fn::RZ + 1;    /* plane tiles resident */
+    static constexpr int BYTES = RING * PLANE * 4;
+};
+
+/* Fill one plane tile: input plane `z` (already mapped through the boundary, or -1: all constant), rows
+ * y0 - RY .. y0 + TY + RY - 1, columns x0 - PAD .. x0 + TX + PAD - 1 (only RX of the PAD columns are used). */
+template <class Fn, int CTA>
+__device__ __forceinline__ void stencil3_fill(typename Fn::in_t *tile, const typename Fn::in_t *src, int zz, int y0, int x0,
+                                              int H, int W, int mode, typename Fn::in_t cval, bool vec_ok) {
+    typedef typename Fn::in_t T;
+    typedef Stencil3Tile<Fn> G;
+    const T *plane = src + (long long)(zz < 0 ? 0 : zz) * H * W;
+    /* centre columns: 16-byte loads where the whole vector is inside the row and aligned */
+    constexpr int VPR = G::TX / 4; /* vectors per row */
+    for (int i = threadIdx.x; i < G::ROWS * VPR; i += CTA) {
+        const int r = i / VPR, v = i - r * VPR;
+        const int yy = bound_coord(y0 - Fn::RY + r, H, mode);
+        const int x = x0 + 4 * v;
+        T *dst = tile + r * G::PITCH + G::PAD + 4 * v;
+        if (zz >= 0 && yy >= 0 && vec_ok && x + 3 < W) {
+            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(plane + (long long)yy * W + x);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int xx = bound_coord(x + k, W, mode);
+                dst[k] = (zz < 0 || yy < 0 || xx < 0) ? cval : plane[(long long)yy * W + xx];
+            }
+        }
+    }
+    /* halo columns, RX on either side */
+    if constexpr (Fn::RX > 0) {
+        for (int i = threadIdx.x; i < G::ROWS * 2 * Fn::RX; i += CTA) {
+            const int r = i / (2 * Fn::RX), h = i - r * (2 * Fn::RX);
+            const int dx = h < Fn::RX ? h - Fn::RX : G::TX + (h - Fn::RX); /* relative to x0 */
+            const int yy = bound_coord(y0 - Fn::RY + r, H, mode);
+            const int xx = bound_coord(x0 + dx, W, mode);
+            tile[r * G::PITCH + G::PAD + dx] = (zz < 0 || yy < 0 || xx < 0) ? cval : plane[(long long)yy * W + xx];
+        }
+    }
+}
+
+template <class Fn, int CTA>
+__device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
+    typedef typename Fn::in_t T;
+    typedef typename Fn::out_t U;
+    typedef Stencil3Tile<Fn> G;
+    static_assert(sizeof(T) == 4, "the rank-3 stencil skeleton stages 4-byte elements");
+    static_assert(CTA == 256 && G::TX == 128, "eight warps, one row of 128 columns per warp and step");
+    constexpr int RZ = Fn::RZ, RY = Fn::RY, RX = Fn::RX;
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    T *ring = reinterpret_cast<T *>(s_raw);
+    const Env env(p);
+    const int D = (int)p.ip[0], H = (int)p.ip[1], W = (int)p.ip[2];
+    const int zrun = (int)p.ip[3], mode = (int)p.ip[4];
+    const T *src = static_cast<const T *>(p.in[0]);
+    U *out = static_cast<U *>(p.out[0]);
+    const T cval = mode == B_CONSTANT ? env.scalar<T>(0) : T();
+    const bool vec_ok = (p.flags & ACCB_F_VEC) != 0 && W % 4 == 0;
+
+    const int tiles_x = (W + G::TX - 1) / G::TX, tiles_y = (H + G::TY - 1) / G::TY;
+    const int zchunks = (D + zrun - 1) / zrun;
+    const long long ntask = (long long)tiles_x * tiles_y * zchunks;
+    const int lane = lane_id(), w = warp_id();
+
+    for (long long task = blockIdx.x; task < ntask; task += gridDim.x) {
+        /* x fastest, then y, then the z-chunk: blocks that run together share halo rows and planes in L2 */
+        const int tx = (int)(task % tiles_x);
+        const int ty = (int)((task / tiles_x) % tiles_y);
+        const int tz = (int)(task / ((long long)tiles_x * tiles_y));
+        const int x0 = tx * G::TX, y0 = ty * G::TY, z0 = tz * zrun;
+        const int z1 = min(D, z0 + zrun);
+        __syncthreads(); /* the previous task's last reads of the ring */
+        /* planes z0 - RZ .. z0 + RZ - 1 go into ring slots by (plane + RZ) mod RING */
+        for (int dz = -RZ; dz < RZ; ++dz) {
+            const int z = z0 + dz;
+            stencil3_fill<Fn, CTA>(ring + (((z + RZ) % G::RING + G::RING) % G::RING) * G::PLANE, src, bound_coord(z, D, mode), y0,
+                                   x0, H, W, mode, cval, vec_ok);
+        }
+        for (int z = z0; z < z1; ++z) {
+            const int zin = z + RZ;
+            stencil3_fill<Fn, CTA>(ring + (((zin + RZ) % G::RING + G::RING) % G::RING) * G::PLANE, src, bound_coord(zin, D, mode),
+                                   y0, x0, H, W, mode, cval, vec_ok);
+            __syncthreads();
+            /* warp w computes rows w, w + 8, ..: lane l the columns 4l .. 4l + 3 */
+            for (int r = w; r < G::TY; r += CTA / 32) {
+                const int y = y0 + r, x = x0 + 4 * lane;
+                if (y < H && x < W) {
+                    T win[2 * RZ + 1][2 * RY + 1][4 + 2 * RX];
+#pragma unroll
+                    for (int dz = 0; dz <= 2 * RZ; ++dz) {
+                        const T *pl = ring + (((z - RZ + dz + RZ) % G::RING + G::RING) % G::RING) * G::PLANE;
+#pragma unroll
+                        for (int dy = 0; dy <= 2 * RY; ++dy) {
+                            const T *row = pl + (r + dy) * G::PITCH + G::PAD + 4 * lane;
+                            const uint4 c = *reinterpret_cast<const uint4 *>(row);
+                            memcpy(&win[dz][dy][RX], &c, 16);
+#pragma unroll
+                            for (int h = 0; h < RX; ++h) {
+                                win[dz][dy][h] = row[h - RX];
+                                win[dz][dy][RX + 4 + h] = row[4 + h];
+                            }
+                        }
+                    }
+                    U o[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        T t[2 * RZ + 1][2 * RY + 1][2 * RX + 1];
+#pragma unroll
+                        for (int dz = 0; dz <= 2 * RZ; ++dz)
+#pragma unroll
+                            for (int dy = 0; dy <= 2 * RY; ++dy)
+#pragma unroll
+                                for (int dx = 0; dx <= 2 * RX; ++dx) t[dz][dy][dx] = win[dz][dy][k + dx];
+                        o[k] = Fn::apply(env, t);
+                    }
+                    U *dst = out + ((long long)z * H + y) * W + x;
+                    if (vec_ok && sizeof(U) == 4 && x + 3 < W) {
+                        uint4 q;
+                        memcpy(&q, o, 16);
+                        __stcs(reinterpret_cast<uint4 *>(dst), q);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            if (x + k < W) dst[k] = o[k];
+                    }
+                }
+            }
+            __syncthreads(); /* the oldest plane's slot is refilled next */
+        }
+    }
+}
+
+}  // namespace accb
+
+/* metadata: element bytes, tile rows, tile columns, -, dynamic shared memory, 2*RZ */
+#define ACCB_INSTANTIATE_STENCIL3(Fn)                                                          \
+    ACCB_META7(10, ACCB_STENCIL3_CTA, sizeof(Fn::in_t), ACCB_STENCIL3_TY, ACCB_STENCIL3_TX, 2 * Fn::RZ, \
+               accb::Stencil3Tile<Fn>::BYTES)                                                  \
+    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL3_CTA)                            \
+        stencil3(const __grid_constant__ accb_kparams p) {                                     \
+        accb::stencil3_body<Fn, ACCB_STENCIL3_CTA>(p);                                         \
+    }

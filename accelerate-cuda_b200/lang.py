@@ -28,8 +28,8 @@ when the program runs, as the reference evaluates shape expressions (Execute.hs:
 innermost dimension of matrices and the segmented ``scanl1Seg`` / ``scanr1Seg``, which the reference rejects
 (PrefixSum.hs:39-46), are the scan skeleton over (value, restart flag) pairs.
 
-Restrictions of this front end (not of the skeletons): ranks up to 3; the stencil skeleton serves vectors and matrices
-of one component (cubes and tuple elements fall back to a gathering ``generate``); seeds and fill values are constants; a ``zipWith`` of arrays of different shape is an error at run time
+Restrictions of this front end (not of the skeletons): ranks up to 3; the stencil skeletons serve arrays of one
+component (tuple elements fall back to a gathering ``generate``); seeds and fill values are constants; a ``zipWith`` of arrays of different shape is an error at run time
 instead of the intersection; no ``acond`` (branch in Python around compiled functions; ``awhile`` exists, see the
 end of this file).
 """
@@ -1581,6 +1581,27 @@ def _stencil_spec(f: Callable, narr: int, tin, tout_probe, pattern, kind: str):
     return KernelSpec("stencil" if narr == 1 else "stencil2", name, text.replace("@N@", name)), out[0].dt
 
 
+def _stencil3_spec(f: Callable, tin, pattern):
+    """The functor of the rank-3 stencil skeleton (csrc/skeletons/stencil3.cuh): t[dz][dy][dx]."""
+    wz, wy, wx = pattern
+
+    def go():
+        w = [[[Exp(tin[0], f"t[{z}][{y}][{x}]") for x in range(wx)] for y in range(wy)] for z in range(wz)]
+        _kenvs.append(_NoEnv())
+        try:
+            return _flat(f(w))
+        finally:
+            _kenvs.pop()
+    body, out = _trace(go)
+    if len(out) != 1:
+        raise NotImplementedError("stencils over tuples")
+    text = (f"struct @N@ : accb::Stencil3<{ctype(tin[0])}, {ctype(out[0].dt)}, {wz // 2}, {wy // 2}, {wx // 2}> {{\n"
+            f"    {_D} {ctype(out[0].dt)} apply(const accb::Env &, const {ctype(tin[0])} (&t)[{wz}][{wy}][{wx}]) {{\n"
+            f"        {body}\n        return {out[0].code};\n    }}\n}};\n")
+    name = _name("Stencil3", text)
+    return KernelSpec("stencil3", name, text.replace("@N@", name)), out[0].dt
+
+
 def _bound(i: Exp, n: Exp, mode: str) -> Exp:
     """One coordinate through the boundary function (Stencil/Extra.hs:200-226); Constant clamps, the caller
     replaces the value."""
@@ -1630,13 +1651,21 @@ def stencil(f: Callable, boundary, arr: Array, pattern=None, iterate: int = 1) -
     """``stencil f boundary arr``.  f receives the neighbourhood as nested lists, ``t[dy][dx]`` for a matrix
     (``t[dx]`` for a vector, ``t[dz][dy][dx]`` for a cube), centre in the middle; pattern = the extents of the
     neighbourhood, 3 per dimension by default.  boundary: "clamp", "mirror", "wrap" or ("constant", value).
-    iterate > 1 applies it repeatedly.  Vectors and matrices of one component go through the stencil skeleton
-    (tiles staged in shared memory); cubes and tuple elements gather, as every stencil of the reference does."""
+    iterate > 1 applies it repeatedly.  Vectors, matrices and cubes of one component go through the stencil
+    skeletons (tiles staged in shared memory); tuple elements gather, as every stencil of the reference does."""
     arr = compute(_as_array(arr))
     if arr.rank == 1 and isinstance(pattern, int):
         pattern = (1, pattern)
+    cube = (arr.rank == 3 and len(arr.dtypes) == 1 and np.dtype(arr.dtypes[0]).itemsize == 4 and
+            all(w % 2 == 1 and w <= 5 for w in (pattern or (3, 3, 3))))
+    if cube:  # the rank-3 skeleton: a block marches along z with the planes it needs in shared memory
+        spec, tout = _stencil3_spec(f, arr.dtypes, tuple(pattern or (3, 3, 3)))
+        mode, const = (boundary[0], np.asarray(boundary[1], dtype=arr.dtypes[0])[()]) if isinstance(boundary, tuple) else (boundary, None)
+        if np.dtype(tout).itemsize == 4 and (iterate <= 1 or tout == arr.dtypes[0]):
+            node = _be().stencil(spec, arr.node, out_dtype=[tout], boundary=mode, constant=const, iters=iterate)
+            return Array(arr.prog, [tout], node=node)
     if len(arr.dtypes) != 1 or arr.rank not in (1, 2) or (pattern is not None and pattern[-1] > 9):
-        # cubes, tuple elements, very wide neighbourhoods: the way the reference does every stencil -- each element
+        # tuple elements, 8-byte cubes, very wide neighbourhoods: the way the reference does every stencil -- each element
         # gathers its neighbourhood through the boundary function (CodeGen/Stencil.hs:55-114, Stencil/Extra.hs:191-226)
         out = arr
         for _ in range(max(1, iterate)):

@@ -307,6 +307,28 @@ struct Smooth1 : accb::Stencil<float, float, 0, 1> {{
 }};
 """)
 
+# rank 3: a 3x3x3 neighbourhood with 27 different weights (w[dz][dy][dx] = (9 dz + 3 dy + dx + 1) / 378), so that
+# a tap read from the wrong plane, row or column changes the result
+WEIGHTED27 = KernelSpec("stencil3", "Weighted27", f"""
+struct Weighted27 : accb::Stencil3<float, float, 1, 1, 1> {{
+    {_D} float apply(const accb::Env &, const float (&t)[3][3][3]) {{
+        float s = 0.0f;
+        for (int z = 0; z < 3; ++z) for (int y = 0; y < 3; ++y) for (int x = 0; x < 3; ++x)
+            s += (float)(9 * z + 3 * y + x + 1) * t[z][y][x];
+        return s * (1.0f / 378.0f);
+    }}
+}};
+""")
+
+# rank 3: the 7-point Laplacian
+LAPLACE3 = KernelSpec("stencil3", "Laplace3", f"""
+struct Laplace3 : accb::Stencil3<float, float, 1, 1, 1> {{
+    {_D} float apply(const accb::Env &, const float (&t)[3][3][3]) {{
+        return t[0][1][1] + t[2][1][1] + t[1][0][1] + t[1][2][1] + t[1][1][0] + t[1][1][2] - 6.0f * t[1][1][1];
+    }}
+}};
+""")
+
 STENCIL2_SUM = KernelSpec("stencil2", "Cross2", f"""
 struct Cross2 : accb::Stencil<float, float, 1, 1> {{
     {_D} float apply(const accb::Env &, const float (&a)[3][3], const float (&b)[3][3]) {{

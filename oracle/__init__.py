@@ -321,6 +321,50 @@ def bound_index(i, sz, mode):
     return i if 0 <= i < sz else None
 
 
+def stencil3d(a, weights, boundary="clamp", cval=0.0) -> np.ndarray:
+    """Linear stencil over a rank-3 array in float64: out[z,y,x] = sum of weights[dz][dy][dx] * a at offset
+    (dz-rz, dy-ry, dx-rx), every coordinate through its boundary on its own and, with Constant, the whole tap
+    replaced as soon as one coordinate is outside (CodeGen/Stencil/Extra.hs:122-128,191-226; the pattern nests
+    outermost dimension first, Stencil.hs:97-98).  numpy's padding modes are the same maps: edge = Clamp,
+    reflect = Mirror (-i, sz-(i-sz+2)), wrap = Wrap; tests/test_oracle.py checks that against bound_index."""
+    a = np.asarray(a, np.float64)
+    wt = np.asarray(weights, np.float64)
+    rz, ry, rx = (s // 2 for s in wt.shape)
+    mode = {"clamp": "edge", "mirror": "reflect", "wrap": "wrap", "constant": "constant"}[boundary]
+    kw = {"constant_values": cval} if boundary == "constant" else {}
+    pad = np.pad(a, ((rz, rz), (ry, ry), (rx, rx)), mode=mode, **kw)
+    d, h, w = a.shape
+    out = np.zeros((d, h, w), np.float64)
+    for dz in range(wt.shape[0]):
+        for dy in range(wt.shape[1]):
+            for dx in range(wt.shape[2]):
+                out += wt[dz, dy, dx] * pad[dz:dz + d, dy:dy + h, dx:dx + w]
+    return out
+
+
+def stencil3d_generic(a, fn, rz, ry, rx, boundary="clamp", cval=0.0):
+    """Generic rank-3 stencil by loops over bound_index (small arrays only): ``fn`` receives the neighbourhood
+    as nested lists t[dz][dy][dx]."""
+    a = np.asarray(a)
+    d, h, w = a.shape
+    out = np.empty((d, h, w), np.float64)
+    for z in range(d):
+        for y in range(h):
+            for x in range(w):
+                nb = []
+                for dz in range(-rz, rz + 1):
+                    plane = []
+                    for dy in range(-ry, ry + 1):
+                        row = []
+                        for dx in range(-rx, rx + 1):
+                            zz, yy, xx = bound_index(z + dz, d, boundary), bound_index(y + dy, h, boundary), bound_index(x + dx, w, boundary)
+                            row.append(cval if (zz is None or yy is None or xx is None) else float(a[zz, yy, xx]))
+                        plane.append(row)
+                    nb.append(plane)
+                out[z, y, x] = fn(nb)
+    return out
+
+
 def stencil_generic(a, fn, ry, rx, boundary="clamp", cval=0.0):
     """Generic 2-D stencil: ``fn`` receives the (2ry+1)x(2rx+1) neighbourhood as a
     nested list, row-major (CodeGen/Stencil.hs:34-44,97-98)."""

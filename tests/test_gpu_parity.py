@@ -606,6 +606,50 @@ def test_stencil_iterated_blur_matches_float64_recurrence(ctx, P, torch_cuda, or
     close(res.cpu().numpy(), oracle.stencil2d_iter(a, workloads.BLUR_WEIGHTS, 10, "clamp"), 1e-6)
 
 
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
+@pytest.mark.parametrize("shape", [(3, 3, 4), (5, 7, 9), (19, 33, 260), (40, 16, 128), (9, 50, 131)])
+def test_stencil_rank3(ctx, P, torch_cuda, oracle, rng, boundary, shape):
+    """Stencils over cubes (mkStencil is rank-polymorphic, Stencil.hs:55-114): 27 different weights against the
+    float64 oracle, ragged and aligned extents, all four boundaries; and the 7-point Laplacian."""
+    t = torch_cuda
+    a = rng.uniform(-1, 1, shape).astype(np.float32)
+    out = t.empty(shape, dtype=t.float32, device="cuda")
+    const = np.float32(0.25) if boundary == "constant" else None
+    ctx.stencil(P.WEIGHTED27, dev(t, a), out, boundary=boundary, constant=const)
+    ctx.sync()
+    w = (np.arange(27, dtype=np.float64).reshape(3, 3, 3) + 1) / 378.0
+    close(out.cpu().numpy(), oracle.stencil3d(a, w, boundary, 0.25), 1e-6)
+    ctx.stencil(P.LAPLACE3, dev(t, a), out, boundary=boundary, constant=const)
+    ctx.sync()
+    lap = np.zeros((3, 3, 3))
+    lap[1, 1, 1] = -6
+    for z, y, x in ((0, 1, 1), (2, 1, 1), (1, 0, 1), (1, 2, 1), (1, 1, 0), (1, 1, 2)):
+        lap[z, y, x] = 1
+    close(out.cpu().numpy(), oracle.stencil3d(a, lap, boundary, 0.25), 1e-5)
+
+
+def test_stencil_rank3_unaligned_source_and_iteration(ctx, P, torch_cuda, oracle, rng):
+    t = torch_cuda
+    shape = (12, 20, 64)
+    a = rng.uniform(-1, 1, shape).astype(np.float32)
+    flat = t.empty(a.size + 1, dtype=t.float32, device="cuda")
+    src = flat[1:].view(shape)  # 4-byte aligned only: scalar loads
+    src.copy_(dev(t, a))
+    out, tmp = t.empty(shape, dtype=t.float32, device="cuda"), t.empty(shape, dtype=t.float32, device="cuda")
+    ctx.stencil(P.WEIGHTED27, src, out, boundary="clamp")
+    ctx.sync()
+    w = (np.arange(27, dtype=np.float64).reshape(3, 3, 3) + 1) / 378.0
+    ref = oracle.stencil3d(a, w, "clamp")
+    close(out.cpu().numpy(), ref, 1e-6)
+    res = ctx.stencil_iterate(P.WEIGHTED27, out, tmp, 2, boundary="clamp")  # three applications in all
+    ctx.sync()
+    for _ in range(2):
+        ref = oracle.stencil3d(ref, w, "clamp")
+    close(res.cpu().numpy(), ref, 1e-5)
+    with pytest.raises(Exception):  # a rank-2 kernel on a cube
+        ctx.stencil(P.BLUR, src, out, boundary="clamp")
+
+
 def test_stencil2_on_different_extents_uses_the_intersection(ctx, P, torch_cuda, oracle, rng):
     t = torch_cuda
     a = rng.uniform(0, 1, (40, 100)).astype(np.float32)

@@ -391,7 +391,8 @@ def test_stencils(ctx, oracle, rng, boundary):
 @pytest.mark.gpu
 @pytest.mark.parametrize("boundary,padmode", [("clamp", "edge"), ("mirror", "reflect"), ("wrap", "wrap"),
                                               (("constant", 2.0), "constant")])
-def test_stencil_over_a_cube_gathers_through_the_boundary_function(ctx, rng, boundary, padmode):
+def test_stencil_over_a_cube_and_over_pairs(ctx, rng, boundary, padmode):
+    """A cube of one 4-byte component runs on the rank-3 stencil skeleton; pairs gather through the boundary function."""
     c = rng.uniform(0, 1, (9, 20, 33)).astype(f32)
     mean27 = lambda t: sum((t[z][y][x] for z in range(3) for y in range(3) for x in range(3)), A.constant(0, f32)) / 27.0  # noqa: E731
     got = A.runWith(ctx, lambda a: A.stencil(mean27, boundary, a), c)

@@ -129,3 +129,15 @@ def test_oracle_reproduces_the_committed_fixtures(oracle, workloads, golden):
     c, p = oracle.blackscholes(g["bs_spot"], g["bs_strike"], g["bs_years"])
     assert np.allclose(c, g["bs_call"], rtol=1e-13, atol=0) and np.allclose(p, g["bs_put"], rtol=1e-13, atol=1e-15)
     assert np.array_equal(oracle.fold_rows_f32(g["matrix"]), g["rowsum"])
+
+
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
+def test_rank3_stencil_oracle_by_padding_equals_the_boundary_functions(oracle, boundary):
+    """The padded-array form used at size against the loop over bound_index (Stencil/Extra.hs:200-226), with 27
+    different weights so that the orientation of the pattern matters."""
+    rng = np.random.default_rng(3)
+    a = rng.uniform(-1, 1, (4, 5, 6)).astype(np.float32)
+    w = (np.arange(27, dtype=np.float64).reshape(3, 3, 3) + 1) / 378.0
+    fn = lambda t: sum(w[z, y, x] * t[z][y][x] for z in range(3) for y in range(3) for x in range(3))  # noqa: E731
+    ref = oracle.stencil3d_generic(a, fn, 1, 1, 1, boundary, 0.5)
+    assert np.allclose(oracle.stencil3d(a, w, boundary, 0.5), ref, rtol=0, atol=1e-12)
