@@ -164,6 +164,9 @@ def lib() -> C.CDLL:
             "accb_group_scan": [vp, vp, vp, vp, arrp, i32, C.POINTER(ll), i32, i32, vp, sz, sz, arrp, arrp],
             "accb_group_permute": [vp, vp, vp, arrp, i32, C.POINTER(ll), vp, sz, C.POINTER(i32), arrp, i32],
             "accb_group_stencil_layout": [vp, i32, i32, i32, i32, C.POINTER(i32), C.POINTER(i32)],
+            "accb_group_stencil2": [vp, vp, arrp, arrp, arrp, C.POINTER(i32), i32, i32, vp, sz, C.POINTER(i32)],
+            "accb_seg_partition": [C.POINTER(i32), ll, i32, C.POINTER(ll)],
+            "accb_group_fold_seg": [vp, vp, arrp, i32, C.POINTER(ll), C.POINTER(vp), C.POINTER(ll), vp, sz, arrp],
             "accb_group_stencil_iterate": [vp, vp, arrp, arrp, C.POINTER(i32), i32, i32, i32, vp, sz,
                                            C.POINTER(i32), C.POINTER(i32)],
             "accb_peer_create": [vp, i32, i32, sz, C.POINTER(vp)],
@@ -359,6 +362,15 @@ class Peer:
         if self.handle:
             lib().accb_peer_destroy(self.handle)
             self.handle = None
+
+
+def seg_partition(offsets, parts: int):
+    """Cuts between segments so that ``parts`` runs of whole segments hold about the same number of elements
+    (``accb_seg_partition``): returns parts + 1 segment numbers."""
+    offs = np.ascontiguousarray(offsets, np.int32)
+    first = (C.c_longlong * (parts + 1))()
+    _check(lib().accb_seg_partition(offs.ctypes.data_as(C.POINTER(C.c_int)), offs.size - 1, parts, first))
+    return list(first)
 
 
 def scan_layout(world: int, rank: int, n_global: int, block_elems: int):
@@ -631,6 +643,22 @@ class Group:
         self._check(lib().accb_group_stencil_layout(self.handle, rank, iters, ry, BOUNDARY[boundary], C.byref(t),
                                                     C.byref(b)))
         return t.value, b.value
+
+    def stencil2(self, kernel, a, b, out, rows, ry: int, boundary="clamp", constant=None):
+        """stencil2 on row slabs padded by ``stencil_layout(rank, 1, ry, boundary)``: the halo rows of both sources
+        are filled from the neighbours; the own rows of ``out`` hold the result."""
+        cb, cn = _bytes_of(constant)
+        self._check(lib().accb_group_stencil2(self.handle, self._k(kernel), _arr_list(a), _arr_list(b), _arr_list(out),
+                                              (C.c_int * len(rows))(*rows), ry, BOUNDARY[boundary], cb, cn, self._cb(a[0])))
+
+    def fold_seg(self, kernel, env, n, offsets, nseg, out, seed=None):
+        """foldSeg split between segments: ``offsets[r]`` is rank r's run of the whole array's offsets (a device
+        array of nseg[r] + 1 Int32 on that rank), rebased by the call."""
+        sb, sn = _bytes_of(seed)
+        e, nenv = self._env(env)
+        ptrs = (C.c_void_p * self.size)(*[_ptr(o) if nseg[r] > 0 else None for r, o in enumerate(offsets)])
+        self._check(lib().accb_group_fold_seg(self.handle, self._k(kernel), e, nenv, self._lls(n), ptrs, self._lls(nseg),
+                                              sb, sn, _arr_list(out)))
 
     def stencil_iterate(self, kernel, a, b, rows, iters: int, ry: int, boundary="clamp", constant=None):
         """Returns the list of slabs (``a`` or ``b``) that hold the result in their own rows."""

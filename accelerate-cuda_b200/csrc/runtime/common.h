@@ -225,6 +225,9 @@ struct PieceState {
 int peer_scan_begin(accb_peer *p, size_t offset, size_t bytes, PeerScanInfo *info, bool count);
 accb_context *peer_context(accb_peer *p);
 
+/* dst[i] = src[i] - src[0] for n values on the device: segment offsets of a slice made to start at zero */
+int rebase_offsets(accb_context *ctx, cudaStream_t s, int *dst, const int *src, long long n);
+
 /* host fault injection: ACCB_FAIL=<site>[:N] makes the N-th call at <site>
  * fail (sites: malloc, nvcc, cache_io) */
 bool inject_failure(const char *site);

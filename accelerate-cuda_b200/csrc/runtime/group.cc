@@ -12,6 +12,8 @@
  *   scan                  slab totals -> rank 0 -> scan of the totals -> one carry per rank
  *   permute               partial destinations -> rank 0, merged one after another
  *   iterated stencil      iters*ry halo rows from each neighbour, once
+ *   stencil2              ry halo rows of both sources from each neighbour
+ *   foldSeg               none: split between segments, every rank's offsets rebased to its slice
  *
  * Exchanged data is copied into the receiving device's own memory before a
  * kernel reads it; devices are ordered with events only, so no kernel ever
@@ -42,6 +44,8 @@ struct accb_group {
     size_t gather_comp = 0;                       /* bytes reserved per component in `gather` */
     char *stage = nullptr;                        /* rank 0: a peer's partial destination */
     size_t stage_bytes = 0;
+    std::vector<int *> seg_offsets;               /* per rank: a slice's segment offsets, rebased to start at zero */
+    std::vector<size_t> seg_capacity;             /* ... and how many values fit */
     std::mutex mu;
     std::string last_error;
 };
@@ -212,6 +216,7 @@ int accb_group_destroy(accb_group *g) {
         if (r < g->ev_b.size() && g->ev_b[r]) cudaEventDestroy(g->ev_b[r]);
         if (r < g->ev_end.size() && g->ev_end[r]) cudaEventDestroy(g->ev_end[r]);
         if (r < g->small.size() && g->small[r]) cudaFree(g->small[r]);
+        if (r < g->seg_offsets.size() && g->seg_offsets[r]) cudaFree(g->seg_offsets[r]);
         if (r == 0) {
             if (g->gather) cudaFree(g->gather);
             if (g->stage) cudaFree(g->stage);
@@ -459,6 +464,127 @@ int accb_group_stencil_layout(accb_group *g, int rank, int iters, int ry, int bo
     return ACCB_OK;
 }
 
+/* Fill the `reach` halo rows of every rank's padded slab a[r] (pt[r] + rows[r] + pb[r] rows) from the neighbours' own
+ * rows by peer copies; afterwards ev_b[r] marks that rank r has read its neighbours. */
+static int fill_halos(accb_group *g, const accb_array *a, const int *rows, const std::vector<int> &pt, const std::vector<int> &pb,
+                      const std::vector<size_t> &row_elems, int reach, int nc, const int *comp_bytes) {
+    const int G = g->n;
+    for (int r = 0; r < G; ++r) GTRY(record(g, g->ev_a, r)); /* the slab's own rows are final */
+    for (int r = 0; r < G; ++r) {
+        const int up = (r + G - 1) % G, down = (r + 1) % G;
+        for (int c = 0; c < nc; ++c) {
+            const size_t rb = row_elems[r] * comp_bytes[c];
+            if (pt[r]) { /* the last rows of the rank above */
+                GTRY(wait_for(g, r, g->ev_a, up));
+                GTRY(copy_between(g, r, a[r].ptr[c], up, (const char *)a[up].ptr[c] + (size_t)(pt[up] + rows[up] - reach) * rb,
+                                  (size_t)reach * rb));
+            }
+            if (pb[r]) { /* the first rows of the rank below */
+                GTRY(wait_for(g, r, g->ev_a, down));
+                GTRY(copy_between(g, r, (char *)a[r].ptr[c] + (size_t)(pt[r] + rows[r]) * rb, down,
+                                  (const char *)a[down].ptr[c] + (size_t)pt[down] * rb, (size_t)reach * rb));
+            }
+        }
+        GTRY(record(g, g->ev_b, r));
+    }
+    return ACCB_OK;
+}
+
+/* padded row slabs of one array per rank: shapes against the layout, elements per row */
+static int check_slabs(accb_group *g, const accb_array *a, const int *rows, const std::vector<int> &pt, const std::vector<int> &pb,
+                       int nc, std::vector<size_t> &row_elems) {
+    for (int r = 0; r < g->n; ++r) {
+        if (a[r].rank < 1 || a[r].rank > 2 || a[r].ncomp != nc)
+            return gfail(g, ACCB_EINVAL, "rank %d: slabs must be vectors or matrices of the same type", r);
+        const int outer = a[r].shape[a[r].rank - 1];
+        row_elems[r] = a[r].rank == 2 ? (size_t)a[r].shape[0] : 1;
+        if (outer != pt[r] + rows[r] + pb[r] || row_elems[r] != row_elems[0])
+            return gfail(g, ACCB_EINVAL, "rank %d: slab of %d rows, expected %d + %d + %d", r, outer, pt[r], rows[r], pb[r]);
+    }
+    return ACCB_OK;
+}
+
+int accb_group_stencil2(accb_group *g, accb_kernel *k, const accb_array *a, const accb_array *b, const accb_array *out,
+                        const int *rows, int ry, int boundary, const void *constant, size_t constant_bytes,
+                        const int *comp_bytes) {
+    GLOCK(g);
+    if (!a || !b || !out || !rows) return gfail(g, ACCB_EINVAL, "null arrays");
+    if (ry < 0) return gfail(g, ACCB_EINVAL, "negative reach");
+    const int G = g->n, nc = a[0].ncomp;
+    GTRY(check_comp(g, nc, comp_bytes));
+    std::vector<int> pt(G), pb(G);
+    std::vector<size_t> re_a(G), re_b(G);
+    for (int r = 0; r < G; ++r) {
+        halo_rows(g, r, ry, boundary, &pt[r], &pb[r]);
+        if (G > 1 && rows[r] < ry) return gfail(g, ACCB_EINVAL, "rank %d owns %d rows, fewer than the halo of %d", r, rows[r], ry);
+    }
+    GTRY(check_slabs(g, a, rows, pt, pb, nc, re_a));
+    GTRY(check_slabs(g, b, rows, pt, pb, nc, re_b));
+    if (G > 1 && ry > 0) {
+        GTRY(fill_halos(g, a, rows, pt, pb, re_a, ry, nc, comp_bytes));
+        /* the second source reuses the events: rank r's copies are ordered on its stream, the neighbours' rows of b
+         * were final before this call as well */
+        GTRY(fill_halos(g, b, rows, pt, pb, re_b, ry, nc, comp_bytes));
+        /* whatever a rank enqueues next may overwrite its sources: the neighbours must have read them by then */
+        for (int r = 0; r < G; ++r) {
+            if (pt[r]) GTRY(wait_for(g, r, g->ev_b, (r + G - 1) % G));
+            if (pb[r]) GTRY(wait_for(g, r, g->ev_b, (r + 1) % G));
+        }
+    }
+    /* every rank applies the stencil to its padded slabs: the result's own rows are right, its halo rows (computed
+     * from rows the rank does not have) are not and belong to the neighbours anyway */
+    for (int r = 0; r < G; ++r)
+        GTRY(inner(g, r, accb_stencil2(g->ctx[r], k, g->st[r], &a[r], &b[r], boundary, constant, constant_bytes, &out[r])));
+    return ACCB_OK;
+}
+
+/* ------------------------------------------------------------ foldSeg */
+int accb_seg_partition(const int *offsets, long long nseg, int parts, long long *first_seg) {
+    if (!offsets || !first_seg || nseg < 0 || parts < 1) return gfail(nullptr, ACCB_EINVAL, "bad segment partition request");
+    /* part p starts at the first segment whose offset reaches p/parts of all elements: runs of whole segments
+     * holding about the same number of elements (a segment is never cut) */
+    const long long total = (long long)offsets[nseg] - offsets[0];
+    first_seg[0] = 0;
+    for (int p = 1; p < parts; ++p) {
+        const long long want = offsets[0] + total * p / parts;
+        const int *it = std::lower_bound(offsets, offsets + nseg + 1, (int)std::min<long long>(want, 0x7fffffffLL));
+        first_seg[p] = std::max(first_seg[p - 1], std::min<long long>(it - offsets, nseg));
+    }
+    first_seg[parts] = nseg;
+    return ACCB_OK;
+}
+
+int accb_group_fold_seg(accb_group *g, accb_kernel *k, const accb_array *env, int nenv, const long long *n,
+                        const int *const *offsets, const long long *nseg, const void *seed, size_t seed_bytes,
+                        const accb_array *out) {
+    GLOCK(g);
+    if (!out || !n || !offsets || !nseg || (nenv > 0 && !env)) return gfail(g, ACCB_EINVAL, "null arrays");
+    if (g->seg_offsets.empty()) {
+        g->seg_offsets.assign(g->n, nullptr);
+        g->seg_capacity.assign(g->n, 0);
+    }
+    for (int r = 0; r < g->n; ++r) {
+        if (nseg[r] < 0 || n[r] < 0) return gfail(g, ACCB_EINVAL, "rank %d: negative extent", r);
+        if (nseg[r] == 0) continue;
+        if (!offsets[r]) return gfail(g, ACCB_EINVAL, "rank %d: null segment offsets", r);
+        CtxGuard guard(g->ctx[r]);
+        const size_t need = (size_t)nseg[r] + 1;
+        if (g->seg_capacity[r] < need) {
+            GTRY(cuda(g, cudaStreamSynchronize(g->st[r]), "cudaStreamSynchronize")); /* earlier folds may still read it */
+            if (g->seg_offsets[r]) cudaFree(g->seg_offsets[r]);
+            g->seg_offsets[r] = nullptr;
+            g->seg_capacity[r] = 0;
+            GTRY(cuda(g, cudaMalloc((void **)&g->seg_offsets[r], need * sizeof(int)), "cudaMalloc"));
+            g->seg_capacity[r] = need;
+        }
+        /* the rank's offsets are a run of the whole array's: made to start at zero, they index its own slice */
+        GTRY(inner(g, r, rebase_offsets(g->ctx[r], g->st[r], g->seg_offsets[r], offsets[r], (long long)need)));
+        GTRY(inner(g, r, accb_fold_seg(g->ctx[r], k, g->st[r], env + (size_t)r * nenv, nenv, 1, n[r], g->seg_offsets[r], nseg[r],
+                                       seed, seed_bytes, &out[r])));
+    }
+    return ACCB_OK;
+}
+
 int accb_group_stencil_iterate(accb_group *g, accb_kernel *k, const accb_array *a, const accb_array *b, const int *rows,
                                int iters, int ry, int boundary, const void *constant, size_t constant_bytes,
                                const int *comp_bytes, int *result_in_b) {
@@ -482,24 +608,7 @@ int accb_group_stencil_iterate(accb_group *g, accb_kernel *k, const accb_array *
                          r, rows[r], reach);
     }
     if (G > 1 && reach > 0) {
-        for (int r = 0; r < G; ++r) GTRY(record(g, g->ev_a, r)); /* the slab's own rows are final */
-        for (int r = 0; r < G; ++r) {
-            const int up = (r + G - 1) % G, down = (r + 1) % G;
-            for (int c = 0; c < nc; ++c) {
-                const size_t rb = row_elems[r] * comp_bytes[c];
-                if (pt[r]) { /* the last rows of the rank above */
-                    GTRY(wait_for(g, r, g->ev_a, up));
-                    GTRY(copy_between(g, r, a[r].ptr[c], up,
-                                      (const char *)a[up].ptr[c] + (size_t)(pt[up] + rows[up] - reach) * rb, (size_t)reach * rb));
-                }
-                if (pb[r]) { /* the first rows of the rank below */
-                    GTRY(wait_for(g, r, g->ev_a, down));
-                    GTRY(copy_between(g, r, (char *)a[r].ptr[c] + (size_t)(pt[r] + rows[r]) * rb, down,
-                                      (const char *)a[down].ptr[c] + (size_t)pt[down] * rb, (size_t)reach * rb));
-                }
-            }
-            GTRY(record(g, g->ev_b, r));
-        }
+        GTRY(fill_halos(g, a, rows, pt, pb, row_elems, reach, nc, comp_bytes));
         /* a rank's second application overwrites a[r]: the neighbours must have read it by then */
         for (int r = 0; r < G; ++r) {
             if (pt[r]) GTRY(wait_for(g, r, g->ev_b, (r + G - 1) % G));

@@ -15,6 +15,8 @@
  * Element i depends only on (seed, stream, i), so any shard of any GPU can
  * produce its own slice.
  */
+#include <algorithm>
+
 #include "common.h"
 
 namespace {
@@ -46,6 +48,13 @@ __global__ void gen_uniform_i32(int *dst, long long n, long long first, unsigned
         const unsigned long long h = hash_at(key, first + i);
         dst[i] = (int)(((h >> 32) * (unsigned long long)m) >> 32);
     }
+}
+
+/* dst[i] = src[i] - src[0]: a run of segment offsets of a larger array, made to start at zero */
+__global__ void rebase_i32(int *dst, const int *src, long long n) {
+    const int base = src[0];
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = src[i] - base;
 }
 
 /* streams: 2 = coin, 3 = Zipf draw, 4 = uniform draw */
@@ -143,3 +152,13 @@ int accb_flush_l2(accb_context *ctx, accb_stream stream) {
 }
 
 } /* extern "C" */
+
+namespace accb_rt {
+int rebase_offsets(accb_context *ctx, cudaStream_t s, int *dst, const int *src, long long n) {
+    if (n <= 0) return ACCB_OK;
+    const int grid = (int)std::min<long long>((n + 255) / 256, 1024);
+    rebase_i32<<<grid, 256, 0, s>>>(dst, src, n);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "rebase_i32");
+}
+}  // namespace accb_rt

@@ -241,6 +241,42 @@ def sharded_stencil_iterate(grid_local: torch.Tensor, iters: int, ry: int, local
     return a[ry:ry + h]
 
 
+def segment_partition(offsets, parts: int):
+    """Cuts between segments for ``parts`` ranks: run p holds the segments from the first one whose offset reaches
+    p/parts of all elements, so the runs hold about the same number of elements and no segment is cut.  The
+    arithmetic of ``accb_seg_partition``.  Returns parts + 1 segment numbers."""
+    offs = torch.as_tensor(offsets).to(torch.int64).cpu()
+    nseg = offs.numel() - 1
+    total = int(offs[nseg] - offs[0])
+    first = [0]
+    for p in range(1, parts):
+        want = int(offs[0]) + total * p // parts
+        cut = int(torch.searchsorted(offs, torch.tensor(want), right=False))
+        first.append(max(first[-1], min(cut, nseg)))
+    return first + [nseg]
+
+
+def sharded_fold_seg(values_local: torch.Tensor, offsets_run: torch.Tensor, local_fold_seg: Callable) -> torch.Tensor:
+    """foldSeg split between segments (no exchange): ``offsets_run`` is this rank's run of the whole array's offsets
+    (its segments + 1 values); rebased to start at zero it indexes the rank's own slice ``values_local``.
+    ``local_fold_seg(values, offsets) -> one result per segment``."""
+    return local_fold_seg(values_local, offsets_run - offsets_run[:1])
+
+
+def sharded_stencil2(a_local: torch.Tensor, b_local: torch.Tensor, ry: int, local_apply: Callable, boundary: str = "clamp",
+                     group=None) -> torch.Tensor:
+    """stencil2 on row slabs: both sources get ry halo rows from the neighbours (``exchange_halos``), then
+    ``local_apply(a_padded, b_padded) -> padded result``; returns the rank's own rows.  Sources of different extents
+    are cut to their intersection before they are dealt out (CUDA/Execute.hs:433-435)."""
+    h, w = a_local.shape
+    pa = torch.empty((h + 2 * ry, w), dtype=a_local.dtype, device=a_local.device)
+    pb = torch.empty((h + 2 * ry, w), dtype=b_local.dtype, device=b_local.device)
+    pa[ry:ry + h], pb[ry:ry + h] = a_local, b_local
+    exchange_halos(pa, ry, boundary, group)
+    exchange_halos(pb, ry, boundary, group)
+    return local_apply(pa, pb)[ry:ry + h]
+
+
 # ------------------------------------------------------------------ exchanges by the library's own kernels
 def peer_buffer(ctx, nbytes: int, group=None):
     """This rank's exchange buffer, connected to the other ranks' buffers (``Peer``): the 64-byte IPC handles travel

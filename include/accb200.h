@@ -469,6 +469,23 @@ ACCB_API int accb_group_stencil_layout(accb_group *grp, int rank, int iters, int
 ACCB_API int accb_group_stencil_iterate(accb_group *grp, accb_kernel *k, const accb_array *a, const accb_array *b,
                                         const int *rows, int iters, int ry, int boundary, const void *constant,
                                         size_t constant_bytes, const int *comp_bytes, int *result_in_b);
+/* stencil2 on the same row slabs: a[r], b[r] and out[r] are slabs of pad_top + rows[r] + pad_bottom rows
+ * (accb_group_stencil_layout with iters = 1); the halo rows of BOTH sources are filled from the neighbours, then every
+ * rank applies the stencil to its padded slabs.  The result's own rows are final; its halo rows are not (they
+ * belong to the neighbours).  Sources of different extents, whose result covers the intersection
+ * (CUDA/Execute.hs:433-435), are cut to the intersection by the caller before they are dealt out. */
+ACCB_API int accb_group_stencil2(accb_group *grp, accb_kernel *k, const accb_array *a, const accb_array *b,
+                                 const accb_array *out, const int *rows, int ry, int boundary, const void *constant,
+                                 size_t constant_bytes, const int *comp_bytes);
+/* foldSeg over a vector, split BETWEEN segments: rank r owns nseg[r] consecutive segments and the n[r] elements they
+ * cover (env[r]: its slice of the sources; out[r]: nseg[r] results).  offsets[r] is a device pointer on rank r to
+ * the nseg[r] + 1 offsets of its segments as they stand in the WHOLE offsets array (CUDA/Execute.hs:320-324); the
+ * call rebases them to the slice and folds.  No exchange.  accb_seg_partition picks the cuts from a host copy of
+ * the offsets: first_seg[0..parts] with runs of whole segments that hold about the same number of elements. */
+ACCB_API int accb_seg_partition(const int *offsets_host, long long nseg, int parts, long long *first_seg);
+ACCB_API int accb_group_fold_seg(accb_group *grp, accb_kernel *k, const accb_array *env, int nenv, const long long *n,
+                                 const int *const *offsets, const long long *nseg, const void *seed,
+                                 size_t seed_bytes, const accb_array *out);
 
 /* ------------------------- exchanges between processes, one per GPU
  * For hosts that run one process per GPU (torchrun, MPI): the small exchanges of the sharded skeletons -- slab

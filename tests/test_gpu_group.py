@@ -182,6 +182,64 @@ def test_group_iterated_blur_with_one_halo_exchange(group, P, torch_cuda, oracle
     close(got, oracle.stencil2d_iter(a, workloads.BLUR_WEIGHTS, iters, boundary, 0.25), 1e-6)
 
 
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
+def test_group_stencil2_on_row_slabs(group, P, torch_cuda, oracle, rng, boundary):
+    """stencil2 over two matrices dealt out as row slabs: both sources' halo rows come from the neighbours
+    (Execute.hs:427-450 on one device)."""
+    t, G = torch_cuda, group.size
+    h, w = 40 * G + 7, 128
+    a, b = rng.uniform(0, 1, (h, w)).astype(np.float32), rng.uniform(0, 1, (h, w)).astype(np.float32)
+    c = cuts(h, G, rng)
+    rows = [c[r + 1] - c[r] for r in range(G)]
+    pads = [group.stencil_layout(r, 1, 1, boundary) for r in range(G)]
+    A, B, O = [], [], []
+    for r in range(G):
+        pt, pb = pads[r]
+        for src, dst in ((a, A), (b, B)):
+            slab = np.full((pt + rows[r] + pb, w), np.nan, np.float32)
+            slab[pt:pt + rows[r]] = src[c[r]:c[r + 1]]
+            dst.append(put(t, slab, group.devices[r]))
+        O.append(t.empty_like(A[-1]))
+    sync_all(t)
+    group.stencil2(P.STENCIL2_SUM, A, B, O, rows, 1, boundary, constant=np.float32(0.25))
+    group.sync()
+    got = np.concatenate([O[r].cpu().numpy()[pads[r][0]:pads[r][0] + rows[r]] for r in range(G)])
+    w1 = np.zeros((3, 3)); w1[1, 1] = 1; w1[1, 0] = w1[1, 2] = 0.5
+    w2 = np.zeros((3, 3)); w2[0, 1] = w2[2, 1] = 0.25; w2[1, 1] = -1
+    close(got, oracle.stencil2_2d(a, b, w1, w2, boundary, 0.25), 1e-6)
+
+
+@pytest.mark.parametrize("nseg,mean", [(1, 5), (10, 3), (5000, 7), (300, 900)])
+def test_group_fold_seg_split_between_segments(group, accb, P, torch_cuda, oracle, rng, nseg, mean):
+    """foldSeg over a vector split BETWEEN segments: every rank gets a run of whole segments holding about the same
+    number of elements, its offsets rebased on the device (Execute.hs:320-324 on one device)."""
+    t, G = torch_cuda, group.size
+    lens = rng.integers(0, 2 * mean + 1, nseg).astype(np.int32)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    n = int(offs[-1])
+    x = rng.integers(-50, 50, max(n, 1)).astype(np.int32)[:n]
+    first = accb.seg_partition(offs, G)
+    sh = __import__("importlib").import_module("accelerate-cuda_b200.sharded")
+    assert first == sh.segment_partition(offs, G) and first[0] == 0 and first[-1] == nseg and sorted(first) == first
+    env, runs, out, cnt, segs = [], [], [], [], []
+    for r in range(G):
+        s0, s1 = first[r], first[r + 1]
+        lo, hi = int(offs[s0]), int(offs[s1])
+        dev = group.devices[r]
+        env.append([put(t, np.concatenate([x[lo:hi], np.zeros(1, np.int32)]), dev)[:hi - lo]])
+        runs.append(put(t, offs[s0:s1 + 1], dev))  # as they stand in the whole array: not starting at zero
+        out.append(t.full((max(s1 - s0, 1),), -99, dtype=t.int32, device=f"cuda:{dev}")[:s1 - s0])
+        cnt.append(hi - lo)
+        segs.append(s1 - s0)
+    sync_all(t)
+    group.fold_seg(P.SEGSUM_I32, env, cnt, runs, segs, out, seed=np.int32(3))
+    group.sync()
+    got = np.concatenate([o.cpu().numpy() for o in out])
+    assert np.array_equal(got, oracle.fold_seg_i32(x, offs, 3))
+    if G > 1 and nseg >= 300:  # the cuts balance elements, not segments
+        assert max(cnt) <= 1.5 * n / G + 2 * (2 * mean + 1)
+
+
 def test_group_stencil_refuses_a_slab_smaller_than_its_halo(group, accb, P, torch_cuda):
     t, G = torch_cuda, group.size
     if G == 1:

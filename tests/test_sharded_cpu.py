@@ -61,6 +61,30 @@ def _worker(rank, world, port, case, ret):
             got = sh.sharded_fold_all(part, lambda a, b: a + b)
             ref = oracle.dot_f32(W.uniform_f32(W.SEED, W.S_XS, n, -1, 1), W.uniform_f32(W.SEED, W.S_YS, n, -1, 1))
             ok = abs(float(got[0]) - ref) <= 1e-12 * abs(ref)
+        elif case == "foldseg":
+            # split between segments: every rank folds a run of whole segments with its offsets rebased
+            rng = np.random.default_rng(5)
+            lens = rng.integers(0, 40, 2000).astype(np.int32)
+            offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+            x = rng.integers(-9, 9, int(offs[-1])).astype(np.int32)
+            first = sh.segment_partition(offs, world)
+            s0, s1 = first[rank], first[rank + 1]
+            fold = lambda v, o: torch.from_numpy(oracle.fold_seg_i32(v.numpy(), o.numpy().astype(np.int32), 2))
+            got = sh.sharded_fold_seg(torch.from_numpy(x[offs[s0]:offs[s1]]), torch.from_numpy(offs[s0:s1 + 1]), fold)
+            ok = np.array_equal(got.numpy(), oracle.fold_seg_i32(x, offs, 2)[s0:s1])
+            sizes = [int(offs[first[r + 1]] - offs[first[r]]) for r in range(world)]
+            ok = ok and max(sizes) - min(sizes) <= 2 * 40  # the runs hold about the same number of elements
+        elif case.startswith("stencil2"):
+            mode = case.split("-")[1]
+            h, w = 9 * world + 4, 24
+            a = W.uniform_f32(W.SEED, W.S_GRID, h * w, 0, 1).reshape(h, w)
+            b = W.uniform_f32(W.SEED, W.S_MATRIX, h * w, 0, 1).reshape(h, w)
+            lo, hi = (rank * (h // world), (rank + 1) * (h // world) if rank < world - 1 else h)
+            w1 = np.array([[0, 1, 0], [2, 3, 4], [0, 5, 0]], np.float64) / 15
+            w2 = np.array([[1, 0, 2], [0, -1, 0], [3, 0, 4]], np.float64) / 9
+            apply2 = lambda p, q: torch.from_numpy(oracle.stencil2_2d(p.numpy(), q.numpy(), w1, w2, mode))  # noqa: E731
+            got = sh.sharded_stencil2(torch.from_numpy(a[lo:hi].copy()), torch.from_numpy(b[lo:hi].copy()), 1, apply2, boundary=mode)
+            ok = np.allclose(got.numpy(), oracle.stencil2_2d(a, b, w1, w2, mode)[lo:hi], rtol=0, atol=1e-14)
         elif case.startswith("stencil"):
             mode = case.split("-")[1]
             h, w, iters = 12 * world + 5, 40, 4
@@ -92,7 +116,8 @@ def _worker(rank, world, port, case, ret):
 
 @pytest.mark.parametrize("world", [2, 3])
 @pytest.mark.parametrize("case", ["scan", "hist", "dot", "stencil-clamp", "stencil-mirror", "stencil-wrap",
-                                  "stencilwide-clamp", "stencilwide-mirror", "stencilwide-wrap", "stencilshort-clamp"])
+                                  "stencilwide-clamp", "stencilwide-mirror", "stencilwide-wrap", "stencilshort-clamp",
+                                  "foldseg", "stencil2-clamp", "stencil2-mirror", "stencil2-wrap"])
 def test_sharded_paths_match_the_single_device_oracle(case, world):
     mgr = mp.Manager()
     ret = mgr.dict()
