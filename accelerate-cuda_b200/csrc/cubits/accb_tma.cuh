@@ -58,4 +58,34 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned 
     return ok != 0;
 }
 
+/* ---- tiled copies through a tensor map (cp.async.bulk.tensor): the host encodes the map (cuTensorMapEncodeTiled)
+ * and passes it as a __grid_constant__ kernel parameter; the kernel only needs its address.  Always this GPU's
+ * own memory, never with cluster multicast.  The innermost coordinate times the element size must be a multiple
+ * of 16 bytes. ---- */
+struct alignas(64) TensorMap {
+    unsigned long long opaque[16]; /* the 128 bytes of a CUtensorMap */
+};
+
+/* global -> shared: the box at (x, y) of the tensor, completion counted in bytes on `bar` */
+__device__ __forceinline__ void tensor_g2s_2d(void *dst, const TensorMap *map, int x, int y, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+/* shared -> global: the box at (x, y); what lies outside the tensor is not written */
+__device__ __forceinline__ void tensor_s2g_2d(const TensorMap *map, int x, int y, const void *src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_addr(src)),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+
+/* writes of this thread to shared memory become visible to the copy engine */
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+/* closes the group of stores issued so far; wait until the engine has READ their shared memory */
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 }  // namespace accb

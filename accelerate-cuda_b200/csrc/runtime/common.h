@@ -51,6 +51,9 @@ struct Driver {
     CUresult (*GetErrorString)(CUresult, const char **) = nullptr;
     CUresult (*MemcpyDtoH)(void *, CUdeviceptr, size_t) = nullptr;
     CUresult (*DevicePrimaryCtxGetState)(CUdevice, unsigned *, int *) = nullptr;
+    CUresult (*TensorMapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                     const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
 };
 const Driver &driver();
 
@@ -129,7 +132,7 @@ namespace accb_rt {
 /* Tuning knobs, read from the environment ONCE when a context is created (never on the launch path):
  *   ACCB_FOLD_STAGE_MAX, ACCB_FOLD_NO_STAGE, ACCB_FOLDSEG_STAGE_MAX, ACCB_FOLDSEG_STAGE_FILL8,
  *   ACCB_FOLDSEG_STAGE_LANES, ACCB_PERMUTE_REPLICAS, ACCB_STENCIL_NO_TILE, ACCB_STENCIL_ROWS,
- *   ACCB_PIPELINE_CHUNK_LOG2, ACCB_NO_PIPELINE. */
+ *   ACCB_PIPELINE_CHUNK_LOG2, ACCB_NO_PIPELINE, ACCB_TRANSPOSE_TMA (0 or 1). */
 struct Tuning {
     long long fold_stage_max = 128;    /* longest row the staged thread-per-row fold takes */
     bool fold_no_stage = false;
@@ -139,6 +142,7 @@ struct Tuning {
     int permute_replicas = 4;          /* shared-memory copies of a privatised permute destination */
     bool stencil_no_tile = false;
     int stencil_rows = 64;             /* band height of the register-form stencil */
+    bool transpose_tma = true;         /* transposed maps of one 4-byte value through tensor-map copies */
     int pipeline_chunk_log2 = 0;       /* chunk of the host pipeline; 0: default */
     bool no_pipeline = false;
     void read_environment();
@@ -202,7 +206,7 @@ int get_function(accb_context *ctx, accb_kernel *k, const char *entry, CUfunctio
 void forget_context(accb_context *ctx); /* unload the modules loaded for a context that is being destroyed */
 int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blocks_per_sm);
 int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, size_t smem,
-           cudaStream_t stream, const accb_kparams &p, bool prefer_smem = true);
+           cudaStream_t stream, const accb_kparams &p, bool prefer_smem = true, void *extra1 = nullptr, void *extra2 = nullptr);
 
 /* exchange buffers (peer.cu), as the block-cyclic scan driver sees them */
 struct PieceState;

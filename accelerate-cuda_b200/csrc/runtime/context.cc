@@ -50,6 +50,8 @@ const Driver &driver() {
         d.GetErrorString = (decltype(d.GetErrorString))sym("cuGetErrorString");
         d.MemcpyDtoH = (decltype(d.MemcpyDtoH))sym("cuMemcpyDtoH_v2");
         d.DevicePrimaryCtxGetState = (decltype(d.DevicePrimaryCtxGetState))sym("cuDevicePrimaryCtxGetState");
+        /* optional: only the tensor-map form of the transposed map needs it */
+        d.TensorMapEncodeTiled = (decltype(d.TensorMapEncodeTiled))dlsym(h, "cuTensorMapEncodeTiled");
         d.ok = ok;
     });
     return d;
@@ -112,6 +114,7 @@ void Tuning::read_environment() {
     permute_replicas = (int)std::max(1LL, num("ACCB_PERMUTE_REPLICAS", permute_replicas));
     stencil_no_tile = getenv("ACCB_STENCIL_NO_TILE") != nullptr;
     stencil_rows = (int)std::max(1LL, num("ACCB_STENCIL_ROWS", stencil_rows));
+    transpose_tma = num("ACCB_TRANSPOSE_TMA", 1) != 0;
     pipeline_chunk_log2 = (int)num("ACCB_PIPELINE_CHUNK_LOG2", 0);
     no_pipeline = getenv("ACCB_NO_PIPELINE") != nullptr;
 }

@@ -41,8 +41,8 @@ int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blo
 }
 
 int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, size_t smem, cudaStream_t stream,
-           const accb_kparams &p, bool prefer_smem) {
-    void *args[] = {const_cast<accb_kparams *>(&p)};
+           const accb_kparams &p, bool prefer_smem, void *extra1, void *extra2) {
+    void *args[] = {const_cast<accb_kparams *>(&p), extra1, extra2}; /* entries with tensor maps take them after the block */
     if (ctx->trace_exec)
         fprintf(stderr, "[accb exec] %s<<<%d,%d,%zu>>> n=%lld\n", name, grid, block, smem, p.n);
     /* an entry that stages tiles in dynamic shared memory wants several of them per SM at the
@@ -245,6 +245,34 @@ int accb_map_transposed(accb_context *ctx, accb_kernel *k, accb_stream stream, c
             return fail(ctx, ACCB_EINVAL, "environment array %d is not the transposed shape of the result", a);
     p.ip[0] = H;
     p.ip[1] = W;
+    if (ctx->tune.transpose_tma && driver().TensorMapEncodeTiled && pr.meta.v[8] == 1 && (p.flags & ACCB_F_VEC) && W % 4 == 0 && H % 4 == 0 && nenv >= 1 &&
+        env[0].ncomp == 1 && out->ncomp == 1) {
+        /* one 4-byte value in, one out: the copy engine moves the tiles, through a tensor map of either matrix
+         * (64x64 tiles as two boxes of 32 columns, the hardware's 128-byte swizzle) */
+        alignas(64) CUtensorMap tin, tout;
+        const cuuint32_t box[2] = {32, 64}, ones[2] = {1, 1};
+        const cuuint64_t din[2] = {(cuuint64_t)W, (cuuint64_t)H}, sin[1] = {(cuuint64_t)W * 4};
+        const cuuint64_t dout[2] = {(cuuint64_t)H, (cuuint64_t)W}, sout[1] = {(cuuint64_t)H * 4};
+        const Driver &d = driver();
+        CUresult e1 = d.TensorMapEncodeTiled(&tin, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, env[0].ptr[0], din, sin, box, ones,
+                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        CUresult e2 = d.TensorMapEncodeTiled(&tout, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, out->ptr[0], dout, sout, box, ones,
+                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (e1 == CUDA_SUCCESS && e2 == CUDA_SUCCESS) {
+            Prep pt;
+            TRY(prepare(ctx, k, "map_transposed_tma", 0, &pt));
+            StreamScratch *sc = scratch_for(ctx, (cudaStream_t)stream);
+            if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+            p.aux[1] = sc->words + 2; /* error word of the bounded wait for the copy */
+            const long long tiles_tma = ceil_div(W, 64) * ceil_div(H, 64);
+            if (tiles_tma > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "matrix too large for one launch");
+            return launch(ctx, pt.fn, "map_transposed_tma", (int)tiles_tma, pt.block, (size_t)pr.meta.v[9], (cudaStream_t)stream, p,
+                          true, &tin, &tout);
+        }
+        /* a map the driver refuses (extents beyond its limits): the other form takes it */
+    }
     const long long tiles = ceil_div(W, 64) * ceil_div(H, 64); /* kTransTile of map.cuh */
     TRY(occupancy(ctx, pr.fn, pr.block, smem, &pr.per_sm));
     const int grid = (int)std::min<long long>(tiles, (long long)ctx->sm_count * pr.per_sm);

@@ -28,6 +28,7 @@
  */
 #pragma once
 #include "../cubits/accb_vec.cuh"
+#include "../cubits/accb_tma.cuh"
 
 namespace accb {
 
@@ -261,6 +262,97 @@ __device__ __forceinline__ void map_transposed_body(const accb_kparams &p) {
     }
 }
 
+/* ---- the transposed form with the copy engine on both sides (one 4-byte input, one 4-byte output): a block
+ * owns one 64x64 tile.  One thread asks for the tile as two boxes of 32 columns x 64 rows through a tensor map
+ * with the hardware's 128-byte swizzle (a row of 32 values is 128 bytes; its 16-byte piece j lands at position
+ * j ^ (row & 7)); every thread then takes one 4x4 block -- four 16-byte reads --, transposes it in registers,
+ * applies the functor and writes four 16-byte pieces into the transposed tile, laid out the same way; one
+ * thread hands that tile to the engine as two boxes of the result.  No load or store instruction touches global
+ * memory, and the engine clips tiles that hang over the edge of the matrices (reads outside give zeros).
+ * The 8 threads that share a shared-memory transaction take blocks (br, bc) = (8A + (u + s) mod 8, 8B + u),
+ * u = 0..7: then both their reads (piece bc, rows 4 br + i) and their writes (piece br, rows 4 bc + k) fall
+ * into 8 different 16-byte columns of the banks. ---- */
+template <class Fn>
+__host__ __device__ constexpr bool trans_tma_ok() {
+    typedef typename Fn::In In;
+    typedef typename Fn::Out Out;
+    if constexpr (In::size == 1 && Out::size == 1)
+        return sizeof(typename type_at<0, In>::type) == 4 && sizeof(typename type_at<0, Out>::type) == 4;
+    else
+        return false;
+}
+constexpr int kTransTmaSmem = 4 * 8192 + 1024; /* two boxes in, two boxes out, room to align to 1024 bytes */
+
+template <class Fn, int CTA>
+__device__ __forceinline__ void map_transposed_tma_body(const accb_kparams &p, const TensorMap *tin, const TensorMap *tout) {
+    if constexpr (trans_tma_ok<Fn>()) {
+        static_assert(CTA == 256, "one 4x4 block of the 64x64 tile per thread");
+        typedef typename type_at<0, typename Fn::In>::type E;
+        typedef typename type_at<0, typename Fn::Out>::type U;
+        extern __shared__ __align__(128) unsigned char s_dyn[];
+        __shared__ __align__(8) unsigned long long s_bar;
+        /* the swizzle works on address bits: the boxes start on multiples of 1024 bytes */
+        unsigned char *s_in = s_dyn + ((1024u - (smem_addr(s_dyn) & 1023u)) & 1023u);
+        unsigned char *s_out = s_in + 2 * 8192;
+        const Env env(p);
+        const int H = (int)p.ip[0], W = (int)p.ip[1]; /* of the source; the result has W rows of H columns */
+        const int tiles_x = (W + 63) / 64;
+        const int y0 = (int)(blockIdx.x / tiles_x) * 64, x0 = (int)(blockIdx.x % tiles_x) * 64;
+        unsigned int *err = static_cast<unsigned int *>(p.aux[1]);
+        if (threadIdx.x == 0) {
+            mbar_init(&s_bar, 1);
+            fence_mbar_init();
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            mbar_expect_tx(&s_bar, 2 * 8192);
+            tensor_g2s_2d(s_in, tin, x0, y0, &s_bar);
+            tensor_g2s_2d(s_in + 8192, tin, x0 + 32, y0, &s_bar);
+        }
+        int tries = 0;
+        while (!mbar_try_wait(&s_bar, 0)) {
+            if (++tries > (1 << 16)) { /* bounded: flag the result invalid and go on */
+                atomicExch(err, 1u);
+                break;
+            }
+        }
+        const int u = threadIdx.x & 7, g = threadIdx.x >> 3;
+        const int br = 8 * ((g >> 3) & 1) + ((u + (g & 7)) & 7), bc = 8 * (g >> 4) + u;
+        uint4 a[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = 4 * br + i;
+            a[i] = *reinterpret_cast<const uint4 *>(s_in + (bc >> 3) * 8192 + r * 128 + (((bc & 7) ^ (r & 7)) << 4));
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int r = 4 * bc + k; /* row of the transposed tile = column of the source */
+            const unsigned in4[4] = {k == 0 ? a[0].x : k == 1 ? a[0].y : k == 2 ? a[0].z : a[0].w,
+                                     k == 0 ? a[1].x : k == 1 ? a[1].y : k == 2 ? a[1].z : a[1].w,
+                                     k == 0 ? a[2].x : k == 1 ? a[2].y : k == 2 ? a[2].z : a[2].w,
+                                     k == 0 ? a[3].x : k == 1 ? a[3].y : k == 2 ? a[3].z : a[3].w};
+            unsigned o4[4];
+            const long long i0 = (long long)(x0 + r) * H + y0 + 4 * br; /* position in the result */
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                U o;
+                Fn::apply(env, env.p.base + i0 + q, trans_unbits<E>(in4[q]), o);
+                o4[q] = trans_bits(o);
+            }
+            *reinterpret_cast<uint4 *>(s_out + (br >> 3) * 8192 + r * 128 + (((br & 7) ^ (r & 7)) << 4)) =
+                make_uint4(o4[0], o4[1], o4[2], o4[3]);
+        }
+        fence_async_shared();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            tensor_s2g_2d(tout, y0, x0, s_out);
+            tensor_s2g_2d(tout, y0 + 32, x0, s_out + 8192);
+            bulk_commit();
+            bulk_wait_read(); /* the shared memory must outlive the engine's reads */
+        }
+    }
+}
+
 /* the transposed form needs element-wise inputs; without any it has nothing to do */
 template <class Fn, int CTA>
 __device__ __forceinline__ void map_transposed_or_nothing(const accb_kparams &p) {
@@ -288,10 +380,12 @@ __host__ __device__ constexpr int map_transposed_smem() {
 #endif
 
 /* Entry point named after the reference's kernel (Mapping.hs:53), and the form for transposed
- * inputs.  Metadata: {.., 0, 0, U, element-wise input components, shared memory of the transposed form}. */
+ * inputs.  Metadata: {.., 0, 0, U, element-wise input components, shared memory of the transposed form, -,
+ * whether the tensor-map transposed form exists, its shared memory}. */
 #define ACCB_INSTANTIATE_MAP(Fn)                                                        \
     ACCB_META12(1, ACCB_MAP_CTA, 0, 0, ACCB_MAP_U, Fn::In::size,                        \
-                (accb::map_transposed_smem<Fn>()), 0, 0, 0, 0, Fn::In::size)            \
+                (accb::map_transposed_smem<Fn>()), 0, accb::trans_tma_ok<Fn>() ? 1 : 0, \
+                accb::kTransTmaSmem, 0, Fn::In::size)                                   \
     extern "C" __global__ void __launch_bounds__(ACCB_MAP_CTA)                          \
         map(const __grid_constant__ accb_kparams p) {                                   \
         accb::map_body<Fn, ACCB_MAP_CTA, ACCB_MAP_U>(p);                                \
@@ -299,4 +393,9 @@ __host__ __device__ constexpr int map_transposed_smem() {
     extern "C" __global__ void __launch_bounds__(ACCB_MAP_CTA, ACCB_TRANS_MINB)         \
         map_transposed(const __grid_constant__ accb_kparams p) {                        \
         accb::map_transposed_or_nothing<Fn, ACCB_MAP_CTA>(p);                           \
+    }                                                                                   \
+    extern "C" __global__ void __launch_bounds__(ACCB_MAP_CTA, 6)                       \
+        map_transposed_tma(const __grid_constant__ accb_kparams p, const __grid_constant__ accb::TensorMap tin, \
+                           const __grid_constant__ accb::TensorMap tout) {              \
+        accb::map_transposed_tma_body<Fn, ACCB_MAP_CTA>(p, &tin, &tout);                \
     }

@@ -384,6 +384,15 @@ struct BlackScholesA {{
 """)
 
 # zipWith with user scalars: out = a*x + y, a read from the scalar block
+# one value in, one out, and the element's index: out[i] = 2 x + (i mod 5)
+SCALE_PLUS_INDEX = KernelSpec("map", "ScalePlusIndex", f"""
+struct ScalePlusIndex {{
+    using In = accb::types<float>;
+    using Out = accb::types<float>;
+    {_D} void apply(const accb::Env &, long long i, float x, float &o) {{ o = 2.0f * x + (float)(i % 5); }}
+}};
+""")
+
 SAXPY = KernelSpec("map", "Saxpy", f"""
 struct Saxpy {{
     using In = accb::types<float, float>;

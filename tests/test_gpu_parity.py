@@ -106,6 +106,27 @@ def test_map_over_transposed_inputs_through_shared_memory_tiles(ctx, P, accb, to
         ctx.map_transposed(P.SAXPY, [dev(t, x), dev(t, y)], t.empty((h + 1, w), device="cuda"), scalars=np.float32(1))
 
 
+@pytest.mark.parametrize("h,w", [(4, 4), (64, 64), (68, 132), (128, 192), (1000, 36), (256, 1028), (257, 1028), (2048, 4100)])
+def test_map_over_one_transposed_input_through_tensor_map_copies(ctx, P, accb, torch_cuda, rng, monkeypatch, h, w):
+    """One 4-byte value in and one out: the copy engine moves the 64x64 tiles through tensor maps (extents that are
+    multiples of 4; tiles that hang over the edge are clipped by the engine), every other shape takes the
+    load / store form.  Both against numpy, with the element index the functor is told, and against each other."""
+    t = torch_cuda
+    x = rng.standard_normal((h, w)).astype(np.float32)
+    out = t.full((w, h), np.nan, dtype=t.float32, device="cuda")
+    ctx.map_transposed(P.SCALE_PLUS_INDEX, [dev(t, x)], out)
+    ctx.sync()
+    ref = 2.0 * x.T.astype(np.float64) + (np.arange(h * w).reshape(w, h) % 5)
+    close(out.cpu().numpy(), ref, 1e-6)
+    monkeypatch.setenv("ACCB_TRANSPOSE_TMA", "0")  # read when a context is created
+    plain = accb.Context(0)
+    out2 = t.full((w, h), np.nan, dtype=t.float32, device="cuda")
+    plain.map_transposed(P.SCALE_PLUS_INDEX, [dev(t, x)], out2)
+    plain.sync()
+    assert t.equal(out, out2)
+    plain.destroy()
+
+
 @pytest.mark.parametrize("n", [7, 4096, 12345])
 def test_map_mixed_widths(ctx, P, torch_cuda, rng, n):
     t = torch_cuda
