@@ -98,8 +98,15 @@
 #ifndef ACCB_SCAN_TMA
 #define ACCB_SCAN_TMA 1 /* 0: hold the tile in registers instead of shared memory */
 #endif
-#ifndef ACCB_SCAN_CTA
-#define ACCB_SCAN_CTA (ACCB_SCAN_TMA ? 256 : 128)
+/* threads per block.  With the tile in shared memory: 256, except that elements of more than 4 bytes (over all
+ * input components) take 128 threads and 9 rows -- 36 KB tiles, six per SM: Int64 2^27 at 5716 GB/s against
+ * 5510 with 256 threads x 4 rows */
+#ifdef ACCB_SCAN_CTA
+#define ACCB_SCAN_CTA_FOR(Fn) ACCB_SCAN_CTA
+#elif ACCB_SCAN_TMA
+#define ACCB_SCAN_CTA_FOR(Fn) (accb::scan_cta_for<Fn::In>::value)
+#else
+#define ACCB_SCAN_CTA_FOR(Fn) 128
 #endif
 /* rows of CTA x 4 elements per tile.  With the tile in shared memory the row count follows the bytes
  * of one element over all input components, so that a tile stays at 32 KB and six blocks fit an SM */
@@ -591,11 +598,17 @@ __device__ __forceinline__ void scan_block_level(const typename Fn::elem *s_warp
 /* ---- full, aligned tile.  SMEM: the raw inputs sit in shared memory (put
  * there by the TMA engine) and are read twice; otherwise they are loaded into
  * registers once and kept there. ---- */
-/* tile rows for a 32 KB tile: 8 for up to 4 bytes per element (all components), 4 up to 8, else 2 */
+/* tile shape: 256 threads x 8 rows (32 KB) for up to 4 bytes per element (all components), 128 threads x 9 rows
+ * (36 KB) up to 8, else 256 x 2 */
 template <class L>
 struct scan_rows_for {
     static constexpr int bpe = smem_offset<L, L::size, 128>::value / 128;
-    static constexpr int value = bpe <= 4 ? 8 : (bpe <= 8 ? 4 : 2);
+    static constexpr int value = bpe <= 4 ? 8 : (bpe <= 8 ? 9 : 2);
+};
+template <class L>
+struct scan_cta_for {
+    static constexpr int bpe = smem_offset<L, L::size, 128>::value / 128;
+    static constexpr int value = (bpe > 4 && bpe <= 8) ? 128 : 256;
 };
 
 /* tile rows of the block-cyclic entries, 128 threads: 36 KB of input per tile */
@@ -904,9 +917,9 @@ __device__ __forceinline__ void scan_body(const accb_kparams &p) {
 /* Entry points named after the reference's kernels (PrefixSum.hs:208,313):
  * exclusive and inclusive, left and right. */
 #define ACCB_SCAN_ENTRY(Fn, name, right, incl)                                                 \
-    extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA, ACCB_SCAN_MINB_FOR(Fn))        \
+    extern "C" __global__ void __launch_bounds__(ACCB_SCAN_CTA_FOR(Fn), ACCB_SCAN_MINB_FOR(Fn)) \
         name(const __grid_constant__ accb_kparams p) {                                         \
-        accb::scan_body<Fn, ACCB_SCAN_CTA, ACCB_SCAN_ROWS_FOR(Fn), right, incl, ACCB_SCAN_TMA != 0, false>(p); \
+        accb::scan_body<Fn, ACCB_SCAN_CTA_FOR(Fn), ACCB_SCAN_ROWS_FOR(Fn), right, incl, ACCB_SCAN_TMA != 0, false>(p); \
     }
 #define ACCB_SCAN_BC_ENTRY(Fn, name, incl)                                                     \
     extern "C" __global__ void __launch_bounds__(ACCB_SCAN_BC_CTA, ACCB_SCAN_BC_MINB)          \
@@ -917,10 +930,10 @@ __device__ __forceinline__ void scan_body(const accb_kparams &p) {
 /* metadata: record bytes, tile elements, rows, ticket mode, dynamic shared memory, bytes of a value; of the
  * block-cyclic entries: threads, tile elements, dynamic shared memory */
 #define ACCB_INSTANTIATE_SCAN(Fn)                                                              \
-    ACCB_META12(5, ACCB_SCAN_CTA, accb::TileStatus<Fn::elem>::kBytes,                          \
-               ACCB_SCAN_CTA * ACCB_SCAN_ROWS_FOR(Fn) * 4, ACCB_SCAN_ROWS_FOR(Fn), ACCB_SCAN_TICKET ? 2 : 0,   \
+    ACCB_META12(5, ACCB_SCAN_CTA_FOR(Fn), accb::TileStatus<Fn::elem>::kBytes,                  \
+               ACCB_SCAN_CTA_FOR(Fn) * ACCB_SCAN_ROWS_FOR(Fn) * 4, ACCB_SCAN_ROWS_FOR(Fn), ACCB_SCAN_TICKET ? 2 : 0,   \
                ACCB_SCAN_TMA ? (accb::smem_offset<Fn::In, Fn::In::size,                        \
-                                                  ACCB_SCAN_CTA * ACCB_SCAN_ROWS_FOR(Fn) * 4>::value)  \
+                                                  ACCB_SCAN_CTA_FOR(Fn) * ACCB_SCAN_ROWS_FOR(Fn) * 4>::value)  \
                              : 0,                                                              \
                sizeof(Fn::elem), ACCB_SCAN_BC_CTA, ACCB_SCAN_BC_CTA * ACCB_SCAN_BC_ROWS_FOR(Fn) * 4,  \
                (accb::smem_offset<Fn::In, Fn::In::size, ACCB_SCAN_BC_CTA * ACCB_SCAN_BC_ROWS_FOR(Fn) * 4>::value), Fn::In::size) \

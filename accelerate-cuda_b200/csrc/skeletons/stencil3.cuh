@@ -11,9 +11,21 @@
  * along z: the 2*RZ+1 input planes a z-step needs sit in a ring of tiles in
  * shared memory, every z-step brings in ONE new plane tile (with its halo in
  * y and x) and retires the oldest, so an input element is requested from
- * memory once per block that needs it instead of once per tap.  The threads
- * of a warp read and write 512 contiguous bytes per row; a thread computes 4
- * adjacent x per row from 16-byte shared-memory reads.
+ * memory once per block that needs it instead of once per tap.  The new
+ * plane is fetched with asynchronous 16-byte copies (cp.async) one z-step
+ * ahead, into a spare slot of the ring, while the current step is computed.
+ * The threads of a warp read and write 512 contiguous bytes per row; a thread
+ * computes 4 adjacent x per row from 16-byte shared-memory reads, its halo
+ * columns handed over by the neighbouring lanes.
+ *
+ * Tried and dropped: a thread that owns one row for the whole run and keeps
+ * the 2*RZ+1 planes of its neighbourhood in registers, reading only the new
+ * plane per z-step.  Shared-memory traffic fell to a third (ncu: l1tex 84 % ->
+ * 30 % busy), the time did not (0.56 ms against 0.45 ms on 512^3): a 3x3x3
+ * window of 54 values plus the functor's temporaries spill at three blocks per
+ * SM, and with one row per warp and step the blocks spend their time at the
+ * barrier.  The kernel is bound by instruction issue (27 multiply-adds per
+ * output for a full 3x3x3 functor), not by shared memory or DRAM.
  *
  * Boundary semantics as for the lower ranks (Extra.hs:200-226): every
  * coordinate is mapped on its own; with Constant the whole tap is the constant
@@ -32,15 +44,19 @@
 #pragma once
 #include "../cubits/accb_vec.cuh"
 #include "../cubits/accb_warp.cuh"
+#include "../cubits/accb_tma.cuh"
 #include "stencil.cuh"
 
 #ifndef ACCB_STENCIL3_CTA
 #define ACCB_STENCIL3_CTA 256
 #endif
 #ifndef ACCB_STENCIL3_TY
-#define ACCB_STENCIL3_TY 16 /* rows of a block's column */
+#define ACCB_STENCIL3_TY 32 /* rows of a block's column: four per warp (512^3, 27 taps: 0.45 ms against 0.53 ms with 16) */
 #endif
 #define ACCB_STENCIL3_TX 128 /* columns of a block's column: one warp row */
+#ifndef ACCB_STENCIL3_MINB
+#define ACCB_STENCIL3_MINB 3 /* resident blocks per SM the compiler must leave registers for */
+#endif
 
 namespace accb {
 
@@ -60,7 +76,7 @@ struct Stencil3Tile {
     static constexpr int PITCH = TX + 2 * PAD;
     static constexpr int ROWS = TY + 2 * Fn::RY;
     static constexpr int PLANE = ROWS * PITCH;     /* values per plane tile */
-    static constexpr int RING = 2 * Fn::RZ + 1;    /* plane tiles resident */
+    static constexpr int RING = 2 * Fn::RZ + 2;    /* plane tiles resident: the 2*RZ+1 in use and the one on its way */
     static constexpr int BYTES = RING * PLANE * 4;
 };
 
@@ -80,7 +96,9 @@ __device__ __forceinline__ void stencil3_fill(typename Fn::in_t *tile, const typ
         const int x = x0 + 4 * v;
         T *dst = tile + r * G::PITCH + G::PAD + 4 * v;
         if (zz >= 0 && yy >= 0 && vec_ok && x + 3 < W) {
-            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(plane + (long long)yy * W + x);
+            /* asynchronous: no register holds the data, the caller waits for the group before the tile is read */
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(plane + (long long)yy * W + x)
+                         : "memory");
         } else {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -124,6 +142,13 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
     const long long ntask = (long long)tiles_x * tiles_y * zchunks;
     const int lane = lane_id(), w = warp_id();
 
+    /* plane z of the cube lives in ring slot (z + RZ) mod RING (z >= -RZ) */
+    auto slot = [&](int z) { return ring + ((z + RZ) % G::RING) * G::PLANE; };
+    auto fetch = [&](int z, int y0, int x0) {
+        stencil3_fill<Fn, CTA>(slot(z), src, bound_coord(z, D, mode), y0, x0, H, W, mode, cval, vec_ok);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
     for (long long task = blockIdx.x; task < ntask; task += gridDim.x) {
         /* x fastest, then y, then the z-chunk: blocks that run together share halo rows and planes in L2 */
         const int tx = (int)(task % tiles_x);
@@ -132,34 +157,36 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
         const int x0 = tx * G::TX, y0 = ty * G::TY, z0 = tz * zrun;
         const int z1 = min(D, z0 + zrun);
         __syncthreads(); /* the previous task's last reads of the ring */
-        /* planes z0 - RZ .. z0 + RZ - 1 go into ring slots by (plane + RZ) mod RING */
-        for (int dz = -RZ; dz < RZ; ++dz) {
-            const int z = z0 + dz;
-            stencil3_fill<Fn, CTA>(ring + (((z + RZ) % G::RING + G::RING) % G::RING) * G::PLANE, src, bound_coord(z, D, mode), y0,
-                                   x0, H, W, mode, cval, vec_ok);
-        }
+        /* planes z0 - RZ .. z0 + RZ are needed by the first step */
+        for (int dz = -RZ; dz <= RZ; ++dz) fetch(z0 + dz, y0, x0);
         for (int z = z0; z < z1; ++z) {
-            const int zin = z + RZ;
-            stencil3_fill<Fn, CTA>(ring + (((zin + RZ) % G::RING + G::RING) % G::RING) * G::PLANE, src, bound_coord(zin, D, mode),
-                                   y0, x0, H, W, mode, cval, vec_ok);
+            /* everything fetched so far has landed; then start on the plane the NEXT step adds, into the slot that
+             * the step before this one read last */
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();
+            if (z + 1 < z1) fetch(z + 1 + RZ, y0, x0);
             /* warp w computes rows w, w + 8, ..: lane l the columns 4l .. 4l + 3 */
             for (int r = w; r < G::TY; r += CTA / 32) {
                 const int y = y0 + r, x = x0 + 4 * lane;
-                if (y < H && x < W) {
+                if (y < H) { /* the same for every lane of the warp: the shuffles below see all 32 */
                     T win[2 * RZ + 1][2 * RY + 1][4 + 2 * RX];
 #pragma unroll
                     for (int dz = 0; dz <= 2 * RZ; ++dz) {
-                        const T *pl = ring + (((z - RZ + dz + RZ) % G::RING + G::RING) % G::RING) * G::PLANE;
+                        const T *pl = slot(z - RZ + dz);
 #pragma unroll
                         for (int dy = 0; dy <= 2 * RY; ++dy) {
                             const T *row = pl + (r + dy) * G::PITCH + G::PAD + 4 * lane;
                             const uint4 c = *reinterpret_cast<const uint4 *>(row);
                             memcpy(&win[dz][dy][RX], &c, 16);
+                            /* the halo columns are the neighbouring lanes' centre columns: shuffles instead of 4-byte
+                             * reads 16 bytes apart (a four-way bank conflict each); only the two lanes at the ends of
+                             * the row read theirs from the tile */
 #pragma unroll
                             for (int h = 0; h < RX; ++h) {
-                                win[dz][dy][h] = row[h - RX];
-                                win[dz][dy][RX + 4 + h] = row[4 + h];
+                                const T from_left = shfl_up(win[dz][dy][4 + h], 1);     /* lane - 1's last RX columns */
+                                const T from_right = shfl_down(win[dz][dy][RX + h], 1); /* lane + 1's first RX columns */
+                                win[dz][dy][h] = lane == 0 ? row[h - RX] : from_left;
+                                win[dz][dy][RX + 4 + h] = lane == 31 ? row[4 + h] : from_right;
                             }
                         }
                     }
@@ -176,7 +203,9 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
                         o[k] = Fn::apply(env, t);
                     }
                     U *dst = out + ((long long)z * H + y) * W + x;
-                    if (vec_ok && sizeof(U) == 4 && x + 3 < W) {
+                    if (x >= W) {
+                        /* beyond the last column: nothing to store */
+                    } else if (vec_ok && sizeof(U) == 4 && x + 3 < W) {
                         uint4 q;
                         memcpy(&q, o, 16);
                         __stcs(reinterpret_cast<uint4 *>(dst), q);
@@ -187,9 +216,9 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
                     }
                 }
             }
-            __syncthreads(); /* the oldest plane's slot is refilled next */
         }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 }  // namespace accb
@@ -198,7 +227,7 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
 #define ACCB_INSTANTIATE_STENCIL3(Fn)                                                          \
     ACCB_META7(10, ACCB_STENCIL3_CTA, sizeof(Fn::in_t), ACCB_STENCIL3_TY, ACCB_STENCIL3_TX, 2 * Fn::RZ, \
                accb::Stencil3Tile<Fn>::BYTES)                                                  \
-    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL3_CTA)                            \
+    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL3_CTA, ACCB_STENCIL3_MINB)        \
         stencil3(const __grid_constant__ accb_kparams p) {                                     \
         accb::stencil3_body<Fn, ACCB_STENCIL3_CTA>(p);                                         \
     }

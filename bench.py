@@ -766,7 +766,7 @@ class Smooth1dWorkload(Workload):
 class TransposeWorkload(Workload):
     """`transpose m` made manifest: the map skeleton over 64x64 shared-memory tiles (the reference runs a transpose
     as a backpermute, i.e. a gather)."""
-    name, dtype = "transpose, Float32 8192 x 8192 (map over shared-memory tiles)", "f32"
+    name, dtype = "transpose, Float32 8192 x 8192 (tiles moved by the copy engine through tensor maps)", "f32"
 
     def setup(self, n=None):
         t, W = self.t, self.W
@@ -809,10 +809,102 @@ class HistHotWorkload(HistWorkload):
         self.ctx.sync()
 
 
-SECONDARY_KERNEL = {"hist_equal": "permute_smem", "hist_hot16": "permute_smem", "scan64": "scanl", "shortrows": "fold_staged", "smvm": "foldSeg_staged", "smooth1d": "stencil_line",
-                    "transpose": "map_transposed"}
-SECONDARY = {"hist_equal": HistEqualWorkload, "hist_hot16": HistHotWorkload, "scan64": Scan64Workload, "shortrows": ShortRowsWorkload, "smvm": SmvmWorkload, "smooth1d": Smooth1dWorkload,
-             "transpose": TransposeWorkload}
+class ScanChainedWorkload(Workload):
+    """The kernel of the scan over several GPUs on ONE GPU (a world of one): the vector in blocks of 32 tiles, block
+    records written and read by the same GPU.  What the chain of blocks costs without any NVLink latency."""
+    name, dtype = "scanl (+) 0, Int32, 2^28, block-chained kernel of the multi-GPU scan (world of one)", "int32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.k = self.ctx.kernel(self.functor("SCAN_ADD_I32")).wait()
+        self.block = 32 * self.ctx.scan_tile(self.k)
+        self.n = (n or W.N28) // self.block * self.block
+        self.x = t.empty(self.n, dtype=t.int32, device="cuda")
+        self.ctx.gen_uniform_i32(self.x, self.n, 0, W.SEED, W.S_SCAN, 16)
+        self.out = t.empty(self.n + 1, dtype=t.int32, device="cuda")
+        _, _, scratch = self.accb.scan_layout(1, 0, self.n, self.block)
+        self.chain = self.accb.Peer(self.ctx, 0, 1, scratch, lambda b: [b])
+        self.bytes = W.bytes_scan(self.n)
+        self.ctx.sync()
+
+    def step(self):
+        self.chain.scan(self.k, [self.x], self.n, self.out, seed=np.int32(0), block_elems=self.block)
+        return 1
+
+    def verify(self):
+        t = self.t
+        ok = bool(t.equal(self.out[1:] - self.out[:-1], self.x)) and int(self.out[0]) == 0
+        return ok and int(self.out[-1]) == int(np.array(int(self.x.sum(dtype=t.int64)) & 0xffffffff, np.uint32).astype(np.int32))
+
+
+class TransposeLoadStoreWorkload(TransposeWorkload):
+    """The same transpose with the tiles moved by load and store instructions (a context created with
+    ACCB_TRANSPOSE_TMA=0) instead of the copy engine."""
+    name = "transpose, Float32 8192 x 8192 (tiles moved by loads and stores)"
+
+    def setup(self, n=None):
+        old = os.environ.get("ACCB_TRANSPOSE_TMA")
+        os.environ["ACCB_TRANSPOSE_TMA"] = "0"  # read when a context is created
+        try:
+            self.ctx = self.accb.Context(self.ctx.device)
+        finally:
+            if old is None:
+                del os.environ["ACCB_TRANSPOSE_TMA"]
+            else:
+                os.environ["ACCB_TRANSPOSE_TMA"] = old
+        super().setup(n)
+
+
+class Stencil3dWorkload(Workload):
+    """27-point weighted stencil over a 512^3 cube (rank 3): a block marches along z with three plane tiles in
+    shared memory."""
+    name, dtype = "stencil 3x3x3 Clamp, Float32 512^3", "f32"
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        self.side = n or 512
+        shape = (self.side,) * 3
+        self.v = t.empty(shape, dtype=t.float32, device="cuda")
+        self.ctx.gen_uniform_f32(self.v, self.side ** 3, 0, W.SEED, W.S_GRID, 0.0, 1.0)
+        self.out = t.empty_like(self.v)
+        self.k = self.ctx.kernel(self.P.WEIGHTED27).wait()
+        self.bytes = 8 * self.side ** 3
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.stencil(self.k, self.v, self.out, boundary="clamp")
+        return 1
+
+    def verify(self):
+        # the first 12 planes against the oracle (clamped at the cut: the last plane compared is two away from it)
+        oracle = importlib.import_module("oracle")
+        w = (np.arange(27, dtype=np.float64).reshape(3, 3, 3) + 1) / 378.0
+        ref = oracle.stencil3d(self.v[:12].cpu().numpy(), w, "clamp")
+        return close_to(self.out[:10].cpu().numpy(), ref[:10], 1e-6)
+
+
+class Stencil3dLaplaceWorkload(Stencil3dWorkload):
+    """The 7-point Laplacian over the same cube: the taps a functor does not use are never read."""
+    name = "stencil 7-point Laplacian Clamp, Float32 512^3"
+
+    def setup(self, n=None):
+        super().setup(n)
+        self.k = self.ctx.kernel(self.P.LAPLACE3).wait()
+
+    def verify(self):
+        oracle = importlib.import_module("oracle")
+        w = np.zeros((3, 3, 3))
+        w[1, 1, 1] = -6
+        for z, y, x in ((0, 1, 1), (2, 1, 1), (1, 0, 1), (1, 2, 1), (1, 1, 0), (1, 1, 2)):
+            w[z, y, x] = 1
+        ref = oracle.stencil3d(self.v[:12].cpu().numpy(), w, "clamp")
+        return close_to(self.out[:10].cpu().numpy(), ref[:10], 1e-5)
+
+
+SECONDARY_KERNEL = {"scan_chained": "scanl_bc", "hist_equal": "permute_smem", "hist_hot16": "permute_smem", "scan64": "scanl", "shortrows": "fold_staged", "smvm": "foldSeg_staged", "smooth1d": "stencil_line",
+                    "transpose": "map_transposed_tma", "transpose_loadstore": "map_transposed", "stencil3d": "stencil3", "stencil3d_laplace": "stencil3"}
+SECONDARY = {"scan_chained": ScanChainedWorkload, "hist_equal": HistEqualWorkload, "hist_hot16": HistHotWorkload, "scan64": Scan64Workload, "shortrows": ShortRowsWorkload, "smvm": SmvmWorkload, "smooth1d": Smooth1dWorkload,
+             "transpose": TransposeWorkload, "transpose_loadstore": TransposeLoadStoreWorkload, "stencil3d": Stencil3dWorkload, "stencil3d_laplace": Stencil3dLaplaceWorkload}
 
 
 # ---- the reference's own algorithms on the same GPU and the same device inputs (baseline/refskel)
