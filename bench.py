@@ -1354,6 +1354,20 @@ def main():
             del w2
             torch.cuda.empty_cache()
             ScanWorkload.distribution = "block-cyclic"
+            # ---- strong scaling: ONE vector of 2^28 elements dealt over all GPUs (the headline's own size), against
+            # ---- one GPU scanning all of it in this run
+            w2 = ScanWorkload(accb, ctx, torch, rank, world)
+            w2.setup(w2.W.N28 // world)
+            if w2.cyclic:
+                ms2, _, ok2 = measure(torch, dist, w2, 10, 3)
+                one = table["scan"]["unsharded_ms"]
+                g = w2.bytes * world / (ms2 * 1e-3) / 1e9
+                table["scan_strong"] = {"GB/s": g, "ms": ms2, "parity_check": ok2, "elements_total": w2.n_global,
+                                        "one_gpu_ms": one, "speedup": one / ms2, "efficiency": one / ms2 / world,
+                                        "workload": "scanl (+) 0, Int32, 2^28 elements over all GPUs"}
+            release(torch, dist, w2)
+            del w2
+            torch.cuda.empty_cache()
         line["skeletons"] = table
     elif rank == 0:
         line["e2e"] = None
