@@ -139,6 +139,8 @@ struct Tuning {
     long long foldseg_stage_max = 384; /* longest average segment the staged foldSeg takes */
     int foldseg_fill8 = 6;             /* eighths of the shared-memory window a run of segments aims to fill */
     int foldseg_lanes = 0;             /* lanes per segment of the staged foldSeg; 0: by segment length */
+    long long foldseg_balanced_min = 4; /* shortest average segment the element-balanced foldSeg takes; < 0: never */
+    int foldseg_span = 0;              /* tiles per block of the element-balanced foldSeg; 0: by size */
     int permute_replicas = 4;          /* shared-memory copies of a privatised permute destination */
     bool stencil_no_tile = false;
     int stencil_rows = 64;             /* band height of the register-form stencil */

@@ -111,6 +111,8 @@ void Tuning::read_environment() {
     foldseg_stage_max = num("ACCB_FOLDSEG_STAGE_MAX", foldseg_stage_max);
     foldseg_fill8 = (int)std::min(8LL, std::max(1LL, num("ACCB_FOLDSEG_STAGE_FILL8", foldseg_fill8)));
     foldseg_lanes = (int)std::max(0LL, num("ACCB_FOLDSEG_STAGE_LANES", 0));
+    foldseg_balanced_min = num("ACCB_FOLDSEG_BALANCED_MIN", foldseg_balanced_min);
+    foldseg_span = (int)std::max(0LL, num("ACCB_FOLDSEG_SPAN", 0));
     permute_replicas = (int)std::max(1LL, num("ACCB_PERMUTE_REPLICAS", permute_replicas));
     stencil_no_tile = getenv("ACCB_STENCIL_NO_TILE") != nullptr;
     stencil_rows = (int)std::max(1LL, num("ACCB_STENCIL_ROWS", stencil_rows));

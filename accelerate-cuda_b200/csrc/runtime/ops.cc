@@ -395,6 +395,8 @@ int accb_fold_dim_at(accb_context *ctx, accb_kernel *k, accb_stream stream, cons
     return launch(ctx, pr.fn, entry, grid, pr.block, 0, (cudaStream_t)stream, p);
 }
 
+static int scan_scratch(accb_context *ctx, cudaStream_t s, long long ntiles, int rec, StreamScratch **out, unsigned *epoch_out);
+
 int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
                   long long rows, long long cols, const int *offsets, long long nseg, const void *seed,
                   size_t seed_bytes, const accb_array *out) {
@@ -420,6 +422,33 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     const char *entry = group > 32 ? "foldSeg_block" : group == 32 ? "foldSeg" : group == 16 ? "foldSeg_g16" : group == 8 ? "foldSeg_g8" : "foldSeg_g4";
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
+    const bool aligned = (rows == 1 || cols % 16 == 0) && (p.flags & ACCB_F_VEC);
+    if (ctx->tune.foldseg_balanced_min >= 0 && avg >= ctx->tune.foldseg_balanced_min && aligned && pr.meta.v[8] > 0 &&
+        pr.meta.v[10] > 0 && cols >= pr.meta.v[8]) {
+        /* work divided by elements: the source row is cut into tiles whatever the segments are; a segment that
+         * spans blocks is completed through the blocks' status records (fold_balanced.cuh) */
+        const long long tile = pr.meta.v[8];
+        const long long tpr = ceil_div(cols, tile);
+        /* a block works through K consecutive tiles (the next tile's copy runs while the current one is reduced):
+         * as many as leave every SM about twenty blocks over the launch, eight at most */
+        const long long span = ctx->tune.foldseg_span > 0
+                                   ? ctx->tune.foldseg_span
+                                   : std::min<long long>(8, std::max<long long>(1, tpr / (20LL * ctx->sm_count)));
+        const long long blocks = rows * ceil_div(tpr, span);
+        if (blocks > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one foldSeg launch");
+        Prep pb;
+        TRY(get_function(ctx, k, "foldSeg_balanced", &pb.fn, &pb.meta));
+        cudaStream_t s = (cudaStream_t)stream;
+        StreamScratch *sc = nullptr;
+        unsigned epoch = 0;
+        TRY(scan_scratch(ctx, s, blocks, pr.meta.v[10], &sc, &epoch));
+        p.ip[3] = epoch;
+        p.ip[4] = tpr;
+        p.ip[5] = span;
+        p.aux[1] = sc->words + 2;
+        p.aux[2] = sc->status;
+        return launch(ctx, pb.fn, "foldSeg_balanced", (int)blocks, pr.meta.v[7], (size_t)pr.meta.v[9], s, p);
+    }
     if (avg <= ctx->tune.foldseg_stage_max && rows * nseg >= 4096 && (rows == 1 || cols % 16 == 0) && pr.meta.v[6] > 0 &&
         (p.flags & ACCB_F_VEC)) {
         /* short segments: a block stages a run of consecutive segments in shared memory and every

@@ -383,7 +383,8 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
 
 }  // namespace accb
 
-#include "fold_staged.cuh" /* short rows and segments */
+#include "fold_staged.cuh"   /* short rows and segments */
+#include "fold_balanced.cuh" /* segments of any length, work divided by elements */
 
 #define ACCB_FOLD_CTA 256
 #define ACCB_FOLD_U 4
@@ -434,12 +435,18 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
     }
 
 /* `foldSeg` is the reference's warp-per-segment form (Reduction.hs:430); the
- * others serve shorter and longer segments */
+ * others serve shorter and longer segments.  Metadata 7..10: block size, elements per tile, shared memory and bytes of a
+ * status record of the balanced form (0: not available for this functor) */
 #define ACCB_INSTANTIATE_FOLD_SEG(Fn)                                                   \
-    ACCB_META7(4, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>),                            \
-               accb::fold_stage_window<Fn::In>::value, 1, ACCB_FOLD_STAGE_CTA,          \
-               (accb::fold_stage_smem<Fn>()))                                           \
+    ACCB_META12(4, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>),                           \
+                accb::fold_stage_window<Fn::In>::value, 1, ACCB_FOLD_STAGE_CTA,         \
+                (accb::fold_stage_smem<Fn>()), ACCB_FOLD_BAL_CTA, (accb::fold_bal_tile<Fn>()),          \
+                (accb::fold_bal_smem<Fn>()), (accb::fold_bal_record<Fn>()), Fn::In::size) \
     ACCB_FOLD_STAGED_ENTRY(Fn, foldSeg_staged, true)                                    \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_BAL_CTA, ACCB_FOLD_BAL_MINB) \
+        foldSeg_balanced(const __grid_constant__ accb_kparams p) {                      \
+        accb::fold_balanced_or_nothing<Fn>(p);                                          \
+    }                                                                                   \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg, 32, 1)                                             \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g16, 16, 2)                                         \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g8, 8, 2)                                           \

@@ -368,6 +368,108 @@ def test_fold_seg_rank2(ctx, P, torch_cuda, rng):
     assert np.array_equal(out.cpu().numpy(), ref)
 
 
+@pytest.fixture(scope="module")
+def ctx_span3(accb, torch_cuda):
+    """A context whose element-balanced foldSeg gives every block three tiles (tuning is read when a context is made)."""
+    import os
+    old = os.environ.get("ACCB_FOLDSEG_SPAN")
+    os.environ["ACCB_FOLDSEG_SPAN"] = "3"
+    try:
+        c = accb.Context(0)
+    finally:
+        if old is None:
+            del os.environ["ACCB_FOLDSEG_SPAN"]
+        else:
+            os.environ["ACCB_FOLDSEG_SPAN"] = old
+    yield c
+    c.sync()
+
+
+def _seg_ref(x, offs, seed):
+    tot = np.concatenate([[0], np.cumsum(x.astype(np.int64))])
+    return (tot[offs[1:]] - tot[offs[:-1]] + seed).astype(np.int64)
+
+
+@pytest.mark.parametrize("case", ["tile_edges", "one_giant", "giant_among_short", "offsets_inside", "leading_empty",
+                                  "all_empty", "ragged_tail", "many_empty_runs"])
+@pytest.mark.parametrize("span", [0, 3])
+def test_fold_seg_balanced_by_elements(ctx, ctx_span3, P, torch_cuda, rng, case, span):
+    """The element-balanced form (tiles of 4096 Int32 elements, 32 per thread): segments that end exactly on
+    chunk and tile boundaries, one segment over many tiles, long segments among short ones, offsets that
+    cover only the middle of the source, empty segments first, last and in runs, no elements at all.  With
+    span 3 every block works through three tiles one after the other (what large inputs get by default)."""
+    t = torch_cuda
+    ctx = ctx_span3 if span else ctx
+    T, V = 4096, 32
+    pad_front = pad_back = 0
+    if case == "tile_edges":
+        lens = np.array([T, V, V, T - 2 * V, 1, T - 1, 2 * T, 0, 0, 3, T - 3, V - 1, 1, 5 * T + 17, 40])
+    elif case == "one_giant":
+        lens = np.array([0, 300 * T + 5, 0])
+    elif case == "giant_among_short":
+        lens = rng.integers(0, 12, 40000)
+        lens[[100, 20000, 39999]] = [50 * T + 1, 3 * T, 9 * T - 7]
+    elif case == "offsets_inside":
+        lens = rng.integers(0, 30, 3000)
+        pad_front, pad_back = 5000, 7003
+    elif case == "leading_empty":
+        lens = np.concatenate([np.zeros(2000, np.int64), rng.integers(1, 20, 2000), np.zeros(1500, np.int64)])
+        pad_front = 4099
+    elif case == "all_empty":
+        lens = np.zeros(3000, np.int64)
+        pad_front, pad_back = 3, 9000
+    elif case == "ragged_tail":
+        lens = rng.integers(0, 64, 1000)
+        lens[-1] += (1 - int(lens.sum())) % 4  # the source ends one element into a 16-byte unit
+    else:
+        lens = rng.integers(1, 9, 30000)
+        for first in range(0, 30000, 700):
+            lens[first:first + 300] = 0
+    offs = (pad_front + np.concatenate([[0], np.cumsum(lens)])).astype(np.int32)
+    n = int(offs[-1]) + pad_back
+    x = rng.integers(-1000, 1000, n).astype(np.int32)
+    out = t.full((lens.size,), 77, dtype=t.int32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_I32, [dev(t, x)], 1, n, dev(t, offs), lens.size, out, seed=np.int32(5))
+    ctx.sync()
+    assert np.array_equal(out.cpu().numpy().astype(np.int64), _seg_ref(x, offs, 5))
+    # fold1Seg: no seed, empty segments are left alone
+    out.fill_(77)
+    ctx.fold_seg(P.SEGSUM_I32, [dev(t, x)], 1, n, dev(t, offs), lens.size, out)
+    ctx.sync()
+    ref = np.where(lens > 0, _seg_ref(x, offs, 0), 77)
+    assert np.array_equal(out.cpu().numpy().astype(np.int64), ref)
+
+
+@pytest.mark.parametrize("span", [0, 3])
+def test_fold_seg_balanced_rows_and_two_inputs(ctx, ctx_span3, P, torch_cuda, rng, span):
+    """Rank 2 (every row cut by the same offsets, rows of several tiles) and a functor with two zipped inputs of
+    float32 and Int32 plus a gathered vector, accumulating in float64."""
+    t = torch_cuda
+    ctx = ctx_span3 if span else ctx
+    lens = rng.integers(0, 400, 200)
+    lens[17] = 20000
+    lens[0] += (-int(lens.sum())) % 16
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    m = rng.integers(-50, 50, (5, int(offs[-1]))).astype(np.int32)
+    out = t.zeros((5, lens.size), dtype=t.int32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_I32, [dev(t, m)], 5, m.shape[1], dev(t, offs), lens.size, out, seed=np.int32(1))
+    ctx.sync()
+    ref = np.stack([_seg_ref(m[r], offs, 1) for r in range(5)])
+    assert np.array_equal(out.cpu().numpy().astype(np.int64), ref)
+    nnz = rng.integers(0, 120, 4000)
+    nnz[[5, 3000]] = [30000, 8200]
+    offs = np.concatenate([[0], np.cumsum(nnz)]).astype(np.int32)
+    vals = rng.uniform(-1, 1, int(offs[-1])).astype(np.float32)
+    cols = rng.integers(0, 5000, int(offs[-1])).astype(np.int32)
+    vec = rng.uniform(-1, 1, 5000).astype(np.float32)
+    of = t.zeros(nnz.size, dtype=t.float32, device="cuda")
+    ctx.fold_seg(P.SMVM, [(dev(t, vals), dev(t, cols)), dev(t, vec)], 1, vals.size, dev(t, offs), nnz.size, of,
+                 seed=np.float32(0))
+    ctx.sync()
+    prod = np.concatenate([(vals * vec[cols]).astype(np.float64), [0.0]])
+    close(of.cpu().numpy(), np.add.reduceat(prod, offs[:-1]) * (nnz > 0), 1e-6)
+
+
 # ------------------------------------------------------------------ scans
 def test_scan_known_answers_from_the_reference_docs(ctx, P, accb, torch_cuda):
     """CodeGen/PrefixSum.hs:149-153, 162-166, 176-180."""
