@@ -22,6 +22,7 @@
 #define ACCB_MAX_AUX 6
 #define ACCB_MAX_IP 12
 #define ACCB_SCALAR_BYTES 64
+#define ACCB_FOLD_DEFER_MAX 1024 /* segments one foldSeg launch can hand over to its second launch (below) */
 
 /* accb_kparams.flags */
 #define ACCB_F_VEC 1u        /* every slot is 16-byte aligned: 128-bit path allowed */
@@ -46,5 +47,16 @@ typedef struct accb_kparams {
                                        is told is base + position (a launch may cover a piece of a larger array) */
     unsigned char scalars[ACCB_SCALAR_BYTES]; /* user scalars, packed in declaration order */
 } accb_kparams;
+
+
+/* Segments far longer than the rest would keep one thread, warp or block of a foldSeg kernel busy long after the
+ * others are done.  Such a segment is put on this list instead (runtime-owned scratch, zero between launches) and
+ * a second launch reduces the listed segments with all blocks. */
+typedef struct accb_deferred_segments {
+    unsigned int count;    /* segments put on the list (may exceed the capacity: the excess was not deferred) */
+    unsigned int finished; /* blocks of the second launch that are done; the last one clears the list */
+    long long unit[ACCB_FOLD_DEFER_MAX];        /* row * segments + segment */
+    unsigned int arrived[ACCB_FOLD_DEFER_MAX];  /* pieces of a listed segment reduced so far */
+} accb_deferred_segments;
 
 #endif

@@ -46,6 +46,7 @@ struct Driver {
     CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int *, CUfunction, int, size_t) = nullptr;
     CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                              CUstream, void **, void **) = nullptr;
+    CUresult (*LaunchKernelEx)(const CUlaunchConfig *, CUfunction, void **, void **) = nullptr; /* optional */
     CUresult (*CtxPushCurrent)(CUcontext) = nullptr;
     CUresult (*CtxPopCurrent)(CUcontext *) = nullptr;
     CUresult (*GetErrorString)(CUresult, const char **) = nullptr;
@@ -104,6 +105,8 @@ namespace accb_rt {
 
 constexpr int kRowCounterBase = 16; /* first row counter in StreamScratch::words */
 constexpr int kRowCounters = 4096;  /* most rows a split fold takes */
+constexpr int kDeferredBase = kRowCounterBase + kRowCounters; /* accb_deferred_segments of foldSeg (8-byte aligned) */
+constexpr int kDeferredWords = (int)(sizeof(accb_deferred_segments) / sizeof(unsigned));
 
 struct StreamScratch {
     void *status = nullptr;       /* scan tile status */
@@ -112,7 +115,8 @@ struct StreamScratch {
     void *partial = nullptr;      /* fold partials */
     size_t partial_bytes = 0;
     unsigned *words = nullptr;    /* [0] fold ticket, [1] scan ticket, [2] error word,
-                                     [kRowCounterBase..] per-row arrival counters of a split fold */
+                                     [kRowCounterBase..] per-row arrival counters of a split fold,
+                                     [kDeferredBase..] the list of segments a foldSeg hands to its second launch */
     unsigned scan_ticket = 0;     /* host mirror of words[1] */
     unsigned epoch = 0;           /* scan launches so far (below 2^29) */
     unsigned graph_epoch = 0;     /* scan launches recorded inside stream captures (offset by 2^29) */
@@ -131,7 +135,7 @@ struct CudaAllocator : DeviceAllocator {
 namespace accb_rt {
 /* Tuning knobs, read from the environment ONCE when a context is created (never on the launch path):
  *   ACCB_FOLD_STAGE_MAX, ACCB_FOLD_NO_STAGE, ACCB_FOLDSEG_STAGE_MAX, ACCB_FOLDSEG_STAGE_FILL8,
- *   ACCB_FOLDSEG_STAGE_LANES, ACCB_PERMUTE_REPLICAS, ACCB_STENCIL_NO_TILE, ACCB_STENCIL_ROWS,
+ *   ACCB_FOLDSEG_STAGE_LANES, ACCB_FOLDSEG_NO_DEFER, ACCB_PERMUTE_REPLICAS, ACCB_STENCIL_NO_TILE, ACCB_STENCIL_ROWS,
  *   ACCB_PIPELINE_CHUNK_LOG2, ACCB_NO_PIPELINE, ACCB_TRANSPOSE_TMA (0 or 1). */
 struct Tuning {
     long long fold_stage_max = 128;    /* longest row the staged thread-per-row fold takes */
@@ -139,8 +143,7 @@ struct Tuning {
     long long foldseg_stage_max = 384; /* longest average segment the staged foldSeg takes */
     int foldseg_fill8 = 6;             /* eighths of the shared-memory window a run of segments aims to fill */
     int foldseg_lanes = 0;             /* lanes per segment of the staged foldSeg; 0: by segment length */
-    long long foldseg_balanced_min = 4; /* shortest average segment the element-balanced foldSeg takes; < 0: never */
-    int foldseg_span = 0;              /* tiles per block of the element-balanced foldSeg; 0: by size */
+    bool foldseg_no_defer = false;     /* never hand long segments over to a second launch */
     int permute_replicas = 4;          /* shared-memory copies of a privatised permute destination */
     bool stencil_no_tile = false;
     int stencil_rows = 64;             /* band height of the register-form stencil */
@@ -209,6 +212,10 @@ void forget_context(accb_context *ctx); /* unload the modules loaded for a conte
 int occupancy(accb_context *ctx, CUfunction fn, int block, size_t smem, int *blocks_per_sm);
 int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, size_t smem,
            cudaStream_t stream, const accb_kparams &p, bool prefer_smem = true, void *extra1 = nullptr, void *extra2 = nullptr);
+/* a launch whose blocks may be scheduled while the launch before it on the stream drains; its kernel waits for
+ * that launch's results itself (griddepcontrol.wait) before it reads them */
+int launch_dependent(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, cudaStream_t stream,
+                     const accb_kparams &p);
 
 /* exchange buffers (peer.cu), as the block-cyclic scan driver sees them */
 struct PieceState;

@@ -50,6 +50,8 @@ const Driver &driver() {
         d.GetErrorString = (decltype(d.GetErrorString))sym("cuGetErrorString");
         d.MemcpyDtoH = (decltype(d.MemcpyDtoH))sym("cuMemcpyDtoH_v2");
         d.DevicePrimaryCtxGetState = (decltype(d.DevicePrimaryCtxGetState))sym("cuDevicePrimaryCtxGetState");
+        /* optional: lets a second launch be scheduled while its predecessor drains */
+        d.LaunchKernelEx = (decltype(d.LaunchKernelEx))dlsym(h, "cuLaunchKernelEx");
         /* optional: only the tensor-map form of the transposed map needs it */
         d.TensorMapEncodeTiled = (decltype(d.TensorMapEncodeTiled))dlsym(h, "cuTensorMapEncodeTiled");
         d.ok = ok;
@@ -111,8 +113,7 @@ void Tuning::read_environment() {
     foldseg_stage_max = num("ACCB_FOLDSEG_STAGE_MAX", foldseg_stage_max);
     foldseg_fill8 = (int)std::min(8LL, std::max(1LL, num("ACCB_FOLDSEG_STAGE_FILL8", foldseg_fill8)));
     foldseg_lanes = (int)std::max(0LL, num("ACCB_FOLDSEG_STAGE_LANES", 0));
-    foldseg_balanced_min = num("ACCB_FOLDSEG_BALANCED_MIN", foldseg_balanced_min);
-    foldseg_span = (int)std::max(0LL, num("ACCB_FOLDSEG_SPAN", 0));
+    foldseg_no_defer = getenv("ACCB_FOLDSEG_NO_DEFER") != nullptr;
     permute_replicas = (int)std::max(1LL, num("ACCB_PERMUTE_REPLICAS", permute_replicas));
     stencil_no_tile = getenv("ACCB_STENCIL_NO_TILE") != nullptr;
     stencil_rows = (int)std::max(1LL, num("ACCB_STENCIL_ROWS", stencil_rows));
@@ -179,7 +180,7 @@ StreamScratch *scratch_for(accb_context *ctx, cudaStream_t s) {
     auto it = ctx->scratch.find(s);
     if (it != ctx->scratch.end()) return &it->second;
     StreamScratch sc;
-    const size_t bytes = (kRowCounterBase + kRowCounters) * sizeof(unsigned);
+    const size_t bytes = (kDeferredBase + kDeferredWords) * sizeof(unsigned);
     if (cudaMalloc((void **)&sc.words, bytes) != cudaSuccess) return nullptr;
     if (cudaMemsetAsync(sc.words, 0, bytes, s) != cudaSuccess) return nullptr;
     return &(ctx->scratch[s] = sc);

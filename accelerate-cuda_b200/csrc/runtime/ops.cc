@@ -56,6 +56,31 @@ int launch(accb_context *ctx, CUfunction fn, const char *name, int grid, int blo
     return st;
 }
 
+int launch_dependent(accb_context *ctx, CUfunction fn, const char *name, int grid, int block, cudaStream_t stream,
+                     const accb_kparams &p) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(stream, &cap);
+    if (!driver().LaunchKernelEx || cap != cudaStreamCaptureStatusNone) return launch(ctx, fn, name, grid, block, 0, stream, p);
+    void *args[] = {const_cast<accb_kparams *>(&p)};
+    if (ctx->trace_exec) fprintf(stderr, "[accb exec] %s<<<%d,%d>>> (dependent) n=%lld\n", name, grid, block, p.n);
+    CUlaunchAttribute attr;
+    memset(&attr, 0, sizeof attr);
+    attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attr.value.programmaticStreamSerializationAllowed = 1;
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDimX = (unsigned)grid;
+    cfg.gridDimY = cfg.gridDimZ = 1;
+    cfg.blockDimX = (unsigned)block;
+    cfg.blockDimY = cfg.blockDimZ = 1;
+    cfg.hStream = (CUstream)stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int st = check_cu(ctx, driver().LaunchKernelEx(&cfg, fn, args, nullptr), name);
+    if (st == ACCB_OK) ctx->launches++;
+    return st;
+}
+
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 /* environment arrays -> slots, shapes, alignment flag */
@@ -395,8 +420,6 @@ int accb_fold_dim_at(accb_context *ctx, accb_kernel *k, accb_stream stream, cons
     return launch(ctx, pr.fn, entry, grid, pr.block, 0, (cudaStream_t)stream, p);
 }
 
-static int scan_scratch(accb_context *ctx, cudaStream_t s, long long ntiles, int rec, StreamScratch **out, unsigned *epoch_out);
-
 int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env, int nenv,
                   long long rows, long long cols, const int *offsets, long long nseg, const void *seed,
                   size_t seed_bytes, const accb_array *out) {
@@ -422,32 +445,32 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     const char *entry = group > 32 ? "foldSeg_block" : group == 32 ? "foldSeg" : group == 16 ? "foldSeg_g16" : group == 8 ? "foldSeg_g8" : "foldSeg_g4";
     Prep pr;
     TRY(prepare(ctx, k, entry, 0, &pr));
-    const bool aligned = (rows == 1 || cols % 16 == 0) && (p.flags & ACCB_F_VEC);
-    if (ctx->tune.foldseg_balanced_min >= 0 && avg >= ctx->tune.foldseg_balanced_min && aligned && pr.meta.v[8] > 0 &&
-        pr.meta.v[10] > 0 && cols >= pr.meta.v[8]) {
-        /* work divided by elements: the source row is cut into tiles whatever the segments are; a segment that
-         * spans blocks is completed through the blocks' status records (fold_balanced.cuh) */
-        const long long tile = pr.meta.v[8];
-        const long long tpr = ceil_div(cols, tile);
-        /* a block works through K consecutive tiles (the next tile's copy runs while the current one is reduced):
-         * as many as leave every SM about twenty blocks over the launch, eight at most */
-        const long long span = ctx->tune.foldseg_span > 0
-                                   ? ctx->tune.foldseg_span
-                                   : std::min<long long>(8, std::max<long long>(1, tpr / (20LL * ctx->sm_count)));
-        const long long blocks = rows * ceil_div(tpr, span);
-        if (blocks > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one foldSeg launch");
-        Prep pb;
-        TRY(get_function(ctx, k, "foldSeg_balanced", &pb.fn, &pb.meta));
-        cudaStream_t s = (cudaStream_t)stream;
-        StreamScratch *sc = nullptr;
-        unsigned epoch = 0;
-        TRY(scan_scratch(ctx, s, blocks, pr.meta.v[10], &sc, &epoch));
-        p.ip[3] = epoch;
-        p.ip[4] = tpr;
-        p.ip[5] = span;
-        p.aux[1] = sc->words + 2;
-        p.aux[2] = sc->status;
-        return launch(ctx, pb.fn, "foldSeg_balanced", (int)blocks, pr.meta.v[7], (size_t)pr.meta.v[9], s, p);
+    /* Segments far longer than the rest (64 K elements where a thread, a warp or a few lanes own a segment, 1 M
+     * where a block does) go on a list, and a second launch reduces them with all blocks; without it one such
+     * segment keeps a single warp or block busy long after the launch would have ended.  Only sources of 4 M
+     * elements and more get the second launch (it costs about three microseconds when the list stays empty). */
+    cudaStream_t s = (cudaStream_t)stream;
+    StreamScratch *sc = scratch_for(ctx, s);
+    if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+    const long long piece = pr.meta.v[7];
+    const bool defer = !ctx->tune.foldseg_no_defer && piece > 0 && cols >= (1LL << 22);
+    auto second_launch = [&](int st) {
+        if (st != ACCB_OK || !defer) return st;
+        Prep pd;
+        int e = prepare(ctx, k, "foldSeg_deferred", 0, &pd);
+        if (e != ACCB_OK) return e;
+        /* a listed segment of n elements has at most n / piece + 1 pieces */
+        const size_t parts = (size_t)(rows * cols / piece) + ACCB_FOLD_DEFER_MAX;
+        e = grow(ctx, &sc->partial, &sc->partial_bytes, parts * std::max(8, pr.meta.v[2]), s, false);
+        if (e != ACCB_OK) return e;
+        accb_kparams q = p;
+        q.aux[1] = sc->partial;
+        return launch_dependent(ctx, pd.fn, "foldSeg_deferred", ctx->sm_count * pd.per_sm, pd.block, s, q);
+    };
+    if (defer) {
+        /* a block per segment fills the GPU only with enough segments: with fewer, every long one is handed over */
+        p.ip[6] = (group > 32 && rows * nseg >= 4LL * ctx->sm_count * pr.per_sm) ? (1LL << 20) : (1LL << 16);
+        p.aux[2] = sc->words + kDeferredBase;
     }
     if (avg <= ctx->tune.foldseg_stage_max && rows * nseg >= 4096 && (rows == 1 || cols % 16 == 0) && pr.meta.v[6] > 0 &&
         (p.flags & ACCB_F_VEC)) {
@@ -456,8 +479,7 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
         const size_t smem = (size_t)pr.meta.v[6];
         Prep ps;
         TRY(get_function(ctx, k, "foldSeg_staged", &ps.fn, &ps.meta)); /* its block size is meta.v[5] */
-        StreamScratch *sc = scratch_for(ctx, (cudaStream_t)stream);
-        if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
+        if (defer) p.ip[6] = 1LL << 16;
         /* a run that overflows the window reads its last segments from global memory, so aim high */
         const long long fill = ctx->tune.foldseg_fill8;
         const long long run =
@@ -470,11 +492,11 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
         p.aux[1] = sc->words + 2;
         const long long blocks = rows * ceil_div(nseg, run);
         if (blocks > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one foldSeg launch");
-        return launch(ctx, ps.fn, "foldSeg_staged", (int)blocks, ps.meta.v[5], smem, (cudaStream_t)stream, p);
+        return second_launch(launch(ctx, ps.fn, "foldSeg_staged", (int)blocks, ps.meta.v[5], smem, s, p));
     }
     const long long units = ceil_div(rows * nseg, pr.block / std::min(group, pr.block));
     const int grid = (int)std::min<long long>(std::max(1LL, units), (long long)ctx->sm_count * pr.per_sm);
-    return launch(ctx, pr.fn, entry, grid, pr.block, 0, (cudaStream_t)stream, p);
+    return second_launch(launch(ctx, pr.fn, entry, grid, pr.block, 0, s, p));
 }
 
 /* ----------------------------------------------------------------- scan */

@@ -93,6 +93,16 @@ __device__ __forceinline__ typename Fn::elem fold_seed(const accb_kparams &p) {
     return Env(p).scalar<T>(0);
 }
 
+/* foldSeg: hand segment `unit` (row * segments + segment) over to the second launch.  False when the list is
+ * full: the caller then reduces the segment itself. */
+__device__ __forceinline__ bool fold_defer(const accb_kparams &p, long long unit) {
+    accb_deferred_segments *dl = static_cast<accb_deferred_segments *>(p.aux[2]);
+    const unsigned idx = atomicAdd(&dl->count, 1u);
+    if (idx >= ACCB_FOLD_DEFER_MAX) return false;
+    dl->unit[idx] = unit;
+    return true;
+}
+
 /* Accumulate elements [lo, lo+len) of the producer into `acc`, all threads of
  * a group of G threads (rank `g`) cooperating; vec_ok says lo and the slots
  * are vector aligned. */
@@ -219,11 +229,27 @@ __device__ __forceinline__ void fold_all_body(const accb_kparams &p) {
  * lanes of a warp still read one contiguous stretch of memory).  A group
  * takes KR units per trip so that short ranges still leave several loads in
  * flight per lane.  `range(w, lo, len, vec)` describes unit w. */
+/* fold_range for a range that starts anywhere: the elements up to the first 16-byte boundary one by one, the rest
+ * with 128-bit loads (`aligned`: the arrays themselves are 16-byte aligned and the range is worth the split) */
+template <class Fn, int U>
+__device__ __forceinline__ void fold_range_from_anywhere(const accb_kparams &p, const Env &env, long long lo, long long len,
+                                                         int g, int G, bool aligned, Opt<typename Fn::acc> &acc) {
+    if (aligned && len >= 2LL * G * V) {
+        const long long head = (V - lo % V) % V;
+        fold_range<Fn, U>(p, env, lo, head, g, G, false, acc);
+        fold_range<Fn, U>(p, env, lo + head, len - head, g, G, true, acc);
+    } else {
+        fold_range<Fn, U>(p, env, lo, len, g, G, false, acc);
+    }
+}
+
 template <class Fn, int CTA, int GROUP, int U, int KR, class Range>
-__device__ __forceinline__ void fold_units(const accb_kparams &p, long long units, Range range) {
+__device__ __forceinline__ void fold_units(const accb_kparams &p, long long units, Range range, long long defer_above = 0,
+                                           bool split_unaligned = false) {
     typedef typename Fn::acc A;
     typedef Opt<A> O;
     __shared__ O s_red[CTA / 32];
+    __shared__ int s_deferred;
     const Env env(p);
     const OptCombine<Fn> oc;
     const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
@@ -242,9 +268,19 @@ __device__ __forceinline__ void fold_units(const accb_kparams &p, long long unit
             long long lo, len;
             bool vec;
             range(w, lo, len, vec);
+            if (defer_above > 0 && len > defer_above) { /* the same for the whole block */
+                if (threadIdx.x == 0) s_deferred = fold_defer(p, w);
+                __syncthreads();
+                const int d = s_deferred;
+                __syncthreads();
+                if (d) continue;
+            }
             O acc;
             acc.have = 0;
-            fold_range<Fn, U>(p, env, lo, len, threadIdx.x, CTA, vec, acc);
+            if (vec || !split_unaligned)
+                fold_range<Fn, U>(p, env, lo, len, threadIdx.x, CTA, vec, acc);
+            else
+                fold_range_from_anywhere<Fn, U>(p, env, lo, len, threadIdx.x, CTA, true, acc);
             acc = block_reduce<CTA>(acc, oc, s_red);
             if (threadIdx.x == 0) finish(w, acc);
         }
@@ -256,21 +292,32 @@ __device__ __forceinline__ void fold_units(const accb_kparams &p, long long unit
         const unsigned gmask = GROUP == 32 ? FULL : (((1u << GROUP) - 1u) << ((threadIdx.x & 31) / GROUP * GROUP));
         for (long long w0 = (long long)blockIdx.x * PER + threadIdx.x / GROUP; w0 < units; w0 += sweep * KR) {
             O acc[KR];
+            bool deferred[KR];
 #pragma unroll
             for (int k = 0; k < KR; ++k) {
                 acc[k].have = 0;
+                deferred[k] = false;
                 const long long w = w0 + k * sweep;
-                if (w < units) {
+                if (w < units) { /* the same for all lanes of the group */
                     long long lo, len;
                     bool vec;
                     range(w, lo, len, vec);
-                    fold_range<Fn, U>(p, env, lo, len, g, GROUP, vec, acc[k]);
+                    if (defer_above > 0 && len > defer_above) {
+                        const int d = g == 0 ? (int)fold_defer(p, w) : 0;
+                        deferred[k] = __shfl_sync(gmask, d, (threadIdx.x & 31) / GROUP * GROUP) != 0;
+                    }
+                    if (deferred[k]) {
+                    } else if (vec || !split_unaligned) {
+                        fold_range<Fn, U>(p, env, lo, len, g, GROUP, vec, acc[k]);
+                    } else {
+                        fold_range_from_anywhere<Fn, U>(p, env, lo, len, g, GROUP, true, acc[k]);
+                    }
                 }
             }
 #pragma unroll
             for (int k = 0; k < KR; ++k) {
                 const long long w = w0 + k * sweep;
-                if (w < units) {
+                if (w < units && !deferred[k]) {
 #pragma unroll
                     for (int m = GROUP / 2; m > 0; m >>= 1) {
                         O o;
@@ -357,11 +404,14 @@ __device__ __forceinline__ void fold_split_body(const accb_kparams &p) {
 /* foldSeg / fold1Seg: unit = (row, segment).  aux[0] = Int32 offsets, length
  * nseg+1: the exclusive scan of the segment lengths (Execute.hs:320-324).
  * ip[0] = rows, ip[1] = cols (innermost extent of the source), ip[2] = nseg.
- * Segments start anywhere, so accesses are scalar. */
+ * Segments start anywhere: one that is long enough is read with 128-bit loads from its first 16-byte
+ * boundary on, the others element by element. */
 template <class Fn, int CTA, int GROUP, int KR>
 __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
     const long long rows = p.ip[0], cols = p.ip[1], nseg = p.ip[2];
     const int *offs = static_cast<const int *>(p.aux[0]);
+    /* once every block is running, the blocks of the second launch may take the places of those that finish */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     fold_units<Fn, CTA, GROUP, 1, KR>(p, rows * nseg, [&](long long w, long long &lo, long long &len, bool &vec) {
         /* a 64-bit division per segment would cost more than a short segment's loads */
         long long r = 0, sgm = w;
@@ -378,13 +428,102 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
         lo = r * cols + b;
         len = offs[sgm + 1] - b;
         vec = false;
-    });
+    }, p.ip[6], (p.flags & ACCB_F_VEC) != 0);
+}
+
+/* The second launch of a foldSeg: the segments that the first launch put on the list (longer than ip[6]
+ * elements), each cut into pieces of ACCB_FOLD_DEFER_PIECE elements that the blocks take in turn -- the scheme
+ * of fold_split, per listed segment: partial results in aux[0] (one per piece, in list order), the block that
+ * completes a segment last combines its pieces in order and applies the seed.  The last block to leave clears
+ * the list.  With an empty list (the usual case) a block reads one word and leaves. */
+#ifndef ACCB_FOLD_DEFER_PIECE
+#define ACCB_FOLD_DEFER_PIECE (1 << 16)
+#endif
+template <class Fn, int CTA, int U>
+__device__ __forceinline__ void fold_deferred_body(const accb_kparams &p) {
+    typedef typename Fn::acc A;
+    typedef Opt<A> O;
+    __shared__ O s_red[CTA / 32];
+    __shared__ int s_last;
+    __shared__ long long s_first[ACCB_FOLD_DEFER_MAX + 1]; /* first piece of every listed segment */
+    const Env env(p);
+    const OptCombine<Fn> oc;
+    const auto oseq = std::make_integer_sequence<int, Fn::Out::size>();
+    const long long cols = p.ip[1], nseg = p.ip[2];
+    constexpr long long PIECE = ACCB_FOLD_DEFER_PIECE;
+    const int *offs = static_cast<const int *>(p.aux[0]);
+    O *partial = static_cast<O *>(p.aux[1]);
+    accb_deferred_segments *dl = static_cast<accb_deferred_segments *>(p.aux[2]);
+    const bool vec_ok = (p.flags & ACCB_F_VEC) != 0;
+    /* the host launches this kernel so that its blocks may be scheduled while the first launch drains: wait
+     * until that launch is complete and its list visible (no effect on an ordinary launch) */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int listed = (int)min(*static_cast<volatile unsigned int *>(&dl->count), (unsigned)ACCB_FOLD_DEFER_MAX);
+    if (listed == 0) return; /* nothing was deferred: the list is clear already */
+    for (int g = threadIdx.x; g < listed; g += CTA) {
+        const long long sgm = dl->unit[g] % nseg;
+        s_first[g + 1] = ((long long)offs[sgm + 1] - offs[sgm] + PIECE - 1) / PIECE;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        s_first[0] = 0;
+        for (int g = 0; g < listed; ++g) s_first[g + 1] += s_first[g];
+    }
+    __syncthreads();
+    const long long pieces = s_first[listed];
+    for (long long it = blockIdx.x; it < pieces; it += gridDim.x) {
+        int g = 0, h = listed; /* s_first[g] <= it < s_first[h] */
+        while (h - g > 1) {
+            const int m = (g + h) >> 1;
+            if (s_first[m] <= it)
+                g = m;
+            else
+                h = m;
+        }
+        const long long w = dl->unit[g], r = w / nseg, sgm = w - r * nseg;
+        const long long pc = it - s_first[g], np = s_first[g + 1] - s_first[g];
+        const long long b = offs[sgm], e = offs[sgm + 1];
+        const long long lo = r * cols + b + pc * PIECE, len = min(PIECE, e - b - pc * PIECE);
+        O acc;
+        acc.have = 0;
+        fold_range_from_anywhere<Fn, U>(p, env, lo, len, threadIdx.x, CTA, vec_ok, acc);
+        acc = block_reduce<CTA>(acc, oc, s_red);
+        if (threadIdx.x == 0) {
+            partial[it] = acc;
+            __threadfence();
+            s_last = atomicAdd(&dl->arrived[g], 1u) == (unsigned)np - 1u;
+        }
+        __syncthreads();
+        if (s_last) { /* uniform over the block */
+            __threadfence();
+            O tot;
+            tot.have = 0;
+            for (long long q = threadIdx.x; q < np; q += CTA) tot = oc(tot, ld_cg(partial + s_first[g] + q));
+            tot = block_reduce<CTA>(tot, oc, s_red);
+            if (threadIdx.x == 0) {
+                dl->arrived[g] = 0u;
+                if (p.flags & ACCB_F_HAS_SEED) {
+                    const A z = Fn::lift(fold_seed<Fn>(p));
+                    tot.v = tot.have ? Fn::combine(tot.v, z) : z;
+                    tot.have = 1;
+                }
+                if (tot.have) fold_put<Fn>(p, w, Fn::lower(tot.v), oseq);
+            }
+        }
+        __syncthreads(); /* s_last and s_red are reused by the next piece */
+    }
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&dl->finished, 1u) == gridDim.x - 1u) { /* every block has read the list */
+            dl->finished = 0u;
+            dl->count = 0u;
+        }
+    }
 }
 
 }  // namespace accb
 
-#include "fold_staged.cuh"   /* short rows and segments */
-#include "fold_balanced.cuh" /* segments of any length, work divided by elements */
+#include "fold_staged.cuh" /* short rows and segments */
 
 #define ACCB_FOLD_CTA 256
 #define ACCB_FOLD_U 4
@@ -435,20 +574,19 @@ __device__ __forceinline__ void fold_seg_body(const accb_kparams &p) {
     }
 
 /* `foldSeg` is the reference's warp-per-segment form (Reduction.hs:430); the
- * others serve shorter and longer segments.  Metadata 7..10: block size, elements per tile, shared memory and bytes of a
- * status record of the balanced form (0: not available for this functor) */
+ * others serve shorter and longer segments; foldSeg_deferred is the second launch for the segments the first one
+ * handed over */
 #define ACCB_INSTANTIATE_FOLD_SEG(Fn)                                                   \
     ACCB_META12(4, ACCB_FOLD_CTA, sizeof(accb::Opt<Fn::acc>),                           \
                 accb::fold_stage_window<Fn::In>::value, 1, ACCB_FOLD_STAGE_CTA,         \
-                (accb::fold_stage_smem<Fn>()), ACCB_FOLD_BAL_CTA, (accb::fold_bal_tile<Fn>()),          \
-                (accb::fold_bal_smem<Fn>()), (accb::fold_bal_record<Fn>()), Fn::In::size) \
+                (accb::fold_stage_smem<Fn>()), ACCB_FOLD_DEFER_PIECE, 0, 0, 0, Fn::In::size) \
     ACCB_FOLD_STAGED_ENTRY(Fn, foldSeg_staged, true)                                    \
-    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_BAL_CTA, ACCB_FOLD_BAL_MINB) \
-        foldSeg_balanced(const __grid_constant__ accb_kparams p) {                      \
-        accb::fold_balanced_or_nothing<Fn>(p);                                          \
-    }                                                                                   \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg, 32, 1)                                             \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g16, 16, 2)                                         \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g8, 8, 2)                                           \
     ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_g4, 4, 4)                                           \
-    ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_block, ACCB_FOLD_CTA, 1)
+    ACCB_FOLD_SEG_ENTRY(Fn, foldSeg_block, ACCB_FOLD_CTA, 1)                            \
+    extern "C" __global__ void __launch_bounds__(ACCB_FOLD_CTA)                         \
+        foldSeg_deferred(const __grid_constant__ accb_kparams p) {                      \
+        accb::fold_deferred_body<Fn, ACCB_FOLD_CTA, ACCB_FOLD_U>(p);                    \
+    }

@@ -26,7 +26,8 @@
  *   as ONE row of rows x cols elements) or, with SEG, aux[0] = Int32 offsets of
  *   length units + 1; ip[4] = S; ip[5] = lanes per unit (1, or a power of two up to 32 for units of a few
  *   hundred elements: then consecutive lanes read consecutive elements of their unit and combine by
- *   shuffles).  aux[1] = error word of the bounded wait.
+ *   shuffles).  aux[1] = error word of the bounded wait.  With SEG and ip[6] > 0, segments longer than ip[6]
+ *   elements are handed over to the second launch (aux[2], see fold_defer).
  * Segment offsets are Int32 (Execute.hs:320-324), so positions inside a row
  * are held in 32-bit registers.
  */
@@ -113,6 +114,9 @@ __device__ __forceinline__ void fold_staged_body(const accb_kparams &p) {
     const int *offs = static_cast<const int *>(p.aux[0]);
     unsigned int *err = static_cast<unsigned int *>(p.aux[1]);
     const bool seeded = (p.flags & ACCB_F_HAS_SEED) != 0;
+    const int defer_above = SEG ? (int)min(p.ip[6], 0x7fffffffLL) : 0; /* 0: never */
+    if constexpr (SEG) /* once every block is running, the second launch's blocks may take the places of those that finish */
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = lane_id(), warp = warp_id();
 
     /* the block's run of units, of row r */
@@ -197,9 +201,17 @@ __device__ __forceinline__ void fold_staged_body(const accb_kparams &p) {
         const int len = e - b;
         O acc;
         acc.have = 0;
+        /* a segment far longer than the rest goes to the second launch (its owner puts it on the list; all lanes that
+         * share it learn the outcome: a full list leaves it here) */
+        bool deferred = false;
+        if constexpr (SEG) {
+            const bool far = defer_above > 0 && valid && len > defer_above;
+            const int d = (far && g == 0) ? (int)fold_defer(p, r * nseg + s_lo + k) : 0;
+            deferred = __shfl_sync(FULL, d, lane - g) != 0;
+        }
         if (G == 1) {
-            const bool coop = len > ACCB_FOLD_STAGE_COOP;
-            if (valid && !coop && len > 0) {
+            const bool coop = len > ACCB_FOLD_STAGE_COOP && !deferred;
+            if (valid && !coop && !deferred && len > 0) {
                 /* one loop of len trips for every lane (two loops, before and after the wrap, would
                  * have different trip counts per lane and run one after the other) */
                 int i = b + ((lane * len) >> 5);
@@ -231,7 +243,8 @@ __device__ __forceinline__ void fold_staged_body(const accb_kparams &p) {
         } else {
             /* (units whose length is a multiple of 32 G put the groups of a warp on the same banks; walking
              * them in rotated chunks of 32 elements cost more instructions than the conflicts do) */
-            if (valid && b >= a0 && e <= w1) {
+            if (deferred) {
+            } else if (valid && b >= a0 && e <= w1) {
 #pragma unroll 4
                 for (int i = b + g; i < e; i += G) add(acc, stage_get<Fn, WIN>(env, s_raw, i - a0, org + i, iseq));
             } else if (valid) {
@@ -239,7 +252,7 @@ __device__ __forceinline__ void fold_staged_body(const accb_kparams &p) {
             }
             for (int m = G >> 1; m > 0; m >>= 1) acc = oc(acc, shfl_xor(acc, m)); /* stays inside the aligned group */
         }
-        if (valid && g == 0) {
+        if (valid && g == 0 && !deferred) {
             if (seeded) {
                 const A z = Fn::lift(fold_seed<Fn>(p));
                 acc.v = acc.have ? Fn::combine(acc.v, z) : z;

@@ -368,23 +368,6 @@ def test_fold_seg_rank2(ctx, P, torch_cuda, rng):
     assert np.array_equal(out.cpu().numpy(), ref)
 
 
-@pytest.fixture(scope="module")
-def ctx_span3(accb, torch_cuda):
-    """A context whose element-balanced foldSeg gives every block three tiles (tuning is read when a context is made)."""
-    import os
-    old = os.environ.get("ACCB_FOLDSEG_SPAN")
-    os.environ["ACCB_FOLDSEG_SPAN"] = "3"
-    try:
-        c = accb.Context(0)
-    finally:
-        if old is None:
-            del os.environ["ACCB_FOLDSEG_SPAN"]
-        else:
-            os.environ["ACCB_FOLDSEG_SPAN"] = old
-    yield c
-    c.sync()
-
-
 def _seg_ref(x, offs, seed):
     tot = np.concatenate([[0], np.cumsum(x.astype(np.int64))])
     return (tot[offs[1:]] - tot[offs[:-1]] + seed).astype(np.int64)
@@ -392,23 +375,21 @@ def _seg_ref(x, offs, seed):
 
 @pytest.mark.parametrize("case", ["tile_edges", "one_giant", "giant_among_short", "offsets_inside", "leading_empty",
                                   "all_empty", "ragged_tail", "many_empty_runs"])
-@pytest.mark.parametrize("span", [0, 3])
-def test_fold_seg_balanced_by_elements(ctx, ctx_span3, P, torch_cuda, rng, case, span):
-    """The element-balanced form (tiles of 4096 Int32 elements, 32 per thread): segments that end exactly on
-    chunk and tile boundaries, one segment over many tiles, long segments among short ones, offsets that
-    cover only the middle of the source, empty segments first, last and in runs, no elements at all.  With
-    span 3 every block works through three tiles one after the other (what large inputs get by default)."""
+def test_fold_seg_segments_of_any_length(ctx, P, torch_cuda, rng, case):
+    """Segments that end exactly on multiples of 32 and 4096 elements, one segment of 4.5 M elements, segments of
+    hundreds of thousands of elements among 600000 short ones (sources of 2^22 elements and more hand segments
+    longer than 65536 elements over to a second launch that splits them over all blocks), offsets that cover only
+    the middle of the source, empty segments first, last and in runs, no elements at all."""
     t = torch_cuda
-    ctx = ctx_span3 if span else ctx
     T, V = 4096, 32
     pad_front = pad_back = 0
     if case == "tile_edges":
         lens = np.array([T, V, V, T - 2 * V, 1, T - 1, 2 * T, 0, 0, 3, T - 3, V - 1, 1, 5 * T + 17, 40])
     elif case == "one_giant":
-        lens = np.array([0, 300 * T + 5, 0])
+        lens = np.array([0, 1100 * T + 5, 0])
     elif case == "giant_among_short":
-        lens = rng.integers(0, 12, 40000)
-        lens[[100, 20000, 39999]] = [50 * T + 1, 3 * T, 9 * T - 7]
+        lens = rng.integers(0, 12, 600000)
+        lens[[100, 20000, 599999]] = [150 * T + 1, 3 * T, 190 * T - 7]
     elif case == "offsets_inside":
         lens = rng.integers(0, 30, 3000)
         pad_front, pad_back = 5000, 7003
@@ -440,24 +421,23 @@ def test_fold_seg_balanced_by_elements(ctx, ctx_span3, P, torch_cuda, rng, case,
     assert np.array_equal(out.cpu().numpy().astype(np.int64), ref)
 
 
-@pytest.mark.parametrize("span", [0, 3])
-def test_fold_seg_balanced_rows_and_two_inputs(ctx, ctx_span3, P, torch_cuda, rng, span):
-    """Rank 2 (every row cut by the same offsets, rows of several tiles) and a functor with two zipped inputs of
-    float32 and Int32 plus a gathered vector, accumulating in float64."""
+def test_fold_seg_long_segments_in_rows_and_with_two_inputs(ctx, P, torch_cuda, rng):
+    """Rank 2 (every row cut by the same offsets; one segment of 1.1 M elements per row is handed to the second
+    launch) and a functor with two zipped inputs of float32 and Int32 plus a gathered vector, accumulating in
+    float64, with a segment of 900000 elements among short ones."""
     t = torch_cuda
-    ctx = ctx_span3 if span else ctx
-    lens = rng.integers(0, 400, 200)
-    lens[17] = 20000
+    lens = rng.integers(0, 16000, 400)
+    lens[17] = 1100000
     lens[0] += (-int(lens.sum())) % 16
     offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
-    m = rng.integers(-50, 50, (5, int(offs[-1]))).astype(np.int32)
-    out = t.zeros((5, lens.size), dtype=t.int32, device="cuda")
-    ctx.fold_seg(P.SEGSUM_I32, [dev(t, m)], 5, m.shape[1], dev(t, offs), lens.size, out, seed=np.int32(1))
+    m = rng.integers(-50, 50, (3, int(offs[-1]))).astype(np.int32)
+    out = t.zeros((3, lens.size), dtype=t.int32, device="cuda")
+    ctx.fold_seg(P.SEGSUM_I32, [dev(t, m)], 3, m.shape[1], dev(t, offs), lens.size, out, seed=np.int32(1))
     ctx.sync()
-    ref = np.stack([_seg_ref(m[r], offs, 1) for r in range(5)])
+    ref = np.stack([_seg_ref(m[r], offs, 1) for r in range(3)])
     assert np.array_equal(out.cpu().numpy().astype(np.int64), ref)
-    nnz = rng.integers(0, 120, 4000)
-    nnz[[5, 3000]] = [30000, 8200]
+    nnz = rng.integers(0, 120, 60000)
+    nnz[[5, 3000]] = [900000, 70001]
     offs = np.concatenate([[0], np.cumsum(nnz)]).astype(np.int32)
     vals = rng.uniform(-1, 1, int(offs[-1])).astype(np.float32)
     cols = rng.integers(0, 5000, int(offs[-1])).astype(np.int32)
