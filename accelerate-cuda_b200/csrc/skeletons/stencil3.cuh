@@ -54,6 +54,11 @@
 #define ACCB_STENCIL3_TY 32 /* rows of a block's column: four per warp (512^3, 27 taps: 0.45 ms against 0.53 ms with 16) */
 #endif
 #define ACCB_STENCIL3_TX 128 /* columns of a block's column: one warp row */
+#ifndef ACCB_STENCIL3_AHEAD
+#define ACCB_STENCIL3_AHEAD 1 /* z-steps between the request for a plane and its first use.  Two or three steps cost a
+                                 resident block per SM and bought nothing (512^3, 7-point: 0.335 ms at one step, 0.42 ms
+                                 at two or three; with 16-row tiles 0.37-0.40 ms at one to three) */
+#endif
 #ifndef ACCB_STENCIL3_MINB
 #define ACCB_STENCIL3_MINB 3 /* resident blocks per SM the compiler must leave registers for */
 #endif
@@ -76,7 +81,8 @@ struct Stencil3Tile {
     static constexpr int PITCH = TX + 2 * PAD;
     static constexpr int ROWS = TY + 2 * Fn::RY;
     static constexpr int PLANE = ROWS * PITCH;     /* values per plane tile */
-    static constexpr int RING = 2 * Fn::RZ + 2;    /* plane tiles resident: the 2*RZ+1 in use and the one on its way */
+    static constexpr int AHEAD = ACCB_STENCIL3_AHEAD;
+    static constexpr int RING = 2 * Fn::RZ + 1 + AHEAD; /* plane tiles resident: the 2*RZ+1 in use and those on their way */
     static constexpr int BYTES = RING * PLANE * 4;
 };
 
@@ -157,14 +163,23 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
         const int x0 = tx * G::TX, y0 = ty * G::TY, z0 = tz * zrun;
         const int z1 = min(D, z0 + zrun);
         __syncthreads(); /* the previous task's last reads of the ring */
-        /* planes z0 - RZ .. z0 + RZ are needed by the first step */
-        for (int dz = -RZ; dz <= RZ; ++dz) fetch(z0 + dz, y0, x0);
+        /* planes z0 - RZ .. z0 + RZ are needed by the first step; AHEAD - 1 more are requested with them.  One
+         * group of copies per plane, also for planes beyond the run (empty groups keep the count below exact) */
+        for (int dz = -RZ; dz <= RZ + G::AHEAD - 1; ++dz) {
+            if (dz <= RZ || z0 + dz - RZ < z1)
+                fetch(z0 + dz, y0, x0);
+            else
+                asm volatile("cp.async.commit_group;" ::: "memory");
+        }
         for (int z = z0; z < z1; ++z) {
-            /* everything fetched so far has landed; then start on the plane the NEXT step adds, into the slot that
-             * the step before this one read last */
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            /* all but the newest AHEAD - 1 planes have landed; then start on the plane that step z + AHEAD adds,
+             * into the slot that the step before this one read last */
+            asm volatile("cp.async.wait_group %0;" ::"n"(G::AHEAD - 1) : "memory");
             __syncthreads();
-            if (z + 1 < z1) fetch(z + 1 + RZ, y0, x0);
+            if (z + G::AHEAD < z1)
+                fetch(z + G::AHEAD + RZ, y0, x0);
+            else
+                asm volatile("cp.async.commit_group;" ::: "memory");
             /* warp w computes rows w, w + 8, ..: lane l the columns 4l .. 4l + 3 */
             for (int r = w; r < G::TY; r += CTA / 32) {
                 const int y = y0 + r, x = x0 + 4 * lane;
