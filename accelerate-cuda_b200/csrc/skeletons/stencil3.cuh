@@ -190,18 +190,19 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
                         const T *pl = slot(z - RZ + dz);
 #pragma unroll
                         for (int dy = 0; dy <= 2 * RY; ++dy) {
-                            const T *row = pl + (r + dy) * G::PITCH + G::PAD + 4 * lane;
-                            const uint4 c = *reinterpret_cast<const uint4 *>(row);
+                            const T *trow = pl + (r + dy) * G::PITCH + G::PAD; /* column x0 of this tile row */
+                            const uint4 c = *reinterpret_cast<const uint4 *>(trow + 4 * lane);
                             memcpy(&win[dz][dy][RX], &c, 16);
                             /* the halo columns are the neighbouring lanes' centre columns: shuffles instead of 4-byte
-                             * reads 16 bytes apart (a four-way bank conflict each); only the two lanes at the ends of
-                             * the row read theirs from the tile */
+                             * reads 16 bytes apart (a four-way bank conflict each); the two lanes at the ends of the row
+                             * take the tile's own halo, which every lane reads from the same address (a broadcast) */
 #pragma unroll
                             for (int h = 0; h < RX; ++h) {
                                 const T from_left = shfl_up(win[dz][dy][4 + h], 1);     /* lane - 1's last RX columns */
                                 const T from_right = shfl_down(win[dz][dy][RX + h], 1); /* lane + 1's first RX columns */
-                                win[dz][dy][h] = lane == 0 ? row[h - RX] : from_left;
-                                win[dz][dy][RX + 4 + h] = lane == 31 ? row[4 + h] : from_right;
+                                const T tile_left = trow[h - RX], tile_right = trow[G::TX + h];
+                                win[dz][dy][h] = lane == 0 ? tile_left : from_left;
+                                win[dz][dy][RX + 4 + h] = lane == 31 ? tile_right : from_right;
                             }
                         }
                     }
