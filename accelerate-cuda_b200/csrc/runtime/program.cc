@@ -65,6 +65,7 @@ struct accb_program {
     std::vector<int> outputs;
     std::vector<std::vector<PoolBuf>> pool; /* per value id, per component (stencil uses 2x) */
     std::vector<std::vector<PoolBuf>> in_pool;
+    PoolBuf slab_pool[4];               /* work grids of a stencil chain run slab by slab: two sets of two */
     cudaStream_t host_stream = nullptr;
     cudaStream_t pipe_stream[3] = {nullptr, nullptr, nullptr}; /* upload, compute, download */
     std::vector<cudaEvent_t> pipe_events;
@@ -571,6 +572,112 @@ static long long inner_elems(const accb_array &a) {
     return n;
 }
 
+/* A chain of rank-2 stencils over ONE host grid (a blur applied ten times, say) does not stream element by
+ * element, but it does by ROW SLABS: a slab of the result depends on the slab of the source plus as many rows above
+ * and below as the whole chain reaches (the sum over its stencils of applications x row radius).  Every slab is
+ * uploaded with that margin, the chain is applied to the widened slab as if it were a whole grid -- rows next to a
+ * cut are wrong by one more row per application, which is what the margin is for, while at the grid's real top and
+ * bottom the slab's edge IS the grid's edge and the boundary condition applies as always -- and the slab's own rows
+ * are downloaded while the next slab is worked on.  Clamp, Mirror and Constant only (Wrap reaches across the grid).
+ * The results are those of the whole-grid run, bit for bit: the same kernels see the same neighbourhoods.
+ * Returns 1 if it handled the run (status in *status), 0 if the program does not fit. */
+static int run_host_slabbed(accb_program *p, const accb_array *host_in, accb_array *host_out, int *status) {
+    *status = ACCB_OK;
+    accb_context *ctx = p->ctx;
+    if (ctx->tune.no_pipeline || p->stream_chunk == 0 || p->ninputs != 1 || p->outputs.size() != 1 || p->nodes.empty()) return 0;
+    if (host_in[0].rank != 2 || p->types[0].ncomp != 1) return 0;
+    long long reach = 0;
+    size_t widest = p->types[0].comp_bytes[0];
+    int prev = 0;
+    for (Node &nd : p->nodes) {
+        if (nd.kind != N_STENCIL || nd.shape_like != prev || nd.boundary == ACCB_WRAP || nd.iters < 1) return 0;
+        if (nd.out_type.ncomp != 1 || nd.out_type.rank != 2) return 0;
+        CUfunction fn;
+        KernelMeta meta;
+        if (get_function(ctx, nd.k, "stencil", &fn, &meta) != ACCB_OK) return 0;
+        reach += (long long)nd.iters * meta.v[7];
+        widest = std::max<size_t>(widest, nd.out_type.comp_bytes[0]);
+        prev = nd.out_id;
+    }
+    if (p->outputs[0] != prev) return 0;
+    const long long W = host_in[0].shape[0], H = host_in[0].shape[1];
+    if (W < 1 || reach < 1) return 0;
+    /* slabs of about 32 MiB, at least eight times the margin, a multiple of 16 rows */
+    long long rows = p->stream_chunk > 0 ? p->stream_chunk / W : (32LL << 20) / (W * (long long)widest);
+    rows = std::max(std::max(rows, 8 * reach), 16LL) / 16 * 16;
+    if (H < 2 * rows) return 0;
+    const long long nslabs = (H + rows - 1) / rows;
+    const size_t in_bytes = p->types[0].comp_bytes[0], out_bytes = p->types[prev].comp_bytes[0];
+    if (!host_out[0].ptr[0]) {
+        *status = fail(ctx, ACCB_EINVAL, "null host buffer for the result");
+        return 1;
+    }
+
+    auto run = [&]() -> int {
+        for (int i = 0; i < 3; ++i)
+            if (!p->pipe_stream[i])
+                TRY(check_cuda(ctx, cudaStreamCreateWithFlags(&p->pipe_stream[i], cudaStreamNonBlocking), "cudaStreamCreate"));
+        cudaStream_t up = p->pipe_stream[0], comp = p->pipe_stream[1], down = p->pipe_stream[2];
+        while ((long long)p->pipe_events.size() < 3 * nslabs) {
+            cudaEvent_t e;
+            TRY(check_cuda(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate"));
+            p->pipe_events.push_back(e);
+        }
+        auto &slots = p->in_pool[0];
+        if (slots.empty()) slots.resize(1);
+        void *dev_in = nullptr;
+        TRY(pool_get(p, slots[0], (size_t)(H * W) * in_bytes, &dev_in));
+        void *work[4];
+        for (int i = 0; i < 4; ++i) TRY(pool_get(p, p->slab_pool[i], (size_t)((rows + 2 * reach) * W) * widest, &work[i]));
+        long long uploaded = 0; /* rows of the source on the device so far */
+        for (long long sl = 0; sl < nslabs; ++sl) {
+            const long long r0 = sl * rows, r1 = std::min(H, r0 + rows);
+            const long long e0 = std::max(0LL, r0 - reach), e1 = std::min(H, r1 + reach);
+            cudaEvent_t ev_up = p->pipe_events[3 * sl], ev_comp = p->pipe_events[3 * sl + 1], ev_down = p->pipe_events[3 * sl + 2];
+            if (uploaded < e1) {
+                TRY(check_cuda(ctx, cudaMemcpyAsync(static_cast<char *>(dev_in) + uploaded * W * in_bytes,
+                                                    static_cast<const char *>(host_in[0].ptr[0]) + uploaded * W * in_bytes,
+                                                    (size_t)((e1 - uploaded) * W) * in_bytes, cudaMemcpyHostToDevice, up), "upload"));
+                uploaded = e1;
+            }
+            TRY(check_cuda(ctx, cudaEventRecord(ev_up, up), "cudaEventRecord"));
+            TRY(check_cuda(ctx, cudaStreamWaitEvent(comp, ev_up, 0), "cudaStreamWaitEvent"));
+            /* this slab's pair of work grids was last read by the download of the slab before the previous one */
+            if (sl >= 2) TRY(check_cuda(ctx, cudaStreamWaitEvent(comp, p->pipe_events[3 * (sl - 2) + 2], 0), "cudaStreamWaitEvent"));
+            accb_array cur = host_in[0];
+            cur.shape[1] = (int)(e1 - e0);
+            cur.ptr[0] = static_cast<char *>(dev_in) + e0 * W * in_bytes;
+            int next_work = 0;
+            for (Node &nd : p->nodes) {
+                const void *sc = nd.scalars.empty() ? nullptr : nd.scalars.data();
+                accb_array a = cur, b = cur;
+                a.ptr[0] = work[2 * (sl & 1) + next_work];
+                b.ptr[0] = work[2 * (sl & 1) + (next_work ^ 1)];
+                TRY(accb_stencil(ctx, nd.k, (accb_stream)comp, &cur, nd.boundary, sc, nd.scalars.size(), &a));
+                int in_b = 0;
+                if (nd.iters > 1)
+                    TRY(accb_stencil_iterate(ctx, nd.k, (accb_stream)comp, &a, &b, nd.iters - 1, nd.boundary, sc, nd.scalars.size(), &in_b));
+                cur = in_b ? b : a;
+                next_work = in_b ? next_work : next_work ^ 1; /* the next stencil writes to the grid `cur` is not in */
+            }
+            TRY(check_cuda(ctx, cudaEventRecord(ev_comp, comp), "cudaEventRecord"));
+            TRY(check_cuda(ctx, cudaStreamWaitEvent(down, ev_comp, 0), "cudaStreamWaitEvent"));
+            TRY(check_cuda(ctx, cudaMemcpyAsync(static_cast<char *>(host_out[0].ptr[0]) + r0 * W * out_bytes,
+                                                static_cast<const char *>(cur.ptr[0]) + (r0 - e0) * W * out_bytes,
+                                                (size_t)((r1 - r0) * W) * out_bytes, cudaMemcpyDeviceToHost, down), "download"));
+            TRY(check_cuda(ctx, cudaEventRecord(ev_down, down), "cudaEventRecord"));
+        }
+        TRY(check_cuda(ctx, cudaStreamSynchronize(down), "cudaStreamSynchronize"));
+        host_out[0].rank = 2;
+        host_out[0].shape[0] = (int)W;
+        host_out[0].shape[1] = (int)H;
+        host_out[0].ncomp = 1;
+        return ACCB_OK;
+    };
+    *status = run();
+    return 1;
+}
+
 /* Returns 1 if it handled the run (status in *status), 0 if the program does not fit. */
 static int run_host_streamed(accb_program *p, const accb_array *host_in, accb_array *host_out, int *status) {
     *status = ACCB_OK;
@@ -868,6 +975,7 @@ int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array
     {
         int st = ACCB_OK;
         if (run_host_streamed(p, host_in, host_out, &st)) return st;
+        if (run_host_slabbed(p, host_in, host_out, &st)) return st;
     }
     if (!p->host_stream) TRY(check_cuda(ctx, cudaStreamCreateWithFlags(&p->host_stream, cudaStreamNonBlocking), "cudaStreamCreate"));
     cudaStream_t s = p->host_stream;
@@ -1174,6 +1282,8 @@ int accb_program_destroy(accb_program *p) {
         for (auto &v : p->in_pool)
             for (auto &b : v)
                 if (b.ptr) cudaFree(b.ptr);
+        for (auto &b : p->slab_pool)
+            if (b.ptr) cudaFree(b.ptr);
         if (p->host_stream) cudaStreamDestroy(p->host_stream);
         for (auto s : p->pipe_stream)
             if (s) cudaStreamDestroy(s);

@@ -688,13 +688,13 @@ __host__ __device__ constexpr int stencil_tile_dim(int which) {
  * launches `stencil_tile` / `stencil2_tile` (rank 2) or `stencil_line` /
  * `stencil2_line` (rank 1) instead when their conditions hold.
  * Metadata: {.., element bytes, rows per tile, columns per tile, outputs per
- * tile of the line form, dynamic shared memory of the tile form}. */
+ * tile of the line form, dynamic shared memory of the tile form, rows the stencil reaches up and down}. */
 #define ACCB_STENCIL_ENTRIES(Fn, id, narr, name, tname, lname)                                 \
-    ACCB_META7(id, ACCB_STENCIL_CTA, sizeof(Fn::in_t),                                         \
+    ACCB_META8(id, ACCB_STENCIL_CTA, sizeof(Fn::in_t),                                         \
                (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(1)),                        \
                (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(2)),                        \
                (accb::stencil_line_len<Fn, ACCB_STENCIL_CTA>()),                               \
-               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(0)))                        \
+               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(0)), Fn::RY)                \
     extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_MINB)          \
         name(const __grid_constant__ accb_kparams p) {                                         \
         accb::stencil_body<Fn, narr, ACCB_STENCIL_CTA>(p);                                     \

@@ -281,14 +281,33 @@ def test_streamed_row_folds_and_tuple_maps(accb, P, ctx, oracle, workloads, rng)
     assert abs(float(w) - ref) <= 1e-5 * abs(ref) + 1e-5 and abs(float(s) - ref) <= 1e-5 * abs(ref) + 1e-5
 
 
+@pytest.mark.parametrize("shape,boundary,iters,chunk", [((512, 260), "clamp", 3, 4096), ((1000, 256), "mirror", 5, 20000),
+                                                        ((333, 1024), "constant", 2, 30000), ((2048, 130), "clamp", 10, 8000)])
+def test_stencil_chains_run_slab_by_slab(accb, P, ctx, oracle, workloads, rng, shape, boundary, iters, chunk):
+    """An iterated stencil on a host grid goes up, through the kernels and down in row slabs with a margin of
+    iters rows either side: bit-identical to the run that uploads the whole grid first, and equal to the oracle's
+    recurrence.  Then a chain of two different stencil nodes."""
+    W = workloads
+    g = rng.uniform(0, 1, shape).astype(np.float32)
+    gt = accb.ArrayType(2, np.float32)
+    const = np.float32(0.25) if boundary == "constant" else None
+    w, s = _both_ways(accb, ctx, lambda a: accb.stencil(P.BLUR, a, boundary=boundary, iters=iters, constant=const), [gt], [g], chunk)
+    assert s.shape == shape and np.array_equal(w, s)
+    ref = oracle.stencil2d_iter(g, W.BLUR_WEIGHTS, iters, boundary, cval=0.25)
+    assert np.all(np.abs(s - ref) <= 1e-5 * np.abs(ref) + 1e-6)
+    w, s = _both_ways(accb, ctx, lambda a: accb.stencil(P.BLUR, accb.stencil(P.BLUR, a, boundary=boundary, iters=2, constant=const),
+                                                          boundary="clamp", iters=1), [gt], [g], chunk)
+    assert np.array_equal(w, s)
+
+
 def test_programs_that_do_not_fit_run_whole(accb, P, ctx, oracle, workloads, rng):
-    """A stencil needs its neighbours' rows and a right scan starts at the far end: such programs are not cut into
-    pieces, whatever the piece size, and give the same results as before."""
+    """A Wrap stencil reaches across the whole grid and a right scan starts at the far end: such programs are not cut
+    into pieces or slabs, whatever the piece size, and give the same results as before."""
     W = workloads
     g = rng.uniform(0, 1, (512, 260)).astype(np.float32)
-    f = accb.run1With(ctx, lambda a: accb.stencil(P.BLUR, a, boundary="clamp", iters=3), accb.ArrayType(2, np.float32))
+    f = accb.run1With(ctx, lambda a: accb.stencil(P.BLUR, a, boundary="wrap", iters=3), accb.ArrayType(2, np.float32))
     r = f.stream_chunk(4096)(g)
-    ref = oracle.stencil2d_iter(g, W.BLUR_WEIGHTS, 3, "clamp")
+    ref = oracle.stencil2d_iter(g, W.BLUR_WEIGHTS, 3, "wrap")
     assert np.all(np.abs(r - ref) <= 1e-5 * np.abs(ref) + 1e-6)
     f.destroy()
     x = rng.integers(-9, 9, 100003).astype(np.int32)
