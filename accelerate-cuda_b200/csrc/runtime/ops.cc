@@ -454,18 +454,22 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
     const long long piece = pr.meta.v[7];
     const bool defer = !ctx->tune.foldseg_no_defer && piece > 0 && cols >= (1LL << 22);
-    auto second_launch = [&](int st) {
-        if (st != ACCB_OK || !defer) return st;
-        Prep pd;
-        int e = prepare(ctx, k, "foldSeg_deferred", 0, &pd);
-        if (e != ACCB_OK) return e;
+    /* everything that can fail is done before the first launch: a list left behind by a launch whose second half
+     * never ran would be reduced, with the wrong arrays, by the next foldSeg on this stream */
+    Prep pd;
+    if (defer) {
+        TRY(prepare(ctx, k, "foldSeg_deferred", 0, &pd));
         /* a listed segment of n elements has at most n / piece + 1 pieces */
         const size_t parts = (size_t)(rows * cols / piece) + ACCB_FOLD_DEFER_MAX;
-        e = grow(ctx, &sc->partial, &sc->partial_bytes, parts * std::max(8, pr.meta.v[2]), s, false);
-        if (e != ACCB_OK) return e;
+        TRY(grow(ctx, &sc->partial, &sc->partial_bytes, parts * std::max(8, pr.meta.v[2]), s, false));
+    }
+    auto second_launch = [&](int st) {
+        if (st != ACCB_OK || !defer) return st;
         accb_kparams q = p;
         q.aux[1] = sc->partial;
-        return launch_dependent(ctx, pd.fn, "foldSeg_deferred", ctx->sm_count * pd.per_sm, pd.block, s, q);
+        st = launch_dependent(ctx, pd.fn, "foldSeg_deferred", ctx->sm_count * pd.per_sm, pd.block, s, q);
+        if (st != ACCB_OK) cudaMemsetAsync(sc->words + kDeferredBase, 0, 2 * sizeof(unsigned), s); /* drop the list */
+        return st;
     };
     if (defer) {
         /* a block per segment fills the GPU only with enough segments: with fewer, every long one is handed over */

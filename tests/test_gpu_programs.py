@@ -177,6 +177,40 @@ def test_program_as_one_cuda_graph_replays_on_new_contents(accb, ctx, torch_cuda
     f.destroy()
 
 
+def test_fold_seg_with_a_long_segment_inside_a_cuda_graph(accb, P, ctx, torch_cuda, rng):
+    """A foldSeg over 5 M elements records two launches (the second one splits the segments that the first one put
+    on its list over all blocks); replays follow the arrays' new contents, also when another segment becomes the
+    long one."""
+    t = torch_cuda
+    nseg = 40000
+    f = accb.run1With(ctx, lambda v, o: accb.fold_seg(P.SEGSUM_I32, [v], o, np.int32, seed=np.int32(2)),
+                      accb.ArrayType(1, np.int32), accb.ArrayType(1, np.int32))
+    lens = rng.integers(0, 100, nseg)
+    lens[777] = 3_000_000
+    n = int(lens.sum())
+    x = t.from_numpy(rng.integers(-50, 50, n).astype(np.int32)).cuda()
+    offs = t.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).cuda()
+    s = t.cuda.Stream()
+    for rep in range(3):
+        if rep == 1:
+            x.add_(1)
+        if rep == 2:  # the long segment moves: same arrays, other contents
+            lens2 = lens.copy()
+            lens2[777], lens2[31000] = lens[31000], lens[777]
+            offs.copy_(t.from_numpy(np.concatenate([[0], np.cumsum(lens2)]).astype(np.int32)))
+        t.cuda.synchronize()
+        before = ctx.launch_count()
+        outs = f.run_device([x, offs], stream=s.cuda_stream, graph=True)
+        s.synchronize()
+        assert (ctx.launch_count() - before == 0) == (rep > 0)
+        got = t.as_tensor(_DevView(outs[0], "<i4"), device="cuda").cpu().numpy()
+        h, o = x.cpu().numpy().astype(np.int64), offs.cpu().numpy()
+        tot = np.concatenate([[0], np.cumsum(h)])
+        assert np.array_equal(got, (tot[o[1:]] - tot[o[:-1]] + 2).astype(np.int32))
+    ctx.sync()
+    f.destroy()
+
+
 # ------------------------------------------------------------- streamed host runs
 _D = "static __device__ __forceinline__"
 
