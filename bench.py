@@ -729,7 +729,7 @@ class SmvmWorkload(Workload):
     def step(self):
         self.ctx.fold_seg(self.k, [(self.vals, self.colidx), self.vec], 1, self.nnz, self.offs, self.rows, self.out,
                           seed=np.float32(0))
-        return 1
+        return 2 if self.nnz >= (1 << 22) else 1  # sources of 2^22 elements and more get the second launch
 
     def verify(self):
         t = self.t
@@ -737,6 +737,65 @@ class SmvmWorkload(Workload):
         csum = t.cat([t.zeros(1, dtype=t.float64, device="cuda"), t.cumsum(prod, 0)])
         ref = csum[self.offs[1:].long()] - csum[self.offs[:-1].long()]
         return bool(((self.out.double() - ref).abs() <= 1e-5 * ref.abs() + 1e-4).all())
+
+
+class FoldSegWorkload(Workload):
+    """foldSeg (+) 0 over 2^27 Int32 cut into segments of random length, mean 50 (0..100)."""
+    name, dtype = "foldSeg (+) 0, Int32, 2^27 elements, segment lengths uniform in 0..100", "int32"
+    mean = 50
+
+    def lengths(self, n):
+        t, W = self.t, self.W
+        lens = t.empty(int(n * 0.95) // self.mean, dtype=t.int32, device="cuda")
+        self.ctx.gen_uniform_i32(lens, lens.numel(), 0, W.SEED, W.S_SCAN, 2 * self.mean + 1)
+        return lens
+
+    def setup(self, n=None):
+        t, W = self.t, self.W
+        n = n or (1 << 27)
+        lens = self.lengths(n)
+        self.nseg = lens.numel()
+        self.offs = t.zeros(self.nseg + 1, dtype=t.int32, device="cuda")
+        self.offs[1:] = t.cumsum(lens.long(), 0).int()
+        self.n = int(self.offs[-1])
+        self.x = t.empty(self.n, dtype=t.int32, device="cuda")
+        self.ctx.gen_uniform_i32(self.x, self.n, 0, W.SEED, W.S_XS, 16)
+        self.out = t.zeros(self.nseg, dtype=t.int32, device="cuda")
+        self.k = self.ctx.kernel(self.functor("SEGSUM_I32")).wait()
+        self.bytes = 4 * self.n + 4 * (self.nseg + 1) + 4 * self.nseg
+        self.ctx.sync()
+
+    def step(self):
+        self.ctx.fold_seg(self.k, [self.x], 1, self.n, self.offs, self.nseg, self.out, seed=np.int32(0))
+        return 2 if self.n >= (1 << 22) else 1  # sources of 2^22 elements and more get the second launch
+
+    def verify(self):
+        t = self.t
+        csum = t.cat([t.zeros(1, dtype=t.int64, device="cuda"), t.cumsum(self.x, 0, dtype=t.int64)])
+        ref = csum[self.offs[1:].long()] - csum[self.offs[:-1].long()]
+        return bool(t.equal(self.out, ref.int()))
+
+
+class FoldSegGiantsWorkload(FoldSegWorkload):
+    """Short segments (0..16 elements) with three of 20 M, 9 M and 3 M elements among them: the long ones are handed
+    to the second launch, which splits them over all blocks."""
+    name = "foldSeg (+) 0, Int32, 8 M segments of 0..16 elements and three of 20 M, 9 M and 3 M"
+    mean = 8
+
+    def lengths(self, n):
+        t, W = self.t, self.W
+        lens = t.empty(8_000_000, dtype=t.int32, device="cuda")
+        self.ctx.gen_uniform_i32(lens, lens.numel(), 0, W.SEED, W.S_SCAN, 17)
+        lens[[5, 4_000_000, 7_999_999]] = t.tensor([20_000_000, 9_000_000, 3_000_001], dtype=t.int32, device="cuda")
+        return lens
+
+
+class FoldSegLongWorkload(FoldSegWorkload):
+    """Eight segments of 2^24 elements: every one goes to the second launch."""
+    name = "foldSeg (+) 0, Int32, 8 segments of 2^24 elements"
+
+    def lengths(self, n):
+        return self.t.full((8,), 1 << 24, dtype=self.t.int32, device="cuda")
 
 
 class Smooth1dWorkload(Workload):
@@ -902,8 +961,10 @@ class Stencil3dLaplaceWorkload(Stencil3dWorkload):
 
 
 SECONDARY_KERNEL = {"scan_chained": "scanl_bc", "hist_equal": "permute_smem", "hist_hot16": "permute_smem", "scan64": "scanl", "shortrows": "fold_staged", "smvm": "foldSeg_staged", "smooth1d": "stencil_line",
+                    "foldseg_irregular": "foldSeg_staged", "foldseg_giants": "foldSeg_staged", "foldseg_long": "foldSeg_deferred",
                     "transpose": "map_transposed_tma", "transpose_loadstore": "map_transposed", "stencil3d": "stencil3", "stencil3d_laplace": "stencil3"}
 SECONDARY = {"scan_chained": ScanChainedWorkload, "hist_equal": HistEqualWorkload, "hist_hot16": HistHotWorkload, "scan64": Scan64Workload, "shortrows": ShortRowsWorkload, "smvm": SmvmWorkload, "smooth1d": Smooth1dWorkload,
+             "foldseg_irregular": FoldSegWorkload, "foldseg_giants": FoldSegGiantsWorkload, "foldseg_long": FoldSegLongWorkload,
              "transpose": TransposeWorkload, "transpose_loadstore": TransposeLoadStoreWorkload, "stencil3d": Stencil3dWorkload, "stencil3d_laplace": Stencil3dLaplaceWorkload}
 
 
