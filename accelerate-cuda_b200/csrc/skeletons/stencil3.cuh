@@ -35,8 +35,9 @@
  * Functor contract (derive from accb::Stencil3<Tin, Tout, RZ, RY, RX>; 4-byte
  * Tin):
  *   static Tout apply(env, const Tin (&t)[2*RZ+1][2*RY+1][2*RX+1]);
+ *   static constexpr bool uses(int dz, int dy, int dx);   optional: the taps apply() reads (default: all)
  * with t[dz][dy][dx] the element at offset (dz-RZ, dy-RY, dx-RX), the order
- * in which Accelerate's stencil patterns nest (outermost dimension first).
+ * in which Accelerate's stencil patterns nest (outermost dimension first); taps that uses() denies read as zero.
  *
  *   in[0] source, out[0] result; ip[0] D, ip[1] H, ip[2] W (planes, rows,
  *   columns); ip[3] planes per block; ip[4] boundary; scalars[0..] the constant.
@@ -70,6 +71,23 @@ struct Stencil3 {
     typedef Tin in_t;
     typedef Tout out_t;
     static constexpr int RZ = RZ_, RY = RY_, RX = RX_;
+    /* does apply() read t[dz][dy][dx]?  A functor that reads only some taps (a 7-point Laplacian reads 7 of 27) says
+     * so by overriding this, and the rows and halo columns nobody reads are then neither loaded nor shuffled (a
+     * warp shuffle whose result is unused is not removed by the compiler). */
+    static constexpr bool uses(int, int, int) { return true; }
+};
+
+/* which parts of row (DZ, DY) of the neighbourhood a functor needs */
+template <class Fn, int DZ, int DY>
+struct Stencil3Row {
+    static constexpr bool some(int lo, int hi) {
+        for (int dx = lo; dx < hi; ++dx)
+            if (Fn::uses(DZ, DY, dx)) return true;
+        return false;
+    }
+    static constexpr bool any = some(0, 2 * Fn::RX + 1);
+    static constexpr bool left = some(0, Fn::RX);                  /* columns left of the thread's own four */
+    static constexpr bool right = some(Fn::RX + 1, 2 * Fn::RX + 1); /* columns right of them */
 };
 
 /* geometry of one plane tile in shared memory: TY + 2*RY rows of PITCH values; the TX centre columns start
@@ -94,14 +112,18 @@ __device__ __forceinline__ void stencil3_fill(typename Fn::in_t *tile, const typ
     typedef typename Fn::in_t T;
     typedef Stencil3Tile<Fn> G;
     const T *plane = src + (long long)(zz < 0 ? 0 : zz) * H * W;
-    /* centre columns: 16-byte loads where the whole vector is inside the row and aligned */
+    /* centre columns: 16-byte loads where the whole vector is inside the row and aligned.  A thread keeps its
+     * column of vectors and walks down the rows, CTA / VPR of them per pass */
     constexpr int VPR = G::TX / 4; /* vectors per row */
-    for (int i = threadIdx.x; i < G::ROWS * VPR; i += CTA) {
-        const int r = i / VPR, v = i - r * VPR;
+    static_assert(CTA % VPR == 0, "whole rows of vectors per pass");
+    constexpr int RPP = CTA / VPR;
+    const int v = threadIdx.x % VPR;
+    const int x = x0 + 4 * v;
+    const bool whole = zz >= 0 && vec_ok && x + 3 < W;
+    T *dst = tile + (threadIdx.x / VPR) * G::PITCH + G::PAD + 4 * v;
+    for (int r = threadIdx.x / VPR; r < G::ROWS; r += RPP, dst += RPP * G::PITCH) {
         const int yy = bound_coord(y0 - Fn::RY + r, H, mode);
-        const int x = x0 + 4 * v;
-        T *dst = tile + r * G::PITCH + G::PAD + 4 * v;
-        if (zz >= 0 && yy >= 0 && vec_ok && x + 3 < W) {
+        if (whole && yy >= 0) {
             /* asynchronous: no register holds the data, the caller waits for the group before the tile is read */
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(plane + (long long)yy * W + x)
                          : "memory");
@@ -123,6 +145,49 @@ __device__ __forceinline__ void stencil3_fill(typename Fn::in_t *tile, const typ
             tile[r * G::PITCH + G::PAD + dx] = (zz < 0 || yy < 0 || xx < 0) ? cval : plane[(long long)yy * W + xx];
         }
     }
+}
+
+/* Row (DZ, DY) of a thread's window: its own 4 columns by one 16-byte read, the RX halo columns either side from
+ * the neighbouring lanes' centre columns by shuffles (instead of 4-byte reads 16 bytes apart: a four-way bank
+ * conflict each); the two lanes at the ends of the row take the tile's own halo, which every lane reads from the
+ * same address (a broadcast).  Parts the functor does not read are skipped. */
+template <class Fn, int DZ, int DY>
+__device__ __forceinline__ void stencil3_row(const typename Fn::in_t *plane, int r, int lane,
+                                             typename Fn::in_t (&w)[4 + 2 * Fn::RX]) {
+    typedef typename Fn::in_t T;
+    typedef Stencil3Tile<Fn> G;
+    typedef Stencil3Row<Fn, DZ, DY> R;
+    constexpr int RX = Fn::RX;
+    if constexpr (R::any) {
+        const T *trow = plane + (r + DY) * G::PITCH + G::PAD; /* column x0 of this tile row */
+        const uint4 c = *reinterpret_cast<const uint4 *>(trow + 4 * lane);
+        memcpy(&w[RX], &c, 16);
+        if constexpr (R::left) {
+#pragma unroll
+            for (int h = 0; h < RX; ++h) {
+                const T from_left = shfl_up(w[4 + h], 1); /* lane - 1's last RX columns */
+                const T tile_left = trow[h - RX];
+                w[h] = lane == 0 ? tile_left : from_left;
+            }
+        }
+        if constexpr (R::right) {
+#pragma unroll
+            for (int h = 0; h < RX; ++h) {
+                const T from_right = shfl_down(w[RX + h], 1); /* lane + 1's first RX columns */
+                const T tile_right = trow[G::TX + h];
+                w[RX + 4 + h] = lane == 31 ? tile_right : from_right;
+            }
+        }
+    }
+}
+/* all rows of the window of output plane z; plane z + dz - RZ lives in ring slot (z + dz) mod RING */
+template <class Fn, int... ZY>
+__device__ __forceinline__ void stencil3_window(const typename Fn::in_t *ring, int z, int r, int lane,
+                                                typename Fn::in_t (&win)[2 * Fn::RZ + 1][2 * Fn::RY + 1][4 + 2 * Fn::RX],
+                                                std::integer_sequence<int, ZY...>) {
+    typedef Stencil3Tile<Fn> G;
+    constexpr int NY = 2 * Fn::RY + 1;
+    (stencil3_row<Fn, ZY / NY, ZY % NY>(ring + ((z + ZY / NY) % G::RING) * G::PLANE, r, lane, win[ZY / NY][ZY % NY]), ...);
 }
 
 template <class Fn, int CTA>
@@ -184,28 +249,8 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
             for (int r = w; r < G::TY; r += CTA / 32) {
                 const int y = y0 + r, x = x0 + 4 * lane;
                 if (y < H) { /* the same for every lane of the warp: the shuffles below see all 32 */
-                    T win[2 * RZ + 1][2 * RY + 1][4 + 2 * RX];
-#pragma unroll
-                    for (int dz = 0; dz <= 2 * RZ; ++dz) {
-                        const T *pl = slot(z - RZ + dz);
-#pragma unroll
-                        for (int dy = 0; dy <= 2 * RY; ++dy) {
-                            const T *trow = pl + (r + dy) * G::PITCH + G::PAD; /* column x0 of this tile row */
-                            const uint4 c = *reinterpret_cast<const uint4 *>(trow + 4 * lane);
-                            memcpy(&win[dz][dy][RX], &c, 16);
-                            /* the halo columns are the neighbouring lanes' centre columns: shuffles instead of 4-byte
-                             * reads 16 bytes apart (a four-way bank conflict each); the two lanes at the ends of the row
-                             * take the tile's own halo, which every lane reads from the same address (a broadcast) */
-#pragma unroll
-                            for (int h = 0; h < RX; ++h) {
-                                const T from_left = shfl_up(win[dz][dy][4 + h], 1);     /* lane - 1's last RX columns */
-                                const T from_right = shfl_down(win[dz][dy][RX + h], 1); /* lane + 1's first RX columns */
-                                const T tile_left = trow[h - RX], tile_right = trow[G::TX + h];
-                                win[dz][dy][h] = lane == 0 ? tile_left : from_left;
-                                win[dz][dy][RX + 4 + h] = lane == 31 ? tile_right : from_right;
-                            }
-                        }
-                    }
+                    T win[2 * RZ + 1][2 * RY + 1][4 + 2 * RX] = {};
+                    stencil3_window<Fn>(ring, z, r, lane, win, std::make_integer_sequence<int, (2 * RZ + 1) * (2 * RY + 1)>());
                     U o[4];
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {

@@ -38,6 +38,7 @@ from __future__ import annotations
 import builtins
 import hashlib
 import importlib
+import re
 from typing import Callable, List, Sequence, Tuple
 
 import numpy as np
@@ -1595,7 +1596,13 @@ def _stencil3_spec(f: Callable, tin, pattern):
     body, out = _trace(go)
     if len(out) != 1:
         raise NotImplementedError("stencils over tuples")
+    # the taps the traced function reads: the skeleton neither loads nor shuffles the rest
+    read = {tuple(int(g) for g in m.groups()) for m in re.finditer(r"\bt\[(\d+)\]\[(\d+)\]\[(\d+)\]", body + " " + out[0].code)}
+    table = ", ".join("{" + ", ".join("{" + ", ".join("true" if (z, y, x) in read else "false" for x in range(wx)) + "}"
+                                         for y in range(wy)) + "}" for z in range(wz))
     text = (f"struct @N@ : accb::Stencil3<{ctype(tin[0])}, {ctype(out[0].dt)}, {wz // 2}, {wy // 2}, {wx // 2}> {{\n"
+            f"    static constexpr bool uses(int z, int y, int x) {{\n"
+            f"        constexpr bool read[{wz}][{wy}][{wx}] = {{{table}}};\n        return read[z][y][x];\n    }}\n"
             f"    {_D} {ctype(out[0].dt)} apply(const accb::Env &, const {ctype(tin[0])} (&t)[{wz}][{wy}][{wx}]) {{\n"
             f"        {body}\n        return {out[0].code};\n    }}\n}};\n")
     name = _name("Stencil3", text)

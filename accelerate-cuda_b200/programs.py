@@ -323,6 +323,7 @@ struct Weighted27 : accb::Stencil3<float, float, 1, 1, 1> {{
 # rank 3: the 7-point Laplacian
 LAPLACE3 = KernelSpec("stencil3", "Laplace3", f"""
 struct Laplace3 : accb::Stencil3<float, float, 1, 1, 1> {{
+    static constexpr bool uses(int z, int y, int x) {{ return (z == 1) + (y == 1) + (x == 1) >= 2; }}  // centre + 6 axis neighbours
     {_D} float apply(const accb::Env &, const float (&t)[3][3][3]) {{
         return t[0][1][1] + t[2][1][1] + t[1][0][1] + t[1][2][1] + t[1][1][0] + t[1][1][2] - 6.0f * t[1][1][1];
     }}
