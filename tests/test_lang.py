@@ -410,6 +410,27 @@ def test_stencil_over_a_cube_and_over_pairs(ctx, rng, boundary, padmode):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("taps", [[(1, 1, 1), (0, 1, 1), (2, 1, 1), (1, 0, 1), (1, 2, 1), (1, 1, 0), (1, 1, 2)],  # 7-point
+                                  [(1, 1, 0), (0, 2, 1)],   # a left halo column in one row, centre columns in another
+                                  [(2, 0, 2)],              # one corner: a right halo column only
+                                  [(0, 0, 0), (2, 2, 2), (1, 1, 1)],
+                                  [(1, 1, 1)]])
+@pytest.mark.parametrize("boundary,padmode", [("clamp", "edge"), (("constant", -1.5), "constant")])
+def test_cube_stencils_that_read_some_of_their_taps(ctx, rng, taps, boundary, padmode):
+    """The functor printed for a rank-3 stencil tells the skeleton which taps the function reads; rows and halo
+    columns that nobody reads are skipped.  The cube is wider than one tile (128 columns, 32 rows) and ragged."""
+    d, h, w = 5, 37, (260 if boundary == "clamp" else 261)  # 16-byte copies of whole vectors, and the element-wise fill
+    c = rng.uniform(0, 1, (d, h, w)).astype(f32)
+    wts = {t: float(i + 1) for i, t in enumerate(taps)}
+    fn = lambda t: sum((wts[(z, y, x)] * t[z][y][x] for z, y, x in taps), A.constant(0, f32))  # noqa: E731
+    got = A.runWith(ctx, lambda a: A.stencil(fn, boundary, a), c)
+    kw = {"constant_values": -1.5} if padmode == "constant" else {}
+    p = np.pad(c.astype(f64), 1, mode=padmode, **kw)
+    ref = sum(wts[(z, y, x)] * p[z:z + d, y:y + h, x:x + w] for z, y, x in taps)
+    close(got, ref, 1e-6)
+
+
+@pytest.mark.gpu
 def test_iterated_stencil_and_stencil2(ctx, rng):
     g = rng.uniform(0, 1, (64, 128)).astype(f32)
     five = lambda t: 0.2 * (t[0][1] + t[1][0] + t[1][1] + t[1][2] + t[2][1])  # noqa: E731
