@@ -739,6 +739,20 @@ class SmvmWorkload(Workload):
         return bool(((self.out.double() - ref).abs() <= 1e-5 * ref.abs() + 1e-4).all())
 
 
+class SmvmBandedWorkload(SmvmWorkload):
+    """The same product with the non-zeros of row r in columns (r mod 2^20) .. + 63: the gathers of neighbouring rows
+    share cache lines, as they do for matrices that come from meshes and grids."""
+    name = "smvm: foldSeg over 2^24 rows, mean 8 non-zeros within 64 columns of a diagonal, Float32"
+
+    def setup(self, n=None):
+        super().setup(n)
+        t = self.t
+        row_of = t.repeat_interleave(t.arange(self.rows, device="cuda"), (self.offs[1:] - self.offs[:-1]).long())
+        self.colidx = ((row_of + self.colidx.long() % 64) % self.ncols).int()
+        del row_of
+        self.ctx.sync()
+
+
 class FoldSegWorkload(Workload):
     """foldSeg (+) 0 over 2^27 Int32 cut into segments of random length, mean 50 (0..100)."""
     name, dtype = "foldSeg (+) 0, Int32, 2^27 elements, segment lengths uniform in 0..100", "int32"
@@ -961,10 +975,10 @@ class Stencil3dLaplaceWorkload(Stencil3dWorkload):
 
 
 SECONDARY_KERNEL = {"scan_chained": "scanl_bc", "hist_equal": "permute_smem", "hist_hot16": "permute_smem", "scan64": "scanl", "shortrows": "fold_staged", "smvm": "foldSeg_staged", "smooth1d": "stencil_line",
-                    "foldseg_irregular": "foldSeg_staged", "foldseg_giants": "foldSeg_staged", "foldseg_long": "foldSeg_deferred",
+                    "smvm_banded": "foldSeg_staged", "foldseg_irregular": "foldSeg_staged", "foldseg_giants": "foldSeg_staged", "foldseg_long": "foldSeg_deferred",
                     "transpose": "map_transposed_tma", "transpose_loadstore": "map_transposed", "stencil3d": "stencil3", "stencil3d_laplace": "stencil3"}
 SECONDARY = {"scan_chained": ScanChainedWorkload, "hist_equal": HistEqualWorkload, "hist_hot16": HistHotWorkload, "scan64": Scan64Workload, "shortrows": ShortRowsWorkload, "smvm": SmvmWorkload, "smooth1d": Smooth1dWorkload,
-             "foldseg_irregular": FoldSegWorkload, "foldseg_giants": FoldSegGiantsWorkload, "foldseg_long": FoldSegLongWorkload,
+             "smvm_banded": SmvmBandedWorkload, "foldseg_irregular": FoldSegWorkload, "foldseg_giants": FoldSegGiantsWorkload, "foldseg_long": FoldSegLongWorkload,
              "transpose": TransposeWorkload, "transpose_loadstore": TransposeLoadStoreWorkload, "stencil3d": Stencil3dWorkload, "stencil3d_laplace": Stencil3dLaplaceWorkload}
 
 
