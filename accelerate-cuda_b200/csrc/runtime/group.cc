@@ -450,6 +450,14 @@ int accb_group_permute(accb_group *g, accb_kernel *k, accb_kernel *k_merge, cons
 }
 
 /* ---------------------------------------------------------- stencil */
+/* elements of one "row" of a slab: the slabs are cut along the outermost dimension, so a row of a matrix is a row
+ * and a row of a cube is a plane */
+static size_t slab_row_elems(const accb_array &a) {
+    size_t n = 1;
+    for (int d = 0; d + 1 < a.rank; ++d) n *= (size_t)a.shape[d];
+    return n;
+}
+
 static void halo_rows(const accb_group *g, int rank, int reach, int boundary, int *top, int *bottom) {
     const bool ring = boundary == ACCB_WRAP && g->n > 1;
     *top = (rank > 0 || ring) ? reach : 0;
@@ -494,10 +502,10 @@ static int fill_halos(accb_group *g, const accb_array *a, const int *rows, const
 static int check_slabs(accb_group *g, const accb_array *a, const int *rows, const std::vector<int> &pt, const std::vector<int> &pb,
                        int nc, std::vector<size_t> &row_elems) {
     for (int r = 0; r < g->n; ++r) {
-        if (a[r].rank < 1 || a[r].rank > 2 || a[r].ncomp != nc)
-            return gfail(g, ACCB_EINVAL, "rank %d: slabs must be vectors or matrices of the same type", r);
+        if (a[r].rank < 1 || a[r].rank > 3 || a[r].ncomp != nc)
+            return gfail(g, ACCB_EINVAL, "rank %d: slabs must be vectors, matrices or cubes of the same type", r);
         const int outer = a[r].shape[a[r].rank - 1];
-        row_elems[r] = a[r].rank == 2 ? (size_t)a[r].shape[0] : 1;
+        row_elems[r] = slab_row_elems(a[r]);
         if (outer != pt[r] + rows[r] + pb[r] || row_elems[r] != row_elems[0])
             return gfail(g, ACCB_EINVAL, "rank %d: slab of %d rows, expected %d + %d + %d", r, outer, pt[r], rows[r], pb[r]);
     }
@@ -597,10 +605,10 @@ int accb_group_stencil_iterate(accb_group *g, accb_kernel *k, const accb_array *
     std::vector<size_t> row_elems(G);
     for (int r = 0; r < G; ++r) {
         halo_rows(g, r, reach, boundary, &pt[r], &pb[r]);
-        if (a[r].rank < 1 || a[r].rank > 2 || b[r].rank != a[r].rank || a[r].ncomp != nc || b[r].ncomp != nc)
-            return gfail(g, ACCB_EINVAL, "rank %d: slabs must be vectors or matrices of the same type", r);
+        if (a[r].rank < 1 || a[r].rank > 3 || b[r].rank != a[r].rank || a[r].ncomp != nc || b[r].ncomp != nc)
+            return gfail(g, ACCB_EINVAL, "rank %d: slabs must be vectors, matrices or cubes of the same type", r);
         const int outer = a[r].shape[a[r].rank - 1];
-        row_elems[r] = a[r].rank == 2 ? (size_t)a[r].shape[0] : 1;
+        row_elems[r] = slab_row_elems(a[r]);
         if (outer != pt[r] + rows[r] + pb[r] || b[r].shape[b[r].rank - 1] != outer || row_elems[r] != row_elems[0])
             return gfail(g, ACCB_EINVAL, "rank %d: slab of %d rows, expected %d + %d + %d", r, outer, pt[r], rows[r], pb[r]);
         if (G > 1 && rows[r] < reach)

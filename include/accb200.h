@@ -468,7 +468,8 @@ ACCB_API int accb_group_permute(accb_group *grp, accb_kernel *k, accb_kernel *k_
  * own rows in the middle of a[r].  The halos are filled from the neighbours' rows by peer copies, then all
  * applications run on the padded slab: what the kernel's boundary treatment does at a padded edge creeps inwards
  * by ry rows per application, exactly as far as the halo reaches.  *result_in_b tells which buffer holds the
- * result (own rows only; the halos hold garbage).  `ry` is the stencil's reach along the outermost dimension. */
+ * result (own rows only; the halos hold garbage).  `ry` is the stencil's reach along the outermost dimension.
+ * Vectors, matrices and cubes: the slabs are cut along the outermost dimension, so a "row" of a cube is a plane. */
 ACCB_API int accb_group_stencil_layout(accb_group *grp, int rank, int iters, int ry, int boundary, int *pad_top,
                                        int *pad_bottom);
 ACCB_API int accb_group_stencil_iterate(accb_group *grp, accb_kernel *k, const accb_array *a, const accb_array *b,

@@ -183,6 +183,35 @@ def test_group_iterated_blur_with_one_halo_exchange(group, P, torch_cuda, oracle
 
 
 @pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
+@pytest.mark.parametrize("iters", [1, 3])
+def test_group_iterated_stencil_over_a_cube_cut_into_slabs_of_planes(group, P, torch_cuda, oracle, rng, boundary, iters):
+    """Rank 3: the slabs are runs of planes, a halo "row" is a whole plane (the 27-tap weighted stencil of the rank-3
+    skeleton, applied iters times with one halo exchange)."""
+    t, G = torch_cuda, group.size
+    d, h, w = 12 * G + 5, 21, 132
+    a = rng.uniform(0, 1, (d, h, w)).astype(np.float32)
+    c = [r * (d // G) for r in range(G)] + [d]
+    planes = [c[r + 1] - c[r] for r in range(G)]
+    pads = [group.stencil_layout(r, iters, 1, boundary) for r in range(G)]
+    A, B = [], []
+    for r in range(G):
+        pt, pb = pads[r]
+        slab = np.full((pt + planes[r] + pb, h, w), np.nan, np.float32)
+        slab[pt:pt + planes[r]] = a[c[r]:c[r + 1]]
+        A.append(put(t, slab, group.devices[r]))
+        B.append(t.empty_like(A[-1]))
+    sync_all(t)
+    res = group.stencil_iterate(P.WEIGHTED27, A, B, planes, iters, 1, boundary, constant=np.float32(0.25))
+    group.sync()
+    got = np.concatenate([res[r].cpu().numpy()[pads[r][0]:pads[r][0] + planes[r]] for r in range(G)])
+    w27 = (np.arange(27, dtype=np.float64).reshape(3, 3, 3) + 1) / 378.0
+    ref = a.astype(np.float64)
+    for _ in range(iters):
+        ref = oracle.stencil3d(ref.astype(np.float32), w27, boundary, 0.25)
+    close(got, ref, 1e-5)
+
+
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
 def test_group_stencil2_on_row_slabs(group, P, torch_cuda, oracle, rng, boundary):
     """stencil2 over two matrices dealt out as row slabs: both sources' halo rows come from the neighbours
     (Execute.hs:427-450 on one device)."""
