@@ -572,9 +572,10 @@ static long long inner_elems(const accb_array &a) {
     return n;
 }
 
-/* A chain of rank-2 stencils over ONE host grid (a blur applied ten times, say) does not stream element by
- * element, but it does by ROW SLABS: a slab of the result depends on the slab of the source plus as many rows above
- * and below as the whole chain reaches (the sum over its stencils of applications x row radius).  Every slab is
+/* A chain of stencils over ONE host grid or cube (a blur applied ten times, say) does not stream element by
+ * element, but it does by ROW SLABS (slabs of planes for a cube): a slab of the result depends on the slab of the
+ * source plus as many rows above and below as the whole chain reaches (the sum over its stencils of applications
+ * x reach along the outermost dimension).  Every slab is
  * uploaded with that margin, the chain is applied to the widened slab as if it were a whole grid -- rows next to a
  * cut are wrong by one more row per application, which is what the margin is for, while at the grid's real top and
  * bottom the slab's edge IS the grid's edge and the boundary condition applies as always -- and the slab's own rows
@@ -585,26 +586,36 @@ static int run_host_slabbed(accb_program *p, const accb_array *host_in, accb_arr
     *status = ACCB_OK;
     accb_context *ctx = p->ctx;
     if (ctx->tune.no_pipeline || p->stream_chunk == 0 || p->ninputs != 1 || p->outputs.size() != 1 || p->nodes.empty()) return 0;
-    if (host_in[0].rank != 2 || p->types[0].ncomp != 1) return 0;
+    const int rank = host_in[0].rank;
+    if ((rank != 2 && rank != 3) || p->types[0].ncomp != 1) return 0;
     long long reach = 0;
     size_t widest = p->types[0].comp_bytes[0];
     int prev = 0;
     for (Node &nd : p->nodes) {
         if (nd.kind != N_STENCIL || nd.shape_like != prev || nd.boundary == ACCB_WRAP || nd.iters < 1) return 0;
-        if (nd.out_type.ncomp != 1 || nd.out_type.rank != 2) return 0;
+        if (nd.out_type.ncomp != 1 || nd.out_type.rank != rank) return 0;
         CUfunction fn;
         KernelMeta meta;
-        if (get_function(ctx, nd.k, "stencil", &fn, &meta) != ACCB_OK) return 0;
-        reach += (long long)nd.iters * meta.v[7];
+        /* how far the stencil reaches along the outermost dimension: rows for a matrix, planes for a cube */
+        if (rank == 2) {
+            if (nd.k->skeleton != SK_STENCIL || get_function(ctx, nd.k, "stencil", &fn, &meta) != ACCB_OK) return 0;
+            reach += (long long)nd.iters * meta.v[7];
+        } else {
+            if (nd.k->skeleton != SK_STENCIL3 || get_function(ctx, nd.k, "stencil3", &fn, &meta) != ACCB_OK) return 0;
+            reach += (long long)nd.iters * (meta.v[5] / 2);
+        }
         widest = std::max<size_t>(widest, nd.out_type.comp_bytes[0]);
         prev = nd.out_id;
     }
     if (p->outputs[0] != prev) return 0;
-    const long long W = host_in[0].shape[0], H = host_in[0].shape[1];
+    /* a "row" is everything below the outermost dimension: a row of a matrix, a plane of a cube */
+    const long long W = rank == 2 ? host_in[0].shape[0] : (long long)host_in[0].shape[0] * host_in[0].shape[1];
+    const long long H = host_in[0].shape[rank - 1];
     if (W < 1 || reach < 1) return 0;
     /* slabs of about 32 MiB, at least eight times the margin, a multiple of 16 rows */
     long long rows = p->stream_chunk > 0 ? p->stream_chunk / W : (32LL << 20) / (W * (long long)widest);
-    rows = std::max(std::max(rows, 8 * reach), 16LL) / 16 * 16;
+    rows = std::max(rows, 8 * reach);
+    if (rank == 2) rows = std::max(rows, 16LL) / 16 * 16;
     if (H < 2 * rows) return 0;
     const long long nslabs = (H + rows - 1) / rows;
     const size_t in_bytes = p->types[0].comp_bytes[0], out_bytes = p->types[prev].comp_bytes[0];
@@ -645,7 +656,7 @@ static int run_host_slabbed(accb_program *p, const accb_array *host_in, accb_arr
             /* this slab's pair of work grids was last read by the download of the slab before the previous one */
             if (sl >= 2) TRY(check_cuda(ctx, cudaStreamWaitEvent(comp, p->pipe_events[3 * (sl - 2) + 2], 0), "cudaStreamWaitEvent"));
             accb_array cur = host_in[0];
-            cur.shape[1] = (int)(e1 - e0);
+            cur.shape[rank - 1] = (int)(e1 - e0);
             cur.ptr[0] = static_cast<char *>(dev_in) + e0 * W * in_bytes;
             int next_work = 0;
             for (Node &nd : p->nodes) {
@@ -668,9 +679,8 @@ static int run_host_slabbed(accb_program *p, const accb_array *host_in, accb_arr
             TRY(check_cuda(ctx, cudaEventRecord(ev_down, down), "cudaEventRecord"));
         }
         TRY(check_cuda(ctx, cudaStreamSynchronize(down), "cudaStreamSynchronize"));
-        host_out[0].rank = 2;
-        host_out[0].shape[0] = (int)W;
-        host_out[0].shape[1] = (int)H;
+        host_out[0].rank = rank;
+        for (int d = 0; d < rank; ++d) host_out[0].shape[d] = host_in[0].shape[d];
         host_out[0].ncomp = 1;
         return ACCB_OK;
     };

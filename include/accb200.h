@@ -403,9 +403,9 @@ ACCB_API int accb_awhile(accb_program *cond, accb_program *body, accb_stream str
  * host_in[i] / host_out[j] point to one host buffer per component.  A program made of maps, folds, left scans
  * and permutes over inputs of one outermost extent is run in pieces (see accb_map_at), so that both directions
  * of the host link and the GPU work at the same time; accb_program_stream_chunk sets the piece size in elements
- * (-1: the default of 2^23, 0: never run in pieces).  A chain of rank-2 stencils over one grid (Clamp, Mirror or
- * Constant boundaries) is run in row slabs instead, each uploaded with as many rows above and below as the chain
- * reaches; the results are bit-identical to the whole-grid run.  Use pinned host memory for the copies to overlap. */
+ * (-1: the default of 2^23, 0: never run in pieces).  A chain of stencils over one grid or cube (Clamp, Mirror or
+ * Constant boundaries) is run in row slabs (slabs of planes) instead, each uploaded with as many rows above and
+ * below as the chain reaches; the results are bit-identical to the whole-grid run.  Use pinned host memory for the copies to overlap. */
 ACCB_API int accb_program_stream_chunk(accb_program *p, long long elements);
 ACCB_API int accb_program_run_host(accb_program *p, const accb_array *host_in, accb_array *host_out);
 ACCB_API int accb_program_destroy(accb_program *p);

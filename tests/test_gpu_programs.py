@@ -334,6 +334,21 @@ def test_stencil_chains_run_slab_by_slab(accb, P, ctx, oracle, workloads, rng, s
     assert np.array_equal(w, s)
 
 
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "constant"])
+def test_cube_stencils_run_in_slabs_of_planes(accb, P, ctx, oracle, rng, boundary):
+    """Rank 3 from host arrays: slabs of planes, each with the planes above and below that the applications reach;
+    bit-identical to the whole-cube run."""
+    c = rng.uniform(0, 1, (70, 24, 132)).astype(np.float32)
+    ct = accb.ArrayType(3, np.float32)
+    const = np.float32(0.25) if boundary == "constant" else None
+    w, s = _both_ways(accb, ctx, lambda a: accb.stencil(P.WEIGHTED27, a, boundary=boundary, iters=2, constant=const), [ct], [c],
+                      8 * 24 * 132)
+    assert s.shape == c.shape and np.array_equal(w, s)
+    w27 = (np.arange(27, dtype=np.float64).reshape(3, 3, 3) + 1) / 378.0
+    ref = oracle.stencil3d(oracle.stencil3d(c, w27, boundary, 0.25).astype(np.float32), w27, boundary, 0.25)
+    assert np.all(np.abs(s - ref) <= 1e-5 * np.abs(ref) + 1e-6)
+
+
 def test_programs_that_do_not_fit_run_whole(accb, P, ctx, oracle, workloads, rng):
     """A Wrap stencil reaches across the whole grid and a right scan starts at the far end: such programs are not cut
     into pieces or slabs, whatever the piece size, and give the same results as before."""
