@@ -121,17 +121,24 @@ __device__ __forceinline__ void stencil3_fill(typename Fn::in_t *tile, const typ
     const int x = x0 + 4 * v;
     const bool whole = zz >= 0 && vec_ok && x + 3 < W;
     T *dst = tile + (threadIdx.x / VPR) * G::PITCH + G::PAD + 4 * v;
-    for (int r = threadIdx.x / VPR; r < G::ROWS; r += RPP, dst += RPP * G::PITCH) {
-        const int yy = bound_coord(y0 - Fn::RY + r, H, mode);
-        if (whole && yy >= 0) {
-            /* asynchronous: no register holds the data, the caller waits for the group before the tile is read */
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(plane + (long long)yy * W + x)
-                         : "memory");
-        } else {
+    if (whole && y0 - Fn::RY >= 0 && y0 - Fn::RY + G::ROWS <= H) {
+        /* all rows of the tile are rows of the cube (every tile but those along two faces): no boundary map */
+        const T *from = plane + (long long)(y0 - Fn::RY + (int)(threadIdx.x / VPR)) * W + x;
+        for (int r = threadIdx.x / VPR; r < G::ROWS; r += RPP, dst += RPP * G::PITCH, from += (long long)RPP * W)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(from) : "memory");
+    } else {
+        for (int r = threadIdx.x / VPR; r < G::ROWS; r += RPP, dst += RPP * G::PITCH) {
+            const int yy = bound_coord(y0 - Fn::RY + r, H, mode);
+            if (whole && yy >= 0) {
+                /* asynchronous: no register holds the data, the caller waits for the group before the tile is read */
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(plane + (long long)yy * W + x)
+                             : "memory");
+            } else {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int xx = bound_coord(x + k, W, mode);
-                dst[k] = (zz < 0 || yy < 0 || xx < 0) ? cval : plane[(long long)yy * W + xx];
+                for (int k = 0; k < 4; ++k) {
+                    const int xx = bound_coord(x + k, W, mode);
+                    dst[k] = (zz < 0 || yy < 0 || xx < 0) ? cval : plane[(long long)yy * W + xx];
+                }
             }
         }
     }
@@ -152,14 +159,14 @@ __device__ __forceinline__ void stencil3_fill(typename Fn::in_t *tile, const typ
  * conflict each); the two lanes at the ends of the row take the tile's own halo, which every lane reads from the
  * same address (a broadcast).  Parts the functor does not read are skipped. */
 template <class Fn, int DZ, int DY>
-__device__ __forceinline__ void stencil3_row(const typename Fn::in_t *plane, int r, int lane,
+__device__ __forceinline__ void stencil3_row(const typename Fn::in_t *ring, int at, int lane,
                                              typename Fn::in_t (&w)[4 + 2 * Fn::RX]) {
     typedef typename Fn::in_t T;
     typedef Stencil3Tile<Fn> G;
     typedef Stencil3Row<Fn, DZ, DY> R;
     constexpr int RX = Fn::RX;
     if constexpr (R::any) {
-        const T *trow = plane + (r + DY) * G::PITCH + G::PAD; /* column x0 of this tile row */
+        const T *trow = ring + at + DY * G::PITCH; /* column x0 of this tile row; `at`: column x0 of window row 0 */
         const uint4 c = *reinterpret_cast<const uint4 *>(trow + 4 * lane);
         memcpy(&w[RX], &c, 16);
         if constexpr (R::left) {
@@ -180,14 +187,14 @@ __device__ __forceinline__ void stencil3_row(const typename Fn::in_t *plane, int
         }
     }
 }
-/* all rows of the window of output plane z; plane z + dz - RZ lives in ring slot (z + dz) mod RING */
+/* all rows of a thread's window: planes[dz] is where the plane tile of input plane z + dz - RZ starts in the ring,
+ * row the offset of column x0 of the window's first row inside a plane tile (both worked out once, not per row) */
 template <class Fn, int... ZY>
-__device__ __forceinline__ void stencil3_window(const typename Fn::in_t *ring, int z, int r, int lane,
+__device__ __forceinline__ void stencil3_window(const typename Fn::in_t *ring, const int (&planes)[2 * Fn::RZ + 1], int row, int lane,
                                                 typename Fn::in_t (&win)[2 * Fn::RZ + 1][2 * Fn::RY + 1][4 + 2 * Fn::RX],
                                                 std::integer_sequence<int, ZY...>) {
-    typedef Stencil3Tile<Fn> G;
     constexpr int NY = 2 * Fn::RY + 1;
-    (stencil3_row<Fn, ZY / NY, ZY % NY>(ring + ((z + ZY / NY) % G::RING) * G::PLANE, r, lane, win[ZY / NY][ZY % NY]), ...);
+    (stencil3_row<Fn, ZY / NY, ZY % NY>(ring, planes[ZY / NY] + row, lane, win[ZY / NY][ZY % NY]), ...);
 }
 
 template <class Fn, int CTA>
@@ -245,12 +252,17 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
                 fetch(z + G::AHEAD + RZ, y0, x0);
             else
                 asm volatile("cp.async.commit_group;" ::: "memory");
+            int planes[2 * RZ + 1]; /* input plane z + dz - RZ lives in ring slot (z + dz) mod RING */
+#pragma unroll
+            for (int dz = 0; dz <= 2 * RZ; ++dz) planes[dz] = (int)((unsigned)(z + dz) % (unsigned)G::RING) * G::PLANE;
+            U *zout = out + (long long)z * H * W;
             /* warp w computes rows w, w + 8, ..: lane l the columns 4l .. 4l + 3 */
             for (int r = w; r < G::TY; r += CTA / 32) {
                 const int y = y0 + r, x = x0 + 4 * lane;
                 if (y < H) { /* the same for every lane of the warp: the shuffles below see all 32 */
                     T win[2 * RZ + 1][2 * RY + 1][4 + 2 * RX] = {};
-                    stencil3_window<Fn>(ring, z, r, lane, win, std::make_integer_sequence<int, (2 * RZ + 1) * (2 * RY + 1)>());
+                    stencil3_window<Fn>(ring, planes, r * G::PITCH + G::PAD, lane, win,
+                                        std::make_integer_sequence<int, (2 * RZ + 1) * (2 * RY + 1)>());
                     U o[4];
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
@@ -263,7 +275,7 @@ __device__ __forceinline__ void stencil3_body(const accb_kparams &p) {
                                 for (int dx = 0; dx <= 2 * RX; ++dx) t[dz][dy][dx] = win[dz][dy][k + dx];
                         o[k] = Fn::apply(env, t);
                     }
-                    U *dst = out + ((long long)z * H + y) * W + x;
+                    U *dst = zout + (long long)y * W + x;
                     if (x >= W) {
                         /* beyond the last column: nothing to store */
                     } else if (vec_ok && sizeof(U) == 4 && x + 3 < W) {
