@@ -115,7 +115,8 @@ def sharded_histogram(local_hist: torch.Tensor, defaults: torch.Tensor, group=No
 
 
 def exchange_halos(grid: torch.Tensor, ry: int, boundary: str = "clamp", group=None):
-    """Refresh the halo rows of a row-slab.
+    """Refresh the halo rows of a row-slab (of a matrix; for a cube cut along its outermost dimension a "row" is
+    a plane).
 
     ``grid`` has ry halo rows above and below the rank's interior rows.  Interior
     edge rows go to the neighbours' halos; at the global top and bottom the halo
@@ -154,13 +155,13 @@ def exchange_halos(grid: torch.Tensor, ry: int, boundary: str = "clamp", group=N
     if has_up:
         pass  # received in place
     elif boundary == "clamp":
-        grid[:ry] = interior[:1].expand(ry, -1)
+        grid[:ry] = interior[:1].expand(ry, *interior.shape[1:])
     elif boundary == "mirror":
         grid[:ry] = interior[1:ry + 1].flip(0)
     if has_down:
         pass  # received in place
     elif boundary == "clamp":
-        grid[-ry:] = interior[-1:].expand(ry, -1)
+        grid[-ry:] = interior[-1:].expand(ry, *interior.shape[1:])
     elif boundary == "mirror":
         grid[-ry:] = interior[-ry - 1:-1].flip(0)
     return grid
@@ -232,8 +233,8 @@ def sharded_stencil_iterate(grid_local: torch.Tensor, iters: int, ry: int, local
     to a slab with halo rows (any boundary treatment in x is the kernel's; rows
     beyond the halo are never read because the halo already carries the
     boundary)."""
-    h, w = grid_local.shape
-    a = torch.empty((h + 2 * ry, w), dtype=grid_local.dtype, device=grid_local.device)
+    h = grid_local.shape[0]
+    a = torch.empty((h + 2 * ry, *grid_local.shape[1:]), dtype=grid_local.dtype, device=grid_local.device)
     a[ry:ry + h] = grid_local
     for _ in range(iters):
         exchange_halos(a, ry, boundary, group)

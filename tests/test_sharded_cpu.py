@@ -85,6 +85,19 @@ def _worker(rank, world, port, case, ret):
             apply2 = lambda p, q: torch.from_numpy(oracle.stencil2_2d(p.numpy(), q.numpy(), w1, w2, mode))  # noqa: E731
             got = sh.sharded_stencil2(torch.from_numpy(a[lo:hi].copy()), torch.from_numpy(b[lo:hi].copy()), 1, apply2, boundary=mode)
             ok = np.allclose(got.numpy(), oracle.stencil2_2d(a, b, w1, w2, mode)[lo:hi], rtol=0, atol=1e-14)
+        elif case.startswith("cube"):
+            # rank 3: slabs of planes, a halo "row" is a plane
+            mode = case.split("-")[1]
+            d, h, w, iters = 6 * world + 3, 7, 12, 3
+            g = W.uniform_f32(W.SEED, W.S_GRID, d * h * w, 0, 1).reshape(d, h, w).astype(np.float64)
+            lo, hi = (rank * (d // world), (rank + 1) * (d // world) if rank < world - 1 else d)
+            w27 = (np.arange(27, dtype=np.float64).reshape(3, 3, 3) + 1) / 378.0
+            apply3 = lambda a: torch.from_numpy(oracle.stencil3d(a.numpy(), w27, mode))  # noqa: E731
+            got = sh.sharded_stencil_iterate(torch.from_numpy(g[lo:hi].copy()), iters, 1, apply3, boundary=mode)
+            ref = g
+            for _ in range(iters):
+                ref = oracle.stencil3d(ref, w27, mode)
+            ok = np.allclose(got.numpy(), ref[lo:hi], rtol=0, atol=1e-14)
         elif case.startswith("stencil"):
             mode = case.split("-")[1]
             h, w, iters = 12 * world + 5, 40, 4
@@ -117,7 +130,8 @@ def _worker(rank, world, port, case, ret):
 @pytest.mark.parametrize("world", [2, 3])
 @pytest.mark.parametrize("case", ["scan", "hist", "dot", "stencil-clamp", "stencil-mirror", "stencil-wrap",
                                   "stencilwide-clamp", "stencilwide-mirror", "stencilwide-wrap", "stencilshort-clamp",
-                                  "foldseg", "stencil2-clamp", "stencil2-mirror", "stencil2-wrap"])
+                                  "foldseg", "stencil2-clamp", "stencil2-mirror", "stencil2-wrap",
+                                  "cube-clamp", "cube-mirror", "cube-wrap"])
 def test_sharded_paths_match_the_single_device_oracle(case, world):
     mgr = mp.Manager()
     ret = mgr.dict()
