@@ -131,6 +131,7 @@ def lib() -> C.CDLL:
             "accb_stencil": [vp, vp, vp, arrp, i32, vp, sz, arrp],
             "accb_stencil2": [vp, vp, vp, arrp, arrp, i32, vp, sz, arrp],
             "accb_stencil_iterate": [vp, vp, vp, arrp, arrp, i32, i32, vp, sz, C.POINTER(i32)],
+            "accb_stencil_iterate_from": [vp, vp, vp, arrp, arrp, arrp, i32, i32, vp, sz, C.POINTER(i32)],
             "accb_program_create": [vp, i32, C.POINTER(accb_value_type), C.POINTER(vp)],
             "accb_program_map": [vp, vp, C.POINTER(i32), i32, i32, C.POINTER(accb_value_type), vp, sz],
             "accb_program_fold": [vp, vp, C.POINTER(i32), i32, i32, i32, vp, sz, C.POINTER(accb_value_type)],
@@ -527,14 +528,16 @@ class Context:
         _check(lib().accb_stencil2(self.handle, self._k(kernel), self._stream(stream), C.byref(a), C.byref(b),
                                    BOUNDARY[boundary], cb, cn, C.byref(o)), self.handle)
 
-    def stencil_iterate(self, kernel, a, b, iters: int, boundary="clamp", constant=None, stream=None):
-        """``iters`` applications ping-ponging between ``a`` and ``b``; returns the array holding the result."""
+    def stencil_iterate(self, kernel, a, b, iters: int, boundary="clamp", constant=None, stream=None, src=None):
+        """``iters`` applications ping-ponging between ``a`` and ``b`` (starting from ``src``, which is only read, if
+        one is given); returns the array holding the result."""
         cb, cn = _bytes_of(constant)
         aa, bb = to_accb_array(a), to_accb_array(b)
+        ss = to_accb_array(src) if src is not None else None
         in_b = C.c_int()
-        _check(lib().accb_stencil_iterate(self.handle, self._k(kernel), self._stream(stream), C.byref(aa),
-                                          C.byref(bb), iters, BOUNDARY[boundary], cb, cn, C.byref(in_b)),
-               self.handle)
+        _check(lib().accb_stencil_iterate_from(self.handle, self._k(kernel), self._stream(stream),
+                                               C.byref(ss) if ss is not None else None, C.byref(aa), C.byref(bb), iters,
+                                               BOUNDARY[boundary], cb, cn, C.byref(in_b)), self.handle)
         return b if in_b.value else a
 
     # -- synthetic inputs

@@ -135,7 +135,7 @@ struct CudaAllocator : DeviceAllocator {
 namespace accb_rt {
 /* Tuning knobs, read from the environment ONCE when a context is created (never on the launch path):
  *   ACCB_FOLD_STAGE_MAX, ACCB_FOLD_NO_STAGE, ACCB_FOLDSEG_STAGE_MAX, ACCB_FOLDSEG_STAGE_FILL8,
- *   ACCB_FOLDSEG_STAGE_LANES, ACCB_FOLDSEG_NO_DEFER, ACCB_PERMUTE_REPLICAS, ACCB_STENCIL_NO_TILE, ACCB_STENCIL_ROWS,
+ *   ACCB_FOLDSEG_STAGE_LANES, ACCB_FOLDSEG_NO_DEFER, ACCB_PERMUTE_REPLICAS, ACCB_STENCIL_NO_TILE, ACCB_STENCIL_NO_FUSE, ACCB_STENCIL_ROWS,
  *   ACCB_PIPELINE_CHUNK_LOG2, ACCB_NO_PIPELINE, ACCB_TRANSPOSE_TMA (0 or 1). */
 struct Tuning {
     long long fold_stage_max = 128;    /* longest row the staged thread-per-row fold takes */
@@ -146,6 +146,7 @@ struct Tuning {
     bool foldseg_no_defer = false;     /* never hand long segments over to a second launch */
     int permute_replicas = 4;          /* shared-memory copies of a privatised permute destination */
     bool stencil_no_tile = false;
+    bool stencil_no_fuse = false;      /* iterated stencils: never two applications per launch */
     int stencil_rows = 64;             /* band height of the register-form stencil */
     bool transpose_tma = true;         /* transposed maps of one 4-byte value through tensor-map copies */
     int pipeline_chunk_log2 = 0;       /* chunk of the host pipeline; 0: default */

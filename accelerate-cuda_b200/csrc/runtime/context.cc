@@ -116,6 +116,7 @@ void Tuning::read_environment() {
     foldseg_no_defer = getenv("ACCB_FOLDSEG_NO_DEFER") != nullptr;
     permute_replicas = (int)std::max(1LL, num("ACCB_PERMUTE_REPLICAS", permute_replicas));
     stencil_no_tile = getenv("ACCB_STENCIL_NO_TILE") != nullptr;
+    stencil_no_fuse = getenv("ACCB_STENCIL_NO_FUSE") != nullptr;
     stencil_rows = (int)std::max(1LL, num("ACCB_STENCIL_ROWS", stencil_rows));
     transpose_tma = num("ACCB_TRANSPOSE_TMA", 1) != 0;
     pipeline_chunk_log2 = (int)num("ACCB_PIPELINE_CHUNK_LOG2", 0);

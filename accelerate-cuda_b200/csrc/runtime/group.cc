@@ -623,11 +623,19 @@ int accb_group_stencil_iterate(accb_group *g, accb_kernel *k, const accb_array *
             if (pb[r]) GTRY(wait_for(g, r, g->ev_b, (r + 1) % G));
         }
     }
-    int in_b = 0;
+    std::vector<int> in_b(G, 0);
     for (int r = 0; r < G; ++r)
         GTRY(inner(g, r, accb_stencil_iterate(g->ctx[r], k, g->st[r], &a[r], &b[r], iters, boundary, constant,
-                                              constant_bytes, &in_b)));
-    *result_in_b = in_b;
+                                              constant_bytes, &in_b[r])));
+    /* a rank whose slab took another number of launches (a very thin slab runs one application per launch, the
+     * others two) ends in the other buffer: copy, so that the answer is the same buffer on every rank */
+    for (int r = 1; r < G; ++r) {
+        if (in_b[r] == in_b[0]) continue;
+        const accb_array &from = in_b[r] ? b[r] : a[r], &to = in_b[r] ? a[r] : b[r];
+        const size_t n = row_elems[r] * (size_t)from.shape[from.rank - 1];
+        for (int c = 0; c < nc; ++c) GTRY(copy_between(g, r, to.ptr[c], r, from.ptr[c], n * comp_bytes[c]));
+    }
+    *result_in_b = in_b[0];
     return ACCB_OK;
 }
 

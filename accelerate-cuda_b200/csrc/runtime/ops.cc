@@ -895,9 +895,14 @@ static int stencil3_launch(accb_context *ctx, accb_kernel *k, cudaStream_t s, co
     return launch(ctx, pr.fn, "stencil3", grid, pr.block, smem, s, p);
 }
 
+/* `twice`, if not null: the caller would like TWO applications of the stencil from src[0] to out in this one launch;
+ * *twice says whether that is what was launched (the two-application tile form: one source, rank 2, 4-byte elements
+ * of one type, 16-byte aligned rows, any boundary but Wrap) or one application as usual. */
 static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, cudaStream_t s,
                           const accb_array *const *src, int nsrc, int boundary, const void *constant,
-                          size_t constant_bytes, const accb_array *out) {
+                          size_t constant_bytes, const accb_array *out, bool *twice = nullptr) {
+    const bool want_twice = twice && *twice;
+    if (twice) *twice = false;
     if (out && out->rank == 3 && nsrc == 1) return stencil3_launch(ctx, k, s, src[0], boundary, constant, constant_bytes, out);
     if (k->skeleton == SK_STENCIL3) return fail(ctx, ACCB_EINVAL, "kernel %s was built for rank-3 arrays", k->key.c_str());
     if (!out || out->rank < 1 || out->rank > 2) return fail(ctx, ACCB_EINVAL, "stencil2 supports rank 1 and 2, stencil rank 1 to 3");
@@ -944,6 +949,17 @@ static int stencil_launch(accb_context *ctx, accb_kernel *k, const char *entry, 
         p.ip[1] = W;
         return launch(ctx, pl.fn, lentry.c_str(), (int)ceil_div(W, pl.meta.v[5]), pl.block, smem, s, p);
     }
+    if (tiled && want_twice && nsrc == 1 && boundary != ACCB_WRAP && pr.meta.v[8] > 0 && !ctx->tune.stencil_no_fuse) {
+        const size_t smem = (size_t)pr.meta.v[8];
+        Prep pt;
+        TRY(prepare(ctx, k, "stencil_tile2", smem, &pt));
+        p.ip[0] = H;
+        p.ip[1] = W;
+        const long long tiles = ceil_div(W, pr.meta.v[4]) * ceil_div(H, pr.meta.v[9]);
+        if (tiles > 0x7fffffffLL) return fail(ctx, ACCB_EINVAL, "array too large for one stencil launch");
+        *twice = true;
+        return launch(ctx, pt.fn, "stencil_tile2", (int)tiles, pt.block, smem, s, p);
+    }
     if (tiled) {
         const std::string tentry = std::string(entry) + "_tile";
         const size_t smem = (size_t)pr.meta.v[6];
@@ -989,14 +1005,29 @@ int accb_stencil2(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
 int accb_stencil_iterate(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *a,
                          const accb_array *b, int iters, int boundary, const void *constant, size_t constant_bytes,
                          int *result_in_b) {
+    return accb_stencil_iterate_from(ctx, k, stream, nullptr, a, b, iters, boundary, constant, constant_bytes, result_in_b);
+}
+
+int accb_stencil_iterate_from(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *src,
+                              const accb_array *a, const accb_array *b, int iters, int boundary, const void *constant,
+                              size_t constant_bytes, int *result_in_b) {
     LOCK(ctx);
     TRY(check_skeleton(ctx, k, {SK_STENCIL, SK_STENCIL3}, "stencil"));
-    if (!a || !b || iters < 0) return fail(ctx, ACCB_EINVAL, "bad argument");
-    const accb_array *cur = a, *nxt = b;
-    for (int i = 0; i < iters; ++i) {
+    if (!a || !b || iters < 0 || (src && iters < 1)) return fail(ctx, ACCB_EINVAL, "bad argument");
+    /* with a separate source the first launch reads it and writes a; cur is always what the next launch reads */
+    const accb_array *cur = src ? src : a, *nxt = src ? a : b, *spare = src ? b : nullptr;
+    for (int left = iters; left > 0;) {
         const accb_array *srcs[1] = {cur};
-        TRY(stencil_launch(ctx, k, "stencil", (cudaStream_t)stream, srcs, 1, boundary, constant, constant_bytes, nxt));
-        std::swap(cur, nxt);
+        bool twice = left >= 2; /* two applications per launch where the kernel has that form: half the traffic */
+        TRY(stencil_launch(ctx, k, "stencil", (cudaStream_t)stream, srcs, 1, boundary, constant, constant_bytes, nxt, &twice));
+        left -= twice ? 2 : 1;
+        if (spare) { /* the source is never written: from now on ping-pong between a and b */
+            cur = nxt;
+            nxt = spare;
+            spare = nullptr;
+        } else {
+            std::swap(cur, nxt);
+        }
     }
     if (result_in_b) *result_in_b = (cur == b);
     return ACCB_OK;

@@ -275,15 +275,13 @@ int run_internal(accb_program *p, cudaStream_t s, const accb_array *inputs, accb
                     TRY(alloc_value(p, nd.out_id, out, fresh));
                     TRY(accb_stencil(ctx, nd.k, s, &like, nd.boundary, sc, nd.scalars.size(), &out));
                 } else {
-                    /* ping-pong: the final grid must land in `out` */
+                    /* ping-pong between the value's two pooled grids; whichever holds the final grid is the value */
                     accb_array tmp = out;
                     TRY(alloc_value(p, nd.out_id, out, fresh, 0));
                     TRY(alloc_value(p, nd.out_id, tmp, false, 1));
-                    accb_array *dst = (nd.iters % 2) ? &out : &tmp;
-                    accb_array *other = (nd.iters % 2) ? &tmp : &out;
-                    TRY(accb_stencil(ctx, nd.k, s, &like, nd.boundary, sc, nd.scalars.size(), dst));
                     int in_b = 0;
-                    TRY(accb_stencil_iterate(ctx, nd.k, s, dst, other, nd.iters - 1, nd.boundary, sc, nd.scalars.size(), &in_b));
+                    TRY(accb_stencil_iterate_from(ctx, nd.k, s, &like, &out, &tmp, nd.iters, nd.boundary, sc, nd.scalars.size(), &in_b));
+                    if (in_b) out = tmp;
                 }
                 break;
             }
@@ -664,10 +662,8 @@ static int run_host_slabbed(accb_program *p, const accb_array *host_in, accb_arr
                 accb_array a = cur, b = cur;
                 a.ptr[0] = work[2 * (sl & 1) + next_work];
                 b.ptr[0] = work[2 * (sl & 1) + (next_work ^ 1)];
-                TRY(accb_stencil(ctx, nd.k, (accb_stream)comp, &cur, nd.boundary, sc, nd.scalars.size(), &a));
                 int in_b = 0;
-                if (nd.iters > 1)
-                    TRY(accb_stencil_iterate(ctx, nd.k, (accb_stream)comp, &a, &b, nd.iters - 1, nd.boundary, sc, nd.scalars.size(), &in_b));
+                TRY(accb_stencil_iterate_from(ctx, nd.k, (accb_stream)comp, &cur, &a, &b, nd.iters, nd.boundary, sc, nd.scalars.size(), &in_b));
                 cur = in_b ? b : a;
                 next_work = in_b ? next_work : next_work ^ 1; /* the next stencil writes to the grid `cur` is not in */
             }

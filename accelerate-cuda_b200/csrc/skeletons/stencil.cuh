@@ -55,6 +55,12 @@
     ((narr) * (2 * Fn::RY + 1) * (4 + 2 * Fn::RX) <= 20 ? 6                    \
                                                         : ((narr) * (2 * Fn::RY + 1) * (4 + 2 * Fn::RX) <= 40 ? 4 : 3))
 #endif
+#ifndef ACCB_STENCIL_TILE2_RPT
+#define ACCB_STENCIL_TILE2_RPT 6 /* two-application tile form: output rows per thread */
+#endif
+#ifndef ACCB_STENCIL_TILE2_MINB
+#define ACCB_STENCIL_TILE2_MINB 4 /* .. resident blocks per SM to leave registers for */
+#endif
 #ifndef ACCB_STENCIL_TMA_SPIN_LIMIT
 #define ACCB_STENCIL_TMA_SPIN_LIMIT (1 << 16)
 #endif
@@ -521,6 +527,225 @@ __device__ __forceinline__ void stencil_tile_body(const accb_kparams &p) {
     }
 }
 
+/* ------------------------------------------------------------------------
+ * Two applications in one launch (an iterated stencil: the same functor applied again and again, e.g. ten
+ * blurs).  Applied one by one, every application reads and writes the whole grid: 8 bytes per point and
+ * application.  Here a block brings in its tile with TWICE the halo, applies the stencil to it into a second
+ * shared-memory tile (the intermediate grid of the block: its output rows and columns plus one halo), and applies
+ * it again from there: one read and one write of the grid for two applications.
+ * The intermediate tile must look to the second application as the whole intermediate grid would: what lies
+ * outside the array is replaced through the boundary function -- by the intermediate value at the mapped
+ * coordinate for Clamp and Mirror (always inside the same tile), by the constant for Constant.  Wrap maps to the
+ * far side of the grid and is not done this way.  The results are those of two separate applications bit for
+ * bit: the same arithmetic on the same float values, the intermediate rounded to 4 bytes in both cases.
+ * One source, 4-byte elements of one type, radius in x of at most 2.
+ * ---------------------------------------------------------------------- */
+template <class Fn, int CTA>
+struct StencilTile2 {
+    static constexpr int RY = Fn::RY, RX = Fn::RX;
+    static constexpr int TXW = 64, TY = CTA / TXW, RPT = ACCB_STENCIL_TILE2_RPT;
+    static constexpr int RB = TY * RPT, TW = TXW * V, HX = 4, PW = TW + 2 * HX;
+    static constexpr int SRI = RB + 4 * RY; /* rows of the source tile */
+    static constexpr int SRM = RB + 2 * RY; /* rows of the intermediate tile */
+    static constexpr int kSmemBytes = (SRI + SRM) * PW * 4;
+};
+
+/* One tile per block, as in the tile form: the blocks resident on an SM overlap one another's copies and
+ * arithmetic.  (Tried: persistent blocks that walk through tiles with the next tile's copies in flight into a
+ * second source buffer.  Ten applications on 8192 x 8192 took 0.74 ms instead of 0.68 ms: the third tile per block
+ * costs a resident block, and the hardware's block scheduling already overlaps what the loop overlapped by hand.) */
+template <class Fn, int CTA>
+__device__ __forceinline__ void stencil_tile2_body(const accb_kparams &p) {
+    typedef typename Fn::in_t T;
+    typedef StencilTile2<Fn, CTA> G;
+    static_assert(sizeof(T) == 4 && 2 * Fn::RX <= G::HX, "4-byte elements, radius in x of at most 2");
+    constexpr int RY = G::RY, RX = G::RX, WIN = 2 * RY + 1, RW = 4 + 2 * RX;
+    extern __shared__ __align__(128) unsigned char s_raw[];
+    __shared__ __align__(8) unsigned long long s_bar;
+    T(*tin)[G::PW] = reinterpret_cast<T(*)[G::PW]>(s_raw);
+    T(*mid)[G::PW] = reinterpret_cast<T(*)[G::PW]>(s_raw + G::SRI * G::PW * 4);
+
+    const Env env(p);
+    const int H = (int)p.ip[0], W = (int)p.ip[1];
+    const int mode = (int)p.ip[4];
+    Source<T> src;
+    src.base = static_cast<const T *>(p.in[0]);
+    src.h = H;
+    src.w = W;
+    src.mode = mode;
+    src.cval = env.scalar<T>(0);
+    src.vec_ok = true;
+    T *out = static_cast<T *>(p.out[0]);
+    unsigned int *err = static_cast<unsigned int *>(p.aux[1]);
+
+    const int ncg = (W + G::TW - 1) / G::TW;
+    const int x0t = (int)(blockIdx.x % ncg) * G::TW, y0t = (int)(blockIdx.x / ncg) * G::RB;
+    /* source rows y0t - 2RY .. (SRI of them), columns [xs, xe) to tile columns [xs - (x0t - HX), ...) */
+    const int xs = max(0, x0t - G::HX), xe = min(W, x0t + G::TW + G::HX);
+    if (threadIdx.x == 0) {
+        mbar_init(&s_bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (warp_id() == 0) {
+        if (lane_id() == 0) {
+            unsigned total = 0;
+            for (int r = 0; r < G::SRI; ++r)
+                if (bound_coord(y0t - 2 * RY + r, H, mode) >= 0) total += (unsigned)(xe - xs) * 4u;
+            mbar_expect_tx(&s_bar, total);
+        }
+        __syncwarp();
+        for (int r = lane_id(); r < G::SRI; r += 32) {
+            const int yy = bound_coord(y0t - 2 * RY + r, H, mode);
+            if (yy >= 0)
+                bulk_g2s(&tin[r][xs - (x0t - G::HX)], src.base + (long long)yy * W + xs, (unsigned)(xe - xs) * 4u, &s_bar);
+        }
+    }
+    int tries = 0;
+    while (!mbar_try_wait(&s_bar, 0)) {
+        if (++tries > ACCB_STENCIL_TMA_SPIN_LIMIT) { /* bounded: flag the result invalid and go on */
+            atomicExch(err, 1u);
+            break;
+        }
+    }
+    /* patch what the copies could not bring: columns outside the array, rows of a Constant boundary */
+    {
+        const int lo = x0t - 2 * RX, hi = min(x0t + G::TW, W) + 2 * RX; /* columns any tap of the first application may touch */
+        const int nleft = max(0, xs - lo), nright = max(0, hi - xe);
+        const int per_row = nleft + nright;
+        for (int i = threadIdx.x; i < G::SRI * per_row; i += CTA) {
+            const int r = i / per_row, j = i - r * per_row;
+            const int c = j < nleft ? lo + j : xe + (j - nleft);
+            tin[r][c - (x0t - G::HX)] = src.at(bound_coord(y0t - 2 * RY + r, H, mode), c);
+        }
+        if (mode == B_CONSTANT) {
+            for (int r = 0; r < G::SRI; ++r) {
+                if (bound_coord(y0t - 2 * RY + r, H, mode) >= 0) continue; /* uniform per block */
+                for (int c = threadIdx.x; c < G::PW; c += CTA) tin[r][c] = src.cval;
+            }
+        }
+    }
+    __syncthreads();
+
+    const int tx = threadIdx.x % G::TXW, ty = threadIdx.x / G::TXW;
+    const int sc = G::HX + tx * V; /* tile column of the thread's first centre column */
+    /* a thread's part of tile row r: its own 4 columns by one 16-byte read, the RX columns either side by 4-byte
+     * reads (taking them from the neighbouring lanes by shuffle instead measured slower here: 0.72 ms against
+     * 0.69 ms for ten applications on 8192 x 8192 -- the kernel is bound by instruction issue) */
+    auto row = [&](const T(*tile)[G::PW], int r, T(&d)[RW]) {
+        const T *q = &tile[r][sc];
+        T c[V];
+        load4<Cache::Default>(q, 0, c);
+#pragma unroll
+        for (int k = 0; k < V; ++k) d[RX + k] = c[k];
+#pragma unroll
+        for (int k = 0; k < RX; ++k) {
+            d[k] = q[k - RX];
+            d[RX + V + k] = q[V + k];
+        }
+    };
+    auto apply4 = [&](T(&win)[WIN][RW], int first, T(&o)[V]) { /* window row dy is win[(first + dy) % WIN] */
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            T t[WIN][2 * RX + 1];
+#pragma unroll
+            for (int dy = 0; dy < WIN; ++dy)
+#pragma unroll
+                for (int dx = 0; dx < 2 * RX + 1; ++dx) t[dy][dx] = win[(first + dy) % WIN][k + dx];
+            o[k] = Fn::apply(env, t);
+        }
+    };
+
+    /* ---- first application: intermediate row m is row y0t - RY + m of the grid and reads source tile rows
+     * m .. m + 2RY; the threads' own 4 columns each, the intermediate rows dealt to the TY thread rows */
+    {
+        constexpr int R1 = (G::SRM + G::TY - 1) / G::TY;
+        const int m0 = ty * R1;
+        T win[WIN][RW];
+#pragma unroll
+        for (int s2 = 0; s2 < WIN - 1; ++s2)
+            if (m0 + s2 < G::SRI) row(tin, m0 + s2, win[s2]);
+#pragma unroll
+        for (int u = 0; u < R1; ++u) {
+            const int m = m0 + u;
+            if (m >= G::SRM) break;
+            row(tin, m + 2 * RY, win[(u + 2 * RY) % WIN]);
+            T o[V];
+            apply4(win, u, o);
+            store4<Cache::Default>(&mid[m][sc], 0, o);
+        }
+        /* the RX columns either side of the tile's own */
+        if constexpr (RX > 0) {
+            for (int i = threadIdx.x; i < G::SRM * 2 * RX; i += CTA) {
+                const int m = i / (2 * RX), h = i - m * (2 * RX);
+                const int c = h < RX ? G::HX - RX + h : G::HX + G::TW + (h - RX); /* tile column */
+                T t[WIN][2 * RX + 1];
+#pragma unroll
+                for (int dy = 0; dy < WIN; ++dy)
+#pragma unroll
+                    for (int dx = 0; dx < 2 * RX + 1; ++dx) t[dy][dx] = tin[m + dy][c + dx - RX];
+                mid[m][c] = Fn::apply(env, t);
+            }
+        }
+    }
+    __syncthreads();
+    /* intermediate values at coordinates outside the array (tiles along the array's edges only): what the
+     * boundary function makes of them */
+    if (y0t - RY < 0 || y0t + G::RB + RY > H || x0t - RX < 0 || x0t + G::TW + RX > W) { /* the same for the whole block */
+        constexpr int MW = G::TW + 2 * RX;
+        for (int i = threadIdx.x; i < G::SRM * MW; i += CTA) {
+            const int m = i / MW, cc = i - m * MW;
+            const int y = y0t - RY + m, c = x0t - RX + cc;
+            if (y >= 0 && y < H && c >= 0 && c < W) continue;
+            if (y < -RY || y >= H + RY || c < -RX || c >= W + RX) continue; /* nothing reads it */
+            const int yy = bound_coord(y, H, mode), xx = bound_coord(c, W, mode);
+            /* the mapped coordinate is inside the array and inside this tile: computed above, never patched here */
+            const bool inside = yy >= 0 && yy < H && xx >= 0 && xx < W;
+            mid[m][cc + G::HX - RX] = inside ? mid[yy - (y0t - RY)][xx - (x0t - G::HX)] : src.cval;
+        }
+        __syncthreads();
+    }
+
+    /* ---- second application: as the tile form, out of the intermediate tile */
+    const int x = x0t + tx * V;
+    if (x >= W) return;
+    T win[WIN][RW];
+#pragma unroll
+    for (int s2 = 0; s2 < WIN - 1; ++s2) row(mid, ty * G::RPT + s2, win[s2]);
+    const bool vec_store = x + V <= W;
+#pragma unroll
+    for (int u = 0; u < G::RPT; ++u) {
+        const int yo = y0t + ty * G::RPT + u;
+        if (yo >= H) break;
+        row(mid, ty * G::RPT + u + 2 * RY, win[(u + 2 * RY) % WIN]);
+        T o[V];
+        apply4(win, u, o);
+        if (vec_store) {
+            store4<Cache::Stream>(out + (long long)yo * W + x, 0, o);
+        } else {
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                if (x + k < W) out[(long long)yo * W + x + k] = o[k];
+        }
+    }
+}
+
+template <class Fn, int CTA>
+__host__ __device__ constexpr bool stencil_tile2_ok() {
+    return sizeof(typename Fn::in_t) == 4 && std::is_same<typename Fn::in_t, typename Fn::out_t>::value && 2 * Fn::RX <= 4;
+}
+template <class Fn, int CTA>
+__device__ __forceinline__ void stencil_tile2_or_nothing(const accb_kparams &p) {
+    if constexpr (stencil_tile2_ok<Fn, CTA>()) stencil_tile2_body<Fn, CTA>(p);
+}
+template <class Fn, int CTA>
+__host__ __device__ constexpr int stencil_tile2_smem() {
+    if constexpr (stencil_tile2_ok<Fn, CTA>())
+        return StencilTile2<Fn, CTA>::kSmemBytes;
+    else
+        return 0;
+}
+
 /* ----------------------------------------------------------------------
  * Line form: rank-1 arrays.  A block's tile is a run of CTA * 4 * RPT
  * elements plus 4 halo elements each side, brought into shared memory by ONE
@@ -688,13 +913,16 @@ __host__ __device__ constexpr int stencil_tile_dim(int which) {
  * launches `stencil_tile` / `stencil2_tile` (rank 2) or `stencil_line` /
  * `stencil2_line` (rank 1) instead when their conditions hold.
  * Metadata: {.., element bytes, rows per tile, columns per tile, outputs per
- * tile of the line form, dynamic shared memory of the tile form, rows the stencil reaches up and down}. */
+ * tile of the line form, dynamic shared memory of the tile form, rows the stencil reaches up and down,
+ * dynamic shared memory of the two-application form (0: not available), its rows per tile}. */
 #define ACCB_STENCIL_ENTRIES(Fn, id, narr, name, tname, lname)                                 \
-    ACCB_META8(id, ACCB_STENCIL_CTA, sizeof(Fn::in_t),                                         \
-               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(1)),                        \
-               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(2)),                        \
-               (accb::stencil_line_len<Fn, ACCB_STENCIL_CTA>()),                               \
-               (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(0)), Fn::RY)                \
+    ACCB_META12(id, ACCB_STENCIL_CTA, sizeof(Fn::in_t),                                        \
+                (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(1)),                       \
+                (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(2)),                       \
+                (accb::stencil_line_len<Fn, ACCB_STENCIL_CTA>()),                              \
+                (accb::stencil_tile_dim<Fn, narr, ACCB_STENCIL_CTA>(0)), Fn::RY,               \
+                ((narr) == 1 ? accb::stencil_tile2_smem<Fn, ACCB_STENCIL_CTA>() : 0),          \
+                (ACCB_STENCIL_CTA / 64 * ACCB_STENCIL_TILE2_RPT), 0, 0)                        \
     extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_MINB)          \
         name(const __grid_constant__ accb_kparams p) {                                         \
         accb::stencil_body<Fn, narr, ACCB_STENCIL_CTA>(p);                                     \
@@ -708,5 +936,10 @@ __host__ __device__ constexpr int stencil_tile_dim(int which) {
         accb::stencil_line_or_nothing<Fn, narr, ACCB_STENCIL_CTA>(p);                          \
     }
 
-#define ACCB_INSTANTIATE_STENCIL(Fn) ACCB_STENCIL_ENTRIES(Fn, 8, 1, stencil, stencil_tile, stencil_line)
+#define ACCB_INSTANTIATE_STENCIL(Fn)                                                           \
+    ACCB_STENCIL_ENTRIES(Fn, 8, 1, stencil, stencil_tile, stencil_line)                        \
+    extern "C" __global__ void __launch_bounds__(ACCB_STENCIL_CTA, ACCB_STENCIL_TILE2_MINB)    \
+        stencil_tile2(const __grid_constant__ accb_kparams p) {                                \
+        accb::stencil_tile2_or_nothing<Fn, ACCB_STENCIL_CTA>(p);                               \
+    }
 #define ACCB_INSTANTIATE_STENCIL2(Fn) ACCB_STENCIL_ENTRIES(Fn, 9, 2, stencil2, stencil2_tile, stencil2_line)

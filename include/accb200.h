@@ -284,6 +284,15 @@ ACCB_API int accb_stencil2(accb_context *ctx, accb_kernel *k, accb_stream stream
 ACCB_API int accb_stencil_iterate(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *a,
                                   const accb_array *b, int iters, int boundary, const void *constant,
                                   size_t constant_bytes, int *result_in_b);
+/* The same with a source of its own that is only read: the first launch goes from `src` to a, the rest ping-pong
+ * between a and b (iters >= 1).  Where the kernel has the form (rank 2, one 4-byte element type, 16-byte aligned
+ * rows of a multiple of 4 elements, any boundary but Wrap), a launch does TWO applications -- the intermediate grid
+ * of a block never leaves shared memory -- so an iterated stencil reads and writes the grid once per two
+ * applications; the results are those of one application per launch bit for bit.  accb_stencil_iterate does the
+ * same from a. */
+ACCB_API int accb_stencil_iterate_from(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *src,
+                                       const accb_array *a, const accb_array *b, int iters, int boundary,
+                                       const void *constant, size_t constant_bytes, int *result_in_b);
 
 /* -------------------------------------- whole programs (AccFFI.h surface)
  * Same struct layouts and entry points as include/AccFFI.h:10-30.  An

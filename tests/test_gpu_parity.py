@@ -450,6 +450,44 @@ def test_fold_seg_long_segments_in_rows_and_with_two_inputs(ctx, P, torch_cuda, 
     close(of.cpu().numpy(), np.add.reduceat(prod, offs[:-1]) * (nnz > 0), 1e-6)
 
 
+@pytest.fixture(scope="module")
+def ctx_one_application_per_launch(accb, torch_cuda):
+    """A context whose iterated stencils never fuse two applications into one launch (tuning is read when a
+    context is made)."""
+    import os
+    os.environ["ACCB_STENCIL_NO_FUSE"] = "1"
+    try:
+        c = accb.Context(0)
+    finally:
+        del os.environ["ACCB_STENCIL_NO_FUSE"]
+    yield c
+    c.sync()
+
+
+@pytest.mark.parametrize("shape", [(16, 256), (33, 260), (100, 516), (257, 1024), (64, 252)])
+@pytest.mark.parametrize("boundary", ["clamp", "mirror", "constant", "wrap"])
+@pytest.mark.parametrize("prog,iters", [("BLUR", 2), ("BLUR", 7), ("LAPLACE", 4), ("BOX5", 3)])
+def test_two_applications_per_launch_equal_one_by_one(ctx, ctx_one_application_per_launch, P, torch_cuda, rng, shape, boundary,
+                                                      prog, iters):
+    """An iterated stencil runs two applications per launch where it can (the intermediate grid of a block stays
+    in shared memory): bit-identical to one application per launch, for tiles along every edge and corner, widths
+    that are not whole tiles, odd counts (the last application goes alone) and a 5x5 neighbourhood (radius 2)."""
+    t = torch_cuda
+    g = rng.uniform(-1, 1, shape).astype(np.float32)
+    const = np.float32(0.5)
+    outs = []
+    for c in (ctx, ctx_one_application_per_launch):
+        a, b = dev(t, g), t.empty(shape, dtype=t.float32, device="cuda")
+        before = c.launch_count()
+        r = c.stencil_iterate(getattr(P, prog), a, b, iters, boundary=boundary, constant=const)
+        c.sync()
+        outs.append((r.cpu().numpy(), c.launch_count() - before))
+    assert np.array_equal(outs[0][0], outs[1][0])
+    assert outs[1][1] == iters
+    if boundary != "wrap" and shape[1] % 4 == 0:
+        assert outs[0][1] == (iters + 1) // 2  # pairs, and the odd one out
+
+
 # ------------------------------------------------------------------ scans
 def test_scan_known_answers_from_the_reference_docs(ctx, P, accb, torch_cuda):
     """CodeGen/PrefixSum.hs:149-153, 162-166, 176-180."""
