@@ -30,7 +30,7 @@ module Data.Array.Accelerate.B200.FFI (
 
   -- * Single launches on device arrays
   c_map, c_foldAll, c_foldDim, c_foldSeg, c_scan, c_permuteDefaults, c_permute,
-  c_stencil, c_stencil2, c_stencilIterate,
+  c_stencil, c_stencil2, c_stencilIterate, c_stencilIterateFrom,
 
   -- * Memory table
   c_malloc, c_use, c_insertUnmanaged, c_withPtr, c_release, c_releaseAfter,
@@ -168,6 +168,10 @@ foreign import ccall safe "accb_stencil2"
 foreign import ccall safe "accb_stencil_iterate"
   c_stencilIterate :: Ptr AccbContext -> Ptr AccbKernel -> Stream -> Ptr AccbArray -> Ptr AccbArray -> CInt -> CInt
                    -> Ptr () -> CSize -> Ptr CInt -> IO Status
+-- the same from a source that is only read; two applications per launch where the kernel has that form
+foreign import ccall safe "accb_stencil_iterate_from"
+  c_stencilIterateFrom :: Ptr AccbContext -> Ptr AccbKernel -> Stream -> Ptr AccbArray -> Ptr AccbArray -> Ptr AccbArray
+                       -> CInt -> CInt -> Ptr () -> CSize -> Ptr CInt -> IO Status
 
 -- memory table: malloc / withRemote / insertUnmanaged / free / reclaim (CUDA/Array/Remote.hs:91-202),
 -- peek / poke (CUDA/Array/Prim.hs:189-391).  Keys are the hash of the host array's StableName.
