@@ -447,13 +447,16 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
     TRY(prepare(ctx, k, entry, 0, &pr));
     /* Segments far longer than the rest (64 K elements where a thread, a warp or a few lanes own a segment, 1 M
      * where a block does) go on a list, and a second launch reduces them with all blocks; without it one such
-     * segment keeps a single warp or block busy long after the launch would have ended.  Only sources of 4 M
-     * elements and more get the second launch (it costs about three microseconds when the list stays empty). */
+     * segment keeps a single warp or block busy long after the launch would have ended.  Only sources of 16 M
+     * elements and more get the second launch (it costs about three microseconds when the list stays empty), and
+     * smaller ones of at least 1 M when a block owns a segment and there are too few segments to fill the GPU. */
     cudaStream_t s = (cudaStream_t)stream;
     StreamScratch *sc = scratch_for(ctx, s);
     if (!sc) return fail(ctx, ACCB_ENOMEM, "cannot allocate stream scratch");
     const long long piece = pr.meta.v[7];
-    const bool defer = !ctx->tune.foldseg_no_defer && piece > 0 && cols >= (1LL << 22);
+    /* few segments under the block-per-segment form: the blocks cannot fill the GPU, every long segment is worth handing over */
+    const bool starved = group > 32 && rows * nseg < 4LL * ctx->sm_count * pr.per_sm;
+    const bool defer = !ctx->tune.foldseg_no_defer && piece > 0 && (cols >= (1LL << 24) || (starved && cols >= (1LL << 20)));
     /* everything that can fail is done before the first launch: a list left behind by a launch whose second half
      * never ran would be reduced, with the wrong arrays, by the next foldSeg on this stream */
     Prep pd;
@@ -472,8 +475,7 @@ int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const a
         return st;
     };
     if (defer) {
-        /* a block per segment fills the GPU only with enough segments: with fewer, every long one is handed over */
-        p.ip[6] = (group > 32 && rows * nseg >= 4LL * ctx->sm_count * pr.per_sm) ? (1LL << 20) : (1LL << 16);
+        p.ip[6] = (group > 32 && !starved) ? (1LL << 20) : (1LL << 16);
         p.aux[2] = sc->words + kDeferredBase;
     }
     if (avg <= ctx->tune.foldseg_stage_max && rows * nseg >= 4096 && (rows == 1 || cols % 16 == 0) && pr.meta.v[6] > 0 &&

@@ -730,7 +730,7 @@ class SmvmWorkload(Workload):
     def step(self):
         self.ctx.fold_seg(self.k, [(self.vals, self.colidx), self.vec], 1, self.nnz, self.offs, self.rows, self.out,
                           seed=np.float32(0))
-        return 2 if self.nnz >= (1 << 22) else 1  # sources of 2^22 elements and more get the second launch
+        return 2 if self.nnz >= (1 << 24) else 1  # sources of 2^24 elements and more get the second launch
 
     def verify(self):
         t = self.t
@@ -782,7 +782,7 @@ class FoldSegWorkload(Workload):
 
     def step(self):
         self.ctx.fold_seg(self.k, [self.x], 1, self.n, self.offs, self.nseg, self.out, seed=np.int32(0))
-        return 2 if self.n >= (1 << 22) else 1  # sources of 2^22 elements and more get the second launch
+        return 2 if self.n >= (1 << 24) else 1  # sources of 2^24 elements and more get the second launch
 
     def verify(self):
         t = self.t

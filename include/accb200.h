@@ -186,8 +186,9 @@ ACCB_API int accb_fold_dim(accb_context *ctx, accb_kernel *k, accb_stream stream
                            const accb_array *out);
 /* offsets: Int32 device array of nseg+1 exclusive-scanned segment lengths.  Segments may have any length: where a
  * thread, a warp or a block owns a segment, one that is far longer than the rest (65536 elements, or 2^20 under a
- * block) is put on a device-side list instead, and for sources of 2^22 elements and more a second launch cuts the
- * listed segments into pieces for all blocks -- about three microseconds when the list stays empty. */
+ * block) is put on a device-side list instead, and for sources of 2^24 elements and more (2^20 when there are too
+ * few segments to fill the GPU with a block each) a second launch cuts the listed segments into pieces for all
+ * blocks -- about three microseconds when the list stays empty. */
 ACCB_API int accb_fold_seg(accb_context *ctx, accb_kernel *k, accb_stream stream, const accb_array *env,
                            int nenv, long long rows, long long cols, const int *offsets, long long nseg,
                            const void *seed, size_t seed_bytes, const accb_array *out);

@@ -377,7 +377,7 @@ def _seg_ref(x, offs, seed):
                                   "all_empty", "ragged_tail", "many_empty_runs"])
 def test_fold_seg_segments_of_any_length(ctx, P, torch_cuda, rng, case):
     """Segments that end exactly on multiples of 32 and 4096 elements, one segment of 4.5 M elements, segments of
-    hundreds of thousands of elements among 600000 short ones (sources of 2^22 elements and more hand segments
+    a million and more elements among 2.6 million short ones (sources of 2^24 elements and more hand segments
     longer than 65536 elements over to a second launch that splits them over all blocks), offsets that cover only
     the middle of the source, empty segments first, last and in runs, no elements at all."""
     t = torch_cuda
@@ -388,8 +388,8 @@ def test_fold_seg_segments_of_any_length(ctx, P, torch_cuda, rng, case):
     elif case == "one_giant":
         lens = np.array([0, 1100 * T + 5, 0])
     elif case == "giant_among_short":
-        lens = rng.integers(0, 12, 600000)
-        lens[[100, 20000, 599999]] = [150 * T + 1, 3 * T, 190 * T - 7]
+        lens = rng.integers(0, 12, 2600000)
+        lens[[100, 20000, 2599999]] = [450 * T + 1, 3 * T, 390 * T - 7]
     elif case == "offsets_inside":
         lens = rng.integers(0, 30, 3000)
         pad_front, pad_back = 5000, 7003
@@ -436,7 +436,7 @@ def test_fold_seg_long_segments_in_rows_and_with_two_inputs(ctx, P, torch_cuda, 
     ctx.sync()
     ref = np.stack([_seg_ref(m[r], offs, 1) for r in range(3)])
     assert np.array_equal(out.cpu().numpy().astype(np.int64), ref)
-    nnz = rng.integers(0, 120, 60000)
+    nnz = rng.integers(0, 120, 270000)
     nnz[[5, 3000]] = [900000, 70001]
     offs = np.concatenate([[0], np.cumsum(nnz)]).astype(np.int32)
     vals = rng.uniform(-1, 1, int(offs[-1])).astype(np.float32)

@@ -178,11 +178,11 @@ def test_program_as_one_cuda_graph_replays_on_new_contents(accb, ctx, torch_cuda
 
 
 def test_fold_seg_with_a_long_segment_inside_a_cuda_graph(accb, P, ctx, torch_cuda, rng):
-    """A foldSeg over 5 M elements records two launches (the second one splits the segments that the first one put
+    """A foldSeg over 18 M elements records two launches (the second one splits the segments that the first one put
     on its list over all blocks); replays follow the arrays' new contents, also when another segment becomes the
     long one."""
     t = torch_cuda
-    nseg = 40000
+    nseg = 300000
     f = accb.run1With(ctx, lambda v, o: accb.fold_seg(P.SEGSUM_I32, [v], o, np.int32, seed=np.int32(2)),
                       accb.ArrayType(1, np.int32), accb.ArrayType(1, np.int32))
     lens = rng.integers(0, 100, nseg)
@@ -196,7 +196,7 @@ def test_fold_seg_with_a_long_segment_inside_a_cuda_graph(accb, P, ctx, torch_cu
             x.add_(1)
         if rep == 2:  # the long segment moves: same arrays, other contents
             lens2 = lens.copy()
-            lens2[777], lens2[31000] = lens[31000], lens[777]
+            lens2[777], lens2[231000] = lens[231000], lens[777]
             offs.copy_(t.from_numpy(np.concatenate([[0], np.cumsum(lens2)]).astype(np.int32)))
         t.cuda.synchronize()
         before = ctx.launch_count()
