@@ -182,6 +182,33 @@ def test_group_iterated_blur_with_one_halo_exchange(group, P, torch_cuda, oracle
     close(got, oracle.stencil2d_iter(a, workloads.BLUR_WEIGHTS, iters, boundary, 0.25), 1e-6)
 
 
+def test_group_stencil_slabs_that_take_different_numbers_of_launches(group, P, torch_cuda, oracle, workloads, rng):
+    """A slab of 16 rows and more runs two applications per launch, a thinner one runs them one by one, so the ranks
+    end in different buffers of their pairs: the answer is still the same-named buffer on every rank."""
+    t, G = torch_cuda, group.size
+    if G < 2:
+        pytest.skip("one rank has one slab")
+    iters, w = 3, 256
+    rows = [24] + [9] * (G - 1)  # rank 0: 24 + 3 halo rows; the others 3 + 9 (+ 3): fewer than 16 only for the last
+    h = sum(rows)
+    a = rng.uniform(0, 1, (h, w)).astype(np.float32)
+    c = np.concatenate([[0], np.cumsum(rows)])
+    pads = [group.stencil_layout(r, iters, 1, "clamp") for r in range(G)]
+    A, B = [], []
+    for r in range(G):
+        pt, pb = pads[r]
+        slab = np.full((pt + rows[r] + pb, w), np.nan, np.float32)
+        slab[pt:pt + rows[r]] = a[c[r]:c[r + 1]]
+        A.append(put(t, slab, group.devices[r]))
+        B.append(t.empty_like(A[-1]))
+    assert A[0].shape[0] >= 16 and A[-1].shape[0] < 16
+    sync_all(t)
+    res = group.stencil_iterate(P.BLUR, A, B, rows, iters, 1, "clamp")
+    group.sync()
+    got = np.concatenate([res[r].cpu().numpy()[pads[r][0]:pads[r][0] + rows[r]] for r in range(G)])
+    close(got, oracle.stencil2d_iter(a, workloads.BLUR_WEIGHTS, iters, "clamp"), 1e-6)
+
+
 @pytest.mark.parametrize("boundary", ["clamp", "mirror", "wrap", "constant"])
 @pytest.mark.parametrize("iters", [1, 3])
 def test_group_iterated_stencil_over_a_cube_cut_into_slabs_of_planes(group, P, torch_cuda, oracle, rng, boundary, iters):
