@@ -81,6 +81,21 @@ def test_integer_arithmetic_follows_the_reference_c_forms():
         assert piece in g, piece
 
 
+def test_cube_stencil_functors_declare_the_taps_they_read():
+    """The functor printed for a rank-3 stencil carries `uses`: true exactly for the taps the function reads, so
+    that the skeleton can skip the rows and halo columns nobody reads."""
+    seven = lambda t: (t[0][1][1] + t[2][1][1] + t[1][0][1] + t[1][2][1] + t[1][1][0] + t[1][1][2]) - 6.0 * t[1][1][1]  # noqa: E731
+    spec = A.specs(lambda a: A.stencil(seven, "clamp", a), A.array(3, f32))[0]
+    assert spec.skeleton == "stencil3" and "static constexpr bool uses(int z, int y, int x)" in spec.source
+    table = spec.source.split("constexpr bool read[3][3][3] = ")[1].split(";")[0]
+    assert table.count("true") == 7 and table.count("false") == 20
+    flat = [w == "true" for w in table.replace("{", " ").replace("}", " ").replace(",", " ").split()]
+    assert [i for i, u in enumerate(flat) if u] == [4, 10, 12, 13, 14, 16, 22]  # (z * 3 + y) * 3 + x
+    every = lambda t: sum((t[z][y][x] for z in range(3) for y in range(3) for x in range(3)), A.constant(0, f32))  # noqa: E731
+    full = A.specs(lambda a: A.stencil(every, "clamp", a), A.array(3, f32))[0].source
+    assert full.split("constexpr bool read[3][3][3] = ")[1].split(";")[0].count("false") == 0
+
+
 def test_the_language_is_typed_like_accelerate():
     with pytest.raises(TypeError):
         A.specs(lambda x, y: A.zipWith(add, x, y), A.vector(f32), A.vector(i32))  # Float + Int
